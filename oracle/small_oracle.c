@@ -1,0 +1,406 @@
+/*
+ * small_oracle.c -- CPU restatement of SMaLL's layer semantics (TEST INFRASTRUCTURE,
+ * see small_oracle.h).  Compile with -ffp-contract=off so that a*b+c is a separate
+ * multiply and add, as in the reference's REF build (CMakeLists.txt:57-58,104-108: no
+ * -mfma on the REF platform).
+ *
+ * The reference expresses every layer as one loop nest
+ * (include/small/abstract_layer.hpp:1368-1823) with separate edge kernels for output
+ * pixels whose window touches padding.  The restatement below computes each output
+ * element directly; what it keeps from the loop nest is
+ *   - the order in which terms are added: input-channel block, kernel row, kernel
+ *     column, channel inside the block (abstract_layer.hpp:1630, :542-563);
+ *   - padded taps are skipped, never multiplied by zero (compute_with_padding,
+ *     abstract_layer.hpp:205-239);
+ *   - a pixel is a "border" pixel when its window leaves the image; border pixels of
+ *     a max pool start from 0, interior ones from their first tap
+ *     (abstract_layer.hpp:515-523, :333, :720, :887).
+ */
+#include "small_oracle.h"
+
+#include <math.h>
+#include <stddef.h>
+#include <stdlib.h>
+
+int32_t so_out_dim(int32_t in, int32_t pad_front, int32_t pad_back, int32_t f, int32_t stride)
+{
+    /* include/small/utils.hpp:159-165 on the padded extent (abstract_layer.hpp:1449-1452) */
+    int32_t o = (in + pad_front + pad_back - f) / stride + 1;
+    return o > 0 ? o : 0;
+}
+
+void so_calc_padding(int32_t in, int32_t f, int32_t stride, int32_t *front, int32_t *back)
+{
+    /* include/small/utils.hpp:43-64 */
+    int32_t p;
+    if (in % stride == 0)
+        p = (f > stride) ? f - stride : 0;
+    else
+        p = (f > (in % stride)) ? f - (in % stride) : 0;
+    *front = p / 2;
+    *back  = p - *front;
+}
+
+/* First-layer exception: buffers.hpp:52-57, interface_abstract.hpp:106-214. */
+static int32_t eff_cib(int32_t C, int32_t cib)
+{
+    return (C < cib && (C == 1 || C == 2 || C == 3)) ? C : cib;
+}
+
+static inline size_t act_idx(int32_t H, int32_t W, int32_t cb, int32_t c, int32_t h, int32_t w)
+{
+    /* buffers.hpp:115-119 */
+    return (size_t)(c / cb) * H * W * cb + (size_t)h * W * cb + (size_t)w * cb + (c % cb);
+}
+
+static inline float apply_act(float v, int act, float slope)
+{
+    if (act == 1)
+        return v > 0.f ? v : 0.f; /* FLOAT_MAX_TILE_C against a zeroed tile */
+    if (act == 2)
+        return v > 0.f ? v : v * slope; /* FLOAT_COND_SCALE_TILE_C, intrinsics_float.h:423-439 */
+    return v;
+}
+
+/* ---------------------------------------------------------------- float conv */
+void so_conv2d_f32(const so_shape *s, const float *in, const float *filt,
+                   const float *bias, int act, float slope, int accumulate, float *out)
+{
+    const int32_t cib = eff_cib(s->C, s->cib), cob = s->cob;
+    const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
+    const int32_t Wo = so_out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    const int32_t ncb = s->C / cib;
+    for (int32_t k = 0; k < s->K; ++k)
+        for (int32_t oh = 0; oh < Ho; ++oh)
+            for (int32_t ow = 0; ow < Wo; ++ow)
+            {
+                const size_t oi = act_idx(Ho, Wo, cob, k, oh, ow);
+                float acc = accumulate ? out[oi] : 0.f;
+                if (bias)
+                    acc = acc + bias[k];
+                for (int32_t b = 0; b < ncb; ++b)
+                    for (int32_t kh = 0; kh < s->Fh; ++kh)
+                    {
+                        const int32_t ih = oh * s->stride - s->pad_t + kh;
+                        if (ih < 0 || ih >= s->H)
+                            continue;
+                        for (int32_t kw = 0; kw < s->Fw; ++kw)
+                        {
+                            const int32_t iw = ow * s->stride - s->pad_l + kw;
+                            if (iw < 0 || iw >= s->W)
+                                continue;
+                            const float *a = in + ((size_t)b * s->H * s->W + (size_t)ih * s->W + iw) * cib;
+                            /* packed_weight_index, buffers.hpp:69-78 */
+                            const float *f = filt + ((((size_t)(k / cob) * ncb + b) * s->Fh + kh) * s->Fw + kw) * cib * cob + (k % cob);
+                            for (int32_t c = 0; c < cib; ++c)
+                                acc = acc + a[c] * f[(size_t)c * cob];
+                        }
+                    }
+                out[oi] = apply_act(acc, act, slope);
+            }
+}
+
+void so_dwconv2d_f32(const so_shape *s, const float *in, const float *filt,
+                     const float *bias, int act, float slope, int accumulate, float *out)
+{
+    /* interface_abstract.hpp:994-1057: G_b = C_ob, K_b = F_cb = 1, op_class 1 */
+    const int32_t cb = s->cob;
+    const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
+    const int32_t Wo = so_out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    for (int32_t c = 0; c < s->C; ++c)
+        for (int32_t oh = 0; oh < Ho; ++oh)
+            for (int32_t ow = 0; ow < Wo; ++ow)
+            {
+                const size_t oi = act_idx(Ho, Wo, cb, c, oh, ow);
+                float acc = accumulate ? out[oi] : 0.f;
+                if (bias)
+                    acc = acc + bias[c];
+                for (int32_t kh = 0; kh < s->Fh; ++kh)
+                {
+                    const int32_t ih = oh * s->stride - s->pad_t + kh;
+                    if (ih < 0 || ih >= s->H)
+                        continue;
+                    for (int32_t kw = 0; kw < s->Fw; ++kw)
+                    {
+                        const int32_t iw = ow * s->stride - s->pad_l + kw;
+                        if (iw < 0 || iw >= s->W)
+                            continue;
+                        const float a = in[act_idx(s->H, s->W, cb, c, ih, iw)];
+                        const float f = filt[(((size_t)(c / cb) * s->Fh + kh) * s->Fw + kw) * cb + (c % cb)];
+                        acc = acc + a * f;
+                    }
+                }
+                out[oi] = apply_act(acc, act, slope);
+            }
+}
+
+/* ---------------------------------------------------------------- float pools */
+static int window_is_interior(const so_shape *s, int32_t oh, int32_t ow)
+{
+    const int32_t h0 = oh * s->stride - s->pad_t, w0 = ow * s->stride - s->pad_l;
+    return h0 >= 0 && w0 >= 0 && h0 + s->Fh <= s->H && w0 + s->Fw <= s->W;
+}
+
+void so_maxpool2d_f32(const so_shape *s, const float *in, float *out)
+{
+    const int32_t cb = s->cob;
+    const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
+    const int32_t Wo = so_out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    for (int32_t c = 0; c < s->C; ++c)
+        for (int32_t oh = 0; oh < Ho; ++oh)
+            for (int32_t ow = 0; ow < Wo; ++ow)
+            {
+                const int32_t h0 = oh * s->stride - s->pad_t, w0 = ow * s->stride - s->pad_l;
+                float m = 0.f; /* border pixels: the tile is zeroed first */
+                if (window_is_interior(s, oh, ow))
+                    m = in[act_idx(s->H, s->W, cb, c, h0, w0)]; /* FLOAT_LOAD_TILE_C_strided */
+                for (int32_t kh = 0; kh < s->Fh; ++kh)
+                    for (int32_t kw = 0; kw < s->Fw; ++kw)
+                    {
+                        const int32_t ih = h0 + kh, iw = w0 + kw;
+                        if (ih < 0 || ih >= s->H || iw < 0 || iw >= s->W)
+                            continue;
+                        const float a = in[act_idx(s->H, s->W, cb, c, ih, iw)];
+                        m = (a > m) ? a : m; /* FLOAT_MAX_TILE_C, intrinsics_float.h:306-321 */
+                    }
+                out[act_idx(Ho, Wo, cb, c, oh, ow)] = m;
+            }
+}
+
+void so_avgpool2d_f32(const so_shape *s, const float *in, float *out)
+{
+    const int32_t cb = s->cob;
+    const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
+    const int32_t Wo = so_out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    /* abstract_layer.hpp:565-569: always 1/(Fh*Fw), padded taps included in the count */
+    const float norm = (float)(1.0 / (1.0 * s->Fh * s->Fw));
+    for (int32_t c = 0; c < s->C; ++c)
+        for (int32_t oh = 0; oh < Ho; ++oh)
+            for (int32_t ow = 0; ow < Wo; ++ow)
+            {
+                const int32_t h0 = oh * s->stride - s->pad_t, w0 = ow * s->stride - s->pad_l;
+                float acc = 0.f;
+                for (int32_t kh = 0; kh < s->Fh; ++kh)
+                    for (int32_t kw = 0; kw < s->Fw; ++kw)
+                    {
+                        const int32_t ih = h0 + kh, iw = w0 + kw;
+                        if (ih < 0 || ih >= s->H || iw < 0 || iw >= s->W)
+                            continue;
+                        acc = acc + in[act_idx(s->H, s->W, cb, c, ih, iw)];
+                    }
+                out[act_idx(Ho, Wo, cb, c, oh, ow)] = acc * norm;
+            }
+}
+
+/* ---------------------------------------------------------------- float elementwise */
+void so_relu_f32(int64_t n, const float *in, float *out)
+{
+    for (int64_t i = 0; i < n; ++i)
+        out[i] = in[i] > 0.f ? in[i] : 0.f;
+}
+
+void so_leaky_relu_f32(int64_t n, const float *in, float slope, float *out)
+{
+    for (int64_t i = 0; i < n; ++i)
+        out[i] = in[i] > 0.f ? in[i] : in[i] * slope;
+}
+
+void so_accum_f32(int64_t n, const float *in, float *out)
+{
+    /* interface_abstract.hpp:1950-1980: OP_ADD with rewrite_output = 0 */
+    for (int64_t i = 0; i < n; ++i)
+        out[i] = out[i] + in[i];
+}
+
+void so_bias_f32(int32_t C, int32_t H, int32_t W, int32_t cb, const float *bias,
+                 int accumulate, float *out)
+{
+    /* interface_abstract.hpp:1992-2060: OP_UPSAMPLE with an "infinite" stride, i.e. the
+     * per-channel value is broadcast to every pixel. */
+    for (int32_t c = 0; c < C; ++c)
+        for (int32_t h = 0; h < H; ++h)
+            for (int32_t w = 0; w < W; ++w)
+            {
+                const size_t i = act_idx(H, W, cb, c, h, w);
+                out[i] = accumulate ? out[i] + bias[c] : bias[c];
+            }
+}
+
+void so_upsample2d_f32(int32_t C, int32_t H, int32_t W, int32_t cb, int32_t scale,
+                       const float *in, float *out)
+{
+    /* interface_abstract.hpp:1845-1888; out[h][w] = in[h/scale][w/scale] */
+    const int32_t Ho = H * scale, Wo = W * scale;
+    for (int32_t c = 0; c < C; ++c)
+        for (int32_t h = 0; h < Ho; ++h)
+            for (int32_t w = 0; w < Wo; ++w)
+                out[act_idx(Ho, Wo, cb, c, h, w)] = in[act_idx(H, W, cb, c, h / scale, w / scale)];
+}
+
+void so_softmax_f32(int32_t C, int32_t H, int32_t W, int32_t cb, const float *in, float *out)
+{
+    /* interface_abstract.hpp:1778-1833: exp pass, one global sum over C*H*W, scale pass.
+     * No max subtraction.  The sum runs in buffer order. */
+    const int64_t n = (int64_t)C * H * W;
+    (void)cb;
+    for (int64_t i = 0; i < n; ++i)
+        out[i] = expf(in[i]);
+    float sum = 0.f;
+    for (int64_t i = 0; i < n; ++i)
+        sum = sum + out[i];
+    const float inv = (float)(1.0 / sum);
+    for (int64_t i = 0; i < n; ++i)
+        out[i] = out[i] * inv;
+}
+
+/* ---------------------------------------------------------------- uint8 */
+int32_t so_requant(int32_t acc, int32_t lshift, int32_t rshift, int32_t multiplier)
+{
+    /* QUINT8_QUANTIZE_TILE_C + VQRDMULH + RNDRSHIFT,
+     * include/small/platforms/reference/intrinsics_quint8.h:481-531.
+     * The clamp to [0,255] uses the template defaults, not the buffer's fields
+     * (q_abstract_layer.hpp:160-161). */
+    const int64_t a = (int64_t)(int32_t)((uint32_t)acc * (uint32_t)(1u << lshift));
+    const int64_t b = (int64_t)multiplier;
+    const int overflow = (a == b) && (a == -2147483648LL);
+    const int64_t prod = a * b;
+    const int32_t nudge = prod >= 0 ? (1 << 30) : (1 - (1 << 30));
+    const int32_t hi = (int32_t)((prod + nudge) / (1LL << 31)); /* truncating division */
+    int32_t v = overflow ? 2147483647 : hi;
+    const int32_t mask = (int32_t)((1LL << rshift) - 1);
+    const int32_t mod = v & mask;
+    const int32_t threshold = (mask >> 1) + ((v < 0) ? -1 : 0);
+    v = (v >> rshift) + ((mod > threshold) ? -1 : 0); /* "one" is ~0 in the reference */
+    return v > 0 ? (v < 255 ? v : 255) : 0;
+}
+
+void so_conv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
+                  const uint8_t *filt, const int32_t *bias, uint8_t *out)
+{
+    const int32_t cib = eff_cib(s->C, s->cib), cob = s->cob;
+    const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
+    const int32_t Wo = so_out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    const int32_t ncb = s->C / cib;
+    for (int32_t k = 0; k < s->K; ++k)
+        for (int32_t oh = 0; oh < Ho; ++oh)
+            for (int32_t ow = 0; ow < Wo; ++ow)
+            {
+                int32_t acc = q->k_zero + (bias ? bias[k] : 0);
+                for (int32_t b = 0; b < ncb; ++b)
+                    for (int32_t kh = 0; kh < s->Fh; ++kh)
+                    {
+                        const int32_t ih = oh * s->stride - s->pad_t + kh;
+                        if (ih < 0 || ih >= s->H)
+                            continue;
+                        for (int32_t kw = 0; kw < s->Fw; ++kw)
+                        {
+                            const int32_t iw = ow * s->stride - s->pad_l + kw;
+                            if (iw < 0 || iw >= s->W)
+                                continue;
+                            const uint8_t *a = in + ((size_t)b * s->H * s->W + (size_t)ih * s->W + iw) * cib;
+                            const uint8_t *f = filt + ((((size_t)(k / cob) * ncb + b) * s->Fh + kh) * s->Fw + kw) * cib * cob + (k % cob);
+                            for (int32_t c = 0; c < cib; ++c) /* QUINT8_CONV_TILE_C :191-206 */
+                                acc += ((int32_t)a[c] + q->zero_in) * ((int32_t)f[(size_t)c * cob] + q->zero_filt);
+                        }
+                    }
+                out[act_idx(Ho, Wo, cob, k, oh, ow)] =
+                    (uint8_t)so_requant(acc, q->lshift, q->rshift, q->multiplier);
+            }
+}
+
+void so_dwconv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
+                    const uint8_t *filt, const int32_t *bias, uint8_t *out)
+{
+    const int32_t cb = s->cob;
+    const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
+    const int32_t Wo = so_out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    for (int32_t c = 0; c < s->C; ++c)
+        for (int32_t oh = 0; oh < Ho; ++oh)
+            for (int32_t ow = 0; ow < Wo; ++ow)
+            {
+                int32_t acc = q->k_zero + (bias ? bias[c] : 0);
+                for (int32_t kh = 0; kh < s->Fh; ++kh)
+                {
+                    const int32_t ih = oh * s->stride - s->pad_t + kh;
+                    if (ih < 0 || ih >= s->H)
+                        continue;
+                    for (int32_t kw = 0; kw < s->Fw; ++kw)
+                    {
+                        const int32_t iw = ow * s->stride - s->pad_l + kw;
+                        if (iw < 0 || iw >= s->W)
+                            continue;
+                        const int32_t a = in[act_idx(s->H, s->W, cb, c, ih, iw)];
+                        const int32_t f = filt[(((size_t)(c / cb) * s->Fh + kh) * s->Fw + kw) * cb + (c % cb)];
+                        acc += (a + q->zero_in) * (f + q->zero_filt); /* QUINT8_DW_TILE_C :270-289 */
+                    }
+                }
+                out[act_idx(Ho, Wo, cb, c, oh, ow)] =
+                    (uint8_t)so_requant(acc, q->lshift, q->rshift, q->multiplier);
+            }
+}
+
+void so_maxpool2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in, uint8_t *out)
+{
+    /* q_abstract_layer.hpp:277-288: interior tiles start from the RAW first tap (no zero
+     * point), border tiles from k_zero; every tap then enters as a + zero_in
+     * (QUINT8_MAX_TILE_C, intrinsics_quint8.h:231-246); the maximum is requantised. */
+    const int32_t cb = s->cob;
+    const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
+    const int32_t Wo = so_out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    for (int32_t c = 0; c < s->C; ++c)
+        for (int32_t oh = 0; oh < Ho; ++oh)
+            for (int32_t ow = 0; ow < Wo; ++ow)
+            {
+                const int32_t h0 = oh * s->stride - s->pad_t, w0 = ow * s->stride - s->pad_l;
+                int32_t m = q->k_zero;
+                if (window_is_interior(s, oh, ow))
+                    m = in[act_idx(s->H, s->W, cb, c, h0, w0)];
+                for (int32_t kh = 0; kh < s->Fh; ++kh)
+                    for (int32_t kw = 0; kw < s->Fw; ++kw)
+                    {
+                        const int32_t ih = h0 + kh, iw = w0 + kw;
+                        if (ih < 0 || ih >= s->H || iw < 0 || iw >= s->W)
+                            continue;
+                        const int32_t a = (int32_t)in[act_idx(s->H, s->W, cb, c, ih, iw)] + q->zero_in;
+                        m = a > m ? a : m;
+                    }
+                out[act_idx(Ho, Wo, cb, c, oh, ow)] =
+                    (uint8_t)so_requant(m, q->lshift, q->rshift, q->multiplier);
+            }
+}
+
+void so_relu_u8(int64_t n, const so_quant *q, const uint8_t *in, uint8_t *out)
+{
+    /* interface_abstract.hpp:1577-1607: OP_RELU, tile seeded with k_zero = 0 */
+    for (int64_t i = 0; i < n; ++i)
+    {
+        int32_t m = q->k_zero;
+        const int32_t a = (int32_t)in[i] + q->zero_in;
+        m = a > m ? a : m;
+        out[i] = (uint8_t)so_requant(m, q->lshift, q->rshift, q->multiplier);
+    }
+}
+
+void so_avgpool2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in, uint8_t *out)
+{
+    const int32_t cb = s->cob;
+    const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
+    const int32_t Wo = so_out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    for (int32_t c = 0; c < s->C; ++c)
+        for (int32_t oh = 0; oh < Ho; ++oh)
+            for (int32_t ow = 0; ow < Wo; ++ow)
+            {
+                const int32_t h0 = oh * s->stride - s->pad_t, w0 = ow * s->stride - s->pad_l;
+                int32_t acc = q->k_zero;
+                for (int32_t kh = 0; kh < s->Fh; ++kh)
+                    for (int32_t kw = 0; kw < s->Fw; ++kw)
+                    {
+                        const int32_t ih = h0 + kh, iw = w0 + kw;
+                        if (ih < 0 || ih >= s->H || iw < 0 || iw >= s->W)
+                            continue;
+                        acc += (int32_t)in[act_idx(s->H, s->W, cb, c, ih, iw)] + q->zero_in;
+                    }
+                out[act_idx(Ho, Wo, cb, c, oh, ow)] =
+                    (uint8_t)so_requant(acc, q->lshift, q->rshift, q->multiplier);
+            }
+}

@@ -1,0 +1,44 @@
+"""Copy the reference's own golden vectors for the hot path into tests/golden/reference/.
+
+The files are the PyTorch-generated regression data the reference's layer tests read
+(test/regression_data, written by test/gen_reg_data.py with torch.manual_seed(0); format:
+big-endian uint32 element count, then raw little-endian float32, test/test_utils.hpp
+:187-215).  Everything up to 150 KB is taken, plus a few 96-channel 30x30 cases that give
+the convolution kernels a non-trivial size.  Run once where the reference tree is mounted:
+
+    python tests/golden/import_reference_goldens.py [/path/to/reference]
+"""
+import os
+import shutil
+import sys
+
+EXTRA = [
+    "{}__conv2d_Ci96_H30_W30_k3_s1_f_Co96_{}.bin",
+    "{}__conv2d_Ci96_H30_W30_k3_s2_f_Co96_{}.bin",
+    "{}__dw_conv_Ci96_H30_W30_k3_s2_f_{}.bin",
+    "{}__pool_Ci96_H30_W30_k3_s2_f_{}.bin",
+]
+
+
+def main():
+    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    src = os.path.join(ref, "test", "regression_data")
+    dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference")
+    os.makedirs(dst, exist_ok=True)
+    names = sorted(os.listdir(src))
+    extra_keys = [e.split("{}")[1] for e in EXTRA]
+    n = 0
+    for name in names:
+        if "yolo" in name or not name.endswith(".bin"):
+            continue  # box decoding is outside the layer path
+        path = os.path.join(src, name)
+        small = os.path.getsize(path) <= 150 * 1024
+        extra = any(k in name for k in extra_keys)
+        if small or extra:
+            shutil.copyfile(path, os.path.join(dst, name))
+            n += 1
+    print(f"copied {n} files to {dst}")
+
+
+if __name__ == "__main__":
+    main()
