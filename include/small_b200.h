@@ -1,0 +1,164 @@
+/*
+ * small_b200.h -- C ABI of libsmall_b200.so, the sm_100a implementation of SMaLL's layer
+ * loop nest and microkernels.
+ *
+ * Each entry point replaces one instantiation family of the reference's templated loop
+ * nest (small::detail::abstract_layer, include/small/abstract_layer.hpp:1358-1823, and
+ * small::quint8_detail::abstract_layer, include/small/q_abstract_layer.hpp:884-1571) as
+ * reached through the functional interface (include/small/interface_abstract.hpp).  The
+ * reference-side binding is include/small/platforms/b200/ (C++ headers that keep the
+ * small:: signatures and forward here).
+ *
+ * Conventions
+ *   - all data pointers are DEVICE pointers (or managed memory) on the current device;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *     calls only enqueue work, they do not synchronise;
+ *   - every function returns SMALL_B200_OK or an error code; the text of the last error of
+ *     the calling thread is available from small_b200_last_error();
+ *   - layouts are SMaLL's packed layouts with channel block 16 for both element types:
+ *       activations  [N][C/16][H][W][16]        (image-major batch; N = 1 is the reference)
+ *       conv filter  [K/16][C/16][Fh][Fw][16][16]
+ *       dw filter    [C/16][Fh][Fw][16]
+ *     with the reference's first-layer exception: C in {1,2,3} means block = C
+ *     (include/small/buffers.hpp:52-57), i.e. an HWC-interleaved image;
+ *   - output size: Ho = (H + pad_t + pad_b - Fh)/stride + 1 (include/small/utils.hpp:159).
+ */
+#ifndef SMALL_B200_H
+#define SMALL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SMALL_B200_CB 16 /* FLOAT_C_ob = FLOAT_C_ib = QUINT8_C_ob = QUINT8_C_ib */
+
+enum
+{
+    SMALL_B200_OK = 0,
+    SMALL_B200_INVALID_ARGUMENT = 1, /* maps to std::invalid_argument (unsupported stride/channels) */
+    SMALL_B200_CUDA_ERROR = 2,       /* maps to std::runtime_error */
+    SMALL_B200_OUT_OF_MEMORY = 3,    /* maps to std::bad_alloc */
+    SMALL_B200_DEVICE_TIMEOUT = 4    /* a bounded device-side wait ran out */
+};
+
+enum
+{
+    SMALL_B200_ACT_NONE = 0,
+    SMALL_B200_ACT_RELU = 1, /* max(x, 0)        FLOAT_MAX_TILE_C on a zeroed tile        */
+    SMALL_B200_ACT_LEAKY = 2 /* x>0 ? x : x*slope FLOAT_COND_SCALE_TILE_C                 */
+};
+
+/* Shape of one windowed layer call.  Mirrors the argument list the functional interface
+ * passes to the loop nest (interface_abstract.hpp:46-58 -> abstract_layer.hpp:1368-1385),
+ * plus the batch and what the fused interface adds (fused_interface_abstract.hpp:217). */
+typedef struct small_b200_layer
+{
+    int32_t N;      /* images in the batch                                               */
+    int32_t C;      /* input channels                                                    */
+    int32_t K;      /* output channels of a dense conv; ignored by per-channel layers    */
+    int32_t H, W;   /* input height / width                                              */
+    int32_t Fh, Fw; /* window                                                            */
+    int32_t stride;
+    int32_t pad_t, pad_b, pad_l, pad_r;
+    int32_t accumulate; /* 1 = Partial* form: start from the existing output            */
+    int32_t act;        /* SMALL_B200_ACT_*, applied after the full reduction            */
+    float slope;        /* LeakyReLU negative slope                                      */
+    /* uint8 path (ignored by float entry points); semantics of
+     * include/small/platforms/reference/intrinsics_quint8.h:191-206,481-531:
+     * acc = k_zero + bias[k] + sum over VALID taps (a + zero_in) * (w + zero_filt),
+     * out = clamp(rounding_shift(high_mul(acc << lshift, multiplier), rshift), 0, 255) */
+    int32_t zero_in, zero_filt;
+    int32_t lshift, rshift, multiplier;
+    int32_t k_zero;
+} small_b200_layer;
+
+/* ---- library / device ------------------------------------------------------------ */
+const char *small_b200_last_error(void);
+int small_b200_device_count(int *count);
+int small_b200_set_device(int device);
+/* Number of kernels this library has launched in this process since it was loaded. */
+uint64_t small_b200_launch_count(void);
+
+/* ---- memory (the platform's alloc_buffer/free_buffer,
+ *      include/small/platforms/reference/Buffer.hpp:36-61, FloatBuffer.hpp:59-77) ------- */
+int small_b200_malloc(size_t bytes, void **ptr);         /* device memory                  */
+int small_b200_malloc_managed(size_t bytes, void **ptr); /* host-visible (Buffer::data()) */
+int small_b200_malloc_host(size_t bytes, void **ptr);    /* pinned host staging            */
+int small_b200_free(void *ptr);
+int small_b200_free_host(void *ptr);
+int small_b200_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream);
+int small_b200_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream);
+int small_b200_memcpy_d2d(void *dst, const void *src, size_t bytes, void *stream);
+int small_b200_prefetch(const void *managed_ptr, size_t bytes, void *stream); /* to the device */
+
+/* ---- streams and graphs ------------------------------------------------------------ */
+int small_b200_stream_create(void **stream);
+int small_b200_stream_destroy(void *stream);
+int small_b200_stream_sync(void *stream);
+int small_b200_device_sync(void);
+/* Capture everything enqueued on `stream` between begin and end into one executable graph. */
+int small_b200_graph_begin(void *stream);
+int small_b200_graph_end(void *stream, void **graph_exec);
+int small_b200_graph_launch(void *graph_exec, void *stream);
+int small_b200_graph_destroy(void *graph_exec);
+
+/* ---- float layers ------------------------------------------------------------------ */
+/* small::Conv2D / PartialConv2D<FloatBuffer> (interface_abstract.hpp:46-221, :416-587) with
+ * the bias-before / activation-after slots of the fused interface
+ * (fused_interface_abstract.hpp:55, :217).  bias may be NULL.  K % 16 == 0;
+ * C % 16 == 0 or C in {1,2,3}; stride in {1,2}. */
+int small_b200_conv2d_f32(const small_b200_layer *L, const float *in, const float *filt,
+                          const float *bias, float *out, void *stream);
+/* small::DepthwiseConv2D / PartialDepthwiseConv2D<FloatBuffer> (:994, :1127) and
+ * DepthwiseConv2D_Bias_ReLU (fused_interface_abstract.hpp:1419). */
+int small_b200_dwconv2d_f32(const small_b200_layer *L, const float *in, const float *filt,
+                            const float *bias, float *out, void *stream);
+/* small::MaxPool2D<FloatBuffer> (:778): border windows start from 0, interior from the
+ * first tap. */
+int small_b200_maxpool2d_f32(const small_b200_layer *L, const float *in, float *out, void *stream);
+/* small::AveragePool2D<FloatBuffer> (:910): sum of valid taps times 1/(Fh*Fw); strides 1,2,3. */
+int small_b200_avgpool2d_f32(const small_b200_layer *L, const float *in, float *out, void *stream);
+/* small::ReLUActivation (:1541), LeakyReLUActivation (:1616), Accum (:1950); n = elements. */
+int small_b200_relu_f32(int64_t n, const float *in, float *out, void *stream);
+int small_b200_leaky_relu_f32(int64_t n, const float *in, float slope, float *out, void *stream);
+int small_b200_accum_f32(int64_t n, const float *in, float *out, void *stream);
+/* small::Bias / PartialBias (:1992, :2035): out[n][c][h][w] (+)= bias[c]. */
+int small_b200_bias_f32(int32_t N, int32_t C, int32_t H, int32_t W, const float *bias,
+                        int32_t accumulate, float *out, void *stream);
+/* small::UpSample2D (:1845), scale 2: out[h][w] = in[h/2][w/2]. */
+int small_b200_upsample2d_f32(int32_t N, int32_t C, int32_t H, int32_t W, const float *in,
+                              float *out, void *stream);
+/* small::SoftMax (:1778): per image, exp / sum over all C*H*W elements, no max subtraction. */
+int small_b200_softmax_f32(int32_t N, int64_t elems_per_image, const float *in, float *out,
+                           void *stream);
+/* small::Concat (:2072): per image, channel concatenation = two contiguous copies.
+ * bytes0 / bytes1 are per-image sizes. */
+int small_b200_concat(int32_t N, size_t bytes0, const void *in0, size_t bytes1, const void *in1,
+                      void *out, void *stream);
+
+/* ---- uint8 layers ------------------------------------------------------------------ */
+/* small::Conv2D<QUInt8Buffer> (:229-404) with an optional per-channel int32 bias added to
+ * the accumulator seed.  The int32 partial sums never leave the chip, so the output buffer
+ * needs no 4x over-allocation (the reference's does, q_abstract_layer.hpp:1144). */
+int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
+                         const int32_t *bias, uint8_t *out, void *stream);
+/* small::DepthwiseConv2D<QUInt8Buffer> (:1059). */
+int small_b200_dwconv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
+                           const int32_t *bias, uint8_t *out, void *stream);
+/* small::MaxPool2D<QUInt8Buffer> (:843): interior windows start from the raw first tap,
+ * border windows from k_zero; taps enter as a + zero_in; the maximum is requantised. */
+int small_b200_maxpool2d_u8(const small_b200_layer *L, const uint8_t *in, uint8_t *out, void *stream);
+/* No counterpart in the reference (it has no quint8 average pool): sum over valid taps of
+ * (a + zero_in), requantised with the layer's multiplier and shifts. */
+int small_b200_avgpool2d_u8(const small_b200_layer *L, const uint8_t *in, uint8_t *out, void *stream);
+/* small::ReLUActivation<QUInt8Buffer> (:1577): requantise max(a + zero_in, k_zero). */
+int small_b200_relu_u8(int64_t n, const small_b200_layer *L, const uint8_t *in, uint8_t *out,
+                       void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SMALL_B200_H */

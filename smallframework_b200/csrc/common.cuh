@@ -1,0 +1,103 @@
+// common.cuh -- shared host/device helpers of libsmall_b200.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "small_b200.h"
+
+namespace sb
+{
+constexpr int CB = SMALL_B200_CB;
+
+extern thread_local std::string g_last_error;
+extern std::atomic<uint64_t> g_launches;
+
+inline int fail(int code, const std::string &msg)
+{
+    g_last_error = msg;
+    return code;
+}
+
+inline int cuda_fail(cudaError_t e, const char *what)
+{
+    return fail(e == cudaErrorMemoryAllocation ? SMALL_B200_OUT_OF_MEMORY : SMALL_B200_CUDA_ERROR,
+                std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+#define SB_CUDA(call)                               \
+    do                                              \
+    {                                               \
+        cudaError_t e_ = (call);                    \
+        if (e_ != cudaSuccess)                      \
+            return sb::cuda_fail(e_, #call);        \
+    } while (0)
+
+// Call after every kernel launch: counts it and turns a launch error into a return code.
+inline int launched(const char *name)
+{
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return cuda_fail(e, name);
+    return SMALL_B200_OK;
+}
+
+inline int out_dim(int in, int pf, int pb, int f, int s)
+{
+    int o = (in + pf + pb - f) / s + 1; // include/small/utils.hpp:159-165 on the padded extent
+    return o > 0 ? o : 0;
+}
+
+// Channel block actually used for `channels` input channels (first-layer exception).
+inline int eff_block(int channels) { return (channels < CB) ? channels : CB; }
+
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+inline int num_sms()
+{
+    static int sms[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64)
+        dev = 0;
+    if (!sms[dev])
+        cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    return sms[dev] ? sms[dev] : 148;
+}
+
+// Shared argument checks of the windowed layers (the reference throws
+// std::invalid_argument for these, interface_abstract.hpp:100,218).
+int check_window_layer(const small_b200_layer *L, const char *name, bool dense, int max_stride);
+
+// Fixed-point tail of the uint8 path; bit-exact restatement of QUINT8_QUANTIZE_TILE_C
+// (include/small/platforms/reference/intrinsics_quint8.h:481-531).
+__host__ __device__ inline int32_t requant(int32_t acc, int32_t lshift, int32_t rshift, int32_t mult)
+{
+    const long long a = (long long)(int32_t)((uint32_t)acc << lshift);
+    const long long b = (long long)mult;
+    const bool overflow = (a == b) && (a == -2147483648LL);
+    const long long prod = a * b;
+    const long long nudge = prod >= 0 ? (1LL << 30) : (1LL - (1LL << 30));
+    const long long q = (prod + nudge) / (1LL << 31); // C division truncates toward zero
+    int32_t v = overflow ? 2147483647 : (int32_t)q;
+    const int32_t mask = (int32_t)((1LL << rshift) - 1);
+    const int32_t mod = v & mask;
+    const int32_t thr = (mask >> 1) + (v < 0 ? -1 : 0);
+    v = (v >> rshift) + (mod > thr ? -1 : 0); // the reference's "one" is ~0
+    return v > 0 ? (v < 255 ? v : 255) : 0;
+}
+
+__device__ __forceinline__ float apply_act(float v, int act, float slope)
+{
+    if (act == SMALL_B200_ACT_RELU)
+        return v > 0.f ? v : 0.f;
+    if (act == SMALL_B200_ACT_LEAKY)
+        return v > 0.f ? v : v * slope;
+    return v;
+}
+} // namespace sb

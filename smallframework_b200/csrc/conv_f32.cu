@@ -1,0 +1,365 @@
+// conv_f32.cu -- fp32 dense convolution on the CUDA cores (FFMA), implicit GEMM over the
+// packed layout.  Replaces small::detail::abstract_layer<FloatBuffer,1,C_ob,C_ib,W_ob,
+// stride,UNROLL,OP_CONV,2,rewrite> (include/small/abstract_layer.hpp:1368-1823) and its
+// FLOAT_CONV_TILE_C microkernel (platforms/reference/intrinsics_float.h:262-281).
+//
+// Work decomposition
+//   CTA  : TH x TW = 128 output pixels of one image  x  BN output channels
+//   loop : input-channel block (16 ch) -> kernel row -> kernel col -> channel, the same
+//          order in which the reference adds terms (abstract_layer.hpp:1630, :542-563)
+//   stage: per input-channel block, the input patch (with halo, zero-filled outside the
+//          image) and that block's filter slice are staged in shared memory with
+//          cp.async, double buffered
+//   thread: 8 consecutive pixels of one tile row x CH output channels in registers
+#include "common.cuh"
+
+namespace
+{
+using namespace sb;
+
+constexpr int TH = 8, TW = 16; // output tile (rows x cols); one thread owns 8 cols of one row
+constexpr int PXT = 8;         // pixels per thread
+
+struct ConvArgs
+{
+    int N, C, K, H, W, Ho, Wo, Fh, Fw, stride, pad_t, pad_l;
+    int cbs;          // input channel blocks
+    int PH, PW;       // patch rows / cols
+    int tiles_h, tiles_w, kblocks; // kblocks = K / BN
+    int accumulate, act;
+    float slope;
+};
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem, bool valid)
+{
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0; // src-size 0 -> the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// BN: output channels per CTA; CH: output channels per thread (two groups of CH/2... for
+// CH = 8 the thread owns channels [4g,4g+4) and [BN/2+4g, BN/2+4g+4) so that a quarter
+// warp reads 128 contiguous bytes of the filter slice; for CH = 4 just [4g,4g+4)).
+template <int BN, int CH, int STRIDE>
+__global__ void __launch_bounds__(16 * BN / CH)
+conv2d_f32_kernel(const ConvArgs a, const float *__restrict__ in, const float *__restrict__ filt,
+                  const float *__restrict__ bias, float *__restrict__ out)
+{
+    constexpr int NT = 16 * BN / CH; // threads
+    constexpr int CG = BN / CH;      // channel groups
+    extern __shared__ __align__(16) float smem[];
+    const int taps = a.Fh * a.Fw;
+    const int patch_f = a.PH * a.PW * CB;  // floats per patch
+    const int wts_f = taps * CB * BN;      // floats per filter slice
+    const int stage_f = patch_f + wts_f;
+
+    // tile coordinates: kb fastest so CTAs that share an input patch run together
+    int bid = blockIdx.x;
+    const int kb = bid % a.kblocks; bid /= a.kblocks;
+    const int tw = bid % a.tiles_w; bid /= a.tiles_w;
+    const int th = bid % a.tiles_h; bid /= a.tiles_h;
+    const int n = bid;
+    const int oh0 = th * TH, ow0 = tw * TW;
+    const int ih0 = oh0 * STRIDE - a.pad_t, iw0 = ow0 * STRIDE - a.pad_l;
+
+    const int tid = threadIdx.x;
+    const int cg = tid % CG;       // channel group (fast: lanes of a quarter warp share pixels)
+    const int pg = tid / CG;       // pixel group 0..15
+    const int r = pg >> 1;         // tile row
+    const int c0 = (pg & 1) * PXT; // first tile col
+
+    const float *in_img = in + (size_t)n * a.C * a.H * a.W;
+    const size_t in_cb_stride = (size_t)a.H * a.W * CB;
+    // filter: [K/16][C/16][taps][16][16]
+    const size_t f_kb16_stride = (size_t)a.cbs * taps * CB * CB;
+
+    auto load_stage = [&](int cb, int buf) {
+        float *patch = smem + buf * stage_f;
+        float *wts = patch + patch_f;
+        // input patch: PH*PW pixels x 4 chunks of 16 B
+        const float *src_cb = in_img + (size_t)cb * in_cb_stride;
+        const int nchunk = a.PH * a.PW * 4;
+        for (int i = tid; i < nchunk; i += NT)
+        {
+            const int q = i & 3, pix = i >> 2;
+            const int pr = pix / a.PW, pc = pix - pr * a.PW;
+            const int ih = ih0 + pr, iw = iw0 + pc;
+            const bool ok = (ih >= 0) && (ih < a.H) && (iw >= 0) && (iw < a.W);
+            const float *src = ok ? src_cb + ((size_t)ih * a.W + iw) * CB + q * 4 : in;
+            cp_async16(patch + pix * CB + q * 4, src, ok);
+        }
+        // filter slice -> smem [tap][c][BN]
+        const int wchunk = taps * CB * (BN / 4);
+        for (int i = tid; i < wchunk; i += NT)
+        {
+            const int k4 = i % (BN / 4);
+            const int tc = i / (BN / 4); // tap*16 + c
+            const int kk = k4 * 4;       // channel inside the CTA's BN
+            const int kb16 = (kb * BN + kk) / CB;
+            const float *src = filt + (size_t)kb16 * f_kb16_stride + (size_t)cb * taps * CB * CB +
+                               (size_t)tc * CB + (kk % CB);
+            cp_async16(wts + tc * BN + kk, src, true);
+        }
+    };
+
+    float acc[PXT][CH];
+#pragma unroll
+    for (int j = 0; j < PXT; ++j)
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+            acc[j][c] = 0.f;
+
+    // channel offsets owned by this thread inside the CTA's BN
+    const int ko0 = cg * 4;
+    const int ko1 = (CH == 8) ? BN / 2 + cg * 4 : 0;
+
+    const int oh = oh0 + r;
+    const bool row_ok = oh < a.Ho;
+
+    // seed: existing output (Partial*) and/or bias, as Bias -> PartialConv2D does
+    // (include/small/Conv2DLayer.hpp:827-835)
+#pragma unroll
+    for (int half = 0; half < CH / 4; ++half)
+    {
+        const int kg = kb * BN + (half ? ko1 : ko0);
+        float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (bias)
+            bv = *reinterpret_cast<const float4 *>(bias + kg);
+#pragma unroll
+        for (int j = 0; j < PXT; ++j)
+        {
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int ow = ow0 + c0 + j;
+            if (a.accumulate && row_ok && ow < a.Wo)
+                s = *reinterpret_cast<const float4 *>(
+                    out + (((size_t)n * (a.K / CB) + kg / CB) * a.Ho * a.Wo + (size_t)oh * a.Wo + ow) * CB + (kg % CB));
+            if (bias)
+            {
+                s.x += bv.x; s.y += bv.y; s.z += bv.z; s.w += bv.w;
+            }
+            acc[j][half * 4 + 0] = s.x; acc[j][half * 4 + 1] = s.y;
+            acc[j][half * 4 + 2] = s.z; acc[j][half * 4 + 3] = s.w;
+        }
+    }
+
+    load_stage(0, 0);
+    cp_async_commit();
+
+    for (int cb = 0; cb < a.cbs; ++cb)
+    {
+        const int buf = cb & 1;
+        if (cb + 1 < a.cbs)
+            load_stage(cb + 1, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+
+        const float *patch = smem + buf * stage_f;
+        const float *wts = patch + patch_f;
+        const float *prow = patch + ((r * STRIDE) * a.PW + c0 * STRIDE) * CB;
+        for (int kh = 0; kh < a.Fh; ++kh)
+        {
+            for (int kw = 0; kw < a.Fw; ++kw)
+            {
+                const float *ap = prow + (kh * a.PW + kw) * CB;
+                const float *wp = wts + (kh * a.Fw + kw) * CB * BN;
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4)
+                {
+                    float4 av[PXT];
+#pragma unroll
+                    for (int j = 0; j < PXT; ++j)
+                        av[j] = *reinterpret_cast<const float4 *>(ap + j * STRIDE * CB + c4 * 4);
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc)
+                    {
+                        const float *wrow = wp + (c4 * 4 + cc) * BN;
+                        const float4 b0 = *reinterpret_cast<const float4 *>(wrow + ko0);
+                        float4 b1 = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (CH == 8)
+                            b1 = *reinterpret_cast<const float4 *>(wrow + ko1);
+#pragma unroll
+                        for (int j = 0; j < PXT; ++j)
+                        {
+                            const float x = (cc == 0) ? av[j].x : (cc == 1) ? av[j].y : (cc == 2) ? av[j].z : av[j].w;
+                            acc[j][0] = fmaf(x, b0.x, acc[j][0]);
+                            acc[j][1] = fmaf(x, b0.y, acc[j][1]);
+                            acc[j][2] = fmaf(x, b0.z, acc[j][2]);
+                            acc[j][3] = fmaf(x, b0.w, acc[j][3]);
+                            if (CH == 8)
+                            {
+                                acc[j][4] = fmaf(x, b1.x, acc[j][4]);
+                                acc[j][5] = fmaf(x, b1.y, acc[j][5]);
+                                acc[j][6] = fmaf(x, b1.z, acc[j][6]);
+                                acc[j][7] = fmaf(x, b1.w, acc[j][7]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    if (!row_ok)
+        return;
+#pragma unroll
+    for (int half = 0; half < CH / 4; ++half)
+    {
+        const int kg = kb * BN + (half ? ko1 : ko0);
+        float *obase = out + (((size_t)n * (a.K / CB) + kg / CB) * a.Ho * a.Wo + (size_t)oh * a.Wo) * CB + (kg % CB);
+#pragma unroll
+        for (int j = 0; j < PXT; ++j)
+        {
+            const int ow = ow0 + c0 + j;
+            if (ow < a.Wo)
+            {
+                float4 v;
+                v.x = apply_act(acc[j][half * 4 + 0], a.act, a.slope);
+                v.y = apply_act(acc[j][half * 4 + 1], a.act, a.slope);
+                v.z = apply_act(acc[j][half * 4 + 2], a.act, a.slope);
+                v.w = apply_act(acc[j][half * 4 + 3], a.act, a.slope);
+                *reinterpret_cast<float4 *>(obase + (size_t)ow * CB) = v;
+            }
+        }
+    }
+}
+
+// First layer: C in {1,2,3}, the image is HWC-interleaved (buffers.hpp:52-57).  One thread
+// per output pixel and 16-channel block; the filter slice [taps][C][16] sits in shared memory.
+__global__ void __launch_bounds__(256)
+conv2d_first_f32_kernel(const ConvArgs a, const float *__restrict__ in, const float *__restrict__ filt,
+                        const float *__restrict__ bias, float *__restrict__ out)
+{
+    extern __shared__ __align__(16) float w[]; // [taps][C][16]
+    const int taps = a.Fh * a.Fw;
+    const int kb = blockIdx.y;
+    const int n = blockIdx.z;
+    const int wn = taps * a.C * CB;
+    const float *fsrc = filt + (size_t)kb * wn;
+    for (int i = threadIdx.x; i < wn; i += blockDim.x)
+        w[i] = fsrc[i];
+    __syncthreads();
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= a.Ho * a.Wo)
+        return;
+    const int oh = p / a.Wo, ow = p - oh * a.Wo;
+    float *o = out + (((size_t)n * (a.K / CB) + kb) * a.Ho * a.Wo + p) * CB;
+    float acc[CB];
+#pragma unroll
+    for (int k = 0; k < CB; ++k)
+    {
+        float s = a.accumulate ? o[k] : 0.f;
+        if (bias)
+            s += bias[kb * CB + k];
+        acc[k] = s;
+    }
+    const float *img = in + (size_t)n * a.C * a.H * a.W;
+    for (int kh = 0; kh < a.Fh; ++kh)
+    {
+        const int ih = oh * a.stride - a.pad_t + kh;
+        if (ih < 0 || ih >= a.H)
+            continue;
+        for (int kw = 0; kw < a.Fw; ++kw)
+        {
+            const int iw = ow * a.stride - a.pad_l + kw;
+            if (iw < 0 || iw >= a.W)
+                continue;
+            const float *px = img + ((size_t)ih * a.W + iw) * a.C;
+            const float *wt = w + (kh * a.Fw + kw) * a.C * CB;
+            for (int c = 0; c < a.C; ++c)
+            {
+                const float x = __ldg(px + c);
+#pragma unroll
+                for (int k = 0; k < CB; ++k)
+                    acc[k] = fmaf(x, wt[c * CB + k], acc[k]);
+            }
+        }
+    }
+#pragma unroll
+    for (int k4 = 0; k4 < CB; k4 += 4)
+    {
+        float4 v;
+        v.x = apply_act(acc[k4 + 0], a.act, a.slope);
+        v.y = apply_act(acc[k4 + 1], a.act, a.slope);
+        v.z = apply_act(acc[k4 + 2], a.act, a.slope);
+        v.w = apply_act(acc[k4 + 3], a.act, a.slope);
+        *reinterpret_cast<float4 *>(o + k4) = v;
+    }
+}
+
+template <int BN, int CH, int STRIDE>
+int launch_conv(const ConvArgs &a, size_t smem_bytes, const float *in, const float *filt,
+                const float *bias, float *out, cudaStream_t st)
+{
+    auto kern = conv2d_f32_kernel<BN, CH, STRIDE>;
+    static bool configured = false; // one attribute call per instantiation and process
+    if (!configured)
+    {
+        SB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        configured = true;
+    }
+    const long long blocks = (long long)a.N * a.tiles_h * a.tiles_w * a.kblocks;
+    kern<<<(unsigned)blocks, 16 * BN / CH, smem_bytes, st>>>(a, in, filt, bias, out);
+    return launched("conv2d_f32_kernel");
+}
+} // namespace
+
+extern "C" int small_b200_conv2d_f32(const small_b200_layer *L, const float *in, const float *filt,
+                                     const float *bias, float *out, void *stream)
+{
+    if (int rc = check_window_layer(L, "Conv2D<float>", true, 2))
+        return rc;
+    ConvArgs a;
+    a.N = L->N; a.C = L->C; a.K = L->K; a.H = L->H; a.W = L->W;
+    a.Fh = L->Fh; a.Fw = L->Fw; a.stride = L->stride; a.pad_t = L->pad_t; a.pad_l = L->pad_l;
+    a.Ho = out_dim(L->H, L->pad_t, L->pad_b, L->Fh, L->stride);
+    a.Wo = out_dim(L->W, L->pad_l, L->pad_r, L->Fw, L->stride);
+    a.accumulate = L->accumulate; a.act = L->act; a.slope = L->slope;
+    if (a.N == 0 || a.Ho == 0 || a.Wo == 0)
+        return SMALL_B200_OK;
+    cudaStream_t st = as_stream(stream);
+
+    if (L->C < CB)
+    {
+        a.cbs = 1; a.PH = a.PW = 0; a.tiles_h = a.tiles_w = a.kblocks = 0;
+        const size_t smem = (size_t)L->Fh * L->Fw * L->C * CB * sizeof(float);
+        if (smem > 48 * 1024)
+            return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> ERROR: first-layer window too large.");
+        dim3 grid((a.Ho * a.Wo + 255) / 256, a.K / CB, a.N);
+        conv2d_first_f32_kernel<<<grid, 256, smem, st>>>(a, in, filt, bias, out);
+        return launched("conv2d_first_f32_kernel");
+    }
+
+    a.cbs = L->C / CB;
+    a.PH = (TH - 1) * L->stride + L->Fh;
+    a.PW = (TW - 1) * L->stride + L->Fw;
+    a.tiles_h = (a.Ho + TH - 1) / TH;
+    a.tiles_w = (a.Wo + TW - 1) / TW;
+    const size_t patch_b = (size_t)a.PH * a.PW * CB * sizeof(float);
+    auto smem_for = [&](int bn) { return 2 * (patch_b + (size_t)L->Fh * L->Fw * CB * bn * sizeof(float)); };
+    const size_t limit = 200 * 1024;
+    int bn = 0;
+    if (a.K % 64 == 0 && smem_for(64) <= limit)
+        bn = 64;
+    else if (a.K % 32 == 0 && smem_for(32) <= limit)
+        bn = 32;
+    else if (smem_for(16) <= limit)
+        bn = 16;
+    else
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> ERROR: window too large for the staged kernel.");
+    a.kblocks = a.K / bn;
+    const size_t smem = smem_for(bn);
+    const bool s2 = L->stride == 2;
+    if (bn == 64)
+        return s2 ? launch_conv<64, 8, 2>(a, smem, in, filt, bias, out, st)
+                  : launch_conv<64, 8, 1>(a, smem, in, filt, bias, out, st);
+    if (bn == 32)
+        return s2 ? launch_conv<32, 4, 2>(a, smem, in, filt, bias, out, st)
+                  : launch_conv<32, 4, 1>(a, smem, in, filt, bias, out, st);
+    return s2 ? launch_conv<16, 4, 2>(a, smem, in, filt, bias, out, st)
+              : launch_conv<16, 4, 1>(a, smem, in, filt, bias, out, st);
+}

@@ -1,0 +1,352 @@
+"""Python mirror of the reference's functional layer interface for device-resident buffers.
+
+Function names, argument order and error behaviour follow
+include/small/interface.hpp:49-497 as defined in include/small/interface_abstract.hpp;
+the only addition is the keyword `batch` (the reference's 2-D functions have no batch
+dimension; here a batch is image-major, every image laid out exactly as the reference
+would lay it out) and `stream`.  Every function only enqueues work on the stream.
+
+Buffers are `FloatBuffer` / `QUInt8Buffer` objects owning a flat torch CUDA tensor; torch
+is used for device memory and streams only.  There is no CPU path: a missing library or a
+non-CUDA buffer raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import ACT_LEAKY, ACT_NONE, ACT_RELU, Layer, check, lib
+from .packing import CB
+
+
+# --------------------------------------------------------------------------- buffers
+class FloatBuffer:
+    """include/small/platforms/b200/Buffer.hpp FloatBuffer: a flat array of float."""
+    W_ob, C_ob, C_ib, SIMD, UNROLL = 6, CB, CB, 4, 1
+    dtype = torch.float32
+
+    def __init__(self, num_elts=0, device="cuda", data=None):
+        if data is not None:
+            self.t = _to_device(data, self.dtype, device)
+        else:
+            self.t = torch.empty(int(num_elts), dtype=self.dtype, device=device)
+
+    def size(self):
+        return self.t.numel()
+
+    def data(self):
+        return self.t
+
+    def ptr(self):
+        return self.t.data_ptr()
+
+    def numpy(self):
+        return self.t.cpu().numpy()
+
+    def swap(self, other):
+        self.__dict__, other.__dict__ = other.__dict__, self.__dict__
+
+    @classmethod
+    def zero(cls):
+        return 0
+
+
+class QUInt8Buffer(FloatBuffer):
+    """QUInt8Buffer with the reference's public quantisation fields, initialised the way
+    quantized_init() does for the range [-1, 1]
+    (include/small/platforms/reference/QUInt8Buffer.hpp:222-272)."""
+    W_ob = 2
+    dtype = torch.uint8
+
+    def __init__(self, num_elts=0, device="cuda", data=None):
+        super().__init__(num_elts, device, data)
+        b = 8
+        max_q = (1 << b) - 1
+        dscale = 2.0 / max_q + 1e-17
+        q, shift = math.frexp(dscale)
+        q_fixed = int(round(q * (1 << 31)))
+        if q_fixed == (1 << 31):
+            q_fixed //= 2
+            shift += 1
+        if shift < -31:
+            shift, q_fixed = 0, 0
+        if shift > 30:
+            shift, q_fixed = 30, (1 << 31) - 1
+        self.b = b
+        self.multiplier = q_fixed
+        self.m_zero = int(np.rint((1.0 * 0 - (-1.0) * max_q) / 2.0))
+        self.scale = float(np.float32(dscale))
+        self.lshift = shift if shift > 0 else 0
+        self.rshift = 0 if shift > 0 else -shift
+        self.min_val, self.max_val, self.offset = 0, 255, 0
+
+    def zero(self):  # instance method here: the zero point is a field
+        return self.m_zero
+
+
+def _to_device(data, dtype, device):
+    if isinstance(data, torch.Tensor):
+        return data.to(device=device, dtype=dtype).contiguous().reshape(-1)
+    np_dtype = np.float32 if dtype == torch.float32 else np.uint8
+    return torch.from_numpy(np.ascontiguousarray(data, dtype=np_dtype).reshape(-1)).to(device)
+
+
+def _stream(stream):
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return getattr(stream, "cuda_stream", stream)
+
+
+def _ptr(buf):
+    if buf is None:
+        return None
+    t = buf.t if isinstance(buf, FloatBuffer) else buf
+    if not t.is_cuda:
+        raise _lib.SmallB200Error("buffers must live on a CUDA device (no CPU path)")
+    return t.data_ptr()
+
+
+def _is_q(buf):
+    return isinstance(buf, QUInt8Buffer)
+
+
+def _layer(batch, C_, K, H, W, Fh, Fw, stride, t, b, l, r, accumulate=0, act=ACT_NONE, slope=0.0,
+           inp=None, filt=None, out=None):
+    L = Layer(batch, C_, K, H, W, Fh, Fw, stride, t, b, l, r, accumulate, act, slope,
+              0, 0, 0, 0, 0, 0)
+    if _is_q(out):
+        L.zero_in = inp.zero() if _is_q(inp) else 0
+        L.zero_filt = filt.zero() if _is_q(filt) else 0
+        L.lshift, L.rshift, L.multiplier = out.lshift, out.rshift, out.multiplier
+        L.k_zero = 0
+    return L
+
+
+def _need(buf, elems, what):
+    if buf.size() < elems:
+        raise ValueError(f"{what}: buffer holds {buf.size()} elements, {elems} needed")
+
+
+# --------------------------------------------------------------------------- dense conv
+def _conv(name, partial, kh, kw, stride, t, b, l, r, K, C_, H, W, inp, filt, out, bias, act,
+          slope, batch, stream):
+    L = _layer(batch, C_, K, H, W, kh, kw, stride, t, b, l, r, int(partial), act, slope, inp, filt, out)
+    ho, wo = L.out_hw()
+    if C_ % CB == 0 or C_ in (1, 2, 3):
+        _need(inp, batch * C_ * H * W, name + " input")
+        _need(filt, K * C_ * kh * kw, name + " filter")
+    if K % CB == 0:
+        _need(out, batch * K * ho * wo, name + " output")
+    fn = lib().small_b200_conv2d_u8 if _is_q(out) else lib().small_b200_conv2d_f32
+    check(fn(C.byref(L), _ptr(inp), _ptr(filt), _ptr(bias), _ptr(out), _stream(stream)))
+
+
+def Conv2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
+           output_channels, input_channels, input_height, input_width,
+           input_buf, filter_buf, output_buf, *, batch=1, stream=None):
+    """small::Conv2D (interface_abstract.hpp:46-221 float, :229-404 quint8)."""
+    _conv("Conv2D", False, kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
+          output_channels, input_channels, input_height, input_width, input_buf, filter_buf,
+          output_buf, None, ACT_NONE, 0.0, batch, stream)
+
+
+def PartialConv2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
+                  output_channels, input_channels, input_height, input_width,
+                  input_buf, filter_buf, output_buf, *, batch=1, stream=None):
+    """small::PartialConv2D (:416-587): accumulates onto the existing output."""
+    _conv("PartialConv2D", True, kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
+          output_channels, input_channels, input_height, input_width, input_buf, filter_buf,
+          output_buf, None, ACT_NONE, 0.0, batch, stream)
+
+
+def Conv2D_ReLU(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
+                output_channels, input_channels, input_height, input_width,
+                input_buf, filter_buf, output_buf, *, batch=1, stream=None):
+    """small::Conv2D_ReLU (fused_interface_abstract.hpp:55)."""
+    _conv("Conv2D_ReLU", False, kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
+          output_channels, input_channels, input_height, input_width, input_buf, filter_buf,
+          output_buf, None, ACT_RELU, 0.0, batch, stream)
+
+
+def Conv2D_Bias_ReLU(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
+                     output_channels, input_channels, input_height, input_width,
+                     input_buf, filter_buf, bias_buf, output_buf, *, batch=1, stream=None):
+    """small::Conv2D_Bias_ReLU (fused_interface_abstract.hpp:217)."""
+    _conv("Conv2D_Bias_ReLU", False, kernel_height, kernel_width, stride, t_pad, b_pad, l_pad,
+          r_pad, output_channels, input_channels, input_height, input_width, input_buf,
+          filter_buf, output_buf, bias_buf, ACT_RELU, 0.0, batch, stream)
+
+
+def Conv2D_Bias_Activation(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
+                           output_channels, input_channels, input_height, input_width,
+                           input_buf, filter_buf, bias_buf, output_buf, *, activation=ACT_NONE,
+                           negative_slope=0.0, batch=1, stream=None):
+    """The single-element-before / -after slots of the reference's fused loop nest
+    (abstract_layer.hpp:131-177) with bias before and none / ReLU / LeakyReLU after; equals
+    the unfused chain Bias -> PartialConv2D -> activation of Conv2DLayer.hpp:827-878.
+    For quint8 buffers bias_buf is an int32 torch tensor added to the accumulator seed."""
+    _conv("Conv2D_Bias_Activation", False, kernel_height, kernel_width, stride, t_pad, b_pad,
+          l_pad, r_pad, output_channels, input_channels, input_height, input_width, input_buf,
+          filter_buf, output_buf, bias_buf, activation, negative_slope, batch, stream)
+
+
+# --------------------------------------------------------------------------- per-channel windows
+def _window(fn_f32, fn_u8, name, has_filter, kh, kw, stride, t, b, l, r, C_, H, W, inp, filt, out,
+            bias, partial, act, slope, batch, stream):
+    L = _layer(batch, C_, C_, H, W, kh, kw, stride, t, b, l, r, int(partial), act, slope, inp, filt, out)
+    ho, wo = L.out_hw()
+    if C_ % CB == 0:
+        _need(inp, batch * C_ * H * W, name + " input")
+        _need(out, batch * C_ * ho * wo, name + " output")
+    fn = getattr(lib(), fn_u8 if _is_q(out) else fn_f32)
+    if has_filter:
+        check(fn(C.byref(L), _ptr(inp), _ptr(filt), _ptr(bias), _ptr(out), _stream(stream)))
+    else:
+        check(fn(C.byref(L), _ptr(inp), _ptr(out), _stream(stream)))
+
+
+def DepthwiseConv2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
+                    input_channels, input_height, input_width,
+                    input_buf, filter_buf, output_buf, *, batch=1, stream=None):
+    """small::DepthwiseConv2D (:994 float, :1059 quint8)."""
+    _window("small_b200_dwconv2d_f32", "small_b200_dwconv2d_u8", "DepthwiseConv2D", True,
+            kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad, input_channels,
+            input_height, input_width, input_buf, filter_buf, output_buf, None, False, ACT_NONE,
+            0.0, batch, stream)
+
+
+def PartialDepthwiseConv2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
+                           input_channels, input_height, input_width,
+                           input_buf, filter_buf, output_buf, *, batch=1, stream=None):
+    """small::PartialDepthwiseConv2D (:1127), float only."""
+    if _is_q(output_buf):
+        raise ValueError("PartialDepthwiseConv2D<quint8> ERROR: not provided.")
+    _window("small_b200_dwconv2d_f32", "small_b200_dwconv2d_u8", "PartialDepthwiseConv2D", True,
+            kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad, input_channels,
+            input_height, input_width, input_buf, filter_buf, output_buf, None, True, ACT_NONE,
+            0.0, batch, stream)
+
+
+def DepthwiseConv2D_Bias_Activation(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad,
+                                    r_pad, input_channels, input_height, input_width,
+                                    input_buf, filter_buf, bias_buf, output_buf, *,
+                                    activation=ACT_NONE, negative_slope=0.0, batch=1, stream=None):
+    """small::DepthwiseConv2D_ReLU / _Bias_ReLU (fused_interface_abstract.hpp:1332, :1419)."""
+    _window("small_b200_dwconv2d_f32", "small_b200_dwconv2d_u8", "DepthwiseConv2D", True,
+            kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad, input_channels,
+            input_height, input_width, input_buf, filter_buf, output_buf, bias_buf, False,
+            activation, negative_slope, batch, stream)
+
+
+def MaxPool2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
+              input_channels, input_height, input_width, input_buf, output_buf, *,
+              batch=1, stream=None):
+    """small::MaxPool2D (:778 float, :843 quint8)."""
+    _window("small_b200_maxpool2d_f32", "small_b200_maxpool2d_u8", "MaxPool2D", False,
+            kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad, input_channels,
+            input_height, input_width, input_buf, None, output_buf, None, False, ACT_NONE, 0.0,
+            batch, stream)
+
+
+def AveragePool2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
+                  input_channels, input_height, input_width, input_buf, output_buf, *,
+                  batch=1, stream=None):
+    """small::AveragePool2D (:910, float); the quint8 form has no counterpart in the reference."""
+    _window("small_b200_avgpool2d_f32", "small_b200_avgpool2d_u8", "AveragePool2D", False,
+            kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad, input_channels,
+            input_height, input_width, input_buf, None, output_buf, None, False, ACT_NONE, 0.0,
+            batch, stream)
+
+
+# --------------------------------------------------------------------------- elementwise
+def _chan_check(name, channels):
+    if channels % CB != 0:
+        raise ValueError(f"{name} ERROR: in_channels unsupported.")
+
+
+def ReLUActivation(input_channels, input_height, input_width, input_buf, output_buf, *,
+                   batch=1, stream=None):
+    """small::ReLUActivation (:1541 float; :1577 quint8 = requantised max(a + zero, 0))."""
+    n = batch * input_channels * input_height * input_width
+    if _is_q(output_buf):
+        _chan_check("ReLUActivation<quint8>", input_channels)
+        L = _layer(batch, input_channels, input_channels, input_height, input_width, 1, 1, 1,
+                   0, 0, 0, 0, inp=input_buf, out=output_buf)
+        check(lib().small_b200_relu_u8(n, C.byref(L), _ptr(input_buf), _ptr(output_buf), _stream(stream)))
+    else:
+        _chan_check("ReLUActivation<float>", input_channels)
+        check(lib().small_b200_relu_f32(n, _ptr(input_buf), _ptr(output_buf), _stream(stream)))
+
+
+def LeakyReLUActivation(input_channels, input_height, input_width, input_buf, filter_buf,
+                        output_buf, *, batch=1, stream=None):
+    """small::LeakyReLUActivation (:1616): the slope arrives as a one-element buffer (or a float)."""
+    _chan_check("LeakyReLUActivation<float>", input_channels)
+    slope = float(filter_buf.t[0].item()) if isinstance(filter_buf, FloatBuffer) else float(filter_buf)
+    n = batch * input_channels * input_height * input_width
+    check(lib().small_b200_leaky_relu_f32(n, _ptr(input_buf), slope, _ptr(output_buf), _stream(stream)))
+
+
+def Accum(input_channels, input_height, input_width, input_buf, output_buf, *, batch=1, stream=None):
+    """small::Accum (:1950): output += input."""
+    _chan_check("Accum<float>", input_channels)
+    n = batch * input_channels * input_height * input_width
+    check(lib().small_b200_accum_f32(n, _ptr(input_buf), _ptr(output_buf), _stream(stream)))
+
+
+def Bias(num_channels, output_height, output_width, input_buf, output_buf, *, batch=1, stream=None):
+    """small::Bias (:1992): output[c, h, w] = bias[c]."""
+    check(lib().small_b200_bias_f32(batch, num_channels, output_height, output_width,
+                                    _ptr(input_buf), 0, _ptr(output_buf), _stream(stream)))
+
+
+def PartialBias(num_channels, output_height, output_width, input_buf, output_buf, *, batch=1,
+                stream=None):
+    """small::PartialBias (:2035): output[c, h, w] += bias[c]."""
+    check(lib().small_b200_bias_f32(batch, num_channels, output_height, output_width,
+                                    _ptr(input_buf), 1, _ptr(output_buf), _stream(stream)))
+
+
+def UpSample2D(scale_factor, input_channels, input_height, input_width, input_buf, output_buf, *,
+               batch=1, stream=None):
+    """small::UpSample2D (:1845): scale 1 copies, scale 2 is nearest-neighbour, others throw."""
+    if scale_factor == 1:
+        n = batch * input_channels * input_height * input_width
+        check(lib().small_b200_memcpy_d2d(_ptr(output_buf), _ptr(input_buf), n * 4, _stream(stream)))
+    elif scale_factor == 2:
+        check(lib().small_b200_upsample2d_f32(batch, input_channels, input_height, input_width,
+                                              _ptr(input_buf), _ptr(output_buf), _stream(stream)))
+    else:
+        raise ValueError("Upsample<float> ERROR: scale factor unsupported (only 1 or 2).")
+
+
+def SoftMax(input_channels, input_height, input_width, input_buf, output_buf, *, batch=1, stream=None):
+    """small::SoftMax (:1778): normalised over ALL input_channels*height*width elements of an
+    image.  Channels padded up to the block size by a layer class would add exp(0) terms, so
+    callers pass the effective element count by keeping padded logits out of the tensor."""
+    _chan_check("SoftMax<float>", input_channels)
+    check(lib().small_b200_softmax_f32(batch, input_channels * input_height * input_width,
+                                       _ptr(input_buf), _ptr(output_buf), _stream(stream)))
+
+
+def Concat(input0_channels, input1_channels, input_height, input_width, input0_buf, input1_buf,
+           output_buf, *, batch=1, stream=None):
+    """small::Concat (:2072): channel concatenation of two packed buffers."""
+    esz = input0_buf.t.element_size()
+    b0 = input0_channels * input_height * input_width * esz
+    b1 = input1_channels * input_height * input_width * esz
+    check(lib().small_b200_concat(batch, b0, _ptr(input0_buf), b1, _ptr(input1_buf),
+                                  _ptr(output_buf), _stream(stream)))
+
+
+def Dense(output_elements, input_elements, input_buf, filter_buf, output_buf, *, batch=1, stream=None):
+    """A fully connected layer the way the reference's models build it: Conv2D 1x1 on a 1x1
+    image with FILTER_FC packing (include/small/models/DSCNNTiny.hpp:255-263).  The
+    reference's own small::Dense (:2113) is an uncalled placeholder that instantiates a
+    depthwise scaling, not a matrix-vector product."""
+    Conv2D(1, 1, 1, 0, 0, 0, 0, output_elements, input_elements, 1, 1, input_buf, filter_buf,
+           output_buf, batch=batch, stream=stream)

@@ -1,0 +1,137 @@
+"""uint8 parity of the CUDA path (through the C ABI) against the oracle: BIT-EXACT.
+
+The oracle itself is pinned bit-for-bit to the compiled reference in
+tests/test_oracle_reference.py; here it runs with the B200 blocking (16), which for integer
+arithmetic gives the same numbers as the reference's blocking of 1
+(test_uint8_blocking_invariance)."""
+import numpy as np
+import pytest
+
+from oracle.bindings import Quant, same_pads, shape
+from smallframework_b200 import interface as S
+from smallframework_b200 import packing as P
+from tests.gpu_util import CB, qbuf
+from tests.util import sample_window_cases
+
+pytestmark = pytest.mark.gpu
+
+
+def _out(n, q):
+    O = S.QUInt8Buffer(n)
+    O.lshift, O.rshift, O.multiplier = q.lshift, q.rshift, q.multiplier
+    return O
+
+
+def _quant(rng, taps_c):
+    """Multiplier / shift so that outputs spread over 0..255 for the given reduction length."""
+    zi = int(rng.choice([0, -128, 128, 5])); zf = int(rng.choice([-128, 0, 128, -7]))
+    rshift = int(np.clip(np.round(np.log2(max(taps_c, 1) * 64 * 64 / 128)), 0, 20))
+    return Quant(zi, zf, 0, rshift, int(rng.integers(1 << 30, (1 << 31) - 1)), 0)
+
+
+CONV_CASES = [
+    # C, K, H, W, Fh, Fw, stride, pads, batch
+    (64, 64, 25, 5, 1, 1, 1, "valid", 5),     # DS-CNN pointwise
+    (1, 64, 49, 10, 10, 4, 2, "same", 3),     # DS-CNN stem (more than one padded row per side)
+    (64, 16, 1, 1, 1, 1, 1, "valid", 7),      # DS-CNN dense head (12 padded to 16)
+    (16, 32, 9, 11, 3, 3, 1, "same", 2),
+    (32, 16, 12, 12, 3, 3, 2, "same", 2),
+    (3, 16, 16, 16, 3, 3, 2, "same", 2),
+    (128, 128, 6, 6, 1, 1, 1, "valid", 4),
+    (16, 16, 7, 5, 5, 3, 1, (2, 2, 1, 1), 1),
+    (256, 256, 3, 3, 1, 1, 1, "valid", 3),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES, ids=lambda c: "C{}_K{}_{}x{}_k{}x{}_s{}_{}_n{}".format(*[
+    "".join(map(str, v)) if isinstance(v, tuple) else v for v in c]))
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_conv2d_u8(oracle, case, with_bias):
+    C, K, H, W, Fh, Fw, s, pm, N = case
+    pads = same_pads(H, W, Fh, Fw, s) if pm == "same" else (0, 0, 0, 0) if pm == "valid" else pm
+    rng = np.random.default_rng(abs(hash((case, with_bias))) % (1 << 31))
+    q = _quant(rng, C * Fh * Fw)
+    x = P.pack_activation(rng.integers(0, 256, (N, C, H, W)).astype(np.uint8))
+    w = P.pack_conv_filter(rng.integers(0, 256, (K, C, Fh, Fw)).astype(np.uint8))
+    bias = rng.integers(-1024, 1025, K).astype(np.int32) if with_bias else None
+    sh = shape(C, K, H, W, Fh, Fw, s, pads, CB)
+    ho, wo = sh.out_hw()
+    I, F, O = qbuf(x, q.zero_in), qbuf(w, q.zero_filt), _out(N * K * ho * wo, q)
+    if with_bias:
+        import torch
+        S.Conv2D_Bias_Activation(Fh, Fw, s, *pads, K, C, H, W, I, F,
+                                 torch.from_numpy(bias).cuda(), O, batch=N)
+    else:
+        S.Conv2D(Fh, Fw, s, *pads, K, C, H, W, I, F, O, batch=N)
+    want = np.stack([oracle.conv2d_u8(sh, q, x[n], w, bias=bias) for n in range(N)])
+    got = O.numpy().reshape(N, -1)
+    assert np.array_equal(got, want)
+    assert want.min() < want.max()  # the case is not degenerate (all clamped)
+
+
+WIN_CASES = sample_window_cases(np.random.default_rng(33), 16, channels=(16, 64), first_layer=False,
+                                max_hw=16)
+
+
+@pytest.mark.parametrize("c", WIN_CASES, ids=lambda c: "C{}_{}x{}_k{}x{}_s{}_p{}".format(
+    *c[:6], "".join(map(str, c[6]))))
+def test_depthwise_pools_relu_u8(oracle, c):
+    C, H, W, Fh, Fw, s, pads = c
+    N = 2
+    rng = np.random.default_rng(abs(hash(c)) % (1 << 31))
+    q = _quant(rng, Fh * Fw)
+    x = P.pack_activation(rng.integers(0, 256, (N, C, H, W)).astype(np.uint8))
+    w = P.pack_dw_filter(rng.integers(0, 256, (C, Fh, Fw)).astype(np.uint8))
+    sh = shape(C, C, H, W, Fh, Fw, s, pads, CB)
+    ho, wo = sh.out_hw()
+    I, F, O = qbuf(x, q.zero_in), qbuf(w, q.zero_filt), _out(N * C * ho * wo, q)
+    S.DepthwiseConv2D(Fh, Fw, s, *pads, C, H, W, I, F, O, batch=N)
+    want = np.stack([oracle.conv2d_u8(sh, q, x[n], w, depthwise=True) for n in range(N)])
+    assert np.array_equal(O.numpy().reshape(N, -1), want)
+    qp = Quant(q.zero_in, 0, 0, 1, 1 << 30, 0)  # spreads a + zero over the output range
+    O = _out(N * C * ho * wo, qp)
+    S.MaxPool2D(Fh, Fw, s, *pads, C, H, W, I, O, batch=N)
+    want = np.stack([oracle.pool2d_u8(sh, qp, x[n]) for n in range(N)])
+    assert np.array_equal(O.numpy().reshape(N, -1), want)
+    qa = Quant(q.zero_in, 0, 0, int(np.ceil(np.log2(Fh * Fw))) + 1, 1 << 30, 0)
+    O = _out(N * C * ho * wo, qa)
+    S.AveragePool2D(Fh, Fw, min(s, 3), *pads, C, H, W, I, O, batch=N)
+    want = np.stack([oracle.pool2d_u8(sh, qa, x[n], average=True) for n in range(N)])
+    assert np.array_equal(O.numpy().reshape(N, -1), want)
+    O = _out(x.size, qp)
+    S.ReLUActivation(C, H, W, I, O, batch=N)
+    assert np.array_equal(O.numpy(), oracle.relu_u8(qp, x.ravel()))
+
+
+def test_default_constructed_buffers_match_the_reference_defaults(oracle):
+    """zero 128, multiplier 1077952576, rshift 6 (QUInt8Buffer.hpp:234-272)."""
+    b = S.QUInt8Buffer(16)
+    assert (b.zero(), b.multiplier, b.lshift, b.rshift) == (128, 1077952576, 0, 6)
+    rng = np.random.default_rng(3)
+    C, K, H, W = 16, 16, 6, 7
+    x = P.pack_activation(rng.integers(0, 256, (C, H, W)).astype(np.uint8))
+    w = P.pack_conv_filter(rng.integers(0, 256, (K, C, 3, 3)).astype(np.uint8))
+    pads = same_pads(H, W, 3, 3, 1)
+    I, F, O = S.QUInt8Buffer(data=x), S.QUInt8Buffer(data=w), S.QUInt8Buffer(K * H * W)
+    S.Conv2D(3, 3, 1, *pads, K, C, H, W, I, F, O)
+    q = Quant(128, 128, 0, 6, 1077952576, 0)
+    assert np.array_equal(O.numpy(), oracle.conv2d_u8(shape(C, K, H, W, 3, 3, 1, pads, CB), q, x, w))
+
+
+def test_full_batch_pointwise_matches_single_images(oracle):
+    """DS-CNN pointwise layer at the BASELINE batch (4096): spot-check images against the
+    oracle and check that the batched result equals per-image calls."""
+    rng = np.random.default_rng(12)
+    C = K = 64; H, W, N = 25, 5, 4096
+    q = Quant(0, -128, 0, 7, 1400000000, 0)
+    x = rng.integers(0, 256, (N, C * H * W)).astype(np.uint8)
+    w = P.pack_conv_filter(rng.integers(0, 256, (K, C, 1, 1)).astype(np.uint8))
+    sh = shape(C, K, H, W, 1, 1, 1, (0, 0, 0, 0), CB)
+    I, F, O = qbuf(x, q.zero_in), qbuf(w, q.zero_filt), _out(N * K * H * W, q)
+    S.Conv2D(1, 1, 1, 0, 0, 0, 0, K, C, H, W, I, F, O, batch=N)
+    got = O.numpy().reshape(N, -1)
+    for n in (0, 1, 777, 4095):
+        assert np.array_equal(got[n], oracle.conv2d_u8(sh, q, x[n], w))
+    O1 = _out(K * H * W, q)
+    S.Conv2D(1, 1, 1, 0, 0, 0, 0, K, C, H, W, qbuf(x[2048], q.zero_in), F, O1)
+    assert np.array_equal(O1.numpy(), got[2048])
