@@ -1,0 +1,278 @@
+"""Layer chains of the benchmark configurations and their executor.
+
+The reference drives the functional interface from fixed layer lists with two ping-pong
+buffers (include/small/models/TinyYoloV2.hpp:92-135, demo/tinyyolov2.cpp:263-386,
+include/small/models/DSCNNTiny.hpp).  `Chain` does the same against the C ABI: packed
+weights are uploaded once, every layer call is enqueued on one stream, and the whole
+sequence is captured in a CUDA graph so that a step is a single graph launch.
+
+Weights are random (seeded); there are no checkpoints.  A layer list is a list of dicts:
+  op      conv | dwconv | maxpool | avgpool
+  C, K    input / output channels (K = effective count; filters are zero-padded to a
+          multiple of 16 like include/small/Conv2DLayer.hpp:393-404 does)
+  H, W, Fh, Fw, stride, pads(t, b, l, r)
+  act     0 none, 1 ReLU, 2 LeakyReLU (slope)
+  w, b    unpacked [K, C, Fh, Fw] (dw: [C, Fh, Fw]) weights and per-channel bias
+  q       uint8 only: dict(zero_in, zero_filt, lshift, rshift, multiplier)
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import Layer, check, lib
+from .packing import CB, calc_padding, output_dim, pack_conv_filter, pack_dw_filter
+
+
+def _same(H, W, Fh, Fw, s):
+    t, b = calc_padding(H, Fh, s)
+    l, r = calc_padding(W, Fw, s)
+    return (t, b, l, r)
+
+
+def _out_hw(L):
+    t, b, l, r = L["pads"]
+    return (output_dim(L["H"], t, b, L["Fh"], L["stride"]),
+            output_dim(L["W"], l, r, L["Fw"], L["stride"]))
+
+
+def _he(rng, shape_, fan_in):
+    return rng.normal(0.0, math.sqrt(2.0 / fan_in), shape_).astype(np.float32)
+
+
+# --------------------------------------------------------------------------- Tiny-YOLOv2 fp32
+def tiny_yolov2(seed=4, size=416):
+    """Eight 3x3 same-pad convolutions (16..1024, 1024) each with bias + LeakyReLU(0.1);
+    2x2 max pool after the first six (stride 2 five times, then stride 1 with pads
+    (0,1,0,1), demo/tinyyolov2.cpp:504-507); a final 1x1 convolution to 125 channels.
+    He-normal weights, biases uniform in [-0.1, 0.1]."""
+    rng = np.random.default_rng(seed)
+    chans = [16, 32, 64, 128, 256, 512, 1024, 1024]
+    layers, c, h = [], 3, size
+    for i, k in enumerate(chans):
+        layers.append(dict(op="conv", name=f"conv{i + 1}", C=c, K=k, H=h, W=h, Fh=3, Fw=3, stride=1,
+                           pads=_same(h, h, 3, 3, 1), act=2, slope=0.1,
+                           w=_he(rng, (k, c, 3, 3), c * 9),
+                           b=rng.uniform(-0.1, 0.1, k).astype(np.float32)))
+        c = k
+        if i < 5:
+            layers.append(dict(op="maxpool", name=f"maxpool{i + 1}", C=c, K=c, H=h, W=h, Fh=2, Fw=2,
+                               stride=2, pads=(0, 0, 0, 0)))
+            h //= 2
+        elif i == 5:
+            layers.append(dict(op="maxpool", name="maxpool6", C=c, K=c, H=h, W=h, Fh=2, Fw=2,
+                               stride=1, pads=(0, 1, 0, 1)))
+    layers.append(dict(op="conv", name="conv9", C=c, K=125, H=h, W=h, Fh=1, Fw=1, stride=1,
+                       pads=(0, 0, 0, 0), act=0, slope=0.0, w=_he(rng, (125, c, 1, 1), c),
+                       b=rng.uniform(-0.1, 0.1, 125).astype(np.float32)))
+    return layers
+
+
+# --------------------------------------------------------------------------- DS-CNN uint8
+def _requant_params(scale):
+    """scale = multiplier * 2^-31 * 2^-rshift with the multiplier in [2^30, 2^31)."""
+    rshift = int(np.clip(math.floor(-math.log2(scale)), 0, 30))
+    mult = int(np.clip(round(scale * 2.0 ** (31 + rshift)), 1, (1 << 31) - 1))
+    return 0, rshift, mult
+
+
+def _calibrate(x, w, bias, zi, zf, stride, pads, depthwise):
+    """int64 accumulators of a few images, computed with torch on the CPU (set-up only):
+    zero padding of the SHIFTED input equals skipping padded taps."""
+    xs = torch.from_numpy(x.astype(np.float64) + zi)
+    ws = torch.from_numpy(w.astype(np.float64) + zf)
+    t, b, l, r = pads
+    xs = torch.nn.functional.pad(xs, (l, r, t, b))
+    groups = xs.shape[1] if depthwise else 1
+    if depthwise:
+        ws = ws[:, None]
+    acc = torch.nn.functional.conv2d(xs, ws, stride=stride, groups=groups)
+    return acc.numpy() + bias.astype(np.float64)[None, :, None, None]
+
+
+def ds_cnn(seed=1, calib_images=8):
+    """DS-CNN keyword spotting, uint8: stem 10x4 stride 2 same-pad to 64 channels; four blocks
+    of depthwise 3x3 + pointwise 1x1 (64 channels); average pool 25x5; dense 64 -> 12.
+    Every convolution ends in the requantisation whose clamp to [0, 255] is the ReLU.
+    Weights are uniform bytes with zero point 128, which in the reference's convention of
+    ADDED offsets (intrinsics_quint8.h:201) is zero_filt = -128; the network input has zero
+    point 128 (zero_in = -128), later activations 0.  Biases are int32 in [-1024, 1024].
+    Multipliers are calibrated on a few seeded images so activations span 0..255."""
+    rng = np.random.default_rng(seed)
+    x = rng.integers(0, 256, (calib_images, 1, 49, 10)).astype(np.uint8)
+    layers = []
+
+    def add(op, name, C_, K, H, W, Fh, Fw, s, pads, zi, cur):
+        depthwise = op == "dwconv"
+        wshape = (C_, Fh, Fw) if depthwise else (K, C_, Fh, Fw)
+        w = rng.integers(0, 256, wshape).astype(np.uint8)
+        b = rng.integers(-1024, 1025, K).astype(np.int32)
+        acc = _calibrate(cur, w, b, zi, -128, s, pads, depthwise)
+        top = max(float(np.percentile(acc, 99.9)), 1.0)
+        lshift, rshift, mult = _requant_params(255.0 / top)
+        layers.append(dict(op=op, name=name, C=C_, K=K, H=H, W=W, Fh=Fh, Fw=Fw, stride=s, pads=pads,
+                           act=0, slope=0.0, w=w, b=b,
+                           q=dict(zero_in=zi, zero_filt=-128, lshift=lshift, rshift=rshift,
+                                  multiplier=mult)))
+        nxt = np.clip(np.rint(acc * (mult * 2.0 ** (-31 - rshift))), 0, 255).astype(np.uint8)
+        return nxt
+
+    cur = add("conv", "stem", 1, 64, 49, 10, 10, 4, 2, _same(49, 10, 10, 4, 2), -128, x)
+    for i in range(4):
+        cur = add("dwconv", f"dw{i + 1}", 64, 64, 25, 5, 3, 3, 1, _same(25, 5, 3, 3, 1), 0, cur)
+        cur = add("conv", f"pw{i + 1}", 64, 64, 25, 5, 1, 1, 1, (0, 0, 0, 0), 0, cur)
+    # average pool: sum of 125 taps requantised by 1/125
+    lshift, rshift, mult = _requant_params(1.0 / 125.0)
+    layers.append(dict(op="avgpool", name="avgpool", C=64, K=64, H=25, W=5, Fh=25, Fw=5, stride=1,
+                       pads=(0, 0, 0, 0),
+                       q=dict(zero_in=0, zero_filt=0, lshift=lshift, rshift=rshift, multiplier=mult)))
+    pooled = np.clip(np.rint(cur.astype(np.float64).sum(axis=(2, 3), keepdims=True) / 125.0), 0, 255
+                     ).astype(np.uint8)
+    add("conv", "dense", 64, 12, 1, 1, 1, 1, 1, (0, 0, 0, 0), 0, pooled)
+    return layers
+
+
+def input_shape(layers):
+    L = layers[0]
+    return (L["C"], L["H"], L["W"])
+
+
+def output_shape(layers):
+    L = layers[-1]
+    ho, wo = _out_hw(L)
+    return (L["K"], ho, wo)
+
+
+def padded(k):
+    return -(-k // CB) * CB
+
+
+def algorithmic_work(L, elt):
+    """(flops, bytes) of one image: 2*Ho*Wo*K*C*Fh*Fw for a dense convolution, all taps
+    counted; bytes = input + output activations plus weights and bias once per launch
+    (returned separately as the third value)."""
+    ho, wo = _out_hw(L)
+    taps = L["Fh"] * L["Fw"]
+    if L["op"] == "conv":
+        flops = 2 * ho * wo * L["K"] * L["C"] * taps
+        wbytes = L["K"] * L["C"] * taps * elt + L["K"] * 4
+    elif L["op"] == "dwconv":
+        flops = 2 * ho * wo * L["C"] * taps
+        wbytes = L["C"] * taps * elt + L["C"] * 4
+    else:
+        flops = ho * wo * L["C"] * taps
+        wbytes = 0
+    abytes = (L["C"] * L["H"] * L["W"] + L["K"] * ho * wo) * elt
+    return flops, abytes, wbytes
+
+
+# --------------------------------------------------------------------------- executor
+class Chain:
+    """A layer list bound to device memory for a fixed batch.
+
+    enqueue(stream) issues every layer through the C ABI; capture() records that sequence
+    into a CUDA graph; launch() replays it.  `x` (input) and `y` (output) are the device
+    tensors at the two ends."""
+
+    def __init__(self, layers, batch, dtype="f32", device="cuda"):
+        self.layers, self.batch, self.dtype = layers, batch, dtype
+        self.tdtype = torch.float32 if dtype == "f32" else torch.uint8
+        self.elt = 4 if dtype == "f32" else 1
+        self.dev = torch.device(device)
+        self.stream = torch.cuda.Stream(device=self.dev)
+        c, h, w = input_shape(layers)
+        self.x = torch.zeros(batch * c * h * w, dtype=self.tdtype, device=self.dev)
+        max_act = 0
+        self.params = []
+        for L in layers:
+            ho, wo = _out_hw(L)
+            kp = padded(L["K"])
+            max_act = max(max_act, batch * kp * ho * wo)
+            wt = bs = None
+            if L["op"] == "conv":
+                wpad = np.zeros((kp,) + L["w"].shape[1:], L["w"].dtype)
+                wpad[:L["K"]] = L["w"]
+                if dtype == "u8" and kp != L["K"]:
+                    # a padded filter must contribute nothing: byte value = -zero_filt
+                    wpad[L["K"]:] = np.uint8(-L["q"]["zero_filt"]) if -L["q"]["zero_filt"] in range(256) else 0
+                wt = torch.from_numpy(pack_conv_filter(wpad)).to(self.dev)
+            elif L["op"] == "dwconv":
+                wt = torch.from_numpy(pack_dw_filter(L["w"])).to(self.dev)
+            if L.get("b") is not None:
+                bp = np.zeros(kp, L["b"].dtype)
+                bp[:L["K"]] = L["b"]
+                bs = torch.from_numpy(bp).to(self.dev)
+            self.params.append((wt, bs))
+        self.bufs = [torch.zeros(max_act, dtype=self.tdtype, device=self.dev) for _ in range(2)]
+        self.graph = None
+        self.y = None
+        self.kernels_per_step = 0
+        self._descs = []
+
+    def _desc(self, L, cin):
+        t, b, l, r = L["pads"]
+        q = L.get("q", {})
+        return Layer(self.batch, cin, padded(L["K"]), L["H"], L["W"], L["Fh"], L["Fw"], L["stride"],
+                     t, b, l, r, 0, L.get("act", 0), L.get("slope", 0.0),
+                     q.get("zero_in", 0), q.get("zero_filt", 0), q.get("lshift", 0),
+                     q.get("rshift", 0), q.get("multiplier", 0), 0)
+
+    def enqueue_layer(self, i, src, dst, stream):
+        L = self.layers[i]
+        wt, bs = self.params[i]
+        cin = L["C"] if i == 0 else padded(L["C"])
+        d = self._desc(L, cin)
+        sfx = "f32" if self.dtype == "f32" else "u8"
+        l = lib()
+        p = lambda t: t.data_ptr() if t is not None else None
+        if L["op"] == "conv":
+            check(getattr(l, f"small_b200_conv2d_{sfx}")(C.byref(d), p(src), p(wt), p(bs), p(dst), stream))
+        elif L["op"] == "dwconv":
+            check(getattr(l, f"small_b200_dwconv2d_{sfx}")(C.byref(d), p(src), p(wt), p(bs), p(dst), stream))
+        elif L["op"] == "maxpool":
+            check(getattr(l, f"small_b200_maxpool2d_{sfx}")(C.byref(d), p(src), p(dst), stream))
+        elif L["op"] == "avgpool":
+            check(getattr(l, f"small_b200_avgpool2d_{sfx}")(C.byref(d), p(src), p(dst), stream))
+        else:
+            raise ValueError(L["op"])
+
+    def enqueue(self, stream=None):
+        stream = self.stream.cuda_stream if stream is None else stream
+        src = self.x
+        n0 = _lib.launch_count()
+        for i in range(len(self.layers)):
+            dst = self.bufs[i & 1]
+            self.enqueue_layer(i, src, dst, stream)
+            src = dst
+        self.kernels_per_step = _lib.launch_count() - n0
+        k, ho, wo = output_shape(self.layers)
+        self.y = src[: self.batch * padded(k) * ho * wo]
+        return self.y
+
+    def capture(self):
+        l = lib()
+        self.stream.synchronize()
+        gp = C.c_void_p()
+        check(l.small_b200_graph_begin(self.stream.cuda_stream))
+        try:
+            self.enqueue()
+        finally:
+            check(l.small_b200_graph_end(self.stream.cuda_stream, C.byref(gp)))
+        self.graph = gp
+        return self
+
+    def launch(self):
+        if self.graph is None:
+            self.capture()
+        check(lib().small_b200_graph_launch(self.graph, self.stream.cuda_stream))
+
+    def __del__(self):
+        try:
+            if self.graph is not None:
+                lib().small_b200_graph_destroy(self.graph)
+        except Exception:
+            pass

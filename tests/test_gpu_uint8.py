@@ -23,10 +23,16 @@ def _out(n, q):
 
 
 def _quant(rng, taps_c):
-    """Multiplier / shift so that outputs spread over 0..255 for the given reduction length."""
+    """Zero points plus a multiplier / shift that spread the accumulator over 0..255 for a
+    reduction of `taps_c` terms of uniform bytes."""
     zi = int(rng.choice([0, -128, 128, 5])); zf = int(rng.choice([-128, 0, 128, -7]))
-    rshift = int(np.clip(np.round(np.log2(max(taps_c, 1) * 64 * 64 / 128)), 0, 20))
-    return Quant(zi, zf, 0, rshift, int(rng.integers(1 << 30, (1 << 31) - 1)), 0)
+    ma, mw = 127.5 + zi, 127.5 + zf
+    var = (74.0 ** 2 + ma ** 2) * (74.0 ** 2 + mw ** 2) - (ma * mw) ** 2
+    top = abs(taps_c * ma * mw) + 2.0 * np.sqrt(taps_c * var)
+    scale = 255.0 / top                      # = multiplier * 2^-31 * 2^-rshift
+    rshift = int(np.clip(np.floor(-np.log2(scale)), 0, 30))
+    mult = int(np.clip(scale * 2.0 ** (31 + rshift), 1 << 20, (1 << 31) - 1))
+    return Quant(zi, zf, 0, rshift, mult, 0)
 
 
 CONV_CASES = [
