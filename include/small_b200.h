@@ -79,6 +79,11 @@ typedef struct small_b200_layer
 const char *small_b200_last_error(void);
 int small_b200_device_count(int *count);
 int small_b200_set_device(int device);
+/* Synchronises the device and reports whether any kernel gave up on a bounded device-side
+ * wait (tensor-core kernels poll their mbarriers with an iteration limit instead of
+ * spinning forever).  *status = 0 when all is well; otherwise SMALL_B200_DEVICE_TIMEOUT is
+ * returned.  No counterpart in the reference (a CPU loop nest has nothing to wait for). */
+int small_b200_device_status(int *status);
 /* Number of kernels this library has launched in this process since it was loaded. */
 uint64_t small_b200_launch_count(void);
 

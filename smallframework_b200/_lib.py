@@ -42,6 +42,7 @@ _LP = C.POINTER(Layer)
 SIGNATURES = {
     "small_b200_device_count": [C.POINTER(C.c_int)],
     "small_b200_set_device": [C.c_int],
+    "small_b200_device_status": [C.POINTER(C.c_int)],
     "small_b200_malloc": [_SZ, C.POINTER(_VP)],
     "small_b200_malloc_managed": [_SZ, C.POINTER(_VP)],
     "small_b200_malloc_host": [_SZ, C.POINTER(_VP)],
@@ -114,6 +115,13 @@ def check(rc: int):
     if rc == OUT_OF_MEMORY:
         raise MemoryError(msg)  # std::bad_alloc
     raise SmallB200Error(f"[{rc}] {msg}")
+
+
+def device_status() -> int:
+    """Synchronise and raise if a kernel gave up on a bounded wait."""
+    v = C.c_int(0)
+    check(lib().small_b200_device_status(C.byref(v)))
+    return v.value
 
 
 def launch_count() -> int:
