@@ -1,0 +1,332 @@
+// Buffer.hpp -- FloatBuffer / QUInt8Buffer of the B200 platform.
+//
+// Same public surface as the reference's CPU buffers (platforms/reference/FloatBuffer.hpp
+// :42-168, QUInt8Buffer.hpp:31-276: value/accum typedefs, blocking constants, deep copy,
+// pointer-swapping move and swap, data(), operator[], size(), zero(), and for uint8 the
+// public quantisation fields).  Storage is CUDA managed memory obtained through the C ABI,
+// so the reference's host-side helpers (pack_buffer, init, file readers) keep working on
+// data().  Layer calls are asynchronous; any host access through data() or operator[]
+// first waits for outstanding device work, and the next layer call moves a host-touched
+// buffer back to the device before launching.
+#pragma once
+
+#include <small_b200.h>
+#include <stdint.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <new>
+#include <stdexcept>
+#include <string>
+#include <type_traits>
+
+namespace small
+{
+namespace b200
+{
+// True while layer calls may still be running on the device.
+inline bool &pending()
+{
+    static bool p = false;
+    return p;
+}
+
+// Images per call for the batched extension (image-major batch); 1 = the reference.
+inline int &batch()
+{
+    static thread_local int n = 1;
+    return n;
+}
+
+struct BatchScope
+{
+    int saved;
+    explicit BatchScope(int n) : saved(batch()) { batch() = n; }
+    ~BatchScope() { batch() = saved; }
+};
+
+inline void throw_on(int rc)
+{
+    if (rc == SMALL_B200_OK)
+        return;
+    std::string msg(small_b200_last_error());
+    if (rc == SMALL_B200_INVALID_ARGUMENT)
+        throw std::invalid_argument(msg);
+    if (rc == SMALL_B200_OUT_OF_MEMORY)
+        throw std::bad_alloc();
+    throw std::runtime_error(msg);
+}
+
+inline void sync_for_host()
+{
+    if (pending())
+    {
+        throw_on(small_b200_device_sync());
+        pending() = false;
+    }
+}
+
+template <typename T>
+class ManagedArray
+{
+public:
+    ManagedArray() : m_num_elts(0), m_buffer(nullptr), m_host_touched(false) {}
+
+    explicit ManagedArray(size_t num_elts) : m_num_elts(num_elts), m_buffer(nullptr), m_host_touched(true)
+    {
+        void *p = nullptr;
+        if (SMALL_B200_OK != small_b200_malloc_managed(num_elts * sizeof(T), &p))
+            throw std::bad_alloc();
+        m_buffer = static_cast<T *>(p);
+    }
+
+    ManagedArray(ManagedArray const &other) : ManagedArray(other.m_num_elts)
+    {
+        sync_for_host();
+        if (m_num_elts)
+            std::memcpy(m_buffer, other.m_buffer, m_num_elts * sizeof(T));
+    }
+
+    ManagedArray(ManagedArray &&other) noexcept : ManagedArray() { swap(other); }
+
+    ManagedArray &operator=(ManagedArray const &other)
+    {
+        if (this != &other)
+        {
+            ManagedArray tmp(other);
+            swap(tmp);
+        }
+        return *this;
+    }
+
+    ManagedArray &operator=(ManagedArray &&other) noexcept
+    {
+        if (this != &other)
+        {
+            release();
+            swap(other);
+        }
+        return *this;
+    }
+
+    ~ManagedArray() { release(); }
+
+    size_t size() const { return m_num_elts; }
+
+    // Host views: wait for the device, remember that the host may have moved the pages.
+    T *data()
+    {
+        touch();
+        return m_buffer;
+    }
+    T const *data() const
+    {
+        touch();
+        return m_buffer;
+    }
+    T &operator[](size_t index)
+    {
+        touch();
+        return m_buffer[index];
+    }
+    T const &operator[](size_t index) const
+    {
+        touch();
+        return m_buffer[index];
+    }
+
+    void swap(ManagedArray &other) noexcept
+    {
+        std::swap(m_num_elts, other.m_num_elts);
+        std::swap(m_buffer, other.m_buffer);
+        std::swap(m_host_touched, other.m_host_touched);
+    }
+
+    // Device view for a layer call: no wait; brings host-touched pages back first.
+    T *device_ptr() const
+    {
+        if (m_host_touched && m_buffer)
+        {
+            small_b200_prefetch(m_buffer, m_num_elts * sizeof(T), nullptr);
+            m_host_touched = false;
+        }
+        pending() = true;
+        return m_buffer;
+    }
+
+private:
+    void touch() const
+    {
+        if (m_buffer)
+        {
+            sync_for_host();
+            m_host_touched = true;
+        }
+    }
+
+    void release() noexcept
+    {
+        if (m_buffer)
+        {
+            if (pending())
+            {
+                small_b200_device_sync();
+                pending() = false;
+            }
+            small_b200_free(m_buffer);
+        }
+        m_buffer = nullptr;
+        m_num_elts = 0;
+    }
+
+    size_t m_num_elts;
+    T *m_buffer;
+    mutable bool m_host_touched;
+};
+} // namespace b200
+
+//****************************************************************************
+class FloatBuffer : public b200::ManagedArray<float>
+{
+public:
+    static uint32_t const W_ob{FLOAT_W_ob};
+    static uint32_t const C_ob{FLOAT_C_ob};
+    static uint32_t const SIMD{FLOAT_SIMD};
+    static uint32_t const UNROLL{FLOAT_UNROLL};
+    static uint32_t const C_ib{FLOAT_C_ib};
+    static uint32_t const NUM_FMA{FLOAT_NUM_FMA};
+    static uint32_t const NUM_MAX{FLOAT_NUM_MAX};
+    static uint32_t const NUM_LOAD{FLOAT_NUM_LOAD};
+    static uint32_t const NUM_STORE{FLOAT_NUM_STORE};
+
+    typedef float value_type;
+    typedef float accum_type;
+
+    using b200::ManagedArray<float>::ManagedArray;
+    FloatBuffer() = default;
+
+    void swap(FloatBuffer &other) { b200::ManagedArray<float>::swap(other); }
+    inline accum_type zero() const { return (accum_type)0; }
+};
+
+//****************************************************************************
+class QUInt8Buffer : public b200::ManagedArray<uint8_t>
+{
+public:
+    static uint32_t const W_ob{QUINT8_W_ob};
+    static uint32_t const C_ob{QUINT8_C_ob};
+    static uint32_t const SIMD{QUINT8_SIMD};
+    static uint32_t const UNROLL{QUINT8_UNROLL};
+    static uint32_t const C_ib{QUINT8_C_ib};
+    static uint32_t const NUM_FMA{QUINT8_NUM_FMA};
+    static uint32_t const NUM_MAX{QUINT8_NUM_MAX};
+    static uint32_t const NUM_LOAD{QUINT8_NUM_LOAD};
+    static uint32_t const NUM_STORE{QUINT8_NUM_STORE};
+
+    typedef uint8_t value_type;
+    typedef int32_t accum_type;
+
+    QUInt8Buffer() : b200::ManagedArray<uint8_t>() { quantized_init(); }
+    explicit QUInt8Buffer(size_t num_elts) : b200::ManagedArray<uint8_t>(num_elts) { quantized_init(); }
+    QUInt8Buffer(QUInt8Buffer const &) = default;
+    QUInt8Buffer &operator=(QUInt8Buffer const &) = default;
+
+    QUInt8Buffer(QUInt8Buffer &&other) noexcept : b200::ManagedArray<uint8_t>()
+    {
+        quantized_init();
+        swap(other);
+    }
+    QUInt8Buffer &operator=(QUInt8Buffer &&other) noexcept
+    {
+        if (this != &other)
+        {
+            QUInt8Buffer empty;
+            swap(empty); // releases this buffer's storage when `empty` dies
+            swap(other);
+        }
+        return *this;
+    }
+
+    void swap(QUInt8Buffer &other)
+    {
+        if (this == &other)
+            return;
+        b200::ManagedArray<uint8_t>::swap(other);
+        std::swap(scale, other.scale);
+        std::swap(offset, other.offset);
+        std::swap(multiplier, other.multiplier);
+        std::swap(lshift, other.lshift);
+        std::swap(rshift, other.rshift);
+        std::swap(m_zero, other.m_zero);
+        std::swap(min_val, other.min_val);
+        std::swap(max_val, other.max_val);
+        std::swap(b, other.b);
+    }
+
+    inline accum_type zero() const { return m_zero; }
+
+public:
+    float scale;
+    int32_t offset;
+    int32_t multiplier;
+    int lshift;
+    int rshift;
+    accum_type m_zero;
+    int min_val;
+    int max_val;
+    uint8_t b;
+
+private:
+    // Parameters for the range [-1, 1] over 8 bits: the same fixed-point construction as
+    // the reference's buffers (multiplier 1077952576, rshift 6, zero 128).
+    void quantized_init()
+    {
+        b = 8;
+        const double levels = 255.0;
+        const double dscale = 2.0 / levels + 1e-17;
+        int shift = 0;
+        const double q = std::frexp(dscale, &shift);
+        long long q_fixed = std::llround(q * (double)(1LL << 31));
+        if (q_fixed == (1LL << 31))
+        {
+            q_fixed /= 2;
+            ++shift;
+        }
+        if (shift < -31)
+        {
+            shift = 0;
+            q_fixed = 0;
+        }
+        if (shift > 30)
+        {
+            shift = 30;
+            q_fixed = (1LL << 31) - 1;
+        }
+        multiplier = (int32_t)q_fixed;
+        m_zero = (accum_type)std::rint(levels / 2.0);
+        scale = (float)dscale;
+        lshift = shift > 0 ? shift : 0;
+        rshift = shift > 0 ? 0 : -shift;
+        min_val = 0;
+        max_val = 255;
+        offset = 0;
+    }
+};
+
+//****************************************************************************
+template <class BufferT>
+inline BufferT *alloc_buffer(size_t num_elts)
+{
+    static_assert(std::is_same_v<BufferT, FloatBuffer> || std::is_same_v<BufferT, QUInt8Buffer>,
+                  "small::alloc_buffer: unsupported buffer type");
+    return new BufferT(num_elts);
+}
+
+template <class BufferT>
+inline void free_buffer(BufferT *buffer)
+{
+    delete buffer;
+}
+
+} // namespace small
