@@ -117,6 +117,20 @@ int small_b200_graph_destroy(void *graph_exec);
  * C % 16 == 0 or C in {1,2,3}; stride in {1,2}. */
 int small_b200_conv2d_f32(const small_b200_layer *L, const float *in, const float *filt,
                           const float *bias, float *out, void *stream);
+/* The same layer on the tensor cores (tcgen05 kind::tf32 with the 3xTF32 operand split, fp32
+ * accumulation in tensor memory), stride 1 only.  The caller provides scratch for the second
+ * halves of both operands, lo = x - (x with the 13 low mantissa bits cleared):
+ *   in_lo          small_b200_split_tf32(in), once per call, as many floats as `in`;
+ *   filt_prepared  small_b200_filter_prepare_tf32x3(filt), once per set of weights,
+ *                  2 * K*C*Fh*Fw floats: the filter re-laid per tap as [c/4][16 k][4 c]
+ *                  (what the tensor core reads directly) followed by its lo copy.
+ * ..._supported() says whether a shape is covered (1) or not (0).  The reference has no
+ * counterpart of the two preparation calls (its filters are used as packed). */
+int small_b200_split_tf32(int64_t n, const float *x, float *lo, void *stream);
+int small_b200_conv2d_f32_tf32x3_supported(const small_b200_layer *L);
+int small_b200_filter_prepare_tf32x3(const small_b200_layer *L, const float *filt, float *prepared, void *stream);
+int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, const float *in_lo,
+                                 const float *filt_prepared, const float *bias, float *out, void *stream);
 /* small::DepthwiseConv2D / PartialDepthwiseConv2D<FloatBuffer> (:994, :1127) and
  * DepthwiseConv2D_Bias_ReLU (fused_interface_abstract.hpp:1419). */
 int small_b200_dwconv2d_f32(const small_b200_layer *L, const float *in, const float *filt,

@@ -1,0 +1,82 @@
+"""fp32 convolution on the tensor cores (tcgen05 kind::tf32, 3xTF32 split) against the oracle:
+max|x - ref| / max|ref| <= 1e-5, the same gate as the CUDA-core kernel."""
+import numpy as np
+import pytest
+
+from oracle.bindings import same_pads, shape
+from smallframework_b200 import _lib
+from smallframework_b200 import interface as S
+from smallframework_b200 import packing as P
+from tests.gpu_util import CB, fbuf, oracle_conv_batch, rel_max_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+CASES = [
+    # C, K, H, W, Fh, Fw, pads, batch
+    (16, 16, 13, 13, 3, 3, "same", 1),      # one 16-channel block, 128+64-row tiles
+    (32, 64, 13, 13, 3, 3, "same", 2),
+    (64, 256, 13, 13, 3, 3, "same", 2),     # 256 output channels per CTA: all of tensor memory
+    (32, 128, 26, 26, 3, 3, "same", 2),     # several M tiles per image
+    (32, 32, 52, 52, 3, 3, "same", 1),
+    (16, 64, 104, 104, 3, 3, "same", 1),
+    (128, 128, 13, 13, 1, 1, "valid", 3),   # pointwise: no junk columns
+    (32, 16, 9, 20, 5, 3, (2, 2, 1, 1), 1),
+    (48, 32, 11, 7, 2, 4, "valid", 2),
+    (32, 48, 8, 8, 3, 3, (0, 1, 0, 1), 2),  # unequal pads
+    (512, 128, 13, 13, 3, 3, "same", 1),    # long reduction: 32 channel blocks
+]
+
+
+def _split(buf):
+    lo = S.FloatBuffer(buf.size())
+    S.split_tf32(buf, lo)
+    return lo
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "C{}_K{}_{}x{}_k{}x{}_{}_n{}".format(*[
+    "".join(map(str, v)) if isinstance(v, tuple) else v for v in c]))
+@pytest.mark.parametrize("mode", ["plain", "partial_bias_leaky"])
+def test_conv2d_3xtf32(oracle, case, mode):
+    C, K, H, W, Fh, Fw, pm, N = case
+    pads = same_pads(H, W, Fh, Fw, 1) if pm == "same" else (0, 0, 0, 0) if pm == "valid" else pm
+    assert S.tf32x3_supported(Fh, Fw, 1, *pads, K, C, H, W)
+    rng = np.random.default_rng(abs(hash((case, mode))) % (1 << 31))
+    x = P.pack_activation(rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32))
+    w = P.pack_conv_filter(rng.normal(0, np.sqrt(2.0 / (C * Fh * Fw)), (K, C, Fh, Fw)).astype(np.float32))
+    bias = rng.uniform(-0.5, 0.5, K).astype(np.float32)
+    sh = shape(C, K, H, W, Fh, Fw, 1, pads, CB)
+    ho, wo = sh.out_hw()
+    I, F = fbuf(x), fbuf(w)
+    Il = _split(I)
+    Fp = S.FloatBuffer(2 * F.size())
+    S.prepare_filter_3xTF32(Fh, Fw, K, C, F, Fp)
+    if mode == "plain":
+        O = S.FloatBuffer(N * K * ho * wo)
+        S.Conv2D_3xTF32(Fh, Fw, 1, *pads, K, C, H, W, I, Il, Fp, None, O, batch=N)
+        want = oracle_conv_batch(oracle, sh, x, w)
+    else:
+        seed = rng.uniform(-1, 1, (N, K * ho * wo)).astype(np.float32)
+        O = fbuf(seed)
+        S.Conv2D_3xTF32(Fh, Fw, 1, *pads, K, C, H, W, I, Il, Fp, fbuf(bias), O, partial=True,
+                        activation=S.ACT_LEAKY, negative_slope=0.1, batch=N)
+        want = oracle_conv_batch(oracle, sh, x, w, bias=bias, act=2, slope=0.1, seed=seed)
+    got = O.numpy().reshape(N, -1)
+    assert _lib.device_status() == 0
+    assert rel_max_err(got, want) <= TOL
+
+
+def test_split_is_exact():
+    rng = np.random.default_rng(0)
+    x = rng.normal(0, 3, 4096).astype(np.float32)
+    X = fbuf(x)
+    lo = _split(X).numpy()
+    hi = (x.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    assert np.array_equal(lo, x - hi)
+    assert np.array_equal(hi + lo, x)
+
+
+def test_unsupported_shapes_are_refused():
+    assert not S.tf32x3_supported(3, 3, 2, 0, 1, 0, 1, 16, 16, 32, 32)   # stride 2
+    assert not S.tf32x3_supported(3, 3, 1, 1, 1, 1, 1, 16, 3, 32, 32)    # first layer
+    assert not S.tf32x3_supported(3, 3, 1, 1, 1, 1, 1, 16, 16, 416, 416) # wider than one TMA box
