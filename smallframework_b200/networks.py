@@ -178,8 +178,14 @@ class Chain:
     into a CUDA graph; launch() replays it.  `x` (input) and `y` (output) are the device
     tensors at the two ends."""
 
-    def __init__(self, layers, batch, dtype="f32", device="cuda"):
+    TC_MIN_CHANNELS = 32
+
+    def __init__(self, layers, batch, dtype="f32", device="cuda", tensor_core="auto"):
+        """tensor_core: "auto" = fp32 convolutions the 3xTF32 kernel covers and that have at
+        least `TC_MIN_CHANNELS` input channels run on the tensor cores; True = every covered
+        layer; False = CUDA cores only."""
         self.layers, self.batch, self.dtype = layers, batch, dtype
+        self.tensor_core = tensor_core
         self.tdtype = torch.float32 if dtype == "f32" else torch.uint8
         self.elt = 4 if dtype == "f32" else 1
         self.dev = torch.device(device)
@@ -208,6 +214,29 @@ class Chain:
                 bs = torch.from_numpy(bp).to(self.dev)
             self.params.append((wt, bs))
         self.bufs = [torch.zeros(max_act, dtype=self.tdtype, device=self.dev) for _ in range(2)]
+        # tensor-core fp32 path: filters re-laid once (hi + lo copies), one scratch buffer for
+        # the lo half of whichever activation tensor feeds the current layer
+        self.prepared = [None] * len(layers)
+        self.lo = None
+        if dtype == "f32" and tensor_core:
+            lo_elems = 0
+            for i, L in enumerate(layers):
+                if L["op"] != "conv" or i == 0:
+                    continue
+                if tensor_core == "auto" and L["C"] < self.TC_MIN_CHANNELS:
+                    continue
+                d = self._desc(L, padded(L["C"]))
+                if not lib().small_b200_conv2d_f32_tf32x3_supported(C.byref(d)):
+                    continue
+                wt = self.params[i][0]
+                prep = torch.empty(2 * wt.numel(), dtype=torch.float32, device=self.dev)
+                check(lib().small_b200_filter_prepare_tf32x3(C.byref(d), wt.data_ptr(), prep.data_ptr(),
+                                                             torch.cuda.current_stream().cuda_stream))
+                self.prepared[i] = prep
+                lo_elems = max(lo_elems, batch * padded(L["C"]) * L["H"] * L["W"])
+            if lo_elems:
+                self.lo = torch.empty(lo_elems, dtype=torch.float32, device=self.dev)
+            torch.cuda.synchronize()
         self.graph = None
         self.y = None
         self.kernels_per_step = 0
@@ -229,7 +258,12 @@ class Chain:
         sfx = "f32" if self.dtype == "f32" else "u8"
         l = lib()
         p = lambda t: t.data_ptr() if t is not None else None
-        if L["op"] == "conv":
+        if L["op"] == "conv" and self.prepared[i] is not None:
+            n_in = self.batch * cin * L["H"] * L["W"]
+            check(l.small_b200_split_tf32(n_in, p(src), p(self.lo), stream))
+            check(l.small_b200_conv2d_f32_tf32x3(C.byref(d), p(src), p(self.lo), p(self.prepared[i]),
+                                                 p(bs), p(dst), stream))
+        elif L["op"] == "conv":
             check(getattr(l, f"small_b200_conv2d_{sfx}")(C.byref(d), p(src), p(wt), p(bs), p(dst), stream))
         elif L["op"] == "dwconv":
             check(getattr(l, f"small_b200_dwconv2d_{sfx}")(C.byref(d), p(src), p(wt), p(bs), p(dst), stream))
