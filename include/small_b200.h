@@ -122,7 +122,7 @@ int small_b200_conv2d_f32(const small_b200_layer *L, const float *in, const floa
  * halves of both operands, lo = x - (x with the 13 low mantissa bits cleared):
  *   in_lo          small_b200_split_tf32(in), once per call, as many floats as `in`;
  *   filt_prepared  small_b200_filter_prepare_tf32x3(filt), once per set of weights,
- *                  2 * K*C*Fh*Fw floats: the filter re-laid per tap as [c/4][16 k][4 c]
+ *                  2 * K*C*Fh*Fw floats: per CTA tile and tap the filter as [c/4][k][4 c]
  *                  (what the tensor core reads directly) followed by its lo copy.
  * ..._supported() says whether a shape is covered (1) or not (0).  The reference has no
  * counterpart of the two preparation calls (its filters are used as packed). */

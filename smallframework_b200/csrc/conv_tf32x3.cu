@@ -18,9 +18,10 @@
 //   The filter [K/16][C/16][tap][16 c][16 k] has the output channel contiguous (MN-major).
 //   kind::tf32 did not accept an MN-major no-swizzle B operand on this hardware (a one-MMA
 //   experiment returned zeros, while the K-major form was exact), so the filter is re-laid
-//   once per set of weights into [K/16][C/16][tap][c/4][16 k][4 c] (prepare_filter_kernel,
-//   which also produces the lo copy); a 5-D TMA box then lands one tap as
-//   [c/4][k][4 c] = the K-major no-swizzle canonical layout, exactly like the activations.
+//   once per set of weights into [K/NT][C/16][tap][c/4][NT k][4 c] (prepare_filter_kernel,
+//   which also produces the lo copy), NT = output channels per CTA.  One tap of one CTA is
+//   then a single contiguous run of NT*64 bytes that IS the K-major no-swizzle canonical
+//   layout ([c/4][k][4 c], like the activations) and arrives by one bulk copy.
 //
 // The lo parts are produced outside this kernel into caller-provided scratch: the filter once
 // per set of weights (prepare), the activations once per call (split_tf32_kernel).
@@ -32,6 +33,7 @@ using namespace sb;
 
 constexpr int MAX_MT = 4;  // accumulator tiles per CTA
 constexpr int B_STAGES = 4;
+constexpr int A_SLOTS_MAX = 4;
 
 struct TcArgs
 {
@@ -65,18 +67,29 @@ split_tf32_kernel(long long n4, const float4 *__restrict__ x, float4 *__restrict
     }
 }
 
-// packed filter [slab][16 c][16 k] -> hi and lo copies in [slab][c/4][16 k][4 c]
+// Output channels per CTA, a function of K alone so that filter preparation and the
+// convolution agree: two tensor-memory buffers x two accumulator tiles x NT columns must fit
+// the 512 columns, and a thread keeps 64 columns of each tile in registers.
+__host__ __device__ inline int pick_nt(int K)
+{
+    return (K % 128 == 0) ? 128 : (K % 64 == 0) ? 64 : (K % 32 == 0) ? 32 : 16;
+}
+
+// packed filter [K/16][slab][16 c][16 k] -> hi and lo copies in [K/NT][slab][c/4][NT k][4 c]
 __global__ void __launch_bounds__(256)
-prepare_filter_kernel(long long n, const float *__restrict__ w, float *__restrict__ hi, float *__restrict__ lo)
+prepare_filter_kernel(long long n, int slabs, int NT, const float *__restrict__ w, float *__restrict__ hi,
+                      float *__restrict__ lo)
 {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n)
         return;
-    const int k = (int)(i & 15), c = (int)((i >> 4) & 15);
-    const long long slab = i >> 8;
+    const int k16 = (int)(i & 15), c = (int)((i >> 4) & 15);
+    const long long t = i >> 8;            // kb16 * slabs + slab
+    const int slab = (int)(t % slabs);
+    const int k = (int)(t / slabs) * 16 + k16;
     const float v = w[i];
     const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
-    const long long o = slab * 256 + (c >> 2) * 64 + k * 4 + (c & 3);
+    const long long o = (((long long)(k / NT) * slabs + slab) * 4 + (c >> 2)) * NT * 4 + (long long)(k % NT) * 4 + (c & 3);
     hi[o] = v;
     lo[o] = v - h;
 }
@@ -96,11 +109,11 @@ constexpr int COLS_PER_THREAD = 64; // of one accumulator tile
 
 __global__ void __launch_bounds__(320, 1)
 conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
-                   const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                   const float *__restrict__ filt_hi, const float *__restrict__ filt_lo,
                    const TcArgs a, const float *__restrict__ bias, float *__restrict__ out, int *status)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t a_full[2], a_empty[2], b_full[B_STAGES], b_empty[B_STAGES];
+    __shared__ __align__(8) uint64_t a_full[A_SLOTS_MAX], a_empty[A_SLOTS_MAX], b_full[B_STAGES], b_empty[B_STAGES];
     __shared__ __align__(8) uint64_t t_full[2], t_empty[2];
     __shared__ uint32_t tmem_base_s;
 
@@ -130,11 +143,8 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
     {
         if (lane == 0)
         {
-            for (int i = 0; i < 2; ++i)
-            {
-                mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1);
-                mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], ACC_WARPS);
-            }
+            for (int i = 0; i < A_SLOTS_MAX; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
+            for (int i = 0; i < 2; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], ACC_WARPS); }
             for (int i = 0; i < B_STAGES; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
             fence_barrier_init();
         }
@@ -174,9 +184,9 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
                     break;
                 uint8_t *bd = sB + (size_t)st * 2 * b_part;
                 mbar_expect_tx(&b_full[st], 2 * b_part);
-                const int slab = cb * a.taps + tap;
-                tma_load_5d(bd, &map_b_hi, 0, 0, nt * (a.NT / CB), 0, slab, &b_full[st]);
-                tma_load_5d(bd + b_part, &map_b_lo, 0, 0, nt * (a.NT / CB), 0, slab, &b_full[st]);
+                const size_t off = ((size_t)nt * steps + (size_t)(cb * a.taps + tap)) * (b_part / 4);
+                tma_load_1d(bd, filt_hi + off, b_part, &b_full[st]);
+                tma_load_1d(bd + b_part, filt_lo + off, b_part, &b_full[st]);
             }
         }
     }
@@ -259,25 +269,26 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
             tc_fence_after_sync();
             if (active)
             {
+                // eight chunks of 16 columns (2 tiles x 4 groups); chunk i+1 is requested from
+                // tensor memory before chunk i is added, so the load latency is covered
+                const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(tb * buf_cols + col0);
+                uint32_t v[2][16];
+                constexpr int NCH = 2 * (COLS_PER_THREAD / 16);
+                auto chunk_ok = [&](int i) { return (i / (COLS_PER_THREAD / 16)) < a.n_mtiles && (i % (COLS_PER_THREAD / 16)) * 16 < my_cols; };
+                auto chunk_addr = [&](int i) { return tbase + (uint32_t)((i / (COLS_PER_THREAD / 16)) * a.NT + (i % (COLS_PER_THREAD / 16)) * 16); };
+                if (chunk_ok(0))
+                    tmem_ld16(chunk_addr(0), v[0]);
 #pragma unroll
-                for (int j = 0; j < 2; ++j)
+                for (int i = 0; i < NCH; ++i)
                 {
-                    if (j < a.n_mtiles)
+                    tmem_ld_wait();
+                    if (i + 1 < NCH && chunk_ok(i + 1))
+                        tmem_ld16(chunk_addr(i + 1), v[(i + 1) & 1]);
+                    if (chunk_ok(i))
                     {
 #pragma unroll
-                        for (int cg = 0; cg < COLS_PER_THREAD / 16; ++cg)
-                        {
-                            if (cg * 16 < my_cols)
-                            {
-                                uint32_t v[16];
-                                tmem_ld16(tmem + ((uint32_t)(quarter * 32) << 16) +
-                                              (uint32_t)(tb * buf_cols + j * a.NT + col0 + cg * 16), v);
-                                tmem_ld_wait();
-#pragma unroll
-                                for (int i = 0; i < 16; ++i)
-                                    acc[j][cg * 16 + i] += __uint_as_float(v[i]);
-                            }
-                        }
+                        for (int e = 0; e < 16; ++e)
+                            acc[i / (COLS_PER_THREAD / 16)][(i % (COLS_PER_THREAD / 16)) * 16 + e] += __uint_as_float(v[i & 1][e]);
                     }
                 }
             }
@@ -372,7 +383,8 @@ int small_b200_filter_prepare_tf32x3(const small_b200_layer *L, const float *fil
     if (!small_b200_conv2d_f32_tf32x3_supported(L))
         return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: shape not covered by the tensor-core path.");
     const long long n = (long long)L->K * L->C * L->Fh * L->Fw;
-    prepare_filter_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(n, filt, prepared, prepared + n);
+    prepare_filter_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(
+        n, (L->C / CB) * L->Fh * L->Fw, pick_nt(L->K), filt, prepared, prepared + n);
     return launched("prepare_filter_kernel");
 }
 
@@ -396,9 +408,7 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
         return SMALL_B200_OK;
     a.PW = L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r);
 
-    // output channels per CTA: two tensor-memory buffers x two accumulator tiles x NT columns
-    // must fit the 512 columns, and a thread keeps 64 columns of each tile in registers
-    a.NT = (a.K % 128 == 0) ? 128 : (a.K % 64 == 0) ? 64 : (a.K % 32 == 0) ? 32 : 16;
+    a.NT = pick_nt(a.K);
     // GEMM rows of one image: the last valid row is (Ho-1)*PW + Wo-1
     const int m_img = (a.Ho - 1) * a.PW + a.Wo;
     const int MT = (m_img <= 128) ? 128 : (m_img <= 192) ? 192 : 256;
@@ -418,17 +428,19 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
         return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: patch too tall.");
     const size_t a_part = (((size_t)a.PR * a.PW * 64) + 127) & ~(size_t)127, b_part = (size_t)a.NT * 64;
     const size_t limit = 220 * 1024;
-    a.a_slots = 2;
-    size_t smem = 2 * 2 * a_part + (size_t)B_STAGES * 2 * b_part;
-    if (smem > limit)
+    // as many activation slots as fit (a layer with few taps per channel block, e.g. 1x1,
+    // needs several patches in flight to cover the TMA latency)
+    size_t smem = 0;
+    for (a.a_slots = (a.cbs < A_SLOTS_MAX ? (a.cbs > 0 ? a.cbs : 1) : A_SLOTS_MAX); a.a_slots >= 1; --a.a_slots)
     {
-        a.a_slots = 1;
-        smem = 2 * a_part + (size_t)B_STAGES * 2 * b_part;
+        smem = (size_t)a.a_slots * 2 * a_part + (size_t)B_STAGES * 2 * b_part;
+        if (smem <= limit)
+            break;
     }
-    if (smem > limit)
+    if (a.a_slots < 1)
         return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: patch does not fit in shared memory.");
 
-    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    CUtensorMap ma_hi, ma_lo;
     {
         // activations [N*cbs][H][W][4 chunks][4 floats]
         const uint64_t dims[5] = {4, (uint64_t)a.W, (uint64_t)a.H, 4, (uint64_t)a.N * a.cbs};
@@ -437,17 +449,6 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
         if (int rc = make_tensor_map(&ma_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, in, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
             return rc;
         if (int rc = make_tensor_map(&ma_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, in_lo, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
-            return rc;
-    }
-    {
-        // prepared filter [K/16][cbs*taps slabs][4 c-chunks][16 k][4 c]
-        const uint64_t slabs = (uint64_t)a.cbs * a.taps;
-        const uint64_t dims[5] = {4, CB, (uint64_t)a.K / CB, 4, slabs};
-        const uint64_t strides[4] = {16, slabs * 1024, 256, 1024};
-        const uint32_t box[5] = {4, CB, (uint32_t)a.NT / CB, 4, 1};
-        if (int rc = make_tensor_map(&mb_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, filt, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
-            return rc;
-        if (int rc = make_tensor_map(&mb_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, filt_lo, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
             return rc;
     }
     static bool configured = false;
@@ -460,7 +461,7 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     if (!status)
         return fail(SMALL_B200_CUDA_ERROR, "device status word not available");
     const long long blocks = (long long)a.N * a.m_tiles_per_img * a.n_tiles;
-    conv_tf32x3_kernel<<<(unsigned)blocks, 320, smem, as_stream(stream)>>>(ma_hi, ma_lo, mb_hi, mb_lo, a, bias, out, status);
+    conv_tf32x3_kernel<<<(unsigned)blocks, 320, smem, as_stream(stream)>>>(ma_hi, ma_lo, filt, filt_lo, a, bias, out, status);
     return launched("conv_tf32x3_kernel");
 }
 } // extern "C"
