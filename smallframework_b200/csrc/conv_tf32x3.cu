@@ -46,7 +46,8 @@ struct TcArgs
     int m_tiles_per_img; // CTAs along M per image
     int NT;              // output channels per CTA
     int n_tiles;         // K / NT
-    int a_slots;         // 1 or 2
+    int a_slots;         // activation patches in flight (1..4)
+    int group;           // filter taps summed in tensor memory before a flush (1 or Fw)
     int accumulate, act;
     float slope;
 };
@@ -193,55 +194,67 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
     else if (warp == 1 && lane == 0)
     {
         // ---------------- MMA issuer ----------------
+        // One thread feeds the tensor core, so the per-MMA instruction count matters: all
+        // descriptor fields except the 16-byte-granular start address are fixed per CTA, and
+        // a new operand position is one 64-bit add on a precomputed descriptor.
         bool ok = true;
         int bs = 0;
-        const uint32_t sa0 = smem_u32(sA), sb0 = smem_u32(sB);
+        const uint64_t a_desc0 = make_smem_desc(smem_u32(sA), a_chunk, 128, 0);
+        const uint64_t b_desc0 = make_smem_desc(smem_u32(sB), b_chunk, 128, 0);
+        const uint32_t idesc0 = make_idesc(1 /*f32*/, 2 /*tf32*/, 2 /*tf32*/, 0 /*A K-major*/, 0 /*B K-major*/,
+                                           (uint32_t)a.mtile_rows[0], (uint32_t)a.NT);
+        const uint32_t idesc1 = make_idesc(1, 2, 2, 0, 0, (uint32_t)(a.n_mtiles > 1 ? a.mtile_rows[1] : 128),
+                                           (uint32_t)a.NT);
+        const uint64_t a_lo_off = a_part >> 4, b_lo_off = b_part >> 4;
+        const uint64_t a_half = (2 * a_chunk) >> 4, b_half = (2 * b_chunk) >> 4;
+        const uint64_t a_tile1 = (uint64_t)a.mtile_rows[0];          // rows of tile 0 = 16-byte entries
+        const bool two_tiles = a.n_mtiles > 1;
         for (int cb = 0; cb < a.cbs && ok; ++cb)
         {
             const int slot = cb % a.a_slots;
             ok = mbar_wait(&a_full[slot], (cb / a.a_slots) & 1, status, 13);
             if (!ok)
                 break;
-            const uint32_t a_hi = sa0 + slot * 2 * a_part, a_lo = a_hi + a_part;
+            const uint64_t a_slot = a_desc0 + ((uint64_t)(slot * 2 * a_part) >> 4) + (uint64_t)m_local0;
+            int kh = 0, kw = 0;
             for (int tap = 0; tap < a.taps && ok; ++tap, ++bs)
             {
                 const int st = bs % B_STAGES;
-                const int tb = bs & 1; // tensor-memory buffer of this tap
+                const int chunk = bs / a.group, in_chunk = bs - chunk * a.group;
+                const int tb = chunk & 1; // tensor-memory buffer of this group of taps
                 ok = mbar_wait(&b_full[st], (bs / B_STAGES) & 1, status, 14);
-                if (ok && bs >= 2)
-                    ok = mbar_wait(&t_empty[tb], ((bs >> 1) - 1) & 1, status, 16);
+                if (ok && in_chunk == 0 && chunk >= 2)
+                    ok = mbar_wait(&t_empty[tb], ((chunk >> 1) - 1) & 1, status, 16);
                 if (!ok)
                     break;
                 tc_fence_after_sync();
-                const uint32_t b_hi = sb0 + st * 2 * b_part, b_lo = b_hi + b_part;
-                const int kh = tap / a.Fw, kw = tap - kh * a.Fw;
-                const uint32_t shift = (uint32_t)(m_local0 + kh * a.PW + kw) * 16;
-                int row_off = 0;
-                for (int j = 0; j < a.n_mtiles; ++j)
+                const uint64_t ah = a_slot + (uint64_t)(kh * a.PW + kw), al = ah + a_lo_off;
+                const uint64_t bh = b_desc0 + ((uint64_t)(st * 2 * b_part) >> 4), bl = bh + b_lo_off;
+                const uint32_t d0 = tmem + (uint32_t)(tb * buf_cols), d1 = d0 + (uint32_t)a.NT;
+                const uint32_t fresh = in_chunk == 0 ? 0u : 1u;
+                // tile 0
+                tc_mma_tf32(d0, al, bh, idesc0, fresh);
+                tc_mma_tf32(d0, ah, bl, idesc0, 1u);
+                tc_mma_tf32(d0, ah, bh, idesc0, 1u);
+                tc_mma_tf32(d0, al + a_half, bh + b_half, idesc0, 1u);
+                tc_mma_tf32(d0, ah + a_half, bl + b_half, idesc0, 1u);
+                tc_mma_tf32(d0, ah + a_half, bh + b_half, idesc0, 1u);
+                if (two_tiles)
                 {
-                    const int rows = a.mtile_rows[j];
-                    const uint32_t idesc = make_idesc(1 /*f32*/, 2 /*tf32*/, 2 /*tf32*/, 0 /*A K-major*/,
-                                                      0 /*B K-major*/, (uint32_t)rows, (uint32_t)a.NT);
-                    const uint32_t d = tmem + (uint32_t)(tb * buf_cols + j * a.NT);
-#pragma unroll
-                    for (int half = 0; half < 2; ++half)
-                    {
-                        const uint32_t aoff = shift + (uint32_t)row_off * 16 + (uint32_t)half * 2 * a_chunk;
-                        const uint32_t boff = (uint32_t)half * 2 * b_chunk;
-                        const uint64_t dah = make_smem_desc(a_hi + aoff, a_chunk, 128, 0);
-                        const uint64_t dal = make_smem_desc(a_lo + aoff, a_chunk, 128, 0);
-                        const uint64_t dbh = make_smem_desc(b_hi + boff, b_chunk, 128, 0);
-                        const uint64_t dbl = make_smem_desc(b_lo + boff, b_chunk, 128, 0);
-                        tc_mma_tf32(d, dal, dbh, idesc, half == 0 ? 0u : 1u);
-                        tc_mma_tf32(d, dah, dbl, idesc, 1u);
-                        tc_mma_tf32(d, dah, dbh, idesc, 1u);
-                    }
-                    row_off += rows;
+                    const uint64_t ah1 = ah + a_tile1, al1 = al + a_tile1;
+                    tc_mma_tf32(d1, al1, bh, idesc1, fresh);
+                    tc_mma_tf32(d1, ah1, bl, idesc1, 1u);
+                    tc_mma_tf32(d1, ah1, bh, idesc1, 1u);
+                    tc_mma_tf32(d1, al1 + a_half, bh + b_half, idesc1, 1u);
+                    tc_mma_tf32(d1, ah1 + a_half, bl + b_half, idesc1, 1u);
+                    tc_mma_tf32(d1, ah1 + a_half, bh + b_half, idesc1, 1u);
                 }
                 tc_commit(&b_empty[st]); // the tap's filter tile is free once these MMAs retire
-                tc_commit(&t_full[tb]);  // and its partial sums are complete
+                if (in_chunk == a.group - 1)
+                    tc_commit(&t_full[tb]); // the group's partial sums are complete
                 if (tap == a.taps - 1)
                     tc_commit(&a_empty[slot]);
+                if (++kw == a.Fw) { kw = 0; ++kh; }
             }
         }
     }
@@ -260,7 +273,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
             for (int c = 0; c < COLS_PER_THREAD; ++c)
                 acc[j][c] = 0.f;
         bool ok = true;
-        for (int g = 0; g < steps && ok; ++g)
+        for (int g = 0; g < steps / a.group && ok; ++g)
         {
             const int tb = g & 1;
             ok = mbar_wait(&t_full[tb], (g >> 1) & 1, status, 15, 1u << 24);
@@ -269,26 +282,43 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
             tc_fence_after_sync();
             if (active)
             {
-                // eight chunks of 16 columns (2 tiles x 4 groups); chunk i+1 is requested from
-                // tensor memory before chunk i is added, so the load latency is covered
+                // four pieces of 32 columns (2 tiles x 2); a tile's two loads are in flight
+                // together, so a flush costs two tensor-memory round trips
                 const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(tb * buf_cols + col0);
-                uint32_t v[2][16];
-                constexpr int NCH = 2 * (COLS_PER_THREAD / 16);
-                auto chunk_ok = [&](int i) { return (i / (COLS_PER_THREAD / 16)) < a.n_mtiles && (i % (COLS_PER_THREAD / 16)) * 16 < my_cols; };
-                auto chunk_addr = [&](int i) { return tbase + (uint32_t)((i / (COLS_PER_THREAD / 16)) * a.NT + (i % (COLS_PER_THREAD / 16)) * 16); };
-                if (chunk_ok(0))
-                    tmem_ld16(chunk_addr(0), v[0]);
 #pragma unroll
-                for (int i = 0; i < NCH; ++i)
+                for (int j = 0; j < 2; ++j)
                 {
-                    tmem_ld_wait();
-                    if (i + 1 < NCH && chunk_ok(i + 1))
-                        tmem_ld16(chunk_addr(i + 1), v[(i + 1) & 1]);
-                    if (chunk_ok(i))
+                    if (j < a.n_mtiles)
                     {
+                        uint32_t v0[32], v1[32];
+                        if (my_cols >= 64)
+                        {
+                            tmem_ld32(tbase + (uint32_t)(j * a.NT), v0);
+                            tmem_ld32(tbase + (uint32_t)(j * a.NT + 32), v1);
+                            tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 16; ++e)
-                            acc[i / (COLS_PER_THREAD / 16)][(i % (COLS_PER_THREAD / 16)) * 16 + e] += __uint_as_float(v[i & 1][e]);
+                            for (int e = 0; e < 32; ++e)
+                            {
+                                acc[j][e] += __uint_as_float(v0[e]);
+                                acc[j][32 + e] += __uint_as_float(v1[e]);
+                            }
+                        }
+                        else if (my_cols == 32)
+                        {
+                            tmem_ld32(tbase + (uint32_t)(j * a.NT), v0);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e)
+                                acc[j][e] += __uint_as_float(v0[e]);
+                        }
+                        else
+                        {
+                            tmem_ld16(tbase + (uint32_t)(j * a.NT), v0);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int e = 0; e < 16; ++e)
+                                acc[j][e] += __uint_as_float(v0[e]);
+                        }
                     }
                 }
             }
@@ -409,6 +439,7 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     a.PW = L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r);
 
     a.NT = pick_nt(a.K);
+    a.group = a.Fw; // one kernel row per flush: taps = Fh * Fw is a multiple of it
     // GEMM rows of one image: the last valid row is (Ho-1)*PW + Wo-1
     const int m_img = (a.Ho - 1) * a.PW + a.Wo;
     const int MT = (m_img <= 128) ? 128 : (m_img <= 192) ? 192 : 256;

@@ -25,6 +25,8 @@ CASES = [
     (48, 32, 11, 7, 2, 4, "valid", 2),
     (32, 48, 8, 8, 3, 3, (0, 1, 0, 1), 2),  # unequal pads
     (512, 128, 13, 13, 3, 3, "same", 1),    # long reduction: 32 channel blocks
+    (1024, 128, 13, 13, 3, 3, "same", 1),   # the longest reduction of the configurations (9216 terms)
+    (1024, 128, 13, 13, 1, 1, "valid", 2),
 ]
 
 
