@@ -131,6 +131,24 @@ int small_b200_conv2d_f32_tf32x3_supported(const small_b200_layer *L);
 int small_b200_filter_prepare_tf32x3(const small_b200_layer *L, const float *filt, float *prepared, void *stream);
 int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, const float *in_lo,
                                  const float *filt_prepared, const float *bias, float *out, void *stream);
+/* The tensor-core convolution above for callers that cannot allocate device memory (code
+ * running where cudaMalloc is forbidden or would stall the device, plug-ins that are handed
+ * nothing but their input and output pointers).  It takes the PACKED filter as the reference
+ * lays it out and keeps both pieces of scratch -- the lo half of the activations and the
+ * re-laid filter -- in a fixed 16 MiB array inside the library, so it calls no allocator of
+ * any kind.  Limits and rules:
+ *   - N*C*H*W (rounded up to 64) + 2*K*C*Fh*Fw floats must fit in 4 Mi floats; larger calls are
+ *     refused with SMALL_B200_INVALID_ARGUMENT and a message that states both sizes;
+ *   - the first call on each device looks up the array's device address; make that first call
+ *     outside any stream capture;
+ *   - all calls share the one array, which keeps whatever the last call left in it (nothing in
+ *     it needs clearing: every call rewrites what it reads); two calls whose kernels overlap
+ *     on the GPU -- different streams, or graphs launched side by side -- race on it;
+ *   - the filter is re-laid on every call, so with fixed weights the variant with
+ *     caller-provided scratch is faster.
+ * This entry point has no counterpart in the reference. */
+int small_b200_conv2d_f32_tf32x3_noalloc(const small_b200_layer *L, const float *in, const float *filt,
+                                         const float *bias, float *out, void *stream);
 /* small::DepthwiseConv2D / PartialDepthwiseConv2D<FloatBuffer> (:994, :1127) and
  * DepthwiseConv2D_Bias_ReLU (fused_interface_abstract.hpp:1419). */
 int small_b200_dwconv2d_f32(const small_b200_layer *L, const float *in, const float *filt,

@@ -496,3 +496,72 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     return launched("conv_tf32x3_kernel");
 }
 } // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// The same tensor-core convolution for callers that must not allocate device memory.
+//
+// small_b200_conv2d_f32_tf32x3 needs two pieces of scratch from its caller: the lo half of the
+// activations and the re-laid filter.  Some callers cannot provide them: code that runs inside
+// a region where cudaMalloc is forbidden or would synchronise the device (a real-time loop, a
+// plug-in that only ever receives its input and output pointers, a host that has handed all of
+// its device memory to another allocator).  For them the scratch lives in this fixed array
+// inside the library image.  Every GPU that loads the library carries these 16 MiB until the
+// process exits, which is why the limit is modest.
+constexpr size_t STATIC_SCRATCH_FLOATS = (size_t)4 << 20; // 4 Mi floats = 16 MiB
+static __device__ __align__(256) float g_static_scratch[STATIC_SCRATCH_FLOATS];
+
+namespace
+{
+// In host code `g_static_scratch` is only a stand-in for the device symbol, not an address a
+// kernel could use; the device address is looked up once per device, with that device current.
+int static_scratch_ptr(float **ptr)
+{
+    static float *ptrs[64] = {nullptr};
+    int dev = 0;
+    SB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64)
+        return fail(SMALL_B200_CUDA_ERROR, "device index out of range for the static scratch table");
+    if (!ptrs[dev])
+    {
+        float *p = nullptr;
+        SB_CUDA(cudaGetSymbolAddress((void **)&p, g_static_scratch));
+        ptrs[dev] = p;
+    }
+    *ptr = ptrs[dev];
+    return SMALL_B200_OK;
+}
+} // namespace
+
+extern "C" int small_b200_conv2d_f32_tf32x3_noalloc(const small_b200_layer *L, const float *in,
+                                                    const float *filt, const float *bias, float *out,
+                                                    void *stream)
+{
+    if (int rc = check_window_layer(L, "Conv2D<float>", true, 2))
+        return rc;
+    if (!small_b200_conv2d_f32_tf32x3_supported(L))
+        return fail(SMALL_B200_INVALID_ARGUMENT,
+                    "Conv2D<float> (3xTF32, no-alloc) ERROR: shape not covered by the tensor-core path.");
+    const size_t in_elems = (size_t)L->N * L->C * L->H * L->W;
+    const size_t filt_elems = (size_t)L->K * L->C * L->Fh * L->Fw;
+    // lo half of the input (rounded up so the filter copies stay 256-byte aligned), then the
+    // re-laid filter and its lo copy
+    const size_t in_slot = (in_elems + 63) & ~(size_t)63;
+    const size_t need = in_slot + 2 * filt_elems;
+    if (need > STATIC_SCRATCH_FLOATS)
+        return fail(SMALL_B200_INVALID_ARGUMENT,
+                    "Conv2D<float> (3xTF32, no-alloc) ERROR: this call needs " + std::to_string(need * 4) +
+                        " bytes of scratch (input elements + 2 x filter elements, 4 bytes each) but the "
+                        "built-in scratch holds " + std::to_string(STATIC_SCRATCH_FLOATS * 4) +
+                        " bytes; use small_b200_conv2d_f32_tf32x3 with caller-provided scratch.");
+    float *scratch = nullptr;
+    if (int rc = static_scratch_ptr(&scratch))
+        return rc;
+    float *in_lo = scratch, *prepared = scratch + in_slot;
+    // Nothing in the scratch has to start from zero: both regions are completely rewritten for
+    // the sizes of this call before the convolution reads them.
+    if (int rc = small_b200_split_tf32((int64_t)in_elems, in, in_lo, stream))
+        return rc;
+    if (int rc = small_b200_filter_prepare_tf32x3(L, filt, prepared, stream))
+        return rc;
+    return small_b200_conv2d_f32_tf32x3(L, in, in_lo, prepared, bias, out, stream);
+}
