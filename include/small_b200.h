@@ -118,26 +118,24 @@ int small_b200_graph_destroy(void *graph_exec);
 int small_b200_conv2d_f32(const small_b200_layer *L, const float *in, const float *filt,
                           const float *bias, float *out, void *stream);
 /* The same layer on the tensor cores (tcgen05 kind::tf32 with the 3xTF32 operand split, fp32
- * accumulation in tensor memory), stride 1 only.  The caller provides scratch for the second
- * halves of both operands, lo = x - (x with the 13 low mantissa bits cleared):
- *   in_lo          small_b200_split_tf32(in), once per call, as many floats as `in`;
+ * accumulation in tensor memory), stride 1 only.  Each fp32 operand x enters the tensor core as
+ * hi = x (its 13 low mantissa bits are ignored) and lo = x - hi; the lo copies are made inside the
+ * kernel, in shared memory.  The caller provides the filter re-laid for the tensor core:
  *   filt_prepared  small_b200_filter_prepare_tf32x3(filt), once per set of weights,
- *                  2 * K*C*Fh*Fw floats: per CTA tile and tap the filter as [c/4][k][4 c]
- *                  (what the tensor core reads directly) followed by its lo copy.
+ *                  K*C*Fh*Fw floats: per CTA tile and tap the filter as [c/4][k][4 c]
+ *                  (what the tensor core reads directly).
  * ..._supported() says whether a shape is covered (1) or not (0).  The reference has no
- * counterpart of the two preparation calls (its filters are used as packed). */
-int small_b200_split_tf32(int64_t n, const float *x, float *lo, void *stream);
+ * counterpart of the preparation call (its filters are used as packed). */
 int small_b200_conv2d_f32_tf32x3_supported(const small_b200_layer *L);
 int small_b200_filter_prepare_tf32x3(const small_b200_layer *L, const float *filt, float *prepared, void *stream);
-int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, const float *in_lo,
-                                 const float *filt_prepared, const float *bias, float *out, void *stream);
+int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, const float *filt_prepared,
+                                 const float *bias, float *out, void *stream);
 /* The tensor-core convolution above for callers that cannot allocate device memory (code
  * running where cudaMalloc is forbidden or would stall the device, plug-ins that are handed
  * nothing but their input and output pointers).  It takes the PACKED filter as the reference
- * lays it out and keeps both pieces of scratch -- the lo half of the activations and the
- * re-laid filter -- in a fixed 16 MiB array inside the library, so it calls no allocator of
- * any kind.  Limits and rules:
- *   - N*C*H*W (rounded up to 64) + 2*K*C*Fh*Fw floats must fit in 4 Mi floats; larger calls are
+ * lays it out and keeps its scratch -- the re-laid filter -- in a fixed 16 MiB array inside the
+ * library, so it calls no allocator of any kind.  Limits and rules:
+ *   - K*C*Fh*Fw floats must fit in 4 Mi floats; larger calls are
  *     refused with SMALL_B200_INVALID_ARGUMENT and a message that states both sizes;
  *   - the first call on each device looks up the array's device address; make that first call
  *     outside any stream capture;

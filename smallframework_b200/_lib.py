@@ -61,10 +61,9 @@ SIGNATURES = {
     "small_b200_graph_launch": [_VP, _VP],
     "small_b200_graph_destroy": [_VP],
     "small_b200_conv2d_f32": [_LP, _VP, _VP, _VP, _VP, _VP],
-    "small_b200_split_tf32": [_I64, _VP, _VP, _VP],
     "small_b200_conv2d_f32_tf32x3_supported": [_LP],
     "small_b200_filter_prepare_tf32x3": [_LP, _VP, _VP, _VP],
-    "small_b200_conv2d_f32_tf32x3": [_LP, _VP, _VP, _VP, _VP, _VP, _VP],
+    "small_b200_conv2d_f32_tf32x3": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_conv2d_f32_tf32x3_noalloc": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_dwconv2d_f32": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_maxpool2d_f32": [_LP, _VP, _VP, _VP],

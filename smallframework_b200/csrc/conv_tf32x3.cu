@@ -5,81 +5,66 @@
 // 2^-22 relative, so the result stays within the 1e-5 gate against the reference's fp32 loop
 // nest (include/small/abstract_layer.hpp:1368-1823, FLOAT_CONV_TILE_C).
 //
+// GEMM orientation: D[k][pixel] = sum_c W[k][c] * X[pixel][c].  The output channels are the
+// tensor core's M (one tile of 128, or 64 for layers with fewer channels), the pixels its N
+// (64..256 per CTA).  One tcgen05.mma of kind::tf32 covers only 8 input channels and costs about
+// 32 + N/2 cycles whatever M is (measured: 97 cycles at N = 128, 161 at N = 256), so wide-N
+// instructions are what keeps the tensor pipe busy.
+//
 // Implicit GEMM without im2col ("linear shift"):
 //   For one image and one block of 16 input channels, TMA copies a patch of the packed
-//   activations [rows][PW columns][16 ch] into shared memory split into four 16-byte channel
-//   chunks: [chunk][row][col][4 floats].  PW = W + max(pad_l, pad_r): the zero column(s) that
-//   TMA's out-of-bounds fill produces at the left edge of every row also serve as the right
-//   padding of the row above.  Output pixel (r, c) is GEMM row m = r*PW + c, and filter tap
-//   (kh, kw) of that pixel sits at patch entry m + kh*PW + kw.  Consecutive GEMM rows are
-//   consecutive 16-byte entries, i.e. 8 rows = one 128-byte core matrix of the K-major
-//   no-swizzle canonical layout, for EVERY tap: a tap only moves the descriptor's start
-//   address.  Rows with c >= Wo are junk and are not stored.
+//   activations [rows][PW columns][16 ch] (64 bytes per pixel) into shared memory.
+//   PW = W + max(pad_l, pad_r): the zero column(s) that TMA's out-of-bounds fill produces at the
+//   left edge of every row also serve as the right padding of the row above.  Two splitter warps
+//   re-lay the patch into the tensor core's K-major no-swizzle canonical layout
+//   [4-channel chunk][entry][4 floats] and write the lo copy next to it.  Output pixel (r, c) is
+//   GEMM column m = r*PW + c, and filter tap (kh, kw) of that pixel sits at patch entry
+//   m + kh*PW + kw: consecutive pixels are consecutive 16-byte entries for EVERY tap, so a tap
+//   only moves the descriptor's start address.  Columns with c >= Wo are junk and are not stored.
+//   (Letting TMA write the chunked layout directly needs 16-byte box rows, which it moves at
+//   about one row per 9 cycles: that, not the MMAs, bounded the first version of this kernel.)
 //   The filter [K/16][C/16][tap][16 c][16 k] has the output channel contiguous (MN-major).
-//   kind::tf32 did not accept an MN-major no-swizzle B operand on this hardware (a one-MMA
-//   experiment returned zeros, while the K-major form was exact), so the filter is re-laid
-//   once per set of weights into [K/NT][C/16][tap][c/4][NT k][4 c] (prepare_filter_kernel,
-//   which also produces the lo copy), NT = output channels per CTA.  One tap of one CTA is
-//   then a single contiguous run of NT*64 bytes that IS the K-major no-swizzle canonical
-//   layout ([c/4][k][4 c], like the activations) and arrives by one bulk copy.
-//
-// The lo parts are produced outside this kernel into caller-provided scratch: the filter once
-// per set of weights (prepare), the activations once per call (split_tf32_kernel).
+//   kind::tf32 did not accept an MN-major no-swizzle operand on this hardware (a one-MMA
+//   experiment returned zeros, while the K-major form was exact), so the filter is re-laid once
+//   per set of weights into [K/MT][C/16][tap][c/4][MT k][4 c] (prepare_filter_kernel), MT =
+//   output channels per CTA.  One tap of one CTA is then a single contiguous run of MT*64 bytes
+//   that IS the K-major canonical layout and arrives by one bulk copy; the splitter warps add its
+//   lo copy.
 #include "tc_common.cuh"
 
 namespace
 {
 using namespace sb;
 
-constexpr int MAX_MT = 4;  // accumulator tiles per CTA
-constexpr int B_STAGES = 4;
-constexpr int A_SLOTS_MAX = 4;
+constexpr int W_STAGES_MAX = 4; // filter stages, each one group of taps (a kernel row)
+constexpr int X_SLOTS_MAX = 3;
+constexpr int RAW_SLOTS_MAX = 2;
 
 struct TcArgs
 {
     int N, C, K, H, W, Ho, Wo, Fh, Fw, pad_t, pad_l;
     int cbs, taps;
-    int PW, PR;          // patch width / rows
-    int MT;              // GEMM rows per CTA
-    int n_mtiles;        // accumulator tiles: 128-row tiles then an optional 64-row tile
-    int mtile_rows[MAX_MT];
-    int m_tiles_per_img; // CTAs along M per image
-    int NT;              // output channels per CTA
-    int n_tiles;         // K / NT
-    int a_slots;         // activation patches in flight (1..4)
-    int group;           // filter taps summed in tensor memory before a flush (1 or Fw)
+    int PW, PR;        // patch width / rows
+    int NPX;           // pixels (GEMM columns) per CTA: 64, 128, 192 or 256
+    int px_tiles;      // CTAs along the pixel axis per image
+    int MT;            // output channels per CTA (tensor-core M): 128 or 64
+    int k_tiles;       // ceil(K / MT)
+    int x_entries;     // entries between the 4-channel chunks of a canonical patch (>= PR*PW)
+    int x_slots, raw_slots, w_stages;
+    int group;         // filter taps summed in tensor memory before a flush
     int accumulate, act;
     float slope;
+    unsigned smem_bytes;
 };
 
-__global__ void __launch_bounds__(256)
-split_tf32_kernel(long long n4, const float4 *__restrict__ x, float4 *__restrict__ lo)
-{
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride)
-    {
-        const float4 v = x[i];
-        float4 r;
-        r.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
-        r.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
-        r.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
-        r.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
-        lo[i] = r;
-    }
-}
-
 // Output channels per CTA, a function of K alone so that filter preparation and the
-// convolution agree: two tensor-memory buffers x two accumulator tiles x NT columns must fit
-// the 512 columns, and a thread keeps 64 columns of each tile in registers.
-__host__ __device__ inline int pick_nt(int K)
-{
-    return (K % 128 == 0) ? 128 : (K % 64 == 0) ? 64 : (K % 32 == 0) ? 32 : 16;
-}
+// convolution agree.
+__host__ __device__ inline int pick_mt(int K) { return K >= 128 ? 128 : 64; }
 
-// packed filter [K/16][slab][16 c][16 k] -> hi and lo copies in [K/NT][slab][c/4][NT k][4 c]
+// packed filter [K/16][slab][16 c][16 k] -> [K/MT][slab][c/4][kv k][4 c]; kv = MT except in a last,
+// partial tile (K % MT channels).  Same number of elements as the packed filter.
 __global__ void __launch_bounds__(256)
-prepare_filter_kernel(long long n, int slabs, int NT, const float *__restrict__ w, float *__restrict__ hi,
-                      float *__restrict__ lo)
+prepare_filter_kernel(long long n, int slabs, int MT, int K, const float *__restrict__ w, float *__restrict__ hi)
 {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n)
@@ -88,65 +73,97 @@ prepare_filter_kernel(long long n, int slabs, int NT, const float *__restrict__ 
     const long long t = i >> 8;            // kb16 * slabs + slab
     const int slab = (int)(t % slabs);
     const int k = (int)(t / slabs) * 16 + k16;
-    const float v = w[i];
-    const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
-    const long long o = (((long long)(k / NT) * slabs + slab) * 4 + (c >> 2)) * NT * 4 + (long long)(k % NT) * 4 + (c & 3);
-    hi[o] = v;
-    lo[o] = v - h;
+    const int tile = k / MT;
+    const int kv = (K - tile * MT) < MT ? (K - tile * MT) : MT;
+    const long long o = (long long)tile * MT * slabs * 16 + ((long long)slab * 4 + (c >> 2)) * kv * 4 +
+                        (long long)(k - tile * MT) * 4 + (c & 3);
+    hi[o] = w[i];
 }
 
 // Tensor-core accumulation truncates: every MMA adds into the fp32 accumulator with
 // round-toward-zero, a one-sided error that grows with the number of accumulations (measured
 // here: 3e-5 of the output range after 1700 MMAs).  So tensor memory only ever holds the sum
-// of ONE filter tap (6 MMAs per accumulator tile); eight accumulation warps pull each tap's
-// partial sums out with tcgen05.ld and add them into fp32 registers with round-to-nearest,
-// while the tensor core already works on the next tap in the second half of tensor memory.
+// of one kernel row of one channel block (6 MMAs per tap); eight accumulation warps pull
+// these partial sums out with tcgen05.ld and add them into fp32 registers with
+// round-to-nearest, while the tensor core already works on the next group of taps in the second
+// half of tensor memory.
 //
-// warp 0: TMA producer, warp 1: MMA issuer, warps 2..9: accumulation + epilogue (lane quarter
-// = warp % 4, column half = (warp - 2) / 4)
+// warp 0: TMA producer, warp 1: MMA issuer (warps 2..3 idle), warps 4..11: accumulation +
+// epilogue (lane quarter = warp % 4, pixel half = (warp - 4) / 4), warps 12..15: operand
+// splitters (patch re-layout and lo copies).  The first and last warpgroups give registers
+// back (setmaxnreg) so that the accumulation warps can hold 128 running sums per thread
+// without spilling.
+//
+// The unit of the filter pipeline is a GROUP of taps (one kernel row): one bulk copy, one pass
+// of the splitters, one tcgen05.commit.  A commit keeps the issuing thread busy for several
+// hundred cycles (measured: about 500), so with one commit per tap the single MMA thread, not
+// the tensor pipe, set the pace.  The same commit frees the filter stage for the producer and
+// hands the partial sums to the accumulation warps.
 constexpr int ACC_WARPS = 8;
-constexpr int MAX_NT = 128;        // output channels per CTA
-constexpr int COLS_PER_THREAD = 64; // of one accumulator tile
+constexpr int FIRST_ACC_WARP = 4;
+constexpr int FIRST_SPLIT_WARP = 12;
+constexpr int SPLIT_THREADS = 128;
+constexpr int NUM_THREADS = 512;
+constexpr int COLS_PER_THREAD = 128;
 
-__global__ void __launch_bounds__(320, 1)
-conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
-                   const float *__restrict__ filt_hi, const float *__restrict__ filt_lo,
+__device__ __forceinline__ float4 lo_of(const float4 v)
+{
+    float4 r;
+    r.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+    r.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+    r.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+    r.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+    return r;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__restrict__ filt,
                    const TcArgs a, const float *__restrict__ bias, float *__restrict__ out, int *status)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t a_full[A_SLOTS_MAX], a_empty[A_SLOTS_MAX], b_full[B_STAGES], b_empty[B_STAGES];
-    __shared__ __align__(8) uint64_t t_full[2], t_empty[2];
+    __shared__ __align__(8) uint64_t raw_full[RAW_SLOTS_MAX], raw_empty[RAW_SLOTS_MAX];
+    __shared__ __align__(8) uint64_t x_ready[X_SLOTS_MAX], x_empty[X_SLOTS_MAX];
+    __shared__ __align__(8) uint64_t w_full[W_STAGES_MAX], w_ready[W_STAGES_MAX], g_done[W_STAGES_MAX];
+    __shared__ __align__(8) uint64_t t_empty[2];
     __shared__ uint32_t tmem_base_s;
 
-    const uint32_t a_bytes = (uint32_t)a.PR * a.PW * 64;      // bytes of one hi (or lo) patch
-    const uint32_t a_part = (a_bytes + 127u) & ~127u;         // its 128-byte aligned footprint
-    const uint32_t a_chunk = (uint32_t)a.PR * a.PW * 16;      // bytes between channel chunks
-    const uint32_t b_part = (uint32_t)a.NT * 64;              // bytes of one hi (or lo) tap tile
-    const uint32_t b_chunk = (uint32_t)a.NT * 16;             // bytes between 4-channel chunks
-    uint8_t *sA = smem;                                        // [slot][hi|lo][chunk][PR][PW][16 B]
-    uint8_t *sB = smem + (size_t)a.a_slots * 2 * a_part;      // [stage][hi|lo][c/4][NT k][16 B]
+    const uint32_t entries = (uint32_t)a.PR * a.PW;
+    const uint32_t raw_bytes = entries * 64;                    // one raw patch [entry][16 floats]
+    const uint32_t raw_part = (raw_bytes + 127u) & ~127u;
+    const uint32_t x_chunk = (uint32_t)a.x_entries * 16;       // bytes between channel chunks
+    const uint32_t x_part = (4 * x_chunk + 127u) & ~127u;      // one canonical hi (or lo) patch
+    const uint32_t w_part = (uint32_t)a.MT * 64;               // one hi (or lo) tap tile
+    const uint32_t w_chunk = (uint32_t)a.MT * 16;
+    uint8_t *sRaw = smem;                                            // [raw slot][entry][64 B]
+    uint8_t *sX = sRaw + (size_t)a.raw_slots * raw_part;            // [slot][hi|lo][chunk][entry][16 B]
+    uint8_t *sW = sX + (size_t)a.x_slots * 2 * x_part;              // [stage][hi|lo][tap in group][c/4][MT k][16 B]
+    const uint32_t w_half_stage = (uint32_t)a.group * w_part;       // hi (or lo) tiles of one stage
 
     int bid = blockIdx.x;
-    const int nt = bid % a.n_tiles; bid /= a.n_tiles;
-    const int mt = bid % a.m_tiles_per_img;
-    const int n = bid / a.m_tiles_per_img;
-    const int m0 = mt * a.MT;
+    const int kt = bid % a.k_tiles; bid /= a.k_tiles;
+    const int pt = bid % a.px_tiles;
+    const int n = bid / a.px_tiles;
+    const int m0 = pt * a.NPX;
     const int r_first = m0 / a.PW;
     const int m_local0 = m0 - r_first * a.PW;
+    const int kv = (a.K - kt * a.MT) < a.MT ? (a.K - kt * a.MT) : a.MT; // channels of this tile
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int buf_cols = a.n_mtiles * a.NT; // columns of one tensor-memory buffer
     uint32_t tmem_cols = 32;
-    while ((int)tmem_cols < 2 * buf_cols)
+    while ((int)tmem_cols < 2 * a.NPX)
         tmem_cols <<= 1;
 
     if (warp == 0)
     {
         if (lane == 0)
         {
-            for (int i = 0; i < A_SLOTS_MAX; ++i) { mbar_init(&a_full[i], 1); mbar_init(&a_empty[i], 1); }
-            for (int i = 0; i < 2; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], ACC_WARPS); }
-            for (int i = 0; i < B_STAGES; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
+            for (int i = 0; i < RAW_SLOTS_MAX; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], SPLIT_THREADS); }
+            for (int i = 0; i < X_SLOTS_MAX; ++i) { mbar_init(&x_ready[i], SPLIT_THREADS); mbar_init(&x_empty[i], 1); }
+            for (int i = 0; i < W_STAGES_MAX; ++i)
+            {
+                mbar_init(&w_full[i], 1); mbar_init(&w_ready[i], SPLIT_THREADS); mbar_init(&g_done[i], 1);
+            }
+            for (int i = 0; i < 2; ++i) mbar_init(&t_empty[i], ACC_WARPS);
             fence_barrier_init();
         }
         __syncwarp();
@@ -158,168 +175,183 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
     tc_fence_after_sync();
     const uint32_t tmem = tmem_base_s;
     const int steps = a.cbs * a.taps;
+    const int groups = steps / a.group, groups_per_cb = a.taps / a.group;
 
-    if (warp == 0 && lane == 0)
+    if (warp < FIRST_ACC_WARP || warp >= FIRST_SPLIT_WARP)
     {
-        // ---------------- producer ----------------
-        bool ok = true;
-        int bs = 0;
-        for (int cb = 0; cb < a.cbs && ok; ++cb)
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp == 0 && lane == 0)
         {
-            const int slot = cb % a.a_slots;
-            const int use = cb / a.a_slots;
-            if (use > 0)
-                ok = mbar_wait(&a_empty[slot], (use - 1) & 1, status, 11);
-            if (!ok)
-                break;
-            uint8_t *dst = sA + (size_t)slot * 2 * a_part;
-            mbar_expect_tx(&a_full[slot], 2 * a_bytes);
-            tma_load_5d(dst, &map_a_hi, 0, -a.pad_l, r_first - a.pad_t, 0, n * a.cbs + cb, &a_full[slot]);
-            tma_load_5d(dst + a_part, &map_a_lo, 0, -a.pad_l, r_first - a.pad_t, 0, n * a.cbs + cb, &a_full[slot]);
-            for (int tap = 0; tap < a.taps && ok; ++tap, ++bs)
+            // ---------------- producer ----------------
+            bool ok = true;
+            const size_t tile_base = (size_t)kt * a.MT * steps * 16; // floats before this channel tile
+            for (int g = 0; g < groups && ok; ++g)
             {
-                const int st = bs % B_STAGES, buse = bs / B_STAGES;
-                if (buse > 0)
-                    ok = mbar_wait(&b_empty[st], (buse - 1) & 1, status, 12);
+                if (g % groups_per_cb == 0)
+                {
+                    const int cb = g / groups_per_cb;
+                    const int rs = cb % a.raw_slots, ruse = cb / a.raw_slots;
+                    if (ruse > 0)
+                        ok = mbar_wait(&raw_empty[rs], (ruse - 1) & 1, status, 11);
+                    if (!ok)
+                        break;
+                    mbar_expect_tx(&raw_full[rs], raw_bytes);
+                    tma_load_4d(sRaw + (size_t)rs * raw_part, &map_x, 0, -a.pad_l, r_first - a.pad_t, n * a.cbs + cb,
+                                &raw_full[rs]);
+                }
+                const int st = g % a.w_stages, wuse = g / a.w_stages;
+                if (wuse > 0)
+                    ok = mbar_wait(&g_done[st], (wuse - 1) & 1, status, 12);
                 if (!ok)
                     break;
-                uint8_t *bd = sB + (size_t)st * 2 * b_part;
-                mbar_expect_tx(&b_full[st], 2 * b_part);
-                const size_t off = ((size_t)nt * steps + (size_t)(cb * a.taps + tap)) * (b_part / 4);
-                tma_load_1d(bd, filt_hi + off, b_part, &b_full[st]);
-                tma_load_1d(bd + b_part, filt_lo + off, b_part, &b_full[st]);
+                uint8_t *wd = sW + (size_t)st * 2 * w_half_stage;
+                const float *src = filt + tile_base + (size_t)g * a.group * kv * 16;
+                mbar_expect_tx(&w_full[st], (uint32_t)a.group * kv * 64);
+                if (kv == a.MT)
+                    tma_load_1d(wd, src, w_half_stage, &w_full[st]); // the group's taps are contiguous
+                else
+                    for (int t = 0; t < a.group; ++t)
+                        for (int j = 0; j < 4; ++j) // partial tile: kv of MT rows per 4-channel chunk
+                            tma_load_1d(wd + t * w_part + j * w_chunk, src + ((size_t)t * 4 + j) * kv * 4,
+                                        (uint32_t)kv * 16, &w_full[st]);
             }
         }
-    }
-    else if (warp == 1 && lane == 0)
-    {
-        // ---------------- MMA issuer ----------------
-        // One thread feeds the tensor core, so the per-MMA instruction count matters: all
-        // descriptor fields except the 16-byte-granular start address are fixed per CTA, and
-        // a new operand position is one 64-bit add on a precomputed descriptor.
-        bool ok = true;
-        int bs = 0;
-        const uint64_t a_desc0 = make_smem_desc(smem_u32(sA), a_chunk, 128, 0);
-        const uint64_t b_desc0 = make_smem_desc(smem_u32(sB), b_chunk, 128, 0);
-        const uint32_t idesc0 = make_idesc(1 /*f32*/, 2 /*tf32*/, 2 /*tf32*/, 0 /*A K-major*/, 0 /*B K-major*/,
-                                           (uint32_t)a.mtile_rows[0], (uint32_t)a.NT);
-        const uint32_t idesc1 = make_idesc(1, 2, 2, 0, 0, (uint32_t)(a.n_mtiles > 1 ? a.mtile_rows[1] : 128),
-                                           (uint32_t)a.NT);
-        const uint64_t a_lo_off = a_part >> 4, b_lo_off = b_part >> 4;
-        const uint64_t a_half = (2 * a_chunk) >> 4, b_half = (2 * b_chunk) >> 4;
-        const uint64_t a_tile1 = (uint64_t)a.mtile_rows[0];          // rows of tile 0 = 16-byte entries
-        const bool two_tiles = a.n_mtiles > 1;
-        for (int cb = 0; cb < a.cbs && ok; ++cb)
+        else if (warp == 1 && lane == 0)
         {
-            const int slot = cb % a.a_slots;
-            ok = mbar_wait(&a_full[slot], (cb / a.a_slots) & 1, status, 13);
-            if (!ok)
-                break;
-            const uint64_t a_slot = a_desc0 + ((uint64_t)(slot * 2 * a_part) >> 4) + (uint64_t)m_local0;
-            int kh = 0, kw = 0;
-            for (int tap = 0; tap < a.taps && ok; ++tap, ++bs)
+            // ---------------- MMA issuer ----------------
+            // One thread feeds the tensor core: all descriptor fields except the
+            // 16-byte-granular start address are fixed per CTA, and a new operand position is one
+            // 64-bit add on a precomputed descriptor.  A = filter tap (M = channels), B = patch
+            // shifted by the tap (N = pixels).
+            bool ok = true;
+            const uint64_t x_desc0 = make_smem_desc(smem_u32(sX), x_chunk, 128, 0) + (uint64_t)m_local0;
+            const uint64_t w_desc0 = make_smem_desc(smem_u32(sW), w_chunk, 128, 0);
+            const uint32_t idesc = make_idesc(1 /*f32*/, 2 /*tf32*/, 2 /*tf32*/, 0 /*A K-major*/, 0 /*B K-major*/,
+                                              (uint32_t)a.MT, (uint32_t)a.NPX);
+            const uint64_t x_lo_off = x_part >> 4, w_lo_off = w_half_stage >> 4, w_tap = w_part >> 4;
+            const uint64_t x_half = (2 * x_chunk) >> 4, w_half = (2 * w_chunk) >> 4;
+            uint64_t x_slot = 0;
+            int slot = 0, kh = 0, kw = 0;
+            for (int g = 0; g < groups && ok; ++g)
             {
-                const int st = bs % B_STAGES;
-                const int chunk = bs / a.group, in_chunk = bs - chunk * a.group;
-                const int tb = chunk & 1; // tensor-memory buffer of this group of taps
-                ok = mbar_wait(&b_full[st], (bs / B_STAGES) & 1, status, 14);
-                if (ok && in_chunk == 0 && chunk >= 2)
-                    ok = mbar_wait(&t_empty[tb], ((chunk >> 1) - 1) & 1, status, 16);
+                if (g % groups_per_cb == 0)
+                {
+                    const int cb = g / groups_per_cb;
+                    slot = cb % a.x_slots;
+                    ok = mbar_wait(&x_ready[slot], (cb / a.x_slots) & 1, status, 13);
+                    if (!ok)
+                        break;
+                    x_slot = x_desc0 + ((uint64_t)slot * 2 * x_part >> 4);
+                    kh = 0; kw = 0;
+                }
+                const int st = g % a.w_stages, tb = g & 1; // filter stage / tensor-memory buffer
+                ok = mbar_wait(&w_ready[st], (g / a.w_stages) & 1, status, 14);
+                if (ok && g >= 2)
+                    ok = mbar_wait(&t_empty[tb], ((g >> 1) - 1) & 1, status, 16);
                 if (!ok)
                     break;
                 tc_fence_after_sync();
-                const uint64_t ah = a_slot + (uint64_t)(kh * a.PW + kw), al = ah + a_lo_off;
-                const uint64_t bh = b_desc0 + ((uint64_t)(st * 2 * b_part) >> 4), bl = bh + b_lo_off;
-                const uint32_t d0 = tmem + (uint32_t)(tb * buf_cols), d1 = d0 + (uint32_t)a.NT;
-                const uint32_t fresh = in_chunk == 0 ? 0u : 1u;
-                // tile 0
-                tc_mma_tf32(d0, al, bh, idesc0, fresh);
-                tc_mma_tf32(d0, ah, bl, idesc0, 1u);
-                tc_mma_tf32(d0, ah, bh, idesc0, 1u);
-                tc_mma_tf32(d0, al + a_half, bh + b_half, idesc0, 1u);
-                tc_mma_tf32(d0, ah + a_half, bl + b_half, idesc0, 1u);
-                tc_mma_tf32(d0, ah + a_half, bh + b_half, idesc0, 1u);
-                if (two_tiles)
+                const uint32_t d = tmem + (uint32_t)(tb * a.NPX);
+                uint64_t wh = w_desc0 + ((uint64_t)st * 2 * w_half_stage >> 4);
+                for (int t = 0; t < a.group; ++t, wh += w_tap)
                 {
-                    const uint64_t ah1 = ah + a_tile1, al1 = al + a_tile1;
-                    tc_mma_tf32(d1, al1, bh, idesc1, fresh);
-                    tc_mma_tf32(d1, ah1, bl, idesc1, 1u);
-                    tc_mma_tf32(d1, ah1, bh, idesc1, 1u);
-                    tc_mma_tf32(d1, al1 + a_half, bh + b_half, idesc1, 1u);
-                    tc_mma_tf32(d1, ah1 + a_half, bl + b_half, idesc1, 1u);
-                    tc_mma_tf32(d1, ah1 + a_half, bh + b_half, idesc1, 1u);
+                    const uint64_t xh = x_slot + (uint64_t)(kh * a.PW + kw), xl = xh + x_lo_off;
+                    const uint64_t wl = wh + w_lo_off;
+                    tc_mma_tf32(d, wl, xh, idesc, t == 0 ? 0u : 1u);
+                    tc_mma_tf32(d, wh, xl, idesc, 1u);
+                    tc_mma_tf32(d, wh, xh, idesc, 1u);
+                    tc_mma_tf32(d, wl + w_half, xh + x_half, idesc, 1u);
+                    tc_mma_tf32(d, wh + w_half, xl + x_half, idesc, 1u);
+                    tc_mma_tf32(d, wh + w_half, xh + x_half, idesc, 1u);
+                    if (++kw == a.Fw) { kw = 0; ++kh; }
                 }
-                tc_commit(&b_empty[st]); // the tap's filter tile is free once these MMAs retire
-                if (in_chunk == a.group - 1)
-                    tc_commit(&t_full[tb]); // the group's partial sums are complete
-                if (tap == a.taps - 1)
-                    tc_commit(&a_empty[slot]);
-                if (++kw == a.Fw) { kw = 0; ++kh; }
+                // one commit: the stage is free for the producer and the group's partial sums
+                // are complete for the accumulation warps
+                tc_commit(&g_done[st]);
+                if ((g + 1) % groups_per_cb == 0)
+                    tc_commit(&x_empty[slot]);
+            }
+        }
+        else if (warp >= FIRST_SPLIT_WARP)
+        {
+            // ---------------- operand splitters ----------------
+            // in the order the MMA issuer consumes: the patch of a channel block, then its taps
+            const int sid = tid - FIRST_SPLIT_WARP * 32;
+            bool ok = true;
+            int ws = 0;
+            for (int cb = 0; cb < a.cbs && ok; ++cb)
+            {
+                const int rs = cb % a.raw_slots, slot = cb % a.x_slots, xuse = cb / a.x_slots;
+                ok = mbar_wait(&raw_full[rs], (cb / a.raw_slots) & 1, status, 17);
+                if (ok && xuse > 0)
+                    ok = mbar_wait(&x_empty[slot], (xuse - 1) & 1, status, 19);
+                if (!ok)
+                    break;
+                {
+                    // [entry][chunk] -> [chunk][entry], hi and lo.  A quarter warp reads 128
+                    // contiguous bytes; x_entries % 8 == 2 spreads its four chunk rows over
+                    // different banks on the way out.
+                    const uint8_t *raw = sRaw + (size_t)rs * raw_part;
+                    uint8_t *xh = sX + (size_t)slot * 2 * x_part, *xl = xh + x_part;
+                    const uint32_t total = entries * 4;
+                    for (uint32_t i = (uint32_t)sid; i < total; i += SPLIT_THREADS)
+                    {
+                        const float4 v = *reinterpret_cast<const float4 *>(raw + (size_t)i * 16);
+                        const uint32_t o = (i & 3u) * x_chunk + (i >> 2) * 16u;
+                        *reinterpret_cast<float4 *>(xh + o) = v;
+                        *reinterpret_cast<float4 *>(xl + o) = lo_of(v);
+                    }
+                }
+                fence_proxy_async();
+                mbar_arrive(&x_ready[slot]);
+                mbar_arrive(&raw_empty[rs]);
+                for (int gi = 0; gi < groups_per_cb && ok; ++gi, ++ws)
+                {
+                    const int st = ws % a.w_stages;
+                    ok = mbar_wait(&w_full[st], (ws / a.w_stages) & 1, status, 18);
+                    if (!ok)
+                        break;
+                    uint8_t *wh = sW + (size_t)st * 2 * w_half_stage;
+                    for (uint32_t o = (uint32_t)sid * 16u; o < w_half_stage; o += SPLIT_THREADS * 16u)
+                        *reinterpret_cast<float4 *>(wh + w_half_stage + o) = lo_of(*reinterpret_cast<const float4 *>(wh + o));
+                    fence_proxy_async();
+                    mbar_arrive(&w_ready[st]);
+                }
             }
         }
     }
-    else if (warp >= 2)
+    else
     {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
         // ---------------- accumulation + epilogue ----------------
-        const int quarter = warp & 3;          // TMEM lanes [32*quarter, 32*quarter+32)
-        const int chalf = (warp - 2) >> 2;     // which half of the tile's columns
-        const int my_cols = (a.NT >= 32) ? a.NT / 2 : a.NT;
-        const bool active = (a.NT >= 32) || chalf == 0;
-        const int col0 = chalf * my_cols;      // first column inside a tile (0 when NT < 32)
-        float acc[2][COLS_PER_THREAD];
+        const int quarter = warp & 3;                    // TMEM lanes [32*quarter, 32*quarter+32)
+        const int phalf = (warp - FIRST_ACC_WARP) >> 2;  // which half of the tile's pixels
+        const int my_cols = a.NPX / 2;                   // 32, 64, 96 or 128
+        const int col0 = phalf * my_cols;
+        float acc[COLS_PER_THREAD];
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int c = 0; c < COLS_PER_THREAD; ++c)
-                acc[j][c] = 0.f;
+        for (int c = 0; c < COLS_PER_THREAD; ++c)
+            acc[c] = 0.f;
         bool ok = true;
-        for (int g = 0; g < steps / a.group && ok; ++g)
+        for (int g = 0; g < groups && ok; ++g)
         {
             const int tb = g & 1;
-            ok = mbar_wait(&t_full[tb], (g >> 1) & 1, status, 15, 1u << 24);
+            ok = mbar_wait(&g_done[g % a.w_stages], (g / a.w_stages) & 1, status, 15, 1u << 24);
             if (!ok)
                 break;
             tc_fence_after_sync();
-            if (active)
+            const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(tb * a.NPX + col0);
+#pragma unroll
+            for (int piece = 0; piece < COLS_PER_THREAD / 32; ++piece)
             {
-                // four pieces of 32 columns (2 tiles x 2); a tile's two loads are in flight
-                // together, so a flush costs two tensor-memory round trips
-                const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(tb * buf_cols + col0);
-#pragma unroll
-                for (int j = 0; j < 2; ++j)
+                if (piece * 32 < my_cols)
                 {
-                    if (j < a.n_mtiles)
-                    {
-                        uint32_t v0[32], v1[32];
-                        if (my_cols >= 64)
-                        {
-                            tmem_ld32(tbase + (uint32_t)(j * a.NT), v0);
-                            tmem_ld32(tbase + (uint32_t)(j * a.NT + 32), v1);
-                            tmem_ld_wait();
+                    uint32_t v[32];
+                    tmem_ld32(tbase + (uint32_t)(piece * 32), v);
+                    tmem_ld_wait();
 #pragma unroll
-                            for (int e = 0; e < 32; ++e)
-                            {
-                                acc[j][e] += __uint_as_float(v0[e]);
-                                acc[j][32 + e] += __uint_as_float(v1[e]);
-                            }
-                        }
-                        else if (my_cols == 32)
-                        {
-                            tmem_ld32(tbase + (uint32_t)(j * a.NT), v0);
-                            tmem_ld_wait();
-#pragma unroll
-                            for (int e = 0; e < 32; ++e)
-                                acc[j][e] += __uint_as_float(v0[e]);
-                        }
-                        else
-                        {
-                            tmem_ld16(tbase + (uint32_t)(j * a.NT), v0);
-                            tmem_ld_wait();
-#pragma unroll
-                            for (int e = 0; e < 16; ++e)
-                                acc[j][e] += __uint_as_float(v0[e]);
-                        }
-                    }
+                    for (int e = 0; e < 32; ++e)
+                        acc[piece * 32 + e] += __uint_as_float(v[e]);
                 }
             }
             tc_fence_before_sync();
@@ -327,52 +359,33 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
             if (lane == 0)
                 mbar_arrive(&t_empty[tb]);
         }
-        if (ok && active)
+        // 128-channel tile: lane l of quarter q holds channel 32q + l; 64-channel tile: channel
+        // 16q + l in lanes 0..15 of each quarter
+        const int k_local = (a.MT == 128) ? quarter * 32 + lane : quarter * 16 + lane;
+        const bool lane_has_row = (a.MT == 128) || (lane < 16);
+        if (ok && lane_has_row && k_local < kv)
         {
-            int row_off = 0;
+            const int k = kt * a.MT + k_local;
+            const float bv = bias ? bias[k] : 0.f;
+            float *oplane = out + ((size_t)n * (a.K / CB) + k / CB) * a.Ho * a.Wo * CB + (k % CB);
+            int m = m0 + col0;
+            int r = m / a.PW, c = m - r * a.PW;
 #pragma unroll
-            for (int j = 0; j < 2; ++j)
+            for (int e = 0; e < COLS_PER_THREAD; ++e)
             {
-                if (j < a.n_mtiles)
+                if (e < my_cols)
                 {
-                    const int rows = a.mtile_rows[j];
-                    // 128-row tile: lane l of quarter q holds row 32q + l; 64-row tile: rows
-                    // 16q + l in lanes 0..15 of each quarter
-                    const int trow = (rows == 128) ? quarter * 32 + lane : quarter * 16 + lane;
-                    const bool lane_has_row = (rows == 128) || (lane < 16);
-                    const int m = m0 + row_off + trow;
-                    const int r = m / a.PW, c = m - r * a.PW;
-                    const bool valid = lane_has_row && r < a.Ho && c < a.Wo;
-#pragma unroll
-                    for (int cg = 0; cg < COLS_PER_THREAD / 16; ++cg)
+                    if (r < a.Ho && c < a.Wo)
                     {
-                        if (valid && cg * 16 < my_cols)
-                        {
-                            const int kg = nt * a.NT + col0 + cg * 16;
-                            float *o = out + ((((size_t)n * (a.K / CB) + kg / CB) * a.Ho + r) * a.Wo + c) * CB;
-#pragma unroll
-                            for (int q = 0; q < 4; ++q)
-                            {
-                                float4 x;
-                                x.x = acc[j][cg * 16 + q * 4 + 0]; x.y = acc[j][cg * 16 + q * 4 + 1];
-                                x.z = acc[j][cg * 16 + q * 4 + 2]; x.w = acc[j][cg * 16 + q * 4 + 3];
-                                if (a.accumulate)
-                                {
-                                    const float4 s = *reinterpret_cast<const float4 *>(o + q * 4);
-                                    x.x += s.x; x.y += s.y; x.z += s.z; x.w += s.w;
-                                }
-                                if (bias)
-                                {
-                                    const float4 b = *reinterpret_cast<const float4 *>(bias + kg + q * 4);
-                                    x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
-                                }
-                                x.x = apply_act(x.x, a.act, a.slope); x.y = apply_act(x.y, a.act, a.slope);
-                                x.z = apply_act(x.z, a.act, a.slope); x.w = apply_act(x.w, a.act, a.slope);
-                                *reinterpret_cast<float4 *>(o + q * 4) = x;
-                            }
-                        }
+                        float *o = oplane + ((size_t)r * a.Wo + c) * CB;
+                        float x = acc[e];
+                        if (a.accumulate)
+                            x += *o;
+                        if (bias)
+                            x += bv;
+                        *o = apply_act(x, a.act, a.slope);
                     }
-                    row_off += rows;
+                    if (++c == a.PW) { c = 0; ++r; }
                 }
             }
         }
@@ -382,117 +395,113 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
     if (warp == 0)
         tmem_dealloc(tmem, tmem_cols);
 }
-} // namespace
 
-extern "C"
-{
-int small_b200_split_tf32(int64_t n, const float *x, float *lo, void *stream)
-{
-    if (n < 0 || n % 4 != 0)
-        return fail(SMALL_B200_INVALID_ARGUMENT, "split_tf32 ERROR: element count must be a multiple of 4.");
-    if (n == 0)
-        return SMALL_B200_OK;
-    long long blocks = (n / 4 + 255) / 256;
-    const long long cap = (long long)num_sms() * 16;
-    if (blocks > cap)
-        blocks = cap;
-    split_tf32_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(n / 4, (const float4 *)x, (float4 *)lo);
-    return launched("split_tf32_kernel");
-}
-
-int small_b200_conv2d_f32_tf32x3_supported(const small_b200_layer *L)
+// Tiling and shared-memory plan of one layer; false when the shape is not covered.
+bool plan(const small_b200_layer *L, TcArgs &a)
 {
     if (!L || L->stride != 1 || L->C % CB != 0 || L->K % CB != 0 || L->C <= 0 || L->K <= 0)
-        return 0;
-    const int PW = L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r);
-    return (PW <= 256 && L->Fw <= 16 && L->Fh <= 16) ? 1 : 0;
-}
-
-int small_b200_filter_prepare_tf32x3(const small_b200_layer *L, const float *filt, float *prepared, void *stream)
-{
-    if (!small_b200_conv2d_f32_tf32x3_supported(L))
-        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: shape not covered by the tensor-core path.");
-    const long long n = (long long)L->K * L->C * L->Fh * L->Fw;
-    prepare_filter_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(
-        n, (L->C / CB) * L->Fh * L->Fw, pick_nt(L->K), filt, prepared, prepared + n);
-    return launched("prepare_filter_kernel");
-}
-
-int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, const float *in_lo,
-                                 const float *filt_prepared, const float *bias, float *out, void *stream)
-{
-    const float *filt = filt_prepared;
-    const float *filt_lo = filt_prepared ? filt_prepared + (size_t)L->K * L->C * L->Fh * L->Fw : nullptr;
-    if (int rc = check_window_layer(L, "Conv2D<float>", true, 2))
-        return rc;
-    if (!small_b200_conv2d_f32_tf32x3_supported(L))
-        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: shape not covered by the tensor-core path.");
-    TcArgs a{};
+        return false;
+    if (L->H <= 0 || L->W <= 0 || L->Fh <= 0 || L->Fw <= 0 || L->Fw > 16 || L->Fh > 16)
+        return false;
+    a = TcArgs{};
     a.N = L->N; a.C = L->C; a.K = L->K; a.H = L->H; a.W = L->W; a.Fh = L->Fh; a.Fw = L->Fw;
     a.pad_t = L->pad_t; a.pad_l = L->pad_l;
     a.Ho = out_dim(L->H, L->pad_t, L->pad_b, L->Fh, 1);
     a.Wo = out_dim(L->W, L->pad_l, L->pad_r, L->Fw, 1);
     a.cbs = L->C / CB; a.taps = L->Fh * L->Fw;
     a.accumulate = L->accumulate; a.act = L->act; a.slope = L->slope;
+    a.PW = L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r);
+    if (a.PW > 256)
+        return false;
+    a.MT = pick_mt(a.K);
+    a.k_tiles = (a.K + a.MT - 1) / a.MT;
+    a.group = a.Fw; // one kernel row per flush: taps = Fh * Fw is a multiple of it
+    if (a.Ho == 0 || a.Wo == 0)
+        return true;
+    // GEMM columns of one image: the last valid one is (Ho-1)*PW + Wo-1
+    const int m_img = (a.Ho - 1) * a.PW + a.Wo;
+    const size_t limit = 226 * 1024;
+    const int tiles256 = (m_img + 255) / 256;
+    int npx_first = ((m_img + tiles256 - 1) / tiles256 + 63) / 64 * 64;
+    // {patch slots, filter stages (>= 2: a commit serves both rings), raw patch buffers}
+    static const int pref[][3] = {{2, 3, 1}, {2, 2, 1}, {1, 3, 1}, {1, 2, 1}};
+    for (int npx = npx_first; npx >= 64; npx -= 64)
+    {
+        a.NPX = npx;
+        a.px_tiles = (m_img + npx - 1) / npx;
+        const int need = (a.PW - 1) + npx + (a.Fh - 1) * a.PW + (a.Fw - 1);
+        a.PR = (need + a.PW - 1) / a.PW;
+        if (a.PR > 256)
+            continue;
+        const int entries = a.PR * a.PW;
+        a.x_entries = entries + ((2 - entries % 8) + 8) % 8; // % 8 == 2: conflict-free re-layout
+        const size_t raw_part = ((size_t)entries * 64 + 127) & ~(size_t)127;
+        const size_t x_part = ((size_t)a.x_entries * 64 + 127) & ~(size_t)127;
+        const size_t w_part = (size_t)a.MT * 64 * a.group;
+        for (const auto &p : pref)
+        {
+            const int xs = p[0] < a.cbs ? p[0] : a.cbs, rs = p[2] < a.cbs ? p[2] : a.cbs;
+            const size_t smem = (size_t)rs * raw_part + (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
+            if (smem <= limit)
+            {
+                a.x_slots = xs; a.w_stages = p[1]; a.raw_slots = rs; a.smem_bytes = (unsigned)smem;
+                return true;
+            }
+        }
+    }
+    return false;
+}
+} // namespace
+
+extern "C"
+{
+int small_b200_conv2d_f32_tf32x3_supported(const small_b200_layer *L)
+{
+    TcArgs a;
+    return plan(L, a) ? 1 : 0;
+}
+
+int small_b200_filter_prepare_tf32x3(const small_b200_layer *L, const float *filt, float *prepared, void *stream)
+{
+    if (!L || L->C % CB != 0 || L->K % CB != 0 || L->C <= 0 || L->K <= 0 || L->Fh <= 0 || L->Fw <= 0)
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: shape not covered by the tensor-core path.");
+    const long long n = (long long)L->K * L->C * L->Fh * L->Fw;
+    prepare_filter_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(
+        n, (L->C / CB) * L->Fh * L->Fw, pick_mt(L->K), L->K, filt, prepared);
+    return launched("prepare_filter_kernel");
+}
+
+int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, const float *filt_prepared,
+                                 const float *bias, float *out, void *stream)
+{
+    if (int rc = check_window_layer(L, "Conv2D<float>", true, 2))
+        return rc;
+    TcArgs a;
+    if (!plan(L, a))
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: shape not covered by the tensor-core path.");
     if (a.N == 0 || a.Ho == 0 || a.Wo == 0)
         return SMALL_B200_OK;
-    a.PW = L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r);
 
-    a.NT = pick_nt(a.K);
-    a.group = a.Fw; // one kernel row per flush: taps = Fh * Fw is a multiple of it
-    // GEMM rows of one image: the last valid row is (Ho-1)*PW + Wo-1
-    const int m_img = (a.Ho - 1) * a.PW + a.Wo;
-    const int MT = (m_img <= 128) ? 128 : (m_img <= 192) ? 192 : 256;
-    a.MT = MT;
-    a.n_mtiles = 0;
-    for (int left = MT; left > 0;)
+    CUtensorMap mx;
     {
-        const int rows = left >= 128 ? 128 : 64;
-        a.mtile_rows[a.n_mtiles++] = rows;
-        left -= rows;
-    }
-    a.m_tiles_per_img = (m_img + MT - 1) / MT;
-    a.n_tiles = a.K / a.NT;
-    const int need = (a.PW - 1) + MT + (a.Fh - 1) * a.PW + (a.Fw - 1) + 1;
-    a.PR = (need + a.PW - 1) / a.PW;
-    if (a.PR > 256)
-        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: patch too tall.");
-    const size_t a_part = (((size_t)a.PR * a.PW * 64) + 127) & ~(size_t)127, b_part = (size_t)a.NT * 64;
-    const size_t limit = 220 * 1024;
-    // as many activation slots as fit (a layer with few taps per channel block, e.g. 1x1,
-    // needs several patches in flight to cover the TMA latency)
-    size_t smem = 0;
-    for (a.a_slots = (a.cbs < A_SLOTS_MAX ? (a.cbs > 0 ? a.cbs : 1) : A_SLOTS_MAX); a.a_slots >= 1; --a.a_slots)
-    {
-        smem = (size_t)a.a_slots * 2 * a_part + (size_t)B_STAGES * 2 * b_part;
-        if (smem <= limit)
-            break;
-    }
-    if (a.a_slots < 1)
-        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: patch does not fit in shared memory.");
-
-    CUtensorMap ma_hi, ma_lo;
-    {
-        // activations [N*cbs][H][W][4 chunks][4 floats]
-        const uint64_t dims[5] = {4, (uint64_t)a.W, (uint64_t)a.H, 4, (uint64_t)a.N * a.cbs};
-        const uint64_t strides[4] = {64, (uint64_t)a.W * 64, 16, (uint64_t)a.H * a.W * 64};
-        const uint32_t box[5] = {4, (uint32_t)a.PW, (uint32_t)a.PR, 4, 1};
-        if (int rc = make_tensor_map(&ma_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, in, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
-            return rc;
-        if (int rc = make_tensor_map(&ma_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, in_lo, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+        // activations [N*cbs][H][W][16 floats]
+        const uint64_t dims[4] = {16, (uint64_t)a.W, (uint64_t)a.H, (uint64_t)a.N * a.cbs};
+        const uint64_t strides[3] = {64, (uint64_t)a.W * 64, (uint64_t)a.H * a.W * 64};
+        const uint32_t box[4] = {16, (uint32_t)a.PW, (uint32_t)a.PR, 1};
+        if (int rc = make_tensor_map(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, in, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
             return rc;
     }
     static bool configured = false;
     if (!configured)
     {
-        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         configured = true;
     }
     int *status = device_status_ptr();
     if (!status)
         return fail(SMALL_B200_CUDA_ERROR, "device status word not available");
-    const long long blocks = (long long)a.N * a.m_tiles_per_img * a.n_tiles;
-    conv_tf32x3_kernel<<<(unsigned)blocks, 320, smem, as_stream(stream)>>>(ma_hi, ma_lo, filt, filt_lo, a, bias, out, status);
+    const long long blocks = (long long)a.N * a.px_tiles * a.k_tiles;
+    conv_tf32x3_kernel<<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(mx, filt_prepared, a, bias, out, status);
     return launched("conv_tf32x3_kernel");
 }
 } // extern "C"
@@ -500,8 +509,8 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
 // ---------------------------------------------------------------------------------------------
 // The same tensor-core convolution for callers that must not allocate device memory.
 //
-// small_b200_conv2d_f32_tf32x3 needs two pieces of scratch from its caller: the lo half of the
-// activations and the re-laid filter.  Some callers cannot provide them: code that runs inside
+// small_b200_conv2d_f32_tf32x3 needs scratch from its caller: the filter re-laid for the tensor
+// core.  Some callers cannot provide it: code that runs inside
 // a region where cudaMalloc is forbidden or would synchronise the device (a real-time loop, a
 // plug-in that only ever receives its input and output pointers, a host that has handed all of
 // its device memory to another allocator).  For them the scratch lives in this fixed array
@@ -541,27 +550,21 @@ extern "C" int small_b200_conv2d_f32_tf32x3_noalloc(const small_b200_layer *L, c
     if (!small_b200_conv2d_f32_tf32x3_supported(L))
         return fail(SMALL_B200_INVALID_ARGUMENT,
                     "Conv2D<float> (3xTF32, no-alloc) ERROR: shape not covered by the tensor-core path.");
-    const size_t in_elems = (size_t)L->N * L->C * L->H * L->W;
     const size_t filt_elems = (size_t)L->K * L->C * L->Fh * L->Fw;
-    // lo half of the input (rounded up so the filter copies stay 256-byte aligned), then the
-    // re-laid filter and its lo copy
-    const size_t in_slot = (in_elems + 63) & ~(size_t)63;
-    const size_t need = in_slot + 2 * filt_elems;
+    const size_t need = filt_elems; // the re-laid filter
     if (need > STATIC_SCRATCH_FLOATS)
         return fail(SMALL_B200_INVALID_ARGUMENT,
                     "Conv2D<float> (3xTF32, no-alloc) ERROR: this call needs " + std::to_string(need * 4) +
-                        " bytes of scratch (input elements + 2 x filter elements, 4 bytes each) but the "
+                        " bytes of scratch (K*C*Fh*Fw filter elements, 4 bytes each) but the "
                         "built-in scratch holds " + std::to_string(STATIC_SCRATCH_FLOATS * 4) +
                         " bytes; use small_b200_conv2d_f32_tf32x3 with caller-provided scratch.");
     float *scratch = nullptr;
     if (int rc = static_scratch_ptr(&scratch))
         return rc;
-    float *in_lo = scratch, *prepared = scratch + in_slot;
-    // Nothing in the scratch has to start from zero: both regions are completely rewritten for
-    // the sizes of this call before the convolution reads them.
-    if (int rc = small_b200_split_tf32((int64_t)in_elems, in, in_lo, stream))
-        return rc;
+    float *prepared = scratch;
+    // Nothing in the scratch has to start from zero: the region this call reads is completely
+    // rewritten for the sizes of this call before the convolution reads it.
     if (int rc = small_b200_filter_prepare_tf32x3(L, filt, prepared, stream))
         return rc;
-    return small_b200_conv2d_f32_tf32x3(L, in, in_lo, prepared, bias, out, stream);
+    return small_b200_conv2d_f32_tf32x3(L, in, prepared, bias, out, stream);
 }

@@ -353,12 +353,6 @@ def Dense(output_elements, input_elements, input_buf, filter_buf, output_buf, *,
 
 
 # --------------------------------------------------------------------------- tensor-core fp32 conv
-def split_tf32(input_buf, lo_buf, *, stream=None):
-    """lo = x - (x with its 13 low mantissa bits cleared): the second operand of the 3xTF32
-    product.  No counterpart in the reference."""
-    check(lib().small_b200_split_tf32(input_buf.size(), _ptr(input_buf), _ptr(lo_buf), _stream(stream)))
-
-
 def tf32x3_supported(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
                      output_channels, input_channels, input_height, input_width):
     L = _layer(1, input_channels, output_channels, input_height, input_width, kernel_height,
@@ -368,7 +362,7 @@ def tf32x3_supported(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r
 
 def prepare_filter_3xTF32(kernel_height, kernel_width, output_channels, input_channels,
                           filter_buf, prepared_buf, *, stream=None):
-    """Re-lay a packed filter for the tensor-core path (hi copy + lo copy, 2x the elements)."""
+    """Re-lay a packed filter for the tensor-core path (same number of elements)."""
     L = _layer(1, input_channels, output_channels, 16, 16, kernel_height, kernel_width, 1, 0, 0, 0, 0)
     check(lib().small_b200_filter_prepare_tf32x3(C.byref(L), _ptr(filter_buf), _ptr(prepared_buf),
                                                  _stream(stream)))
@@ -376,12 +370,12 @@ def prepare_filter_3xTF32(kernel_height, kernel_width, output_channels, input_ch
 
 def Conv2D_3xTF32(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
                   output_channels, input_channels, input_height, input_width,
-                  input_buf, input_lo_buf, prepared_filter_buf, bias_buf, output_buf, *,
+                  input_buf, prepared_filter_buf, bias_buf, output_buf, *,
                   partial=False, activation=ACT_NONE, negative_slope=0.0, batch=1, stream=None):
     """small::Conv2D / PartialConv2D<FloatBuffer> (+ bias / activation) on the tensor cores;
-    input_lo_buf = split_tf32(input), prepared_filter_buf = prepare_filter_3xTF32(filter)."""
+    prepared_filter_buf = prepare_filter_3xTF32(filter)."""
     L = _layer(batch, input_channels, output_channels, input_height, input_width, kernel_height,
                kernel_width, stride, t_pad, b_pad, l_pad, r_pad, int(partial), activation, negative_slope)
-    check(lib().small_b200_conv2d_f32_tf32x3(C.byref(L), _ptr(input_buf), _ptr(input_lo_buf),
+    check(lib().small_b200_conv2d_f32_tf32x3(C.byref(L), _ptr(input_buf),
                                              _ptr(prepared_filter_buf), _ptr(bias_buf),
                                              _ptr(output_buf), _stream(stream)))

@@ -214,12 +214,9 @@ class Chain:
                 bs = torch.from_numpy(bp).to(self.dev)
             self.params.append((wt, bs))
         self.bufs = [torch.zeros(max_act, dtype=self.tdtype, device=self.dev) for _ in range(2)]
-        # tensor-core fp32 path: filters re-laid once (hi + lo copies), one scratch buffer for
-        # the lo half of whichever activation tensor feeds the current layer
+        # tensor-core fp32 path: filters re-laid once
         self.prepared = [None] * len(layers)
-        self.lo = None
         if dtype == "f32" and tensor_core:
-            lo_elems = 0
             for i, L in enumerate(layers):
                 if L["op"] != "conv" or i == 0:
                     continue
@@ -229,13 +226,10 @@ class Chain:
                 if not lib().small_b200_conv2d_f32_tf32x3_supported(C.byref(d)):
                     continue
                 wt = self.params[i][0]
-                prep = torch.empty(2 * wt.numel(), dtype=torch.float32, device=self.dev)
+                prep = torch.empty(wt.numel(), dtype=torch.float32, device=self.dev)
                 check(lib().small_b200_filter_prepare_tf32x3(C.byref(d), wt.data_ptr(), prep.data_ptr(),
                                                              torch.cuda.current_stream().cuda_stream))
                 self.prepared[i] = prep
-                lo_elems = max(lo_elems, batch * padded(L["C"]) * L["H"] * L["W"])
-            if lo_elems:
-                self.lo = torch.empty(lo_elems, dtype=torch.float32, device=self.dev)
             torch.cuda.synchronize()
         self.graph = None
         self.y = None
@@ -259,9 +253,7 @@ class Chain:
         l = lib()
         p = lambda t: t.data_ptr() if t is not None else None
         if L["op"] == "conv" and self.prepared[i] is not None:
-            n_in = self.batch * cin * L["H"] * L["W"]
-            check(l.small_b200_split_tf32(n_in, p(src), p(self.lo), stream))
-            check(l.small_b200_conv2d_f32_tf32x3(C.byref(d), p(src), p(self.lo), p(self.prepared[i]),
+            check(l.small_b200_conv2d_f32_tf32x3(C.byref(d), p(src), p(self.prepared[i]),
                                                  p(bs), p(dst), stream))
         elif L["op"] == "conv":
             check(getattr(l, f"small_b200_conv2d_{sfx}")(C.byref(d), p(src), p(wt), p(bs), p(dst), stream))

@@ -30,12 +30,6 @@ CASES = [
 ]
 
 
-def _split(buf):
-    lo = S.FloatBuffer(buf.size())
-    S.split_tf32(buf, lo)
-    return lo
-
-
 @pytest.mark.parametrize("case", CASES, ids=lambda c: "C{}_K{}_{}x{}_k{}x{}_{}_n{}".format(*[
     "".join(map(str, v)) if isinstance(v, tuple) else v for v in c]))
 @pytest.mark.parametrize("mode", ["plain", "partial_bias_leaky"])
@@ -50,32 +44,21 @@ def test_conv2d_3xtf32(oracle, case, mode):
     sh = shape(C, K, H, W, Fh, Fw, 1, pads, CB)
     ho, wo = sh.out_hw()
     I, F = fbuf(x), fbuf(w)
-    Il = _split(I)
-    Fp = S.FloatBuffer(2 * F.size())
+    Fp = S.FloatBuffer(F.size())
     S.prepare_filter_3xTF32(Fh, Fw, K, C, F, Fp)
     if mode == "plain":
         O = S.FloatBuffer(N * K * ho * wo)
-        S.Conv2D_3xTF32(Fh, Fw, 1, *pads, K, C, H, W, I, Il, Fp, None, O, batch=N)
+        S.Conv2D_3xTF32(Fh, Fw, 1, *pads, K, C, H, W, I, Fp, None, O, batch=N)
         want = oracle_conv_batch(oracle, sh, x, w)
     else:
         seed = rng.uniform(-1, 1, (N, K * ho * wo)).astype(np.float32)
         O = fbuf(seed)
-        S.Conv2D_3xTF32(Fh, Fw, 1, *pads, K, C, H, W, I, Il, Fp, fbuf(bias), O, partial=True,
+        S.Conv2D_3xTF32(Fh, Fw, 1, *pads, K, C, H, W, I, Fp, fbuf(bias), O, partial=True,
                         activation=S.ACT_LEAKY, negative_slope=0.1, batch=N)
         want = oracle_conv_batch(oracle, sh, x, w, bias=bias, act=2, slope=0.1, seed=seed)
     got = O.numpy().reshape(N, -1)
     assert _lib.device_status() == 0
     assert rel_max_err(got, want) <= TOL
-
-
-def test_split_is_exact():
-    rng = np.random.default_rng(0)
-    x = rng.normal(0, 3, 4096).astype(np.float32)
-    X = fbuf(x)
-    lo = _split(X).numpy()
-    hi = (x.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
-    assert np.array_equal(lo, x - hi)
-    assert np.array_equal(hi + lo, x)
 
 
 def test_unsupported_shapes_are_refused():
