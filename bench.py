@@ -336,6 +336,33 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def run_one_layer(args):
+    """Launches one layer of the workload alone (after running the chain once so that its input
+    holds real activations): the command ncu captures, one kernel class at a time."""
+    import torch
+
+    from smallframework_b200 import _lib, networks
+    wl = WORKLOADS[args.workload]
+    batch = args.batch or 8
+    layers = make_layers(args.workload)
+    chain = networks.Chain(layers, batch, wl["dtype"])
+    xp = make_input(args.workload, layers, batch, wl["seed"])
+    chain.x.copy_(torch.from_numpy(xp).reshape(-1))
+    chain.enqueue()
+    chain.stream.synchronize()
+    idx = [i for i, L in enumerate(layers) if L.get("name") == args.profile_layer]
+    if not idx:
+        raise SystemExit(f"no layer named {args.profile_layer!r}: " + ", ".join(L["name"] for L in layers))
+    i = idx[0]
+    src = chain.x if i == 0 else chain.bufs[(i - 1) & 1]
+    st = chain.stream.cuda_stream
+    for _ in range(args.steps):
+        chain.enqueue_layer(i, src, chain.bufs[i & 1], st)
+    chain.stream.synchronize()
+    print(json.dumps({"profile_layer": args.profile_layer, "batch": batch, "launches": args.steps,
+                      "device_status": _lib.device_status()}))
+
+
 def per_layer_report(chain, layers, batch, wl, clocks, torch):
     """Times every layer's launch alone with CUDA events on the launching stream (inputs of
     each layer at this batch are far larger than L2) and charges it against its roofline:
@@ -400,8 +427,12 @@ def main():
     ap.add_argument("--workload", default="tinyyolov2", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-layer", default="",
+                    help="run only this layer (by name) --steps times on a small batch: the ncu target")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_layer:
+        run_one_layer(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

@@ -119,11 +119,12 @@ int small_b200_conv2d_f32(const small_b200_layer *L, const float *in, const floa
                           const float *bias, float *out, void *stream);
 /* The same layer on the tensor cores (tcgen05 kind::tf32 with the 3xTF32 operand split, fp32
  * accumulation in tensor memory), stride 1 only.  Each fp32 operand x enters the tensor core as
- * hi = x (its 13 low mantissa bits are ignored) and lo = x - hi; the lo copies are made inside the
- * kernel, in shared memory.  The caller provides the filter re-laid for the tensor core:
+ * hi = x (its 13 low mantissa bits are ignored) and lo = x - hi; the lo copy of the activations
+ * is made inside the kernel, in shared memory.  The caller provides the filter re-laid for the
+ * tensor core:
  *   filt_prepared  small_b200_filter_prepare_tf32x3(filt), once per set of weights,
- *                  K*C*Fh*Fw floats: per CTA tile and tap the filter as [c/4][k][4 c]
- *                  (what the tensor core reads directly).
+ *                  2 * K*C*Fh*Fw floats: per CTA tile and tap the filter as [c/4][k][4 c]
+ *                  (what the tensor core reads directly) followed by its lo copy.
  * ..._supported() says whether a shape is covered (1) or not (0).  The reference has no
  * counterpart of the preparation call (its filters are used as packed). */
 int small_b200_conv2d_f32_tf32x3_supported(const small_b200_layer *L);
@@ -133,9 +134,9 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
 /* The tensor-core convolution above for callers that cannot allocate device memory (code
  * running where cudaMalloc is forbidden or would stall the device, plug-ins that are handed
  * nothing but their input and output pointers).  It takes the PACKED filter as the reference
- * lays it out and keeps its scratch -- the re-laid filter -- in a fixed 16 MiB array inside the
- * library, so it calls no allocator of any kind.  Limits and rules:
- *   - K*C*Fh*Fw floats must fit in 4 Mi floats; larger calls are
+ * lays it out and keeps its scratch -- the re-laid filter and its lo copy -- in a fixed 16 MiB
+ * array inside the library, so it calls no allocator of any kind.  Limits and rules:
+ *   - 2*K*C*Fh*Fw floats must fit in 4 Mi floats; larger calls are
  *     refused with SMALL_B200_INVALID_ARGUMENT and a message that states both sizes;
  *   - the first call on each device looks up the array's device address; make that first call
  *     outside any stream capture;

@@ -28,8 +28,9 @@
 //   experiment returned zeros, while the K-major form was exact), so the filter is re-laid once
 //   per set of weights into [K/MT][C/16][tap][c/4][MT k][4 c] (prepare_filter_kernel), MT =
 //   output channels per CTA.  One tap of one CTA is then a single contiguous run of MT*64 bytes
-//   that IS the K-major canonical layout and arrives by one bulk copy; the splitter warps add its
-//   lo copy.
+//   that IS the K-major canonical layout and arrives by one bulk copy; its lo copy is made by the
+//   same preparation step and loaded next to it (making it in shared memory like the patch's
+//   cost more shared-memory bandwidth than the tensor core could spare).
 #include "tc_common.cuh"
 
 namespace
@@ -61,10 +62,11 @@ struct TcArgs
 // convolution agree.
 __host__ __device__ inline int pick_mt(int K) { return K >= 128 ? 128 : 64; }
 
-// packed filter [K/16][slab][16 c][16 k] -> [K/MT][slab][c/4][kv k][4 c]; kv = MT except in a last,
-// partial tile (K % MT channels).  Same number of elements as the packed filter.
+// packed filter [K/16][slab][16 c][16 k] -> hi and lo copies in [K/MT][slab][c/4][kv k][4 c];
+// kv = MT except in a last, partial tile (K % MT channels).
 __global__ void __launch_bounds__(256)
-prepare_filter_kernel(long long n, int slabs, int MT, int K, const float *__restrict__ w, float *__restrict__ hi)
+prepare_filter_kernel(long long n, int slabs, int MT, int K, const float *__restrict__ w, float *__restrict__ hi,
+                      float *__restrict__ lo)
 {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n)
@@ -77,7 +79,9 @@ prepare_filter_kernel(long long n, int slabs, int MT, int K, const float *__rest
     const int kv = (K - tile * MT) < MT ? (K - tile * MT) : MT;
     const long long o = (long long)tile * MT * slabs * 16 + ((long long)slab * 4 + (c >> 2)) * kv * 4 +
                         (long long)(k - tile * MT) * 4 + (c & 3);
-    hi[o] = w[i];
+    const float v = w[i];
+    hi[o] = v;
+    lo[o] = v - __uint_as_float(__float_as_uint(v) & 0xffffe000u);
 }
 
 // Tensor-core accumulation truncates: every MMA adds into the fp32 accumulator with
@@ -118,12 +122,12 @@ __device__ __forceinline__ float4 lo_of(const float4 v)
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__restrict__ filt,
-                   const TcArgs a, const float *__restrict__ bias, float *__restrict__ out, int *status)
+                   const float *__restrict__ filt_lo, const TcArgs a, const float *__restrict__ bias, float *__restrict__ out, int *status)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t raw_full[RAW_SLOTS_MAX], raw_empty[RAW_SLOTS_MAX];
     __shared__ __align__(8) uint64_t x_ready[X_SLOTS_MAX], x_empty[X_SLOTS_MAX];
-    __shared__ __align__(8) uint64_t w_full[W_STAGES_MAX], w_ready[W_STAGES_MAX], g_done[W_STAGES_MAX];
+    __shared__ __align__(8) uint64_t w_full[W_STAGES_MAX], g_done[W_STAGES_MAX];
     __shared__ __align__(8) uint64_t t_empty[2];
     __shared__ uint32_t tmem_base_s;
 
@@ -161,7 +165,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             for (int i = 0; i < X_SLOTS_MAX; ++i) { mbar_init(&x_ready[i], SPLIT_THREADS); mbar_init(&x_empty[i], 1); }
             for (int i = 0; i < W_STAGES_MAX; ++i)
             {
-                mbar_init(&w_full[i], 1); mbar_init(&w_ready[i], SPLIT_THREADS); mbar_init(&g_done[i], 1);
+                mbar_init(&w_full[i], 1); mbar_init(&g_done[i], 1);
             }
             for (int i = 0; i < 2; ++i) mbar_init(&t_empty[i], ACC_WARPS);
             fence_barrier_init();
@@ -205,15 +209,22 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                 if (!ok)
                     break;
                 uint8_t *wd = sW + (size_t)st * 2 * w_half_stage;
-                const float *src = filt + tile_base + (size_t)g * a.group * kv * 16;
-                mbar_expect_tx(&w_full[st], (uint32_t)a.group * kv * 64);
+                const size_t off = tile_base + (size_t)g * a.group * kv * 16;
+                mbar_expect_tx(&w_full[st], 2u * a.group * kv * 64);
                 if (kv == a.MT)
-                    tma_load_1d(wd, src, w_half_stage, &w_full[st]); // the group's taps are contiguous
+                {
+                    tma_load_1d(wd, filt + off, w_half_stage, &w_full[st]); // the group's taps are contiguous
+                    tma_load_1d(wd + w_half_stage, filt_lo + off, w_half_stage, &w_full[st]);
+                }
                 else
                     for (int t = 0; t < a.group; ++t)
                         for (int j = 0; j < 4; ++j) // partial tile: kv of MT rows per 4-channel chunk
-                            tma_load_1d(wd + t * w_part + j * w_chunk, src + ((size_t)t * 4 + j) * kv * 4,
-                                        (uint32_t)kv * 16, &w_full[st]);
+                        {
+                            const size_t o = off + ((size_t)t * 4 + j) * kv * 4;
+                            tma_load_1d(wd + t * w_part + j * w_chunk, filt + o, (uint32_t)kv * 16, &w_full[st]);
+                            tma_load_1d(wd + w_half_stage + t * w_part + j * w_chunk, filt_lo + o, (uint32_t)kv * 16,
+                                        &w_full[st]);
+                        }
             }
         }
         else if (warp == 1 && lane == 0)
@@ -230,55 +241,57 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                               (uint32_t)a.MT, (uint32_t)a.NPX);
             const uint64_t x_lo_off = x_part >> 4, w_lo_off = w_half_stage >> 4, w_tap = w_part >> 4;
             const uint64_t x_half = (2 * x_chunk) >> 4, w_half = (2 * w_chunk) >> 4;
-            uint64_t x_slot = 0;
-            int slot = 0, kh = 0, kw = 0;
-            for (int g = 0; g < groups && ok; ++g)
+            // The tensor pipe's queue holds only a handful of MMAs, so whatever this thread does
+            // between two groups beyond issuing (waits, commits, index arithmetic) shows up as
+            // idle tensor cycles: the loop keeps its counters incrementally, no divisions.
+            const uint64_t w_stage_step = (uint64_t)2 * w_half_stage >> 4;
+            const uint64_t x_slot_step = (uint64_t)2 * x_part >> 4;
+            int slot = 0, xphase = 0, st = 0, wphase = 0, g = 0;
+            uint64_t x_slot = x_desc0, w_stage = w_desc0;
+            for (int cb = 0; cb < a.cbs && ok; ++cb)
             {
-                if (g % groups_per_cb == 0)
-                {
-                    const int cb = g / groups_per_cb;
-                    slot = cb % a.x_slots;
-                    ok = mbar_wait(&x_ready[slot], (cb / a.x_slots) & 1, status, 13);
-                    if (!ok)
-                        break;
-                    x_slot = x_desc0 + ((uint64_t)slot * 2 * x_part >> 4);
-                    kh = 0; kw = 0;
-                }
-                const int st = g % a.w_stages, tb = g & 1; // filter stage / tensor-memory buffer
-                ok = mbar_wait(&w_ready[st], (g / a.w_stages) & 1, status, 14);
-                if (ok && g >= 2)
-                    ok = mbar_wait(&t_empty[tb], ((g >> 1) - 1) & 1, status, 16);
+                ok = mbar_wait(&x_ready[slot], xphase, status, 13);
                 if (!ok)
                     break;
-                tc_fence_after_sync();
-                const uint32_t d = tmem + (uint32_t)(tb * a.NPX);
-                uint64_t wh = w_desc0 + ((uint64_t)st * 2 * w_half_stage >> 4);
-                for (int t = 0; t < a.group; ++t, wh += w_tap)
+                uint64_t x_row = x_slot; // patch position of tap (kh, 0)
+                for (int gi = 0; gi < groups_per_cb && ok; ++gi, ++g)
                 {
-                    const uint64_t xh = x_slot + (uint64_t)(kh * a.PW + kw), xl = xh + x_lo_off;
-                    const uint64_t wl = wh + w_lo_off;
-                    tc_mma_tf32(d, wl, xh, idesc, t == 0 ? 0u : 1u);
-                    tc_mma_tf32(d, wh, xl, idesc, 1u);
-                    tc_mma_tf32(d, wh, xh, idesc, 1u);
-                    tc_mma_tf32(d, wl + w_half, xh + x_half, idesc, 1u);
-                    tc_mma_tf32(d, wh + w_half, xl + x_half, idesc, 1u);
-                    tc_mma_tf32(d, wh + w_half, xh + x_half, idesc, 1u);
-                    if (++kw == a.Fw) { kw = 0; ++kh; }
+                    const int tb = g & 1; // tensor-memory buffer of this group
+                    ok = mbar_wait(&w_full[st], wphase, status, 14);
+                    if (ok && g >= 2)
+                        ok = mbar_wait(&t_empty[tb], ((g >> 1) - 1) & 1, status, 16);
+                    if (!ok)
+                        break;
+                    tc_fence_after_sync();
+                    const uint32_t d = tmem + (uint32_t)(tb * a.NPX);
+                    uint64_t wh = w_stage, xh = x_row;
+                    for (int t = 0; t < a.group; ++t, wh += w_tap, ++xh)
+                    {
+                        const uint64_t xl = xh + x_lo_off, wl = wh + w_lo_off;
+                        tc_mma_tf32(d, wl, xh, idesc, t == 0 ? 0u : 1u);
+                        tc_mma_tf32(d, wh, xl, idesc, 1u);
+                        tc_mma_tf32(d, wh, xh, idesc, 1u);
+                        tc_mma_tf32(d, wl + w_half, xh + x_half, idesc, 1u);
+                        tc_mma_tf32(d, wh + w_half, xl + x_half, idesc, 1u);
+                        tc_mma_tf32(d, wh + w_half, xh + x_half, idesc, 1u);
+                    }
+                    // one commit: the stage is free for the producer and the group's partial
+                    // sums are complete for the accumulation warps
+                    tc_commit(&g_done[st]);
+                    x_row += (uint64_t)(a.group == a.Fw ? a.PW : 1);
+                    w_stage += w_stage_step;
+                    if (++st == a.w_stages) { st = 0; wphase ^= 1; w_stage = w_desc0; }
                 }
-                // one commit: the stage is free for the producer and the group's partial sums
-                // are complete for the accumulation warps
-                tc_commit(&g_done[st]);
-                if ((g + 1) % groups_per_cb == 0)
-                    tc_commit(&x_empty[slot]);
+                tc_commit(&x_empty[slot]);
+                x_slot += x_slot_step;
+                if (++slot == a.x_slots) { slot = 0; xphase ^= 1; x_slot = x_desc0; }
             }
         }
         else if (warp >= FIRST_SPLIT_WARP)
         {
             // ---------------- operand splitters ----------------
-            // in the order the MMA issuer consumes: the patch of a channel block, then its taps
             const int sid = tid - FIRST_SPLIT_WARP * 32;
             bool ok = true;
-            int ws = 0;
             for (int cb = 0; cb < a.cbs && ok; ++cb)
             {
                 const int rs = cb % a.raw_slots, slot = cb % a.x_slots, xuse = cb / a.x_slots;
@@ -305,18 +318,6 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                 fence_proxy_async();
                 mbar_arrive(&x_ready[slot]);
                 mbar_arrive(&raw_empty[rs]);
-                for (int gi = 0; gi < groups_per_cb && ok; ++gi, ++ws)
-                {
-                    const int st = ws % a.w_stages;
-                    ok = mbar_wait(&w_full[st], (ws / a.w_stages) & 1, status, 18);
-                    if (!ok)
-                        break;
-                    uint8_t *wh = sW + (size_t)st * 2 * w_half_stage;
-                    for (uint32_t o = (uint32_t)sid * 16u; o < w_half_stage; o += SPLIT_THREADS * 16u)
-                        *reinterpret_cast<float4 *>(wh + w_half_stage + o) = lo_of(*reinterpret_cast<const float4 *>(wh + o));
-                    fence_proxy_async();
-                    mbar_arrive(&w_ready[st]);
-                }
             }
         }
     }
@@ -467,7 +468,7 @@ int small_b200_filter_prepare_tf32x3(const small_b200_layer *L, const float *fil
         return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: shape not covered by the tensor-core path.");
     const long long n = (long long)L->K * L->C * L->Fh * L->Fw;
     prepare_filter_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(
-        n, (L->C / CB) * L->Fh * L->Fw, pick_mt(L->K), L->K, filt, prepared);
+        n, (L->C / CB) * L->Fh * L->Fw, pick_mt(L->K), L->K, filt, prepared, prepared + n);
     return launched("prepare_filter_kernel");
 }
 
@@ -501,7 +502,8 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     if (!status)
         return fail(SMALL_B200_CUDA_ERROR, "device status word not available");
     const long long blocks = (long long)a.N * a.px_tiles * a.k_tiles;
-    conv_tf32x3_kernel<<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(mx, filt_prepared, a, bias, out, status);
+    conv_tf32x3_kernel<<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
+        mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.taps, a, bias, out, status);
     return launched("conv_tf32x3_kernel");
 }
 } // extern "C"
@@ -510,7 +512,7 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
 // The same tensor-core convolution for callers that must not allocate device memory.
 //
 // small_b200_conv2d_f32_tf32x3 needs scratch from its caller: the filter re-laid for the tensor
-// core.  Some callers cannot provide it: code that runs inside
+// core, with its lo copy.  Some callers cannot provide it: code that runs inside
 // a region where cudaMalloc is forbidden or would synchronise the device (a real-time loop, a
 // plug-in that only ever receives its input and output pointers, a host that has handed all of
 // its device memory to another allocator).  For them the scratch lives in this fixed array
@@ -551,11 +553,11 @@ extern "C" int small_b200_conv2d_f32_tf32x3_noalloc(const small_b200_layer *L, c
         return fail(SMALL_B200_INVALID_ARGUMENT,
                     "Conv2D<float> (3xTF32, no-alloc) ERROR: shape not covered by the tensor-core path.");
     const size_t filt_elems = (size_t)L->K * L->C * L->Fh * L->Fw;
-    const size_t need = filt_elems; // the re-laid filter
+    const size_t need = 2 * filt_elems; // the re-laid filter and its lo copy
     if (need > STATIC_SCRATCH_FLOATS)
         return fail(SMALL_B200_INVALID_ARGUMENT,
                     "Conv2D<float> (3xTF32, no-alloc) ERROR: this call needs " + std::to_string(need * 4) +
-                        " bytes of scratch (K*C*Fh*Fw filter elements, 4 bytes each) but the "
+                        " bytes of scratch (2 x K*C*Fh*Fw filter elements, 4 bytes each) but the "
                         "built-in scratch holds " + std::to_string(STATIC_SCRATCH_FLOATS * 4) +
                         " bytes; use small_b200_conv2d_f32_tf32x3 with caller-provided scratch.");
     float *scratch = nullptr;

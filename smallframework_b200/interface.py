@@ -362,7 +362,7 @@ def tf32x3_supported(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r
 
 def prepare_filter_3xTF32(kernel_height, kernel_width, output_channels, input_channels,
                           filter_buf, prepared_buf, *, stream=None):
-    """Re-lay a packed filter for the tensor-core path (same number of elements)."""
+    """Re-lay a packed filter for the tensor-core path (hi copy + lo copy, 2x the elements)."""
     L = _layer(1, input_channels, output_channels, 16, 16, kernel_height, kernel_width, 1, 0, 0, 0, 0)
     check(lib().small_b200_filter_prepare_tf32x3(C.byref(L), _ptr(filter_buf), _ptr(prepared_buf),
                                                  _stream(stream)))

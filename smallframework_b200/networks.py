@@ -214,7 +214,7 @@ class Chain:
                 bs = torch.from_numpy(bp).to(self.dev)
             self.params.append((wt, bs))
         self.bufs = [torch.zeros(max_act, dtype=self.tdtype, device=self.dev) for _ in range(2)]
-        # tensor-core fp32 path: filters re-laid once
+        # tensor-core fp32 path: filters re-laid once (hi + lo copies)
         self.prepared = [None] * len(layers)
         if dtype == "f32" and tensor_core:
             for i, L in enumerate(layers):
@@ -226,7 +226,7 @@ class Chain:
                 if not lib().small_b200_conv2d_f32_tf32x3_supported(C.byref(d)):
                     continue
                 wt = self.params[i][0]
-                prep = torch.empty(wt.numel(), dtype=torch.float32, device=self.dev)
+                prep = torch.empty(2 * wt.numel(), dtype=torch.float32, device=self.dev)
                 check(lib().small_b200_filter_prepare_tf32x3(C.byref(d), wt.data_ptr(), prep.data_ptr(),
                                                              torch.cuda.current_stream().cuda_stream))
                 self.prepared[i] = prep

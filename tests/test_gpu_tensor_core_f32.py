@@ -44,7 +44,7 @@ def test_conv2d_3xtf32(oracle, case, mode):
     sh = shape(C, K, H, W, Fh, Fw, 1, pads, CB)
     ho, wo = sh.out_hw()
     I, F = fbuf(x), fbuf(w)
-    Fp = S.FloatBuffer(F.size())
+    Fp = S.FloatBuffer(2 * F.size())
     S.prepare_filter_3xTF32(Fh, Fw, K, C, F, Fp)
     if mode == "plain":
         O = S.FloatBuffer(N * K * ho * wo)

@@ -43,7 +43,7 @@ def _run_both(rng, N, Cn, K, H, W, Fh, Fw, with_bias):
     got = S.FloatBuffer(data=np.full(n_out, np.nan, np.float32))
     _lib.check(_lib.lib().small_b200_conv2d_f32_tf32x3_noalloc(C.byref(L), I.ptr(), F.ptr(), bp, got.ptr(), st))
 
-    prep = S.FloatBuffer(F.size())
+    prep = S.FloatBuffer(2 * F.size())
     want = S.FloatBuffer(data=np.full(n_out, np.nan, np.float32))
     S.prepare_filter_3xTF32(Fh, Fw, K, Cn, F, prep)
     _lib.check(_lib.lib().small_b200_conv2d_f32_tf32x3(C.byref(L), I.ptr(), prep.ptr(), bp, want.ptr(), st))
@@ -64,7 +64,7 @@ def test_no_alloc_matches_the_ordinary_entry_point_twice_in_a_row():
 
 
 def test_no_alloc_refuses_what_does_not_fit():
-    # 1024 x 1024 x 3 x 3 filter floats exceed the 4 Mi floats of built-in scratch
+    # two copies of 1024 x 1024 x 3 x 3 filter floats exceed the 4 Mi floats of built-in scratch
     L = _layer(64, 1024, 1024, 13, 13, 3, 3, (1, 1, 1, 1))
     rc = _lib.lib().small_b200_conv2d_f32_tf32x3_noalloc(C.byref(L), None, None, None, None, None)
     assert rc == _lib.INVALID_ARGUMENT
