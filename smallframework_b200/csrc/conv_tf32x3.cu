@@ -364,29 +364,66 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         // 16q + l in lanes 0..15 of each quarter
         const int k_local = (a.MT == 128) ? quarter * 32 + lane : quarter * 16 + lane;
         const bool lane_has_row = (a.MT == 128) || (lane < 16);
-        if (ok && lane_has_row && k_local < kv)
+        // Epilogue through shared memory (every operand buffer is dead once the last group has
+        // been flushed): a thread owns one channel of up to 128 pixels, the packed output wants
+        // 16 channels of one pixel together.  Rows of MT + 16 floats keep both the
+        // channel-wise writes and the float4 reads free of bank conflicts.
+        const int pitch = a.MT + 16;
+        float *stage = reinterpret_cast<float *>(smem);
+        if (ok && lane_has_row)
         {
-            const int k = kt * a.MT + k_local;
-            const float bv = bias ? bias[k] : 0.f;
-            float *oplane = out + ((size_t)n * (a.K / CB) + k / CB) * a.Ho * a.Wo * CB + (k % CB);
-            int m = m0 + col0;
-            int r = m / a.PW, c = m - r * a.PW;
-#pragma unroll
-            for (int e = 0; e < COLS_PER_THREAD; ++e)
+            float *srow = stage + (size_t)col0 * pitch + k_local;
+            if (a.MT == 128)
             {
-                if (e < my_cols)
+#pragma unroll
+                for (int e = 0; e < COLS_PER_THREAD; ++e)
+                    if (e < my_cols)
+                        srow[e * 144] = acc[e];
+            }
+            else
+            {
+#pragma unroll
+                for (int e = 0; e < COLS_PER_THREAD; ++e)
+                    if (e < my_cols)
+                        srow[e * 80] = acc[e];
+            }
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory"); // the eight accumulation warps
+        if (ok)
+        {
+            const int kbs = kv / CB;                   // channel blocks this tile really has
+            const int psub = lane >> 2, q4 = lane & 3; // 8 pixels x 4 float4 per warp and step
+            const size_t plane = (size_t)a.Ho * a.Wo * CB;
+            float *obase = out + ((size_t)n * (a.K / CB) + (size_t)kt * (a.MT / CB)) * plane + q4 * 4;
+            const float *bbase = bias ? bias + kt * a.MT + q4 * 4 : nullptr;
+            for (int pg = warp - FIRST_ACC_WARP; pg < a.NPX / 8; pg += ACC_WARPS)
+            {
+                const int px = pg * 8 + psub;
+                const int m = m0 + px;
+                const int r = m / a.PW, c = m - r * a.PW;
+                if (r < a.Ho && c < a.Wo)
                 {
-                    if (r < a.Ho && c < a.Wo)
+                    const float *sp = stage + (size_t)px * pitch + q4 * 4;
+                    float *o = obase + ((size_t)r * a.Wo + c) * CB;
+#pragma unroll 4
+                    for (int kb = 0; kb < kbs; ++kb)
                     {
-                        float *o = oplane + ((size_t)r * a.Wo + c) * CB;
-                        float x = acc[e];
+                        float4 x = *reinterpret_cast<const float4 *>(sp + kb * CB);
+                        float *ok_ = o + (size_t)kb * plane;
                         if (a.accumulate)
-                            x += *o;
-                        if (bias)
-                            x += bv;
-                        *o = apply_act(x, a.act, a.slope);
+                        {
+                            const float4 s4 = *reinterpret_cast<const float4 *>(ok_);
+                            x.x += s4.x; x.y += s4.y; x.z += s4.z; x.w += s4.w;
+                        }
+                        if (bbase)
+                        {
+                            const float4 b = *reinterpret_cast<const float4 *>(bbase + kb * CB);
+                            x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+                        }
+                        x.x = apply_act(x.x, a.act, a.slope); x.y = apply_act(x.y, a.act, a.slope);
+                        x.z = apply_act(x.z, a.act, a.slope); x.w = apply_act(x.w, a.act, a.slope);
+                        *reinterpret_cast<float4 *>(ok_) = x;
                     }
-                    if (++c == a.PW) { c = 0; ++r; }
                 }
             }
         }
@@ -442,7 +479,10 @@ bool plan(const small_b200_layer *L, TcArgs &a)
         for (const auto &p : pref)
         {
             const int xs = p[0] < a.cbs ? p[0] : a.cbs, rs = p[2] < a.cbs ? p[2] : a.cbs;
-            const size_t smem = (size_t)rs * raw_part + (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
+            size_t smem = (size_t)rs * raw_part + (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
+            const size_t epilogue = (size_t)npx * (a.MT + 16) * 4; // output staging reuses the buffers
+            if (smem < epilogue)
+                smem = epilogue;
             if (smem <= limit)
             {
                 a.x_slots = xs; a.w_stages = p[1]; a.raw_slots = rs; a.smem_bytes = (unsigned)smem;
