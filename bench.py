@@ -75,7 +75,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -296,9 +296,9 @@ def run_gpu_arm(args):
     n_before = _lib.launch_count()
     with ClockSampler(local) as clk:
         ms = timed(step_resident, args.steps)
-    for _ in range(2):
-        step_e2e()
-    ms_e2e = timed(step_e2e, args.steps)
+        for _ in range(2):
+            step_e2e()
+        ms_e2e = timed(step_e2e, args.steps)
     total_images = batch * world * args.steps
     value = total_images / (ms * 1e-3)
     e2e_value = total_images / (ms_e2e * 1e-3)
@@ -354,30 +354,60 @@ def run_one_layer(args):
     if not idx:
         raise SystemExit(f"no layer named {args.profile_layer!r}: " + ", ".join(L["name"] for L in layers))
     i = idx[0]
-    src = chain.x if i == 0 else chain.bufs[(i - 1) & 1]
+    io = chain.io_plan()[i]
+    if io is None:
+        raise SystemExit(f"{args.profile_layer} runs inside its producer's kernel: profile that layer")
     st = chain.stream.cuda_stream
     for _ in range(args.steps):
-        chain.enqueue_layer(i, src, chain.bufs[i & 1], st)
+        chain.enqueue_layer(i, io[0], io[1], st)
     chain.stream.synchronize()
     print(json.dumps({"profile_layer": args.profile_layer, "batch": batch, "launches": args.steps,
                       "device_status": _lib.device_status()}))
 
 
+# DRAM traffic of the dominant kernel's launch at the bench size, from a one-pass ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum); the profile summary that holds it is named.
+MEASURED_TRAFFIC = {
+}
+
+
+def kernel_class(chain, i, L, dtype):
+    """Which kernel runs layer i and what bounds it."""
+    if L["op"] == "conv":
+        if dtype == "f32":
+            if chain.prepared[i] is not None:
+                return "conv_tf32x3_kernel (tcgen05 kind::tf32, 3xTF32)", "tf32x3"
+            return ("conv2d_first_f32_kernel (FFMA)" if L["C"] < 16 else "conv2d_f32_kernel (FFMA)"), "ffma"
+        pw = (L["Fh"] == 1 and L["Fw"] == 1 and L["stride"] == 1 and L["C"] % 32 == 0 and L["C"] <= 256)
+        return ("pw_u8_tc_kernel (tcgen05 kind::i8)", "i8") if pw else ("conv2d_u8_direct_kernel", "cuda_u8")
+    return {"dwconv": "depthwise", "maxpool": "max pool", "avgpool": "average pool"}[L["op"]], "stream"
+
+
 def per_layer_report(chain, layers, batch, wl, clocks, torch):
     """Times every layer's launch alone with CUDA events on the launching stream (inputs of
     each layer at this batch are far larger than L2) and charges it against its roofline:
-    t_roof = max(flops / pipe peak, bytes / HBM peak)."""
+    t_roof = max(flops / pipe peak, bytes / HBM peak).  Pipe peaks: the fp32 FMA pipe at the
+    sampled clock for CUDA-core convolutions; for the 3xTF32 tensor-core convolution one sixth of
+    the measured bf16 rate (tf32 runs at half the bf16 rate and every product takes three
+    MMAs); for uint8 tensor-core layers twice the measured bf16 rate."""
     from smallframework_b200 import networks
     peaks = load_peaks()
     sm_mhz = clocks.get("sm_mhz") or 1700.0
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     ffma_tflops = sms * 128 * 2 * sm_mhz * 1e6 / 1e12   # fp32 FMA pipe at the observed clock
+    pipes = {"ffma": ffma_tflops, "tf32x3": peaks["tensor"] / 6.0, "i8": peaks["tensor"] * 2.0,
+             "cuda_u8": ffma_tflops, "stream": ffma_tflops}
     elt = chain.elt
     st = chain.stream.cuda_stream
     reps = 5
-    rows, src = [], chain.x
+    rows = []
+    plan = chain.io_plan()
     for i, L in enumerate(layers):
-        dst = chain.bufs[i & 1]
+        if plan[i] is None:
+            rows.append({"layer": L.get("name", L["op"]), "kernel": "fused into " + layers[chain.fused_into[i]]["name"],
+                         "ms": 0.0, "tflops": 0.0, "gbs": 0.0, "bound": "fused", "roofline_frac": None})
+            continue
+        src, dst = plan[i]
         for _ in range(2):
             chain.enqueue_layer(i, src, dst, st)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -388,33 +418,44 @@ def per_layer_report(chain, layers, batch, wl, clocks, torch):
         chain.stream.synchronize()
         ms = e0.elapsed_time(e1) / reps
         flops, abytes, wbytes = networks.algorithmic_work(L, elt)
+        if (i + 1) in chain.fused_into:
+            # the producer stores the pooled tensor only: its input + the pool's output
+            pf, pb, _ = networks.algorithmic_work(layers[i + 1], elt)
+            abytes = L["C"] * L["H"] * L["W"] * elt + (pb - layers[i + 1]["C"] * layers[i + 1]["H"] * layers[i + 1]["W"] * elt)
+            flops += pf
         flops *= batch
         nbytes = abytes * batch + wbytes
-        pipe = ffma_tflops if wl["dtype"] == "f32" else ffma_tflops  # CUDA-core path for both today
-        t_flop = flops / (pipe * 1e12)
+        kname, kcls = kernel_class(chain, i, L, wl["dtype"])
+        if (i + 1) in chain.fused_into:
+            kname += " + 2x2 max pool"
+        t_flop = flops / (pipes[kcls] * 1e12)
         t_mem = nbytes / (peaks["hbm"] * 1e9)
-        rows.append({"layer": L.get("name", L["op"]), "ms": round(ms, 4),
+        rows.append({"layer": L.get("name", L["op"]), "kernel": kname, "ms": round(ms, 4),
                      "tflops": round(flops / (ms * 1e-3) / 1e12, 3),
                      "gbs": round(nbytes / (ms * 1e-3) / 1e9, 1),
-                     "bound": "pipe" if t_flop > t_mem else "hbm",
+                     "bound": ("tensor" if kcls in ("tf32x3", "i8") else "fp32 pipe") if t_flop > t_mem else "hbm",
                      "roofline_frac": round(max(t_flop, t_mem) / (ms * 1e-3), 4)})
-        src = dst
     top = max(range(len(rows)), key=lambda i: rows[i]["ms"])
     L = layers[top]
     flops, abytes, wbytes = networks.algorithmic_work(L, elt)
-    if L["op"] == "conv":
+    kname, kcls = kernel_class(chain, top, L, wl["dtype"])
+    traffic = MEASURED_TRAFFIC.get((rows[top]["layer"], batch))
+    if rows[top]["bound"] != "hbm":
         achieved = flops * batch / (rows[top]["ms"] * 1e-3) / 1e12
         roof = {"bound": "tensor", "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s",
-                "frac": achieved / peaks["tensor"], "traffic": None,
-                "kernel": rows[top]["layer"], "peak_source": f"bf16 sustained, of {peaks['source']}",
-                "pipe": {"name": "fp32 FFMA (CUDA cores)", "peak": ffma_tflops,
-                         "frac": achieved / ffma_tflops,
-                         "note": "SMs x 128 lanes x 2 x SM clock sampled under load"}}
+                "frac": achieved / peaks["tensor"], "traffic": traffic,
+                "kernel": kname, "layer": rows[top]["layer"],
+                "peak_source": f"dense bf16 GEMM, sustained, of {peaks['source']}",
+                "pipe": {"peak": pipes[kcls], "frac": achieved / pipes[kcls],
+                         "note": {"tf32x3": "fp32 result from three tf32 MMAs per product and tf32 at half the "
+                                            "bf16 rate: one sixth of the bf16 peak is what this kernel can reach",
+                                  "ffma": "SMs x 128 lanes x 2 x SM clock sampled under load",
+                                  "i8": "twice the bf16 rate"}.get(kcls, "")}}
     else:
         achieved = (abytes * batch + wbytes) / (rows[top]["ms"] * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm"], "traffic": None, "kernel": rows[top]["layer"],
-                "peak_source": f"copy bandwidth, of {peaks['source']}"}
+                "frac": achieved / peaks["hbm"], "traffic": traffic, "kernel": kname,
+                "layer": rows[top]["layer"], "peak_source": f"copy bandwidth, of {peaks['source']}"}
     return {"roofline": roof, "layers": rows}
 
 

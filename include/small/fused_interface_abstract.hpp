@@ -4,8 +4,10 @@
 // One-op forms (conv / depthwise conv with bias before and ReLU after) run as ONE kernel:
 // bias seeds the accumulators and the activation is applied in the output tile, which is
 // what the reference's fused loop nest does (abstract_layer.hpp:2268-2969).
-// Two-op forms (conv -> max pool, conv -> depthwise conv) run the fused first op into a
-// device scratch buffer owned by this header and the second op from there.  The reference's
+// conv -> 2x2 stride-2 max pool is one kernel too where the shapes allow (the pool is taken in
+// registers before anything is stored).  The other two-op forms (other pools, conv -> depthwise
+// conv) run the fused first op into a device scratch buffer owned by this header and the second
+// op from there.  The reference's
 // `inter_output_buf` argument is per-thread scratch of its CPU loop nest
 // (abstract_layer.hpp:3382,3409) with no defined content on return; it is left untouched.
 #pragma once
@@ -84,10 +86,24 @@ template <class BufferT>
 inline void conv_then_pool(int act, BufferT const *bias, SMALL_B200_CONV_ARGS, SMALL_B200_POOL_ARGS,
                            int K, int C, int H, int W, BufferT const &in, BufferT const &filt, BufferT &out)
 {
-    FloatBuffer &mid = fused_scratch(conv_out_elems(K, H, W, SMALL_B200_CONV_PASS));
-    conv(false, act, SMALL_B200_CONV_PASS, K, C, H, W, in, filt, bias, mid);
     const int Hm = small::output_dim(H + conv_t_pad + conv_b_pad, conv_stride, conv_kernel_height);
     const int Wm = small::output_dim(W + conv_l_pad + conv_r_pad, conv_stride, conv_kernel_width);
+    if constexpr (!is_quint8<BufferT>)
+    {
+        // one kernel when the pair of shapes is covered: the pool is taken in registers
+        small_b200_layer Lc = describe(C, K, H, W, conv_kernel_height, conv_kernel_width, conv_stride,
+                                       conv_t_pad, conv_b_pad, conv_l_pad, conv_r_pad, 0, act);
+        small_b200_layer Lp = describe(K, K, Hm, Wm, pool_kernel_height, pool_kernel_width, pool_stride,
+                                       pool_t_pad, pool_b_pad, pool_l_pad, pool_r_pad);
+        if (small_b200_conv2d_maxpool_f32_supported(&Lc, &Lp))
+        {
+            throw_on(small_b200_conv2d_maxpool_f32(&Lc, &Lp, in.device_ptr(), filt.device_ptr(),
+                                                   bias ? bias->device_ptr() : nullptr, out.device_ptr(), nullptr));
+            return;
+        }
+    }
+    FloatBuffer &mid = fused_scratch(conv_out_elems(K, H, W, SMALL_B200_CONV_PASS));
+    conv(false, act, SMALL_B200_CONV_PASS, K, C, H, W, in, filt, bias, mid);
     pool(false, SMALL_B200_POOL_PASS, K, Hm, Wm, mid, out);
 }
 

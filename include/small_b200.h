@@ -117,6 +117,15 @@ int small_b200_graph_destroy(void *graph_exec);
  * C % 16 == 0 or C in {1,2,3}; stride in {1,2}. */
 int small_b200_conv2d_f32(const small_b200_layer *L, const float *in, const float *filt,
                           const float *bias, float *out, void *stream);
+/* small::Conv2D_Maxpool2D / Conv2D_ReLU_Maxpool2D / Conv2D_Bias_ReLU_Maxpool2D<FloatBuffer>
+ * (fused_interface_abstract.hpp:463-1418): the convolution `conv` (stride 1, bias / activation
+ * slots as above) followed by the 2x2 stride-2 unpadded max pool `pool` in ONE kernel; the
+ * full-size activation never reaches memory.  `out` holds the pooled tensor
+ * [N][K/16][Ho/2][Wo/2][16].  ..._supported() says whether the pair of shapes is covered (even
+ * Ho and Wo, K % 32 == 0 unless it is a first layer with C in {1,2,3}, pool 2x2/2 without padding); other pairs run as two calls. */
+int small_b200_conv2d_maxpool_f32_supported(const small_b200_layer *conv, const small_b200_layer *pool);
+int small_b200_conv2d_maxpool_f32(const small_b200_layer *conv, const small_b200_layer *pool, const float *in,
+                                  const float *filt, const float *bias, float *out, void *stream);
 /* The same layer on the tensor cores (tcgen05 kind::tf32 with the 3xTF32 operand split, fp32
  * accumulation in tensor memory), stride 1 only.  Each fp32 operand x enters the tensor core as
  * hi = x (its 13 low mantissa bits are ignored) and lo = x - hi; the lo copy of the activations

@@ -28,6 +28,7 @@ struct ConvArgs
     int tiles_h, tiles_w, kblocks; // kblocks = K / BN
     int accumulate, act;
     float slope;
+    int pool; // 1 = a 2x2 stride-2 max pool follows inside the kernel (output is Ho/2 x Wo/2)
 };
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem, bool valid)
@@ -43,7 +44,11 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // BN: output channels per CTA; CH: output channels per thread (two groups of CH/2... for
 // CH = 8 the thread owns channels [4g,4g+4) and [BN/2+4g, BN/2+4g+4) so that a quarter
 // warp reads 128 contiguous bytes of the filter slice; for CH = 4 just [4g,4g+4)).
-template <int BN, int CH, int STRIDE>
+//
+// POOL: the 2x2 stride-2 max pool that follows the convolution (fused_interface_abstract.hpp:463,
+// Conv2D_Bias_ReLU_Maxpool2D) is taken in registers: a thread's 8 pixels hold four horizontal
+// pairs, and the two rows of a pair of rows sit 16 lanes apart in the same warp.
+template <int BN, int CH, int STRIDE, bool POOL>
 __global__ void __launch_bounds__(16 * BN / CH)
 conv2d_f32_kernel(const ConvArgs a, const float *__restrict__ in, const float *__restrict__ filt,
                   const float *__restrict__ bias, float *__restrict__ out)
@@ -204,6 +209,35 @@ conv2d_f32_kernel(const ConvArgs a, const float *__restrict__ in, const float *_
         __syncthreads();
     }
 
+    if (POOL)
+    {
+        // bias and activation are already in; rows r and r^1 live in lanes l and l^(2*CG)
+        static_assert(!POOL || CG == 8, "the pooled epilogue pairs rows 16 lanes apart");
+        const int Hp = a.Ho / 2, Wp = a.Wo / 2;
+#pragma unroll
+        for (int half = 0; half < CH / 4; ++half)
+        {
+            const int kg = kb * BN + (half ? ko1 : ko0);
+            float *obase = out + (((size_t)n * (a.K / CB) + kg / CB) * Hp * Wp + (size_t)(oh >> 1) * Wp) * CB + (kg % CB);
+#pragma unroll
+            for (int j = 0; j < PXT; j += 2)
+            {
+                float v[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                {
+                    const float x0 = apply_act(acc[j][half * 4 + q], a.act, a.slope);
+                    const float x1 = apply_act(acc[j + 1][half * 4 + q], a.act, a.slope);
+                    const float m = fmaxf(x0, x1);
+                    v[q] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2 * CG));
+                }
+                const int pw = (ow0 + c0 + j) >> 1;
+                if ((r & 1) == 0 && row_ok && pw < Wp)
+                    *reinterpret_cast<float4 *>(obase + (size_t)pw * CB) = make_float4(v[0], v[1], v[2], v[3]);
+            }
+        }
+        return;
+    }
     if (!row_ok)
         return;
 #pragma unroll
@@ -291,11 +325,178 @@ conv2d_first_f32_kernel(const ConvArgs a, const float *__restrict__ in, const fl
     }
 }
 
-template <int BN, int CH, int STRIDE>
+// First layer followed by a 2x2 stride-2 max pool: one thread per POOLED pixel and 16-channel
+// block computes the four convolution outputs under it (64 accumulators), so the full-size
+// activation never reaches memory.  Stride-1 convolution, even Ho and Wo.
+__global__ void __launch_bounds__(128)
+conv2d_first_pool_f32_kernel(const ConvArgs a, const float *__restrict__ in, const float *__restrict__ filt,
+                             const float *__restrict__ bias, float *__restrict__ out)
+{
+    extern __shared__ __align__(16) float w[]; // [taps][C][16]
+    const int taps = a.Fh * a.Fw;
+    const int kb = blockIdx.y;
+    const int n = blockIdx.z;
+    const int wn = taps * a.C * CB;
+    const float *fsrc = filt + (size_t)kb * wn;
+    for (int i = threadIdx.x; i < wn; i += blockDim.x)
+        w[i] = fsrc[i];
+    __syncthreads();
+    const int Hp = a.Ho / 2, Wp = a.Wo / 2;
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= Hp * Wp)
+        return;
+    const int ph = p / Wp, pw = p - ph * Wp;
+    float acc[4][CB];
+#pragma unroll
+    for (int k = 0; k < CB; ++k)
+    {
+        const float s = bias ? bias[kb * CB + k] : 0.f;
+        acc[0][k] = s; acc[1][k] = s; acc[2][k] = s; acc[3][k] = s;
+    }
+    const float *img = in + (size_t)n * a.C * a.H * a.W;
+    const int ih0 = 2 * ph - a.pad_t, iw0 = 2 * pw - a.pad_l;
+    // input rows ih0 .. ih0+Fh and columns iw0 .. iw0+Fw feed the 2x2 outputs
+    for (int dr = 0; dr <= a.Fh; ++dr)
+    {
+        const int ih = ih0 + dr;
+        if (ih < 0 || ih >= a.H)
+            continue;
+        for (int dc = 0; dc <= a.Fw; ++dc)
+        {
+            const int iw = iw0 + dc;
+            if (iw < 0 || iw >= a.W)
+                continue;
+            const float *px = img + ((size_t)ih * a.W + iw) * a.C;
+            for (int c = 0; c < a.C; ++c)
+            {
+                const float x = __ldg(px + c);
+                // output (oy, ox) of the 2x2 block sees this pixel through tap (dr-oy, dc-ox)
+#pragma unroll
+                for (int oy = 0; oy < 2; ++oy)
+                {
+                    const int kh = dr - oy;
+                    if (kh < 0 || kh >= a.Fh)
+                        continue;
+#pragma unroll
+                    for (int ox = 0; ox < 2; ++ox)
+                    {
+                        const int kw = dc - ox;
+                        if (kw < 0 || kw >= a.Fw)
+                            continue;
+                        const float4 *wt = reinterpret_cast<const float4 *>(w + ((kh * a.Fw + kw) * a.C + c) * CB);
+#pragma unroll
+                        for (int k4 = 0; k4 < 4; ++k4)
+                        {
+                            const float4 wv = wt[k4];
+                            float *ac = acc[oy * 2 + ox] + k4 * 4;
+                            ac[0] = fmaf(x, wv.x, ac[0]); ac[1] = fmaf(x, wv.y, ac[1]);
+                            ac[2] = fmaf(x, wv.z, ac[2]); ac[3] = fmaf(x, wv.w, ac[3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    float *o = out + (((size_t)n * (a.K / CB) + kb) * Hp * Wp + p) * CB;
+#pragma unroll
+    for (int k4 = 0; k4 < CB; k4 += 4)
+    {
+        float v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            v[q] = fmaxf(fmaxf(apply_act(acc[0][k4 + q], a.act, a.slope), apply_act(acc[1][k4 + q], a.act, a.slope)),
+                         fmaxf(apply_act(acc[2][k4 + q], a.act, a.slope), apply_act(acc[3][k4 + q], a.act, a.slope)));
+        *reinterpret_cast<float4 *>(o + k4) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+}
+
+// The same for compile-time shapes (the 3-channel 3x3 first layer of the image networks): the
+// (FH+1) x (FW+1) x C input patch of the 2x2 block sits in registers and every filter vector
+// fetched from shared memory feeds all four outputs (16 FMAs per 128-bit load).
+template <int C, int FH, int FW>
+__global__ void __launch_bounds__(128)
+conv2d_first_pool_fixed_f32_kernel(const ConvArgs a, const float *__restrict__ in, const float *__restrict__ filt,
+                                   const float *__restrict__ bias, float *__restrict__ out)
+{
+    __shared__ __align__(16) float w[FH * FW * C * CB]; // [taps][C][16]
+    const int kb = blockIdx.y;
+    const int n = blockIdx.z;
+    constexpr int wn = FH * FW * C * CB;
+    const float *fsrc = filt + (size_t)kb * wn;
+    for (int i = threadIdx.x; i < wn; i += blockDim.x)
+        w[i] = fsrc[i];
+    __syncthreads();
+    const int Hp = a.Ho / 2, Wp = a.Wo / 2;
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= Hp * Wp)
+        return;
+    const int ph = p / Wp, pw = p - ph * Wp;
+    const float *img = in + (size_t)n * C * a.H * a.W;
+    const int ih0 = 2 * ph - a.pad_t, iw0 = 2 * pw - a.pad_l;
+    float x[FH + 1][FW + 1][C];
+#pragma unroll
+    for (int dr = 0; dr <= FH; ++dr)
+    {
+        const int ih = ih0 + dr;
+        const bool rok = ih >= 0 && ih < a.H;
+#pragma unroll
+        for (int dc = 0; dc <= FW; ++dc)
+        {
+            const int iw = iw0 + dc;
+            const bool ok = rok && iw >= 0 && iw < a.W;
+            const float *px = img + ((size_t)(ok ? ih : 0) * a.W + (ok ? iw : 0)) * C;
+#pragma unroll
+            for (int c = 0; c < C; ++c)
+                x[dr][dc][c] = ok ? __ldg(px + c) : 0.f; // a padded tap adds nothing
+        }
+    }
+    float acc[4][CB];
+#pragma unroll
+    for (int k = 0; k < CB; ++k)
+    {
+        const float s = bias ? bias[kb * CB + k] : 0.f;
+        acc[0][k] = s; acc[1][k] = s; acc[2][k] = s; acc[3][k] = s;
+    }
+#pragma unroll
+    for (int kh = 0; kh < FH; ++kh)
+#pragma unroll
+        for (int kw = 0; kw < FW; ++kw)
+#pragma unroll
+            for (int c = 0; c < C; ++c)
+            {
+                const float4 *wt = reinterpret_cast<const float4 *>(w + ((kh * FW + kw) * C + c) * CB);
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4)
+                {
+                    const float4 wv = wt[k4];
+#pragma unroll
+                    for (int o = 0; o < 4; ++o)
+                    {
+                        const float xv = x[(o >> 1) + kh][(o & 1) + kw][c];
+                        float *ac = acc[o] + k4 * 4;
+                        ac[0] = fmaf(xv, wv.x, ac[0]); ac[1] = fmaf(xv, wv.y, ac[1]);
+                        ac[2] = fmaf(xv, wv.z, ac[2]); ac[3] = fmaf(xv, wv.w, ac[3]);
+                    }
+                }
+            }
+    float *o = out + (((size_t)n * (a.K / CB) + kb) * Hp * Wp + p) * CB;
+#pragma unroll
+    for (int k4 = 0; k4 < CB; k4 += 4)
+    {
+        float v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            v[q] = fmaxf(fmaxf(apply_act(acc[0][k4 + q], a.act, a.slope), apply_act(acc[1][k4 + q], a.act, a.slope)),
+                         fmaxf(apply_act(acc[2][k4 + q], a.act, a.slope), apply_act(acc[3][k4 + q], a.act, a.slope)));
+        *reinterpret_cast<float4 *>(o + k4) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+}
+
+template <int BN, int CH, int STRIDE, bool POOL = false>
 int launch_conv(const ConvArgs &a, size_t smem_bytes, const float *in, const float *filt,
                 const float *bias, float *out, cudaStream_t st)
 {
-    auto kern = conv2d_f32_kernel<BN, CH, STRIDE>;
+    auto kern = conv2d_f32_kernel<BN, CH, STRIDE, POOL>;
     static bool configured = false; // one attribute call per instantiation and process
     if (!configured)
     {
@@ -308,12 +509,16 @@ int launch_conv(const ConvArgs &a, size_t smem_bytes, const float *in, const flo
 }
 } // namespace
 
-extern "C" int small_b200_conv2d_f32(const small_b200_layer *L, const float *in, const float *filt,
-                                     const float *bias, float *out, void *stream)
+namespace
+{
+// pool: 0 = plain convolution; 1 = fused 2x2 stride-2 max pool (the caller has checked the shape)
+int conv2d_f32_impl(const small_b200_layer *L, int pool, const float *in, const float *filt,
+                    const float *bias, float *out, void *stream)
 {
     if (int rc = check_window_layer(L, "Conv2D<float>", true, 2))
         return rc;
     ConvArgs a;
+    a.pool = pool;
     a.N = L->N; a.C = L->C; a.K = L->K; a.H = L->H; a.W = L->W;
     a.Fh = L->Fh; a.Fw = L->Fw; a.stride = L->stride; a.pad_t = L->pad_t; a.pad_l = L->pad_l;
     a.Ho = out_dim(L->H, L->pad_t, L->pad_b, L->Fh, L->stride);
@@ -329,6 +534,17 @@ extern "C" int small_b200_conv2d_f32(const small_b200_layer *L, const float *in,
         const size_t smem = (size_t)L->Fh * L->Fw * L->C * CB * sizeof(float);
         if (smem > 48 * 1024)
             return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> ERROR: first-layer window too large.");
+        if (pool)
+        {
+            dim3 grid(((a.Ho / 2) * (a.Wo / 2) + 127) / 128, a.K / CB, a.N);
+            if (L->C == 3 && L->Fh == 3 && L->Fw == 3)
+            {
+                conv2d_first_pool_fixed_f32_kernel<3, 3, 3><<<grid, 128, 0, st>>>(a, in, filt, bias, out);
+                return launched("conv2d_first_pool_fixed_f32_kernel");
+            }
+            conv2d_first_pool_f32_kernel<<<grid, 128, smem, st>>>(a, in, filt, bias, out);
+            return launched("conv2d_first_pool_f32_kernel");
+        }
         dim3 grid((a.Ho * a.Wo + 255) / 256, a.K / CB, a.N);
         conv2d_first_f32_kernel<<<grid, 256, smem, st>>>(a, in, filt, bias, out);
         return launched("conv2d_first_f32_kernel");
@@ -343,6 +559,15 @@ extern "C" int small_b200_conv2d_f32(const small_b200_layer *L, const float *in,
     auto smem_for = [&](int bn) { return 2 * (patch_b + (size_t)L->Fh * L->Fw * CB * bn * sizeof(float)); };
     const size_t limit = 200 * 1024;
     int bn = 0;
+    if (pool)
+    {
+        // the pooled epilogue is written for 8 channel groups per pixel group
+        if (a.K % 64 == 0 && smem_for(64) <= limit)
+            return launch_conv<64, 8, 1, true>(((a.kblocks = a.K / 64), a), smem_for(64), in, filt, bias, out, st);
+        if (a.K % 32 == 0 && smem_for(32) <= limit)
+            return launch_conv<32, 4, 1, true>(((a.kblocks = a.K / 32), a), smem_for(32), in, filt, bias, out, st);
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D+MaxPool2D<float> ERROR: shape not covered by the fused kernel.");
+    }
     if (a.K % 64 == 0 && smem_for(64) <= limit)
         bn = 64;
     else if (a.K % 32 == 0 && smem_for(32) <= limit)
@@ -363,3 +588,37 @@ extern "C" int small_b200_conv2d_f32(const small_b200_layer *L, const float *in,
     return s2 ? launch_conv<16, 4, 2>(a, smem, in, filt, bias, out, st)
               : launch_conv<16, 4, 1>(a, smem, in, filt, bias, out, st);
 }
+} // namespace
+
+extern "C"
+{
+int small_b200_conv2d_f32(const small_b200_layer *L, const float *in, const float *filt, const float *bias,
+                          float *out, void *stream)
+{
+    return conv2d_f32_impl(L, 0, in, filt, bias, out, stream);
+}
+
+int small_b200_conv2d_maxpool_f32_supported(const small_b200_layer *conv, const small_b200_layer *pool)
+{
+    if (!conv || !pool || conv->stride != 1 || conv->accumulate)
+        return 0;
+    if (conv->K % (conv->C < CB ? 16 : 32) != 0) // the staged kernel pairs rows inside a warp: 32 or 64 channels per CTA
+        return 0;
+    if (pool->Fh != 2 || pool->Fw != 2 || pool->stride != 2 || pool->pad_t || pool->pad_b || pool->pad_l || pool->pad_r)
+        return 0;
+    const int Ho = out_dim(conv->H, conv->pad_t, conv->pad_b, conv->Fh, 1);
+    const int Wo = out_dim(conv->W, conv->pad_l, conv->pad_r, conv->Fw, 1);
+    if (Ho <= 0 || Wo <= 0 || Ho % 2 || Wo % 2 || pool->H != Ho || pool->W != Wo || pool->C != conv->K ||
+        pool->N != conv->N)
+        return 0;
+    return 1;
+}
+
+int small_b200_conv2d_maxpool_f32(const small_b200_layer *conv, const small_b200_layer *pool, const float *in,
+                                  const float *filt, const float *bias, float *out, void *stream)
+{
+    if (!small_b200_conv2d_maxpool_f32_supported(conv, pool))
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D+MaxPool2D<float> ERROR: shape not covered by the fused kernel.");
+    return conv2d_f32_impl(conv, 1, in, filt, bias, out, stream);
+}
+} // extern "C"

@@ -194,6 +194,37 @@ def Conv2D_Bias_Activation(kernel_height, kernel_width, stride, t_pad, b_pad, l_
           filter_buf, output_buf, bias_buf, activation, negative_slope, batch, stream)
 
 
+def conv2d_maxpool_supported(conv_kernel_height, conv_kernel_width, conv_stride, conv_pads,
+                             pool_kernel_height, pool_kernel_width, pool_stride, pool_pads,
+                             output_channels, input_channels, input_height, input_width):
+    """Whether Conv2D_Bias_Activation_Maxpool2D runs as one kernel for this pair of shapes."""
+    Lc = _layer(1, input_channels, output_channels, input_height, input_width, conv_kernel_height,
+                conv_kernel_width, conv_stride, *conv_pads)
+    ho, wo = Lc.out_hw()
+    Lp = _layer(1, output_channels, output_channels, ho, wo, pool_kernel_height, pool_kernel_width,
+                pool_stride, *pool_pads)
+    return bool(lib().small_b200_conv2d_maxpool_f32_supported(C.byref(Lc), C.byref(Lp)))
+
+
+def Conv2D_Bias_Activation_Maxpool2D(conv_kernel_height, conv_kernel_width, conv_stride, conv_pads,
+                                     pool_kernel_height, pool_kernel_width, pool_stride, pool_pads,
+                                     output_channels, input_channels, input_height, input_width,
+                                     input_buf, filter_buf, bias_buf, output_buf, *,
+                                     activation=ACT_NONE, negative_slope=0.0, batch=1, stream=None):
+    """small::Conv2D_Maxpool2D / Conv2D_ReLU_Maxpool2D / Conv2D_Bias_ReLU_Maxpool2D
+    (fused_interface_abstract.hpp:463-1418 of the reference) as ONE kernel, float buffers, for
+    the shapes conv2d_maxpool_supported() accepts; bias_buf may be None."""
+    Lc = _layer(batch, input_channels, output_channels, input_height, input_width, conv_kernel_height,
+                conv_kernel_width, conv_stride, *conv_pads, 0, activation, negative_slope)
+    ho, wo = Lc.out_hw()
+    Lp = _layer(batch, output_channels, output_channels, ho, wo, pool_kernel_height, pool_kernel_width,
+                pool_stride, *pool_pads)
+    po, pw = Lp.out_hw()
+    _need(output_buf, batch * output_channels * po * pw, "Conv2D_Maxpool2D output")
+    check(lib().small_b200_conv2d_maxpool_f32(C.byref(Lc), C.byref(Lp), _ptr(input_buf), _ptr(filter_buf),
+                                              _ptr(bias_buf), _ptr(output_buf), _stream(stream)))
+
+
 # --------------------------------------------------------------------------- per-channel windows
 def _window(fn_f32, fn_u8, name, has_filter, kh, kw, stride, t, b, l, r, C_, H, W, inp, filt, out,
             bias, partial, act, slope, batch, stream):

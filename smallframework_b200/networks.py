@@ -180,11 +180,15 @@ class Chain:
 
     TC_MIN_CHANNELS = 32
 
-    def __init__(self, layers, batch, dtype="f32", device="cuda", tensor_core="auto"):
+    def __init__(self, layers, batch, dtype="f32", device="cuda", tensor_core="auto", fuse_pool=True):
         """tensor_core: "auto" = fp32 convolutions the 3xTF32 kernel covers and that have at
         least `TC_MIN_CHANNELS` input channels run on the tensor cores; True = every covered
-        layer; False = CUDA cores only."""
+        layer; False = CUDA cores only.  fuse_pool: a CUDA-core convolution followed by a 2x2
+        stride-2 max pool runs as one kernel where the library covers the pair (the reference's
+        Conv2D_Bias_ReLU_Maxpool2D path); the pool's entry in `fused_into` then names its
+        producer and enqueue_layer() does nothing for it."""
         self.layers, self.batch, self.dtype = layers, batch, dtype
+        self.fuse_pool = fuse_pool
         self.tensor_core = tensor_core
         self.tdtype = torch.float32 if dtype == "f32" else torch.uint8
         self.elt = 4 if dtype == "f32" else 1
@@ -231,6 +235,16 @@ class Chain:
                                                              torch.cuda.current_stream().cuda_stream))
                 self.prepared[i] = prep
             torch.cuda.synchronize()
+        self.fused_into = {}  # index of a max pool -> index of the convolution that absorbs it
+        if dtype == "f32" and fuse_pool:
+            for i in range(len(layers) - 1):
+                L, Pn = layers[i], layers[i + 1]
+                if L["op"] != "conv" or Pn["op"] != "maxpool" or self.prepared[i] is not None:
+                    continue
+                dc = self._desc(L, L["C"] if i == 0 else padded(L["C"]))
+                dp = self._desc(Pn, padded(Pn["C"]))
+                if lib().small_b200_conv2d_maxpool_f32_supported(C.byref(dc), C.byref(dp)):
+                    self.fused_into[i + 1] = i
         self.graph = None
         self.y = None
         self.kernels_per_step = 0
@@ -252,7 +266,12 @@ class Chain:
         sfx = "f32" if self.dtype == "f32" else "u8"
         l = lib()
         p = lambda t: t.data_ptr() if t is not None else None
-        if L["op"] == "conv" and self.prepared[i] is not None:
+        if i in self.fused_into:
+            return  # computed by its producer
+        if L["op"] == "conv" and (i + 1) in self.fused_into:
+            dp = self._desc(self.layers[i + 1], padded(self.layers[i + 1]["C"]))
+            check(l.small_b200_conv2d_maxpool_f32(C.byref(d), C.byref(dp), p(src), p(wt), p(bs), p(dst), stream))
+        elif L["op"] == "conv" and self.prepared[i] is not None:
             check(l.small_b200_conv2d_f32_tf32x3(C.byref(d), p(src), p(self.prepared[i]),
                                                  p(bs), p(dst), stream))
         elif L["op"] == "conv":
@@ -266,12 +285,27 @@ class Chain:
         else:
             raise ValueError(L["op"])
 
+    def io_plan(self):
+        """(source, destination) tensors of every layer in the order enqueue() runs them;
+        None for a layer that its producer absorbs."""
+        plan, src = [], self.x
+        for i in range(len(self.layers)):
+            if i in self.fused_into:
+                plan.append(None)  # its producer wrote the pooled tensor
+                continue
+            dst = self.bufs[1] if src is self.bufs[0] else self.bufs[0]
+            plan.append((src, dst))
+            src = dst
+        return plan
+
     def enqueue(self, stream=None):
         stream = self.stream.cuda_stream if stream is None else stream
         src = self.x
         n0 = _lib.launch_count()
-        for i in range(len(self.layers)):
-            dst = self.bufs[i & 1]
+        for i, io in enumerate(self.io_plan()):
+            if io is None:
+                continue
+            src, dst = io
             self.enqueue_layer(i, src, dst, stream)
             src = dst
         self.kernels_per_step = _lib.launch_count() - n0

@@ -286,3 +286,60 @@ def test_full_size_tiny_yolo_layer_linearity():
     y1, y2, y12 = run(x1, N), run(x2, N), run(x1 + x2, N)
     assert rel_max_err(y12, y1 + y2) <= 1e-5
     assert np.array_equal(run(x1[5:6], 1)[0], y1[5])
+
+
+FUSED_POOL_CASES = [
+    # C, K, H, W, Fh, Fw, conv pads, batch
+    (3, 16, 20, 24, 3, 3, "same", 2),     # first layer (HWC image), 4 x 16 accumulators per thread
+    (3, 64, 32, 32, 3, 3, "same", 1),
+    (1, 32, 12, 10, 3, 3, "same", 2),
+    (16, 32, 24, 40, 3, 3, "same", 2),    # staged kernel, 32-channel CTA (Tiny-YOLOv2 conv2 shape class)
+    (32, 64, 16, 16, 3, 3, "same", 2),    # staged kernel, 64-channel CTA
+    (16, 32, 10, 22, 3, 3, "valid", 1),   # output 8 x 20: tiles that overhang the image
+    (16, 64, 18, 18, 1, 1, "valid", 1),
+]
+
+
+@pytest.mark.parametrize("case", FUSED_POOL_CASES, ids=lambda c: "C{}_K{}_{}x{}_k{}x{}_{}_n{}".format(*c))
+@pytest.mark.parametrize("mode", ["plain", "bias_relu", "bias_leaky"])
+def test_conv2d_maxpool_fused(oracle, case, mode):
+    """Conv2D(+bias)(+activation) -> MaxPool2D 2x2 / 2 as ONE kernel (the reference's
+    Conv2D_Bias_ReLU_Maxpool2D family, fused_interface_abstract.hpp:463-1418) against the oracle's
+    convolution followed by its max pool."""
+    C, K, H, W, Fh, Fw, pm, N = case
+    pads = _pads(H, W, Fh, Fw, 1, pm)
+    rng = np.random.default_rng(abs(hash((case, mode))) % (1 << 31))
+    x = rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    w = rng.normal(0, np.sqrt(2.0 / (C * Fh * Fw)), (K, C, Fh, Fw)).astype(np.float32)
+    bias = None if mode == "plain" else rng.uniform(-0.5, 0.5, K).astype(np.float32)
+    act, slope = {"plain": (0, 0.0), "bias_relu": (S.ACT_RELU, 0.0), "bias_leaky": (S.ACT_LEAKY, 0.1)}[mode]
+    sh = shape(C, K, H, W, Fh, Fw, 1, pads, CB)
+    ho, wo = sh.out_hw()
+    shp = shape(K, K, ho, wo, 2, 2, 2, (0, 0, 0, 0), CB)
+    assert S.conv2d_maxpool_supported(Fh, Fw, 1, pads, 2, 2, 2, (0, 0, 0, 0), K, C, H, W)
+    xp, wp = P.pack_activation(x), P.pack_conv_filter(w)
+    O = S.FloatBuffer(N * K * (ho // 2) * (wo // 2))
+    S.Conv2D_Bias_Activation_Maxpool2D(Fh, Fw, 1, pads, 2, 2, 2, (0, 0, 0, 0), K, C, H, W, fbuf(xp), fbuf(wp),
+                                       None if bias is None else fbuf(bias), O, activation=act,
+                                       negative_slope=slope, batch=N)
+    got = O.numpy().reshape(N, -1)
+    conv = oracle_conv_batch(oracle, sh, xp, wp, bias=bias, act=act, slope=slope)
+    want = np.stack([oracle.pool2d_f32(shp, conv[n]) for n in range(N)])
+    assert rel_max_err(got, want) <= TOL
+    if C >= CB:
+        # the staged kernel adds in the same order with or without the pool: bit-identical to
+        # the two-kernel path
+        mid, two = S.FloatBuffer(N * K * ho * wo), S.FloatBuffer(N * K * (ho // 2) * (wo // 2))
+        S.Conv2D_Bias_Activation(Fh, Fw, 1, *pads, K, C, H, W, fbuf(xp), fbuf(wp),
+                                 None if bias is None else fbuf(bias), mid, activation=act,
+                                 negative_slope=slope, batch=N)
+        S.MaxPool2D(2, 2, 2, 0, 0, 0, 0, K, ho, wo, mid, two, batch=N)
+        assert np.array_equal(got, two.numpy().reshape(N, -1))
+
+
+def test_conv2d_maxpool_fused_refuses_other_pools():
+    assert not S.conv2d_maxpool_supported(3, 3, 1, (1, 1, 1, 1), 2, 2, 1, (0, 1, 0, 1), 32, 16, 13, 13)  # stride-1 pool
+    assert not S.conv2d_maxpool_supported(3, 3, 1, (1, 1, 1, 1), 3, 3, 2, (0, 0, 0, 0), 32, 16, 16, 16)  # 3x3 pool
+    assert not S.conv2d_maxpool_supported(3, 3, 1, (1, 1, 1, 1), 2, 2, 2, (0, 0, 0, 0), 32, 16, 13, 13)  # odd output
+    assert not S.conv2d_maxpool_supported(3, 3, 2, (0, 1, 0, 1), 2, 2, 2, (0, 0, 0, 0), 32, 16, 16, 16)  # stride-2 conv
+    assert not S.conv2d_maxpool_supported(3, 3, 1, (1, 1, 1, 1), 2, 2, 2, (0, 0, 0, 0), 16, 16, 16, 16)  # 16 channels
