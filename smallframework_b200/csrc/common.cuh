@@ -92,6 +92,69 @@ __host__ __device__ inline int32_t requant(int32_t acc, int32_t lshift, int32_t 
     return v > 0 ? (v < 255 ? v : 255) : 0;
 }
 
+#ifdef __CUDACC__
+// The same tail for a positive multiplier (every quantiser in practice), in 32-bit arithmetic:
+// a non-positive input ends at 0 after the clamp, and for a positive one the nudge is 2^30, the
+// truncating division a plain shift and the rounding threshold mask >> 1.  About a third of the
+// instructions of the general form; bit-identical to it (the uint8 GPU tests compare every layer
+// with the oracle, which is pinned to the reference).
+static __device__ __noinline__ int32_t requant_general(int32_t acc, int32_t lshift, int32_t rshift, int32_t mult)
+{
+    return requant(acc, lshift, rshift, mult);
+}
+// Unclamped result of the tail for a positive multiplier: with t = v * mult + 2^30 the reference's
+// two steps (t >> 31, then the rounding shift "floor minus one when the remainder exceeds half")
+// collapse into u = t >> (30 + rshift), r = (u >> 1) - (u & 1) for rshift >= 1 (the remainder
+// exceeds mask >> 1 exactly when bit rshift-1 of t >> 31 is set) and r = t >> 31 for rshift = 0.
+__device__ __forceinline__ int32_t requant_raw(int32_t acc, int32_t lshift, int32_t rshift, int32_t mult)
+{
+    int32_t v = (int32_t)((uint32_t)acc << lshift);
+    v = v > 0 ? v : 0;
+    // one wide multiply-add (a 32-bit multiply-high would go to the slow special-function pipe)
+    const unsigned long long t = (unsigned long long)(uint32_t)v * (uint32_t)mult + (1ull << 30);
+    const uint32_t u = (uint32_t)(t >> (30 + rshift));
+    return (int32_t)(u >> 1) - (int32_t)(u & (rshift > 0 ? 1u : 0u));
+}
+__device__ __forceinline__ int32_t requant_dev(int32_t acc, int32_t lshift, int32_t rshift, int32_t mult)
+{
+    if (mult <= 0)
+        return requant_general(acc, lshift, rshift, mult);
+    const int32_t r = requant_raw(acc, lshift, rshift, mult);
+    return r < 0 ? 0 : (r > 255 ? 255 : r);
+}
+// Four results clamped to 0..255 and packed, lowest byte first, by two saturating pack-converts.
+__device__ __forceinline__ uint32_t pack4_sat(int32_t r0, int32_t r1, int32_t r2, int32_t r3)
+{
+    uint32_t hi, d;
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(r3), "r"(r2), "r"(0));
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(r1), "r"(r0), "r"(hi));
+    return d;
+}
+// 16 accumulators -> 16 output bytes
+__device__ __forceinline__ uint4 requant_pack16(const int32_t *acc, int32_t lshift, int32_t rshift, int32_t mult)
+{
+    int32_t r[16];
+    if (mult <= 0)
+    {
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+            r[k] = requant_general(acc[k], lshift, rshift, mult);
+    }
+    else
+    {
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+            r[k] = requant_raw(acc[k], lshift, rshift, mult);
+    }
+    uint4 o;
+    o.x = pack4_sat(r[0], r[1], r[2], r[3]);
+    o.y = pack4_sat(r[4], r[5], r[6], r[7]);
+    o.z = pack4_sat(r[8], r[9], r[10], r[11]);
+    o.w = pack4_sat(r[12], r[13], r[14], r[15]);
+    return o;
+}
+#endif
+
 __device__ __forceinline__ float apply_act(float v, int act, float slope)
 {
     if (act == SMALL_B200_ACT_RELU)

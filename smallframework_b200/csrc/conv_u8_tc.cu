@@ -95,34 +95,38 @@ struct PwArgs
 
 constexpr int TILE_M = 128;
 
+// Persistent: a CTA keeps its slice of the filter (and the per-channel correction terms) and
+// walks over pixel tiles; loads, MMAs and the epilogue of consecutive tiles overlap through two
+// activation stages in shared memory and two accumulator buffers in tensor memory.
+//   warps 0..3  epilogue: thread t owns pixel t of the tile = TMEM lane t
+//   warp 4      lane 0 issues the TMA loads (and the warp owns the TMEM allocation)
+//   warp 5      lane 0 issues the MMAs
 template <int NT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(192)
 pw_u8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const PwArgs a, const uint8_t *__restrict__ filt,
                 const int32_t *__restrict__ bias, uint8_t *__restrict__ out, int *status)
 {
-    constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
+    constexpr uint32_t TMEM_COLS = 2 * NT < 32 ? 32 : 2 * NT;
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full_bar, mma_bar;
+    __shared__ __align__(8) uint64_t full_bar[2], mma_bar[2], done_bar[2], b_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ int corr[NT];
 
-    uint8_t *sA = smem;                                  // [cbs][128][16]
-    uint8_t *sB = smem + (size_t)a.cbs * TILE_M * CB;    // [NT/16][cbs][16][16]
     const uint32_t a_bytes = (uint32_t)a.cbs * TILE_M * CB;
     const uint32_t b_bytes = (uint32_t)(NT / CB) * a.cbs * CB * CB;
+    uint8_t *sA = smem;                   // [stage][cbs][128][16]
+    uint8_t *sB = smem + 2 * (size_t)a_bytes; // [NT/16][cbs][16][16]
 
-    int bid = blockIdx.x;
-    const int nb = bid % a.nblocks; bid /= a.nblocks;
-    const int tile = bid % a.tiles;
-    const int g = bid / a.tiles;
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int nb = blockIdx.y;
+    const int total = a.groups * a.tiles;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    if (warp == 0)
+    if (warp == 4)
     {
-        if (tid == 0)
+        if (lane == 0)
         {
-            mbar_init(&full_bar, 1);
-            mbar_init(&mma_bar, 1);
+            for (int i = 0; i < 2; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&mma_bar[i], 1); mbar_init(&done_bar[i], 4); }
+            mbar_init(&b_bar, 1);
             fence_barrier_init();
         }
         __syncwarp();
@@ -134,89 +138,122 @@ pw_u8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const PwArgs a, const
     tc_fence_after_sync();
     const uint32_t tmem = tmem_base_s;
 
-    if (tid == 0)
+    if (warp == 4 && lane == 0)
     {
-        mbar_expect_tx(&full_bar, a_bytes + b_bytes);
-        tma_load_3d(sA, &map_a, 0, tile * TILE_M, g * a.cbs, &full_bar);
-        tma_load_1d(sB, filt + (size_t)nb * b_bytes, b_bytes, &full_bar);
+        mbar_expect_tx(&b_bar, b_bytes);
+        tma_load_1d(sB, filt + (size_t)nb * b_bytes, b_bytes, &b_bar);
+        bool ok = true;
+        int i = 0;
+        for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++i)
+        {
+            const int s = i & 1;
+            if (i >= 2)
+                ok = mbar_wait(&done_bar[s], ((i >> 1) - 1) & 1, status, 3);
+            if (!ok)
+                break;
+            const int tile = item % a.tiles, g = item / a.tiles;
+            mbar_expect_tx(&full_bar[s], a_bytes);
+            tma_load_3d(sA + (size_t)s * a_bytes, &map_a, 0, tile * TILE_M, g * a.cbs, &full_bar[s]);
+        }
     }
-    bool ok = mbar_wait(&full_bar, 0, status, 1);
-
-    if (tid == 0 && ok)
+    else if (warp == 5 && lane == 0)
     {
-        tc_fence_after_sync();
+        bool ok = mbar_wait(&b_bar, 0, status, 4);
         constexpr uint32_t idesc = make_idesc(2 /*s32*/, 0 /*u8*/, 0 /*u8*/, 0 /*A K-major*/, 1 /*B MN-major*/,
                                               TILE_M, NT);
-        const uint32_t sa = smem_u32(sA), sb_ = smem_u32(sB);
-        for (int j = 0; j < a.cbs / 2; ++j)
+        const uint32_t sb_ = smem_u32(sB);
+        int i = 0;
+        for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++i)
         {
-            const uint64_t da = make_smem_desc(sa + j * 2 * TILE_M * CB, TILE_M * CB, 8 * CB, 0);
-            const uint64_t db = make_smem_desc(sb_ + j * 2 * CB * CB, 8 * CB, a.cbs * CB * CB, 0);
-            tc_mma_i8(tmem, da, db, idesc, j > 0 ? 1u : 0u);
-        }
-        tc_commit(&mma_bar);
-    }
-
-    // while the tensor core works: row sum of this thread's pixel, column sums of the filter
-    int asum = 0;
-    if (ok && a.zero_filt != 0)
-    {
-        for (int cb = 0; cb < a.cbs; ++cb)
-        {
-            const uint4 v = *reinterpret_cast<const uint4 *>(sA + ((size_t)cb * TILE_M + tid) * CB);
-            asum = (int)__dp4a(v.x, 0x01010101u, (unsigned)asum);
-            asum = (int)__dp4a(v.y, 0x01010101u, (unsigned)asum);
-            asum = (int)__dp4a(v.z, 0x01010101u, (unsigned)asum);
-            asum = (int)__dp4a(v.w, 0x01010101u, (unsigned)asum);
-        }
-    }
-    if (tid < NT)
-    {
-        const int kg = nb * NT + tid;
-        int c = a.k_zero + (bias ? bias[kg] : 0) + a.cbs * CB * a.zero_in * a.zero_filt;
-        if (ok && a.zero_in != 0)
-        {
-            int wsum = 0;
-            const uint8_t *col = sB + (size_t)(tid / CB) * a.cbs * CB * CB + (tid % CB);
-            for (int i = 0; i < a.cbs * CB; ++i)
-                wsum += col[i * CB];
-            c += a.zero_in * wsum;
-        }
-        corr[tid] = c;
-    }
-    __syncthreads();
-
-    ok = ok && mbar_wait(&mma_bar, 0, status, 2);
-    tc_fence_after_sync();
-    const int p = tile * TILE_M + tid;
-    if (ok)
-    {
-        const int base = a.zero_filt * asum;
-        uint8_t *orow = out + (size_t)g * a.out_group_stride + (size_t)p * a.out_pix_stride;
-#pragma unroll
-        for (int c0 = 0; c0 < NT; c0 += 16)
-        {
-            uint32_t r[16];
-            tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c0, r);
-            tmem_ld_wait();
-            int q[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-                q[i] = requant((int)r[i] + base + corr[c0 + i], a.lshift, a.rshift, a.mult);
-            if (p < a.P)
+            const int s = i & 1;
+            ok = mbar_wait(&full_bar[s], (i >> 1) & 1, status, 1);
+            if (!ok)
+                break;
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(sA + (size_t)s * a_bytes);
+            for (int j = 0; j < a.cbs / 2; ++j)
             {
-                uint4 o;
-                o.x = (unsigned)q[0] | ((unsigned)q[1] << 8) | ((unsigned)q[2] << 16) | ((unsigned)q[3] << 24);
-                o.y = (unsigned)q[4] | ((unsigned)q[5] << 8) | ((unsigned)q[6] << 16) | ((unsigned)q[7] << 24);
-                o.z = (unsigned)q[8] | ((unsigned)q[9] << 8) | ((unsigned)q[10] << 16) | ((unsigned)q[11] << 24);
-                o.w = (unsigned)q[12] | ((unsigned)q[13] << 8) | ((unsigned)q[14] << 16) | ((unsigned)q[15] << 24);
-                *reinterpret_cast<uint4 *>(orow + (size_t)((nb * NT + c0) / CB) * a.out_plane_stride) = o;
+                const uint64_t da = make_smem_desc(sa + j * 2 * TILE_M * CB, TILE_M * CB, 8 * CB, 0);
+                const uint64_t db = make_smem_desc(sb_ + j * 2 * CB * CB, 8 * CB, a.cbs * CB * CB, 0);
+                tc_mma_i8(tmem + (uint32_t)(s * NT), da, db, idesc, j > 0 ? 1u : 0u);
             }
+            tc_commit(&mma_bar[s]);
+        }
+    }
+    else if (warp < 4)
+    {
+        // per-channel constants: k_zero + bias + C*zI*zF + zI * (column sum of the filter)
+        bool ok = mbar_wait(&b_bar, 0, status, 5);
+        if (tid < NT)
+        {
+            const int kg = nb * NT + tid;
+            int c = a.k_zero + (bias ? bias[kg] : 0) + a.cbs * CB * a.zero_in * a.zero_filt;
+            if (ok && a.zero_in != 0)
+            {
+                int wsum = 0;
+                const uint8_t *col = sB + (size_t)(tid / CB) * a.cbs * CB * CB + (tid % CB);
+                for (int i = 0; i < a.cbs * CB; ++i)
+                    wsum += col[i * CB];
+                c += a.zero_in * wsum;
+            }
+            corr[tid] = c;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        int i = 0;
+        for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++i)
+        {
+            const int s = i & 1;
+            const int tile = item % a.tiles, g = item / a.tiles;
+            ok = mbar_wait(&full_bar[s], (i >> 1) & 1, status, 6);
+            if (!ok)
+                break;
+            // while the tensor core works: row sum of this thread's pixel
+            int asum = 0;
+            if (a.zero_filt != 0)
+            {
+                const uint8_t *arow = sA + (size_t)s * a_bytes + (size_t)tid * CB;
+                for (int cb = 0; cb < a.cbs; ++cb)
+                {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(arow + (size_t)cb * TILE_M * CB);
+                    asum = (int)__dp4a(v.x, 0x01010101u, (unsigned)asum);
+                    asum = (int)__dp4a(v.y, 0x01010101u, (unsigned)asum);
+                    asum = (int)__dp4a(v.z, 0x01010101u, (unsigned)asum);
+                    asum = (int)__dp4a(v.w, 0x01010101u, (unsigned)asum);
+                }
+            }
+            ok = mbar_wait(&mma_bar[s], (i >> 1) & 1, status, 2);
+            if (!ok)
+                break;
+            tc_fence_after_sync();
+            const int p = tile * TILE_M + tid;
+            const int base = a.zero_filt * asum;
+            uint8_t *orow = out + (size_t)g * a.out_group_stride + (size_t)p * a.out_pix_stride;
+#pragma unroll
+            for (int c0 = 0; c0 < NT; c0 += 16)
+            {
+                uint32_t r[16];
+                tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(s * NT + c0), r);
+                tmem_ld_wait();
+                int q[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                    q[e] = (int)r[e] + base + corr[c0 + e];
+                const uint4 o = requant_pack16(q, a.lshift, a.rshift, a.mult);
+                if (p < a.P)
+                {
+                    *reinterpret_cast<uint4 *>(orow + (size_t)((nb * NT + c0) / CB) * a.out_plane_stride) = o;
+                }
+            }
+            // stage s of shared memory and buffer s of tensor memory are free again
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(&done_bar[s]);
         }
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 0)
+    if (warp == 4)
         tmem_dealloc(tmem, TMEM_COLS);
 }
 
@@ -228,14 +265,29 @@ int launch_pw(const CUtensorMap &map, const PwArgs &a, size_t smem, const uint8_
     static bool configured = false;
     if (!configured)
     {
-        SB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         configured = true;
     }
-    const long long blocks = (long long)a.groups * a.tiles * a.nblocks;
     int *status = device_status_ptr();
     if (!status)
         return fail(SMALL_B200_CUDA_ERROR, "device status word not available");
-    kern<<<(unsigned)blocks, 128, smem, st>>>(map, a, filt, bias, out, status);
+    // as many CTAs as fit at once: tensor memory (2 * NT of 512 columns) and shared memory
+    int per_sm = 512 / (2 * NT < 32 ? 32 : 2 * NT);
+    const int by_smem = (int)((220 * 1024) / (smem + 2048));
+    if (per_sm > by_smem)
+        per_sm = by_smem;
+    if (per_sm > 8)
+        per_sm = 8;
+    if (per_sm < 1)
+        per_sm = 1;
+    const long long total = (long long)a.groups * a.tiles;
+    long long gx = (long long)num_sms() * per_sm / a.nblocks;
+    if (gx < 1)
+        gx = 1;
+    if (gx > total)
+        gx = total;
+    dim3 grid((unsigned)gx, (unsigned)a.nblocks);
+    kern<<<grid, 192, smem, st>>>(map, a, filt, bias, out, status);
     return launched("pw_u8_tc_kernel");
 }
 } // namespace
@@ -255,8 +307,8 @@ int conv2d_u8_tensor_core(const small_b200_layer *L, const uint8_t *in, const ui
     if (L->N == 0 || HW == 0)
         return SMALL_B200_OK;
     int nt = (L->K % 128 == 0) ? 128 : (L->K % 64 == 0) ? 64 : (L->K % 32 == 0) ? 32 : 16;
-    size_t smem = (size_t)cbs * TILE_M * CB + (size_t)nt * L->C;
-    if (smem > 96 * 1024)
+    size_t smem = 2 * (size_t)cbs * TILE_M * CB + (size_t)nt * L->C; // two activation stages + the filter slice
+    if (smem > 160 * 1024)
         return -1;
 
     PwArgs a;

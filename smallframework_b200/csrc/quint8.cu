@@ -101,10 +101,8 @@ conv2d_u8_direct_kernel(const QArgs a, const uint8_t *__restrict__ in, const uin
             }
         }
     }
-#pragma unroll
-    for (int k = 0; k < CB; ++k)
-        acc[k] = requant(acc[k], a.lshift, a.rshift, a.mult);
-    *reinterpret_cast<uint4 *>(out + (((size_t)n * (a.K / CB) + kb) * a.Ho * a.Wo + p) * CB) = pack16(acc);
+    *reinterpret_cast<uint4 *>(out + (((size_t)n * (a.K / CB) + kb) * a.Ho * a.Wo + p) * CB) =
+        requant_pack16(acc, a.lshift, a.rshift, a.mult);
 }
 
 // OP: 0 depthwise conv, 1 max pool, 2 average pool; one thread per output pixel and block
@@ -176,10 +174,265 @@ window_u8_kernel(const QArgs a, const uint8_t *__restrict__ in, const uint8_t *_
             }
         }
     }
+    *reinterpret_cast<uint4 *>(out + o * CB) = requant_pack16(acc, a.lshift, a.rshift, a.mult);
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Fast paths for the quantisation every configuration here uses: filter zero point -128 (the
+// reference ADDS offsets, so w + zero_filt is a signed byte) and input zero point 0 or -128
+// (a + zero_in is an unsigned or a signed byte).  The products then fit dp4a, four per
+// instruction.  Padded taps must contribute nothing: their shifted activation is 0.
+__device__ __forceinline__ int dp4a_us(unsigned a, unsigned b, int c) // unsigned a bytes x signed b bytes
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+template <bool SIGNED_IN>
+__device__ __forceinline__ int dp4a_in(unsigned a, unsigned b, int c)
+{
+    return SIGNED_IN ? __dp4a((int)a, (int)b, c) : dp4a_us(a, b, c);
+}
+
+// 4 x 4 byte transpose: r[t] holds 4 channels of tap t; c[j] gets the 4 taps of channel j
+__device__ __forceinline__ void transpose4x4(const unsigned r0, const unsigned r1, const unsigned r2,
+                                             const unsigned r3, unsigned *c)
+{
+    const unsigned t0 = __byte_perm(r0, r1, 0x5140), t1 = __byte_perm(r2, r3, 0x5140);
+    const unsigned t2 = __byte_perm(r0, r1, 0x7362), t3 = __byte_perm(r2, r3, 0x7362);
+    c[0] = __byte_perm(t0, t1, 0x5410); c[1] = __byte_perm(t0, t1, 0x7632);
+    c[2] = __byte_perm(t2, t3, 0x5410); c[3] = __byte_perm(t2, t3, 0x7632);
+}
+
+// Depthwise convolution: one thread per output pixel and block of 16 channels.  A depthwise sum
+// runs over TAPS of one channel while the packed layout keeps CHANNELS of one pixel together, so
+// the taps are taken four at a time and byte-transposed (8 PRMT per 4 x 4) into dp4a operands;
+// the filter is transposed once per CTA into shared memory as signed bytes.
+// QUADS > 0: the number of tap groups is known at compile time and every tap is loaded before
+// the arithmetic starts (one round trip to memory instead of one per group).
+template <bool SIGNED_IN, int QUADS>
+__global__ void __launch_bounds__(256)
+dwconv_u8_dp4a_kernel(const QArgs a, const uint8_t *__restrict__ in, const uint8_t *__restrict__ filt,
+                      const int32_t *__restrict__ bias, uint8_t *__restrict__ out)
+{
+    extern __shared__ __align__(16) unsigned sw[]; // [cb][quad][16 ch]: (w ^ 0x80) of 4 taps; then tap -> (kh, kw)
+    const int taps = a.Fh * a.Fw, quads = QUADS > 0 ? QUADS : (taps + 3) / 4, cbs = a.C / CB;
+    short2 *tap_pos = reinterpret_cast<short2 *>(sw + cbs * quads * CB);
+    for (int i = threadIdx.x; i < cbs * quads * CB; i += blockDim.x)
+    {
+        const int ch = i % CB, q = (i / CB) % quads, cb = i / (CB * quads);
+        unsigned wv = 0;
+        for (int t = 0; t < 4; ++t)
+        {
+            const int tap = 4 * q + t;
+            if (tap < taps)
+                wv |= (unsigned)(filt[((size_t)cb * taps + tap) * CB + ch] ^ 0x80u) << (8 * t);
+        }
+        sw[i] = wv; // a missing tap keeps weight 0
+    }
+    for (int i = threadIdx.x; i < quads * 4; i += blockDim.x)
+        tap_pos[i] = i < taps ? make_short2((short)(i / a.Fw), (short)(i % a.Fw)) : make_short2(-30000, -30000);
+    __syncthreads();
+
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = (long long)a.N * cbs * a.Ho * a.Wo;
+    if (i >= total)
+        return;
+    const long long o = i;
+    const int ow = (int)(i % a.Wo); i /= a.Wo;
+    const int oh = (int)(i % a.Ho); i /= a.Ho; // i = n*(C/16)+cb
+    const int cb = (int)(i % cbs);
+    const uint8_t *plane = in + (size_t)i * a.H * a.W * CB;
+    const int h0 = oh * a.stride - a.pad_t, w0 = ow * a.stride - a.pad_l;
+    int acc[CB];
 #pragma unroll
     for (int k = 0; k < CB; ++k)
-        acc[k] = requant(acc[k], a.lshift, a.rshift, a.mult);
-    *reinterpret_cast<uint4 *>(out + o * CB) = pack16(acc);
+        acc[k] = a.k_zero + (bias ? bias[cb * CB + k] : 0);
+    const uint4 *wq = reinterpret_cast<const uint4 *>(sw + (size_t)cb * quads * CB);
+    if (QUADS > 0)
+    {
+        uint4 v[QUADS > 0 ? QUADS * 4 : 1];
+#pragma unroll
+        for (int t = 0; t < QUADS * 4; ++t)
+        {
+            const short2 pos = tap_pos[t];
+            const int ih = h0 + pos.x, iw = w0 + pos.y;
+            v[t] = make_uint4(0u, 0u, 0u, 0u);
+            if (pos.x >= 0 && ih >= 0 && ih < a.H && iw >= 0 && iw < a.W)
+            {
+                v[t] = *reinterpret_cast<const uint4 *>(plane + ((size_t)ih * a.W + iw) * CB);
+                if (SIGNED_IN)
+                {
+                    v[t].x ^= 0x80808080u; v[t].y ^= 0x80808080u; v[t].z ^= 0x80808080u; v[t].w ^= 0x80808080u;
+                }
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < QUADS; ++q)
+        {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+            {
+                unsigned c[4];
+                const unsigned r0 = g == 0 ? v[4 * q].x : g == 1 ? v[4 * q].y : g == 2 ? v[4 * q].z : v[4 * q].w;
+                const unsigned r1 = g == 0 ? v[4 * q + 1].x : g == 1 ? v[4 * q + 1].y : g == 2 ? v[4 * q + 1].z : v[4 * q + 1].w;
+                const unsigned r2 = g == 0 ? v[4 * q + 2].x : g == 1 ? v[4 * q + 2].y : g == 2 ? v[4 * q + 2].z : v[4 * q + 2].w;
+                const unsigned r3 = g == 0 ? v[4 * q + 3].x : g == 1 ? v[4 * q + 3].y : g == 2 ? v[4 * q + 3].z : v[4 * q + 3].w;
+                transpose4x4(r0, r1, r2, r3, c);
+                const uint4 w4 = wq[q * 4 + g];
+                acc[4 * g + 0] = dp4a_in<SIGNED_IN>(c[0], w4.x, acc[4 * g + 0]);
+                acc[4 * g + 1] = dp4a_in<SIGNED_IN>(c[1], w4.y, acc[4 * g + 1]);
+                acc[4 * g + 2] = dp4a_in<SIGNED_IN>(c[2], w4.z, acc[4 * g + 2]);
+                acc[4 * g + 3] = dp4a_in<SIGNED_IN>(c[3], w4.w, acc[4 * g + 3]);
+            }
+        }
+    }
+    else
+    for (int q = 0; q < quads; ++q)
+    {
+        unsigned r[4][4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+        {
+            const short2 pos = tap_pos[4 * q + t];
+            const int ih = h0 + pos.x, iw = w0 + pos.y;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (pos.x >= 0 && ih >= 0 && ih < a.H && iw >= 0 && iw < a.W)
+            {
+                v = *reinterpret_cast<const uint4 *>(plane + ((size_t)ih * a.W + iw) * CB);
+                if (SIGNED_IN)
+                {
+                    v.x ^= 0x80808080u; v.y ^= 0x80808080u; v.z ^= 0x80808080u; v.w ^= 0x80808080u;
+                }
+            }
+            r[t][0] = v.x; r[t][1] = v.y; r[t][2] = v.z; r[t][3] = v.w;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+        {
+            unsigned c[4];
+            transpose4x4(r[0][g], r[1][g], r[2][g], r[3][g], c);
+            const uint4 w4 = wq[q * 4 + g];
+            acc[4 * g + 0] = dp4a_in<SIGNED_IN>(c[0], w4.x, acc[4 * g + 0]);
+            acc[4 * g + 1] = dp4a_in<SIGNED_IN>(c[1], w4.y, acc[4 * g + 1]);
+            acc[4 * g + 2] = dp4a_in<SIGNED_IN>(c[2], w4.z, acc[4 * g + 2]);
+            acc[4 * g + 3] = dp4a_in<SIGNED_IN>(c[3], w4.w, acc[4 * g + 3]);
+        }
+    }
+    *reinterpret_cast<uint4 *>(out + o * CB) = requant_pack16(acc, a.lshift, a.rshift, a.mult);
+}
+
+// Dense convolution of a ONE-channel image (the first layer of the keyword-spotting network):
+// the Fw taps of a kernel row are consecutive bytes of the image, so a row of the window is one
+// (unaligned) 32-bit word per 4 taps and feeds dp4a directly.  A CTA takes IMGS images: it
+// keeps them zero-padded in shared memory (shifted to signed bytes when zero_in = -128) next to
+// the filter as [kb][kh][quad][16 k] words of 4 kw-bytes; a thread makes one pixel x 16 channels.
+constexpr int C1_IMGS = 2;
+template <bool SIGNED_IN>
+__global__ void __launch_bounds__(256)
+conv2d_u8_c1_dp4a_kernel(const QArgs a, const uint8_t *__restrict__ in, const uint8_t *__restrict__ filt,
+                         const int32_t *__restrict__ bias, uint8_t *__restrict__ out, int pitch, int prow)
+{
+    extern __shared__ __align__(16) unsigned smem_u[];
+    const int quads = (a.Fw + 3) / 4, kbs = a.K / CB;
+    unsigned *sw = smem_u;                                    // [kb][kh][quad][16]
+    uint8_t *simg = reinterpret_cast<uint8_t *>(sw + (size_t)kbs * a.Fh * quads * CB); // [img][prow][pitch]
+    const int n0 = blockIdx.x * C1_IMGS;
+    const int imgs = (a.N - n0) < C1_IMGS ? (a.N - n0) : C1_IMGS;
+    for (int i = threadIdx.x; i < kbs * a.Fh * quads * CB; i += blockDim.x)
+    {
+        const int k = i % CB, q = (i / CB) % quads, kh = (i / (CB * quads)) % a.Fh, kb = i / (CB * quads * a.Fh);
+        unsigned wv = 0;
+        for (int t = 0; t < 4; ++t)
+        {
+            const int kw = 4 * q + t;
+            if (kw < a.Fw) // filter [K/16][1][Fh][Fw][1][16]
+                wv |= (unsigned)(filt[(((size_t)kb * a.Fh + kh) * a.Fw + kw) * CB + k] ^ 0x80u) << (8 * t);
+        }
+        sw[i] = wv;
+    }
+    const int img_bytes = prow * pitch;
+    for (int i = threadIdx.x; i < C1_IMGS * img_bytes / 4; i += blockDim.x)
+        reinterpret_cast<unsigned *>(simg)[i] = 0u;
+    __syncthreads();
+    for (int i = threadIdx.x; i < imgs * a.H * a.W; i += blockDim.x)
+    {
+        const int im = i / (a.H * a.W), p = i - im * a.H * a.W;
+        const int h = p / a.W, w = p - h * a.W;
+        const uint8_t v = in[(size_t)(n0 + im) * a.H * a.W + p];
+        simg[(size_t)im * img_bytes + (h + a.pad_t) * pitch + (w + a.pad_l)] = SIGNED_IN ? (uint8_t)(v ^ 0x80u) : v;
+    }
+    __syncthreads();
+    const int px = a.Ho * a.Wo;
+    const int items = imgs * kbs * px;
+    for (int it = threadIdx.x; it < items; it += blockDim.x)
+    {
+        const int p = it % px, kb = (it / px) % kbs, im = it / (px * kbs);
+        const int oh = p / a.Wo, ow = p - oh * a.Wo;
+        int acc[CB];
+#pragma unroll
+        for (int k = 0; k < CB; ++k)
+            acc[k] = a.k_zero + (bias ? bias[kb * CB + k] : 0);
+        const uint8_t *row = simg + (size_t)im * img_bytes + (oh * a.stride) * pitch + ow * a.stride;
+        const uint4 *wk = reinterpret_cast<const uint4 *>(sw + (size_t)kb * a.Fh * quads * CB);
+        for (int kh = 0; kh < a.Fh; ++kh, row += pitch)
+        {
+            for (int q = 0; q < quads; ++q)
+            {
+                const uint8_t *pw = row + 4 * q;
+                const unsigned *al = reinterpret_cast<const unsigned *>(pw - ((size_t)pw & 3));
+                const unsigned aw = __funnelshift_r(al[0], al[1], 8 * (unsigned)((size_t)pw & 3));
+                const uint4 *w4 = wk + (kh * quads + q) * 4;
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                {
+                    const uint4 wv = w4[g];
+                    acc[4 * g + 0] = dp4a_in<SIGNED_IN>(aw, wv.x, acc[4 * g + 0]);
+                    acc[4 * g + 1] = dp4a_in<SIGNED_IN>(aw, wv.y, acc[4 * g + 1]);
+                    acc[4 * g + 2] = dp4a_in<SIGNED_IN>(aw, wv.z, acc[4 * g + 2]);
+                    acc[4 * g + 3] = dp4a_in<SIGNED_IN>(aw, wv.w, acc[4 * g + 3]);
+                }
+            }
+        }
+        *reinterpret_cast<uint4 *>(out + (((size_t)(n0 + im) * kbs + kb) * px + p) * CB) =
+            requant_pack16(acc, a.lshift, a.rshift, a.mult);
+    }
+}
+
+// Global average pool (window = whole image, no padding): one warp per image and 16-channel
+// block; lanes stride over the pixels, then a shuffle tree adds the 16 channel sums.
+__global__ void __launch_bounds__(256)
+global_avgpool_u8_kernel(const QArgs a, const uint8_t *__restrict__ in, uint8_t *__restrict__ out)
+{
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const long long planes = (long long)a.N * (a.C / CB);
+    if (warp >= planes)
+        return;
+    const int px = a.H * a.W;
+    const uint4 *plane = reinterpret_cast<const uint4 *>(in + (size_t)warp * px * CB);
+    int acc[CB];
+#pragma unroll
+    for (int k = 0; k < CB; ++k)
+        acc[k] = 0;
+    for (int p = lane; p < px; p += 32)
+    {
+        const uint4 v = plane[p];
+#pragma unroll
+        for (int k = 0; k < CB; ++k)
+            acc[k] += byte_of(v, k);
+    }
+#pragma unroll
+    for (int k = 0; k < CB; ++k)
+    {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+            acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], off);
+        acc[k] = requant_dev(acc[k] + px * a.zero_in + a.k_zero, a.lshift, a.rshift, a.mult);
+    }
+    if (lane == 0)
+        *reinterpret_cast<uint4 *>(out + (size_t)warp * CB) = pack16(acc);
 }
 
 __global__ void __launch_bounds__(256)
@@ -194,7 +447,7 @@ relu_u8_kernel(long long n16, const QArgs a, const uint8_t *in, uint8_t *out) //
         for (int k = 0; k < CB; ++k)
         {
             const int x = byte_of(v, k) + a.zero_in;
-            r[k] = requant(x > a.k_zero ? x : a.k_zero, a.lshift, a.rshift, a.mult);
+            r[k] = requant_dev(x > a.k_zero ? x : a.k_zero, a.lshift, a.rshift, a.mult);
         }
         *reinterpret_cast<uint4 *>(out + i * 16) = pack16(r);
     }
@@ -231,6 +484,30 @@ int launch_window(const small_b200_layer *L, const char *name, int max_stride, c
     const long long items = (long long)a.N * (a.C / CB) * a.Ho * a.Wo;
     if (items == 0)
         return SMALL_B200_OK;
+    if (OP == 0 && a.zero_filt == -128 && (a.zero_in == 0 || a.zero_in == -128) && a.Fh * a.Fw <= 64 && a.C <= 2048)
+    {
+        const int quads = (a.Fh * a.Fw + 3) / 4;
+        const size_t smem = (size_t)(a.C / CB) * quads * CB * 4 + (size_t)quads * 4 * sizeof(short2);
+        const unsigned blocks = (unsigned)((items + 255) / 256);
+        const bool sgn = a.zero_in != 0;
+        cudaStream_t st = as_stream(stream);
+        if (quads == 3) // 3x3
+            sgn ? dwconv_u8_dp4a_kernel<true, 3><<<blocks, 256, smem, st>>>(a, in, filt, bias, out)
+                : dwconv_u8_dp4a_kernel<false, 3><<<blocks, 256, smem, st>>>(a, in, filt, bias, out);
+        else if (quads == 1)
+            sgn ? dwconv_u8_dp4a_kernel<true, 1><<<blocks, 256, smem, st>>>(a, in, filt, bias, out)
+                : dwconv_u8_dp4a_kernel<false, 1><<<blocks, 256, smem, st>>>(a, in, filt, bias, out);
+        else
+            sgn ? dwconv_u8_dp4a_kernel<true, 0><<<blocks, 256, smem, st>>>(a, in, filt, bias, out)
+                : dwconv_u8_dp4a_kernel<false, 0><<<blocks, 256, smem, st>>>(a, in, filt, bias, out);
+        return launched("dwconv_u8_dp4a_kernel");
+    }
+    if (OP == 2 && a.Fh == a.H && a.Fw == a.W && !L->pad_t && !L->pad_b && !L->pad_l && !L->pad_r)
+    {
+        const long long warps = (long long)a.N * (a.C / CB);
+        global_avgpool_u8_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, as_stream(stream)>>>(a, in, out);
+        return launched("global_avgpool_u8_kernel");
+    }
     window_u8_kernel<OP><<<(unsigned)((items + 255) / 256), 256, 0, as_stream(stream)>>>(a, in, filt, bias, out);
     return launched(name);
 }
@@ -262,6 +539,30 @@ int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uin
     QArgs a; fill(L, a, true);
     if (a.N == 0 || a.Ho == 0 || a.Wo == 0)
         return SMALL_B200_OK;
+    if (a.C == 1 && a.zero_filt == -128 && (a.zero_in == 0 || a.zero_in == -128))
+    {
+        // one-channel image: rows of the window are words of the (zero-padded) image
+        const int quads = (a.Fw + 3) / 4;
+        const int pitch = ((a.W + L->pad_l + L->pad_r + 4 * quads + 8) + 3) & ~3; // room for the unaligned read
+        const int prow = a.H + L->pad_t + L->pad_b + 1;
+        const size_t smem = (size_t)(a.K / CB) * a.Fh * quads * CB * 4 + (size_t)C1_IMGS * prow * pitch;
+        if (smem <= 160 * 1024)
+        {
+            static bool configured = false;
+            if (!configured)
+            {
+                SB_CUDA(cudaFuncSetAttribute(conv2d_u8_c1_dp4a_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+                SB_CUDA(cudaFuncSetAttribute(conv2d_u8_c1_dp4a_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+                configured = true;
+            }
+            const unsigned blocks = (unsigned)((a.N + C1_IMGS - 1) / C1_IMGS);
+            if (a.zero_in == 0)
+                conv2d_u8_c1_dp4a_kernel<false><<<blocks, 256, smem, as_stream(stream)>>>(a, in, filt, bias, out, pitch, prow);
+            else
+                conv2d_u8_c1_dp4a_kernel<true><<<blocks, 256, smem, as_stream(stream)>>>(a, in, filt, bias, out, pitch, prow);
+            return launched("conv2d_u8_c1_dp4a_kernel");
+        }
+    }
     dim3 grid((a.Ho * a.Wo + 127) / 128, a.K / CB, a.N);
     conv2d_u8_direct_kernel<<<grid, 128, 0, as_stream(stream)>>>(a, in, filt, bias, out);
     return launched("conv2d_u8_direct_kernel");

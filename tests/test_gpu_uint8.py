@@ -143,3 +143,91 @@ def test_full_batch_pointwise_matches_single_images(oracle):
     O1 = _out(K * H * W, q)
     S.Conv2D(1, 1, 1, 0, 0, 0, 0, K, C, H, W, qbuf(x[2048], q.zero_in), F, O1)
     assert np.array_equal(O1.numpy(), got[2048])
+
+
+# The dp4a fast paths (filter zero point -128, input zero point 0 or -128) against the oracle.
+FAST_DW_CASES = [
+    # C, H, W, Fh, Fw, stride, pads
+    (64, 25, 5, 3, 3, 1, "same"),        # DS-CNN depthwise
+    (16, 9, 12, 3, 3, 2, "same"),
+    (32, 11, 7, 5, 5, 1, (2, 2, 2, 2)),  # 25 taps: 7 groups of four, the last one partial
+    (48, 6, 6, 2, 2, 1, (0, 1, 0, 1)),
+    (16, 8, 8, 1, 1, 1, "valid"),
+    (128, 6, 6, 3, 3, 1, "same"),
+]
+
+
+@pytest.mark.parametrize("c", FAST_DW_CASES, ids=lambda c: "C{}_{}x{}_k{}x{}_s{}".format(*c[:6]))
+@pytest.mark.parametrize("zero_in", [0, -128])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_depthwise_u8_dp4a_path(oracle, c, zero_in, with_bias):
+    import torch
+    C, H, W, Fh, Fw, s, pm = c
+    pads = same_pads(H, W, Fh, Fw, s) if pm == "same" else (0, 0, 0, 0) if pm == "valid" else pm
+    N = 3
+    rng = np.random.default_rng(abs(hash((c, zero_in, with_bias))) % (1 << 31))
+    top = Fh * Fw * 128.0 * 128.0 * 0.6
+    rshift = int(np.clip(np.floor(-np.log2(255.0 / top)), 0, 30))
+    q = Quant(zero_in, -128, 0, rshift, int(255.0 / top * 2.0 ** (31 + rshift)), 0)
+    x = P.pack_activation(rng.integers(0, 256, (N, C, H, W)).astype(np.uint8))
+    w = P.pack_dw_filter(rng.integers(0, 256, (C, Fh, Fw)).astype(np.uint8))
+    bias = rng.integers(-4096, 4097, C).astype(np.int32) if with_bias else None
+    sh = shape(C, C, H, W, Fh, Fw, s, pads, CB)
+    ho, wo = sh.out_hw()
+    I, F, O = qbuf(x, zero_in), qbuf(w, -128), _out(N * C * ho * wo, q)
+    if with_bias:
+        S.DepthwiseConv2D_Bias_Activation(Fh, Fw, s, *pads, C, H, W, I, F, torch.from_numpy(bias).cuda(), O, batch=N)
+    else:
+        S.DepthwiseConv2D(Fh, Fw, s, *pads, C, H, W, I, F, O, batch=N)
+    want = np.stack([oracle.conv2d_u8(sh, q, x[n], w, bias=bias, depthwise=True) for n in range(N)])
+    assert np.array_equal(O.numpy().reshape(N, -1), want)
+    assert 0 < want.mean() < 255 and want.min() < want.max()
+
+
+FAST_C1_CASES = [
+    # K, H, W, Fh, Fw, stride, pads, batch
+    (64, 49, 10, 10, 4, 2, "same", 9),    # DS-CNN stem; 9 images = two full CTAs of 4 and one of 1
+    (16, 12, 10, 3, 3, 1, "same", 2),
+    (32, 9, 14, 5, 7, 2, "same", 5),      # 7 taps per row: two words, the second partial
+    (16, 8, 8, 1, 1, 1, "valid", 1),
+    (16, 7, 9, 2, 5, 1, (1, 0, 2, 2), 4),
+]
+
+
+@pytest.mark.parametrize("c", FAST_C1_CASES, ids=lambda c: "K{}_{}x{}_k{}x{}_s{}_n{}".format(*c[:6], c[7]))
+@pytest.mark.parametrize("zero_in", [0, -128])
+def test_conv2d_u8_one_channel_dp4a_path(oracle, c, zero_in):
+    import torch
+    K, H, W, Fh, Fw, s, pm, N = c
+    pads = same_pads(H, W, Fh, Fw, s) if pm == "same" else (0, 0, 0, 0) if pm == "valid" else pm
+    rng = np.random.default_rng(abs(hash((c, zero_in))) % (1 << 31))
+    top = Fh * Fw * 128.0 * 128.0 * 0.5
+    rshift = int(np.clip(np.floor(-np.log2(255.0 / top)), 0, 30))
+    q = Quant(zero_in, -128, 0, rshift, int(255.0 / top * 2.0 ** (31 + rshift)), 0)
+    x = P.pack_activation(rng.integers(0, 256, (N, 1, H, W)).astype(np.uint8))
+    w = P.pack_conv_filter(rng.integers(0, 256, (K, 1, Fh, Fw)).astype(np.uint8))
+    bias = rng.integers(-4096, 4097, K).astype(np.int32)
+    sh = shape(1, K, H, W, Fh, Fw, s, pads, CB)
+    ho, wo = sh.out_hw()
+    I, F, O = qbuf(x, zero_in), qbuf(w, -128), _out(N * K * ho * wo, q)
+    S.Conv2D_Bias_Activation(Fh, Fw, s, *pads, K, 1, H, W, I, F, torch.from_numpy(bias).cuda(), O, batch=N)
+    want = np.stack([oracle.conv2d_u8(sh, q, x[n], w, bias=bias) for n in range(N)])
+    assert np.array_equal(O.numpy().reshape(N, -1), want)
+    assert want.min() < want.max()
+
+
+@pytest.mark.parametrize("shape_", [(64, 25, 5), (16, 3, 3), (256, 7, 9)])
+@pytest.mark.parametrize("zero_in", [0, -128, 7])
+def test_global_average_pool_u8(oracle, shape_, zero_in):
+    C, H, W = shape_
+    N = 5
+    rng = np.random.default_rng(C * H + W + zero_in + 1000)
+    x = P.pack_activation(rng.integers(0, 256, (N, C, H, W)).astype(np.uint8))
+    rshift = int(np.floor(np.log2(H * W)))  # multiplier = 2^(31 + rshift) / taps lies in [2^30, 2^31)
+    q = Quant(zero_in, 0, 0, rshift, int(2.0 ** (31 + rshift) / (H * W) * 0.99), 0)
+    sh = shape(C, C, H, W, H, W, 1, (0, 0, 0, 0), CB)
+    I, O = qbuf(x, zero_in), _out(N * C, q)
+    S.AveragePool2D(H, W, 1, 0, 0, 0, 0, C, H, W, I, O, batch=N)
+    want = np.stack([oracle.pool2d_u8(sh, q, x[n], average=True) for n in range(N)])
+    assert np.array_equal(O.numpy().reshape(N, -1), want)
+    assert want.min() < want.max()
