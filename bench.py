@@ -32,6 +32,12 @@ WORKLOADS = {
                        desc="Tiny-YOLOv2 fp32 3x416x416, 512 images over 8 GPUs = 64 per GPU"),
     "dscnn": dict(dtype="u8", per_gpu_batch=4096, seed=1,
                   desc="DS-CNN uint8 1x49x10, batch 4096 per GPU"),
+    # the other configurations (parity-test cases; benchable on request)
+    "resnet8": dict(dtype="f32", per_gpu_batch=1024, seed=0, desc="ResNet-8 fp32 3x32x32, batch 1024 per GPU"),
+    "mobilenet": dict(dtype="f32", per_gpu_batch=2048, seed=2,
+                      desc="MobileNet-v1 x0.25 fp32 3x96x96, batch 2048 per GPU"),
+    "mobilenet_u8": dict(dtype="u8", per_gpu_batch=2048, seed=2,
+                         desc="MobileNet-v1 x0.25 uint8 3x96x96, batch 2048 per GPU"),
 }
 METRIC = "inferences/s"
 
@@ -47,7 +53,13 @@ def load_peaks():
 
 def make_layers(workload):
     from smallframework_b200 import networks
-    return networks.tiny_yolov2(seed=4) if workload == "tinyyolov2" else networks.ds_cnn(seed=1)
+    if workload == "tinyyolov2":
+        return networks.tiny_yolov2(seed=4)
+    if workload == "dscnn":
+        return networks.ds_cnn(seed=1)
+    if workload == "resnet8":
+        return networks.resnet8(seed=0)
+    return networks.mobilenet_v1_025(seed=2, dtype="u8" if workload.endswith("u8") else "f32")
 
 
 def make_input(workload, layers, batch, seed):
@@ -323,6 +335,8 @@ def run_gpu_arm(args):
         line.update(per_layer_report(chain, layers, batch, wl, clocks, torch))
     if world > 1:
         dist.barrier()
+    if args.workload not in ("tinyyolov2", "dscnn"):
+        args.no_cpu_baseline = True  # the reference arm times the two headline chains only
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
             line["cpu_baseline"] = time_reference(args.workload, layers, os.cpu_count() or 1)
@@ -384,7 +398,8 @@ def kernel_class(chain, i, L, dtype):
             return ("conv2d_first_f32_kernel (FFMA)" if L["C"] < 16 else "conv2d_f32_kernel (FFMA)"), "ffma"
         pw = (L["Fh"] == 1 and L["Fw"] == 1 and L["stride"] == 1 and L["C"] % 32 == 0 and L["C"] <= 256)
         return ("pw_u8_tc_kernel (tcgen05 kind::i8)", "i8") if pw else ("conv2d_u8_direct_kernel", "cuda_u8")
-    return {"dwconv": "depthwise", "maxpool": "max pool", "avgpool": "average pool"}[L["op"]], "stream"
+    return {"dwconv": "depthwise", "maxpool": "max pool", "avgpool": "average pool", "softmax": "softmax",
+            "alias": "alias"}[L["op"]], "stream"
 
 
 def per_layer_report(chain, layers, batch, wl, clocks, torch):
@@ -407,6 +422,8 @@ def per_layer_report(chain, layers, batch, wl, clocks, torch):
     rows = []
     plan = chain.io_plan()
     for i, L in enumerate(layers):
+        if L["op"] == "alias":
+            continue
         if plan[i] is None:
             rows.append({"layer": L.get("name", L["op"]), "kernel": "fused into " + layers[chain.fused_into[i]]["name"],
                          "ms": 0.0, "tflops": 0.0, "gbs": 0.0, "bound": "fused", "roofline_frac": None})

@@ -136,6 +136,118 @@ def ds_cnn(seed=1, calib_images=8):
     return layers
 
 
+# --------------------------------------------------------------------------- ResNet-8 fp32
+def resnet8(seed=0, size=32):
+    """ResNet-8 of the MLCommons-Tiny image-classification model the reference's
+    include/small/models/Resnet8Tiny.hpp builds: stem conv 3x3 16ch + ReLU; three residual stages
+    (16 ch stride 1 identity shortcut; 32 ch stride 2 and 64 ch stride 2 with 1x1 stride-2
+    convolution shortcuts), each conv3x3 + ReLU, conv3x3, add, ReLU; global average pool;
+    dense 64 -> 10 (a 1x1 convolution on the 1x1 image); softmax.  The add is done the way the
+    reference does it (Resnet8Tiny.hpp:284-288): the second convolution is a PartialConv2D that
+    accumulates onto the shortcut's buffer, with the ReLU in the same kernel here.
+    Layers name their buffers (src/dst): this list is a small DAG.  He-normal weights, biases 0."""
+    rng = np.random.default_rng(seed)
+    L, h = [], size
+    conv = lambda name, c, k, hh, f, s, act, src, dst, acc=0: dict(
+        op="conv", name=name, C=c, K=k, H=hh, W=hh, Fh=f, Fw=f, stride=s, pads=_same(hh, hh, f, f, s),
+        act=act, slope=0.0, w=_he(rng, (k, c, f, f), c * f * f), b=None, src=src, dst=dst, accumulate=acc)
+    L.append(conv("stem", 3, 16, h, 3, 1, 1, "in", "x"))
+    # stage 1: identity shortcut -> accumulate onto the stage input itself
+    L.append(conv("s1a", 16, 16, h, 3, 1, 1, "x", "a"))
+    L.append(conv("s1b", 16, 16, h, 3, 1, 1, "a", "x", acc=1))
+    c = 16
+    for st, k in ((2, 32), (3, 64)):
+        L.append(conv(f"s{st}a", c, k, h, 3, 2, 1, "x", "a"))
+        L.append(conv(f"s{st}sc", c, k, h, 1, 2, 0, "x", "y"))
+        h //= 2
+        L.append(conv(f"s{st}b", k, k, h, 3, 1, 1, "a", "y", acc=1))
+        L.append(dict(op="alias", name=f"s{st}out", src="y", dst="x", C=k, K=k, H=h, W=h, Fh=1, Fw=1, stride=1,
+                      pads=(0, 0, 0, 0)))
+        c = k
+    L.append(dict(op="avgpool", name="avgpool", C=c, K=c, H=h, W=h, Fh=h, Fw=h, stride=1, pads=(0, 0, 0, 0),
+                  src="x", dst="p"))
+    L.append(dict(op="conv", name="dense", C=c, K=10, H=1, W=1, Fh=1, Fw=1, stride=1, pads=(0, 0, 0, 0), act=0,
+                  slope=0.0, w=_he(rng, (10, c, 1, 1), c), b=None, src="p", dst="d"))
+    L.append(dict(op="softmax", name="softmax", C=10, K=10, H=1, W=1, Fh=1, Fw=1, stride=1, pads=(0, 0, 0, 0),
+                  src="d", dst="o"))
+    return L
+
+
+# --------------------------------------------------------------------------- MobileNet-v1 x0.25
+def mobilenet_v1_025(seed=2, size=96, dtype="f32"):
+    """MobileNet-v1 width 0.25 (include/small/models/MobileNetTiny.hpp): stem conv 3x3 8ch stride 2;
+    13 depthwise-separable blocks (channels 16,32,32,64,64,128,128x5,256,256; stride 2 at blocks
+    2,4,6,12), every convolution followed by ReLU; average pool 3x3; dense 256 -> 2; softmax (fp32).
+    uint8: zero points as in ds_cnn(), multipliers calibrated on a few seeded images."""
+    rng = np.random.default_rng(seed)
+    chans = [16, 32, 32, 64, 64, 128, 128, 128, 128, 128, 128, 256, 256]
+    strides = [1, 2, 1, 2, 1, 2, 1, 1, 1, 1, 1, 2, 1]
+    u8 = dtype == "u8"
+    cur = rng.integers(0, 256, (2, 3, size, size)).astype(np.uint8) if u8 else None
+    L = []
+
+    def add(op, name, C_, K, H, Fh, s, zi):
+        nonlocal cur
+        pads = _same(H, H, Fh, Fh, s)
+        dw = op == "dwconv"
+        wshape = (C_, Fh, Fh) if dw else (K, C_, Fh, Fh)
+        d = dict(op=op, name=name, C=C_, K=K, H=H, W=H, Fh=Fh, Fw=Fh, stride=s, pads=pads, act=0 if u8 else 1,
+                 slope=0.0)
+        if u8:
+            w = rng.integers(0, 256, wshape).astype(np.uint8)
+            b = rng.integers(-1024, 1025, K).astype(np.int32)
+            acc = _calibrate(cur, w, b, zi, -128, s, pads, dw)
+            top = max(float(np.percentile(acc, 99.9)), 1.0)
+            lshift, rshift, mult = _requant_params(255.0 / top)
+            d.update(w=w, b=b, q=dict(zero_in=zi, zero_filt=-128, lshift=lshift, rshift=rshift, multiplier=mult))
+            cur = np.clip(np.rint(acc * (mult * 2.0 ** (-31 - rshift))), 0, 255).astype(np.uint8)
+        else:
+            d.update(w=_he(rng, wshape, (1 if dw else C_) * Fh * Fh), b=None)
+        L.append(d)
+
+    h = size
+    add("conv", "stem", 3, 8, h, 3, 2, -128)
+    h //= 2
+    c = 8
+    for i, (k, s) in enumerate(zip(chans, strides)):
+        add("dwconv", f"dw{i + 1}", c, c, h, 3, s, 0)
+        h //= s
+        add("conv", f"pw{i + 1}", c, k, h, 1, 1, 0)
+        c = k
+    if u8:
+        lshift, rshift, mult = _requant_params(1.0 / (h * h))
+        L.append(dict(op="avgpool", name="avgpool", C=c, K=c, H=h, W=h, Fh=h, Fw=h, stride=1, pads=(0, 0, 0, 0),
+                      q=dict(zero_in=0, zero_filt=0, lshift=lshift, rshift=rshift, multiplier=mult)))
+        cur = np.clip(np.rint(cur.astype(np.float64).sum(axis=(2, 3), keepdims=True) / (h * h)), 0, 255).astype(np.uint8)
+        add("conv", "dense", c, 2, 1, 1, 1, 0)
+    else:
+        L.append(dict(op="avgpool", name="avgpool", C=c, K=c, H=h, W=h, Fh=h, Fw=h, stride=1, pads=(0, 0, 0, 0)))
+        L.append(dict(op="conv", name="dense", C=c, K=2, H=1, W=1, Fh=1, Fw=1, stride=1, pads=(0, 0, 0, 0), act=0,
+                      slope=0.0, w=_he(rng, (2, c, 1, 1), c), b=None))
+        L.append(dict(op="softmax", name="softmax", C=2, K=2, H=1, W=1, Fh=1, Fw=1, stride=1, pads=(0, 0, 0, 0)))
+    return L
+
+
+# --------------------------------------------------------------------------- YOLOv3-tiny layer sweep
+def yolov3_tiny_convs(seed=3, size=416):
+    """The 13 convolution layers of YOLOv3-tiny at 416x416 (test/cfg_data/yolov3-tiny.cfg:26-173 of
+    the reference), each a one-layer list to be timed alone: inputs U[-1,1), weights N(0, 0.05),
+    bias + LeakyReLU(0.1) except the two linear 1x1 heads.  255 output channels pad to 256."""
+    rng = np.random.default_rng(seed)
+    s = size
+    spec = [(3, 16, s, 3, 2), (16, 32, s // 2, 3, 2), (32, 64, s // 4, 3, 2), (64, 128, s // 8, 3, 2),
+            (128, 256, s // 16, 3, 2), (256, 512, s // 32, 3, 2), (512, 1024, s // 32, 3, 2),
+            (1024, 256, s // 32, 1, 2), (256, 512, s // 32, 3, 2), (512, 255, s // 32, 1, 0),
+            (256, 128, s // 32, 1, 2), (384, 256, s // 16, 3, 2), (256, 255, s // 16, 1, 0)]
+    out = []
+    for i, (c, k, h, f, act) in enumerate(spec):
+        out.append([dict(op="conv", name=f"y3t{i}", C=c, K=k, H=h, W=h, Fh=f, Fw=f, stride=1,
+                         pads=_same(h, h, f, f, 1), act=act, slope=0.1,
+                         w=rng.normal(0.0, 0.05, (k, c, f, f)).astype(np.float32),
+                         b=rng.uniform(-0.1, 0.1, k).astype(np.float32))])
+    return out
+
+
 def input_shape(layers):
     L = layers[0]
     return (L["C"], L["H"], L["W"])
@@ -151,6 +263,32 @@ def padded(k):
     return -(-k // CB) * CB
 
 
+def padded_params(L, first, dtype):
+    """(packed filter, bias) of a conv / dwconv layer with channel counts rounded up to the block
+    of 16 the way include/small/Conv2DLayer.hpp:393-404 pads odd channel counts: filters of padded
+    OUTPUT channels and weights of padded INPUT channels contribute nothing (zero for fp32; for
+    uint8 the byte whose shifted value w + zero_filt is 0), padded biases are 0."""
+    kp = padded(L["K"])
+    zero_w = 0
+    if dtype == "u8":
+        zf = L["q"]["zero_filt"]
+        zero_w = np.uint8(-zf) if -zf in range(256) else 0
+    if L["op"] == "conv":
+        cp = L["C"] if first else padded(L["C"])
+        w = np.full((kp, cp) + L["w"].shape[2:], zero_w, L["w"].dtype)
+        w[:L["K"], :L["C"]] = L["w"]
+        wt = pack_conv_filter(w)
+    else:
+        w = np.full((kp,) + L["w"].shape[1:], zero_w, L["w"].dtype)
+        w[:L["K"]] = L["w"]
+        wt = pack_dw_filter(w)
+    b = None
+    if L.get("b") is not None:
+        b = np.zeros(kp, L["b"].dtype)
+        b[:L["K"]] = L["b"]
+    return wt, b
+
+
 def algorithmic_work(L, elt):
     """(flops, bytes) of one image: 2*Ho*Wo*K*C*Fh*Fw for a dense convolution, all taps
     counted; bytes = input + output activations plus weights and bias once per launch
@@ -163,6 +301,8 @@ def algorithmic_work(L, elt):
     elif L["op"] == "dwconv":
         flops = 2 * ho * wo * L["C"] * taps
         wbytes = L["C"] * taps * elt + L["C"] * 4
+    elif L["op"] in ("softmax", "alias"):
+        flops, wbytes = ho * wo * L["C"], 0
     else:
         flops = ho * wo * L["C"] * taps
         wbytes = 0
@@ -202,30 +342,32 @@ class Chain:
             ho, wo = _out_hw(L)
             kp = padded(L["K"])
             max_act = max(max_act, batch * kp * ho * wo)
+            if L["op"] == "alias":
+                self.params.append((None, None))
+                continue
             wt = bs = None
-            if L["op"] == "conv":
-                wpad = np.zeros((kp,) + L["w"].shape[1:], L["w"].dtype)
-                wpad[:L["K"]] = L["w"]
-                if dtype == "u8" and kp != L["K"]:
-                    # a padded filter must contribute nothing: byte value = -zero_filt
-                    wpad[L["K"]:] = np.uint8(-L["q"]["zero_filt"]) if -L["q"]["zero_filt"] in range(256) else 0
-                wt = torch.from_numpy(pack_conv_filter(wpad)).to(self.dev)
-            elif L["op"] == "dwconv":
-                wt = torch.from_numpy(pack_dw_filter(L["w"])).to(self.dev)
-            if L.get("b") is not None:
-                bp = np.zeros(kp, L["b"].dtype)
-                bp[:L["K"]] = L["b"]
-                bs = torch.from_numpy(bp).to(self.dev)
+            if L["op"] in ("conv", "dwconv"):
+                w_np, b_np = padded_params(L, len(self.params) == 0, dtype)
+                wt = torch.from_numpy(w_np).to(self.dev)
+                if b_np is not None:
+                    bs = torch.from_numpy(b_np).to(self.dev)
             self.params.append((wt, bs))
         self.bufs = [torch.zeros(max_act, dtype=self.tdtype, device=self.dev) for _ in range(2)]
+        # layers that name their buffers (a small DAG, e.g. residual stages) get one tensor per name
+        self.named = {"in": self.x}
+        for L in layers:
+            for key in ("src", "dst"):
+                if key in L and L[key] not in self.named:
+                    self.named[L[key]] = torch.zeros(max_act, dtype=self.tdtype, device=self.dev)
         # tensor-core fp32 path: filters re-laid once (hi + lo copies)
         self.prepared = [None] * len(layers)
         if dtype == "f32" and tensor_core:
             for i, L in enumerate(layers):
                 if L["op"] != "conv" or i == 0:
                     continue
-                if tensor_core == "auto" and L["C"] < self.TC_MIN_CHANNELS:
-                    continue
+                ho, wo = _out_hw(L)
+                if tensor_core == "auto" and (L["C"] < self.TC_MIN_CHANNELS or ho * wo < 32):
+                    continue  # narrow layers and 1x1 images (dense heads) stay on the CUDA cores
                 d = self._desc(L, padded(L["C"]))
                 if not lib().small_b200_conv2d_f32_tf32x3_supported(C.byref(d)):
                     continue
@@ -239,7 +381,7 @@ class Chain:
         if dtype == "f32" and fuse_pool:
             for i in range(len(layers) - 1):
                 L, Pn = layers[i], layers[i + 1]
-                if L["op"] != "conv" or Pn["op"] != "maxpool" or self.prepared[i] is not None:
+                if L["op"] != "conv" or Pn["op"] != "maxpool" or self.prepared[i] is not None or "src" in L:
                     continue
                 dc = self._desc(L, L["C"] if i == 0 else padded(L["C"]))
                 dp = self._desc(Pn, padded(Pn["C"]))
@@ -254,7 +396,7 @@ class Chain:
         t, b, l, r = L["pads"]
         q = L.get("q", {})
         return Layer(self.batch, cin, padded(L["K"]), L["H"], L["W"], L["Fh"], L["Fw"], L["stride"],
-                     t, b, l, r, 0, L.get("act", 0), L.get("slope", 0.0),
+                     t, b, l, r, L.get("accumulate", 0), L.get("act", 0), L.get("slope", 0.0),
                      q.get("zero_in", 0), q.get("zero_filt", 0), q.get("lshift", 0),
                      q.get("rshift", 0), q.get("multiplier", 0), 0)
 
@@ -282,6 +424,10 @@ class Chain:
             check(getattr(l, f"small_b200_maxpool2d_{sfx}")(C.byref(d), p(src), p(dst), stream))
         elif L["op"] == "avgpool":
             check(getattr(l, f"small_b200_avgpool2d_{sfx}")(C.byref(d), p(src), p(dst), stream))
+        elif L["op"] == "softmax":
+            check(l.small_b200_softmax_f32(self.batch, cin * L["H"] * L["W"], p(src), p(dst), stream))
+        elif L["op"] == "alias":
+            pass  # the next layers read `src` under the name `dst`
         else:
             raise ValueError(L["op"])
 
@@ -289,9 +435,16 @@ class Chain:
         """(source, destination) tensors of every layer in the order enqueue() runs them;
         None for a layer that its producer absorbs."""
         plan, src = [], self.x
-        for i in range(len(self.layers)):
+        names = dict(self.named)
+        for i, L in enumerate(self.layers):
             if i in self.fused_into:
                 plan.append(None)  # its producer wrote the pooled tensor
+                continue
+            if "src" in L:
+                if L["op"] == "alias":
+                    names[L["dst"]] = names[L["src"]]
+                plan.append((names[L["src"]], names[L["dst"]]))
+                src = names[L["dst"]]
                 continue
             dst = self.bufs[1] if src is self.bufs[0] else self.bufs[0]
             plan.append((src, dst))

@@ -38,33 +38,33 @@ def oracle_conv_batch(oracle, sh, xs, wp, bias=None, act=0, slope=0.0, seed=None
 
 def oracle_chain(oracle, layers, x_packed, dtype="f32"):
     """One image through a layer list (smallframework_b200.networks format) on the oracle,
-    blocking 16, padded output channels like the executor."""
-    from smallframework_b200.networks import padded
+    blocking 16, padded output channels like the executor.  Layers that name their buffers
+    (src / dst, residual stages) read and write a dictionary of tensors; `accumulate` seeds the
+    convolution with the destination's content (PartialConv2D)."""
+    from smallframework_b200.networks import padded, padded_params
     cur = x_packed
+    named = {"in": x_packed}
     for i, L in enumerate(layers):
+        if "src" in L:
+            cur = named[L["src"]]
         cin = L["C"] if i == 0 else padded(L["C"])
         kp = padded(L["K"])
         sh = shape(cin, kp, L["H"], L["W"], L["Fh"], L["Fw"], L["stride"], L["pads"], CB)
         if L["op"] in ("conv", "dwconv"):
             dw = L["op"] == "dwconv"
-            if dw:
-                w = P.pack_dw_filter(L["w"])
-            else:
-                wp = np.zeros((kp,) + L["w"].shape[1:], L["w"].dtype)
-                wp[:L["K"]] = L["w"]
-                if dtype == "u8" and kp != L["K"]:
-                    wp[L["K"]:] = np.uint8(-L["q"]["zero_filt"])
-                w = P.pack_conv_filter(wp)
-            b = None
-            if L.get("b") is not None:
-                b = np.zeros(kp, L["b"].dtype); b[:L["K"]] = L["b"]
+            w, b = padded_params(L, i == 0, dtype)
             if dtype == "f32":
+                seed = named[L["dst"]].copy() if L.get("accumulate") else None
                 cur = oracle.conv2d_f32(sh, cur, w, bias=b, act=L.get("act", 0), slope=L.get("slope", 0.0),
-                                        depthwise=dw)
+                                        out=seed, depthwise=dw)
             else:
                 q = L["q"]
                 cur = oracle.conv2d_u8(sh, Quant(q["zero_in"], q["zero_filt"], q["lshift"], q["rshift"],
                                                  q["multiplier"], 0), cur, w, bias=b, depthwise=dw)
+        elif L["op"] == "softmax":
+            cur = oracle.softmax_f32(cin, L["H"], L["W"], CB, cur)
+        elif L["op"] == "alias":
+            pass
         else:
             avg = L["op"] == "avgpool"
             if dtype == "f32":
@@ -73,4 +73,6 @@ def oracle_chain(oracle, layers, x_packed, dtype="f32"):
                 q = L["q"] if "q" in L else dict(zero_in=0, zero_filt=0, lshift=0, rshift=0, multiplier=1 << 30)
                 cur = oracle.pool2d_u8(sh, Quant(q["zero_in"], 0, q["lshift"], q["rshift"], q["multiplier"], 0),
                                        cur, average=avg)
+        if "dst" in L:
+            named[L["dst"]] = cur
     return cur
