@@ -130,27 +130,41 @@ __device__ __forceinline__ uint32_t pack4_sat(int32_t r0, int32_t r1, int32_t r2
     asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(r1), "r"(r0), "r"(hi));
     return d;
 }
+// Four accumulators -> four output bytes.  The inlined path covers a positive multiplier with
+// rshift >= 2 (every quantiser in practice): the shift by 30 + rshift then only needs the high word
+// of the product.  Everything else goes through one out-of-line routine so that the unrolled
+// epilogues carry a single copy of the arithmetic.
+static __device__ __noinline__ uint32_t requant_pack4_general(int32_t a0, int32_t a1, int32_t a2, int32_t a3,
+                                                              int32_t lshift, int32_t rshift, int32_t mult)
+{
+    return pack4_sat(requant(a0, lshift, rshift, mult), requant(a1, lshift, rshift, mult),
+                     requant(a2, lshift, rshift, mult), requant(a3, lshift, rshift, mult));
+}
+__device__ __forceinline__ uint32_t requant_pack4(int32_t a0, int32_t a1, int32_t a2, int32_t a3, int32_t lshift,
+                                                  int32_t rshift, int32_t mult)
+{
+    if (mult <= 0 || rshift < 2)
+        return requant_pack4_general(a0, a1, a2, a3, lshift, rshift, mult);
+    int32_t r[4] = {a0, a1, a2, a3};
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+    {
+        int32_t v = (int32_t)((uint32_t)r[k] << lshift);
+        v = v > 0 ? v : 0;
+        const unsigned long long t = (unsigned long long)(uint32_t)v * (uint32_t)mult + (1ull << 30);
+        const uint32_t u = (uint32_t)(t >> 32) >> (rshift - 2);
+        r[k] = (int32_t)(u >> 1) - (int32_t)(u & 1u);
+    }
+    return pack4_sat(r[0], r[1], r[2], r[3]);
+}
 // 16 accumulators -> 16 output bytes
 __device__ __forceinline__ uint4 requant_pack16(const int32_t *acc, int32_t lshift, int32_t rshift, int32_t mult)
 {
-    int32_t r[16];
-    if (mult <= 0)
-    {
-#pragma unroll
-        for (int k = 0; k < 16; ++k)
-            r[k] = requant_general(acc[k], lshift, rshift, mult);
-    }
-    else
-    {
-#pragma unroll
-        for (int k = 0; k < 16; ++k)
-            r[k] = requant_raw(acc[k], lshift, rshift, mult);
-    }
     uint4 o;
-    o.x = pack4_sat(r[0], r[1], r[2], r[3]);
-    o.y = pack4_sat(r[4], r[5], r[6], r[7]);
-    o.z = pack4_sat(r[8], r[9], r[10], r[11]);
-    o.w = pack4_sat(r[12], r[13], r[14], r[15]);
+    o.x = requant_pack4(acc[0], acc[1], acc[2], acc[3], lshift, rshift, mult);
+    o.y = requant_pack4(acc[4], acc[5], acc[6], acc[7], lshift, rshift, mult);
+    o.z = requant_pack4(acc[8], acc[9], acc[10], acc[11], lshift, rshift, mult);
+    o.w = requant_pack4(acc[12], acc[13], acc[14], acc[15], lshift, rshift, mult);
     return o;
 }
 #endif

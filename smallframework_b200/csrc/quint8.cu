@@ -323,6 +323,107 @@ dwconv_u8_dp4a_kernel(const QArgs a, const uint8_t *__restrict__ in, const uint8
     *reinterpret_cast<uint4 *>(out + o * CB) = requant_pack16(acc, a.lshift, a.rshift, a.mult);
 }
 
+// Depthwise 3x3, stride 1, a row strip per thread: TW neighbouring outputs of one row x 8
+// channels.  The three taps of a kernel COLUMN of one input pixel are transposed once and serve
+// the (up to) three outputs that see this input column through kw = 0, 1, 2, so a strip of TW
+// outputs costs TW + 2 transposes instead of 3 * TW, and the index arithmetic is paid once per
+// strip.  Filter words in shared memory: [cb][half][kw][8 ch] = (w[0][kw], w[1][kw], w[2][kw], 0)
+// as signed bytes.
+template <bool SIGNED_IN, int TW>
+__global__ void __launch_bounds__(256)
+dwconv3x3_u8_rows_kernel(const QArgs a, const uint8_t *__restrict__ in, const uint8_t *__restrict__ filt,
+                         const int32_t *__restrict__ bias, uint8_t *__restrict__ out, int strips, int pad_t, int pad_l)
+{
+    extern __shared__ __align__(16) unsigned sw[]; // [cb][half][kw][8]
+    const int cbs = a.C / CB;
+    for (int i = threadIdx.x; i < cbs * 48; i += blockDim.x)
+    {
+        const int j = i % 8, kw = (i / 8) % 3, half = (i / 24) % 2, cb = i / 48;
+        const int ch = half * 8 + j;
+        unsigned wv = 0;
+        for (int kh = 0; kh < 3; ++kh)
+            wv |= (unsigned)(filt[(((size_t)cb * 3 + kh) * 3 + kw) * CB + ch] ^ 0x80u) << (8 * kh);
+        sw[i] = wv;
+    }
+    __syncthreads();
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = (long long)a.N * cbs * a.Ho * strips * 2;
+    if (i >= total)
+        return;
+    const int half = (int)(i & 1); i >>= 1;
+    const int strip = (int)(i % strips); i /= strips;
+    const int oh = (int)(i % a.Ho); i /= a.Ho; // i = n * cbs + cb
+    const int cb = (int)(i % cbs);
+    const uint8_t *plane = in + (size_t)i * a.H * a.W * CB + half * 8;
+    const int ow0 = strip * TW;
+    unsigned wreg[3][8];
+    {
+        const uint4 *wp = reinterpret_cast<const uint4 *>(sw + ((size_t)cb * 2 + half) * 24);
+#pragma unroll
+        for (int kw = 0; kw < 3; ++kw)
+        {
+            const uint4 w0 = wp[kw * 2], w1 = wp[kw * 2 + 1];
+            wreg[kw][0] = w0.x; wreg[kw][1] = w0.y; wreg[kw][2] = w0.z; wreg[kw][3] = w0.w;
+            wreg[kw][4] = w1.x; wreg[kw][5] = w1.y; wreg[kw][6] = w1.z; wreg[kw][7] = w1.w;
+        }
+    }
+    int acc[TW][8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+    {
+        const int s0 = a.k_zero + (bias ? bias[cb * CB + half * 8 + j] : 0);
+#pragma unroll
+        for (int o = 0; o < TW; ++o)
+            acc[o][j] = s0;
+    }
+    const int ih0 = oh - pad_t;
+    const bool rok0 = ih0 >= 0 && ih0 < a.H, rok1 = ih0 + 1 >= 0 && ih0 + 1 < a.H, rok2 = ih0 + 2 >= 0 && ih0 + 2 < a.H;
+    const uint8_t *row0 = plane + (size_t)ih0 * a.W * CB, *row1 = row0 + (size_t)a.W * CB, *row2 = row1 + (size_t)a.W * CB;
+#pragma unroll
+    for (int x = 0; x < TW + 2; ++x)
+    {
+        const int xi = ow0 - pad_l + x;
+        if (xi < 0 || xi >= a.W)
+            continue; // a padded column adds nothing
+        uint2 r0 = make_uint2(0u, 0u), r1 = make_uint2(0u, 0u), r2 = make_uint2(0u, 0u);
+        if (rok0) r0 = *reinterpret_cast<const uint2 *>(row0 + (size_t)xi * CB);
+        if (rok1) r1 = *reinterpret_cast<const uint2 *>(row1 + (size_t)xi * CB);
+        if (rok2) r2 = *reinterpret_cast<const uint2 *>(row2 + (size_t)xi * CB);
+        if (SIGNED_IN)
+        {
+            if (rok0) { r0.x ^= 0x80808080u; r0.y ^= 0x80808080u; }
+            if (rok1) { r1.x ^= 0x80808080u; r1.y ^= 0x80808080u; }
+            if (rok2) { r2.x ^= 0x80808080u; r2.y ^= 0x80808080u; }
+        }
+        unsigned c[8];
+        transpose4x4(r0.x, r1.x, r2.x, 0u, c);
+        transpose4x4(r0.y, r1.y, r2.y, 0u, c + 4);
+#pragma unroll
+        for (int kw = 0; kw < 3; ++kw)
+        {
+            const int o = x - kw; // output o of the strip sees input column x through tap column kw
+            if (o >= 0 && o < TW)
+            {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    acc[o][j] = dp4a_in<SIGNED_IN>(c[j], wreg[kw][j], acc[o][j]);
+            }
+        }
+    }
+    uint8_t *orow = out + (((size_t)i * a.Ho + oh) * a.Wo) * CB + half * 8;
+#pragma unroll
+    for (int o = 0; o < TW; ++o)
+    {
+        if (ow0 + o < a.Wo)
+        {
+            uint2 v;
+            v.x = requant_pack4(acc[o][0], acc[o][1], acc[o][2], acc[o][3], a.lshift, a.rshift, a.mult);
+            v.y = requant_pack4(acc[o][4], acc[o][5], acc[o][6], acc[o][7], a.lshift, a.rshift, a.mult);
+            *reinterpret_cast<uint2 *>(orow + (size_t)(ow0 + o) * CB) = v;
+        }
+    }
+}
+
 // Dense convolution of a ONE-channel image (the first layer of the keyword-spotting network):
 // the Fw taps of a kernel row are consecutive bytes of the image, so a row of the window is one
 // (unaligned) 32-bit word per 4 taps and feeds dp4a directly.  A CTA takes IMGS images: it
@@ -484,6 +585,29 @@ int launch_window(const small_b200_layer *L, const char *name, int max_stride, c
     const long long items = (long long)a.N * (a.C / CB) * a.Ho * a.Wo;
     if (items == 0)
         return SMALL_B200_OK;
+    if (OP == 0 && a.zero_filt == -128 && (a.zero_in == 0 || a.zero_in == -128) && a.Fh == 3 && a.Fw == 3 &&
+        a.stride == 1 && a.C <= 2048 && a.Wo >= 3)
+    {
+        // 3x3 stride 1: row strips of 4, 5 or 6 outputs per thread, whichever tiles the width best
+        const bool sgn = a.zero_in != 0;
+        cudaStream_t st = as_stream(stream);
+        int tw = 6, waste = 1 << 30;
+        for (int t = 6; t >= 4; --t)
+        {
+            const int w_ = (a.Wo + t - 1) / t * t - a.Wo;
+            if (w_ < waste) { waste = w_; tw = t; }
+        }
+        const int strips = (a.Wo + tw - 1) / tw;
+        const long long threads = (long long)a.N * (a.C / CB) * a.Ho * strips * 2;
+        const unsigned blocks = (unsigned)((threads + 255) / 256);
+        const size_t smem = (size_t)(a.C / CB) * 48 * 4;
+#define SB_DW_ROWS(S, T) dwconv3x3_u8_rows_kernel<S, T><<<blocks, 256, smem, st>>>(a, in, filt, bias, out, strips, L->pad_t, L->pad_l)
+        if (tw == 6) { if (sgn) SB_DW_ROWS(true, 6); else SB_DW_ROWS(false, 6); }
+        else if (tw == 5) { if (sgn) SB_DW_ROWS(true, 5); else SB_DW_ROWS(false, 5); }
+        else { if (sgn) SB_DW_ROWS(true, 4); else SB_DW_ROWS(false, 4); }
+#undef SB_DW_ROWS
+        return launched("dwconv3x3_u8_rows_kernel");
+    }
     if (OP == 0 && a.zero_filt == -128 && (a.zero_in == 0 || a.zero_in == -128) && a.Fh * a.Fw <= 64 && a.C <= 2048)
     {
         const int quads = (a.Fh * a.Fw + 3) / 4;
