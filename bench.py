@@ -397,9 +397,22 @@ def kernel_class(chain, i, L, dtype):
                 return "conv_tf32x3_kernel (tcgen05 kind::tf32, 3xTF32)", "tf32x3"
             return ("conv2d_first_f32_kernel (FFMA)" if L["C"] < 16 else "conv2d_f32_kernel (FFMA)"), "ffma"
         pw = (L["Fh"] == 1 and L["Fw"] == 1 and L["stride"] == 1 and L["C"] % 32 == 0 and L["C"] <= 256)
-        return ("pw_u8_tc_kernel (tcgen05 kind::i8)", "i8") if pw else ("conv2d_u8_direct_kernel", "cuda_u8")
-    return {"dwconv": "depthwise", "maxpool": "max pool", "avgpool": "average pool", "softmax": "softmax",
-            "alias": "alias"}[L["op"]], "stream"
+        if pw:
+            return "pw_u8_tc_kernel (tcgen05 kind::i8)", "i8"
+        ho, wo = networks_out_hw(L)
+        if L["C"] == 1 and L["Fw"] <= 4 and L["Fh"] <= 16 and ho * wo <= 128 and L["K"] <= 128:
+            return "stem_u8_tc_kernel (im2col in shared memory + tcgen05 kind::i8)", "i8"
+        return "conv2d_u8_direct_kernel", "cuda_u8"
+    if L["op"] == "dwconv" and dtype == "u8":
+        rows = L["Fh"] == 3 and L["Fw"] == 3 and L["stride"] == 1
+        return ("dwconv3x3_u8_rows_kernel (dp4a)" if rows else "dwconv_u8_dp4a_kernel"), "stream"
+    return {"dwconv": "window_f32_kernel (depthwise)", "maxpool": "max pool", "avgpool": "average pool",
+            "softmax": "softmax", "alias": "alias"}[L["op"]], "stream"
+
+
+def networks_out_hw(L):
+    from smallframework_b200.networks import _out_hw
+    return _out_hw(L)
 
 
 def per_layer_report(chain, layers, batch, wl, clocks, torch):

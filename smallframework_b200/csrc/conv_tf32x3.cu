@@ -462,34 +462,41 @@ bool plan(const small_b200_layer *L, TcArgs &a)
     const int tiles256 = (m_img + 255) / 256;
     int npx_first = ((m_img + tiles256 - 1) / tiles256 + 63) / 64 * 64;
     // {patch slots, filter stages (>= 2: a commit serves both rings), raw patch buffers}
+    // {patch slots, filter stages (>= 2: a commit serves both rings), raw patch buffers}
     static const int pref[][3] = {{2, 3, 1}, {2, 2, 1}, {1, 3, 1}, {1, 2, 1}};
-    for (int npx = npx_first; npx >= 64; npx -= 64)
-    {
-        a.NPX = npx;
-        a.px_tiles = (m_img + npx - 1) / npx;
-        const int need = (a.PW - 1) + npx + (a.Fh - 1) * a.PW + (a.Fw - 1);
-        a.PR = (need + a.PW - 1) / a.PW;
-        if (a.PR > 256)
-            continue;
-        const int entries = a.PR * a.PW;
-        a.x_entries = entries + ((2 - entries % 8) + 8) % 8; // % 8 == 2: conflict-free re-layout
-        const size_t raw_part = ((size_t)entries * 64 + 127) & ~(size_t)127;
-        const size_t x_part = ((size_t)a.x_entries * 64 + 127) & ~(size_t)127;
-        const size_t w_part = (size_t)a.MT * 64 * a.group;
-        for (const auto &p : pref)
+    // First pass: only plans that keep two patches in flight (a layer with few channel blocks
+    // per CTA otherwise waits for every patch's load and re-layout), even at a narrower tile;
+    // second pass: anything that fits.
+    for (int pass = 0; pass < 2; ++pass)
+        for (int npx = npx_first; npx >= (pass == 0 ? 128 : 64); npx -= 64)
         {
-            const int xs = p[0] < a.cbs ? p[0] : a.cbs, rs = p[2] < a.cbs ? p[2] : a.cbs;
-            size_t smem = (size_t)rs * raw_part + (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
-            const size_t epilogue = (size_t)npx * (a.MT + 16) * 4; // output staging reuses the buffers
-            if (smem < epilogue)
-                smem = epilogue;
-            if (smem <= limit)
+            a.NPX = npx;
+            a.px_tiles = (m_img + npx - 1) / npx;
+            const int need = (a.PW - 1) + npx + (a.Fh - 1) * a.PW + (a.Fw - 1);
+            a.PR = (need + a.PW - 1) / a.PW;
+            if (a.PR > 256)
+                continue;
+            const int entries = a.PR * a.PW;
+            a.x_entries = entries + ((2 - entries % 8) + 8) % 8; // % 8 == 2: conflict-free re-layout
+            const size_t raw_part = ((size_t)entries * 64 + 127) & ~(size_t)127;
+            const size_t x_part = ((size_t)a.x_entries * 64 + 127) & ~(size_t)127;
+            const size_t w_part = (size_t)a.MT * 64 * a.group;
+            for (const auto &p : pref)
             {
-                a.x_slots = xs; a.w_stages = p[1]; a.raw_slots = rs; a.smem_bytes = (unsigned)smem;
-                return true;
+                const int xs = p[0] < a.cbs ? p[0] : a.cbs, rs = p[2] < a.cbs ? p[2] : a.cbs;
+                if (pass == 0 && xs < (a.cbs < 2 ? a.cbs : 2))
+                    continue;
+                size_t smem = (size_t)rs * raw_part + (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
+                const size_t epilogue = (size_t)npx * (a.MT + 16) * 4; // output staging reuses the buffers
+                if (smem < epilogue)
+                    smem = epilogue;
+                if (smem <= limit)
+                {
+                    a.x_slots = xs; a.w_stages = p[1]; a.raw_slots = rs; a.smem_bytes = (unsigned)smem;
+                    return true;
+                }
             }
         }
-    }
     return false;
 }
 } // namespace

@@ -290,6 +290,205 @@ int launch_pw(const CUtensorMap &map, const PwArgs &a, size_t smem, const uint8_
     kern<<<grid, 192, smem, st>>>(map, a, filt, bias, out, status);
     return launched("pw_u8_tc_kernel");
 }
+
+// ---------------------------------------------------------------------------------------------
+// First layer on a ONE-channel image (the 10x4 stride-2 stem of the keyword-spotting network) as
+// an im2col GEMM on the tensor core: a kernel row of the window is Fw <= 4 consecutive image
+// bytes = one 32-bit word, so pixel p's row of the A tile is Fh words (K = 4*Fh, padded to 64).
+// The epilogue threads build the tile of the NEXT image in shared memory while the MMAs of the
+// current one run.  Both operands enter as signed (or the activations as unsigned) bytes already
+// shifted by their zero points -- zero_filt = -128, zero_in = -128 or 0 -- and padded taps are
+// zero bytes, so the accumulator needs no zero-point correction at all.
+struct StemArgs
+{
+    int N, H, W, Ho, Wo, Fh, Fw, stride, pad_t, pad_l, K;
+    int pitch, prow; // padded image in shared memory
+    int lshift, rshift, mult, k_zero;
+};
+
+template <int NT, bool SIGNED_IN>
+__global__ void __launch_bounds__(160)
+stem_u8_tc_kernel(const StemArgs a, const uint8_t *__restrict__ in, const uint8_t *__restrict__ filt,
+                  const int32_t *__restrict__ bias, uint8_t *__restrict__ out, int *status)
+{
+    constexpr uint32_t TMEM_COLS = 2 * NT < 32 ? 32 : 2 * NT;
+    constexpr int KCH = 4; // 16-byte chunks of K = 64
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ __align__(8) uint64_t built_bar[2], mma_bar[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int seed[NT];
+
+    uint8_t *sA = smem;                                   // [stage][chunk 4][128 px][16 B]
+    uint8_t *sB = sA + 2 * KCH * TILE_M * CB;             // [chunk 4][NT][16 B]
+    uint8_t *sI = sB + KCH * NT * CB;                     // [stage][prow][pitch] padded image
+    const int img_bytes = a.prow * a.pitch;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int px = a.Ho * a.Wo;
+
+    if (warp == 4)
+    {
+        if (lane == 0)
+        {
+            for (int i = 0; i < 2; ++i) { mbar_init(&built_bar[i], 128); mbar_init(&mma_bar[i], 1); }
+            fence_barrier_init();
+        }
+        __syncwarp();
+        tmem_alloc(&tmem_base_s, TMEM_COLS);
+        tmem_relinquish();
+    }
+    // filter -> K-major canonical [chunk][n][16 B]: byte k = kh*4 + kw of output channel n
+    for (int i = tid; i < KCH * NT * CB; i += blockDim.x)
+    {
+        const int b = i % CB, n = (i / CB) % NT, j = i / (CB * NT);
+        const int k = j * CB + b, kh = k >> 2, kw = k & 3;
+        uint8_t v = 0;
+        if (kh < a.Fh && kw < a.Fw && n < a.K) // filter [K/16][1][Fh][Fw][1][16]
+            v = filt[((((size_t)(n / CB)) * a.Fh + kh) * a.Fw + kw) * CB + (n % CB)] ^ 0x80u;
+        sB[i] = v;
+    }
+    for (int i = tid; i < 2 * KCH * TILE_M * CB / 16; i += blockDim.x) // rows of missing pixels / taps stay zero
+        reinterpret_cast<uint4 *>(sA)[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = tid; i < 2 * img_bytes / 4; i += blockDim.x)
+        reinterpret_cast<unsigned *>(sI)[i] = 0u;
+    if (tid < NT)
+        seed[tid] = a.k_zero + ((bias && tid < a.K) ? bias[tid] : 0);
+    fence_proxy_async();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = tmem_base_s;
+    const int first = blockIdx.x, step = gridDim.x;
+
+    if (warp < 4)
+    {
+        const int p = tid;                 // this thread's pixel = TMEM lane
+        const int oh = p / a.Wo, ow = p - oh * a.Wo;
+        auto build = [&](int n, int s) {
+            // image n -> padded signed image -> this pixel's row of the A tile in stage s
+            uint8_t *img = sI + (size_t)s * img_bytes;
+            const uint8_t *src = in + (size_t)n * a.H * a.W;
+            for (int i = tid; i < a.H * a.W; i += 128)
+            {
+                const int h = i / a.W, w = i - h * a.W;
+                const uint8_t v = src[i];
+                img[(h + a.pad_t) * a.pitch + (w + a.pad_l)] = SIGNED_IN ? (uint8_t)(v ^ 0x80u) : v;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (p < px)
+            {
+                const uint8_t *row = img + (oh * a.stride) * a.pitch + ow * a.stride;
+                uint8_t *arow = sA + (size_t)s * KCH * TILE_M * CB + (size_t)p * CB;
+                for (int j = 0; j * 4 < a.Fh; ++j)
+                {
+                    unsigned wv[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                    for (int t = 0; t < 4; ++t)
+                    {
+                        const int kh = j * 4 + t;
+                        if (kh < a.Fh)
+                        {
+                            const uint8_t *pw = row + kh * a.pitch;
+                            const unsigned *al = reinterpret_cast<const unsigned *>(pw - ((size_t)pw & 3));
+                            wv[t] = __funnelshift_r(al[0], al[1], 8 * (unsigned)((size_t)pw & 3));
+                            if (a.Fw < 4)
+                                wv[t] &= (1u << (8 * a.Fw)) - 1u;
+                        }
+                    }
+                    *reinterpret_cast<uint4 *>(arow + (size_t)j * TILE_M * CB) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                }
+            }
+            fence_proxy_async();
+            mbar_arrive(&built_bar[s]);
+        };
+        bool ok = true;
+        if (first < a.N)
+            build(first, 0);
+        int i = 0;
+        for (int n = first; n < a.N && ok; n += step, ++i)
+        {
+            const int s = i & 1;
+            if (n + step < a.N)
+            {
+                // stage s^1 was read by the MMAs of image i-1, whose completion this thread has
+                // already waited for in the previous iteration
+                asm volatile("bar.sync 1, 128;" ::: "memory"); // everyone is done reading image i-1's padded copy
+                build(n + step, s ^ 1);
+            }
+            ok = mbar_wait(&mma_bar[s], (i >> 1) & 1, status, 7);
+            if (!ok)
+                break;
+            tc_fence_after_sync();
+#pragma unroll
+            for (int c0 = 0; c0 < NT; c0 += 16)
+            {
+                uint32_t r[16];
+                tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(s * NT + c0), r);
+                tmem_ld_wait();
+                int q[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                    q[e] = (int)r[e] + seed[c0 + e];
+                const uint4 o = requant_pack16(q, a.lshift, a.rshift, a.mult);
+                if (p < px && c0 < a.K)
+                    *reinterpret_cast<uint4 *>(out + (((size_t)n * (a.K / CB) + c0 / CB) * px + p) * CB) = o;
+            }
+            tc_fence_before_sync();
+        }
+    }
+    else if (warp == 4 && lane == 0)
+    {
+        const uint32_t idesc = make_idesc(2 /*s32*/, SIGNED_IN ? 1u : 0u, 1 /*s8*/, 0 /*A K-major*/, 0 /*B K-major*/,
+                                          TILE_M, NT);
+        const uint32_t sb_ = smem_u32(sB);
+        bool ok = true;
+        int i = 0;
+        for (int n = first; n < a.N && ok; n += step, ++i)
+        {
+            const int s = i & 1;
+            ok = mbar_wait(&built_bar[s], (i >> 1) & 1, status, 8);
+            if (!ok)
+                break;
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(sA + (size_t)s * KCH * TILE_M * CB);
+            for (int j = 0; j < KCH / 2; ++j) // K = 32 per MMA = two 16-byte chunks
+            {
+                const uint64_t da = make_smem_desc(sa + j * 2 * TILE_M * CB, TILE_M * CB, 8 * CB, 0);
+                const uint64_t db = make_smem_desc(sb_ + j * 2 * NT * CB, NT * CB, 8 * CB, 0);
+                tc_mma_i8(tmem + (uint32_t)(s * NT), da, db, idesc, j > 0 ? 1u : 0u);
+            }
+            tc_commit(&mma_bar[s]);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4)
+        tmem_dealloc(tmem, TMEM_COLS);
+}
+
+template <int NT, bool SIGNED_IN>
+int launch_stem(const StemArgs &a, size_t smem, const uint8_t *in, const uint8_t *filt, const int32_t *bias,
+                uint8_t *out, cudaStream_t st)
+{
+    auto kern = stem_u8_tc_kernel<NT, SIGNED_IN>;
+    static bool configured = false;
+    if (!configured)
+    {
+        SB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        configured = true;
+    }
+    int *status = device_status_ptr();
+    if (!status)
+        return fail(SMALL_B200_CUDA_ERROR, "device status word not available");
+    int per_sm = 512 / (2 * NT < 32 ? 32 : 2 * NT);
+    const int by_smem = (int)((220 * 1024) / (smem + 2048));
+    if (per_sm > by_smem) per_sm = by_smem;
+    if (per_sm > 8) per_sm = 8;
+    if (per_sm < 1) per_sm = 1;
+    long long grid = (long long)num_sms() * per_sm;
+    if (grid > a.N) grid = a.N;
+    kern<<<(unsigned)grid, 160, smem, st>>>(a, in, filt, bias, out, status);
+    return launched("stem_u8_tc_kernel");
+}
 } // namespace
 
 namespace sb
@@ -345,6 +544,39 @@ int conv2d_u8_tensor_core(const small_b200_layer *L, const uint8_t *in, const ui
     case 32: return launch_pw<32>(map, a, smem, filt, bias, out, st);
     default: return launch_pw<16>(map, a, smem, filt, bias, out, st);
     }
+}
+} // namespace sb
+
+namespace sb
+{
+// The one-channel first layer on the tensor core; -1 when the shape is not covered.
+int conv2d_u8_one_channel_tc(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt, const int32_t *bias,
+                             uint8_t *out, cudaStream_t st)
+{
+    if (L->C != 1 || L->zero_filt != -128 || (L->zero_in != 0 && L->zero_in != -128))
+        return -1;
+    if (L->Fw > 4 || L->Fh > 16 || L->K % CB != 0 || L->K > 128)
+        return -1;
+    StemArgs a;
+    a.N = L->N; a.H = L->H; a.W = L->W; a.Fh = L->Fh; a.Fw = L->Fw; a.stride = L->stride;
+    a.pad_t = L->pad_t; a.pad_l = L->pad_l; a.K = L->K;
+    a.Ho = out_dim(L->H, L->pad_t, L->pad_b, L->Fh, L->stride);
+    a.Wo = out_dim(L->W, L->pad_l, L->pad_r, L->Fw, L->stride);
+    if (a.Ho * a.Wo > TILE_M || a.Ho * a.Wo <= 0)
+        return -1;
+    if (a.N == 0)
+        return SMALL_B200_OK;
+    a.pitch = ((L->W + L->pad_l + L->pad_r + 12) + 3) & ~3; // room for the unaligned window read
+    a.prow = L->H + L->pad_t + L->pad_b + 1;
+    a.lshift = L->lshift; a.rshift = L->rshift; a.mult = L->multiplier; a.k_zero = L->k_zero;
+    const int nt = L->K <= 64 ? 64 : 128;
+    const size_t smem = 2 * 4 * TILE_M * CB + (size_t)4 * nt * CB + 2 * (size_t)a.prow * a.pitch;
+    if (smem > 96 * 1024)
+        return -1;
+    const bool sgn = L->zero_in != 0;
+    if (nt == 64)
+        return sgn ? launch_stem<64, true>(a, smem, in, filt, bias, out, st) : launch_stem<64, false>(a, smem, in, filt, bias, out, st);
+    return sgn ? launch_stem<128, true>(a, smem, in, filt, bias, out, st) : launch_stem<128, false>(a, smem, in, filt, bias, out, st);
 }
 } // namespace sb
 

@@ -643,6 +643,8 @@ namespace sb
 // the shape is not covered, otherwise a SMALL_B200_* code.
 int conv2d_u8_tensor_core(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
                           const int32_t *bias, uint8_t *out, cudaStream_t st);
+int conv2d_u8_one_channel_tc(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
+                             const int32_t *bias, uint8_t *out, cudaStream_t st);
 }
 
 extern "C"
@@ -663,6 +665,11 @@ int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uin
     QArgs a; fill(L, a, true);
     if (a.N == 0 || a.Ho == 0 || a.Wo == 0)
         return SMALL_B200_OK;
+    {
+        const int tc1 = conv2d_u8_one_channel_tc(L, in, filt, bias, out, as_stream(stream));
+        if (tc1 >= 0)
+            return tc1;
+    }
     if (a.C == 1 && a.zero_filt == -128 && (a.zero_in == 0 || a.zero_in == -128))
     {
         // one-channel image: rows of the window are words of the (zero-padded) image
