@@ -11,6 +11,7 @@
 
 #include <stdint.h>
 
+#include <cstdlib>
 #include <stdexcept>
 #include <type_traits>
 
@@ -49,6 +50,20 @@ inline void quantise(small_b200_layer &L, BufferT const &in, BufferT const *filt
     }
 }
 
+// Off by default: the reference's own tests accept |x - golden| <= 1e-5 + 5e-3 |golden| element by
+// element (test/include/test_utils.hpp), which on outputs of magnitude 10..30 only the sequential
+// fp32 sum of the CUDA-core kernel meets; the 3xTF32 kernel is within 1e-5 of the output RANGE.
+// SMALL_B200_TENSOR_CORE=1 in the environment, or small::b200::tensor_core() = true, turns it on.
+inline bool &tensor_core()
+{
+    static bool on = [] {
+        const char *e = std::getenv("SMALL_B200_TENSOR_CORE");
+        return e && e[0] == '1';
+    }();
+    return on;
+}
+inline bool tensor_core_enabled() { return tensor_core(); }
+
 template <class BufferT>
 inline void conv(bool partial, int act, int kh, int kw, int stride, int t, int b, int l, int r,
                  int K, int C, int H, int W, BufferT const &in, BufferT const &filt,
@@ -64,8 +79,27 @@ inline void conv(bool partial, int act, int kh, int kw, int stride, int t, int b
         throw_on(small_b200_conv2d_u8(&L, in.device_ptr(), filt.device_ptr(), nullptr, out.device_ptr(), nullptr));
     }
     else
-        throw_on(small_b200_conv2d_f32(&L, in.device_ptr(), filt.device_ptr(),
-                                       bias ? bias->device_ptr() : nullptr, out.device_ptr(), nullptr));
+    {
+        // Wide stride-1 layers run on the tensor cores (tcgen05 kind::tf32, 3xTF32 split).  The
+        // kernel wants the filter re-laid; that copy is made once and kept with the filter buffer
+        // until the host touches the buffer again.
+        const int Ho = small::output_dim(H + t + b, stride, kh), Wo = small::output_dim(W + l + r, stride, kw);
+        if (tensor_core_enabled() && C >= 32 && Ho * Wo >= 32 && small_b200_conv2d_f32_tf32x3_supported(&L))
+        {
+            const uint64_t key = ((uint64_t)K << 40) ^ ((uint64_t)C << 20) ^ ((uint64_t)kh << 8) ^ (uint64_t)kw;
+            float *prepared = filt.companion(key);
+            if (!prepared)
+            {
+                prepared = filt.make_companion(key, 2 * (size_t)K * C * kh * kw);
+                throw_on(small_b200_filter_prepare_tf32x3(&L, filt.device_ptr(), prepared, nullptr));
+            }
+            throw_on(small_b200_conv2d_f32_tf32x3(&L, in.device_ptr(), prepared, bias ? bias->device_ptr() : nullptr,
+                                                  out.device_ptr(), nullptr));
+        }
+        else
+            throw_on(small_b200_conv2d_f32(&L, in.device_ptr(), filt.device_ptr(),
+                                           bias ? bias->device_ptr() : nullptr, out.device_ptr(), nullptr));
+    }
 }
 
 template <class BufferT>

@@ -71,9 +71,10 @@ template <typename T>
 class ManagedArray
 {
 public:
-    ManagedArray() : m_num_elts(0), m_buffer(nullptr), m_host_touched(false) {}
+    ManagedArray() : m_num_elts(0), m_buffer(nullptr), m_host_touched(false), m_companion(nullptr), m_companion_key(0) {}
 
-    explicit ManagedArray(size_t num_elts) : m_num_elts(num_elts), m_buffer(nullptr), m_host_touched(true)
+    explicit ManagedArray(size_t num_elts)
+        : m_num_elts(num_elts), m_buffer(nullptr), m_host_touched(true), m_companion(nullptr), m_companion_key(0)
     {
         void *p = nullptr;
         if (SMALL_B200_OK != small_b200_malloc_managed(num_elts * sizeof(T), &p))
@@ -141,6 +142,23 @@ public:
         std::swap(m_num_elts, other.m_num_elts);
         std::swap(m_buffer, other.m_buffer);
         std::swap(m_host_touched, other.m_host_touched);
+        std::swap(m_companion, other.m_companion);
+        std::swap(m_companion_key, other.m_companion_key);
+    }
+
+    // A device-only companion derived from the contents (a filter re-laid for the tensor cores).
+    // It lives as long as the host does not look at the buffer: data() / operator[] may be
+    // followed by writes, so they drop it and the next layer call derives it again.
+    T *companion(uint64_t key) const { return (m_companion && m_companion_key == key) ? m_companion : nullptr; }
+    T *make_companion(uint64_t key, size_t elems) const
+    {
+        drop_companion();
+        void *p = nullptr;
+        if (SMALL_B200_OK != small_b200_malloc(elems * sizeof(T), &p))
+            throw std::bad_alloc();
+        m_companion = static_cast<T *>(p);
+        m_companion_key = key;
+        return m_companion;
     }
 
     // Device view for a layer call: no wait; brings host-touched pages back first.
@@ -162,6 +180,21 @@ private:
         {
             sync_for_host();
             m_host_touched = true;
+            drop_companion();
+        }
+    }
+
+    void drop_companion() const noexcept
+    {
+        if (m_companion)
+        {
+            if (pending())
+            {
+                small_b200_device_sync();
+                pending() = false;
+            }
+            small_b200_free(m_companion);
+            m_companion = nullptr;
         }
     }
 
@@ -176,6 +209,7 @@ private:
             }
             small_b200_free(m_buffer);
         }
+        drop_companion();
         m_buffer = nullptr;
         m_num_elts = 0;
     }
@@ -183,6 +217,8 @@ private:
     size_t m_num_elts;
     T *m_buffer;
     mutable bool m_host_touched;
+    mutable T *m_companion;
+    mutable uint64_t m_companion_key;
 };
 } // namespace b200
 

@@ -40,3 +40,21 @@ def test_reference_driver(name):
                        stderr=subprocess.STDOUT, text=True, timeout=900)
     tail = "\n".join(r.stdout.splitlines()[-25:])
     assert r.returncode == 0, f"{name} failed:\n{tail}"
+
+
+# Drivers that compare the functional chain with the Model / DAGModel classes, or that apply a
+# tolerance relative to the result: they also pass with the tensor-core fp32 convolution switched on
+# (the layer functions then re-lay each filter once and keep that copy with the filter buffer).
+TENSOR_CORE_DRIVERS = ["test_tinyyolov2", "test_resnet8", "test_autoencoder", "test_partial_conv2d"]
+
+
+@pytest.mark.parametrize("name", TENSOR_CORE_DRIVERS)
+def test_reference_driver_on_tensor_cores(name):
+    exe = os.path.join(BUILD, "bin", name)
+    if not os.path.exists(exe):
+        pytest.skip(f"{exe} not built (run make -C tests/reference_drivers where the reference is mounted)")
+    env = dict(os.environ, OMP_NUM_THREADS="4", SMALL_B200_TENSOR_CORE="1")
+    r = subprocess.run([exe], cwd=os.path.join(BUILD, "run"), env=env, stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT, text=True, timeout=900)
+    tail = "\n".join(r.stdout.splitlines()[-25:])
+    assert r.returncode == 0, f"{name} failed with SMALL_B200_TENSOR_CORE=1:\n{tail}"
