@@ -157,6 +157,35 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     while ((int)tmem_cols < 2 * a.NPX)
         tmem_cols <<= 1;
 
+    const int steps = a.cbs * a.taps;
+    const int groups = steps / a.group, groups_per_cb = a.taps / a.group;
+    const size_t tile_base = (size_t)kt * a.MT * steps * 16; // floats before this channel tile
+    auto issue_patch = [&](int cb) {
+        const int rs = cb % a.raw_slots;
+        mbar_expect_tx(&raw_full[rs], raw_bytes);
+        tma_load_4d(sRaw + (size_t)rs * raw_part, &map_x, 0, -a.pad_l, r_first - a.pad_t, n * a.cbs + cb, &raw_full[rs]);
+    };
+    auto issue_filter = [&](int g) {
+        const int st = g % a.w_stages;
+        uint8_t *wd = sW + (size_t)st * 2 * w_half_stage;
+        const size_t off = tile_base + (size_t)g * a.group * kv * 16;
+        mbar_expect_tx(&w_full[st], 2u * a.group * kv * 64);
+        if (kv == a.MT)
+        {
+            tma_load_1d(wd, filt + off, w_half_stage, &w_full[st]); // the group's taps are contiguous
+            tma_load_1d(wd + w_half_stage, filt_lo + off, w_half_stage, &w_full[st]);
+        }
+        else
+            for (int t = 0; t < a.group; ++t)
+                for (int j = 0; j < 4; ++j) // partial tile: kv of MT rows per 4-channel chunk
+                {
+                    const size_t o = off + ((size_t)t * 4 + j) * kv * 4;
+                    tma_load_1d(wd + t * w_part + j * w_chunk, filt + o, (uint32_t)kv * 16, &w_full[st]);
+                    tma_load_1d(wd + w_half_stage + t * w_part + j * w_chunk, filt_lo + o, (uint32_t)kv * 16,
+                                &w_full[st]);
+                }
+    };
+
     if (warp == 0)
     {
         if (lane == 0)
@@ -169,6 +198,11 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             }
             for (int i = 0; i < 2; ++i) mbar_init(&t_empty[i], ACC_WARPS);
             fence_barrier_init();
+            // The first patch and the first filter stage only need their barriers: their round
+            // trip to memory overlaps the tensor-memory allocation and the CTA-wide barrier
+            // (a quarter of the life of a CTA on layers with few channel blocks).
+            issue_patch(0);
+            issue_filter(0);
         }
         __syncwarp();
         tmem_alloc(&tmem_base_s, tmem_cols);
@@ -178,8 +212,6 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = tmem_base_s;
-    const int steps = a.cbs * a.taps;
-    const int groups = steps / a.group, groups_per_cb = a.taps / a.group;
 
     if (warp < FIRST_ACC_WARP || warp >= FIRST_SPLIT_WARP)
     {
@@ -188,10 +220,9 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         {
             // ---------------- producer ----------------
             bool ok = true;
-            const size_t tile_base = (size_t)kt * a.MT * steps * 16; // floats before this channel tile
             for (int g = 0; g < groups && ok; ++g)
             {
-                if (g % groups_per_cb == 0)
+                if (g % groups_per_cb == 0 && g > 0) // patch 0 is already on its way
                 {
                     const int cb = g / groups_per_cb;
                     const int rs = cb % a.raw_slots, ruse = cb / a.raw_slots;
@@ -199,32 +230,16 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                         ok = mbar_wait(&raw_empty[rs], (ruse - 1) & 1, status, 11);
                     if (!ok)
                         break;
-                    mbar_expect_tx(&raw_full[rs], raw_bytes);
-                    tma_load_4d(sRaw + (size_t)rs * raw_part, &map_x, 0, -a.pad_l, r_first - a.pad_t, n * a.cbs + cb,
-                                &raw_full[rs]);
+                    issue_patch(cb);
                 }
+                if (g == 0)
+                    continue; // so is filter stage 0
                 const int st = g % a.w_stages, wuse = g / a.w_stages;
                 if (wuse > 0)
                     ok = mbar_wait(&g_done[st], (wuse - 1) & 1, status, 12);
                 if (!ok)
                     break;
-                uint8_t *wd = sW + (size_t)st * 2 * w_half_stage;
-                const size_t off = tile_base + (size_t)g * a.group * kv * 16;
-                mbar_expect_tx(&w_full[st], 2u * a.group * kv * 64);
-                if (kv == a.MT)
-                {
-                    tma_load_1d(wd, filt + off, w_half_stage, &w_full[st]); // the group's taps are contiguous
-                    tma_load_1d(wd + w_half_stage, filt_lo + off, w_half_stage, &w_full[st]);
-                }
-                else
-                    for (int t = 0; t < a.group; ++t)
-                        for (int j = 0; j < 4; ++j) // partial tile: kv of MT rows per 4-channel chunk
-                        {
-                            const size_t o = off + ((size_t)t * 4 + j) * kv * 4;
-                            tma_load_1d(wd + t * w_part + j * w_chunk, filt + o, (uint32_t)kv * 16, &w_full[st]);
-                            tma_load_1d(wd + w_half_stage + t * w_part + j * w_chunk, filt_lo + o, (uint32_t)kv * 16,
-                                        &w_full[st]);
-                        }
+                issue_filter(g);
             }
         }
         else if (warp == 1 && lane == 0)
