@@ -48,6 +48,8 @@ struct TcArgs
     int PW, PR;        // patch width / rows
     int NPX;           // pixels (GEMM columns) per CTA: 64, 128, 192 or 256
     int px_tiles;      // CTAs along the pixel axis per image
+    int tiled;         // 0: tiles are ranges of full-width rows; 1: TH x TW pixel tiles
+    int TW, TH, tiles_x; // tiled mode: valid columns / rows of a tile, tiles per row of tiles
     int MT;            // output channels per CTA (tensor-core M): 128 or 64
     int k_tiles;       // ceil(K / MT)
     int x_entries;     // entries between the 4-channel chunks of a canonical patch (>= PR*PW)
@@ -147,9 +149,21 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     const int kt = bid % a.k_tiles; bid /= a.k_tiles;
     const int pt = bid % a.px_tiles;
     const int n = bid / a.px_tiles;
-    const int m0 = pt * a.NPX;
-    const int r_first = m0 / a.PW;
-    const int m_local0 = m0 - r_first * a.PW;
+    // first patch row / column in image coordinates, first GEMM column inside the patch, and how
+    // many columns of a patch row are real outputs
+    int row_base, col_base, m_local0, tw_valid, th_valid;
+    if (!a.tiled)
+    {
+        const int m0 = pt * a.NPX;
+        row_base = m0 / a.PW; col_base = 0; m_local0 = m0 - row_base * a.PW;
+        tw_valid = a.Wo; th_valid = a.Ho;
+    }
+    else
+    {
+        const int ty = pt / a.tiles_x, tx = pt - ty * a.tiles_x;
+        row_base = ty * a.TH; col_base = tx * a.TW; m_local0 = 0;
+        tw_valid = (a.Wo - col_base) < a.TW ? (a.Wo - col_base) : a.TW; th_valid = a.TH;
+    }
     const int kv = (a.K - kt * a.MT) < a.MT ? (a.K - kt * a.MT) : a.MT; // channels of this tile
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -163,7 +177,8 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     auto issue_patch = [&](int cb) {
         const int rs = cb % a.raw_slots;
         mbar_expect_tx(&raw_full[rs], raw_bytes);
-        tma_load_4d(sRaw + (size_t)rs * raw_part, &map_x, 0, -a.pad_l, r_first - a.pad_t, n * a.cbs + cb, &raw_full[rs]);
+        tma_load_4d(sRaw + (size_t)rs * raw_part, &map_x, 0, col_base - a.pad_l, row_base - a.pad_t, n * a.cbs + cb,
+                    &raw_full[rs]);
     };
     auto issue_filter = [&](int g) {
         const int st = g % a.w_stages;
@@ -414,9 +429,10 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             for (int pg = warp - FIRST_ACC_WARP; pg < a.NPX / 8; pg += ACC_WARPS)
             {
                 const int px = pg * 8 + psub;
-                const int m = m0 + px;
-                const int r = m / a.PW, c = m - r * a.PW;
-                if (r < a.Ho && c < a.Wo)
+                const int ml = m_local0 + px;
+                const int rl = ml / a.PW, cl = ml - rl * a.PW;
+                const int r = row_base + rl, c = col_base + cl;
+                if (cl < tw_valid && rl < th_valid && r < a.Ho)
                 {
                     const float *sp = stage + (size_t)px * pitch + q4 * 4;
                     float *o = obase + ((size_t)r * a.Wo + c) * CB;
@@ -449,6 +465,64 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         tmem_dealloc(tmem, tmem_cols);
 }
 
+// Wide images: TH x TW pixel tiles.  A tile's patch is (TH + Fh) x (TW + Fw - 1) pixels, so the
+// halo stays small (a range of full-width rows of a 208-wide image drags two whole rows of halo
+// along for every 256 outputs).  GEMM column j of a tile is patch-linear: row j / PW, column j % PW,
+// columns >= TW of each patch row are junk.
+bool plan_tiled(const small_b200_layer *L, TcArgs &a)
+{
+    const size_t limit = 226 * 1024;
+    double best = 0.0;
+    int best_tw = 0, best_th = 0;
+    for (int tw = 8; tw <= a.Wo && tw + a.Fw - 1 <= 256; ++tw)
+    {
+        const int pw = tw + a.Fw - 1;
+        int th = (256 - tw) / pw + 1;
+        if (th > a.Ho)
+            th = a.Ho;
+        const int npx = ((th - 1) * pw + tw + 63) / 64 * 64;
+        const long long tiles = (long long)((a.Wo + tw - 1) / tw) * ((a.Ho + th - 1) / th);
+        const double eff = (double)a.Wo * a.Ho / ((double)tiles * npx);
+        if (eff > best + 1e-9)
+        {
+            best = eff; best_tw = tw; best_th = th;
+        }
+    }
+    if (!best_tw)
+        return false;
+    a.tiled = 1; a.TW = best_tw; a.TH = best_th;
+    a.PW = a.TW + a.Fw - 1;
+    a.PR = a.TH + a.Fh; // one row more than the taps reach: the junk tail of the last row reads it
+    if (a.PR > 256)
+        return false;
+    a.NPX = ((a.TH - 1) * a.PW + a.TW + 63) / 64 * 64;
+    a.tiles_x = (a.Wo + a.TW - 1) / a.TW;
+    a.px_tiles = a.tiles_x * ((a.Ho + a.TH - 1) / a.TH);
+    // the last GEMM column's last tap must stay inside the patch
+    if ((a.NPX - 1) + (a.Fh - 1) * a.PW + (a.Fw - 1) >= a.PR * a.PW)
+        a.PR = ((a.NPX - 1) + (a.Fh - 1) * a.PW + (a.Fw - 1)) / a.PW + 1;
+    const int entries = a.PR * a.PW;
+    a.x_entries = entries + ((2 - entries % 8) + 8) % 8;
+    const size_t raw_part = ((size_t)entries * 64 + 127) & ~(size_t)127;
+    const size_t x_part = ((size_t)a.x_entries * 64 + 127) & ~(size_t)127;
+    const size_t w_part = (size_t)a.MT * 64 * a.group;
+    static const int pref[][3] = {{3, 3, 2}, {2, 3, 2}, {2, 3, 1}, {2, 2, 1}, {1, 3, 1}, {1, 2, 1}};
+    for (const auto &p : pref)
+    {
+        const int xs = p[0] < a.cbs ? p[0] : a.cbs, rs = p[2] < a.cbs ? p[2] : a.cbs;
+        size_t smem = (size_t)rs * raw_part + (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
+        const size_t epilogue = (size_t)a.NPX * (a.MT + 16) * 4;
+        if (smem < epilogue)
+            smem = epilogue;
+        if (smem <= limit)
+        {
+            a.x_slots = xs; a.w_stages = p[1]; a.raw_slots = rs; a.smem_bytes = (unsigned)smem;
+            return true;
+        }
+    }
+    return false;
+}
+
 // Tiling and shared-memory plan of one layer; false when the shape is not covered.
 bool plan(const small_b200_layer *L, TcArgs &a)
 {
@@ -464,19 +538,18 @@ bool plan(const small_b200_layer *L, TcArgs &a)
     a.cbs = L->C / CB; a.taps = L->Fh * L->Fw;
     a.accumulate = L->accumulate; a.act = L->act; a.slope = L->slope;
     a.PW = L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r);
-    if (a.PW > 256)
-        return false;
     a.MT = pick_mt(a.K);
     a.k_tiles = (a.K + a.MT - 1) / a.MT;
     a.group = a.Fw; // one kernel row per flush: taps = Fh * Fw is a multiple of it
     if (a.Ho == 0 || a.Wo == 0)
         return true;
+    if (L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r) > 40)
+        return plan_tiled(L, a);
     // GEMM columns of one image: the last valid one is (Ho-1)*PW + Wo-1
     const int m_img = (a.Ho - 1) * a.PW + a.Wo;
     const size_t limit = 226 * 1024;
     const int tiles256 = (m_img + 255) / 256;
     int npx_first = ((m_img + tiles256 - 1) / tiles256 + 63) / 64 * 64;
-    // {patch slots, filter stages (>= 2: a commit serves both rings), raw patch buffers}
     // {patch slots, filter stages (>= 2: a commit serves both rings), raw patch buffers}
     static const int pref[][3] = {{2, 3, 1}, {2, 2, 1}, {1, 3, 1}, {1, 2, 1}};
     // First pass: only plans that keep two patches in flight (a layer with few channel blocks

@@ -27,6 +27,12 @@ CASES = [
     (512, 128, 13, 13, 3, 3, "same", 1),    # long reduction: 32 channel blocks
     (1024, 128, 13, 13, 3, 3, "same", 1),   # the longest reduction of the configurations (9216 terms)
     (1024, 128, 13, 13, 1, 1, "valid", 2),
+    # wide images: TH x TW pixel tiles (partial tiles at the right and bottom edges)
+    (16, 32, 40, 130, 3, 3, "same", 2),
+    (32, 64, 70, 90, 3, 3, "same", 1),
+    (16, 16, 9, 300, 1, 1, "valid", 1),
+    (32, 48, 33, 75, 5, 3, (2, 2, 1, 1), 1),
+    (16, 32, 50, 64, 3, 3, "valid", 2),
 ]
 
 
@@ -64,4 +70,4 @@ def test_conv2d_3xtf32(oracle, case, mode):
 def test_unsupported_shapes_are_refused():
     assert not S.tf32x3_supported(3, 3, 2, 0, 1, 0, 1, 16, 16, 32, 32)   # stride 2
     assert not S.tf32x3_supported(3, 3, 1, 1, 1, 1, 1, 16, 3, 32, 32)    # first layer
-    assert not S.tf32x3_supported(3, 3, 1, 1, 1, 1, 1, 16, 16, 416, 416) # wider than one TMA box
+    assert S.tf32x3_supported(3, 3, 1, 1, 1, 1, 1, 16, 16, 416, 416)     # wide images: 2-D pixel tiles
