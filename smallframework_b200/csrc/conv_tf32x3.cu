@@ -58,6 +58,9 @@ struct TcArgs
     int accumulate, act;
     float slope;
     unsigned smem_bytes;
+    unsigned stage_off;  // byte offset of the output staging rows (0: they alias the operand buffers)
+    int total_tiles;     // N * px_tiles * k_tiles
+    int persistent;      // 1: one CTA per SM walks over the tiles; 0: one tile per CTA
 };
 
 // Output channels per CTA, a function of K alone so that filter preparation and the
@@ -122,6 +125,49 @@ __device__ __forceinline__ float4 lo_of(const float4 v)
     return r;
 }
 
+// One tile of work: an image, a range of pixels and a block of MT output channels.
+struct Tile
+{
+    int n, kt, kv;             // image, channel tile, channels this tile really has
+    int row_base, col_base;    // first patch row / column in image coordinates (before padding)
+    int m_local0;              // first GEMM column inside the patch
+    int tw_valid, th_valid;    // real outputs per patch row / patch rows that hold outputs
+};
+
+__device__ __forceinline__ Tile decode_tile(const TcArgs &a, int t)
+{
+    Tile T;
+    T.kt = t % a.k_tiles; t /= a.k_tiles;
+    const int pt = t % a.px_tiles;
+    T.n = t / a.px_tiles;
+    if (!a.tiled)
+    {
+        const int m0 = pt * a.NPX;
+        T.row_base = m0 / a.PW; T.col_base = 0; T.m_local0 = m0 - T.row_base * a.PW;
+        T.tw_valid = a.Wo; T.th_valid = a.Ho;
+    }
+    else
+    {
+        const int ty = pt / a.tiles_x, tx = pt - ty * a.tiles_x;
+        T.row_base = ty * a.TH; T.col_base = tx * a.TW; T.m_local0 = 0;
+        T.tw_valid = (a.Wo - T.col_base) < a.TW ? (a.Wo - T.col_base) : a.TW; T.th_valid = a.TH;
+    }
+    T.kv = (a.K - T.kt * a.MT) < a.MT ? (a.K - T.kt * a.MT) : a.MT;
+    return T;
+}
+
+// A CTA walks over tiles blockIdx.x, blockIdx.x + gridDim.x, ...  With a grid of one CTA per SM the
+// roles run ahead of one another across tile boundaries: the producer, the splitters and the MMA
+// issuer start the next tile while the accumulation warps still write the previous one out, which
+// hides the start-up and the epilogue of a tile (half the life of a CTA on layers with few channel
+// blocks).  All ring positions and barrier phases therefore count patches and groups over the whole
+// life of the CTA.  With one tile per CTA (grid = number of tiles) the loop runs once and the
+// output staging may alias the operand buffers (stage_off = 0).
+// PERSIST = false: exactly one tile per CTA, known at compile time.
+#define SB_TILE_LOOP(cond_extra) \
+    for (int t = first_tile, once_ = 0; (PERSIST ? (t < a.total_tiles) : (once_ == 0)) && (cond_extra); t += tile_step, ++once_)
+
+template <bool PERSIST>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__restrict__ filt,
                    const float *__restrict__ filt_lo, const TcArgs a, const float *__restrict__ bias, float *__restrict__ out, int *status)
@@ -145,27 +191,6 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     uint8_t *sW = sX + (size_t)a.x_slots * 2 * x_part;              // [stage][hi|lo][tap in group][c/4][MT k][16 B]
     const uint32_t w_half_stage = (uint32_t)a.group * w_part;       // hi (or lo) tiles of one stage
 
-    int bid = blockIdx.x;
-    const int kt = bid % a.k_tiles; bid /= a.k_tiles;
-    const int pt = bid % a.px_tiles;
-    const int n = bid / a.px_tiles;
-    // first patch row / column in image coordinates, first GEMM column inside the patch, and how
-    // many columns of a patch row are real outputs
-    int row_base, col_base, m_local0, tw_valid, th_valid;
-    if (!a.tiled)
-    {
-        const int m0 = pt * a.NPX;
-        row_base = m0 / a.PW; col_base = 0; m_local0 = m0 - row_base * a.PW;
-        tw_valid = a.Wo; th_valid = a.Ho;
-    }
-    else
-    {
-        const int ty = pt / a.tiles_x, tx = pt - ty * a.tiles_x;
-        row_base = ty * a.TH; col_base = tx * a.TW; m_local0 = 0;
-        tw_valid = (a.Wo - col_base) < a.TW ? (a.Wo - col_base) : a.TW; th_valid = a.TH;
-    }
-    const int kv = (a.K - kt * a.MT) < a.MT ? (a.K - kt * a.MT) : a.MT; // channels of this tile
-
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint32_t tmem_cols = 32;
     while ((int)tmem_cols < 2 * a.NPX)
@@ -173,19 +198,21 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
 
     const int steps = a.cbs * a.taps;
     const int groups = steps / a.group, groups_per_cb = a.taps / a.group;
-    const size_t tile_base = (size_t)kt * a.MT * steps * 16; // floats before this channel tile
-    auto issue_patch = [&](int cb) {
-        const int rs = cb % a.raw_slots;
+    const int first_tile = blockIdx.x, tile_step = gridDim.x;
+
+    // patch number pc / group number gc count over every tile of this CTA
+    auto issue_patch = [&](const Tile &T, int cb, int pc) {
+        const int rs = pc % a.raw_slots;
         mbar_expect_tx(&raw_full[rs], raw_bytes);
-        tma_load_4d(sRaw + (size_t)rs * raw_part, &map_x, 0, col_base - a.pad_l, row_base - a.pad_t, n * a.cbs + cb,
-                    &raw_full[rs]);
+        tma_load_4d(sRaw + (size_t)rs * raw_part, &map_x, 0, T.col_base - a.pad_l, T.row_base - a.pad_t,
+                    T.n * a.cbs + cb, &raw_full[rs]);
     };
-    auto issue_filter = [&](int g) {
-        const int st = g % a.w_stages;
+    auto issue_filter = [&](const Tile &T, int g, int gc) {
+        const int st = gc % a.w_stages;
         uint8_t *wd = sW + (size_t)st * 2 * w_half_stage;
-        const size_t off = tile_base + (size_t)g * a.group * kv * 16;
-        mbar_expect_tx(&w_full[st], 2u * a.group * kv * 64);
-        if (kv == a.MT)
+        const size_t off = (size_t)T.kt * a.MT * steps * 16 + (size_t)g * a.group * T.kv * 16;
+        mbar_expect_tx(&w_full[st], 2u * a.group * T.kv * 64);
+        if (T.kv == a.MT)
         {
             tma_load_1d(wd, filt + off, w_half_stage, &w_full[st]); // the group's taps are contiguous
             tma_load_1d(wd + w_half_stage, filt_lo + off, w_half_stage, &w_full[st]);
@@ -194,9 +221,9 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             for (int t = 0; t < a.group; ++t)
                 for (int j = 0; j < 4; ++j) // partial tile: kv of MT rows per 4-channel chunk
                 {
-                    const size_t o = off + ((size_t)t * 4 + j) * kv * 4;
-                    tma_load_1d(wd + t * w_part + j * w_chunk, filt + o, (uint32_t)kv * 16, &w_full[st]);
-                    tma_load_1d(wd + w_half_stage + t * w_part + j * w_chunk, filt_lo + o, (uint32_t)kv * 16,
+                    const size_t o = off + ((size_t)t * 4 + j) * T.kv * 4;
+                    tma_load_1d(wd + t * w_part + j * w_chunk, filt + o, (uint32_t)T.kv * 16, &w_full[st]);
+                    tma_load_1d(wd + w_half_stage + t * w_part + j * w_chunk, filt_lo + o, (uint32_t)T.kv * 16,
                                 &w_full[st]);
                 }
     };
@@ -214,10 +241,10 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             for (int i = 0; i < 2; ++i) mbar_init(&t_empty[i], ACC_WARPS);
             fence_barrier_init();
             // The first patch and the first filter stage only need their barriers: their round
-            // trip to memory overlaps the tensor-memory allocation and the CTA-wide barrier
-            // (a quarter of the life of a CTA on layers with few channel blocks).
-            issue_patch(0);
-            issue_filter(0);
+            // trip to memory overlaps the tensor-memory allocation and the CTA-wide barrier.
+            const Tile T = decode_tile(a, first_tile);
+            issue_patch(T, 0, 0);
+            issue_filter(T, 0, 0);
         }
         __syncwarp();
         tmem_alloc(&tmem_base_s, tmem_cols);
@@ -230,31 +257,39 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
 
     if (warp < FIRST_ACC_WARP || warp >= FIRST_SPLIT_WARP)
     {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
         if (warp == 0 && lane == 0)
         {
             // ---------------- producer ----------------
             bool ok = true;
-            for (int g = 0; g < groups && ok; ++g)
+            int pc = 0, gc = 0;
+            SB_TILE_LOOP(ok)
             {
-                if (g % groups_per_cb == 0 && g > 0) // patch 0 is already on its way
+                const Tile T = decode_tile(a, t);
+                for (int g = 0; g < groups && ok; ++g, ++gc)
                 {
-                    const int cb = g / groups_per_cb;
-                    const int rs = cb % a.raw_slots, ruse = cb / a.raw_slots;
-                    if (ruse > 0)
-                        ok = mbar_wait(&raw_empty[rs], (ruse - 1) & 1, status, 11);
+                    if (g % groups_per_cb == 0)
+                    {
+                        if (pc > 0) // patch 0 of the first tile is already on its way
+                        {
+                            const int rs = pc % a.raw_slots, ruse = pc / a.raw_slots;
+                            if (ruse > 0)
+                                ok = mbar_wait(&raw_empty[rs], (ruse - 1) & 1, status, 11);
+                            if (!ok)
+                                break;
+                            issue_patch(T, g / groups_per_cb, pc);
+                        }
+                        ++pc;
+                    }
+                    if (gc == 0)
+                        continue; // so is filter stage 0
+                    const int st = gc % a.w_stages, wuse = gc / a.w_stages;
+                    if (wuse > 0)
+                        ok = mbar_wait(&g_done[st], (wuse - 1) & 1, status, 12);
                     if (!ok)
                         break;
-                    issue_patch(cb);
+                    issue_filter(T, g, gc);
                 }
-                if (g == 0)
-                    continue; // so is filter stage 0
-                const int st = g % a.w_stages, wuse = g / a.w_stages;
-                if (wuse > 0)
-                    ok = mbar_wait(&g_done[st], (wuse - 1) & 1, status, 12);
-                if (!ok)
-                    break;
-                issue_filter(g);
             }
         }
         else if (warp == 1 && lane == 0)
@@ -264,57 +299,62 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             // 16-byte-granular start address are fixed per CTA, and a new operand position is one
             // 64-bit add on a precomputed descriptor.  A = filter tap (M = channels), B = patch
             // shifted by the tap (N = pixels).
+            // The tensor pipe's queue holds only a handful of MMAs, so whatever this thread does
+            // between two groups beyond issuing (waits, commits, index arithmetic) shows up as
+            // idle tensor cycles: the loop keeps its counters incrementally, no divisions.
             bool ok = true;
-            const uint64_t x_desc0 = make_smem_desc(smem_u32(sX), x_chunk, 128, 0) + (uint64_t)m_local0;
+            const uint64_t x_desc_base = make_smem_desc(smem_u32(sX), x_chunk, 128, 0);
             const uint64_t w_desc0 = make_smem_desc(smem_u32(sW), w_chunk, 128, 0);
             const uint32_t idesc = make_idesc(1 /*f32*/, 2 /*tf32*/, 2 /*tf32*/, 0 /*A K-major*/, 0 /*B K-major*/,
                                               (uint32_t)a.MT, (uint32_t)a.NPX);
             const uint64_t x_lo_off = x_part >> 4, w_lo_off = w_half_stage >> 4, w_tap = w_part >> 4;
             const uint64_t x_half = (2 * x_chunk) >> 4, w_half = (2 * w_chunk) >> 4;
-            // The tensor pipe's queue holds only a handful of MMAs, so whatever this thread does
-            // between two groups beyond issuing (waits, commits, index arithmetic) shows up as
-            // idle tensor cycles: the loop keeps its counters incrementally, no divisions.
             const uint64_t w_stage_step = (uint64_t)2 * w_half_stage >> 4;
             const uint64_t x_slot_step = (uint64_t)2 * x_part >> 4;
-            int slot = 0, xphase = 0, st = 0, wphase = 0, g = 0;
-            uint64_t x_slot = x_desc0, w_stage = w_desc0;
-            for (int cb = 0; cb < a.cbs && ok; ++cb)
+            int slot = 0, xphase = 0, st = 0, wphase = 0, g = 0; // g counts groups over all tiles
+            uint64_t x_slot_off = 0, w_stage = w_desc0;
+            SB_TILE_LOOP(ok)
             {
-                ok = mbar_wait(&x_ready[slot], xphase, status, 13);
-                if (!ok)
-                    break;
-                uint64_t x_row = x_slot; // patch position of tap (kh, 0)
-                for (int gi = 0; gi < groups_per_cb && ok; ++gi, ++g)
+                const Tile T = decode_tile(a, t);
+                const uint64_t x_desc0 = x_desc_base + (uint64_t)T.m_local0;
+                for (int cb = 0; cb < a.cbs && ok; ++cb)
                 {
-                    const int tb = g & 1; // tensor-memory buffer of this group
-                    ok = mbar_wait(&w_full[st], wphase, status, 14);
-                    if (ok && g >= 2)
-                        ok = mbar_wait(&t_empty[tb], ((g >> 1) - 1) & 1, status, 16);
+                    ok = mbar_wait(&x_ready[slot], xphase, status, 13);
                     if (!ok)
                         break;
-                    tc_fence_after_sync();
-                    const uint32_t d = tmem + (uint32_t)(tb * a.NPX);
-                    uint64_t wh = w_stage, xh = x_row;
-                    for (int t = 0; t < a.group; ++t, wh += w_tap, ++xh)
+                    uint64_t x_row = x_desc0 + x_slot_off; // patch position of tap (kh, 0)
+                    for (int gi = 0; gi < groups_per_cb && ok; ++gi, ++g)
                     {
-                        const uint64_t xl = xh + x_lo_off, wl = wh + w_lo_off;
-                        tc_mma_tf32(d, wl, xh, idesc, t == 0 ? 0u : 1u);
-                        tc_mma_tf32(d, wh, xl, idesc, 1u);
-                        tc_mma_tf32(d, wh, xh, idesc, 1u);
-                        tc_mma_tf32(d, wl + w_half, xh + x_half, idesc, 1u);
-                        tc_mma_tf32(d, wh + w_half, xl + x_half, idesc, 1u);
-                        tc_mma_tf32(d, wh + w_half, xh + x_half, idesc, 1u);
+                        const int tb = g & 1; // tensor-memory buffer of this group
+                        ok = mbar_wait(&w_full[st], wphase, status, 14);
+                        if (ok && g >= 2)
+                            ok = mbar_wait(&t_empty[tb], ((g >> 1) - 1) & 1, status, 16);
+                        if (!ok)
+                            break;
+                        tc_fence_after_sync();
+                        const uint32_t d = tmem + (uint32_t)(tb * a.NPX);
+                        uint64_t wh = w_stage, xh = x_row;
+                        for (int tp = 0; tp < a.group; ++tp, wh += w_tap, ++xh)
+                        {
+                            const uint64_t xl = xh + x_lo_off, wl = wh + w_lo_off;
+                            tc_mma_tf32(d, wl, xh, idesc, tp == 0 ? 0u : 1u);
+                            tc_mma_tf32(d, wh, xl, idesc, 1u);
+                            tc_mma_tf32(d, wh, xh, idesc, 1u);
+                            tc_mma_tf32(d, wl + w_half, xh + x_half, idesc, 1u);
+                            tc_mma_tf32(d, wh + w_half, xl + x_half, idesc, 1u);
+                            tc_mma_tf32(d, wh + w_half, xh + x_half, idesc, 1u);
+                        }
+                        // one commit: the stage is free for the producer and the group's partial
+                        // sums are complete for the accumulation warps
+                        tc_commit(&g_done[st]);
+                        x_row += (uint64_t)(a.group == a.Fw ? a.PW : 1);
+                        w_stage += w_stage_step;
+                        if (++st == a.w_stages) { st = 0; wphase ^= 1; w_stage = w_desc0; }
                     }
-                    // one commit: the stage is free for the producer and the group's partial
-                    // sums are complete for the accumulation warps
-                    tc_commit(&g_done[st]);
-                    x_row += (uint64_t)(a.group == a.Fw ? a.PW : 1);
-                    w_stage += w_stage_step;
-                    if (++st == a.w_stages) { st = 0; wphase ^= 1; w_stage = w_desc0; }
+                    tc_commit(&x_empty[slot]);
+                    x_slot_off += x_slot_step;
+                    if (++slot == a.x_slots) { slot = 0; xphase ^= 1; x_slot_off = 0; }
                 }
-                tc_commit(&x_empty[slot]);
-                x_slot += x_slot_step;
-                if (++slot == a.x_slots) { slot = 0; xphase ^= 1; x_slot = x_desc0; }
             }
         }
         else if (warp >= FIRST_SPLIT_WARP)
@@ -322,140 +362,218 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             // ---------------- operand splitters ----------------
             const int sid = tid - FIRST_SPLIT_WARP * 32;
             bool ok = true;
-            for (int cb = 0; cb < a.cbs && ok; ++cb)
-            {
-                const int rs = cb % a.raw_slots, slot = cb % a.x_slots, xuse = cb / a.x_slots;
-                ok = mbar_wait(&raw_full[rs], (cb / a.raw_slots) & 1, status, 17);
-                if (ok && xuse > 0)
-                    ok = mbar_wait(&x_empty[slot], (xuse - 1) & 1, status, 19);
-                if (!ok)
-                    break;
+            int pc = 0;
+            SB_TILE_LOOP(ok)
+                for (int cb = 0; cb < a.cbs && ok; ++cb, ++pc)
                 {
-                    // [entry][chunk] -> [chunk][entry], hi and lo.  A quarter warp reads 128
-                    // contiguous bytes; x_entries % 8 == 2 spreads its four chunk rows over
-                    // different banks on the way out.
-                    const uint8_t *raw = sRaw + (size_t)rs * raw_part;
-                    uint8_t *xh = sX + (size_t)slot * 2 * x_part, *xl = xh + x_part;
-                    const uint32_t total = entries * 4;
-                    for (uint32_t i = (uint32_t)sid; i < total; i += SPLIT_THREADS)
+                    const int rs = pc % a.raw_slots, slot = pc % a.x_slots, xuse = pc / a.x_slots;
+                    ok = mbar_wait(&raw_full[rs], (pc / a.raw_slots) & 1, status, 17);
+                    if (ok && xuse > 0)
+                        ok = mbar_wait(&x_empty[slot], (xuse - 1) & 1, status, 19);
+                    if (!ok)
+                        break;
                     {
-                        const float4 v = *reinterpret_cast<const float4 *>(raw + (size_t)i * 16);
-                        const uint32_t o = (i & 3u) * x_chunk + (i >> 2) * 16u;
-                        *reinterpret_cast<float4 *>(xh + o) = v;
-                        *reinterpret_cast<float4 *>(xl + o) = lo_of(v);
+                        // [entry][chunk] -> [chunk][entry], hi and lo.  A quarter warp reads 128
+                        // contiguous bytes; x_entries % 8 == 2 spreads its four chunk rows over
+                        // different banks on the way out.
+                        const uint8_t *raw = sRaw + (size_t)rs * raw_part;
+                        uint8_t *xh = sX + (size_t)slot * 2 * x_part, *xl = xh + x_part;
+                        const uint32_t total = entries * 4;
+                        for (uint32_t i = (uint32_t)sid; i < total; i += SPLIT_THREADS)
+                        {
+                            const float4 v = *reinterpret_cast<const float4 *>(raw + (size_t)i * 16);
+                            const uint32_t o = (i & 3u) * x_chunk + (i >> 2) * 16u;
+                            *reinterpret_cast<float4 *>(xh + o) = v;
+                            *reinterpret_cast<float4 *>(xl + o) = lo_of(v);
+                        }
                     }
+                    fence_proxy_async();
+                    mbar_arrive(&x_ready[slot]);
+                    mbar_arrive(&raw_empty[rs]);
                 }
-                fence_proxy_async();
-                mbar_arrive(&x_ready[slot]);
-                mbar_arrive(&raw_empty[rs]);
-            }
         }
     }
     else
     {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
         // ---------------- accumulation + epilogue ----------------
         const int quarter = warp & 3;                    // TMEM lanes [32*quarter, 32*quarter+32)
         const int phalf = (warp - FIRST_ACC_WARP) >> 2;  // which half of the tile's pixels
         const int my_cols = a.NPX / 2;                   // 32, 64, 96 or 128
         const int col0 = phalf * my_cols;
-        float acc[COLS_PER_THREAD];
-#pragma unroll
-        for (int c = 0; c < COLS_PER_THREAD; ++c)
-            acc[c] = 0.f;
-        bool ok = true;
-        for (int g = 0; g < groups && ok; ++g)
-        {
-            const int tb = g & 1;
-            ok = mbar_wait(&g_done[g % a.w_stages], (g / a.w_stages) & 1, status, 15, 1u << 24);
-            if (!ok)
-                break;
-            tc_fence_after_sync();
-            const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(tb * a.NPX + col0);
-#pragma unroll
-            for (int piece = 0; piece < COLS_PER_THREAD / 32; ++piece)
-            {
-                if (piece * 32 < my_cols)
-                {
-                    uint32_t v[32];
-                    tmem_ld32(tbase + (uint32_t)(piece * 32), v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e)
-                        acc[piece * 32 + e] += __uint_as_float(v[e]);
-                }
-            }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive(&t_empty[tb]);
-        }
         // 128-channel tile: lane l of quarter q holds channel 32q + l; 64-channel tile: channel
         // 16q + l in lanes 0..15 of each quarter
         const int k_local = (a.MT == 128) ? quarter * 32 + lane : quarter * 16 + lane;
         const bool lane_has_row = (a.MT == 128) || (lane < 16);
-        // Epilogue through shared memory (every operand buffer is dead once the last group has
-        // been flushed): a thread owns one channel of up to 128 pixels, the packed output wants
-        // 16 channels of one pixel together.  Rows of MT + 16 floats keep both the
-        // channel-wise writes and the float4 reads free of bank conflicts.
+        // Output staging rows of MT + 16 floats (free of bank conflicts both for the channel-wise
+        // writes and for the float4 reads); a persistent CTA stages 32 pixels of each half at a time.
         const int pitch = a.MT + 16;
-        float *stage = reinterpret_cast<float *>(smem);
-        if (ok && lane_has_row)
+        float *stage = reinterpret_cast<float *>(smem + a.stage_off);
+        const int psub = lane >> 2, q4 = lane & 3; // 8 pixels x 4 float4 per warp and step
+        const size_t plane = (size_t)a.Ho * a.Wo * CB;
+        bool ok = true;
+        int gc = 0;
+        SB_TILE_LOOP(ok)
         {
-            float *srow = stage + (size_t)col0 * pitch + k_local;
-            if (a.MT == 128)
-            {
+            const Tile T = decode_tile(a, t);
+            float acc[COLS_PER_THREAD];
 #pragma unroll
-                for (int e = 0; e < COLS_PER_THREAD; ++e)
-                    if (e < my_cols)
-                        srow[e * 144] = acc[e];
+            for (int c = 0; c < COLS_PER_THREAD; ++c)
+                acc[c] = 0.f;
+            for (int g = 0; g < groups && ok; ++g, ++gc)
+            {
+                const int tb = gc & 1;
+                ok = mbar_wait(&g_done[gc % a.w_stages], (gc / a.w_stages) & 1, status, 15, 1u << 24);
+                if (!ok)
+                    break;
+                tc_fence_after_sync();
+                const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(tb * a.NPX + col0);
+#pragma unroll
+                for (int piece = 0; piece < COLS_PER_THREAD / 32; ++piece)
+                {
+                    if (piece * 32 < my_cols)
+                    {
+                        uint32_t v[32];
+                        tmem_ld32(tbase + (uint32_t)(piece * 32), v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e)
+                            acc[piece * 32 + e] += __uint_as_float(v[e]);
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&t_empty[tb]);
+            }
+            // Epilogue (the other roles are already at work on the next tile): a thread owns one
+            // channel of up to 128 pixels, the packed output wants 16 channels of one pixel together.
+            const int kbs = T.kv / CB; // channel blocks this tile really has
+            float *obase = out + ((size_t)T.n * (a.K / CB) + (size_t)T.kt * (a.MT / CB)) * plane + q4 * 4;
+            // this thread's four channels of every channel block, fetched once per tile (a load per
+            // pixel inside the store loop costs a round trip to L2 each time)
+            float4 bias_r[8];
+#pragma unroll
+            for (int kb = 0; kb < 8; ++kb)
+                bias_r[kb] = (bias && kb < kbs) ? *reinterpret_cast<const float4 *>(bias + T.kt * a.MT + q4 * 4 + kb * CB)
+                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (!PERSIST)
+            {
+                // one tile per CTA: every operand buffer is dead, the whole tile is staged at once
+                if (ok && lane_has_row)
+                {
+                    float *srow = stage + (size_t)col0 * pitch + k_local;
+                    if (a.MT == 128)
+                    {
+#pragma unroll
+                        for (int e = 0; e < COLS_PER_THREAD; ++e)
+                            if (e < my_cols)
+                                srow[e * 144] = acc[e];
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int e = 0; e < COLS_PER_THREAD; ++e)
+                            if (e < my_cols)
+                                srow[e * 80] = acc[e];
+                    }
+                }
+                asm volatile("bar.sync 1, 256;" ::: "memory"); // the eight accumulation warps
+                if (ok)
+                {
+                    for (int pg = warp - FIRST_ACC_WARP; pg < a.NPX / 8; pg += ACC_WARPS)
+                    {
+                        const int px = pg * 8 + psub;
+                        const int ml = T.m_local0 + px;
+                        const int rl = ml / a.PW, cl = ml - rl * a.PW;
+                        const int r = T.row_base + rl, c = T.col_base + cl;
+                        if (cl < T.tw_valid && rl < T.th_valid && r < a.Ho)
+                        {
+                            const float *sp = stage + (size_t)px * pitch + q4 * 4;
+                            float *o = obase + ((size_t)r * a.Wo + c) * CB;
+#pragma unroll
+                            for (int kb = 0; kb < 8; ++kb)
+                              if (kb < kbs)
+                            {
+                                float4 x = *reinterpret_cast<const float4 *>(sp + kb * CB);
+                                float *ok_ = o + (size_t)kb * plane;
+                                if (a.accumulate)
+                                {
+                                    const float4 s4 = *reinterpret_cast<const float4 *>(ok_);
+                                    x.x += s4.x; x.y += s4.y; x.z += s4.z; x.w += s4.w;
+                                }
+                                {
+                                    const float4 b = bias_r[kb];
+                                    x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+                                }
+                                x.x = apply_act(x.x, a.act, a.slope); x.y = apply_act(x.y, a.act, a.slope);
+                                x.z = apply_act(x.z, a.act, a.slope); x.w = apply_act(x.w, a.act, a.slope);
+                                *reinterpret_cast<float4 *>(ok_) = x;
+                            }
+                        }
+                    }
+                }
             }
             else
             {
 #pragma unroll
-                for (int e = 0; e < COLS_PER_THREAD; ++e)
-                    if (e < my_cols)
-                        srow[e * 80] = acc[e];
-            }
-        }
-        asm volatile("bar.sync 1, 256;" ::: "memory"); // the eight accumulation warps
-        if (ok)
-        {
-            const int kbs = kv / CB;                   // channel blocks this tile really has
-            const int psub = lane >> 2, q4 = lane & 3; // 8 pixels x 4 float4 per warp and step
-            const size_t plane = (size_t)a.Ho * a.Wo * CB;
-            float *obase = out + ((size_t)n * (a.K / CB) + (size_t)kt * (a.MT / CB)) * plane + q4 * 4;
-            const float *bbase = bias ? bias + kt * a.MT + q4 * 4 : nullptr;
-            for (int pg = warp - FIRST_ACC_WARP; pg < a.NPX / 8; pg += ACC_WARPS)
+            for (int piece = 0; piece < COLS_PER_THREAD / 32; ++piece)
             {
-                const int px = pg * 8 + psub;
-                const int ml = m_local0 + px;
-                const int rl = ml / a.PW, cl = ml - rl * a.PW;
-                const int r = row_base + rl, c = col_base + cl;
-                if (cl < tw_valid && rl < th_valid && r < a.Ho)
+                if (piece * 32 < my_cols) // uniform over the CTA
                 {
-                    const float *sp = stage + (size_t)px * pitch + q4 * 4;
-                    float *o = obase + ((size_t)r * a.Wo + c) * CB;
-#pragma unroll 4
-                    for (int kb = 0; kb < kbs; ++kb)
+                    if (ok && lane_has_row)
                     {
-                        float4 x = *reinterpret_cast<const float4 *>(sp + kb * CB);
-                        float *ok_ = o + (size_t)kb * plane;
-                        if (a.accumulate)
+                        float *srow = stage + (size_t)(phalf * 32) * pitch + k_local;
+                        if (a.MT == 128)
                         {
-                            const float4 s4 = *reinterpret_cast<const float4 *>(ok_);
-                            x.x += s4.x; x.y += s4.y; x.z += s4.z; x.w += s4.w;
+#pragma unroll
+                            for (int e = 0; e < 32; ++e)
+                                srow[e * 144] = acc[piece * 32 + e];
                         }
-                        if (bbase)
+                        else
                         {
-                            const float4 b = *reinterpret_cast<const float4 *>(bbase + kb * CB);
-                            x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+#pragma unroll
+                            for (int e = 0; e < 32; ++e)
+                                srow[e * 80] = acc[piece * 32 + e];
                         }
-                        x.x = apply_act(x.x, a.act, a.slope); x.y = apply_act(x.y, a.act, a.slope);
-                        x.z = apply_act(x.z, a.act, a.slope); x.w = apply_act(x.w, a.act, a.slope);
-                        *reinterpret_cast<float4 *>(ok_) = x;
                     }
+                    asm volatile("bar.sync 1, 256;" ::: "memory"); // the eight accumulation warps
+                    if (ok)
+                    {
+                        // staged row s holds pixel (s / 32) * my_cols + piece * 32 + s % 32 of the tile
+                        const int s_row = (warp - FIRST_ACC_WARP) * 8 + psub;
+                        const int px = (s_row >> 5) * my_cols + piece * 32 + (s_row & 31);
+                        const int ml = T.m_local0 + px;
+                        const int rl = ml / a.PW, cl = ml - rl * a.PW;
+                        const int r = T.row_base + rl, c = T.col_base + cl;
+                        if (cl < T.tw_valid && rl < T.th_valid && r < a.Ho)
+                        {
+                            const float *sp = stage + (size_t)s_row * pitch + q4 * 4;
+                            float *o = obase + ((size_t)r * a.Wo + c) * CB;
+#pragma unroll
+                            for (int kb = 0; kb < 8; ++kb)
+                              if (kb < kbs)
+                            {
+                                float4 x = *reinterpret_cast<const float4 *>(sp + kb * CB);
+                                float *ok_ = o + (size_t)kb * plane;
+                                if (a.accumulate)
+                                {
+                                    const float4 s4 = *reinterpret_cast<const float4 *>(ok_);
+                                    x.x += s4.x; x.y += s4.y; x.z += s4.z; x.w += s4.w;
+                                }
+                                {
+                                    const float4 b = bias_r[kb];
+                                    x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+                                }
+                                x.x = apply_act(x.x, a.act, a.slope); x.y = apply_act(x.y, a.act, a.slope);
+                                x.z = apply_act(x.z, a.act, a.slope); x.w = apply_act(x.w, a.act, a.slope);
+                                *reinterpret_cast<float4 *>(ok_) = x;
+                            }
+                        }
+                    }
+                    asm volatile("bar.sync 1, 256;" ::: "memory"); // before the staging rows are reused
                 }
+            }
             }
         }
     }
@@ -465,13 +583,47 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         tmem_dealloc(tmem, tmem_cols);
 }
 
+// Picks ring depths for the patch / filter sizes already in `a`.  Narrow layers run persistent (one
+// CTA per SM walks over the tiles, roles overlap across tiles), which needs the output staging rows
+// next to the operand buffers; the others keep the deepest rings and let the staging alias them.  need_two: only accept plans with two patches in flight.
+bool fit_rings(TcArgs &a, bool need_two)
+{
+    const size_t limit = 226 * 1024;
+    const int entries = a.PR * a.PW;
+    a.x_entries = entries + ((2 - entries % 8) + 8) % 8; // % 8 == 2: conflict-free re-layout
+    const size_t raw_part = ((size_t)entries * 64 + 127) & ~(size_t)127;
+    const size_t x_part = ((size_t)a.x_entries * 64 + 127) & ~(size_t)127;
+    const size_t w_part = (size_t)a.MT * 64 * a.group;
+    const size_t staging = (size_t)64 * (a.MT + 16) * 4; // 32 pixels of each half of the tile
+    // {patch slots, filter stages (>= 2: a commit serves both rings), raw patch buffers}
+    static const int pref[][3] = {{3, 3, 2}, {2, 3, 2}, {2, 3, 1}, {2, 2, 1}, {1, 3, 1}, {1, 2, 1}};
+    // persistent where it pays and fits: narrow layers (64-channel tiles: small filter stages and
+    // staging rows, little work per tile); wide ones need the shared memory for deeper rings
+    for (int persistent = (a.MT == 64 ? 1 : 0); persistent >= 0; --persistent)
+        for (const auto &p : pref)
+        {
+            const int xs = p[0] < a.cbs || persistent ? p[0] : a.cbs, rs = p[2] < a.cbs || persistent ? p[2] : a.cbs;
+            if (need_two && xs < 2 && a.cbs >= 2)
+                continue;
+            const size_t ops = (size_t)rs * raw_part + (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
+            const size_t full = (size_t)a.NPX * (a.MT + 16) * 4; // one tile per CTA stages the whole tile
+            const size_t smem = persistent ? ops + staging : (ops > full ? ops : full);
+            if (smem <= limit)
+            {
+                a.x_slots = xs; a.w_stages = p[1]; a.raw_slots = rs; a.smem_bytes = (unsigned)smem;
+                a.persistent = persistent; a.stage_off = persistent ? (unsigned)ops : 0u;
+                return true;
+            }
+        }
+    return false;
+}
+
 // Wide images: TH x TW pixel tiles.  A tile's patch is (TH + Fh) x (TW + Fw - 1) pixels, so the
 // halo stays small (a range of full-width rows of a 208-wide image drags two whole rows of halo
 // along for every 256 outputs).  GEMM column j of a tile is patch-linear: row j / PW, column j % PW,
 // columns >= TW of each patch row are junk.
 bool plan_tiled(const small_b200_layer *L, TcArgs &a)
 {
-    const size_t limit = 226 * 1024;
     double best = 0.0;
     int best_tw = 0, best_th = 0;
     for (int tw = 8; tw <= a.Wo && tw + a.Fw - 1 <= 256; ++tw)
@@ -501,26 +653,7 @@ bool plan_tiled(const small_b200_layer *L, TcArgs &a)
     // the last GEMM column's last tap must stay inside the patch
     if ((a.NPX - 1) + (a.Fh - 1) * a.PW + (a.Fw - 1) >= a.PR * a.PW)
         a.PR = ((a.NPX - 1) + (a.Fh - 1) * a.PW + (a.Fw - 1)) / a.PW + 1;
-    const int entries = a.PR * a.PW;
-    a.x_entries = entries + ((2 - entries % 8) + 8) % 8;
-    const size_t raw_part = ((size_t)entries * 64 + 127) & ~(size_t)127;
-    const size_t x_part = ((size_t)a.x_entries * 64 + 127) & ~(size_t)127;
-    const size_t w_part = (size_t)a.MT * 64 * a.group;
-    static const int pref[][3] = {{3, 3, 2}, {2, 3, 2}, {2, 3, 1}, {2, 2, 1}, {1, 3, 1}, {1, 2, 1}};
-    for (const auto &p : pref)
-    {
-        const int xs = p[0] < a.cbs ? p[0] : a.cbs, rs = p[2] < a.cbs ? p[2] : a.cbs;
-        size_t smem = (size_t)rs * raw_part + (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
-        const size_t epilogue = (size_t)a.NPX * (a.MT + 16) * 4;
-        if (smem < epilogue)
-            smem = epilogue;
-        if (smem <= limit)
-        {
-            a.x_slots = xs; a.w_stages = p[1]; a.raw_slots = rs; a.smem_bytes = (unsigned)smem;
-            return true;
-        }
-    }
-    return false;
+    return fit_rings(a, false);
 }
 
 // Tiling and shared-memory plan of one layer; false when the shape is not covered.
@@ -543,15 +676,12 @@ bool plan(const small_b200_layer *L, TcArgs &a)
     a.group = a.Fw; // one kernel row per flush: taps = Fh * Fw is a multiple of it
     if (a.Ho == 0 || a.Wo == 0)
         return true;
-    if (L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r) > 40)
+    if (L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r) > 64)
         return plan_tiled(L, a);
     // GEMM columns of one image: the last valid one is (Ho-1)*PW + Wo-1
     const int m_img = (a.Ho - 1) * a.PW + a.Wo;
-    const size_t limit = 226 * 1024;
     const int tiles256 = (m_img + 255) / 256;
     int npx_first = ((m_img + tiles256 - 1) / tiles256 + 63) / 64 * 64;
-    // {patch slots, filter stages (>= 2: a commit serves both rings), raw patch buffers}
-    static const int pref[][3] = {{2, 3, 1}, {2, 2, 1}, {1, 3, 1}, {1, 2, 1}};
     // First pass: only plans that keep two patches in flight (a layer with few channel blocks
     // per CTA otherwise waits for every patch's load and re-layout), even at a narrower tile;
     // second pass: anything that fits.
@@ -564,26 +694,8 @@ bool plan(const small_b200_layer *L, TcArgs &a)
             a.PR = (need + a.PW - 1) / a.PW;
             if (a.PR > 256)
                 continue;
-            const int entries = a.PR * a.PW;
-            a.x_entries = entries + ((2 - entries % 8) + 8) % 8; // % 8 == 2: conflict-free re-layout
-            const size_t raw_part = ((size_t)entries * 64 + 127) & ~(size_t)127;
-            const size_t x_part = ((size_t)a.x_entries * 64 + 127) & ~(size_t)127;
-            const size_t w_part = (size_t)a.MT * 64 * a.group;
-            for (const auto &p : pref)
-            {
-                const int xs = p[0] < a.cbs ? p[0] : a.cbs, rs = p[2] < a.cbs ? p[2] : a.cbs;
-                if (pass == 0 && xs < (a.cbs < 2 ? a.cbs : 2))
-                    continue;
-                size_t smem = (size_t)rs * raw_part + (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
-                const size_t epilogue = (size_t)npx * (a.MT + 16) * 4; // output staging reuses the buffers
-                if (smem < epilogue)
-                    smem = epilogue;
-                if (smem <= limit)
-                {
-                    a.x_slots = xs; a.w_stages = p[1]; a.raw_slots = rs; a.smem_bytes = (unsigned)smem;
-                    return true;
-                }
-            }
+            if (fit_rings(a, pass == 0))
+                return true;
         }
     return false;
 }
@@ -630,15 +742,26 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     static bool configured = false;
     if (!configured)
     {
-        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         configured = true;
     }
     int *status = device_status_ptr();
     if (!status)
         return fail(SMALL_B200_CUDA_ERROR, "device status word not available");
-    const long long blocks = (long long)a.N * a.px_tiles * a.k_tiles;
-    conv_tf32x3_kernel<<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
-        mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.taps, a, bias, out, status);
+    const long long tiles = (long long)a.N * a.px_tiles * a.k_tiles;
+    if (tiles > 0x7fffffffLL)
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: too many tiles.");
+    a.total_tiles = (int)tiles;
+    long long blocks = tiles;
+    if (a.persistent && blocks > num_sms())
+        blocks = num_sms();
+    if (a.persistent)
+        conv_tf32x3_kernel<true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
+            mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.taps, a, bias, out, status);
+    else
+        conv_tf32x3_kernel<false><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
+            mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.taps, a, bias, out, status);
     return launched("conv_tf32x3_kernel");
 }
 } // extern "C"
