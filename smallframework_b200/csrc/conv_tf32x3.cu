@@ -61,6 +61,7 @@ struct TcArgs
     unsigned stage_off;  // byte offset of the output staging rows (0: they alias the operand buffers)
     int total_tiles;     // N * px_tiles * k_tiles
     int persistent;      // 1: one CTA per SM walks over the tiles; 0: one tile per CTA
+    int ksplit;          // 2: a cluster of two CTAs shares a tile, each reduces half of the channel blocks
 };
 
 // Output channels per CTA, a function of K alone so that filter preparation and the
@@ -167,7 +168,7 @@ __device__ __forceinline__ Tile decode_tile(const TcArgs &a, int t)
 #define SB_TILE_LOOP(cond_extra) \
     for (int t = first_tile, once_ = 0; (PERSIST ? (t < a.total_tiles) : (once_ == 0)) && (cond_extra); t += tile_step, ++once_)
 
-template <bool PERSIST>
+template <bool PERSIST, bool SPLIT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__restrict__ filt,
                    const float *__restrict__ filt_lo, const TcArgs a, const float *__restrict__ bias, float *__restrict__ out, int *status)
@@ -177,6 +178,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     __shared__ __align__(8) uint64_t x_ready[X_SLOTS_MAX], x_empty[X_SLOTS_MAX];
     __shared__ __align__(8) uint64_t w_full[W_STAGES_MAX], g_done[W_STAGES_MAX];
     __shared__ __align__(8) uint64_t t_empty[2];
+    __shared__ __align__(8) uint64_t peer_staged, peer_done; // split reduction: hand-over between the two CTAs
     __shared__ uint32_t tmem_base_s;
 
     const uint32_t entries = (uint32_t)a.PR * a.PW;
@@ -196,21 +198,28 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     while ((int)tmem_cols < 2 * a.NPX)
         tmem_cols <<= 1;
 
+    // Split reduction (one tile per CTA only): the two CTAs of a cluster take one half of the channel
+    // blocks each; rank 1 hands its sums to rank 0 through shared memory at the end.  It turns the
+    // 3.46 waves of the 13x13 layers at batch 64 into 7 half-waves.
+    constexpr bool split = SPLIT && !PERSIST;
+    const uint32_t crank = split ? cluster_ctarank() : 0u;
+    const int cbs_l = split ? a.cbs / 2 : a.cbs;     // channel blocks this CTA reduces
+    const int cb_begin = (int)crank * cbs_l;
     const int steps = a.cbs * a.taps;
-    const int groups = steps / a.group, groups_per_cb = a.taps / a.group;
-    const int first_tile = blockIdx.x, tile_step = gridDim.x;
+    const int groups_per_cb = a.taps / a.group, groups = cbs_l * groups_per_cb;
+    const int first_tile = split ? blockIdx.x / 2 : blockIdx.x, tile_step = gridDim.x;
 
     // patch number pc / group number gc count over every tile of this CTA
     auto issue_patch = [&](const Tile &T, int cb, int pc) {
         const int rs = pc % a.raw_slots;
         mbar_expect_tx(&raw_full[rs], raw_bytes);
         tma_load_4d(sRaw + (size_t)rs * raw_part, &map_x, 0, T.col_base - a.pad_l, T.row_base - a.pad_t,
-                    T.n * a.cbs + cb, &raw_full[rs]);
+                    T.n * a.cbs + cb_begin + cb, &raw_full[rs]);
     };
     auto issue_filter = [&](const Tile &T, int g, int gc) {
         const int st = gc % a.w_stages;
         uint8_t *wd = sW + (size_t)st * 2 * w_half_stage;
-        const size_t off = (size_t)T.kt * a.MT * steps * 16 + (size_t)g * a.group * T.kv * 16;
+        const size_t off = (size_t)T.kt * a.MT * steps * 16 + (size_t)(g + cb_begin * groups_per_cb) * a.group * T.kv * 16;
         mbar_expect_tx(&w_full[st], 2u * a.group * T.kv * 64);
         if (T.kv == a.MT)
         {
@@ -239,6 +248,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                 mbar_init(&w_full[i], 1); mbar_init(&g_done[i], 1);
             }
             for (int i = 0; i < 2; ++i) mbar_init(&t_empty[i], ACC_WARPS);
+            mbar_init(&peer_staged, ACC_WARPS); mbar_init(&peer_done, ACC_WARPS);
             fence_barrier_init();
             // The first patch and the first filter stage only need their barriers: their round
             // trip to memory overlaps the tensor-memory allocation and the CTA-wide barrier.
@@ -251,7 +261,10 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         tmem_relinquish();
     }
     tc_fence_before_sync();
-    __syncthreads();
+    if (split)
+        cluster_sync_all(); // the peer's barriers exist before anybody can arrive on them
+    else
+        __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = tmem_base_s;
 
@@ -317,7 +330,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             {
                 const Tile T = decode_tile(a, t);
                 const uint64_t x_desc0 = x_desc_base + (uint64_t)T.m_local0;
-                for (int cb = 0; cb < a.cbs && ok; ++cb)
+                for (int cb = 0; cb < cbs_l && ok; ++cb)
                 {
                     ok = mbar_wait(&x_ready[slot], xphase, status, 13);
                     if (!ok)
@@ -364,7 +377,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             bool ok = true;
             int pc = 0;
             SB_TILE_LOOP(ok)
-                for (int cb = 0; cb < a.cbs && ok; ++cb, ++pc)
+                for (int cb = 0; cb < cbs_l && ok; ++cb, ++pc)
                 {
                     const int rs = pc % a.raw_slots, slot = pc % a.x_slots, xuse = pc / a.x_slots;
                     ok = mbar_wait(&raw_full[rs], (pc / a.raw_slots) & 1, status, 17);
@@ -479,6 +492,25 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     }
                 }
                 asm volatile("bar.sync 1, 256;" ::: "memory"); // the eight accumulation warps
+                uint32_t peer_stage = 0;
+                if (split)
+                {
+                    if (crank == 1)
+                    {
+                        // hand the staged half-sums to rank 0, then stay until it has read them
+                        if (lane == 0)
+                        {
+                            asm volatile("fence.acq_rel.cluster;" ::: "memory");
+                            mbar_arrive_remote(map_to_cta(&peer_staged, 0));
+                        }
+                        ok = mbar_wait_cluster(&peer_done, 0, status, 21) && false; // rank 1 stores nothing
+                    }
+                    else
+                    {
+                        ok = ok && mbar_wait_cluster(&peer_staged, 0, status, 20);
+                        peer_stage = map_to_cta(stage, 1);
+                    }
+                }
                 if (ok)
                 {
                     for (int pg = warp - FIRST_ACC_WARP; pg < a.NPX / 8; pg += ACC_WARPS)
@@ -490,12 +522,18 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                         if (cl < T.tw_valid && rl < T.th_valid && r < a.Ho)
                         {
                             const float *sp = stage + (size_t)px * pitch + q4 * 4;
+                            const uint32_t rp = peer_stage + (uint32_t)(((size_t)px * pitch + q4 * 4) * 4);
                             float *o = obase + ((size_t)r * a.Wo + c) * CB;
 #pragma unroll
                             for (int kb = 0; kb < 8; ++kb)
                               if (kb < kbs)
                             {
                                 float4 x = *reinterpret_cast<const float4 *>(sp + kb * CB);
+                                if (split)
+                                {
+                                    const float4 y = ld_cluster_f4(rp + (uint32_t)(kb * CB * 4)); // rank 1's half
+                                    x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+                                }
                                 float *ok_ = o + (size_t)kb * plane;
                                 if (a.accumulate)
                                 {
@@ -512,6 +550,13 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                             }
                         }
                     }
+                }
+                if (split && crank == 0)
+                {
+                    // rank 1 may leave: its staging rows have been read
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive_remote(map_to_cta(&peer_done, 1));
                 }
             }
             else
@@ -742,8 +787,9 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     static bool configured = false;
     if (!configured)
     {
-        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         configured = true;
     }
     int *status = device_status_ptr();
@@ -756,11 +802,36 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     long long blocks = tiles;
     if (a.persistent && blocks > num_sms())
         blocks = num_sms();
+    a.ksplit = 1;
+    if (!a.persistent && a.cbs >= 64 && a.cbs % 2 == 0)
+    {
+        // a cluster of two CTAs per tile, each reducing half of the channel blocks, when that
+        // shortens the tail: 512 tiles on 148 SMs are 4 rounds, 1024 half tiles are 7 half rounds
+        const long long sms = num_sms();
+        const long long rounds1 = (tiles + sms - 1) / sms, rounds2 = (2 * tiles + sms - 1) / sms;
+        if (rounds2 * 100 <= rounds1 * 2 * 93)
+        {
+            a.ksplit = 2;
+            blocks = 2 * tiles;
+        }
+    }
     if (a.persistent)
-        conv_tf32x3_kernel<true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
+        conv_tf32x3_kernel<true, false><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
             mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.taps, a, bias, out, status);
+    else if (a.ksplit == 2)
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)blocks); cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = a.smem_bytes; cfg.stream = as_stream(stream);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        const float *flo = filt_prepared + (size_t)a.K * a.C * a.taps;
+        SB_CUDA(cudaLaunchKernelEx(&cfg, conv_tf32x3_kernel<false, true>, mx, filt_prepared, flo, a, bias, out, status));
+    }
     else
-        conv_tf32x3_kernel<false><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
+        conv_tf32x3_kernel<false, false><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
             mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.taps, a, bias, out, status);
     return launched("conv_tf32x3_kernel");
 }
