@@ -20,7 +20,7 @@ DRIVERS = ["test_buffer", "test_tensor", "test_packing", "test_conv2d", "test_co
            "test_partial_conv2d", "test_dw_conv", "test_maxpool", "test_averagepool", "test_relu",
            "test_leaky", "test_softmax", "test_partial_bias", "test_shortcut", "test_upsample2d",
            "test_route_concat", "test_tinyyolov2", "test_resnet8", "test_dscnn",
-           "test_dscnn_square", "test_mobilenet", "test_autoencoder"]
+           "test_dscnn_square", "test_mobilenet", "test_autoencoder", "test_conv1d"]
 
 # Sub-tests that need files the reference's own checkout lacks (its .MISSING_LARGE_BLOBS);
 # they fail on every platform, the CPU ones included.
