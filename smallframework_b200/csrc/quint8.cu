@@ -330,7 +330,7 @@ dwconv_u8_dp4a_kernel(const QArgs a, const uint8_t *__restrict__ in, const uint8
 // strip.  Filter words in shared memory: [cb][half][kw][8 ch] = (w[0][kw], w[1][kw], w[2][kw], 0)
 // as signed bytes.
 template <bool SIGNED_IN, int TW>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 dwconv3x3_u8_rows_kernel(const QArgs a, const uint8_t *__restrict__ in, const uint8_t *__restrict__ filt,
                          const int32_t *__restrict__ bias, uint8_t *__restrict__ out, int strips, int pad_t, int pad_l)
 {

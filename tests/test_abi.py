@@ -48,3 +48,27 @@ def test_argument_errors_need_no_gpu():
     assert b"in_channels unsupported" in l.small_b200_last_error()
     with pytest.raises(ValueError):
         _lib.check(_lib.INVALID_ARGUMENT)
+
+
+def _layer(C_, K, H, W, Fh, Fw, s, pads, N=1):
+    t, b, l, r = pads
+    return _lib.Layer(N, C_, K, H, W, Fh, Fw, s, t, b, l, r, 0, 0, 0.0, 0, 0, 0, 0, 0, 0)
+
+
+def test_shape_queries_need_no_gpu():
+    """Which shapes the tensor-core convolution and the fused convolution + max pool cover is decided
+    on the host (tiling and shared-memory plan), without touching a device."""
+    l = _lib.lib()
+    tc = lambda *a: bool(l.small_b200_conv2d_f32_tf32x3_supported(ctypes.byref(_layer(*a))))
+    assert tc(1024, 1024, 13, 13, 3, 3, 1, (1, 1, 1, 1), 64)      # Tiny-YOLOv2 conv8: rows of the full width
+    assert tc(32, 64, 104, 104, 3, 3, 1, (1, 1, 1, 1), 64)        # conv3: TH x TW pixel tiles
+    assert tc(16, 32, 416, 416, 3, 3, 1, (1, 1, 1, 1))            # any width
+    assert tc(1024, 128, 13, 13, 1, 1, 1, (0, 0, 0, 0))           # pointwise
+    assert not tc(16, 32, 32, 32, 3, 3, 2, (0, 1, 0, 1))          # stride 2: CUDA-core kernel
+    assert not tc(3, 16, 32, 32, 3, 3, 1, (1, 1, 1, 1))           # first layer
+    assert not tc(16, 24, 32, 32, 3, 3, 1, (1, 1, 1, 1))          # 24 output channels: not a multiple of 16
+    fused = lambda conv, pool: bool(l.small_b200_conv2d_maxpool_f32_supported(ctypes.byref(conv), ctypes.byref(pool)))
+    conv = _layer(3, 16, 416, 416, 3, 3, 1, (1, 1, 1, 1), 4)
+    assert fused(conv, _layer(16, 16, 416, 416, 2, 2, 2, (0, 0, 0, 0), 4))
+    assert not fused(conv, _layer(16, 16, 416, 416, 2, 2, 1, (0, 1, 0, 1), 4))   # stride-1 pool
+    assert not fused(conv, _layer(16, 16, 208, 208, 2, 2, 2, (0, 0, 0, 0), 4))   # pool of another tensor
