@@ -98,7 +98,7 @@ prepare_filter_kernel(long long n, int slabs, int MT, int K, const float *__rest
 // round-to-nearest, while the tensor core already works on the next group of taps in the second
 // half of tensor memory.
 //
-// warp 0: TMA producer, warp 1: MMA issuer (warps 2..3 idle), warps 4..11: accumulation +
+// warp 0: TMA producer, warps 1..2: MMA issuers (warp 3 idle), warps 4..11: accumulation +
 // epilogue (lane quarter = warp % 4, pixel half = (warp - 4) / 4), warps 12..15: operand
 // splitters (patch re-layout and lo copies).  The first and last warpgroups give registers
 // back (setmaxnreg) so that the accumulation warps can hold 128 running sums per thread
@@ -242,7 +242,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         if (lane == 0)
         {
             for (int i = 0; i < RAW_SLOTS_MAX; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], SPLIT_THREADS); }
-            for (int i = 0; i < X_SLOTS_MAX; ++i) { mbar_init(&x_ready[i], SPLIT_THREADS); mbar_init(&x_empty[i], 1); }
+            for (int i = 0; i < X_SLOTS_MAX; ++i) { mbar_init(&x_ready[i], SPLIT_THREADS); mbar_init(&x_empty[i], 2); }
             for (int i = 0; i < W_STAGES_MAX; ++i)
             {
                 mbar_init(&w_full[i], 1); mbar_init(&g_done[i], 1);
@@ -305,16 +305,20 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                 }
             }
         }
-        else if (warp == 1 && lane == 0)
+        else if ((warp == 1 || warp == 2) && lane == 0)
         {
-            // ---------------- MMA issuer ----------------
-            // One thread feeds the tensor core: all descriptor fields except the
-            // 16-byte-granular start address are fixed per CTA, and a new operand position is one
-            // 64-bit add on a precomputed descriptor.  A = filter tap (M = channels), B = patch
-            // shifted by the tap (N = pixels).
-            // The tensor pipe's queue holds only a handful of MMAs, so whatever this thread does
-            // between two groups beyond issuing (waits, commits, index arithmetic) shows up as
-            // idle tensor cycles: the loop keeps its counters incrementally, no divisions.
+            // ---------------- MMA issuers ----------------
+            // All descriptor fields except the 16-byte-granular start address are fixed per CTA,
+            // and a new operand position is one 64-bit add on a precomputed descriptor.  A = filter
+            // tap (M = channels), B = patch shifted by the tap (N = pixels).
+            // Issuing one MMA costs a thread about as long as the tensor pipe needs for it
+            // (measured: one thread sustains an N = 192 MMA every 122 cycles, the pipe takes 96;
+            // two threads together reach the 96), and whatever the thread does between two groups
+            // (three barrier waits of about 200 cycles each, the commit) is idle tensor time on top.
+            // Two threads therefore take the groups in turn, one per tensor-memory buffer: while
+            // one waits for its filter stage and its buffer, the other one's MMAs keep the pipe
+            // busy.  The groups are independent sums, so the two threads need no order between them.
+            const int me = warp - 1; // this thread issues the groups with (g & 1) == me
             bool ok = true;
             const uint64_t x_desc_base = make_smem_desc(smem_u32(sX), x_chunk, 128, 0);
             const uint64_t w_desc0 = make_smem_desc(smem_u32(sW), w_chunk, 128, 0);
@@ -338,33 +342,35 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     uint64_t x_row = x_desc0 + x_slot_off; // patch position of tap (kh, 0)
                     for (int gi = 0; gi < groups_per_cb && ok; ++gi, ++g)
                     {
-                        const int tb = g & 1; // tensor-memory buffer of this group
-                        ok = mbar_wait(&w_full[st], wphase, status, 14);
-                        if (ok && g >= 2)
-                            ok = mbar_wait(&t_empty[tb], ((g >> 1) - 1) & 1, status, 16);
-                        if (!ok)
-                            break;
-                        tc_fence_after_sync();
-                        const uint32_t d = tmem + (uint32_t)(tb * a.NPX);
-                        uint64_t wh = w_stage, xh = x_row;
-                        for (int tp = 0; tp < a.group; ++tp, wh += w_tap, ++xh)
+                        if ((g & 1) == me)
                         {
-                            const uint64_t xl = xh + x_lo_off, wl = wh + w_lo_off;
-                            tc_mma_tf32(d, wl, xh, idesc, tp == 0 ? 0u : 1u);
-                            tc_mma_tf32(d, wh, xl, idesc, 1u);
-                            tc_mma_tf32(d, wh, xh, idesc, 1u);
-                            tc_mma_tf32(d, wl + w_half, xh + x_half, idesc, 1u);
-                            tc_mma_tf32(d, wh + w_half, xl + x_half, idesc, 1u);
-                            tc_mma_tf32(d, wh + w_half, xh + x_half, idesc, 1u);
+                            ok = mbar_wait(&w_full[st], wphase, status, 14);
+                            if (ok && g >= 2)
+                                ok = mbar_wait(&t_empty[me], ((g >> 1) - 1) & 1, status, 16);
+                            if (!ok)
+                                break;
+                            tc_fence_after_sync();
+                            const uint32_t d = tmem + (uint32_t)(me * a.NPX); // tensor-memory buffer g & 1
+                            uint64_t wh = w_stage, xh = x_row;
+                            for (int tp = 0; tp < a.group; ++tp, wh += w_tap, ++xh)
+                            {
+                                const uint64_t xl = xh + x_lo_off, wl = wh + w_lo_off;
+                                tc_mma_tf32(d, wl, xh, idesc, tp == 0 ? 0u : 1u);
+                                tc_mma_tf32(d, wh, xl, idesc, 1u);
+                                tc_mma_tf32(d, wh, xh, idesc, 1u);
+                                tc_mma_tf32(d, wl + w_half, xh + x_half, idesc, 1u);
+                                tc_mma_tf32(d, wh + w_half, xl + x_half, idesc, 1u);
+                                tc_mma_tf32(d, wh + w_half, xh + x_half, idesc, 1u);
+                            }
+                            // one commit: the stage is free for the producer and the group's partial
+                            // sums are complete for the accumulation warps
+                            tc_commit(&g_done[st]);
                         }
-                        // one commit: the stage is free for the producer and the group's partial
-                        // sums are complete for the accumulation warps
-                        tc_commit(&g_done[st]);
                         x_row += (uint64_t)(a.group == a.Fw ? a.PW : 1);
                         w_stage += w_stage_step;
                         if (++st == a.w_stages) { st = 0; wphase ^= 1; w_stage = w_desc0; }
                     }
-                    tc_commit(&x_empty[slot]);
+                    tc_commit(&x_empty[slot]); // both issuers: the slot is free once the MMAs of either are done
                     x_slot_off += x_slot_step;
                     if (++slot == a.x_slots) { slot = 0; xphase ^= 1; x_slot_off = 0; }
                 }
