@@ -7,22 +7,28 @@
 //
 // GEMM orientation: D[k][pixel] = sum_c W[k][c] * X[pixel][c].  The output channels are the
 // tensor core's M (one tile of 128, or 64 for layers with fewer channels), the pixels its N
-// (64..256 per CTA).  One tcgen05.mma of kind::tf32 covers only 8 input channels and costs about
-// 32 + N/2 cycles whatever M is (measured: 97 cycles at N = 128, 161 at N = 256), so wide-N
-// instructions are what keeps the tensor pipe busy.
+// (64..256 per CTA).  One tcgen05.mma of kind::tf32 covers only 8 input channels and occupies
+// the tensor pipe for N/2 cycles whatever M is, with a floor of about 80 cycles (measured with
+// two issuing threads: 83 cycles at N = 128, 96 at N = 192, 128 at N = 256), so wide-N instructions
+// are what keeps the pipe busy.  Every MMA reads its operands from shared memory (10 KB at N = 192):
+// at full rate that alone is 107 of the 128 bytes per cycle shared memory delivers, which makes
+// shared-memory bandwidth, not the tensor pipe, the ceiling of the wide layers.
 //
 // Implicit GEMM without im2col ("linear shift"):
 //   For one image and one block of 16 input channels, TMA copies a patch of the packed
 //   activations [rows][PW columns][16 ch] (64 bytes per pixel) into shared memory.
 //   PW = W + max(pad_l, pad_r): the zero column(s) that TMA's out-of-bounds fill produces at the
-//   left edge of every row also serve as the right padding of the row above.  Two splitter warps
-//   re-lay the patch into the tensor core's K-major no-swizzle canonical layout
-//   [4-channel chunk][entry][4 floats] and write the lo copy next to it.  Output pixel (r, c) is
-//   GEMM column m = r*PW + c, and filter tap (kh, kw) of that pixel sits at patch entry
-//   m + kh*PW + kw: consecutive pixels are consecutive 16-byte entries for EVERY tap, so a tap
-//   only moves the descriptor's start address.  Columns with c >= Wo are junk and are not stored.
-//   (Letting TMA write the chunked layout directly needs 16-byte box rows, which it moves at
-//   about one row per 9 cycles: that, not the MMAs, bounded the first version of this kernel.)
+//   left edge of every row also serve as the right padding of the row above.  The copy writes
+//   the patch in the 64-byte swizzle, and that IS a K-major operand of the tensor core: rows of
+//   64 bytes (one pixel's 16 channels), 8-pixel groups 512 bytes apart; the hardware applies the
+//   swizzle to absolute shared-memory addresses, so a descriptor may start at any pixel.  The raw
+//   fp32 patch serves as the hi operand as it is; four splitter warps write the lo copy to the
+//   same offsets of a second buffer.  Output pixel (r, c) is GEMM column m = r*PW + c, and filter
+//   tap (kh, kw) of that pixel sits at patch entry m + kh*PW + kw: consecutive pixels are
+//   consecutive rows for EVERY tap, so a tap only moves the descriptor's start address by 64 bytes
+//   per pixel.  Columns with c >= Wo are junk and are not stored.
+//   (A no-swizzle K-major patch needs 16-byte box rows from TMA, which it moves at about one row
+//   per 9 cycles, or a re-layout pass through shared memory: both were slower.)
 //   The filter [K/16][C/16][tap][16 c][16 k] has the output channel contiguous (MN-major).
 //   kind::tf32 did not accept an MN-major no-swizzle operand on this hardware (a one-MMA
 //   experiment returned zeros, while the K-major form was exact), so the filter is re-laid once
@@ -39,7 +45,6 @@ using namespace sb;
 
 constexpr int W_STAGES_MAX = 4; // filter stages, each one group of taps (a kernel row)
 constexpr int X_SLOTS_MAX = 3;
-constexpr int RAW_SLOTS_MAX = 2;
 
 struct TcArgs
 {
@@ -52,8 +57,7 @@ struct TcArgs
     int TW, TH, tiles_x; // tiled mode: valid columns / rows of a tile, tiles per row of tiles
     int MT;            // output channels per CTA (tensor-core M): 128 or 64
     int k_tiles;       // ceil(K / MT)
-    int x_entries;     // entries between the 4-channel chunks of a canonical patch (>= PR*PW)
-    int x_slots, raw_slots, w_stages;
+    int x_slots, w_stages;
     int group;         // filter taps summed in tensor memory before a flush
     int accumulate, act;
     float slope;
@@ -100,15 +104,13 @@ prepare_filter_kernel(long long n, int slabs, int MT, int K, const float *__rest
 //
 // warp 0: TMA producer, warps 1..2: MMA issuers (warp 3 idle), warps 4..11: accumulation +
 // epilogue (lane quarter = warp % 4, pixel half = (warp - 4) / 4), warps 12..15: operand
-// splitters (patch re-layout and lo copies).  The first and last warpgroups give registers
+// splitters (lo copy of every patch).  The first and last warpgroups give registers
 // back (setmaxnreg) so that the accumulation warps can hold 128 running sums per thread
 // without spilling.
 //
-// The unit of the filter pipeline is a GROUP of taps (one kernel row): one bulk copy, one pass
-// of the splitters, one tcgen05.commit.  A commit keeps the issuing thread busy for several
-// hundred cycles (measured: about 500), so with one commit per tap the single MMA thread, not
-// the tensor pipe, set the pace.  The same commit frees the filter stage for the producer and
-// hands the partial sums to the accumulation warps.
+// The unit of the filter pipeline is a GROUP of taps (one kernel row): one bulk copy and one
+// tcgen05.commit, which frees the filter stage for the producer and hands the partial sums to
+// the accumulation warps.
 constexpr int ACC_WARPS = 8;
 constexpr int FIRST_ACC_WARP = 4;
 constexpr int FIRST_SPLIT_WARP = 12;
@@ -174,22 +176,18 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                    const float *__restrict__ filt_lo, const TcArgs a, const float *__restrict__ bias, float *__restrict__ out, int *status)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t raw_full[RAW_SLOTS_MAX], raw_empty[RAW_SLOTS_MAX];
-    __shared__ __align__(8) uint64_t x_ready[X_SLOTS_MAX], x_empty[X_SLOTS_MAX];
+    __shared__ __align__(8) uint64_t x_full[X_SLOTS_MAX], x_ready[X_SLOTS_MAX], x_empty[X_SLOTS_MAX];
     __shared__ __align__(8) uint64_t w_full[W_STAGES_MAX], g_done[W_STAGES_MAX];
     __shared__ __align__(8) uint64_t t_empty[2];
     __shared__ __align__(8) uint64_t peer_staged, peer_done; // split reduction: hand-over between the two CTAs
     __shared__ uint32_t tmem_base_s;
 
     const uint32_t entries = (uint32_t)a.PR * a.PW;
-    const uint32_t raw_bytes = entries * 64;                    // one raw patch [entry][16 floats]
-    const uint32_t raw_part = (raw_bytes + 127u) & ~127u;
-    const uint32_t x_chunk = (uint32_t)a.x_entries * 16;       // bytes between channel chunks
-    const uint32_t x_part = (4 * x_chunk + 127u) & ~127u;      // one canonical hi (or lo) patch
+    const uint32_t x_bytes = entries * 64;                      // one patch [entry][16 floats]
+    const uint32_t x_part = (x_bytes + 1023u) & ~1023u;         // hi (or lo) copy; keeps the swizzle pattern anchored
     const uint32_t w_part = (uint32_t)a.MT * 64;               // one hi (or lo) tap tile
     const uint32_t w_chunk = (uint32_t)a.MT * 16;
-    uint8_t *sRaw = smem;                                            // [raw slot][entry][64 B]
-    uint8_t *sX = sRaw + (size_t)a.raw_slots * raw_part;            // [slot][hi|lo][chunk][entry][16 B]
+    uint8_t *sX = smem;                                              // [slot][hi|lo][entry][64 B, 64-byte swizzle]
     uint8_t *sW = sX + (size_t)a.x_slots * 2 * x_part;              // [stage][hi|lo][tap in group][c/4][MT k][16 B]
     const uint32_t w_half_stage = (uint32_t)a.group * w_part;       // hi (or lo) tiles of one stage
 
@@ -211,10 +209,10 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
 
     // patch number pc / group number gc count over every tile of this CTA
     auto issue_patch = [&](const Tile &T, int cb, int pc) {
-        const int rs = pc % a.raw_slots;
-        mbar_expect_tx(&raw_full[rs], raw_bytes);
-        tma_load_4d(sRaw + (size_t)rs * raw_part, &map_x, 0, T.col_base - a.pad_l, T.row_base - a.pad_t,
-                    T.n * a.cbs + cb_begin + cb, &raw_full[rs]);
+        const int slot = pc % a.x_slots;
+        mbar_expect_tx(&x_full[slot], x_bytes);
+        tma_load_4d(sX + (size_t)slot * 2 * x_part, &map_x, 0, T.col_base - a.pad_l, T.row_base - a.pad_t,
+                    T.n * a.cbs + cb_begin + cb, &x_full[slot]);
     };
     auto issue_filter = [&](const Tile &T, int g, int gc) {
         const int st = gc % a.w_stages;
@@ -241,8 +239,10 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     {
         if (lane == 0)
         {
-            for (int i = 0; i < RAW_SLOTS_MAX; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], SPLIT_THREADS); }
-            for (int i = 0; i < X_SLOTS_MAX; ++i) { mbar_init(&x_ready[i], SPLIT_THREADS); mbar_init(&x_empty[i], 2); }
+            for (int i = 0; i < X_SLOTS_MAX; ++i)
+            {
+                mbar_init(&x_full[i], 1); mbar_init(&x_ready[i], SPLIT_THREADS); mbar_init(&x_empty[i], 2);
+            }
             for (int i = 0; i < W_STAGES_MAX; ++i)
             {
                 mbar_init(&w_full[i], 1); mbar_init(&g_done[i], 1);
@@ -285,9 +285,9 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     {
                         if (pc > 0) // patch 0 of the first tile is already on its way
                         {
-                            const int rs = pc % a.raw_slots, ruse = pc / a.raw_slots;
-                            if (ruse > 0)
-                                ok = mbar_wait(&raw_empty[rs], (ruse - 1) & 1, status, 11);
+                            const int slot = pc % a.x_slots, xuse = pc / a.x_slots;
+                            if (xuse > 0) // both issuers' MMAs on the slot's previous patch are done
+                                ok = mbar_wait(&x_empty[slot], (xuse - 1) & 1, status, 11);
                             if (!ok)
                                 break;
                             issue_patch(T, g / groups_per_cb, pc);
@@ -320,12 +320,14 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             // busy.  The groups are independent sums, so the two threads need no order between them.
             const int me = warp - 1; // this thread issues the groups with (g & 1) == me
             bool ok = true;
-            const uint64_t x_desc_base = make_smem_desc(smem_u32(sX), x_chunk, 128, 0);
+            // patch: rows of 64 bytes (one pixel's 16 channels) in the 64-byte swizzle the bulk copy
+            // wrote; 8-pixel groups are 512 bytes apart; a pixel further is 4 descriptor units
+            const uint64_t x_desc_base = make_smem_desc(smem_u32(sX), 16, 512, 4);
             const uint64_t w_desc0 = make_smem_desc(smem_u32(sW), w_chunk, 128, 0);
             const uint32_t idesc = make_idesc(1 /*f32*/, 2 /*tf32*/, 2 /*tf32*/, 0 /*A K-major*/, 0 /*B K-major*/,
                                               (uint32_t)a.MT, (uint32_t)a.NPX);
             const uint64_t x_lo_off = x_part >> 4, w_lo_off = w_half_stage >> 4, w_tap = w_part >> 4;
-            const uint64_t x_half = (2 * x_chunk) >> 4, w_half = (2 * w_chunk) >> 4;
+            const uint64_t x_half = 2, w_half = (2 * w_chunk) >> 4; // channels 8..15 of the block
             const uint64_t w_stage_step = (uint64_t)2 * w_half_stage >> 4;
             const uint64_t x_slot_step = (uint64_t)2 * x_part >> 4;
             int slot = 0, xphase = 0, st = 0, wphase = 0, g = 0; // g counts groups over all tiles
@@ -333,7 +335,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             SB_TILE_LOOP(ok)
             {
                 const Tile T = decode_tile(a, t);
-                const uint64_t x_desc0 = x_desc_base + (uint64_t)T.m_local0;
+                const uint64_t x_desc0 = x_desc_base + (uint64_t)T.m_local0 * 4;
                 for (int cb = 0; cb < cbs_l && ok; ++cb)
                 {
                     ok = mbar_wait(&x_ready[slot], xphase, status, 13);
@@ -352,7 +354,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                             tc_fence_after_sync();
                             const uint32_t d = tmem + (uint32_t)(me * a.NPX); // tensor-memory buffer g & 1
                             uint64_t wh = w_stage, xh = x_row;
-                            for (int tp = 0; tp < a.group; ++tp, wh += w_tap, ++xh)
+                            for (int tp = 0; tp < a.group; ++tp, wh += w_tap, xh += 4)
                             {
                                 const uint64_t xl = xh + x_lo_off, wl = wh + w_lo_off;
                                 tc_mma_tf32(d, wl, xh, idesc, tp == 0 ? 0u : 1u);
@@ -366,7 +368,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                             // sums are complete for the accumulation warps
                             tc_commit(&g_done[st]);
                         }
-                        x_row += (uint64_t)(a.group == a.Fw ? a.PW : 1);
+                        x_row += (uint64_t)(a.group == a.Fw ? a.PW : 1) * 4;
                         w_stage += w_stage_step;
                         if (++st == a.w_stages) { st = 0; wphase ^= 1; w_stage = w_desc0; }
                     }
@@ -385,30 +387,22 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             SB_TILE_LOOP(ok)
                 for (int cb = 0; cb < cbs_l && ok; ++cb, ++pc)
                 {
-                    const int rs = pc % a.raw_slots, slot = pc % a.x_slots, xuse = pc / a.x_slots;
-                    ok = mbar_wait(&raw_full[rs], (pc / a.raw_slots) & 1, status, 17);
-                    if (ok && xuse > 0)
-                        ok = mbar_wait(&x_empty[slot], (xuse - 1) & 1, status, 19);
+                    const int slot = pc % a.x_slots;
+                    ok = mbar_wait(&x_full[slot], (pc / a.x_slots) & 1, status, 17);
                     if (!ok)
                         break;
                     {
-                        // [entry][chunk] -> [chunk][entry], hi and lo.  A quarter warp reads 128
-                        // contiguous bytes; x_entries % 8 == 2 spreads its four chunk rows over
-                        // different banks on the way out.
-                        const uint8_t *raw = sRaw + (size_t)rs * raw_part;
-                        uint8_t *xh = sX + (size_t)slot * 2 * x_part, *xl = xh + x_part;
+                        // The patch as the bulk copy wrote it is the hi operand (the tensor core
+                        // ignores the 13 low mantissa bits of an fp32 word read as tf32); the lo copy
+                        // takes the same place in its own buffer, so the swizzle needs no thought.
+                        const float4 *xh = reinterpret_cast<const float4 *>(sX + (size_t)slot * 2 * x_part);
+                        float4 *xl = reinterpret_cast<float4 *>(sX + (size_t)slot * 2 * x_part + x_part);
                         const uint32_t total = entries * 4;
                         for (uint32_t i = (uint32_t)sid; i < total; i += SPLIT_THREADS)
-                        {
-                            const float4 v = *reinterpret_cast<const float4 *>(raw + (size_t)i * 16);
-                            const uint32_t o = (i & 3u) * x_chunk + (i >> 2) * 16u;
-                            *reinterpret_cast<float4 *>(xh + o) = v;
-                            *reinterpret_cast<float4 *>(xl + o) = lo_of(v);
-                        }
+                            xl[i] = lo_of(xh[i]);
                     }
                     fence_proxy_async();
                     mbar_arrive(&x_ready[slot]);
-                    mbar_arrive(&raw_empty[rs]);
                 }
         }
     }
@@ -641,27 +635,25 @@ bool fit_rings(TcArgs &a, bool need_two)
 {
     const size_t limit = 226 * 1024;
     const int entries = a.PR * a.PW;
-    a.x_entries = entries + ((2 - entries % 8) + 8) % 8; // % 8 == 2: conflict-free re-layout
-    const size_t raw_part = ((size_t)entries * 64 + 127) & ~(size_t)127;
-    const size_t x_part = ((size_t)a.x_entries * 64 + 127) & ~(size_t)127;
+    const size_t x_part = ((size_t)entries * 64 + 1023) & ~(size_t)1023;
     const size_t w_part = (size_t)a.MT * 64 * a.group;
     const size_t staging = (size_t)64 * (a.MT + 16) * 4; // 32 pixels of each half of the tile
-    // {patch slots, filter stages (>= 2: a commit serves both rings), raw patch buffers}
-    static const int pref[][3] = {{3, 3, 2}, {2, 3, 2}, {2, 3, 1}, {2, 2, 1}, {1, 3, 1}, {1, 2, 1}};
+    // {patch slots, filter stages (>= 2: a commit serves both rings)}
+    static const int pref[][2] = {{3, 3}, {2, 3}, {2, 2}, {1, 3}, {1, 2}};
     // persistent where it pays and fits: narrow layers (64-channel tiles: small filter stages and
     // staging rows, little work per tile); wide ones need the shared memory for deeper rings
     for (int persistent = (a.MT == 64 ? 1 : 0); persistent >= 0; --persistent)
         for (const auto &p : pref)
         {
-            const int xs = p[0] < a.cbs || persistent ? p[0] : a.cbs, rs = p[2] < a.cbs || persistent ? p[2] : a.cbs;
+            const int xs = p[0] < a.cbs || persistent ? p[0] : a.cbs;
             if (need_two && xs < 2 && a.cbs >= 2)
                 continue;
-            const size_t ops = (size_t)rs * raw_part + (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
+            const size_t ops = (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
             const size_t full = (size_t)a.NPX * (a.MT + 16) * 4; // one tile per CTA stages the whole tile
             const size_t smem = persistent ? ops + staging : (ops > full ? ops : full);
             if (smem <= limit)
             {
-                a.x_slots = xs; a.w_stages = p[1]; a.raw_slots = rs; a.smem_bytes = (unsigned)smem;
+                a.x_slots = xs; a.w_stages = p[1]; a.smem_bytes = (unsigned)smem;
                 a.persistent = persistent; a.stage_off = persistent ? (unsigned)ops : 0u;
                 return true;
             }
@@ -734,7 +726,7 @@ bool plan(const small_b200_layer *L, TcArgs &a)
     const int tiles256 = (m_img + 255) / 256;
     int npx_first = ((m_img + tiles256 - 1) / tiles256 + 63) / 64 * 64;
     // First pass: only plans that keep two patches in flight (a layer with few channel blocks
-    // per CTA otherwise waits for every patch's load and re-layout), even at a narrower tile;
+    // per CTA otherwise waits for every patch's load and lo copy), even at a narrower tile;
     // second pass: anything that fits.
     for (int pass = 0; pass < 2; ++pass)
         for (int npx = npx_first; npx >= (pass == 0 ? 128 : 64); npx -= 64)
@@ -787,7 +779,7 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
         const uint64_t dims[4] = {16, (uint64_t)a.W, (uint64_t)a.H, (uint64_t)a.N * a.cbs};
         const uint64_t strides[3] = {64, (uint64_t)a.W * 64, (uint64_t)a.H * a.W * 64};
         const uint32_t box[4] = {16, (uint32_t)a.PW, (uint32_t)a.PR, 1};
-        if (int rc = make_tensor_map(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, in, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+        if (int rc = make_tensor_map(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, in, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;
     }
     static bool configured = false;
