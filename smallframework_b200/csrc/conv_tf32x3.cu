@@ -14,6 +14,12 @@
 // at full rate that alone is 107 of the 128 bytes per cycle shared memory delivers, which makes
 // shared-memory bandwidth, not the tensor pipe, the ceiling of the wide layers.
 //
+// Layers with 32 or 64 output channels turn the GEMM around (PIXM): 128 pixels are the M of one MMA
+// and all output channels its N, D[pixel][k].  Both dimensions of the instruction are then used in
+// full (a 64-row M costs the same pipe time as 128 rows), an MMA takes N/2 = 16 or 32 cycles, and a
+// thread of the accumulation warps owns one pixel with all its channels: its sums go to the packed
+// output as 64-byte runs without any transposition.  Three threads issue the MMAs there.
+//
 // Implicit GEMM without im2col ("linear shift"):
 //   For one image and one block of 16 input channels, TMA copies a patch of the packed
 //   activations [rows][PW columns][16 ch] (64 bytes per pixel) into shared memory.
@@ -58,6 +64,8 @@ struct TcArgs
     int MT;            // output channels per CTA (tensor-core M): 128 or 64
     int k_tiles;       // ceil(K / MT)
     int x_slots, w_stages;
+    int pixm;          // 1: pixels on the tensor core's M, output channels on its N (K = 32 or 64)
+    int tbufs;         // accumulator buffers in tensor memory: 2, or 4 when 4 * NPX <= 512 columns
     int group;         // filter taps summed in tensor memory before a flush
     int accumulate, act;
     float slope;
@@ -99,8 +107,9 @@ prepare_filter_kernel(long long n, int slabs, int MT, int K, const float *__rest
 // here: 3e-5 of the output range after 1700 MMAs).  So tensor memory only ever holds the sum
 // of one kernel row of one channel block (6 MMAs per tap); eight accumulation warps pull
 // these partial sums out with tcgen05.ld and add them into fp32 registers with
-// round-to-nearest, while the tensor core already works on the next group of taps in the second
-// half of tensor memory.
+// round-to-nearest, while the tensor core already works on the next groups of taps in the other
+// accumulator buffers of tensor memory (two of 192 or 256 columns, four when a buffer needs at
+// most 128).
 //
 // warp 0: TMA producer, warps 1..2: MMA issuers (warp 3 idle), warps 4..11: accumulation +
 // epilogue (lane quarter = warp % 4, pixel half = (warp - 4) / 4), warps 12..15: operand
@@ -170,7 +179,7 @@ __device__ __forceinline__ Tile decode_tile(const TcArgs &a, int t)
 #define SB_TILE_LOOP(cond_extra) \
     for (int t = first_tile, once_ = 0; (PERSIST ? (t < a.total_tiles) : (once_ == 0)) && (cond_extra); t += tile_step, ++once_)
 
-template <bool PERSIST, bool SPLIT>
+template <bool PERSIST, bool SPLIT, bool PIXM = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__restrict__ filt,
                    const float *__restrict__ filt_lo, const TcArgs a, const float *__restrict__ bias, float *__restrict__ out, int *status)
@@ -178,7 +187,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t x_full[X_SLOTS_MAX], x_ready[X_SLOTS_MAX], x_empty[X_SLOTS_MAX];
     __shared__ __align__(8) uint64_t w_full[W_STAGES_MAX], g_done[W_STAGES_MAX];
-    __shared__ __align__(8) uint64_t t_empty[2];
+    __shared__ __align__(8) uint64_t t_full[4], t_empty[4];
     __shared__ __align__(8) uint64_t peer_staged, peer_done; // split reduction: hand-over between the two CTAs
     __shared__ uint32_t tmem_base_s;
 
@@ -186,14 +195,13 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     const uint32_t x_bytes = entries * 64;                      // one patch [entry][16 floats]
     const uint32_t x_part = (x_bytes + 1023u) & ~1023u;         // hi (or lo) copy; keeps the swizzle pattern anchored
     const uint32_t w_part = (uint32_t)a.MT * 64;               // one hi (or lo) tap tile
-    const uint32_t w_chunk = (uint32_t)a.MT * 16;
     uint8_t *sX = smem;                                              // [slot][hi|lo][entry][64 B, 64-byte swizzle]
     uint8_t *sW = sX + (size_t)a.x_slots * 2 * x_part;              // [stage][hi|lo][tap in group][c/4][MT k][16 B]
     const uint32_t w_half_stage = (uint32_t)a.group * w_part;       // hi (or lo) tiles of one stage
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint32_t tmem_cols = 32;
-    while ((int)tmem_cols < 2 * a.NPX)
+    while ((int)tmem_cols < (PIXM ? a.tbufs * (a.NPX >> 7) * a.K : a.tbufs * a.NPX))
         tmem_cols <<= 1;
 
     // Split reduction (one tile per CTA only): the two CTAs of a cluster take one half of the channel
@@ -219,20 +227,10 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         uint8_t *wd = sW + (size_t)st * 2 * w_half_stage;
         const size_t off = (size_t)T.kt * a.MT * steps * 16 + (size_t)(g + cb_begin * groups_per_cb) * a.group * T.kv * 16;
         mbar_expect_tx(&w_full[st], 2u * a.group * T.kv * 64);
-        if (T.kv == a.MT)
-        {
-            tma_load_1d(wd, filt + off, w_half_stage, &w_full[st]); // the group's taps are contiguous
-            tma_load_1d(wd + w_half_stage, filt_lo + off, w_half_stage, &w_full[st]);
-        }
-        else
-            for (int t = 0; t < a.group; ++t)
-                for (int j = 0; j < 4; ++j) // partial tile: kv of MT rows per 4-channel chunk
-                {
-                    const size_t o = off + ((size_t)t * 4 + j) * T.kv * 4;
-                    tma_load_1d(wd + t * w_part + j * w_chunk, filt + o, (uint32_t)T.kv * 16, &w_full[st]);
-                    tma_load_1d(wd + w_half_stage + t * w_part + j * w_chunk, filt_lo + o, (uint32_t)T.kv * 16,
-                                &w_full[st]);
-                }
+        // the group's taps are contiguous, [tap][c/4][kv k][4 c]: a partial last tile (kv < MT) simply
+        // is a shorter run, and the MMA descriptors take kv * 16 bytes as the chunk stride
+        tma_load_1d(wd, filt + off, (uint32_t)a.group * T.kv * 64, &w_full[st]);
+        tma_load_1d(wd + w_half_stage, filt_lo + off, (uint32_t)a.group * T.kv * 64, &w_full[st]);
     };
 
     if (warp == 0)
@@ -241,13 +239,13 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         {
             for (int i = 0; i < X_SLOTS_MAX; ++i)
             {
-                mbar_init(&x_full[i], 1); mbar_init(&x_ready[i], SPLIT_THREADS); mbar_init(&x_empty[i], 2);
+                mbar_init(&x_full[i], 1); mbar_init(&x_ready[i], SPLIT_THREADS); mbar_init(&x_empty[i], PIXM ? 3 : 2);
             }
             for (int i = 0; i < W_STAGES_MAX; ++i)
             {
                 mbar_init(&w_full[i], 1); mbar_init(&g_done[i], 1);
             }
-            for (int i = 0; i < 2; ++i) mbar_init(&t_empty[i], ACC_WARPS);
+            for (int i = 0; i < 4; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], ACC_WARPS); }
             mbar_init(&peer_staged, ACC_WARPS); mbar_init(&peer_done, ACC_WARPS);
             fence_barrier_init();
             // The first patch and the first filter stage only need their barriers: their round
@@ -305,7 +303,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                 }
             }
         }
-        else if ((warp == 1 || warp == 2) && lane == 0)
+        else if (warp >= 1 && warp <= (PIXM ? 3 : 2) && lane == 0)
         {
             // ---------------- MMA issuers ----------------
             // All descriptor fields except the 16-byte-granular start address are fixed per CTA,
@@ -318,24 +316,33 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             // Two threads therefore take the groups in turn, one per tensor-memory buffer: while
             // one waits for its filter stage and its buffer, the other one's MMAs keep the pipe
             // busy.  The groups are independent sums, so the two threads need no order between them.
-            const int me = warp - 1; // this thread issues the groups with (g & 1) == me
+            // Pixel-major tiles (PIXM: M = 128 pixels, N = all 32 or 64 output channels) have cheap
+            // MMAs (N/2 cycles each), so a third thread joins to keep up with the pipe.
+            constexpr int NISS = PIXM ? 3 : 2;
+            const int me = warp - 1; // this thread issues the groups with g % NISS == me
+            int turn = 0;            // g % NISS
+            const bool own_t_full = PIXM || a.tbufs > a.w_stages;
+            const int mtiles = a.NPX >> 7; // PIXM: blocks of 128 pixels per tile
+            const int tb_mask = a.tbufs - 1, tb_shift = a.tbufs == 4 ? 2 : 1; // group g sums in buffer g % tbufs
             bool ok = true;
             // patch: rows of 64 bytes (one pixel's 16 channels) in the 64-byte swizzle the bulk copy
             // wrote; 8-pixel groups are 512 bytes apart; a pixel further is 4 descriptor units
             const uint64_t x_desc_base = make_smem_desc(smem_u32(sX), 16, 512, 4);
-            const uint64_t w_desc0 = make_smem_desc(smem_u32(sW), w_chunk, 128, 0);
             const uint32_t idesc = make_idesc(1 /*f32*/, 2 /*tf32*/, 2 /*tf32*/, 0 /*A K-major*/, 0 /*B K-major*/,
-                                              (uint32_t)a.MT, (uint32_t)a.NPX);
-            const uint64_t x_lo_off = x_part >> 4, w_lo_off = w_half_stage >> 4, w_tap = w_part >> 4;
-            const uint64_t x_half = 2, w_half = (2 * w_chunk) >> 4; // channels 8..15 of the block
+                                              PIXM ? 128u : (uint32_t)a.MT, PIXM ? (uint32_t)a.K : (uint32_t)a.NPX);
+            const uint64_t x_lo_off = x_part >> 4, w_lo_off = w_half_stage >> 4;
+            const uint64_t x_half = 2; // channels 8..15 of the block
             const uint64_t w_stage_step = (uint64_t)2 * w_half_stage >> 4;
             const uint64_t x_slot_step = (uint64_t)2 * x_part >> 4;
             int slot = 0, xphase = 0, st = 0, wphase = 0, g = 0; // g counts groups over all tiles
-            uint64_t x_slot_off = 0, w_stage = w_desc0;
+            uint64_t x_slot_off = 0, w_stage_off = 0;
             SB_TILE_LOOP(ok)
             {
                 const Tile T = decode_tile(a, t);
                 const uint64_t x_desc0 = x_desc_base + (uint64_t)T.m_local0 * 4;
+                // filter stage: [tap][c/4][kv rows][16 B], kv = channels of this tile
+                const uint64_t w_desc0 = make_smem_desc(smem_u32(sW), (uint32_t)T.kv * 16, 128, 0);
+                const uint64_t w_tap = (uint64_t)T.kv * 4, w_half = (uint64_t)T.kv * 2;
                 for (int cb = 0; cb < cbs_l && ok; ++cb)
                 {
                     ok = mbar_wait(&x_ready[slot], xphase, status, 13);
@@ -344,17 +351,36 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     uint64_t x_row = x_desc0 + x_slot_off; // patch position of tap (kh, 0)
                     for (int gi = 0; gi < groups_per_cb && ok; ++gi, ++g)
                     {
-                        if ((g & 1) == me)
+                        if (turn == me)
                         {
                             ok = mbar_wait(&w_full[st], wphase, status, 14);
-                            if (ok && g >= 2)
-                                ok = mbar_wait(&t_empty[me], ((g >> 1) - 1) & 1, status, 16);
+                            if (ok && g > tb_mask)
+                                ok = mbar_wait(&t_empty[g & tb_mask], ((g >> tb_shift) - 1) & 1, status, 16);
                             if (!ok)
                                 break;
                             tc_fence_after_sync();
-                            const uint32_t d = tmem + (uint32_t)(me * a.NPX); // tensor-memory buffer g & 1
-                            uint64_t wh = w_stage, xh = x_row;
-                            for (int tp = 0; tp < a.group; ++tp, wh += w_tap, xh += 4)
+                            uint64_t wh = w_desc0 + w_stage_off, xh = x_row;
+                            if (PIXM)
+                            {
+                                const uint32_t d0 = tmem + (uint32_t)((g & tb_mask) * mtiles * a.K);
+                                for (int tp = 0; tp < a.group; ++tp, wh += w_tap, xh += 4)
+                                {
+                                    const uint64_t wl = wh + w_lo_off;
+                                    for (int mt = 0; mt < mtiles; ++mt)
+                                    {
+                                        const uint64_t xa = xh + (uint64_t)mt * 512, xl = xa + x_lo_off; // 128 pixels on
+                                        const uint32_t d = d0 + (uint32_t)(mt * a.K);
+                                        tc_mma_tf32(d, xa, wl, idesc, tp == 0 ? 0u : 1u);
+                                        tc_mma_tf32(d, xl, wh, idesc, 1u);
+                                        tc_mma_tf32(d, xa, wh, idesc, 1u);
+                                        tc_mma_tf32(d, xa + x_half, wl + w_half, idesc, 1u);
+                                        tc_mma_tf32(d, xl + x_half, wh + w_half, idesc, 1u);
+                                        tc_mma_tf32(d, xa + x_half, wh + w_half, idesc, 1u);
+                                    }
+                                }
+                            }
+                            const uint32_t d = tmem + (uint32_t)((g & tb_mask) * a.NPX);
+                            for (int tp = 0; !PIXM && tp < a.group; ++tp, wh += w_tap, xh += 4)
                             {
                                 const uint64_t xl = xh + x_lo_off, wl = wh + w_lo_off;
                                 tc_mma_tf32(d, wl, xh, idesc, tp == 0 ? 0u : 1u);
@@ -364,13 +390,19 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                 tc_mma_tf32(d, wh + w_half, xl + x_half, idesc, 1u);
                                 tc_mma_tf32(d, wh + w_half, xh + x_half, idesc, 1u);
                             }
-                            // one commit: the stage is free for the producer and the group's partial
-                            // sums are complete for the accumulation warps
+                            // the stage is free for the producer and the group's partial sums are
+                            // complete for the accumulation warps: one commit serves both while the
+                            // accumulator ring is no deeper than the filter ring (a waiter must not fall
+                            // two phases behind its barrier)
                             tc_commit(&g_done[st]);
+                            if (own_t_full)
+                                tc_commit(&t_full[g & tb_mask]);
                         }
+                        if (++turn == NISS)
+                            turn = 0;
                         x_row += (uint64_t)(a.group == a.Fw ? a.PW : 1) * 4;
-                        w_stage += w_stage_step;
-                        if (++st == a.w_stages) { st = 0; wphase ^= 1; w_stage = w_desc0; }
+                        w_stage_off += w_stage_step;
+                        if (++st == a.w_stages) { st = 0; wphase ^= 1; w_stage_off = 0; }
                     }
                     tc_commit(&x_empty[slot]); // both issuers: the slot is free once the MMAs of either are done
                     x_slot_off += x_slot_step;
@@ -409,6 +441,92 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     else
     {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
+        if (PIXM)
+        {
+            // ---------------- accumulation + epilogue, pixel-major ----------------
+            // A thread owns one pixel (its tensor-memory lane) and all K <= 64 output channels of it:
+            // the running sums need 64 registers, a flush is one or two loads, and the epilogue
+            // writes 64 contiguous bytes per channel block straight from the registers (a warp
+            // covers 32 consecutive pixels: no transposition through shared memory, no barrier).
+            const int quarter = warp & 3, mt = (warp - FIRST_ACC_WARP) >> 2;
+            const int mtiles = a.NPX >> 7;
+            const bool active = mt < mtiles;
+            const size_t plane = (size_t)a.Ho * a.Wo * CB;
+            bool ok = true;
+            int gc = 0;
+            SB_TILE_LOOP(ok)
+            {
+                const Tile T = decode_tile(a, t);
+                float acc[64];
+#pragma unroll
+                for (int c = 0; c < 64; ++c)
+                    acc[c] = 0.f;
+                for (int g = 0; g < groups && ok; ++g, ++gc)
+                {
+                    const int tb = gc & 3;
+                    ok = mbar_wait(&t_full[tb], (gc >> 2) & 1, status, 15, 1u << 24);
+                    if (!ok)
+                        break;
+                    tc_fence_after_sync();
+                    if (active)
+                    {
+                        const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((tb * mtiles + mt) * a.K);
+#pragma unroll
+                        for (int piece = 0; piece < 2; ++piece)
+                            if (piece * 32 < a.K)
+                            {
+                                uint32_t v[32];
+                                tmem_ld32(tbase + (uint32_t)(piece * 32), v);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int e = 0; e < 32; ++e)
+                                    acc[piece * 32 + e] += __uint_as_float(v[e]);
+                            }
+                    }
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&t_empty[tb]);
+                }
+                if (ok && active)
+                {
+                    const int ml = T.m_local0 + mt * 128 + quarter * 32 + lane;
+                    const int rl = ml / a.PW, cl = ml - rl * a.PW;
+                    const int r = T.row_base + rl, c = T.col_base + cl;
+                    if (cl < T.tw_valid && rl < T.th_valid && r < a.Ho)
+                    {
+                        float *o = out + (size_t)T.n * (a.K / CB) * plane + ((size_t)r * a.Wo + c) * CB;
+#pragma unroll
+                        for (int kb = 0; kb < 4; ++kb)
+                            if (kb * CB < a.K)
+                            {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                {
+                                    float4 x = make_float4(acc[kb * 16 + 4 * j], acc[kb * 16 + 4 * j + 1], acc[kb * 16 + 4 * j + 2],
+                                                           acc[kb * 16 + 4 * j + 3]);
+                                    float4 *op = reinterpret_cast<float4 *>(o + (size_t)kb * plane) + j;
+                                    if (a.accumulate)
+                                    {
+                                        const float4 s4 = *op;
+                                        x.x += s4.x; x.y += s4.y; x.z += s4.z; x.w += s4.w;
+                                    }
+                                    if (bias)
+                                    {
+                                        const float4 b = __ldg(reinterpret_cast<const float4 *>(bias) + kb * 4 + j);
+                                        x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+                                    }
+                                    x.x = apply_act(x.x, a.act, a.slope); x.y = apply_act(x.y, a.act, a.slope);
+                                    x.z = apply_act(x.z, a.act, a.slope); x.w = apply_act(x.w, a.act, a.slope);
+                                    *op = x;
+                                }
+                            }
+                    }
+                }
+            }
+        }
+        else
+        {
         // ---------------- accumulation + epilogue ----------------
         const int quarter = warp & 3;                    // TMEM lanes [32*quarter, 32*quarter+32)
         const int phalf = (warp - FIRST_ACC_WARP) >> 2;  // which half of the tile's pixels
@@ -435,8 +553,11 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                 acc[c] = 0.f;
             for (int g = 0; g < groups && ok; ++g, ++gc)
             {
-                const int tb = gc & 1;
-                ok = mbar_wait(&g_done[gc % a.w_stages], (gc / a.w_stages) & 1, status, 15, 1u << 24);
+                const int tb = gc & (a.tbufs - 1);
+                if (a.tbufs > a.w_stages)
+                    ok = mbar_wait(&t_full[tb], (gc >> (a.tbufs == 4 ? 2 : 1)) & 1, status, 15, 1u << 24);
+                else
+                    ok = mbar_wait(&g_done[gc % a.w_stages], (gc / a.w_stages) & 1, status, 15, 1u << 24);
                 if (!ok)
                     break;
                 tc_fence_after_sync();
@@ -621,6 +742,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             }
             }
         }
+        }
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -642,7 +764,7 @@ bool fit_rings(TcArgs &a, bool need_two)
     static const int pref[][2] = {{3, 3}, {2, 3}, {2, 2}, {1, 3}, {1, 2}};
     // persistent where it pays and fits: narrow layers (64-channel tiles: small filter stages and
     // staging rows, little work per tile); wide ones need the shared memory for deeper rings
-    for (int persistent = (a.MT == 64 ? 1 : 0); persistent >= 0; --persistent)
+    for (int persistent = (a.MT == 64 ? 1 : 0); persistent >= (a.pixm ? 1 : 0); --persistent)
         for (const auto &p : pref)
         {
             const int xs = p[0] < a.cbs || persistent ? p[0] : a.cbs;
@@ -650,10 +772,11 @@ bool fit_rings(TcArgs &a, bool need_two)
                 continue;
             const size_t ops = (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
             const size_t full = (size_t)a.NPX * (a.MT + 16) * 4; // one tile per CTA stages the whole tile
-            const size_t smem = persistent ? ops + staging : (ops > full ? ops : full);
+            const size_t smem = persistent ? ops + (a.pixm ? 0 : staging) : (ops > full ? ops : full);
             if (smem <= limit)
             {
                 a.x_slots = xs; a.w_stages = p[1]; a.smem_bytes = (unsigned)smem;
+                a.tbufs = (a.pixm || 4 * a.NPX <= 512) ? 4 : 2;
                 a.persistent = persistent; a.stage_off = persistent ? (unsigned)ops : 0u;
                 return true;
             }
@@ -669,13 +792,14 @@ bool plan_tiled(const small_b200_layer *L, TcArgs &a)
 {
     double best = 0.0;
     int best_tw = 0, best_th = 0;
-    for (int tw = 8; tw <= a.Wo && tw + a.Fw - 1 <= 256; ++tw)
+    const int cap = 256, gran = a.pixm ? 128 : 64;
+    for (int tw = 8; tw <= a.Wo && tw + a.Fw - 1 <= cap; ++tw)
     {
         const int pw = tw + a.Fw - 1;
-        int th = (256 - tw) / pw + 1;
+        int th = (cap - tw) / pw + 1;
         if (th > a.Ho)
             th = a.Ho;
-        const int npx = ((th - 1) * pw + tw + 63) / 64 * 64;
+        const int npx = ((th - 1) * pw + tw + gran - 1) / gran * gran;
         const long long tiles = (long long)((a.Wo + tw - 1) / tw) * ((a.Ho + th - 1) / th);
         const double eff = (double)a.Wo * a.Ho / ((double)tiles * npx);
         if (eff > best + 1e-9)
@@ -690,7 +814,7 @@ bool plan_tiled(const small_b200_layer *L, TcArgs &a)
     a.PR = a.TH + a.Fh; // one row more than the taps reach: the junk tail of the last row reads it
     if (a.PR > 256)
         return false;
-    a.NPX = ((a.TH - 1) * a.PW + a.TW + 63) / 64 * 64;
+    a.NPX = ((a.TH - 1) * a.PW + a.TW + gran - 1) / gran * gran;
     a.tiles_x = (a.Wo + a.TW - 1) / a.TW;
     a.px_tiles = a.tiles_x * ((a.Ho + a.TH - 1) / a.TH);
     // the last GEMM column's last tap must stay inside the patch
@@ -700,7 +824,7 @@ bool plan_tiled(const small_b200_layer *L, TcArgs &a)
 }
 
 // Tiling and shared-memory plan of one layer; false when the shape is not covered.
-bool plan(const small_b200_layer *L, TcArgs &a)
+bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm)
 {
     if (!L || L->stride != 1 || L->C % CB != 0 || L->K % CB != 0 || L->C <= 0 || L->K <= 0)
         return false;
@@ -717,6 +841,8 @@ bool plan(const small_b200_layer *L, TcArgs &a)
     a.MT = pick_mt(a.K);
     a.k_tiles = (a.K + a.MT - 1) / a.MT;
     a.group = a.Fw; // one kernel row per flush: taps = Fh * Fw is a multiple of it
+    // few output channels: pixels on the tensor core's M (see the kernel's PIXM paths)
+    a.pixm = pixm ? 1 : 0;
     if (a.Ho == 0 || a.Wo == 0)
         return true;
     if (L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r) > 64)
@@ -724,12 +850,13 @@ bool plan(const small_b200_layer *L, TcArgs &a)
     // GEMM columns of one image: the last valid one is (Ho-1)*PW + Wo-1
     const int m_img = (a.Ho - 1) * a.PW + a.Wo;
     const int tiles256 = (m_img + 255) / 256;
-    int npx_first = ((m_img + tiles256 - 1) / tiles256 + 63) / 64 * 64;
+    const int gran = a.pixm ? 128 : 64;
+    int npx_first = ((m_img + tiles256 - 1) / tiles256 + gran - 1) / gran * gran;
     // First pass: only plans that keep two patches in flight (a layer with few channel blocks
     // per CTA otherwise waits for every patch's load and lo copy), even at a narrower tile;
     // second pass: anything that fits.
     for (int pass = 0; pass < 2; ++pass)
-        for (int npx = npx_first; npx >= (pass == 0 ? 128 : 64); npx -= 64)
+        for (int npx = npx_first; npx >= (pass == 0 ? 128 : gran); npx -= gran)
         {
             a.NPX = npx;
             a.px_tiles = (m_img + npx - 1) / npx;
@@ -741,6 +868,13 @@ bool plan(const small_b200_layer *L, TcArgs &a)
                 return true;
         }
     return false;
+}
+bool plan(const small_b200_layer *L, TcArgs &a)
+{
+    const bool want_pixm = L && (L->K == 32 || L->K == 64);
+    if (want_pixm && plan_as(L, a, true))
+        return true;
+    return plan_as(L, a, false);
 }
 } // namespace
 
@@ -786,6 +920,7 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     if (!configured)
     {
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         configured = true;
@@ -813,7 +948,10 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
             blocks = 2 * tiles;
         }
     }
-    if (a.persistent)
+    if (a.pixm)
+        conv_tf32x3_kernel<true, false, true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
+            mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.taps, a, bias, out, status);
+    else if (a.persistent)
         conv_tf32x3_kernel<true, false><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
             mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.taps, a, bias, out, status);
     else if (a.ksplit == 2)

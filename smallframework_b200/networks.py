@@ -318,7 +318,7 @@ class Chain:
     into a CUDA graph; launch() replays it.  `x` (input) and `y` (output) are the device
     tensors at the two ends."""
 
-    TC_MIN_CHANNELS = 32
+    TC_MIN_CHANNELS = 16
 
     def __init__(self, layers, batch, dtype="f32", device="cuda", tensor_core="auto", fuse_pool=True):
         """tensor_core: "auto" = fp32 convolutions the 3xTF32 kernel covers and that have at

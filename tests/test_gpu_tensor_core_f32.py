@@ -33,6 +33,15 @@ CASES = [
     (16, 16, 9, 300, 1, 1, "valid", 1),
     (32, 48, 33, 75, 5, 3, (2, 2, 1, 1), 1),
     (16, 32, 50, 64, 3, 3, "valid", 2),
+    # small tiles: four accumulator buffers in tensor memory (128 or 64 pixels per tile)
+    (32, 128, 8, 8, 3, 3, "same", 3),
+    (64, 256, 6, 6, 3, 3, "same", 2),
+    (32, 144, 10, 10, 3, 3, "same", 2),     # partial last channel tile (16 of 128 rows)
+    # 32 or 64 output channels: pixels on the tensor core's M (one or two blocks of 128 pixels)
+    (16, 32, 8, 8, 3, 3, "same", 5),
+    (256, 64, 13, 13, 3, 3, "same", 2),
+    (32, 64, 26, 26, 1, 1, "valid", 2),
+    (48, 32, 20, 20, 5, 5, (2, 2, 2, 2), 1),
 ]
 
 
