@@ -89,6 +89,7 @@ struct PwArgs
     int K;       // output channels
     int tiles;   // ceil(P / 128)
     int nblocks; // K / NT
+    int bulk;    // 1: a channel block of a tile is one contiguous run of pixels (plain bulk copies)
     long long out_pix_stride, out_plane_stride, out_group_stride; // bytes
     int zero_in, zero_filt, lshift, rshift, mult, k_zero;
 };
@@ -98,19 +99,24 @@ constexpr int TILE_M = 128;
 // Persistent: a CTA keeps its slice of the filter (and the per-channel correction terms) and
 // walks over pixel tiles; loads, MMAs and the epilogue of consecutive tiles overlap through two
 // activation stages in shared memory and two accumulator buffers in tensor memory.
-//   warps 0..3  epilogue: thread t owns pixel t of the tile = TMEM lane t
-//   warp 4      lane 0 issues the TMA loads (and the warp owns the TMEM allocation)
-//   warp 5      lane 0 issues the MMAs
+//   warps 0..7  epilogue: a thread owns one pixel of the tile (= TMEM lane 32 * (warp % 4) + lane)
+//               and one half of the tile's output channels (warp / 4); the epilogue is a chain of
+//               dependent steps (barrier, tensor-memory load, requantisation, store), so twice the
+//               warps hide twice the latency
+//   warp 8      lane 0 issues the TMA loads (and the warp owns the TMEM allocation)
+//   warp 9      lane 0 issues the MMAs
+constexpr int PW_EPI_WARPS = 8, PW_THREADS = (PW_EPI_WARPS + 2) * 32;
 template <int NT>
-__global__ void __launch_bounds__(192)
-pw_u8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const PwArgs a, const uint8_t *__restrict__ filt,
+__global__ void __launch_bounds__(PW_THREADS)
+pw_u8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const PwArgs a, const uint8_t *__restrict__ in,
+                const uint8_t *__restrict__ filt,
                 const int32_t *__restrict__ bias, uint8_t *__restrict__ out, int *status)
 {
     constexpr uint32_t TMEM_COLS = 2 * NT < 32 ? 32 : 2 * NT;
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[2], mma_bar[2], done_bar[2], b_bar;
     __shared__ uint32_t tmem_base_s;
-    __shared__ int corr[NT];
+    __shared__ __align__(16) int corr[NT];
 
     const uint32_t a_bytes = (uint32_t)a.cbs * TILE_M * CB;
     const uint32_t b_bytes = (uint32_t)(NT / CB) * a.cbs * CB * CB;
@@ -121,11 +127,11 @@ pw_u8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const PwArgs a, const
     const int total = a.groups * a.tiles;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    if (warp == 4)
+    if (warp == PW_EPI_WARPS)
     {
         if (lane == 0)
         {
-            for (int i = 0; i < 2; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&mma_bar[i], 1); mbar_init(&done_bar[i], 4); }
+            for (int i = 0; i < 2; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&mma_bar[i], 1); mbar_init(&done_bar[i], PW_EPI_WARPS); }
             mbar_init(&b_bar, 1);
             fence_barrier_init();
         }
@@ -138,7 +144,7 @@ pw_u8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const PwArgs a, const
     tc_fence_after_sync();
     const uint32_t tmem = tmem_base_s;
 
-    if (warp == 4 && lane == 0)
+    if (warp == PW_EPI_WARPS && lane == 0)
     {
         mbar_expect_tx(&b_bar, b_bytes);
         tma_load_1d(sB, filt + (size_t)nb * b_bytes, b_bytes, &b_bar);
@@ -152,11 +158,26 @@ pw_u8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const PwArgs a, const
             if (!ok)
                 break;
             const int tile = item % a.tiles, g = item / a.tiles;
-            mbar_expect_tx(&full_bar[s], a_bytes);
-            tma_load_3d(sA + (size_t)s * a_bytes, &map_a, 0, tile * TILE_M, g * a.cbs, &full_bar[s]);
+            if (a.bulk)
+            {
+                // [cb][pixel][16 B] in memory as in shared memory: one run per channel block (a tiled
+                // copy with 16-byte rows moves a row every few cycles and set the pace of this kernel);
+                // rows past the image keep stale bytes, their results are never stored
+                const int rows = (a.P - tile * TILE_M) < TILE_M ? (a.P - tile * TILE_M) : TILE_M;
+                mbar_expect_tx(&full_bar[s], (uint32_t)(a.cbs * rows * CB));
+                for (int cb = 0; cb < a.cbs; ++cb)
+                    tma_load_1d(sA + (size_t)s * a_bytes + (size_t)cb * TILE_M * CB,
+                                in + (((size_t)g * a.cbs + cb) * a.P + (size_t)tile * TILE_M) * CB, (uint32_t)(rows * CB),
+                                &full_bar[s]);
+            }
+            else
+            {
+                mbar_expect_tx(&full_bar[s], a_bytes);
+                tma_load_3d(sA + (size_t)s * a_bytes, &map_a, 0, tile * TILE_M, g * a.cbs, &full_bar[s]);
+            }
         }
     }
-    else if (warp == 5 && lane == 0)
+    else if (warp == PW_EPI_WARPS + 1 && lane == 0)
     {
         bool ok = mbar_wait(&b_bar, 0, status, 4);
         constexpr uint32_t idesc = make_idesc(2 /*s32*/, 0 /*u8*/, 0 /*u8*/, 0 /*A K-major*/, 1 /*B MN-major*/,
@@ -180,8 +201,11 @@ pw_u8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const PwArgs a, const
             tc_commit(&mma_bar[s]);
         }
     }
-    else if (warp < 4)
+    else if (warp < PW_EPI_WARPS)
     {
+        const int px_t = (warp & 3) * 32 + lane;      // this thread's pixel of the tile = its TMEM lane
+        constexpr int CPW = NT >= 32 ? NT / 2 : NT;  // output channels per warp group
+        const int c_begin = (warp >> 2) * CPW;
         // per-channel constants: k_zero + bias + C*zI*zF + zI * (column sum of the filter)
         bool ok = mbar_wait(&b_bar, 0, status, 5);
         if (tid < NT)
@@ -198,7 +222,7 @@ pw_u8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const PwArgs a, const
             }
             corr[tid] = c;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         int i = 0;
         for (int item = blockIdx.x; item < total && ok; item += gridDim.x, ++i)
         {
@@ -211,7 +235,7 @@ pw_u8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const PwArgs a, const
             int asum = 0;
             if (a.zero_filt != 0)
             {
-                const uint8_t *arow = sA + (size_t)s * a_bytes + (size_t)tid * CB;
+                const uint8_t *arow = sA + (size_t)s * a_bytes + (size_t)px_t * CB;
                 for (int cb = 0; cb < a.cbs; ++cb)
                 {
                     const uint4 v = *reinterpret_cast<const uint4 *>(arow + (size_t)cb * TILE_M * CB);
@@ -225,19 +249,28 @@ pw_u8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const PwArgs a, const
             if (!ok)
                 break;
             tc_fence_after_sync();
-            const int p = tile * TILE_M + tid;
+            const int p = tile * TILE_M + px_t;
             const int base = a.zero_filt * asum;
             uint8_t *orow = out + (size_t)g * a.out_group_stride + (size_t)p * a.out_pix_stride;
 #pragma unroll
-            for (int c0 = 0; c0 < NT; c0 += 16)
+            for (int cc = 0; cc < CPW; cc += 16)
             {
+                const int c0 = c_begin + cc;
+                if (c0 >= NT)
+                    break; // 16 channels per CTA: the second warp group only keeps the barriers' count
                 uint32_t r[16];
-                tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(s * NT + c0), r);
+                tmem_ld16(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(s * NT + c0), r);
                 tmem_ld_wait();
                 int q[16];
 #pragma unroll
-                for (int e = 0; e < 16; ++e)
-                    q[e] = (int)r[e] + base + corr[c0 + e];
+                for (int e4 = 0; e4 < 4; ++e4)
+                {
+                    const int4 cr = *reinterpret_cast<const int4 *>(corr + c0 + 4 * e4); // c0 is a multiple of 16
+                    q[4 * e4 + 0] = (int)r[4 * e4 + 0] + base + cr.x;
+                    q[4 * e4 + 1] = (int)r[4 * e4 + 1] + base + cr.y;
+                    q[4 * e4 + 2] = (int)r[4 * e4 + 2] + base + cr.z;
+                    q[4 * e4 + 3] = (int)r[4 * e4 + 3] + base + cr.w;
+                }
                 const uint4 o = requant_pack16(q, a.lshift, a.rshift, a.mult);
                 if (p < a.P)
                 {
@@ -253,12 +286,12 @@ pw_u8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const PwArgs a, const
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 4)
+    if (warp == PW_EPI_WARPS)
         tmem_dealloc(tmem, TMEM_COLS);
 }
 
 template <int NT>
-int launch_pw(const CUtensorMap &map, const PwArgs &a, size_t smem, const uint8_t *filt, const int32_t *bias,
+int launch_pw(const CUtensorMap &map, const PwArgs &a, size_t smem, const uint8_t *in, const uint8_t *filt, const int32_t *bias,
               uint8_t *out, cudaStream_t st)
 {
     auto kern = pw_u8_tc_kernel<NT>;
@@ -287,7 +320,7 @@ int launch_pw(const CUtensorMap &map, const PwArgs &a, size_t smem, const uint8_
     if (gx > total)
         gx = total;
     dim3 grid((unsigned)gx, (unsigned)a.nblocks);
-    kern<<<grid, 192, smem, st>>>(map, a, filt, bias, out, status);
+    kern<<<grid, PW_THREADS, smem, st>>>(map, a, in, filt, bias, out, status);
     return launched("pw_u8_tc_kernel");
 }
 
@@ -519,7 +552,7 @@ int conv2d_u8_tensor_core(const small_b200_layer *L, const uint8_t *in, const ui
     if (HW == 1)
     {
         // dense layer: the batch is the pixel axis; image n holds its planes contiguously
-        a.P = L->N; a.groups = 1;
+        a.P = L->N; a.groups = 1; a.bulk = 0;
         dims[0] = CB; dims[1] = (uint64_t)L->N; dims[2] = (uint64_t)cbs;
         strides[0] = (uint64_t)cbs * CB; strides[1] = CB;
         a.out_pix_stride = (long long)(L->K / CB) * CB; a.out_plane_stride = CB; a.out_group_stride = 0;
@@ -527,6 +560,7 @@ int conv2d_u8_tensor_core(const small_b200_layer *L, const uint8_t *in, const ui
     else
     {
         a.P = HW; a.groups = L->N;
+        a.bulk = (reinterpret_cast<uintptr_t>(in) % 16 == 0) ? 1 : 0;
         dims[0] = CB; dims[1] = (uint64_t)HW; dims[2] = (uint64_t)L->N * cbs;
         strides[0] = CB; strides[1] = (uint64_t)HW * CB;
         a.out_pix_stride = CB; a.out_plane_stride = (long long)HW * CB;
@@ -539,10 +573,10 @@ int conv2d_u8_tensor_core(const small_b200_layer *L, const uint8_t *in, const ui
         return rc;
     switch (nt)
     {
-    case 128: return launch_pw<128>(map, a, smem, filt, bias, out, st);
-    case 64: return launch_pw<64>(map, a, smem, filt, bias, out, st);
-    case 32: return launch_pw<32>(map, a, smem, filt, bias, out, st);
-    default: return launch_pw<16>(map, a, smem, filt, bias, out, st);
+    case 128: return launch_pw<128>(map, a, smem, in, filt, bias, out, st);
+    case 64: return launch_pw<64>(map, a, smem, in, filt, bias, out, st);
+    case 32: return launch_pw<32>(map, a, smem, in, filt, bias, out, st);
+    default: return launch_pw<16>(map, a, smem, in, filt, bias, out, st);
     }
 }
 } // namespace sb
