@@ -273,7 +273,27 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         {
             // ---------------- producer ----------------
             bool ok = true;
-            int pc = 0, gc = 0;
+            // Patches run ahead of the filter stages where a slot is free: a patch is a tiled copy of
+            // a few hundred 64-byte rows from memory and takes several thousand cycles, more than
+            // the MMAs of a tile with one or two channel blocks.  The look-ahead never waits (a wait
+            // here would hold back the filter stages); only the patch of the group at hand does.
+            // The patch cursor (p_t, p_cb) walks the same (tile, channel block) sequence as everybody else.
+            int pc = 1, gc = 0, q = 0; // pc: patches issued (patch 0 already is), q: patches the groups have entered
+            int p_t = first_tile, p_cb = 1;
+            if (p_cb == cbs_l)
+            {
+                p_cb = 0;
+                p_t += tile_step;
+            }
+            auto next_patch = [&]() {
+                issue_patch(decode_tile(a, p_t), p_cb, pc);
+                ++pc;
+                if (++p_cb == cbs_l)
+                {
+                    p_cb = 0;
+                    p_t += tile_step;
+                }
+            };
             SB_TILE_LOOP(ok)
             {
                 const Tile T = decode_tile(a, t);
@@ -281,17 +301,20 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                 {
                     if (g % groups_per_cb == 0)
                     {
-                        if (pc > 0) // patch 0 of the first tile is already on its way
+                        if (pc <= q) // the look-ahead has not reached this group's patch: now it must go
                         {
                             const int slot = pc % a.x_slots, xuse = pc / a.x_slots;
-                            if (xuse > 0) // both issuers' MMAs on the slot's previous patch are done
+                            if (xuse > 0) // all issuers' MMAs on the slot's previous patch are done
                                 ok = mbar_wait(&x_empty[slot], (xuse - 1) & 1, status, 11);
                             if (!ok)
                                 break;
-                            issue_patch(T, g / groups_per_cb, pc);
+                            next_patch();
                         }
-                        ++pc;
+                        ++q;
                     }
+                    while (pc < q - 1 + a.x_slots && (PERSIST ? p_t < a.total_tiles : p_t == first_tile) &&
+                           (pc < a.x_slots || mbar_test(&x_empty[pc % a.x_slots], ((pc / a.x_slots) - 1) & 1)))
+                        next_patch();
                     if (gc == 0)
                         continue; // so is filter stage 0
                     const int st = gc % a.w_stages, wuse = gc / a.w_stages;
