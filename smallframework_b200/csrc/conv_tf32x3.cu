@@ -280,19 +280,22 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             // The patch cursor (p_t, p_cb) walks the same (tile, channel block) sequence as everybody else.
             int pc = 1, gc = 0, q = 0; // pc: patches issued (patch 0 already is), q: patches the groups have entered
             int p_t = first_tile, p_cb = 1;
-            if (p_cb == cbs_l)
-            {
-                p_cb = 0;
-                p_t += tile_step;
-            }
-            auto next_patch = [&]() {
-                issue_patch(decode_tile(a, p_t), p_cb, pc);
-                ++pc;
-                if (++p_cb == cbs_l)
+            Tile PT = decode_tile(a, p_t); // decoded once per tile (the decode divides)
+            auto step_cursor = [&]() {
+                if (p_cb == cbs_l)
                 {
                     p_cb = 0;
                     p_t += tile_step;
+                    if (PERSIST && p_t < a.total_tiles)
+                        PT = decode_tile(a, p_t);
                 }
+            };
+            step_cursor();
+            auto next_patch = [&]() {
+                issue_patch(PT, p_cb, pc);
+                ++pc;
+                ++p_cb;
+                step_cursor();
             };
             SB_TILE_LOOP(ok)
             {
@@ -464,6 +467,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     else
     {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
+        const float act_ns = act_neg_scale(a.act, a.slope); // activation: v > 0 ? v : v * act_ns
         if (PIXM)
         {
             // ---------------- accumulation + epilogue, pixel-major ----------------
@@ -480,10 +484,15 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             SB_TILE_LOOP(ok)
             {
                 const Tile T = decode_tile(a, t);
+                // the bias seeds the sums (these loads overlap the wait for the first group)
                 float acc[64];
 #pragma unroll
-                for (int c = 0; c < 64; ++c)
-                    acc[c] = 0.f;
+                for (int c4 = 0; c4 < 16; ++c4)
+                {
+                    const float4 b = (bias && c4 * 4 < a.K) ? __ldg(reinterpret_cast<const float4 *>(bias) + c4)
+                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+                    acc[4 * c4] = b.x; acc[4 * c4 + 1] = b.y; acc[4 * c4 + 2] = b.z; acc[4 * c4 + 3] = b.w;
+                }
                 for (int g = 0; g < groups && ok; ++g, ++gc)
                 {
                     const int tb = gc & 3;
@@ -534,13 +543,8 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                         const float4 s4 = *op;
                                         x.x += s4.x; x.y += s4.y; x.z += s4.z; x.w += s4.w;
                                     }
-                                    if (bias)
-                                    {
-                                        const float4 b = __ldg(reinterpret_cast<const float4 *>(bias) + kb * 4 + j);
-                                        x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
-                                    }
-                                    x.x = apply_act(x.x, a.act, a.slope); x.y = apply_act(x.y, a.act, a.slope);
-                                    x.z = apply_act(x.z, a.act, a.slope); x.w = apply_act(x.w, a.act, a.slope);
+                                    x.x = apply_act_ns(x.x, act_ns); x.y = apply_act_ns(x.y, act_ns);
+                                    x.z = apply_act_ns(x.z, act_ns); x.w = apply_act_ns(x.w, act_ns);
                                     *op = x;
                                 }
                             }
@@ -570,10 +574,12 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         SB_TILE_LOOP(ok)
         {
             const Tile T = decode_tile(a, t);
+            // the bias of this thread's channel seeds its sums (rank 0 only when two CTAs share a tile)
+            const float seed = (bias && crank == 0 && lane_has_row && k_local < T.kv) ? __ldg(bias + T.kt * a.MT + k_local) : 0.f;
             float acc[COLS_PER_THREAD];
 #pragma unroll
             for (int c = 0; c < COLS_PER_THREAD; ++c)
-                acc[c] = 0.f;
+                acc[c] = seed;
             for (int g = 0; g < groups && ok; ++g, ++gc)
             {
                 const int tb = gc & (a.tbufs - 1);
@@ -607,13 +613,6 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             // channel of up to 128 pixels, the packed output wants 16 channels of one pixel together.
             const int kbs = T.kv / CB; // channel blocks this tile really has
             float *obase = out + ((size_t)T.n * (a.K / CB) + (size_t)T.kt * (a.MT / CB)) * plane + q4 * 4;
-            // this thread's four channels of every channel block, fetched once per tile (a load per
-            // pixel inside the store loop costs a round trip to L2 each time)
-            float4 bias_r[8];
-#pragma unroll
-            for (int kb = 0; kb < 8; ++kb)
-                bias_r[kb] = (bias && kb < kbs) ? *reinterpret_cast<const float4 *>(bias + T.kt * a.MT + q4 * 4 + kb * CB)
-                                                : make_float4(0.f, 0.f, 0.f, 0.f);
             if (!PERSIST)
             {
                 // one tile per CTA: every operand buffer is dead, the whole tile is staged at once
@@ -684,12 +683,8 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                     const float4 s4 = *reinterpret_cast<const float4 *>(ok_);
                                     x.x += s4.x; x.y += s4.y; x.z += s4.z; x.w += s4.w;
                                 }
-                                {
-                                    const float4 b = bias_r[kb];
-                                    x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
-                                }
-                                x.x = apply_act(x.x, a.act, a.slope); x.y = apply_act(x.y, a.act, a.slope);
-                                x.z = apply_act(x.z, a.act, a.slope); x.w = apply_act(x.w, a.act, a.slope);
+                                x.x = apply_act_ns(x.x, act_ns); x.y = apply_act_ns(x.y, act_ns);
+                                x.z = apply_act_ns(x.z, act_ns); x.w = apply_act_ns(x.w, act_ns);
                                 *reinterpret_cast<float4 *>(ok_) = x;
                             }
                         }
@@ -750,12 +745,8 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                     const float4 s4 = *reinterpret_cast<const float4 *>(ok_);
                                     x.x += s4.x; x.y += s4.y; x.z += s4.z; x.w += s4.w;
                                 }
-                                {
-                                    const float4 b = bias_r[kb];
-                                    x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
-                                }
-                                x.x = apply_act(x.x, a.act, a.slope); x.y = apply_act(x.y, a.act, a.slope);
-                                x.z = apply_act(x.z, a.act, a.slope); x.w = apply_act(x.w, a.act, a.slope);
+                                x.x = apply_act_ns(x.x, act_ns); x.y = apply_act_ns(x.y, act_ns);
+                                x.z = apply_act_ns(x.z, act_ns); x.w = apply_act_ns(x.w, act_ns);
                                 *reinterpret_cast<float4 *>(ok_) = x;
                             }
                         }
