@@ -226,8 +226,8 @@ conv2d_f32_kernel(const ConvArgs a, const float *__restrict__ in, const float *_
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
                 {
-                    const float x0 = apply_act(acc[j][half * 4 + q], a.act, a.slope);
-                    const float x1 = apply_act(acc[j + 1][half * 4 + q], a.act, a.slope);
+                    const float x0 = apply_act_ns(acc[j][half * 4 + q], act_neg_scale(a.act, a.slope));
+                    const float x1 = apply_act_ns(acc[j + 1][half * 4 + q], act_neg_scale(a.act, a.slope));
                     const float m = fmaxf(x0, x1);
                     v[q] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2 * CG));
                 }
@@ -252,10 +252,10 @@ conv2d_f32_kernel(const ConvArgs a, const float *__restrict__ in, const float *_
             if (ow < a.Wo)
             {
                 float4 v;
-                v.x = apply_act(acc[j][half * 4 + 0], a.act, a.slope);
-                v.y = apply_act(acc[j][half * 4 + 1], a.act, a.slope);
-                v.z = apply_act(acc[j][half * 4 + 2], a.act, a.slope);
-                v.w = apply_act(acc[j][half * 4 + 3], a.act, a.slope);
+                v.x = apply_act_ns(acc[j][half * 4 + 0], act_neg_scale(a.act, a.slope));
+                v.y = apply_act_ns(acc[j][half * 4 + 1], act_neg_scale(a.act, a.slope));
+                v.z = apply_act_ns(acc[j][half * 4 + 2], act_neg_scale(a.act, a.slope));
+                v.w = apply_act_ns(acc[j][half * 4 + 3], act_neg_scale(a.act, a.slope));
                 *reinterpret_cast<float4 *>(obase + (size_t)ow * CB) = v;
             }
         }
@@ -317,10 +317,10 @@ conv2d_first_f32_kernel(const ConvArgs a, const float *__restrict__ in, const fl
     for (int k4 = 0; k4 < CB; k4 += 4)
     {
         float4 v;
-        v.x = apply_act(acc[k4 + 0], a.act, a.slope);
-        v.y = apply_act(acc[k4 + 1], a.act, a.slope);
-        v.z = apply_act(acc[k4 + 2], a.act, a.slope);
-        v.w = apply_act(acc[k4 + 3], a.act, a.slope);
+        v.x = apply_act_ns(acc[k4 + 0], act_neg_scale(a.act, a.slope));
+        v.y = apply_act_ns(acc[k4 + 1], act_neg_scale(a.act, a.slope));
+        v.z = apply_act_ns(acc[k4 + 2], act_neg_scale(a.act, a.slope));
+        v.w = apply_act_ns(acc[k4 + 3], act_neg_scale(a.act, a.slope));
         *reinterpret_cast<float4 *>(o + k4) = v;
     }
 }
@@ -404,8 +404,8 @@ conv2d_first_pool_f32_kernel(const ConvArgs a, const float *__restrict__ in, con
         float v[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-            v[q] = fmaxf(fmaxf(apply_act(acc[0][k4 + q], a.act, a.slope), apply_act(acc[1][k4 + q], a.act, a.slope)),
-                         fmaxf(apply_act(acc[2][k4 + q], a.act, a.slope), apply_act(acc[3][k4 + q], a.act, a.slope)));
+            v[q] = fmaxf(fmaxf(apply_act_ns(acc[0][k4 + q], act_neg_scale(a.act, a.slope)), apply_act_ns(acc[1][k4 + q], act_neg_scale(a.act, a.slope))),
+                         fmaxf(apply_act_ns(acc[2][k4 + q], act_neg_scale(a.act, a.slope)), apply_act_ns(acc[3][k4 + q], act_neg_scale(a.act, a.slope))));
         *reinterpret_cast<float4 *>(o + k4) = make_float4(v[0], v[1], v[2], v[3]);
     }
 }
@@ -486,8 +486,8 @@ conv2d_first_pool_fixed_f32_kernel(const ConvArgs a, const float *__restrict__ i
         float v[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-            v[q] = fmaxf(fmaxf(apply_act(acc[0][k4 + q], a.act, a.slope), apply_act(acc[1][k4 + q], a.act, a.slope)),
-                         fmaxf(apply_act(acc[2][k4 + q], a.act, a.slope), apply_act(acc[3][k4 + q], a.act, a.slope)));
+            v[q] = fmaxf(fmaxf(apply_act_ns(acc[0][k4 + q], act_neg_scale(a.act, a.slope)), apply_act_ns(acc[1][k4 + q], act_neg_scale(a.act, a.slope))),
+                         fmaxf(apply_act_ns(acc[2][k4 + q], act_neg_scale(a.act, a.slope)), apply_act_ns(acc[3][k4 + q], act_neg_scale(a.act, a.slope))));
         *reinterpret_cast<float4 *>(o + k4) = make_float4(v[0], v[1], v[2], v[3]);
     }
 }
