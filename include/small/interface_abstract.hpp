@@ -13,6 +13,7 @@
 
 #include <cstdlib>
 #include <stdexcept>
+#include <string>
 #include <type_traits>
 
 #include <small/op_type.hpp>
@@ -121,6 +122,23 @@ inline void dwconv(bool partial, int act, int kh, int kw, int stride, int t, int
 }
 
 template <class BufferT>
+inline void groupconv(bool partial, int kh, int kw, int stride, int groups, int t, int b, int l, int r,
+                      int C, int H, int W, BufferT const &in, BufferT const &filt, BufferT &out)
+{
+    const char *type = is_quint8<BufferT> ? "quint8" : "float";
+    if (C % SMALL_B200_CB != 0)
+        throw std::invalid_argument(std::string("GroupConv2D<") + type + "> ERROR: in_channels unsupported.");
+    small_b200_layer L = describe(C, C, H, W, kh, kw, stride, t, b, l, r, partial);
+    quantise(L, in, &filt, out);
+    if constexpr (is_quint8<BufferT>)
+        throw_on(small_b200_groupconv2d_u8(&L, groups, in.device_ptr(), filt.device_ptr(), nullptr,
+                                           out.device_ptr(), nullptr));
+    else
+        throw_on(small_b200_groupconv2d_f32(&L, groups, in.device_ptr(), filt.device_ptr(), nullptr,
+                                            out.device_ptr(), nullptr));
+}
+
+template <class BufferT>
 inline void pool(bool average, int kh, int kw, int stride, int t, int b, int l, int r, int C, int H,
                  int W, BufferT const &in, BufferT &out)
 {
@@ -186,21 +204,29 @@ void PartialDepthwiseConv2D(int kernel_height, int kernel_width, int stride,
                  (BufferT const *)nullptr, output_buf);
 }
 
-// No driver of the reference calls the grouped form, and its float variant is only
-// meaningful for a channel block of 1 (interface_abstract.hpp:1291 uses op_class 2 with
-// G_b = C_ob); it is not provided on this platform.
+// Grouped convolution (reference: interface_abstract.hpp:1265, :1332, :1402, :1470).  The 16
+// lanes of a block are 16 groups, each a convolution from input_channels to input_channels
+// channels: I [G/16][C][H][W][16], F [G/16][C][C][Fh][Fw][16], O [G/16][C][Ho][Wo][16].  The
+// same argument checks and messages as the reference, plus a check of output_groups (the
+// reference's nest silently assumes a multiple of the block).
 template <class BufferT, bool = true>
-void GroupConv2D(int, int, int, int, uint8_t, uint8_t, uint8_t, uint8_t, int, int, int,
-                 BufferT const &, BufferT const &, BufferT &)
+void GroupConv2D(int kernel_height, int kernel_width, int stride, int output_groups,
+                 uint8_t t_pad, uint8_t b_pad, uint8_t l_pad, uint8_t r_pad,
+                 int input_channels, int input_height, int input_width,
+                 BufferT const &input_buf, BufferT const &filter_buf, BufferT &output_buf)
 {
-    throw std::invalid_argument("GroupConv2D ERROR: not provided on the B200 platform.");
+    b200::groupconv(false, kernel_height, kernel_width, stride, output_groups, t_pad, b_pad, l_pad,
+                    r_pad, input_channels, input_height, input_width, input_buf, filter_buf, output_buf);
 }
 
 template <class BufferT, bool = true>
-void PartialGroupConv2D(int, int, int, int, uint8_t, uint8_t, uint8_t, uint8_t, int, int, int,
-                        BufferT const &, BufferT const &, BufferT &)
+void PartialGroupConv2D(int kernel_height, int kernel_width, int stride, int output_groups,
+                        uint8_t t_pad, uint8_t b_pad, uint8_t l_pad, uint8_t r_pad,
+                        int input_channels, int input_height, int input_width,
+                        BufferT const &input_buf, BufferT const &filter_buf, BufferT &output_buf)
 {
-    throw std::invalid_argument("PartialGroupConv2D ERROR: not provided on the B200 platform.");
+    b200::groupconv(true, kernel_height, kernel_width, stride, output_groups, t_pad, b_pad, l_pad,
+                    r_pad, input_channels, input_height, input_width, input_buf, filter_buf, output_buf);
 }
 
 template <class BufferT, bool = true>

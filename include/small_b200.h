@@ -161,6 +161,19 @@ int small_b200_conv2d_f32_tf32x3_noalloc(const small_b200_layer *L, const float 
  * DepthwiseConv2D_Bias_ReLU (fused_interface_abstract.hpp:1419). */
 int small_b200_dwconv2d_f32(const small_b200_layer *L, const float *in, const float *filt,
                             const float *bias, float *out, void *stream);
+/* small::GroupConv2D / PartialGroupConv2D<FloatBuffer> (:1265, :1402): `groups` independent
+ * convolutions, each from L->C input channels to L->K output channels (the reference's
+ * interface passes its input_channels argument for both).  Layouts of the loop nest with
+ * G_b = 16, K_b = F_cb = 1 (abstract_layer.hpp:1419-1432): the 16 lanes of a block are 16
+ * groups,
+ *   in [N][G/16][C][H][W][16]   filt [G/16][K][C][Fh][Fw][16]   out [N][G/16][K][Ho][Wo][16]
+ * bias (may be NULL) is laid out like one output pixel, [G/16][K][16].  groups % 16 == 0;
+ * stride in {1,2}.  The reference's own float instantiation treats the lanes of a block as a
+ * dense channel block (op_class 2, :1291), which is a grouped convolution only for a channel
+ * block of 1; this entry point computes the grouped convolution the layout describes and is
+ * checked against the reference built with a channel block of 1. */
+int small_b200_groupconv2d_f32(const small_b200_layer *L, int32_t groups, const float *in, const float *filt,
+                               const float *bias, float *out, void *stream);
 /* small::MaxPool2D<FloatBuffer> (:778): border windows start from 0, interior from the
  * first tap. */
 int small_b200_maxpool2d_f32(const small_b200_layer *L, const float *in, float *out, void *stream);
@@ -193,6 +206,11 @@ int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uin
 /* small::DepthwiseConv2D<QUInt8Buffer> (:1059). */
 int small_b200_dwconv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
                            const int32_t *bias, uint8_t *out, void *stream);
+/* small::GroupConv2D<QUInt8Buffer> (:1332; lane-wise op_class 1 at :1358), layouts as in the
+ * float form, arithmetic as in small_b200_conv2d_u8.  The Partial form (:1470) would reload
+ * int32 partial sums from the uint8 output and is refused like PartialConv2D<quint8>. */
+int small_b200_groupconv2d_u8(const small_b200_layer *L, int32_t groups, const uint8_t *in, const uint8_t *filt,
+                              const int32_t *bias, uint8_t *out, void *stream);
 /* small::MaxPool2D<QUInt8Buffer> (:843): interior windows start from the raw first tap,
  * border windows from k_zero; taps enter as a + zero_in; the maximum is requantised. */
 int small_b200_maxpool2d_u8(const small_b200_layer *L, const uint8_t *in, uint8_t *out, void *stream);

@@ -101,6 +101,17 @@ class Oracle:
            C.c_int(int(accumulate)), _p(o))
         return o
 
+    def groupconv2d_f32(self, s, groups, x, f, bias=None, act=0, slope=0.0, out=None):
+        """`groups` convolutions s.C -> s.K; s.cob is the group block."""
+        ho, wo = s.out_hw()
+        accumulate = out is not None
+        o = _f32(out).copy() if accumulate else np.zeros(groups * s.K * ho * wo, np.float32)
+        b = _f32(bias) if bias is not None else None
+        x, f = _f32(x), _f32(f)
+        self.lib.so_groupconv2d_f32(C.byref(s), C.c_int32(groups), _p(x), _p(f), _p(b), C.c_int(act),
+                                    C.c_float(slope), C.c_int(int(accumulate)), _p(o))
+        return o
+
     def pool2d_f32(self, s, x, average=False):
         ho, wo = s.out_hw()
         o = np.zeros(s.C * ho * wo, np.float32)
@@ -145,6 +156,14 @@ class Oracle:
         b = np.ascontiguousarray(bias, dtype=np.int32) if bias is not None else None
         fn = self.lib.so_dwconv2d_u8 if depthwise else self.lib.so_conv2d_u8
         fn(C.byref(s), C.byref(q), _p(x), _p(f), _p(b), _p(o))
+        return o
+
+    def groupconv2d_u8(self, s, q, groups, x, f, bias=None):
+        ho, wo = s.out_hw()
+        o = np.zeros(groups * s.K * ho * wo, np.uint8)
+        x, f = _u8(x), _u8(f)
+        b = np.ascontiguousarray(bias, dtype=np.int32) if bias is not None else None
+        self.lib.so_groupconv2d_u8(C.byref(s), C.byref(q), C.c_int32(groups), _p(x), _p(f), _p(b), _p(o))
         return o
 
     def pool2d_u8(self, s, q, x, average=False):
@@ -221,6 +240,22 @@ class Ref:
         x, f = _u8(x), _u8(f)
         self._check(self.lib.ref_conv2d_u8(C.byref(s), C.byref(q), C.c_int(int(depthwise)),
                                            _p(x), _p(f), _p(o)))
+        return o
+
+    def groupconv2d_f32(self, s, groups, x, f, out=None):
+        """small::GroupConv2D / PartialGroupConv2D: `groups` groups of s.C channels each."""
+        ho, wo = s.out_hw()
+        o = _f32(out).copy() if out is not None else np.zeros(groups * s.C * ho * wo, np.float32)
+        x, f = _f32(x), _f32(f)
+        self._check(self.lib.ref_groupconv2d_f32(C.byref(s), C.c_int(groups), _p(x), _p(f),
+                                                 C.c_int(int(out is not None)), _p(o)))
+        return o
+
+    def groupconv2d_u8(self, s, q, groups, x, f):
+        ho, wo = s.out_hw()
+        o = np.zeros(groups * s.C * ho * wo, np.uint8)
+        x, f = _u8(x), _u8(f)
+        self._check(self.lib.ref_groupconv2d_u8(C.byref(s), C.byref(q), C.c_int(groups), _p(x), _p(f), _p(o)))
         return o
 
     def maxpool2d_u8(self, s, q, x):

@@ -126,6 +126,30 @@ int ref_dwconv2d_f32(const so_shape *s, const float *in, const float *filt, int 
     })
 }
 
+// small::GroupConv2D / PartialGroupConv2D<FloatBuffer> (interface_abstract.hpp:1265, :1402):
+// `groups` groups of s->C channels each (the interface has one argument for the input and the
+// output channels of a group).
+int ref_groupconv2d_f32(const so_shape *s, int groups, const float *in, const float *filt, int partial,
+                        float *out)
+{
+    const size_t ni = (size_t)groups * s->C * s->H * s->W;
+    const size_t nf = (size_t)groups * s->C * s->C * s->Fh * s->Fw;
+    const size_t no = (size_t)groups * s->C * out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride) *
+                      out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    GUARD({
+        auto I = make<small::FloatBuffer>(in, ni);
+        auto F = make<small::FloatBuffer>(filt, nf);
+        auto O = make<small::FloatBuffer>(out, no);
+        if (partial)
+            small::PartialGroupConv2D(s->Fh, s->Fw, s->stride, groups, s->pad_t, s->pad_b, s->pad_l,
+                                      s->pad_r, s->C, s->H, s->W, I, F, O);
+        else
+            small::GroupConv2D(s->Fh, s->Fw, s->stride, groups, s->pad_t, s->pad_b, s->pad_l, s->pad_r,
+                               s->C, s->H, s->W, I, F, O);
+        std::memcpy(out, O.data(), no * sizeof(float));
+    })
+}
+
 int ref_pool2d_f32(const so_shape *s, int average, const float *in, float *out)
 {
     const size_t ni = (size_t)s->C * s->H * s->W;
@@ -224,6 +248,26 @@ int ref_conv2d_u8(const so_shape *s, const so_quant *q, int depthwise, const uin
         else
             small::Conv2D(s->Fh, s->Fw, s->stride, s->pad_t, s->pad_b, s->pad_l, s->pad_r, s->K,
                           s->C, s->H, s->W, I, F, O);
+        std::memcpy(out, O.data(), no);
+    })
+}
+
+// small::GroupConv2D<QUInt8Buffer> (interface_abstract.hpp:1332)
+int ref_groupconv2d_u8(const so_shape *s, const so_quant *q, int groups, const uint8_t *in,
+                       const uint8_t *filt, uint8_t *out)
+{
+    const size_t ni = (size_t)groups * s->C * s->H * s->W;
+    const size_t nf = (size_t)groups * s->C * s->C * s->Fh * s->Fw;
+    const size_t no = (size_t)groups * s->C * out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride) *
+                      out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    GUARD({
+        ref_set_threads(1);
+        auto I = make<small::QUInt8Buffer>(in, ni);
+        auto F = make<small::QUInt8Buffer>(filt, nf);
+        auto O = make<small::QUInt8Buffer>(nullptr, no, 4 * no + 64);
+        set_q(I, &F, O, q);
+        small::GroupConv2D(s->Fh, s->Fw, s->stride, groups, s->pad_t, s->pad_b, s->pad_l, s->pad_r,
+                           s->C, s->H, s->W, I, F, O);
         std::memcpy(out, O.data(), no);
     })
 }

@@ -134,6 +134,56 @@ void so_dwconv2d_f32(const so_shape *s, const float *in, const float *filt,
             }
 }
 
+/* Grouped convolution (interface_abstract.hpp:1265-1330 float, :1332-1400 quint8): the loop
+ * nest with G_b = gb, K_b = F_cb = 1, whose layouts (abstract_layer.hpp:1419-1432) are
+ *   I [G/gb][C][H][W][gb]   F [G/gb][K][C][Fh][Fw][gb]   O [G/gb][K][Ho][Wo][gb]
+ * s->C / s->K are the channels of ONE group, s->cob is gb.  Reduction order of the nest:
+ * input channel, kernel row, kernel column; padded taps skipped.  With gb = 1 the float
+ * result is bit-identical to the reference's REF platform (tests/test_oracle_reference.py);
+ * for larger blocks the reference's float instantiation is not a grouped convolution (it
+ * uses the dense microkernel, op_class 2), so there the layout above is the definition. */
+static inline size_t grp_idx(int32_t planes, int32_t H, int32_t W, int32_t gb, int32_t g, int32_t p,
+                             int32_t h, int32_t w)
+{
+    return ((((size_t)(g / gb) * planes + p) * H + h) * W + w) * gb + (g % gb);
+}
+
+void so_groupconv2d_f32(const so_shape *s, int32_t groups, const float *in, const float *filt,
+                        const float *bias, int act, float slope, int accumulate, float *out)
+{
+    const int32_t gb = s->cob;
+    const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
+    const int32_t Wo = so_out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    for (int32_t g = 0; g < groups; ++g)
+        for (int32_t k = 0; k < s->K; ++k)
+            for (int32_t oh = 0; oh < Ho; ++oh)
+                for (int32_t ow = 0; ow < Wo; ++ow)
+                {
+                    const size_t oi = grp_idx(s->K, Ho, Wo, gb, g, k, oh, ow);
+                    float acc = accumulate ? out[oi] : 0.f;
+                    if (bias)
+                        acc = acc + bias[((size_t)(g / gb) * s->K + k) * gb + (g % gb)];
+                    for (int32_t c = 0; c < s->C; ++c)
+                        for (int32_t kh = 0; kh < s->Fh; ++kh)
+                        {
+                            const int32_t ih = oh * s->stride - s->pad_t + kh;
+                            if (ih < 0 || ih >= s->H)
+                                continue;
+                            for (int32_t kw = 0; kw < s->Fw; ++kw)
+                            {
+                                const int32_t iw = ow * s->stride - s->pad_l + kw;
+                                if (iw < 0 || iw >= s->W)
+                                    continue;
+                                const float a = in[grp_idx(s->C, s->H, s->W, gb, g, c, ih, iw)];
+                                const float f = filt[grp_idx(s->K * s->C, s->Fh, s->Fw, gb, g,
+                                                             k * s->C + c, kh, kw)];
+                                acc = acc + a * f;
+                            }
+                        }
+                    out[oi] = apply_act(acc, act, slope);
+                }
+}
+
 /* ---------------------------------------------------------------- float pools */
 static int window_is_interior(const so_shape *s, int32_t oh, int32_t ow)
 {
@@ -337,6 +387,43 @@ void so_dwconv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
                 out[act_idx(Ho, Wo, cb, c, oh, ow)] =
                     (uint8_t)so_requant(acc, q->lshift, q->rshift, q->multiplier);
             }
+}
+
+void so_groupconv2d_u8(const so_shape *s, const so_quant *q, int32_t groups, const uint8_t *in,
+                       const uint8_t *filt, const int32_t *bias, uint8_t *out)
+{
+    /* q_abstract_layer.hpp:894 with op_class 1 (interface_abstract.hpp:1358): lane-wise
+     * QUINT8_DW_TILE_C per input channel of the group */
+    const int32_t gb = s->cob;
+    const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
+    const int32_t Wo = so_out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    for (int32_t g = 0; g < groups; ++g)
+        for (int32_t k = 0; k < s->K; ++k)
+            for (int32_t oh = 0; oh < Ho; ++oh)
+                for (int32_t ow = 0; ow < Wo; ++ow)
+                {
+                    int32_t acc = q->k_zero +
+                                  (bias ? bias[((size_t)(g / gb) * s->K + k) * gb + (g % gb)] : 0);
+                    for (int32_t c = 0; c < s->C; ++c)
+                        for (int32_t kh = 0; kh < s->Fh; ++kh)
+                        {
+                            const int32_t ih = oh * s->stride - s->pad_t + kh;
+                            if (ih < 0 || ih >= s->H)
+                                continue;
+                            for (int32_t kw = 0; kw < s->Fw; ++kw)
+                            {
+                                const int32_t iw = ow * s->stride - s->pad_l + kw;
+                                if (iw < 0 || iw >= s->W)
+                                    continue;
+                                const int32_t a = in[grp_idx(s->C, s->H, s->W, gb, g, c, ih, iw)];
+                                const int32_t f = filt[grp_idx(s->K * s->C, s->Fh, s->Fw, gb, g,
+                                                               k * s->C + c, kh, kw)];
+                                acc += (a + q->zero_in) * (f + q->zero_filt);
+                            }
+                        }
+                    out[grp_idx(s->K, Ho, Wo, gb, g, k, oh, ow)] =
+                        (uint8_t)so_requant(acc, q->lshift, q->rshift, q->multiplier);
+                }
 }
 
 void so_maxpool2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in, uint8_t *out)

@@ -62,8 +62,11 @@ void so_conv2d_f32(const so_shape *s, const float *in, const float *filt,
                    const float *bias, int act, float slope, int accumulate, float *out);
 void so_dwconv2d_f32(const so_shape *s, const float *in, const float *filt,
                      const float *bias, int act, float slope, int accumulate, float *out);
-/* groups = number of groups; s->C = input channels per group is implied by
- * C_total/groups; K = output channels per group. Layout: I [G/gb][Cg][H][W][gb]. */
+/* Grouped convolution: `groups` convolutions from s->C to s->K channels each; s->cob is the
+ * group block gb.  I [G/gb][C][H][W][gb], F [G/gb][K][C][Fh][Fw][gb], O [G/gb][K][Ho][Wo][gb];
+ * bias is laid out like one output pixel. */
+void so_groupconv2d_f32(const so_shape *s, int32_t groups, const float *in, const float *filt,
+                        const float *bias, int act, float slope, int accumulate, float *out);
 void so_maxpool2d_f32(const so_shape *s, const float *in, float *out);
 void so_avgpool2d_f32(const so_shape *s, const float *in, float *out);
 void so_relu_f32(int64_t n, const float *in, float *out);
@@ -85,6 +88,8 @@ void so_conv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
                   const uint8_t *filt, const int32_t *bias, uint8_t *out);
 void so_dwconv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
                     const uint8_t *filt, const int32_t *bias, uint8_t *out);
+void so_groupconv2d_u8(const so_shape *s, const so_quant *q, int32_t groups, const uint8_t *in,
+                       const uint8_t *filt, const int32_t *bias, uint8_t *out);
 void so_maxpool2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in, uint8_t *out);
 void so_relu_u8(int64_t n, const so_quant *q, const uint8_t *in, uint8_t *out);
 /* NOT in the reference (no quint8 AveragePool2D exists there): sum of (a+zero_in)

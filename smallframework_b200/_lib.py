@@ -68,6 +68,7 @@ SIGNATURES = {
     "small_b200_conv2d_f32_tf32x3": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_conv2d_f32_tf32x3_noalloc": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_dwconv2d_f32": [_LP, _VP, _VP, _VP, _VP, _VP],
+    "small_b200_groupconv2d_f32": [_LP, C.c_int32, _VP, _VP, _VP, _VP, _VP],
     "small_b200_maxpool2d_f32": [_LP, _VP, _VP, _VP],
     "small_b200_avgpool2d_f32": [_LP, _VP, _VP, _VP],
     "small_b200_relu_f32": [_I64, _VP, _VP, _VP],
@@ -79,6 +80,7 @@ SIGNATURES = {
     "small_b200_concat": [_I32, _SZ, _VP, _SZ, _VP, _VP, _VP],
     "small_b200_conv2d_u8": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_dwconv2d_u8": [_LP, _VP, _VP, _VP, _VP, _VP],
+    "small_b200_groupconv2d_u8": [_LP, C.c_int32, _VP, _VP, _VP, _VP, _VP],
     "small_b200_maxpool2d_u8": [_LP, _VP, _VP, _VP],
     "small_b200_avgpool2d_u8": [_LP, _VP, _VP, _VP],
     "small_b200_relu_u8": [_I64, _LP, _VP, _VP, _VP],

@@ -273,6 +273,43 @@ def DepthwiseConv2D_Bias_Activation(kernel_height, kernel_width, stride, t_pad, 
             activation, negative_slope, batch, stream)
 
 
+def _group(name, partial, kh, kw, stride, groups, t, b, l, r, C_, H, W, inp, filt, out, bias, act,
+           slope, batch, stream):
+    if C_ % CB != 0:
+        raise ValueError(f"{name} ERROR: in_channels unsupported.")
+    L = _layer(batch, C_, C_, H, W, kh, kw, stride, t, b, l, r, int(partial), act, slope, inp, filt, out)
+    ho, wo = L.out_hw()
+    if groups > 0 and groups % CB == 0:
+        _need(inp, batch * groups * C_ * H * W, name + " input")
+        _need(filt, groups * C_ * C_ * kh * kw, name + " filter")
+        _need(out, batch * groups * C_ * ho * wo, name + " output")
+    fn = lib().small_b200_groupconv2d_u8 if _is_q(out) else lib().small_b200_groupconv2d_f32
+    check(fn(C.byref(L), C.c_int32(groups), _ptr(inp), _ptr(filt), _ptr(bias), _ptr(out), _stream(stream)))
+
+
+def GroupConv2D(kernel_height, kernel_width, stride, output_groups, t_pad, b_pad, l_pad, r_pad,
+                input_channels, input_height, input_width, input_buf, filter_buf, output_buf, *,
+                bias_buf=None, activation=ACT_NONE, negative_slope=0.0, batch=1, stream=None):
+    """small::GroupConv2D (:1265 float, :1332 quint8): `output_groups` convolutions, each from
+    `input_channels` to `input_channels` channels; the 16 lanes of a block are 16 groups
+    (in [G/16][C][H][W][16], filter [G/16][K][C][Fh][Fw][16], out [G/16][K][Ho][Wo][16])."""
+    _group("GroupConv2D", False, kernel_height, kernel_width, stride, output_groups, t_pad, b_pad,
+           l_pad, r_pad, input_channels, input_height, input_width, input_buf, filter_buf,
+           output_buf, bias_buf, activation, negative_slope, batch, stream)
+
+
+def PartialGroupConv2D(kernel_height, kernel_width, stride, output_groups, t_pad, b_pad, l_pad, r_pad,
+                       input_channels, input_height, input_width, input_buf, filter_buf, output_buf,
+                       *, batch=1, stream=None):
+    """small::PartialGroupConv2D (:1402), float only (the quint8 form, :1470, would reload int32
+    partial sums from the uint8 output)."""
+    if _is_q(output_buf):
+        raise ValueError("PartialGroupConv2D<quint8> ERROR: not provided.")
+    _group("PartialGroupConv2D", True, kernel_height, kernel_width, stride, output_groups, t_pad,
+           b_pad, l_pad, r_pad, input_channels, input_height, input_width, input_buf, filter_buf,
+           output_buf, None, ACT_NONE, 0.0, batch, stream)
+
+
 def MaxPool2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
               input_channels, input_height, input_width, input_buf, output_buf, *,
               batch=1, stream=None):
