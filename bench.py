@@ -379,6 +379,48 @@ def run_one_layer(args):
                       "device_status": _lib.device_status()}))
 
 
+def run_layer_sweep(args):
+    """The single-layer sweep: the 13 convolutions of YOLOv3-tiny at 416x416, fp32, each built,
+    run and timed alone at the given batch (default 256) and charged against its roofline like
+    the layers of a network.  Prints one JSON line with a row per layer; it is a report of layer
+    times, not an inferences/s figure."""
+    import torch
+
+    from smallframework_b200 import networks
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    batch = args.batch or 256
+    wl = dict(dtype="f32")
+    rows, total_ms, total_flops = [], 0.0, 0.0
+    with ClockSampler(0) as clk:
+        for layers in networks.yolov3_tiny_convs(seed=3):
+            chain = networks.Chain(layers, batch, "f32")
+            c, h, w = networks.input_shape(layers)
+            g = torch.Generator(device="cuda").manual_seed(3)
+            chain.x.copy_(torch.rand(chain.x.numel(), device="cuda", generator=g) * 2 - 1)
+            chain.enqueue()
+            chain.stream.synchronize()
+            rep = per_layer_report(chain, layers, batch, wl, {"sm_mhz": 1965.0}, torch)  # alone: full clocks
+            row = rep["layers"][0]
+            L = layers[0]
+            row["shape"] = f"{L['C']}->{L['K']} {L['Fh']}x{L['Fw']} @{L['H']}"
+            rows.append(row)
+            total_ms += row["ms"]
+            total_flops += row["tflops"] * row["ms"]
+            del chain
+            torch.cuda.empty_cache()
+    peaks = load_peaks()
+    print(json.dumps({
+        "workload": f"YOLOv3-tiny convolution layers, fp32, 416x416, batch {batch}, each timed alone",
+        "data": "synthetic (seeded): inputs U[-1,1), weights N(0, 0.05)", "dtype": "f32",
+        "sum_ms": round(total_ms, 4), "mean_tflops": round(total_flops / total_ms, 2) if total_ms else None,
+        "peaks": {"hbm_gbs": peaks["hbm"], "bf16_tflops_burst": peaks["tensor_burst"], "source": peaks["source"]},
+        "clocks": clk.summary(), "layers": rows}), flush=True)
+
+
 # DRAM traffic of the dominant kernel's launch at the bench size, from a one-pass ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum); the profile summary that holds it is named.
 MEASURED_TRAFFIC = {
@@ -500,13 +542,15 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="tinyyolov2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="tinyyolov2", choices=sorted(WORKLOADS) + ["yolov3tiny_layers"])
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-layer", default="",
                     help="run only this layer (by name) --steps times on a small batch: the ncu target")
     args = ap.parse_args()
-    if args.profile_layer:
+    if args.workload == "yolov3tiny_layers":
+        run_layer_sweep(args)
+    elif args.profile_layer:
         run_one_layer(args)
     elif args.impl == "reference":
         run_reference_arm(args)

@@ -363,7 +363,7 @@ class Chain:
         self.prepared = [None] * len(layers)
         if dtype == "f32" and tensor_core:
             for i, L in enumerate(layers):
-                if L["op"] != "conv" or i == 0:
+                if L["op"] != "conv" or (i == 0 and L["C"] % CB != 0):
                     continue
                 ho, wo = _out_hw(L)
                 if tensor_core == "auto" and (L["C"] < self.TC_MIN_CHANNELS or ho * wo < 32):
