@@ -98,7 +98,7 @@ inline void conv_then_pool(int act, BufferT const *bias, SMALL_B200_CONV_ARGS, S
         if (small_b200_conv2d_maxpool_f32_supported(&Lc, &Lp))
         {
             throw_on(small_b200_conv2d_maxpool_f32(&Lc, &Lp, in.device_ptr(), filt.device_ptr(),
-                                                   bias ? bias->device_ptr() : nullptr, out.device_ptr(), nullptr));
+                                                   bias ? bias->device_ptr() : nullptr, out.device_ptr(), b200::stream()));
             return;
         }
     }

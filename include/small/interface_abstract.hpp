@@ -77,7 +77,7 @@ inline void conv(bool partial, int act, int kh, int kw, int stride, int t, int b
         if (bias)
             throw std::invalid_argument("Conv2D<quint8> ERROR: a uint8 bias buffer is not meaningful; "
                                         "pass an int32 bias through the C ABI.");
-        throw_on(small_b200_conv2d_u8(&L, in.device_ptr(), filt.device_ptr(), nullptr, out.device_ptr(), nullptr));
+        throw_on(small_b200_conv2d_u8(&L, in.device_ptr(), filt.device_ptr(), nullptr, out.device_ptr(), b200::stream()));
     }
     else
     {
@@ -92,14 +92,14 @@ inline void conv(bool partial, int act, int kh, int kw, int stride, int t, int b
             if (!prepared)
             {
                 prepared = filt.make_companion(key, 2 * (size_t)K * C * kh * kw);
-                throw_on(small_b200_filter_prepare_tf32x3(&L, filt.device_ptr(), prepared, nullptr));
+                throw_on(small_b200_filter_prepare_tf32x3(&L, filt.device_ptr(), prepared, b200::stream()));
             }
             throw_on(small_b200_conv2d_f32_tf32x3(&L, in.device_ptr(), prepared, bias ? bias->device_ptr() : nullptr,
-                                                  out.device_ptr(), nullptr));
+                                                  out.device_ptr(), b200::stream()));
         }
         else
             throw_on(small_b200_conv2d_f32(&L, in.device_ptr(), filt.device_ptr(),
-                                           bias ? bias->device_ptr() : nullptr, out.device_ptr(), nullptr));
+                                           bias ? bias->device_ptr() : nullptr, out.device_ptr(), b200::stream()));
     }
 }
 
@@ -114,11 +114,11 @@ inline void dwconv(bool partial, int act, int kh, int kw, int stride, int t, int
     {
         if (partial || bias)
             throw std::invalid_argument("DepthwiseConv2D<quint8> ERROR: partial / bias form not provided.");
-        throw_on(small_b200_dwconv2d_u8(&L, in.device_ptr(), filt.device_ptr(), nullptr, out.device_ptr(), nullptr));
+        throw_on(small_b200_dwconv2d_u8(&L, in.device_ptr(), filt.device_ptr(), nullptr, out.device_ptr(), b200::stream()));
     }
     else
         throw_on(small_b200_dwconv2d_f32(&L, in.device_ptr(), filt.device_ptr(),
-                                         bias ? bias->device_ptr() : nullptr, out.device_ptr(), nullptr));
+                                         bias ? bias->device_ptr() : nullptr, out.device_ptr(), b200::stream()));
 }
 
 template <class BufferT>
@@ -132,10 +132,10 @@ inline void groupconv(bool partial, int kh, int kw, int stride, int groups, int 
     quantise(L, in, &filt, out);
     if constexpr (is_quint8<BufferT>)
         throw_on(small_b200_groupconv2d_u8(&L, groups, in.device_ptr(), filt.device_ptr(), nullptr,
-                                           out.device_ptr(), nullptr));
+                                           out.device_ptr(), b200::stream()));
     else
         throw_on(small_b200_groupconv2d_f32(&L, groups, in.device_ptr(), filt.device_ptr(), nullptr,
-                                            out.device_ptr(), nullptr));
+                                            out.device_ptr(), b200::stream()));
 }
 
 template <class BufferT>
@@ -146,10 +146,10 @@ inline void pool(bool average, int kh, int kw, int stride, int t, int b, int l, 
     quantise(L, in, (BufferT const *)nullptr, out);
     if constexpr (is_quint8<BufferT>)
         throw_on((average ? small_b200_avgpool2d_u8 : small_b200_maxpool2d_u8)(
-            &L, in.device_ptr(), out.device_ptr(), nullptr));
+            &L, in.device_ptr(), out.device_ptr(), b200::stream()));
     else
         throw_on((average ? small_b200_avgpool2d_f32 : small_b200_maxpool2d_f32)(
-            &L, in.device_ptr(), out.device_ptr(), nullptr));
+            &L, in.device_ptr(), out.device_ptr(), b200::stream()));
 }
 
 inline void require_block(int channels, int block, char const *msg)
@@ -260,12 +260,12 @@ void ReLUActivation(int input_channels, int input_height, int input_width,
         small_b200_layer L = b200::describe(input_channels, input_channels, input_height, input_width,
                                             1, 1, 1, 0, 0, 0, 0);
         b200::quantise(L, input_buf, (BufferT const *)nullptr, output_buf);
-        b200::throw_on(small_b200_relu_u8(n, &L, input_buf.device_ptr(), output_buf.device_ptr(), nullptr));
+        b200::throw_on(small_b200_relu_u8(n, &L, input_buf.device_ptr(), output_buf.device_ptr(), b200::stream()));
     }
     else
     {
         b200::require_block(input_channels, FLOAT_C_ib, "ReLUActivation<float> ERROR: in_channels unsupported.");
-        b200::throw_on(small_b200_relu_f32(n, input_buf.device_ptr(), output_buf.device_ptr(), nullptr));
+        b200::throw_on(small_b200_relu_f32(n, input_buf.device_ptr(), output_buf.device_ptr(), b200::stream()));
     }
 }
 
@@ -276,9 +276,9 @@ void LeakyReLUActivation(int input_channels, int input_height, int input_width,
 {
     static_assert(!b200::is_quint8<BufferT>, "LeakyReLUActivation: no quint8 form in the reference either");
     b200::require_block(input_channels, FLOAT_C_ib, "LeakyReLUActivation<float> ERROR: in_channels unsupported.");
-    const float slope = filter_buf.data()[0];
+    const float slope = filter_buf.peek(0); // a parameter no kernel writes: no wait for the device
     const int64_t n = (int64_t)b200::batch() * input_channels * input_height * input_width;
-    b200::throw_on(small_b200_leaky_relu_f32(n, input_buf.device_ptr(), slope, output_buf.device_ptr(), nullptr));
+    b200::throw_on(small_b200_leaky_relu_f32(n, input_buf.device_ptr(), slope, output_buf.device_ptr(), b200::stream()));
 }
 
 template <class BufferT, bool = true>
@@ -294,7 +294,7 @@ void SoftMax(int input_channels, int input_height, int input_width,
     static_assert(!b200::is_quint8<BufferT>, "SoftMax: float only, as in the reference");
     b200::require_block(input_channels, FLOAT_C_ib, "SoftMax<float> ERROR: in_channels unsupported.");
     b200::throw_on(small_b200_softmax_f32(b200::batch(), (int64_t)input_channels * input_height * input_width,
-                                          input_buf.device_ptr(), output_buf.device_ptr(), nullptr));
+                                          input_buf.device_ptr(), output_buf.device_ptr(), b200::stream()));
 }
 
 template <class BufferT, bool = true>
@@ -308,7 +308,7 @@ void UpSample2D(int scale_factor, int input_channels, int input_height, int inpu
     {
         b200::require_block(input_channels, FLOAT_C_ib, "Upsample<float> ERROR: in_channels unsupported.");
         b200::throw_on(small_b200_upsample2d_f32(b200::batch(), input_channels, input_height, input_width,
-                                                 input_buf.device_ptr(), output_buf.device_ptr(), nullptr));
+                                                 input_buf.device_ptr(), output_buf.device_ptr(), b200::stream()));
     }
     else
         throw std::invalid_argument("Upsample<float> ERROR: scale factor unsupported (only 1 or 2).");
@@ -321,7 +321,7 @@ void Accum(int input_channels, int input_height, int input_width,
     static_assert(!b200::is_quint8<BufferT>, "Accum: float only, as in the reference");
     b200::require_block(input_channels, FLOAT_C_ib, "Accum<float> ERROR: in_channels unsupported.");
     const int64_t n = (int64_t)b200::batch() * input_channels * input_height * input_width;
-    b200::throw_on(small_b200_accum_f32(n, input_buf.device_ptr(), output_buf.device_ptr(), nullptr));
+    b200::throw_on(small_b200_accum_f32(n, input_buf.device_ptr(), output_buf.device_ptr(), b200::stream()));
 }
 
 template <class BufferT, bool = true>
@@ -331,7 +331,7 @@ void Bias(int num_channels, int output_height, int output_width,
     static_assert(!b200::is_quint8<BufferT>, "Bias: float only, as in the reference");
     b200::require_block(num_channels, FLOAT_C_ob, "Bias<float> ERROR: in_channels unsupported.");
     b200::throw_on(small_b200_bias_f32(b200::batch(), num_channels, output_height, output_width,
-                                       input_buf.device_ptr(), 0, output_buf.device_ptr(), nullptr));
+                                       input_buf.device_ptr(), 0, output_buf.device_ptr(), b200::stream()));
 }
 
 template <class BufferT, bool = true>
@@ -341,7 +341,7 @@ void PartialBias(int num_channels, int output_height, int output_width,
     static_assert(!b200::is_quint8<BufferT>, "PartialBias: float only, as in the reference");
     b200::require_block(num_channels, FLOAT_C_ob, "PartialBias<float> ERROR: in_channels unsupported.");
     b200::throw_on(small_b200_bias_f32(b200::batch(), num_channels, output_height, output_width,
-                                       input_buf.device_ptr(), 1, output_buf.device_ptr(), nullptr));
+                                       input_buf.device_ptr(), 1, output_buf.device_ptr(), b200::stream()));
 }
 
 // Channel concatenation of two packed buffers = two contiguous copies per image
@@ -356,7 +356,7 @@ void Concat(uint32_t input0_channels, uint32_t input1_channels,
                                      (size_t)input0_channels * input_height * input_width * esz,
                                      input0_buf.device_ptr(),
                                      (size_t)input1_channels * input_height * input_width * esz,
-                                     input1_buf.device_ptr(), output_buf.device_ptr(), nullptr));
+                                     input1_buf.device_ptr(), output_buf.device_ptr(), b200::stream()));
 }
 
 // The reference's Dense is a placeholder that instantiates a 1x1 depthwise operation over a

@@ -46,6 +46,26 @@ struct BatchScope
     ~BatchScope() { batch() = saved; }
 };
 
+// Stream the layer calls of this thread are enqueued on (nullptr = the default stream), and
+// whether that stream is being captured into a graph (see InferenceGraph below).
+inline void *&stream()
+{
+    static thread_local void *s = nullptr;
+    return s;
+}
+inline bool &capturing()
+{
+    static thread_local bool c = false;
+    return c;
+}
+
+struct StreamScope
+{
+    void *saved;
+    explicit StreamScope(void *s) : saved(stream()) { stream() = s; }
+    ~StreamScope() { stream() = saved; }
+};
+
 inline void throw_on(int rc)
 {
     if (rc == SMALL_B200_OK)
@@ -60,6 +80,9 @@ inline void throw_on(int rc)
 
 inline void sync_for_host()
 {
+    if (capturing())
+        throw std::runtime_error("small::b200: host access to a buffer (data(), operator[], copy) while a graph "
+                                 "is being captured; a captured inference must only enqueue layer calls");
     if (pending())
     {
         throw_on(small_b200_device_sync());
@@ -137,6 +160,10 @@ public:
         return m_buffer[index];
     }
 
+    // Element i as the host sees it, without waiting for the device and without marking the buffer
+    // host-touched: for small read-only parameters (an activation slope) that no kernel writes.
+    T peek(size_t index) const { return m_buffer[index]; }
+
     void swap(ManagedArray &other) noexcept
     {
         std::swap(m_num_elts, other.m_num_elts);
@@ -164,9 +191,9 @@ public:
     // Device view for a layer call: no wait; brings host-touched pages back first.
     T *device_ptr() const
     {
-        if (m_host_touched && m_buffer)
+        if (m_host_touched && m_buffer && !capturing()) // a capture only records kernels; pages move on demand
         {
-            small_b200_prefetch(m_buffer, m_num_elts * sizeof(T), nullptr);
+            small_b200_prefetch(m_buffer, m_num_elts * sizeof(T), stream());
             m_host_touched = false;
         }
         pending() = true;
@@ -219,6 +246,82 @@ private:
     mutable bool m_host_touched;
     mutable T *m_companion;
     mutable uint64_t m_companion_key;
+};
+// A whole inference as one CUDA graph.  The reference's Model classes (Model.hpp:74,
+// models/TinyYoloV2.hpp:93, DSCNNTiny.hpp, Resnet8Tiny.hpp, MobileNetTiny.hpp) run a network as a
+// sequence of Layer::compute_output() calls, each of which ends in the layer functions of this
+// platform; on a GPU every one of them is a kernel launch from the host.  capture() runs the
+// callable once as it is (so that buffers are on the device and filters are re-laid where the
+// tensor-core convolution wants them: nothing is left to allocate), then once more with this
+// thread's layer calls recorded into a graph; launch() replays the recorded kernels on the same
+// buffers with one call.  Whatever the callable returned in the recorded run (the model's output
+// tensors) is where every replay leaves its results.  Combine with BatchScope for a batch.
+//     small::b200::InferenceGraph g;
+//     std::vector<small::Tensor<BufferT>*> out;
+//     g.capture([&] { out = model.inference(&input); });
+//     g.launch(); ... out[0]->buffer()[i]   // host access waits for the device
+// The callable must only enqueue layer calls: host access to a buffer inside it throws.
+class InferenceGraph
+{
+public:
+    InferenceGraph() : m_stream(nullptr), m_exec(nullptr) { throw_on(small_b200_stream_create(&m_stream)); }
+    InferenceGraph(InferenceGraph const &) = delete;
+    InferenceGraph &operator=(InferenceGraph const &) = delete;
+    ~InferenceGraph()
+    {
+        small_b200_device_sync();
+        if (m_exec)
+            small_b200_graph_destroy(m_exec);
+        small_b200_stream_destroy(m_stream);
+    }
+
+    template <class Callable>
+    void capture(Callable &&run)
+    {
+        if (m_exec)
+        {
+            throw_on(small_b200_device_sync());
+            throw_on(small_b200_graph_destroy(m_exec));
+            m_exec = nullptr;
+        }
+        run();
+        throw_on(small_b200_device_sync());
+        pending() = false;
+        StreamScope on(m_stream);
+        throw_on(small_b200_graph_begin(m_stream));
+        capturing() = true;
+        try
+        {
+            run();
+        }
+        catch (...)
+        {
+            capturing() = false;
+            void *dead = nullptr;
+            small_b200_graph_end(m_stream, &dead); // ends the capture; its graph is discarded
+            if (dead)
+                small_b200_graph_destroy(dead);
+            throw;
+        }
+        capturing() = false;
+        throw_on(small_b200_graph_end(m_stream, &m_exec));
+        pending() = false; // the recorded run launched nothing
+    }
+
+    bool captured() const { return m_exec != nullptr; }
+
+    void launch()
+    {
+        if (!m_exec)
+            throw std::logic_error("small::b200::InferenceGraph::launch before capture");
+        throw_on(small_b200_graph_launch(m_exec, m_stream));
+        pending() = true;
+    }
+
+    void sync() { throw_on(small_b200_stream_sync(m_stream)); }
+
+private:
+    void *m_stream, *m_exec;
 };
 } // namespace b200
 

@@ -1,0 +1,173 @@
+// model_graph.cpp -- the reference's Model classes on the B200 platform, eager and as one CUDA graph.
+//
+// Builds small::TinyYoloV2<FloatBuffer> (include/small/models/TinyYoloV2.hpp of the reference, used
+// unchanged) with seeded random filters, runs inference() the way the reference's drivers do
+// (every layer call is a kernel launch from the host), then records the same inference() with
+// small::b200::InferenceGraph and replays it.  Checks:
+//   - the replayed graph leaves bit-identical results to the eager run, on repeated replays too;
+//   - with small::b200::BatchScope(B) and an input shape whose batch entry is B, every image of
+//     the batch equals the single-image result of that image;
+//   - host access to a buffer inside a capture is refused with an exception, and the graph object
+//     can be used again afterwards.
+// Prints the time per inference of both forms.  Exit code 0 = all checks passed.
+//
+//   model_graph [image size = 416] [batch = 4] [timed runs = 20]
+#include <chrono>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <random>
+#include <vector>
+
+#include <small.h>
+#include <small/models/TinyYoloV2.hpp>
+
+using BufferT = small::FloatBuffer;
+
+static double now_ms()
+{
+    using namespace std::chrono;
+    return duration<double, std::milli>(steady_clock::now().time_since_epoch()).count();
+}
+
+static void fill(BufferT &b, std::mt19937 &rng, float lo, float hi)
+{
+    std::uniform_real_distribution<float> d(lo, hi);
+    float *p = b.data();
+    for (size_t i = 0; i < b.size(); ++i)
+        p[i] = d(rng);
+}
+
+int main(int argc, char **argv)
+{
+    const uint32_t size = argc > 1 ? (uint32_t)std::atoi(argv[1]) : 416;
+    const uint32_t batch = argc > 2 ? (uint32_t)std::atoi(argv[2]) : 4;
+    const int runs = argc > 3 ? std::atoi(argv[3]) : 20;
+    int failures = 0;
+    std::mt19937 rng(4);
+
+    // filters of the nine convolutions, already in the packed layout (random numbers have no order)
+    const uint32_t chans[10] = {3, 16, 32, 64, 128, 256, 512, 1024, 1024, 16};
+    std::vector<BufferT *> filters;
+    for (int l = 0; l < 9; ++l)
+    {
+        const uint32_t k = (l == 8) ? 1 : 3;
+        BufferT *f = new BufferT((size_t)chans[l + 1] * chans[l] * k * k);
+        const float bound = std::sqrt(6.0f / (float)(chans[l] * k * k)); // He-uniform keeps activations O(1)
+        fill(*f, rng, -bound, bound);
+        filters.push_back(f);
+    }
+
+    // ---- one image: eager, then recorded and replayed
+    std::vector<float> single;
+    {
+        small::shape_type shape({1UL, 3UL, size, size});
+        BufferT image((size_t)3 * size * size);
+        fill(image, rng, 0.f, 1.f);
+        small::TinyYoloV2<BufferT> model(shape, filters, true);
+        small::Tensor<BufferT> input(shape, image);
+
+        auto out = model.inference(&input);
+        const size_t n = out[0]->size();
+        single.assign(out[0]->buffer().data(), out[0]->buffer().data() + n);
+
+        double t0 = now_ms();
+        for (int r = 0; r < runs; ++r)
+            out = model.inference(&input);
+        (void)out[0]->buffer().data(); // waits for the device
+        const double eager_ms = (now_ms() - t0) / runs;
+
+        small::b200::InferenceGraph graph;
+        std::vector<small::Tensor<BufferT> *> gout;
+        graph.capture([&] { gout = model.inference(&input); });
+        for (int rep = 0; rep < 2; ++rep)
+        {
+            graph.launch();
+            const float *g = gout[0]->buffer().data();
+            if (gout[0]->size() != n || std::memcmp(g, single.data(), n * sizeof(float)) != 0)
+            {
+                std::printf("FAIL: replay %d differs from the eager run\n", rep);
+                ++failures;
+            }
+        }
+        t0 = now_ms();
+        for (int r = 0; r < runs; ++r)
+            graph.launch();
+        graph.sync();
+        const double graph_ms = (now_ms() - t0) / runs;
+        std::printf("TinyYoloV2 %ux%u, 1 image: eager %.3f ms, graph %.3f ms per inference\n", size, size,
+                    eager_ms, graph_ms);
+
+        // host access inside a capture is an error, and the object survives it
+        bool threw = false;
+        try
+        {
+            graph.capture([&] {
+                gout = model.inference(&input);
+                (void)gout[0]->buffer().data();
+            });
+        }
+        catch (std::runtime_error const &)
+        {
+            threw = true;
+        }
+        if (!threw)
+        {
+            std::printf("FAIL: host access inside a capture was not refused\n");
+            ++failures;
+        }
+        graph.capture([&] { gout = model.inference(&input); });
+        graph.launch();
+        if (std::memcmp(gout[0]->buffer().data(), single.data(), n * sizeof(float)) != 0)
+        {
+            std::printf("FAIL: replay after a refused capture differs\n");
+            ++failures;
+        }
+    }
+
+    // ---- a batch: image-major [B][C/16][H][W][16]; every image must equal its single-image result
+    {
+        small::shape_type shape({(size_t)batch, 3UL, size, size});
+        const size_t per_image = (size_t)3 * size * size;
+        BufferT images(per_image * batch);
+        fill(images, rng, 0.f, 1.f);
+        small::b200::BatchScope scope((int)batch);
+        small::TinyYoloV2<BufferT> model(shape, filters, true);
+        small::Tensor<BufferT> input(shape, images);
+        small::b200::InferenceGraph graph;
+        std::vector<small::Tensor<BufferT> *> gout;
+        graph.capture([&] { gout = model.inference(&input); });
+        graph.launch();
+        const size_t n = gout[0]->size() / batch;
+        std::vector<float> batched(gout[0]->buffer().data(), gout[0]->buffer().data() + n * batch);
+        double t0 = now_ms();
+        for (int r = 0; r < runs; ++r)
+            graph.launch();
+        graph.sync();
+        std::printf("TinyYoloV2 %ux%u, %u images: graph %.3f ms per image\n", size, size, batch,
+                    (now_ms() - t0) / runs / batch);
+
+        small::b200::BatchScope one(1);
+        small::shape_type shape1({1UL, 3UL, size, size});
+        small::TinyYoloV2<BufferT> model1(shape1, filters, true);
+        for (uint32_t b = 0; b < batch; ++b)
+        {
+            BufferT image(per_image);
+            std::memcpy(image.data(), images.data() + b * per_image, per_image * sizeof(float));
+            small::Tensor<BufferT> input1(shape1, image);
+            auto out = model1.inference(&input1);
+            if (out[0]->size() != n ||
+                std::memcmp(out[0]->buffer().data(), batched.data() + b * n, n * sizeof(float)) != 0)
+            {
+                std::printf("FAIL: image %u of the batch differs from its single-image result\n", b);
+                ++failures;
+            }
+        }
+    }
+
+    for (auto f : filters)
+        delete f;
+    std::printf(failures ? "FAILED (%d)\n" : "OK\n", failures);
+    return failures ? 1 : 0;
+}

@@ -58,3 +58,19 @@ def test_reference_driver_on_tensor_cores(name):
                        stderr=subprocess.STDOUT, text=True, timeout=900)
     tail = "\n".join(r.stdout.splitlines()[-25:])
     assert r.returncode == 0, f"{name} failed with SMALL_B200_TENSOR_CORE=1:\n{tail}"
+
+
+@pytest.mark.parametrize("tensor_core", ["0", "1"])
+def test_model_classes_as_cuda_graph(tensor_core):
+    """tests/drivers/model_graph.cpp: the reference's TinyYoloV2 Model class run eagerly, recorded with
+    small::b200::InferenceGraph and replayed (bit-identical), and batched with BatchScope (every image
+    equals its single-image result)."""
+    exe = os.path.join(BUILD, "bin", "model_graph")
+    if not os.path.exists(exe):
+        pytest.skip(f"{exe} not built (run make -C tests/reference_drivers where the reference is mounted)")
+    env = dict(os.environ, OMP_NUM_THREADS="4", SMALL_B200_TENSOR_CORE=tensor_core)
+    r = subprocess.run([exe, "416", "3", "10"], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                       text=True, timeout=900)
+    tail = "\n".join(l for l in r.stdout.splitlines() if not l.startswith("Model::dtor"))[-2000:]
+    print(tail)
+    assert r.returncode == 0, f"model_graph failed (SMALL_B200_TENSOR_CORE={tensor_core}):\n{tail}"

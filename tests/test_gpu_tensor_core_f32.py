@@ -27,6 +27,11 @@ CASES = [
     (512, 128, 13, 13, 3, 3, "same", 1),    # long reduction: 32 channel blocks
     (1024, 128, 13, 13, 3, 3, "same", 1),   # the longest reduction of the configurations (9216 terms)
     (1024, 128, 13, 13, 1, 1, "valid", 2),
+    # pointwise layers fetch their patches with plain asynchronous copies: several pixel tiles per
+    # image with a partial last one, a plane smaller than a patch, many tiles per CTA
+    (256, 256, 26, 26, 1, 1, "valid", 2),
+    (64, 128, 7, 5, 1, 1, "valid", 5),
+    (32, 144, 13, 13, 1, 1, "valid", 160),
     # wide images: TH x TW pixel tiles (partial tiles at the right and bottom edges)
     (16, 32, 40, 130, 3, 3, "same", 2),
     (32, 64, 70, 90, 3, 3, "same", 1),
