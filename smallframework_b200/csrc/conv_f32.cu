@@ -413,7 +413,12 @@ conv2d_first_pool_f32_kernel(const ConvArgs a, const float *__restrict__ in, con
 // The same for compile-time shapes (the 3-channel 3x3 first layer of the image networks): the
 // (FH+1) x (FW+1) x C input patch of the 2x2 block sits in registers and every filter vector
 // fetched from shared memory feeds all four outputs (16 FMAs per 128-bit load).
-template <int C, int FH, int FW>
+// POOL = false: the same register patch without the pool (the first layer on its own): the four
+// outputs of a thread's 2x2 block are stored.  A thread's two outputs of a row are 128 contiguous
+// bytes and a warp's are 4 KB, but written straight from the registers every store instruction
+// would touch 32 separate 16-byte pieces; the warp passes each row through its own 4.5 KB of shared
+// memory (144-byte pitch: conflict-free both ways) and writes 512 contiguous bytes per instruction.
+template <int C, int FH, int FW, bool POOL = true>
 __global__ void __launch_bounds__(128)
 conv2d_first_pool_fixed_f32_kernel(const ConvArgs a, const float *__restrict__ in, const float *__restrict__ filt,
                                    const float *__restrict__ bias, float *__restrict__ out)
@@ -427,9 +432,14 @@ conv2d_first_pool_fixed_f32_kernel(const ConvArgs a, const float *__restrict__ i
         w[i] = fsrc[i];
     __syncthreads();
     const int Hp = a.Ho / 2, Wp = a.Wo / 2;
-    const int p = blockIdx.x * blockDim.x + threadIdx.x;
-    if (p >= Hp * Wp)
-        return;
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool live = p < Hp * Wp;
+    if (!live)
+    {
+        if (POOL)
+            return;
+        p = Hp * Wp - 1; // computes a pixel it will not store: the warp's staging needs every lane
+    }
     const int ph = p / Wp, pw = p - ph * Wp;
     const float *img = in + (size_t)n * C * a.H * a.W;
     const int ih0 = 2 * ph - a.pad_t, iw0 = 2 * pw - a.pad_l;
@@ -479,6 +489,44 @@ conv2d_first_pool_fixed_f32_kernel(const ConvArgs a, const float *__restrict__ i
                     }
                 }
             }
+    if (!POOL)
+    {
+        __shared__ __align__(16) float stage[4][32 * 36]; // per warp: 32 threads x (128 bytes + 16 of padding)
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        float *mine = stage[warp] + lane * 36;
+        const float ns = act_neg_scale(a.act, a.slope);
+        float *plane = out + ((size_t)n * (a.K / CB) + kb) * a.Ho * a.Wo * CB;
+#pragma unroll
+        for (int dr = 0; dr < 2; ++dr)
+        {
+#pragma unroll
+            for (int dc = 0; dc < 2; ++dc)
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4)
+                {
+                    const float *ac = acc[dr * 2 + dc] + k4 * 4;
+                    *reinterpret_cast<float4 *>(mine + dc * 16 + k4 * 4) =
+                        make_float4(apply_act_ns(ac[0], ns), apply_act_ns(ac[1], ns), apply_act_ns(ac[2], ns),
+                                    apply_act_ns(ac[3], ns));
+                }
+            __syncwarp();
+            // piece j of the warp's 32 x 8 pieces belongs to thread j / 8: pooled pixel p0 + j / 8
+#pragma unroll
+            for (int it = 0; it < 8; ++it)
+            {
+                const int j = it * 32 + lane, t = j >> 3, piece = j & 7;
+                const int pt = blockIdx.x * blockDim.x + warp * 32 + t;
+                if (pt < Hp * Wp)
+                {
+                    const int pht = pt / Wp, pwt = pt - pht * Wp;
+                    const float4 v = *reinterpret_cast<const float4 *>(stage[warp] + t * 36 + piece * 4);
+                    *reinterpret_cast<float4 *>(plane + ((size_t)(2 * pht + dr) * a.Wo + 2 * pwt) * CB + piece * 4) = v;
+                }
+            }
+            __syncwarp();
+        }
+        return;
+    }
     float *o = out + (((size_t)n * (a.K / CB) + kb) * Hp * Wp + p) * CB;
 #pragma unroll
     for (int k4 = 0; k4 < CB; k4 += 4)
@@ -544,6 +592,14 @@ int conv2d_f32_impl(const small_b200_layer *L, int pool, const float *in, const 
             }
             conv2d_first_pool_f32_kernel<<<grid, 128, smem, st>>>(a, in, filt, bias, out);
             return launched("conv2d_first_pool_f32_kernel");
+        }
+        if (L->C == 3 && L->Fh == 3 && L->Fw == 3 && L->stride == 1 && !L->accumulate && a.Ho % 2 == 0 &&
+            a.Wo % 2 == 0 && a.Ho > 0 && a.Wo > 0)
+        {
+            // 2x2 output blocks from a register patch, rows written through shared memory
+            dim3 grid(((a.Ho / 2) * (a.Wo / 2) + 127) / 128, a.K / CB, a.N);
+            conv2d_first_pool_fixed_f32_kernel<3, 3, 3, false><<<grid, 128, 0, st>>>(a, in, filt, bias, out);
+            return launched("conv2d_first_fixed_f32_kernel");
         }
         dim3 grid((a.Ho * a.Wo + 255) / 256, a.K / CB, a.N);
         conv2d_first_f32_kernel<<<grid, 256, smem, st>>>(a, in, filt, bias, out);

@@ -67,6 +67,12 @@ struct TcArgs
     int pixm;          // 1: pixels on the tensor core's M, output channels on its N (K = 32 or 64)
     int tbufs;         // accumulator buffers in tensor memory: 2, or 4 when 4 * NPX <= 512 columns
     int group;         // filter taps summed in tensor memory before a flush
+    // 1x1 layers: `cg` channel blocks travel as ONE patch of cg planes and are summed in tensor memory
+    // as if they were the cg taps of a kernel row (cbs and taps then count these bundles: cbs = C/16/cg,
+    // taps = group = cg).  A group of a 1x1 layer would otherwise be six MMAs, a third of the hand-overs
+    // between the roles that a 3x3 kernel row pays for eighteen.  tap_step: descriptor units (16 bytes)
+    // between the operand positions of two taps of a group: 4 (one pixel) or one plane of the patch.
+    int cg, tap_step;
     int accumulate, act;
     float slope;
     unsigned smem_bytes;
@@ -192,7 +198,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     __shared__ uint32_t tmem_base_s;
 
     const uint32_t entries = (uint32_t)a.PR * a.PW;
-    const uint32_t x_bytes = entries * 64;                      // one patch [entry][16 floats]
+    const uint32_t x_bytes = entries * 64 * (uint32_t)a.cg;     // one patch [plane][entry][16 floats]
     const uint32_t x_part = (x_bytes + 1023u) & ~1023u;         // hi (or lo) copy; keeps the swizzle pattern anchored
     const uint32_t w_part = (uint32_t)a.MT * 64;               // one hi (or lo) tap tile
     uint8_t *sX = smem;                                              // [slot][hi|lo][entry][64 B, 64-byte swizzle]
@@ -220,7 +226,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         const int slot = pc % a.x_slots;
         mbar_expect_tx(&x_full[slot], x_bytes);
         tma_load_4d(sX + (size_t)slot * 2 * x_part, &map_x, 0, T.col_base - a.pad_l, T.row_base - a.pad_t,
-                    T.n * a.cbs + cb_begin + cb, &x_full[slot]);
+                    (T.n * a.cbs + cb_begin + cb) * a.cg, &x_full[slot]);
     };
     auto issue_filter = [&](const Tile &T, int g, int gc) {
         const int st = gc % a.w_stages;
@@ -358,6 +364,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                               PIXM ? 128u : (uint32_t)a.MT, PIXM ? (uint32_t)a.K : (uint32_t)a.NPX);
             const uint64_t x_lo_off = x_part >> 4, w_lo_off = w_half_stage >> 4;
             const uint64_t x_half = 2; // channels 8..15 of the block
+            const uint64_t tap_step = (uint64_t)a.tap_step;
             const uint64_t w_stage_step = (uint64_t)2 * w_half_stage >> 4;
             const uint64_t x_slot_step = (uint64_t)2 * x_part >> 4;
             int slot = 0, xphase = 0, st = 0, wphase = 0, g = 0; // g counts groups over all tiles
@@ -389,7 +396,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                             if (PIXM)
                             {
                                 const uint32_t d0 = tmem + (uint32_t)((g & tb_mask) * mtiles * a.K);
-                                for (int tp = 0; tp < a.group; ++tp, wh += w_tap, xh += 4)
+                                for (int tp = 0; tp < a.group; ++tp, wh += w_tap, xh += tap_step)
                                 {
                                     const uint64_t wl = wh + w_lo_off;
                                     for (int mt = 0; mt < mtiles; ++mt)
@@ -406,7 +413,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                 }
                             }
                             const uint32_t d = tmem + (uint32_t)((g & tb_mask) * a.NPX);
-                            for (int tp = 0; !PIXM && tp < a.group; ++tp, wh += w_tap, xh += 4)
+                            for (int tp = 0; !PIXM && tp < a.group; ++tp, wh += w_tap, xh += tap_step)
                             {
                                 const uint64_t xl = xh + x_lo_off, wl = wh + w_lo_off;
                                 tc_mma_tf32(d, wl, xh, idesc, tp == 0 ? 0u : 1u);
@@ -455,7 +462,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                         // takes the same place in its own buffer, so the swizzle needs no thought.
                         const float4 *xh = reinterpret_cast<const float4 *>(sX + (size_t)slot * 2 * x_part);
                         float4 *xl = reinterpret_cast<float4 *>(sX + (size_t)slot * 2 * x_part + x_part);
-                        const uint32_t total = entries * 4;
+                        const uint32_t total = x_bytes >> 4;
                         for (uint32_t i = (uint32_t)sid; i < total; i += SPLIT_THREADS)
                             xl[i] = lo_of(xh[i]);
                     }
@@ -771,7 +778,7 @@ bool fit_rings(TcArgs &a, bool need_two)
 {
     const size_t limit = 226 * 1024;
     const int entries = a.PR * a.PW;
-    const size_t x_part = ((size_t)entries * 64 + 1023) & ~(size_t)1023;
+    const size_t x_part = ((size_t)entries * 64 * a.cg + 1023) & ~(size_t)1023;
     const size_t w_part = (size_t)a.MT * 64 * a.group;
     const size_t staging = (size_t)64 * (a.MT + 16) * 4; // 32 pixels of each half of the tile
     // {patch slots, filter stages (>= 2: a commit serves both rings)}
@@ -855,12 +862,18 @@ bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm)
     a.MT = pick_mt(a.K);
     a.k_tiles = (a.K + a.MT - 1) / a.MT;
     a.group = a.Fw; // one kernel row per flush: taps = Fh * Fw is a multiple of it
+    a.cg = 1; a.tap_step = 4;
     // few output channels: pixels on the tensor core's M (see the kernel's PIXM paths)
     a.pixm = pixm ? 1 : 0;
     if (a.Ho == 0 || a.Wo == 0)
         return true;
     if (L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r) > 64)
         return plan_tiled(L, a);
+    // 1x1 layer: two channel blocks per patch and per group (see TcArgs::cg)
+    if (a.taps == 1 && a.cbs % 2 == 0)
+    {
+        a.cg = 2; a.cbs /= 2; a.taps = 2; a.group = 2;
+    }
     // GEMM columns of one image: the last valid one is (Ho-1)*PW + Wo-1
     const int m_img = (a.Ho - 1) * a.PW + a.Wo;
     const int tiles256 = (m_img + 255) / 256;
@@ -876,6 +889,14 @@ bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm)
             a.px_tiles = (m_img + npx - 1) / npx;
             const int need = (a.PW - 1) + npx + (a.Fh - 1) * a.PW + (a.Fw - 1);
             a.PR = (need + a.PW - 1) / a.PW;
+            if (a.cg > 1)
+            {
+                // the planes of a patch lie back to back: each must keep the phase of the 64-byte
+                // swizzle (a multiple of eight 64-byte rows)
+                while ((a.PR * a.PW) % 8)
+                    ++a.PR;
+                a.tap_step = a.PR * a.PW * 4;
+            }
             if (a.PR > 256)
                 continue;
             if (fit_rings(a, pass == 0))
@@ -924,9 +945,9 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     CUtensorMap mx;
     {
         // activations [N*cbs][H][W][16 floats]
-        const uint64_t dims[4] = {16, (uint64_t)a.W, (uint64_t)a.H, (uint64_t)a.N * a.cbs};
+        const uint64_t dims[4] = {16, (uint64_t)a.W, (uint64_t)a.H, (uint64_t)a.N * a.cbs * a.cg};
         const uint64_t strides[3] = {64, (uint64_t)a.W * 64, (uint64_t)a.H * a.W * 64};
-        const uint32_t box[4] = {16, (uint32_t)a.PW, (uint32_t)a.PR, 1};
+        const uint32_t box[4] = {16, (uint32_t)a.PW, (uint32_t)a.PR, (uint32_t)a.cg};
         if (int rc = make_tensor_map(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, in, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;
     }
@@ -964,10 +985,10 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     }
     if (a.pixm)
         conv_tf32x3_kernel<true, false, true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
-            mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.taps, a, bias, out, status);
+            mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.Fh * a.Fw, a, bias, out, status);
     else if (a.persistent)
         conv_tf32x3_kernel<true, false><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
-            mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.taps, a, bias, out, status);
+            mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.Fh * a.Fw, a, bias, out, status);
     else if (a.ksplit == 2)
     {
         cudaLaunchConfig_t cfg = {};
@@ -977,12 +998,12 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr; cfg.numAttrs = 1;
-        const float *flo = filt_prepared + (size_t)a.K * a.C * a.taps;
+        const float *flo = filt_prepared + (size_t)a.K * a.C * a.Fh * a.Fw;
         SB_CUDA(cudaLaunchKernelEx(&cfg, conv_tf32x3_kernel<false, true>, mx, filt_prepared, flo, a, bias, out, status));
     }
     else
         conv_tf32x3_kernel<false, false><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
-            mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.taps, a, bias, out, status);
+            mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.Fh * a.Fw, a, bias, out, status);
     return launched("conv_tf32x3_kernel");
 }
 } // extern "C"
