@@ -971,13 +971,16 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     if (a.persistent && blocks > num_sms())
         blocks = num_sms();
     a.ksplit = 1;
-    if (!a.persistent && a.cbs >= 64 && a.cbs % 2 == 0)
+    if (!a.persistent && a.cbs * a.cg >= 64 && a.cbs % 2 == 0)
     {
         // a cluster of two CTAs per tile, each reducing half of the channel blocks, when that
         // shortens the tail: 512 tiles on 148 SMs are 4 rounds, 1024 half tiles are 7 half rounds
         const long long sms = num_sms();
         const long long rounds1 = (tiles + sms - 1) / sms, rounds2 = (2 * tiles + sms - 1) / sms;
-        if (rounds2 * 100 <= rounds1 * 2 * 93)
+        // a 1x1 layer's half tile is too little work to pay for the hand-over between the two CTAs
+        // unless the tiles alone leave SMs idle (measured: 512 tiles of 1024->256 at 13x13 0.22 ms
+        // whole, 0.25 ms split; 64 tiles of 1024->128 0.050 ms whole, 0.035 ms split)
+        if (rounds2 * 100 <= rounds1 * 2 * 93 && (a.cg == 1 || 2 * tiles <= sms))
         {
             a.ksplit = 2;
             blocks = 2 * tiles;
