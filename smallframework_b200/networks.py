@@ -366,8 +366,9 @@ class Chain:
                 if L["op"] != "conv" or (i == 0 and L["C"] % CB != 0):
                     continue
                 ho, wo = _out_hw(L)
-                if tensor_core == "auto" and (L["C"] < self.TC_MIN_CHANNELS or ho * wo < 32):
-                    continue  # narrow layers and 1x1 images (dense heads) stay on the CUDA cores
+                if tensor_core == "auto" and (L["C"] < self.TC_MIN_CHANNELS or padded(L["K"]) < 32 or ho * wo < 9):
+                    continue  # narrow layers (a 16-channel output uses a quarter of the smallest MMA tile)
+                    # and 1x1 / 2x2 images (dense heads) stay on the CUDA cores
                 d = self._desc(L, padded(L["C"]))
                 if not lib().small_b200_conv2d_f32_tf32x3_supported(C.byref(d)):
                     continue
