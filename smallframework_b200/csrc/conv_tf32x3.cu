@@ -73,6 +73,14 @@ struct TcArgs
     // between the roles that a 3x3 kernel row pays for eighteen.  tap_step: descriptor units (16 bytes)
     // between the operand positions of two taps of a group: 4 (one pixel) or one plane of the patch.
     int cg, tap_step;
+    // Output addressing in floats: pixel (r, c) of channel block kb lies at kb * o_kb_stride +
+    // r * o_row_stride + c * 16 behind the image's first element.  Normally Ho*Wo*16 and Wo*16.
+    // rows_view: a 1x1 layer on small images (H*W <= 64) is planned as ONE image whose rows are the
+    // images of the batch (N' = 1, H' = N, W' = H*W): a 1x1 layer has no neighbourhoods, so a tile may
+    // run across images and no tile is mostly empty (a 3x3-pixel image would fill 9 of a tile's 64
+    // columns).  Only the strides differ: input rows are a whole image apart, and so are output rows.
+    int rows_view;
+    long long o_kb_stride, o_row_stride;
     int accumulate, act;
     float slope;
     unsigned smem_bytes;
@@ -485,7 +493,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             const int quarter = warp & 3, mt = (warp - FIRST_ACC_WARP) >> 2;
             const int mtiles = a.NPX >> 7;
             const bool active = mt < mtiles;
-            const size_t plane = (size_t)a.Ho * a.Wo * CB;
+            const size_t plane = (size_t)a.o_kb_stride;
             bool ok = true;
             int gc = 0;
             SB_TILE_LOOP(ok)
@@ -534,7 +542,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     const int r = T.row_base + rl, c = T.col_base + cl;
                     if (cl < T.tw_valid && rl < T.th_valid && r < a.Ho)
                     {
-                        float *o = out + (size_t)T.n * (a.K / CB) * plane + ((size_t)r * a.Wo + c) * CB;
+                        float *o = out + (size_t)T.n * (a.K / CB) * plane + (size_t)r * a.o_row_stride + (size_t)c * CB;
 #pragma unroll
                         for (int kb = 0; kb < 4; ++kb)
                             if (kb * CB < a.K)
@@ -575,7 +583,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         const int pitch = a.MT + 16;
         float *stage = reinterpret_cast<float *>(smem + a.stage_off);
         const int psub = lane >> 2, q4 = lane & 3; // 8 pixels x 4 float4 per warp and step
-        const size_t plane = (size_t)a.Ho * a.Wo * CB;
+        const size_t plane = (size_t)a.o_kb_stride;
         bool ok = true;
         int gc = 0;
         SB_TILE_LOOP(ok)
@@ -673,7 +681,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                         {
                             const float *sp = stage + (size_t)px * pitch + q4 * 4;
                             const uint32_t rp = peer_stage + (uint32_t)(((size_t)px * pitch + q4 * 4) * 4);
-                            float *o = obase + ((size_t)r * a.Wo + c) * CB;
+                            float *o = obase + (size_t)r * a.o_row_stride + (size_t)c * CB;
 #pragma unroll
                             for (int kb = 0; kb < 8; ++kb)
                               if (kb < kbs)
@@ -740,7 +748,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                         if (cl < T.tw_valid && rl < T.th_valid && r < a.Ho)
                         {
                             const float *sp = stage + (size_t)s_row * pitch + q4 * 4;
-                            float *o = obase + ((size_t)r * a.Wo + c) * CB;
+                            float *o = obase + (size_t)r * a.o_row_stride + (size_t)c * CB;
 #pragma unroll
                             for (int kb = 0; kb < 8; ++kb)
                               if (kb < kbs)
@@ -904,12 +912,33 @@ bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm)
         }
     return false;
 }
-bool plan(const small_b200_layer *L, TcArgs &a)
+bool plan_shape(const small_b200_layer *L, TcArgs &a)
 {
     const bool want_pixm = L && (L->K == 32 || L->K == 64);
     if (want_pixm && plan_as(L, a, true))
         return true;
     return plan_as(L, a, false);
+}
+bool plan(const small_b200_layer *L, TcArgs &a)
+{
+    if (L && L->Fh == 1 && L->Fw == 1 && L->stride == 1 && !L->pad_t && !L->pad_b && !L->pad_l && !L->pad_r &&
+        L->N > 1 && L->H > 0 && L->W > 0 && (long long)L->H * L->W <= 64)
+    {
+        small_b200_layer V = *L; // the batch as the rows of one image (TcArgs::rows_view)
+        V.N = 1; V.H = L->N; V.W = L->H * L->W;
+        if (plan_shape(&V, a))
+        {
+            a.rows_view = 1;
+            a.o_kb_stride = (long long)V.W * CB;
+            a.o_row_stride = (long long)(L->K / CB) * V.W * CB;
+            return true;
+        }
+    }
+    if (!plan_shape(L, a))
+        return false;
+    a.o_kb_stride = (long long)a.Ho * a.Wo * CB;
+    a.o_row_stride = (long long)a.Wo * CB;
+    return true;
 }
 } // namespace
 
@@ -946,7 +975,12 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     {
         // activations [N*cbs][H][W][16 floats]
         const uint64_t dims[4] = {16, (uint64_t)a.W, (uint64_t)a.H, (uint64_t)a.N * a.cbs * a.cg};
-        const uint64_t strides[3] = {64, (uint64_t)a.W * 64, (uint64_t)a.H * a.W * 64};
+        uint64_t strides[3] = {64, (uint64_t)a.W * 64, (uint64_t)a.H * a.W * 64};
+        if (a.rows_view) // rows are images (C*P floats apart), planes the channel blocks of one image
+        {
+            strides[1] = (uint64_t)a.C * a.W * 4;
+            strides[2] = (uint64_t)a.W * 64;
+        }
         const uint32_t box[4] = {16, (uint32_t)a.PW, (uint32_t)a.PR, (uint32_t)a.cg};
         if (int rc = make_tensor_map(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, in, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;

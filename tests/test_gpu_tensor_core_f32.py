@@ -32,6 +32,12 @@ CASES = [
     (256, 256, 26, 26, 1, 1, "valid", 2),
     (64, 128, 7, 5, 1, 1, "valid", 5),
     (32, 144, 13, 13, 1, 1, "valid", 160),
+    # pointwise layers on small images: the batch becomes the rows of one image, tiles run across images
+    (128, 256, 3, 3, 1, 1, "valid", 37),
+    (64, 128, 6, 6, 1, 1, "valid", 10),
+    (32, 64, 4, 4, 1, 1, "valid", 70),
+    (48, 32, 8, 8, 1, 1, "valid", 3),
+    (256, 128, 1, 1, 1, 1, "valid", 300),
     # wide images: TH x TW pixel tiles (partial tiles at the right and bottom edges)
     (16, 32, 40, 130, 3, 3, "same", 2),
     (32, 64, 70, 90, 3, 3, "same", 1),
