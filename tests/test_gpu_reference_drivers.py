@@ -45,7 +45,8 @@ def test_reference_driver(name):
 # Drivers that compare the functional chain with the Model / DAGModel classes, or that apply a
 # tolerance relative to the result: they also pass with the tensor-core fp32 convolution switched on
 # (the layer functions then re-lay each filter once and keep that copy with the filter buffer).
-TENSOR_CORE_DRIVERS = ["test_tinyyolov2", "test_resnet8", "test_autoencoder", "test_partial_conv2d"]
+TENSOR_CORE_DRIVERS = ["test_tinyyolov2", "test_resnet8", "test_autoencoder", "test_partial_conv2d", "test_mobilenet",
+                       "test_dscnn", "test_dscnn_square"]
 
 
 @pytest.mark.parametrize("name", TENSOR_CORE_DRIVERS)
