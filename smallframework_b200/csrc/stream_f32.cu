@@ -109,6 +109,78 @@ window_f32_kernel(const WinArgs a, const float *__restrict__ in, const float *__
     st4(dst, acc);
 }
 
+// Depthwise 3x3, stride S: a thread owns four channels of FOUR neighbouring output pixels of a row.
+// The 3 x (3S + 3) input values it needs are loaded once (18 or 27 loads for four outputs instead of
+// 36) and the nine filter vectors once instead of four times; the one-pixel form above is bound by
+// its load instructions, not by memory.  Same order of additions (kernel row, then column); a padded
+// tap enters as zero.  Flat index over [N][C/16][Ho][strips][4 quads].
+template <int S>
+__global__ void __launch_bounds__(256)
+dwconv3x3_f32_strip_kernel(const WinArgs a, int strips, const float *__restrict__ in, const float *__restrict__ filt,
+                           const float *__restrict__ bias, float *__restrict__ out)
+{
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = (long long)a.N * (a.C / CB) * a.Ho * strips * 4;
+    if (i >= total)
+        return;
+    const int q = (int)(i & 3); i >>= 2;
+    const int st = (int)(i % strips); i /= strips;
+    const int oh = (int)(i % a.Ho); i /= a.Ho; // i = n * (C/16) + cb
+    const int cb = (int)(i % (a.C / CB));
+    const float *src = in + (size_t)i * a.H * a.W * CB + q * 4;
+    const int ow0 = st * 4;
+    float *dst = out + (((size_t)i * a.Ho + oh) * a.Wo + ow0) * CB + q * 4;
+    const int h0 = oh * S - a.pad_t, w0 = ow0 * S - a.pad_l;
+    constexpr int NC = 3 * S + 3;
+    float4 f[9];
+#pragma unroll
+    for (int t = 0; t < 9; ++t)
+        f[t] = __ldg(reinterpret_cast<const float4 *>(filt + ((size_t)cb * 9 + t) * CB + q * 4));
+    float4 acc[4];
+#pragma unroll
+    for (int o = 0; o < 4; ++o)
+    {
+        acc[o] = (a.accumulate && ow0 + o < a.Wo) ? ld4(dst + o * CB) : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (bias)
+        {
+            const float4 b = ld4(bias + cb * CB + q * 4);
+            acc[o].x += b.x; acc[o].y += b.y; acc[o].z += b.z; acc[o].w += b.w;
+        }
+    }
+#pragma unroll
+    for (int kh = 0; kh < 3; ++kh)
+    {
+        const int ih = h0 + kh;
+        if (ih < 0 || ih >= a.H)
+            continue;
+        float4 x[NC];
+#pragma unroll
+        for (int j = 0; j < NC; ++j)
+        {
+            const int iw = w0 + j;
+            x[j] = (iw >= 0 && iw < a.W) ? ld4(src + ((size_t)ih * a.W + iw) * CB) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int o = 0; o < 4; ++o)
+#pragma unroll
+            for (int kw = 0; kw < 3; ++kw)
+            {
+                const float4 xv = x[o * S + kw], fv = f[kh * 3 + kw];
+                acc[o].x = fmaf(xv.x, fv.x, acc[o].x); acc[o].y = fmaf(xv.y, fv.y, acc[o].y);
+                acc[o].z = fmaf(xv.z, fv.z, acc[o].z); acc[o].w = fmaf(xv.w, fv.w, acc[o].w);
+            }
+    }
+#pragma unroll
+    for (int o = 0; o < 4; ++o)
+        if (ow0 + o < a.Wo)
+        {
+            float4 v = acc[o];
+            v.x = apply_act(v.x, a.act, a.slope); v.y = apply_act(v.y, a.act, a.slope);
+            v.z = apply_act(v.z, a.act, a.slope); v.w = apply_act(v.w, a.act, a.slope);
+            st4(dst + o * CB, v);
+        }
+}
+
 // OP: 0 ReLU, 1 LeakyReLU, 2 Accum (out += in).  n4 = number of float4.
 template <int OP>
 __global__ void __launch_bounds__(256)
@@ -256,6 +328,16 @@ int small_b200_dwconv2d_f32(const small_b200_layer *L, const float *in, const fl
     const long long items = (long long)a.N * (a.C / CB) * a.Ho * a.Wo * 4;
     if (items == 0)
         return SMALL_B200_OK;
+    if (a.Fh == 3 && a.Fw == 3 && a.Wo >= 4)
+    {
+        const int strips = (a.Wo + 3) / 4;
+        const long long threads = (long long)a.N * (a.C / CB) * a.Ho * strips * 4;
+        if (a.stride == 1)
+            dwconv3x3_f32_strip_kernel<1><<<blocks_for(threads), 256, 0, as_stream(stream)>>>(a, strips, in, filt, bias, out);
+        else
+            dwconv3x3_f32_strip_kernel<2><<<blocks_for(threads), 256, 0, as_stream(stream)>>>(a, strips, in, filt, bias, out);
+        return launched("dwconv3x3_f32_strip_kernel");
+    }
     window_f32_kernel<0><<<blocks_for(items), 256, 0, as_stream(stream)>>>(a, in, filt, bias, out);
     return launched("dwconv2d_f32");
 }
