@@ -366,9 +366,15 @@ class Chain:
                 if L["op"] != "conv" or (i == 0 and L["C"] % CB != 0):
                     continue
                 ho, wo = _out_hw(L)
-                if tensor_core == "auto" and (L["C"] < self.TC_MIN_CHANNELS or padded(L["K"]) < 32 or ho * wo < 9):
+                # 1x1 layers of a batch on small images (dense heads included): the tensor-core kernel
+                # takes the batch as the rows of one image, so its tiles are full whatever the image size
+                across_images = (L["Fh"] == 1 and L["Fw"] == 1 and L["stride"] == 1 and not any(L["pads"])
+                                 and L["H"] * L["W"] <= 64 and batch * L["H"] * L["W"] >= 256)
+                if tensor_core == "auto" and L["C"] < self.TC_MIN_CHANNELS:
+                    continue
+                if tensor_core == "auto" and not across_images and (padded(L["K"]) < 32 or ho * wo < 9):
                     continue  # narrow layers (a 16-channel output uses a quarter of the smallest MMA tile)
-                    # and 1x1 / 2x2 images (dense heads) stay on the CUDA cores
+                    # and tiny images stay on the CUDA cores
                 d = self._desc(L, padded(L["C"]))
                 if not lib().small_b200_conv2d_f32_tf32x3_supported(C.byref(d)):
                     continue
