@@ -85,11 +85,10 @@ inline void conv(bool partial, int act, int kh, int kw, int stride, int t, int b
         // kernel wants the filter re-laid; that copy is made once and kept with the filter buffer
         // until the host touches the buffer again.
         const int Ho = small::output_dim(H + t + b, stride, kh), Wo = small::output_dim(W + l + r, stride, kw);
-        // (not 16-channel outputs, a quarter of the smallest MMA tile; small images only for 1x1
-        // layers of a batch, whose tiles run across images)
+        // (small images only for 1x1 layers of a batch, whose tiles run across images)
         const bool across_images = kh == 1 && kw == 1 && stride == 1 && !t && !b && !l && !r && H * W <= 64 &&
                                    (long long)H * W * batch() >= 256; // dense heads of a batch included
-        const bool wide_enough = across_images || (K >= 32 && Ho * Wo >= 32);
+        const bool wide_enough = across_images || Ho * Wo >= 32;
         if (tensor_core_enabled() && C >= 16 && wide_enough && small_b200_conv2d_f32_tf32x3_supported(&L))
         {
             const uint64_t key = ((uint64_t)K << 40) ^ ((uint64_t)C << 20) ^ ((uint64_t)kh << 8) ^ (uint64_t)kw;

@@ -518,6 +518,17 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     if (active)
                     {
                         const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((tb * mtiles + mt) * a.K);
+                        if (a.K == 16) // a buffer is 16 columns wide: the 32-column load would reach past it
+                        {
+                            uint32_t v[16];
+                            tmem_ld16(tbase, v);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int e = 0; e < 16; ++e)
+                                acc[e] += __uint_as_float(v[e]);
+                        }
+                        else
+                        {
 #pragma unroll
                         for (int piece = 0; piece < 2; ++piece)
                             if (piece * 32 < a.K)
@@ -529,6 +540,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                 for (int e = 0; e < 32; ++e)
                                     acc[piece * 32 + e] += __uint_as_float(v[e]);
                             }
+                        }
                     }
                     tc_fence_before_sync();
                     __syncwarp();
@@ -914,7 +926,7 @@ bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm)
 }
 bool plan_shape(const small_b200_layer *L, TcArgs &a)
 {
-    const bool want_pixm = L && (L->K == 32 || L->K == 64);
+    const bool want_pixm = L && (L->K == 16 || L->K == 32 || L->K == 64);
     if (want_pixm && plan_as(L, a, true))
         return true;
     return plan_as(L, a, false);

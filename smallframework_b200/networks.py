@@ -372,9 +372,8 @@ class Chain:
                                  and L["H"] * L["W"] <= 64 and batch * L["H"] * L["W"] >= 256)
                 if tensor_core == "auto" and L["C"] < self.TC_MIN_CHANNELS:
                     continue
-                if tensor_core == "auto" and not across_images and (padded(L["K"]) < 32 or ho * wo < 9):
-                    continue  # narrow layers (a 16-channel output uses a quarter of the smallest MMA tile)
-                    # and tiny images stay on the CUDA cores
+                if tensor_core == "auto" and not across_images and ho * wo < 9:
+                    continue  # tiny images stay on the CUDA cores
                 d = self._desc(L, padded(L["C"]))
                 if not lib().small_b200_conv2d_f32_tf32x3_supported(C.byref(d)):
                     continue

@@ -53,6 +53,11 @@ CASES = [
     (256, 64, 13, 13, 3, 3, "same", 2),
     (32, 64, 26, 26, 1, 1, "valid", 2),
     (48, 32, 20, 20, 5, 5, (2, 2, 2, 2), 1),
+    # 16 output channels: the narrowest MMA (N = 16), 16-column accumulator buffers
+    (16, 16, 32, 32, 3, 3, "same", 4),
+    (32, 16, 13, 13, 3, 3, "same", 3),
+    (64, 16, 8, 8, 1, 1, "valid", 9),
+    (256, 16, 1, 1, 1, 1, "valid", 500),
 ]
 
 
