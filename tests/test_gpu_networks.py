@@ -58,7 +58,7 @@ def test_ds_cnn_chain_bit_exact(oracle):
 
 
 def test_work_totals():
-    """Algorithmic work per image of the two benchmark networks."""
+    """Algorithmic work per image of the two benchmark networks (hand-computed from the layer shapes)."""
     ly = networks.tiny_yolov2()
     assert abs(sum(networks.algorithmic_work(L, 4)[0] for L in ly if L["op"] == "conv") - 6.971e9) < 1e7
     ld = networks.ds_cnn(calib_images=1)
