@@ -85,8 +85,11 @@ inline void sync_for_host()
                                  "is being captured; a captured inference must only enqueue layer calls");
     if (pending())
     {
-        throw_on(small_b200_device_sync());
+        // waits for the device; a kernel that gave up on a bounded wait left stale output behind,
+        // which must not reach host code silently: it surfaces here as std::runtime_error
         pending() = false;
+        int status = 0;
+        throw_on(small_b200_device_status(&status));
     }
 }
 

@@ -82,8 +82,16 @@ int small_b200_set_device(int device);
 /* Synchronises the device and reports whether any kernel gave up on a bounded device-side
  * wait (tensor-core kernels poll their mbarriers with an iteration limit instead of
  * spinning forever).  *status = 0 when all is well; otherwise SMALL_B200_DEVICE_TIMEOUT is
- * returned.  No counterpart in the reference (a CPU loop nest has nothing to wait for). */
+ * returned and the word is cleared (a failure is reported once; while it is set, every other
+ * bounded wait gives up early too, so that a whole launch drains quickly).  No counterpart in
+ * the reference (a CPU loop nest has nothing to wait for). */
 int small_b200_device_status(int *status);
+/* Self-test of that mechanism: launches one warp that holds tensor memory and waits, with the
+ * same bounded wait the tensor-core kernels use and a limit of `polls` polls (1..4096), on a
+ * barrier nobody arrives on.  The wait gives up by construction, the kernel frees its tensor
+ * memory and returns; the next small_b200_device_status() reports SMALL_B200_DEVICE_TIMEOUT
+ * (code 99) and clears it.  No counterpart in the reference. */
+int small_b200_selftest_bounded_wait(uint32_t polls, void *stream);
 /* Number of kernels this library has launched in this process since it was loaded. */
 uint64_t small_b200_launch_count(void);
 

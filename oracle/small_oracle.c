@@ -63,6 +63,11 @@ static inline float apply_act(float v, int act, float slope)
 }
 
 /* ---------------------------------------------------------------- float conv */
+/* Every output element is an independent sum, so the outputs of one channel block (cob
+ * accumulators side by side, which the compiler may keep in vector registers) and the rows of
+ * the image (OpenMP) are computed in parallel; the order of additions INSIDE each sum is the
+ * sequential one of the loop nest, so the result does not depend on the thread count. */
+#define SO_MAX_COB 64
 void so_conv2d_f32(const so_shape *s, const float *in, const float *filt,
                    const float *bias, int act, float slope, int accumulate, float *out)
 {
@@ -70,14 +75,24 @@ void so_conv2d_f32(const so_shape *s, const float *in, const float *filt,
     const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
     const int32_t Wo = so_out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
     const int32_t ncb = s->C / cib;
-    for (int32_t k = 0; k < s->K; ++k)
+    const int32_t kbs = (s->K + cob - 1) / cob;
+    if (cob > SO_MAX_COB)
+        return;
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int32_t kb = 0; kb < kbs; ++kb)
         for (int32_t oh = 0; oh < Ho; ++oh)
+        {
+            const int32_t kv = (s->K - kb * cob) < cob ? (s->K - kb * cob) : cob;
             for (int32_t ow = 0; ow < Wo; ++ow)
             {
-                const size_t oi = act_idx(Ho, Wo, cob, k, oh, ow);
-                float acc = accumulate ? out[oi] : 0.f;
-                if (bias)
-                    acc = acc + bias[k];
+                float acc[SO_MAX_COB];
+                float *o = out + act_idx(Ho, Wo, cob, kb * cob, oh, ow);
+                for (int32_t j = 0; j < kv; ++j)
+                {
+                    acc[j] = accumulate ? o[j] : 0.f;
+                    if (bias)
+                        acc[j] = acc[j] + bias[kb * cob + j];
+                }
                 for (int32_t b = 0; b < ncb; ++b)
                     for (int32_t kh = 0; kh < s->Fh; ++kh)
                     {
@@ -91,13 +106,20 @@ void so_conv2d_f32(const so_shape *s, const float *in, const float *filt,
                                 continue;
                             const float *a = in + ((size_t)b * s->H * s->W + (size_t)ih * s->W + iw) * cib;
                             /* packed_weight_index, buffers.hpp:69-78 */
-                            const float *f = filt + ((((size_t)(k / cob) * ncb + b) * s->Fh + kh) * s->Fw + kw) * cib * cob + (k % cob);
+                            const float *f = filt + ((((size_t)kb * ncb + b) * s->Fh + kh) * s->Fw + kw) * cib * cob;
                             for (int32_t c = 0; c < cib; ++c)
-                                acc = acc + a[c] * f[(size_t)c * cob];
+                            {
+                                const float av = a[c];
+                                const float *fc = f + (size_t)c * cob;
+                                for (int32_t j = 0; j < kv; ++j)
+                                    acc[j] = acc[j] + av * fc[j];
+                            }
                         }
                     }
-                out[oi] = apply_act(acc, act, slope);
+                for (int32_t j = 0; j < kv; ++j)
+                    o[j] = apply_act(acc[j], act, slope);
             }
+        }
 }
 
 void so_dwconv2d_f32(const so_shape *s, const float *in, const float *filt,

@@ -70,6 +70,25 @@ inline int num_sms()
     return sms[dev] ? sms[dev] : 148;
 }
 
+// Function attributes (the opt-in to more than 48 KB of dynamic shared memory) belong to a
+// device, not to the process: a call site keeps one of these per kernel family and sets its
+// attributes the first time each device launches it.
+struct PerDeviceOnce
+{
+    std::atomic<bool> done[64];
+    // true when the CURRENT device still needs its set-up; call mark() after it succeeded
+    bool needed(int *dev_out)
+    {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 0 || dev >= 64)
+            dev = 0;
+        *dev_out = dev;
+        return !done[dev].load(std::memory_order_acquire);
+    }
+    void mark(int dev) { done[dev].store(true, std::memory_order_release); }
+};
+
 // Shared argument checks of the windowed layers (the reference throws
 // std::invalid_argument for these, interface_abstract.hpp:100,218).
 int check_window_layer(const small_b200_layer *L, const char *name, bool dense, int max_stride);

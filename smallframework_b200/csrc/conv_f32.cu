@@ -545,11 +545,12 @@ int launch_conv(const ConvArgs &a, size_t smem_bytes, const float *in, const flo
                 const float *bias, float *out, cudaStream_t st)
 {
     auto kern = conv2d_f32_kernel<BN, CH, STRIDE, POOL>;
-    static bool configured = false; // one attribute call per instantiation and process
-    if (!configured)
+    static PerDeviceOnce configured; // one attribute call per instantiation and device
+    int dev;
+    if (configured.needed(&dev))
     {
         SB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        configured = true;
+        configured.mark(dev);
     }
     const long long blocks = (long long)a.N * a.tiles_h * a.tiles_w * a.kblocks;
     kern<<<(unsigned)blocks, 16 * BN / CH, smem_bytes, st>>>(a, in, filt, bias, out);

@@ -204,6 +204,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     __shared__ __align__(8) uint64_t t_full[4], t_empty[4];
     __shared__ __align__(8) uint64_t peer_staged, peer_done; // split reduction: hand-over between the two CTAs
     __shared__ uint32_t tmem_base_s;
+    __shared__ int acc_failed; // an accumulation warp gave up on a wait: all eight leave at the same tile
 
     const uint32_t entries = (uint32_t)a.PR * a.PW;
     const uint32_t x_bytes = entries * 64 * (uint32_t)a.cg;     // one patch [plane][entry][16 floats]
@@ -251,6 +252,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     {
         if (lane == 0)
         {
+            acc_failed = 0;
             for (int i = 0; i < X_SLOTS_MAX; ++i)
             {
                 mbar_init(&x_full[i], 1); mbar_init(&x_ready[i], SPLIT_THREADS); mbar_init(&x_empty[i], PIXM ? 3 : 2);
@@ -748,7 +750,14 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                 srow[e * 80] = acc[piece * 32 + e];
                         }
                     }
+                    // The give-up decision is made for the CTA, not per warp: the named barrier below
+                    // needs all eight warps at every tile, so a warp whose wait ran out says so before
+                    // the barrier and everybody reads it after, and all leave the tile loop together.
+                    if (!ok)
+                        *reinterpret_cast<volatile int *>(&acc_failed) = 1;
                     asm volatile("bar.sync 1, 256;" ::: "memory"); // the eight accumulation warps
+                    if (*reinterpret_cast<volatile int *>(&acc_failed))
+                        ok = false;
                     if (ok)
                     {
                         // staged row s holds pixel (s / 32) * my_cols + piece * 32 + s % 32 of the tile
@@ -997,14 +1006,15 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
         if (int rc = make_tensor_map(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, in, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;
     }
-    static bool configured = false;
-    if (!configured)
+    static PerDeviceOnce configured;
+    int dev;
+    if (configured.needed(&dev))
     {
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        configured = true;
+        configured.mark(dev);
     }
     int *status = device_status_ptr();
     if (!status)

@@ -295,11 +295,12 @@ int launch_pw(const CUtensorMap &map, const PwArgs &a, size_t smem, const uint8_
               uint8_t *out, cudaStream_t st)
 {
     auto kern = pw_u8_tc_kernel<NT>;
-    static bool configured = false;
-    if (!configured)
+    static PerDeviceOnce configured;
+    int dev;
+    if (configured.needed(&dev))
     {
         SB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        configured = true;
+        configured.mark(dev);
     }
     int *status = device_status_ptr();
     if (!status)
@@ -503,11 +504,12 @@ int launch_stem(const StemArgs &a, size_t smem, const uint8_t *in, const uint8_t
                 uint8_t *out, cudaStream_t st)
 {
     auto kern = stem_u8_tc_kernel<NT, SIGNED_IN>;
-    static bool configured = false;
-    if (!configured)
+    static PerDeviceOnce configured;
+    int dev;
+    if (configured.needed(&dev))
     {
         SB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-        configured = true;
+        configured.mark(dev);
     }
     int *status = device_status_ptr();
     if (!status)
@@ -621,9 +623,53 @@ extern "C" int small_b200_device_status(int *status)
     int *p = sb::device_status_ptr();
     if (p)
         SB_CUDA(cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost));
-    *status = v;
+    if (status)
+        *status = v;
     if (v != 0)
+    {
+        // reported once: the word is cleared so that later kernels wait with their full limits again
+        SB_CUDA(cudaMemset(p, 0, sizeof(int)));
         return sb::fail(SMALL_B200_DEVICE_TIMEOUT,
                         "a bounded device-side wait ran out (code " + std::to_string(v) + ")");
+    }
     return SMALL_B200_OK;
+}
+
+namespace
+{
+// One warp: a barrier that nobody ever arrives on, a 32-column tensor-memory allocation as the
+// tensor-core kernels hold one, and the same bounded wait they use.  The wait runs out after
+// `polls` polls by construction, the status word gets `code`, tensor memory is released and the
+// kernel returns.
+__global__ void __launch_bounds__(32) bounded_wait_selftest_kernel(uint32_t polls, int code, int *status)
+{
+    __shared__ __align__(8) uint64_t never;
+    __shared__ uint32_t tmem_base_s;
+    if (threadIdx.x == 0)
+    {
+        sb::mbar_init(&never, 1);
+        sb::fence_barrier_init();
+    }
+    __syncwarp();
+    sb::tmem_alloc(&tmem_base_s, 32);
+    sb::tmem_relinquish();
+    sb::tc_fence_before_sync();
+    __syncwarp();
+    sb::tc_fence_after_sync();
+    if (threadIdx.x == 0)
+        sb::mbar_wait(&never, 0, status, code, polls);
+    __syncwarp();
+    sb::tmem_dealloc(tmem_base_s, 32);
+}
+} // namespace
+
+extern "C" int small_b200_selftest_bounded_wait(uint32_t polls, void *stream)
+{
+    if (polls == 0 || polls > 4096)
+        return sb::fail(SMALL_B200_INVALID_ARGUMENT, "selftest_bounded_wait: polls must be in 1..4096");
+    int *status = sb::device_status_ptr();
+    if (!status)
+        return sb::fail(SMALL_B200_CUDA_ERROR, "device status word not available");
+    bounded_wait_selftest_kernel<<<1, 32, 0, sb::as_stream(stream)>>>(polls, 99, status);
+    return sb::launched("bounded_wait_selftest_kernel");
 }

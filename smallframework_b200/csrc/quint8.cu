@@ -679,12 +679,13 @@ int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uin
         const size_t smem = (size_t)(a.K / CB) * a.Fh * quads * CB * 4 + (size_t)C1_IMGS * prow * pitch;
         if (smem <= 160 * 1024)
         {
-            static bool configured = false;
-            if (!configured)
+            static PerDeviceOnce configured;
+            int dev;
+            if (configured.needed(&dev))
             {
                 SB_CUDA(cudaFuncSetAttribute(conv2d_u8_c1_dp4a_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
                 SB_CUDA(cudaFuncSetAttribute(conv2d_u8_c1_dp4a_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-                configured = true;
+                configured.mark(dev);
             }
             const unsigned blocks = (unsigned)((a.N + C1_IMGS - 1) / C1_IMGS);
             if (a.zero_in == 0)

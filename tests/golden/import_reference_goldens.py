@@ -6,7 +6,7 @@ big-endian uint32 element count, then raw little-endian float32, test/test_utils
 :187-215).  Everything up to 150 KB is taken, plus a few 96-channel 30x30 cases that give
 the convolution kernels a non-trivial size.  Run once where the reference tree is mounted:
 
-    python tests/golden/import_reference_goldens.py [/path/to/reference]
+    python tests/golden/import_reference_goldens.py /path/to/reference
 """
 import os
 import shutil
@@ -21,7 +21,9 @@ EXTRA = [
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    ref = sys.argv[1]
     src = os.path.join(ref, "test", "regression_data")
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference")
     os.makedirs(dst, exist_ok=True)

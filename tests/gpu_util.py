@@ -36,43 +36,96 @@ def oracle_conv_batch(oracle, sh, xs, wp, bias=None, act=0, slope=0.0, seed=None
     return np.stack(outs)
 
 
-def oracle_chain(oracle, layers, x_packed, dtype="f32"):
-    """One image through a layer list (smallframework_b200.networks format) on the oracle,
-    blocking 16, padded output channels like the executor.  Layers that name their buffers
-    (src / dst, residual stages) read and write a dictionary of tensors; `accumulate` seeds the
-    convolution with the destination's content (PartialConv2D)."""
+def oracle_layer(oracle, L, first, cur, dtype="f32", seed=None):
+    """One layer of a layer list (smallframework_b200.networks format) on the oracle for ONE
+    packed image `cur`, blocking 16, output channels padded like the executor pads them.
+    `seed`: the destination's previous content for a layer with `accumulate` (PartialConv2D)."""
     from smallframework_b200.networks import padded, padded_params
+    cin = L["C"] if first else padded(L["C"])
+    kp = padded(L["K"])
+    sh = shape(cin, kp, L["H"], L["W"], L["Fh"], L["Fw"], L["stride"], L["pads"], CB)
+    if L["op"] in ("conv", "dwconv"):
+        dw = L["op"] == "dwconv"
+        w, b = padded_params(L, first, dtype)
+        if dtype == "f32":
+            return oracle.conv2d_f32(sh, cur, w, bias=b, act=L.get("act", 0), slope=L.get("slope", 0.0),
+                                     out=seed, depthwise=dw)
+        q = L["q"]
+        return oracle.conv2d_u8(sh, Quant(q["zero_in"], q["zero_filt"], q["lshift"], q["rshift"],
+                                          q["multiplier"], 0), cur, w, bias=b, depthwise=dw)
+    if L["op"] == "softmax":
+        return oracle.softmax_f32(cin, L["H"], L["W"], CB, cur)
+    if L["op"] == "alias":
+        return cur
+    avg = L["op"] == "avgpool"
+    if dtype == "f32":
+        return oracle.pool2d_f32(sh, cur, average=avg)
+    q = L["q"] if "q" in L else dict(zero_in=0, zero_filt=0, lshift=0, rshift=0, multiplier=1 << 30)
+    return oracle.pool2d_u8(sh, Quant(q["zero_in"], 0, q["lshift"], q["rshift"], q["multiplier"], 0),
+                            cur, average=avg)
+
+
+def oracle_chain(oracle, layers, x_packed, dtype="f32"):
+    """One image through a layer list on the oracle.  Layers that name their buffers (src / dst,
+    residual stages) read and write a dictionary of tensors; `accumulate` seeds the convolution
+    with the destination's content (PartialConv2D)."""
     cur = x_packed
     named = {"in": x_packed}
     for i, L in enumerate(layers):
         if "src" in L:
             cur = named[L["src"]]
-        cin = L["C"] if i == 0 else padded(L["C"])
-        kp = padded(L["K"])
-        sh = shape(cin, kp, L["H"], L["W"], L["Fh"], L["Fw"], L["stride"], L["pads"], CB)
-        if L["op"] in ("conv", "dwconv"):
-            dw = L["op"] == "dwconv"
-            w, b = padded_params(L, i == 0, dtype)
-            if dtype == "f32":
-                seed = named[L["dst"]].copy() if L.get("accumulate") else None
-                cur = oracle.conv2d_f32(sh, cur, w, bias=b, act=L.get("act", 0), slope=L.get("slope", 0.0),
-                                        out=seed, depthwise=dw)
-            else:
-                q = L["q"]
-                cur = oracle.conv2d_u8(sh, Quant(q["zero_in"], q["zero_filt"], q["lshift"], q["rshift"],
-                                                 q["multiplier"], 0), cur, w, bias=b, depthwise=dw)
-        elif L["op"] == "softmax":
-            cur = oracle.softmax_f32(cin, L["H"], L["W"], CB, cur)
-        elif L["op"] == "alias":
-            pass
-        else:
-            avg = L["op"] == "avgpool"
-            if dtype == "f32":
-                cur = oracle.pool2d_f32(sh, cur, average=avg)
-            else:
-                q = L["q"] if "q" in L else dict(zero_in=0, zero_filt=0, lshift=0, rshift=0, multiplier=1 << 30)
-                cur = oracle.pool2d_u8(sh, Quant(q["zero_in"], 0, q["lshift"], q["rshift"], q["multiplier"], 0),
-                                       cur, average=avg)
+        seed = named[L["dst"]].copy() if (L.get("accumulate") and dtype == "f32") else None
+        cur = oracle_layer(oracle, L, i == 0, cur, dtype, seed)
         if "dst" in L:
             named[L["dst"]] = cur
     return cur
+
+
+def run_layers_checked(oracle, chain, layers, images, dtype="f32", tol=1e-5):
+    """Runs `chain` eagerly, one layer call at a time, and after each call compares the images
+    in `images` with the oracle applied to THE SAME INPUT the device kernel read (so a layer's
+    error is its own, not the chain's).  A max pool that its producer absorbs is checked together
+    with that producer.  Returns per-layer (name, worst error) -- errors are max|x-ref|/max|ref| for
+    fp32 and the count of differing bytes for uint8."""
+    from smallframework_b200 import _lib
+    from smallframework_b200.networks import _out_hw, padded
+    st = chain.stream.cuda_stream
+    plan = chain.io_plan()
+    report = []
+    N = chain.batch
+    for i, io in enumerate(plan):
+        if io is None:
+            continue
+        L = layers[i]
+        if L["op"] == "alias":
+            continue
+        src, dst = io
+        chain.stream.synchronize()
+        cin = L["C"] if i == 0 else padded(L["C"])
+        n_in = cin * L["H"] * L["W"]
+        last = L
+        fused_pool = (i + 1) in chain.fused_into
+        if fused_pool:
+            last = layers[i + 1]
+        ho, wo = _out_hw(last)
+        n_out = padded(last["K"]) * ho * wo
+        xin = {n: src[n * n_in:(n + 1) * n_in].cpu().numpy() for n in images}
+        before = {n: dst[n * n_out:(n + 1) * n_out].cpu().numpy() for n in images} if L.get("accumulate") else {}
+        chain.enqueue_layer(i, src, dst, st)
+        chain.stream.synchronize()
+        assert _lib.device_status() == 0, L["name"]
+        worst = 0.0
+        for n in images:
+            want = oracle_layer(oracle, L, i == 0, xin[n], dtype, before.get(n))
+            if fused_pool:
+                want = oracle_layer(oracle, layers[i + 1], False, want, dtype)
+            got = dst[n * n_out:(n + 1) * n_out].cpu().numpy()
+            if dtype == "f32":
+                err = rel_max_err(got, want)
+                assert err <= tol, (L["name"], n, err)
+            else:
+                err = float(np.count_nonzero(got != want))
+                assert err == 0, (L["name"], n, err)
+            worst = max(worst, err)
+        report.append((L["name"] + ("+pool" if fused_pool else ""), worst))
+    return report

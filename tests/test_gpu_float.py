@@ -1,5 +1,5 @@
 """fp32 parity of the CUDA path (through the C ABI) against the oracle, the reference's
-golden vectors and, at BASELINE sizes, size-independent properties.
+golden vectors and, at benchmark sizes, size-independent properties.
 
 Gate for contractions: max|x - ref| / max|ref| <= 1e-5 against the oracle run with the same
 blocking (16), i.e. the same order of additions; the only difference left is fused
@@ -269,16 +269,18 @@ def test_errors_match_the_reference():
         S.ReLUActivation(8, 2, 2, I, O)
 
 
-def test_full_size_tiny_yolo_layer_linearity():
-    """At a BASELINE-sized layer (128 -> 256 channels at 26x26, batch 8) the oracle would take
-    minutes, so check properties: conv(x1 + x2) = conv(x1) + conv(x2) within fp32 rounding,
-    and every image of a batch equals the same image run alone."""
+def test_full_size_tiny_yolo_layer_linearity(oracle):
+    """A Tiny-YOLOv2 sized layer (128 -> 256 channels at 26x26, batch 8) on the CUDA-core kernel:
+    against the oracle for two of the images, plus two properties over the whole batch:
+    conv(x1 + x2) = conv(x1) + conv(x2) within fp32 rounding, and every image of a batch equals
+    the same image run alone."""
     rng = np.random.default_rng(9)
     C, K, H, W, N = 128, 256, 26, 26, 8
     pads = same_pads(H, W, 3, 3, 1)
     x1 = rng.uniform(0, 1, (N, C, H, W)).astype(np.float32)
     x2 = rng.uniform(0, 1, (N, C, H, W)).astype(np.float32)
-    F = fbuf(P.pack_conv_filter(rng.normal(0, np.sqrt(2 / (C * 9)), (K, C, 3, 3)).astype(np.float32)))
+    wp = P.pack_conv_filter(rng.normal(0, np.sqrt(2 / (C * 9)), (K, C, 3, 3)).astype(np.float32))
+    F = fbuf(wp)
     def run(x, n):
         O = S.FloatBuffer(n * K * H * W)
         S.Conv2D(3, 3, 1, *pads, K, C, H, W, fbuf(P.pack_activation(x)), F, O, batch=n)
@@ -286,6 +288,10 @@ def test_full_size_tiny_yolo_layer_linearity():
     y1, y2, y12 = run(x1, N), run(x2, N), run(x1 + x2, N)
     assert rel_max_err(y12, y1 + y2) <= 1e-5
     assert np.array_equal(run(x1[5:6], 1)[0], y1[5])
+    sh = shape(C, K, H, W, 3, 3, 1, pads, CB)
+    xp = P.pack_activation(x1)
+    for n in (0, 7):
+        assert rel_max_err(y1[n], oracle.conv2d_f32(sh, xp[n], wp)) <= TOL
 
 
 FUSED_POOL_CASES = [

@@ -1,6 +1,6 @@
-"""Whole layer chains (smallframework_b200.networks.Chain, one CUDA graph) against the oracle
-run layer by layer: Tiny-YOLOv2 at a reduced image size (the oracle needs seconds per image at
-416x416) on both fp32 paths, DS-CNN uint8 at full size, bit-exact."""
+"""Whole layer chains (smallframework_b200.networks.Chain, one CUDA graph) against the oracle's
+chain: fast cases at reduced image sizes on both fp32 paths, DS-CNN uint8, bit-exact.  The same
+networks at the sizes the benchmark runs are in test_gpu_full_size.py."""
 import numpy as np
 import pytest
 import torch
@@ -78,7 +78,7 @@ def _run_chain(layers, x, dtype, **kw):
 
 @pytest.mark.parametrize("tensor_core", [False, "auto"])
 def test_resnet8_chain(oracle, tensor_core):
-    """BASELINE configuration 1: residual stages as PartialConv2D onto the shortcut's buffer
+    """ResNet-8: residual stages as PartialConv2D onto the shortcut's buffer
     (include/small/models/Resnet8Tiny.hpp:284-288), stride-2 convolutions, global average pool,
     dense head, softmax."""
     layers = networks.resnet8(seed=0)
@@ -94,7 +94,7 @@ def test_resnet8_chain(oracle, tensor_core):
 
 
 def test_mobilenet_v1_025_chain_fp32(oracle):
-    """BASELINE configuration 3, fp32: 13 depthwise-separable blocks with stride-2 depthwise layers."""
+    """MobileNet-v1 x0.25 fp32: 13 depthwise-separable blocks with stride-2 depthwise layers."""
     layers = networks.mobilenet_v1_025(seed=2, dtype="f32")
     N = 2
     rng = np.random.default_rng(11)
@@ -106,7 +106,7 @@ def test_mobilenet_v1_025_chain_fp32(oracle):
 
 
 def test_mobilenet_v1_025_chain_uint8_bit_exact(oracle):
-    """BASELINE configuration 3, uint8: every layer requantised, bit-exact through 28 layers."""
+    """MobileNet-v1 x0.25 uint8: every layer requantised, bit-exact through 28 layers."""
     layers = networks.mobilenet_v1_025(seed=2, dtype="u8")
     N = 2
     rng = np.random.default_rng(12)
@@ -120,9 +120,9 @@ def test_mobilenet_v1_025_chain_uint8_bit_exact(oracle):
 
 @pytest.mark.parametrize("idx", range(13))
 def test_yolov3_tiny_layer(oracle, idx):
-    """BASELINE configuration 4: the 13 convolution shapes of YOLOv3-tiny, each alone, at a
-    reduced image size (channel counts, kernel sizes and the 255 -> 256 padding are the real ones;
-    the full 416x416 layers are covered by the linearity test of the full-size Tiny-YOLOv2 layers)."""
+    """The 13 convolution shapes of YOLOv3-tiny, each alone, at a reduced image size (channel
+    counts, kernel sizes and the 255 -> 256 padding are the real ones); the 416x416 layers are in
+    test_gpu_full_size.py."""
     layers = networks.yolov3_tiny_convs(seed=3, size=64)[idx]
     L = layers[0]
     N = 2

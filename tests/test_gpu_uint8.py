@@ -127,7 +127,7 @@ def test_default_constructed_buffers_match_the_reference_defaults(oracle):
 
 
 def test_full_batch_pointwise_matches_single_images(oracle):
-    """DS-CNN pointwise layer at the BASELINE batch (4096): spot-check images against the
+    """DS-CNN pointwise layer at the benchmark's batch (4096): spot-check images against the
     oracle and check that the batched result equals per-image calls."""
     rng = np.random.default_rng(12)
     C = K = 64; H, W, N = 25, 5, 4096
