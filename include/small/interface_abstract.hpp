@@ -51,15 +51,17 @@ inline void quantise(small_b200_layer &L, BufferT const &in, BufferT const *filt
     }
 }
 
-// Off by default: the reference's own tests accept |x - golden| <= 1e-5 + 5e-3 |golden| element by
-// element (test/include/test_utils.hpp), which on outputs of magnitude 10..30 only the sequential
-// fp32 sum of the CUDA-core kernel meets; the 3xTF32 kernel is within 1e-5 of the output RANGE.
-// SMALL_B200_TENSOR_CORE=1 in the environment, or small::b200::tensor_core() = true, turns it on.
+// On by default: fp32 convolutions the library prefers on the tensor cores
+// (small_b200_conv2d_f32_tf32x3_preferred) run there.  Against an fp64 recomputation the 3xTF32
+// kernel is closer to the exact result than the reference's sequential fp32 sum, and the
+// reference's own tests (|x - golden| <= 1e-5 + 5e-3 |golden| element by element,
+// test/include/test_utils.hpp) pass on it.  SMALL_B200_TENSOR_CORE=0 in the environment, or
+// small::b200::tensor_core() = false, keeps every convolution on the CUDA cores.
 inline bool &tensor_core()
 {
     static bool on = [] {
         const char *e = std::getenv("SMALL_B200_TENSOR_CORE");
-        return e && e[0] == '1';
+        return !(e && e[0] == '0');
     }();
     return on;
 }
@@ -84,12 +86,7 @@ inline void conv(bool partial, int act, int kh, int kw, int stride, int t, int b
         // Wide stride-1 layers run on the tensor cores (tcgen05 kind::tf32, 3xTF32 split).  The
         // kernel wants the filter re-laid; that copy is made once and kept with the filter buffer
         // until the host touches the buffer again.
-        const int Ho = small::output_dim(H + t + b, stride, kh), Wo = small::output_dim(W + l + r, stride, kw);
-        // (small images only for 1x1 layers of a batch, whose tiles run across images)
-        const bool across_images = kh == 1 && kw == 1 && stride == 1 && !t && !b && !l && !r && H * W <= 64 &&
-                                   (long long)H * W * batch() >= 256; // dense heads of a batch included
-        const bool wide_enough = across_images || Ho * Wo >= 32;
-        if (tensor_core_enabled() && C >= 16 && wide_enough && small_b200_conv2d_f32_tf32x3_supported(&L))
+        if (tensor_core_enabled() && small_b200_conv2d_f32_tf32x3_preferred(&L))
         {
             const uint64_t key = ((uint64_t)K << 40) ^ ((uint64_t)C << 20) ^ ((uint64_t)kh << 8) ^ (uint64_t)kw;
             float *prepared = filt.companion(key);

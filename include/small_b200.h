@@ -145,6 +145,12 @@ int small_b200_conv2d_maxpool_f32(const small_b200_layer *conv, const small_b200
  * ..._supported() says whether a shape is covered (1) or not (0).  The reference has no
  * counterpart of the preparation call (its filters are used as packed). */
 int small_b200_conv2d_f32_tf32x3_supported(const small_b200_layer *L);
+/* The library's own choice between the two fp32 convolutions for a shape and batch: 1 when the
+ * tensor-core kernel covers it and is the faster one (at least 16 input channels, and either an
+ * image of at least 9 output pixels or a 1x1 layer whose tiles run across the images of a batch
+ * of at least 256 pixels in all), else 0.  The C++ platform headers and the Python executor both
+ * ask here, so they pick the same kernel for the same call. */
+int small_b200_conv2d_f32_tf32x3_preferred(const small_b200_layer *L);
 int small_b200_filter_prepare_tf32x3(const small_b200_layer *L, const float *filt, float *prepared, void *stream);
 int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, const float *filt_prepared,
                                  const float *bias, float *out, void *stream);

@@ -406,6 +406,11 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                             if (PIXM)
                             {
                                 const uint32_t d0 = tmem + (uint32_t)((g & tb_mask) * mtiles * a.K);
+                                // The small cross terms of the whole group first, the hi*hi terms last: the
+                                // tensor core adds into its accumulator with truncation, an error of one ulp OF
+                                // THE ACCUMULATOR per MMA, so only the MMAs issued while it holds full-size sums
+                                // (two per tap instead of six) contribute a full-size error.
+                                uint64_t wh2 = wh, xh2 = xh;
                                 for (int tp = 0; tp < a.group; ++tp, wh += w_tap, xh += tap_step)
                                 {
                                     const uint64_t wl = wh + w_lo_off;
@@ -415,23 +420,33 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                         const uint32_t d = d0 + (uint32_t)(mt * a.K);
                                         tc_mma_tf32(d, xa, wl, idesc, tp == 0 ? 0u : 1u);
                                         tc_mma_tf32(d, xl, wh, idesc, 1u);
-                                        tc_mma_tf32(d, xa, wh, idesc, 1u);
                                         tc_mma_tf32(d, xa + x_half, wl + w_half, idesc, 1u);
                                         tc_mma_tf32(d, xl + x_half, wh + w_half, idesc, 1u);
-                                        tc_mma_tf32(d, xa + x_half, wh + w_half, idesc, 1u);
                                     }
                                 }
+                                for (int tp = 0; tp < a.group; ++tp, wh2 += w_tap, xh2 += tap_step)
+                                    for (int mt = 0; mt < mtiles; ++mt)
+                                    {
+                                        const uint64_t xa = xh2 + (uint64_t)mt * 512;
+                                        const uint32_t d = d0 + (uint32_t)(mt * a.K);
+                                        tc_mma_tf32(d, xa, wh2, idesc, 1u);
+                                        tc_mma_tf32(d, xa + x_half, wh2 + w_half, idesc, 1u);
+                                    }
                             }
                             const uint32_t d = tmem + (uint32_t)((g & tb_mask) * a.NPX);
+                            uint64_t wh2 = wh, xh2 = xh; // cross terms first, hi*hi last (see the pixel-major loop)
                             for (int tp = 0; !PIXM && tp < a.group; ++tp, wh += w_tap, xh += tap_step)
                             {
                                 const uint64_t xl = xh + x_lo_off, wl = wh + w_lo_off;
                                 tc_mma_tf32(d, wl, xh, idesc, tp == 0 ? 0u : 1u);
                                 tc_mma_tf32(d, wh, xl, idesc, 1u);
-                                tc_mma_tf32(d, wh, xh, idesc, 1u);
                                 tc_mma_tf32(d, wl + w_half, xh + x_half, idesc, 1u);
                                 tc_mma_tf32(d, wh + w_half, xl + x_half, idesc, 1u);
-                                tc_mma_tf32(d, wh + w_half, xh + x_half, idesc, 1u);
+                            }
+                            for (int tp = 0; !PIXM && tp < a.group; ++tp, wh2 += w_tap, xh2 += tap_step)
+                            {
+                                tc_mma_tf32(d, wh2, xh2, idesc, 1u);
+                                tc_mma_tf32(d, wh2 + w_half, xh2 + x_half, idesc, 1u);
                             }
                             // the stage is free for the producer and the group's partial sums are
                             // complete for the accumulation warps: one commit serves both while the
@@ -969,6 +984,18 @@ int small_b200_conv2d_f32_tf32x3_supported(const small_b200_layer *L)
 {
     TcArgs a;
     return plan(L, a) ? 1 : 0;
+}
+
+int small_b200_conv2d_f32_tf32x3_preferred(const small_b200_layer *L)
+{
+    TcArgs a;
+    if (!L || L->C < 16 || !plan(L, a))
+        return 0;
+    // tiles that run across the images of a batch (1x1 layers on small images, dense heads) are full
+    // whatever the image size; otherwise an image must give a tile something to do
+    if (a.rows_view)
+        return (long long)L->N * L->H * L->W >= 256 ? 1 : 0;
+    return (long long)a.Ho * a.Wo >= 9 ? 1 : 0;
 }
 
 int small_b200_filter_prepare_tf32x3(const small_b200_layer *L, const float *filt, float *prepared, void *stream)

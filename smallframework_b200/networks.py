@@ -318,11 +318,9 @@ class Chain:
     into a CUDA graph; launch() replays it.  `x` (input) and `y` (output) are the device
     tensors at the two ends."""
 
-    TC_MIN_CHANNELS = 16
-
     def __init__(self, layers, batch, dtype="f32", device="cuda", tensor_core="auto", fuse_pool=True):
-        """tensor_core: "auto" = fp32 convolutions the 3xTF32 kernel covers and that have at
-        least `TC_MIN_CHANNELS` input channels run on the tensor cores; True = every covered
+        """tensor_core: "auto" = fp32 convolutions run on the tensor cores where the library
+        prefers them there (small_b200_conv2d_f32_tf32x3_preferred); True = every covered
         layer; False = CUDA cores only.  fuse_pool: a CUDA-core convolution followed by a 2x2
         stride-2 max pool runs as one kernel where the library covers the pair (the reference's
         Conv2D_Bias_ReLU_Maxpool2D path); the pool's entry in `fused_into` then names its
@@ -365,16 +363,10 @@ class Chain:
             for i, L in enumerate(layers):
                 if L["op"] != "conv" or (i == 0 and L["C"] % CB != 0):
                     continue
-                ho, wo = _out_hw(L)
-                # 1x1 layers of a batch on small images (dense heads included): the tensor-core kernel
-                # takes the batch as the rows of one image, so its tiles are full whatever the image size
-                across_images = (L["Fh"] == 1 and L["Fw"] == 1 and L["stride"] == 1 and not any(L["pads"])
-                                 and L["H"] * L["W"] <= 64 and batch * L["H"] * L["W"] >= 256)
-                if tensor_core == "auto" and L["C"] < self.TC_MIN_CHANNELS:
-                    continue
-                if tensor_core == "auto" and not across_images and ho * wo < 9:
-                    continue  # tiny images stay on the CUDA cores
                 d = self._desc(L, padded(L["C"]))
+                # "auto": the library's own choice (the C++ platform headers ask the same function)
+                if tensor_core == "auto" and not lib().small_b200_conv2d_f32_tf32x3_preferred(C.byref(d)):
+                    continue
                 if not lib().small_b200_conv2d_f32_tf32x3_supported(C.byref(d)):
                     continue
                 wt = self.params[i][0]

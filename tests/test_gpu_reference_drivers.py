@@ -42,23 +42,25 @@ def test_reference_driver(name):
     assert r.returncode == 0, f"{name} failed:\n{tail}"
 
 
-# Drivers that compare the functional chain with the Model / DAGModel classes, or that apply a
-# tolerance relative to the result: they also pass with the tensor-core fp32 convolution switched on
-# (the layer functions then re-lay each filter once and keep that copy with the filter buffer).
-TENSOR_CORE_DRIVERS = ["test_tinyyolov2", "test_resnet8", "test_autoencoder", "test_partial_conv2d", "test_mobilenet",
-                       "test_dscnn", "test_dscnn_square"]
+# The platform runs fp32 convolutions on the tensor cores by default; the drivers that contain fp32
+# convolutions are run once more with every convolution kept on the CUDA cores.
+CONV_DRIVERS = ["test_conv2d", "test_conv2d_rect", "test_partial_conv2d", "test_tinyyolov2", "test_resnet8",
+                "test_autoencoder", "test_mobilenet", "test_dscnn", "test_dscnn_square", "test_conv1d"]
 
 
-@pytest.mark.parametrize("name", TENSOR_CORE_DRIVERS)
-def test_reference_driver_on_tensor_cores(name):
+@pytest.mark.parametrize("name", CONV_DRIVERS)
+def test_reference_driver_on_cuda_cores_only(name):
     exe = os.path.join(BUILD, "bin", name)
     if not os.path.exists(exe):
         pytest.skip(f"{exe} not built (run make -C tests/reference_drivers where the reference is mounted)")
-    env = dict(os.environ, OMP_NUM_THREADS="4", SMALL_B200_TENSOR_CORE="1")
-    r = subprocess.run([exe], cwd=os.path.join(BUILD, "run"), env=env, stdout=subprocess.PIPE,
+    cmd = [exe]
+    if name in SKIP:
+        cmd += ["--skip"] + SKIP[name]
+    env = dict(os.environ, OMP_NUM_THREADS="4", SMALL_B200_TENSOR_CORE="0")
+    r = subprocess.run(cmd, cwd=os.path.join(BUILD, "run"), env=env, stdout=subprocess.PIPE,
                        stderr=subprocess.STDOUT, text=True, timeout=900)
     tail = "\n".join(r.stdout.splitlines()[-25:])
-    assert r.returncode == 0, f"{name} failed with SMALL_B200_TENSOR_CORE=1:\n{tail}"
+    assert r.returncode == 0, f"{name} failed with SMALL_B200_TENSOR_CORE=0:\n{tail}"
 
 
 @pytest.mark.parametrize("tensor_core", ["0", "1"])
