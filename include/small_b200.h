@@ -217,6 +217,31 @@ int small_b200_concat(int32_t N, size_t bytes0, const void *in0, size_t bytes1, 
  * needs no 4x over-allocation (the reference's does, q_abstract_layer.hpp:1144). */
 int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
                          const int32_t *bias, uint8_t *out, void *stream);
+/* Two uint8 layers as ONE kernel, the intermediate activation kept in shared memory: the
+ * reference's Conv2D_ReLU_DepthwiseConv2D_ReLU fusion (fused_interface_abstract.hpp:1840, float
+ * there) for quint8 buffers, where the clamp of the requantisation is the ReLU.  `conv` is a 1x1
+ * convolution (C % 32 == 0, C <= 128) or a one-channel first layer (Fw <= 4, Fh <= 16), K in
+ * {32, 64}, on an image whose OUTPUT has at most 128 pixels; `dw` is the 3x3 stride-1 depthwise
+ * convolution with pads 1,1,1,1 of that output.  Both run on the tensor cores (a depthwise tap
+ * as a GEMM with a diagonal weight block).  Filter zero points must be -128, the intermediate's
+ * zero point (dw->zero_in) 0 or -128.  Each layer carries its own requantisation in its
+ * descriptor; biases may be NULL.  ..._supported() says whether a pair is covered; other pairs
+ * run as two calls.  Bit-identical to the two calls. */
+int small_b200_conv2d_dwconv2d_u8_supported(const small_b200_layer *conv, const small_b200_layer *dw);
+int small_b200_conv2d_dwconv2d_u8(const small_b200_layer *conv, const small_b200_layer *dw, const uint8_t *in,
+                                  const uint8_t *conv_filt, const int32_t *conv_bias, const uint8_t *dw_filt,
+                                  const int32_t *dw_bias, uint8_t *out, void *stream);
+/* The tail of the keyword-spotting network (include/small/models/DSCNNTiny.hpp) as one kernel:
+ * `conv` as above, the global average pool `pool` of its output (window = the whole image) and
+ * the dense layer `dense` (a 1x1 convolution on the pooled 1x1 image, K <= 128) on the pooled
+ * vector.  `out` holds [N][dense->K] bytes.  Bit-identical to the three calls.  The reference has
+ * no such entry (it has no quint8 average pool at all). */
+int small_b200_conv2d_avgpool_dense_u8_supported(const small_b200_layer *conv, const small_b200_layer *pool,
+                                                 const small_b200_layer *dense);
+int small_b200_conv2d_avgpool_dense_u8(const small_b200_layer *conv, const small_b200_layer *pool,
+                                       const small_b200_layer *dense, const uint8_t *in, const uint8_t *conv_filt,
+                                       const int32_t *conv_bias, const uint8_t *dense_filt, const int32_t *dense_bias,
+                                       uint8_t *out, void *stream);
 /* small::DepthwiseConv2D<QUInt8Buffer> (:1059). */
 int small_b200_dwconv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
                            const int32_t *bias, uint8_t *out, void *stream);

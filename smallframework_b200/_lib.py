@@ -82,6 +82,10 @@ SIGNATURES = {
     "small_b200_concat": [_I32, _SZ, _VP, _SZ, _VP, _VP, _VP],
     "small_b200_conv2d_u8": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_dwconv2d_u8": [_LP, _VP, _VP, _VP, _VP, _VP],
+    "small_b200_conv2d_dwconv2d_u8_supported": [_LP, _LP],
+    "small_b200_conv2d_dwconv2d_u8": [_LP, _LP, _VP, _VP, _VP, _VP, _VP, _VP, _VP],
+    "small_b200_conv2d_avgpool_dense_u8_supported": [_LP, _LP, _LP],
+    "small_b200_conv2d_avgpool_dense_u8": [_LP, _LP, _LP, _VP, _VP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_groupconv2d_u8": [_LP, C.c_int32, _VP, _VP, _VP, _VP, _VP],
     "small_b200_maxpool2d_u8": [_LP, _VP, _VP, _VP],
     "small_b200_avgpool2d_u8": [_LP, _VP, _VP, _VP],

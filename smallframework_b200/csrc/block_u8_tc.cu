@@ -1,0 +1,716 @@
+// block_u8_tc.cu -- two (or three) uint8 layers of a small-image network as ONE kernel, with the
+// intermediate activation kept in shared memory.
+//
+//   stage 1   a dense layer on the tensor core: a 1x1 convolution (activations arrive by one bulk
+//             copy per image) or the one-channel first layer as an im2col GEMM (built in shared
+//             memory, see conv_u8_tc.cu).  Its int32 sums are requantised by four epilogue warps
+//             and written, as uint8, into shared memory -- never to global memory.
+//   stage 2   DW:   a 3x3 stride-1 'same' depthwise convolution of that intermediate, ALSO on the
+//                   tensor core: a depthwise tap is a GEMM whose weight matrix is diagonal, and the
+//                   tensor pipe is idle anyway while the integer ALUs requantise.  Per tap (kh, kw)
+//                   and 32 channels one tcgen05.mma.kind::i8 with M = 128 pixels, N = K = 32 and a
+//                   diagonal 32x32 weight block adds  D[p][ch] += X[p + (kh-1)W + (kw-1)][ch] * w[ch].
+//                   The shift is only a different start address of the A operand ("linear shift"):
+//                   the intermediate is stored three times, once per kernel column kw, each copy
+//                   displaced by (1 - kw) pixels and with the image column that would wrap around
+//                   to the neighbouring row zeroed, plus W + 1 zero pixels above and below; so tap
+//                   (kh, kw) of output pixel p is entry p + kh*W of copy kw for every p, and padded
+//                   taps read zeros, which for operands already shifted by their zero points is
+//                   the reference's "padded taps are skipped".
+//             POOL: the global average pool of the intermediate followed by a dense layer on the
+//                   pooled vector (the tail of the keyword-spotting network), on the CUDA cores:
+//                   per image it is 64 sums and a 64 x 16 matrix-vector product.
+//
+// This is the reference's Conv2D_ReLU_DepthwiseConv2D_ReLU fusion
+// (include/small/fused_interface_abstract.hpp:1840) for quint8 buffers, where the clamp of the
+// requantisation is the ReLU; the reference keeps an intermediate buffer per output tile in
+// cache for the same purpose.
+//
+// Roles (320 threads): warps 0..3 stage-1 epilogue (thread = pixel = tensor-memory lane),
+// warps 4..7 stage-2 epilogue, warp 8 bulk-copy producer (and owner of the tensor-memory
+// allocation), warp 9 MMA issuer.  A CTA walks over images n = blockIdx.x, + gridDim.x, ...;
+// activations, the intermediate and both accumulators are double-buffered, so stage 1 of image
+// j + 1 overlaps the stage-1 epilogue of image j and stage 2 of image j - 1.
+// Requirements (else the layers run as separate kernels): H*W <= 128; filter zero points -128
+// (weights enter the tensor core as signed bytes); zero point of the intermediate 0 or -128.
+#include "tc_common.cuh"
+
+namespace
+{
+using namespace sb;
+
+constexpr int BM = 128;            // pixels per image tile = tensor-memory lanes
+constexpr int BLOCK_THREADS = 320;
+constexpr int EPI_THREADS = 128;
+
+struct Requant
+{
+    int lshift, rshift, mult, k_zero;
+};
+
+struct BlockArgs
+{
+    int N, H, W, HW;   // images; size of the intermediate (= output of stage 1 = output of a DW stage 2)
+    int C;             // stage-1 input channels (1x1 form: multiple of 32; first-layer form: 1)
+    int E;             // entries (pixels) per channel block of one shifted copy of the intermediate
+    // first-layer form only: the raw image and its window
+    int H0, W0, Fh, Fw, stride, pad_t, pad_l, pitch, prow;
+    int zero_in1;      // input zero point of stage 1
+    int mid_signed;    // 1: the intermediate's zero point is -128 (stored as signed bytes)
+    Requant q1, q2;    // stage 1; stage 2 (DW: the depthwise layer, POOL: the average pool)
+    // POOL form: the dense layer
+    int Kd, zero_pool, zero_in_d, zero_filt_d;
+    Requant qd;
+};
+
+// Role-uniform give-up: a thread whose bounded wait ran out raises the role's flag; everybody
+// looks at it after the role's next named barrier and leaves the image loop together, so nobody
+// waits at a barrier for a warp that has left.
+struct RoleFlag
+{
+    int v;
+};
+
+// 32 accumulators of one pixel (32 consecutive channels) -> 32 output bytes.  The common quantiser
+// takes the seeded form (common.cuh); any other one adds the constants and goes the general way.
+__device__ __forceinline__ void requant32(const uint32_t *r, const int *corr, const long long *seed, const Requant &q,
+                                          uint4 *o2)
+{
+    if (requant_is_fast(q.lshift, q.rshift, q.mult))
+    {
+        const int bit = 1 << (q.rshift - 2), sh1 = q.rshift - 1;
+        uint32_t w[8];
+#pragma unroll
+        for (int e4 = 0; e4 < 8; ++e4)
+        {
+            int x[4];
+#pragma unroll
+            for (int e2 = 0; e2 < 2; ++e2)
+            {
+                const longlong2 sd = *reinterpret_cast<const longlong2 *>(seed + 4 * e4 + 2 * e2);
+                x[2 * e2] = requant_seeded_raw((int)r[4 * e4 + 2 * e2], q.mult, sd.x, bit, sh1);
+                x[2 * e2 + 1] = requant_seeded_raw((int)r[4 * e4 + 2 * e2 + 1], q.mult, sd.y, bit, sh1);
+            }
+            w[e4] = pack4_sat(x[0], x[1], x[2], x[3]);
+        }
+        o2[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        o2[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    else
+    {
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2)
+        {
+            int v[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+                v[e] = (int)r[16 * c2 + e] + corr[16 * c2 + e];
+            o2[c2] = requant_pack16(v, q.lshift, q.rshift, q.mult);
+        }
+    }
+}
+
+template <int K, bool STEM, bool POOL, bool SIGNED_IN>
+__global__ void __launch_bounds__(BLOCK_THREADS, 2)
+block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint8_t *__restrict__ filt1,
+                   const int32_t *__restrict__ bias1, const uint8_t *__restrict__ filt2,
+                   const int32_t *__restrict__ bias2, uint8_t *__restrict__ out, int *status)
+{
+    constexpr int KB = K / CB;                       // channel blocks of the intermediate
+    constexpr int KCH = 4;                           // first-layer form: 16-byte chunks of the im2col K = 64
+    constexpr uint32_t TMEM_COLS = POOL ? (2 * K < 32 ? 32 : 2 * K) : 4 * K;
+    constexpr int TAPS = 9;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ __align__(8) uint64_t a_full[2], d1_full[2], d1_free[2], p_full[2], p_free[2], d2_full[2], d2_free[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ __align__(16) int corr1[K], corr2[K];         // per-channel constants added to every accumulator
+    __shared__ __align__(16) long long seed1[K], seed2[K];  // the same as seeds of the wide multiply (common.cuh)
+    __shared__ __align__(16) uint8_t pooled[2][K];
+    __shared__ RoleFlag failed1, failed2;
+
+    const int cbs = a.C / CB;
+    const uint32_t a_stage = STEM ? (uint32_t)(KCH * BM * CB) : (uint32_t)(a.C * BM);
+    const uint32_t b1_bytes = STEM ? (uint32_t)(KCH * K * CB) : (uint32_t)(K * a.C);
+    const uint32_t b2_bytes = POOL ? 0u : (uint32_t)(TAPS * (K / 32) * 1024);
+    const uint32_t copy_bytes = (uint32_t)(KB * a.E * CB);
+    const uint32_t p_stage = (POOL ? 1u : 3u) * copy_bytes;
+    uint8_t *sA = smem;                          // [stage][...]
+    uint8_t *sB1 = sA + 2 * a_stage;
+    uint8_t *sB2 = sB1 + b1_bytes;               // [tap][K/32][2 k-chunks][32 n][16 B], diagonal
+    uint8_t *sP = sB2 + b2_bytes;                // [stage][copy kw][cb][entry][16 B]
+    uint8_t *sI = sP + 2 * p_stage;              // first-layer form: [stage][prow][pitch] padded image
+    const int img_bytes = STEM ? a.prow * a.pitch : 0;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int first = blockIdx.x, step = gridDim.x;
+    const int count = first < a.N ? (a.N - first + step - 1) / step : 0;
+
+    if (warp == 8)
+    {
+        if (lane == 0)
+        {
+            for (int i = 0; i < 2; ++i)
+            {
+                mbar_init(&a_full[i], STEM ? EPI_THREADS : 1);
+                mbar_init(&d1_full[i], 1); mbar_init(&d1_free[i], 4);
+                mbar_init(&p_full[i], EPI_THREADS); mbar_init(&p_free[i], POOL ? 4 : 1);
+                mbar_init(&d2_full[i], 1); mbar_init(&d2_free[i], 4);
+            }
+            failed1.v = 0; failed2.v = 0;
+            fence_barrier_init();
+        }
+        __syncwarp();
+        tmem_alloc(&tmem_base_s, TMEM_COLS);
+        tmem_relinquish();
+    }
+    // ---- operands that stay for the life of the CTA
+    if (STEM)
+    {
+        // filter -> K-major [chunk][n][16 B]: byte k = kh*4 + kw of output channel n, as signed bytes
+        for (int i = tid; i < KCH * K * CB; i += BLOCK_THREADS)
+        {
+            const int b = i % CB, n = (i / CB) % K, j = i / (CB * K);
+            const int k = j * CB + b, kh = k >> 2, kw = k & 3;
+            uint8_t v = 0;
+            if (kh < a.Fh && kw < a.Fw) // filter [K/16][1][Fh][Fw][1][16]
+                v = filt1[((((size_t)(n / CB)) * a.Fh + kh) * a.Fw + kw) * CB + (n % CB)] ^ 0x80u;
+            sB1[i] = v;
+        }
+        for (int i = tid; i < (int)(2 * a_stage / 16); i += BLOCK_THREADS) // rows of missing pixels / taps stay zero
+            reinterpret_cast<uint4 *>(sA)[i] = make_uint4(0u, 0u, 0u, 0u);
+        for (int i = tid; i < 2 * img_bytes / 4; i += BLOCK_THREADS)
+            reinterpret_cast<unsigned *>(sI)[i] = 0u;
+    }
+    else
+    {
+        // filter slabs [K/16][C/16][16 c][16 k] as they lie in memory, as signed bytes (w - 128)
+        const unsigned *src = reinterpret_cast<const unsigned *>(filt1);
+        for (int i = tid; i < (int)(b1_bytes / 4); i += BLOCK_THREADS)
+            reinterpret_cast<unsigned *>(sB1)[i] = __ldg(src + i) ^ 0x80808080u;
+    }
+    for (int i = tid; i < (int)((b2_bytes + 2 * p_stage) / 16); i += BLOCK_THREADS) // sB2 and sP are adjacent
+        reinterpret_cast<uint4 *>(sB2)[i] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    if (!POOL)
+    {
+        // depthwise filter [K/16][3][3][16] -> per tap and 32 channels a diagonal 32 x 32 block, K-major
+        for (int i = tid; i < TAPS * K; i += BLOCK_THREADS)
+        {
+            const int ch = i % K, tap = i / K;
+            const uint8_t w = filt2[((size_t)(ch / CB) * TAPS + tap) * CB + (ch % CB)] ^ 0x80u;
+            const int c32 = ch & 31;
+            sB2[(size_t)(tap * (K / 32) + (ch >> 5)) * 1024 + (c32 >> 4) * 512 + c32 * 16 + (c32 & 15)] = w;
+        }
+    }
+    if (tid < K)
+    {
+        int c = a.q1.k_zero + (bias1 ? bias1[tid] : 0);
+        if (!STEM && a.zero_in1 != 0)
+        {
+            int wsum = 0; // sum over input channels of (w + zero_filt), from the signed copy
+            const int8_t *col = reinterpret_cast<const int8_t *>(sB1) + (size_t)(tid / CB) * cbs * CB * CB + (tid % CB);
+            for (int i = 0; i < a.C; ++i)
+                wsum += col[i * CB];
+            c += a.zero_in1 * wsum;
+        }
+        corr1[tid] = c;
+        seed1[tid] = requant_seed(c, a.q1.mult);
+        const int c2 = POOL ? 0 : a.q2.k_zero + (bias2 ? bias2[tid] : 0);
+        corr2[tid] = c2;
+        seed2[tid] = requant_seed(c2, a.q2.mult);
+    }
+    fence_proxy_async();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = tmem_base_s;
+
+    if (warp == 8)
+    {
+        // ---------------- producer (1x1 form): one bulk copy per image ----------------
+        if (!STEM && lane == 0)
+        {
+            const uint32_t bytes = (uint32_t)(a.C * a.HW);
+            bool ok = true;
+            for (int j = 0; j < count && ok; ++j)
+            {
+                const int s = j & 1;
+                if (j >= 2) // the MMAs that read this stage two images ago are done
+                    ok = mbar_wait(&d1_full[s], ((j >> 1) - 1) & 1, status, 31);
+                if (!ok)
+                    break;
+                mbar_expect_tx(&a_full[s], bytes);
+                tma_load_1d(sA + (size_t)s * a_stage, in + (size_t)(first + j * step) * bytes, bytes, &a_full[s]);
+            }
+        }
+    }
+    else if (warp == 9)
+    {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0)
+        {
+            const uint32_t idesc1 = STEM ? make_idesc(2, SIGNED_IN ? 1u : 0u, 1, 0, 0, BM, K)
+                                         : make_idesc(2, 0 /*u8*/, 1 /*s8*/, 0 /*A K-major*/, 1 /*B MN-major*/, BM, K);
+            const uint32_t idesc2 = make_idesc(2, a.mid_signed ? 1u : 0u, 1, 0, 0, BM, 32);
+            const uint32_t sb1 = smem_u32(sB1), sb2 = smem_u32(sB2);
+            bool ok = true;
+            auto second = [&](int jj) {
+                const int t = jj & 1;
+                ok = mbar_wait(&p_full[t], (jj >> 1) & 1, status, 33);
+                if (ok && jj >= 2)
+                    ok = mbar_wait(&d2_free[t], ((jj >> 1) - 1) & 1, status, 34);
+                if (!ok)
+                    return;
+                tc_fence_after_sync();
+                const uint32_t pbase = smem_u32(sP + (size_t)t * p_stage);
+                for (int c32 = 0; c32 < K / 32; ++c32)
+                {
+                    const uint32_t d = tmem + (uint32_t)(2 * K + t * K + c32 * 32);
+#pragma unroll
+                    for (int tap = 0; tap < TAPS; ++tap)
+                    {
+                        const int kh = tap / 3, kw = tap - 3 * kh;
+                        const uint64_t da = make_smem_desc(pbase + (uint32_t)kw * copy_bytes + (uint32_t)(2 * c32 * a.E * CB) +
+                                                               (uint32_t)(kh * a.W * CB),
+                                                           (uint32_t)(a.E * CB), 8 * CB, 0);
+                        const uint64_t db = make_smem_desc(sb2 + (uint32_t)((tap * (K / 32) + c32) * 1024), 32 * CB, 8 * CB, 0);
+                        tc_mma_i8(d, da, db, idesc2, tap > 0 ? 1u : 0u);
+                    }
+                }
+                tc_commit(&d2_full[t]); // the sums are complete ...
+                tc_commit(&p_free[t]);  // ... and this copy of the intermediate may be overwritten
+            };
+            for (int j = 0; j < count && ok; ++j)
+            {
+                const int s = j & 1;
+                ok = mbar_wait(&a_full[s], (j >> 1) & 1, status, 32);
+                if (ok && j >= 2)
+                    ok = mbar_wait(&d1_free[s], ((j >> 1) - 1) & 1, status, 35);
+                if (!ok)
+                    break;
+                tc_fence_after_sync();
+                const uint32_t sa = smem_u32(sA + (size_t)s * a_stage);
+                const uint32_t d1 = tmem + (uint32_t)(s * K);
+                if (STEM)
+                {
+                    for (int i = 0; i < KCH / 2; ++i) // 32 bytes of K per MMA = two 16-byte chunks
+                    {
+                        const uint64_t da = make_smem_desc(sa + i * 2 * BM * CB, BM * CB, 8 * CB, 0);
+                        const uint64_t db = make_smem_desc(sb1 + i * 2 * K * CB, K * CB, 8 * CB, 0);
+                        tc_mma_i8(d1, da, db, idesc1, i > 0 ? 1u : 0u);
+                    }
+                }
+                else
+                {
+                    // channel block cb of the image lies HW pixels after block cb - 1 (the image is one
+                    // contiguous run); lanes >= HW read into the next block: their sums are never used
+                    for (int i = 0; i < cbs / 2; ++i)
+                    {
+                        const uint64_t da = make_smem_desc(sa + (uint32_t)(i * 2 * a.HW * CB), (uint32_t)(a.HW * CB), 8 * CB, 0);
+                        const uint64_t db = make_smem_desc(sb1 + i * 2 * CB * CB, 8 * CB, (uint32_t)(cbs * CB * CB), 0);
+                        tc_mma_i8(d1, da, db, idesc1, i > 0 ? 1u : 0u);
+                    }
+                }
+                tc_commit(&d1_full[s]);
+                if (!POOL && j >= 1)
+                    second(j - 1);
+            }
+            if (!POOL && ok && count > 0)
+                second(count - 1);
+        }
+    }
+    else if (warp < 4)
+    {
+        // ---------------- stage-1 epilogue: requantise into the shifted copies ----------------
+        const int q = tid;                         // this thread's pixel = tensor-memory lane
+        const int cq = q % a.W;
+        const bool wraps_left = cq == a.W - 1;     // copy kw = 0 must not show this pixel to the next row
+        const bool wraps_right = cq == 0;          // copy kw = 2 must not show it to the previous row
+        const uint32_t sx = a.mid_signed ? 0x80808080u : 0u;
+        bool ok = true;
+        // first-layer form: the im2col tile of an image is built by these warps (see conv_u8_tc.cu)
+        const int oh = q / a.W, ow = q - oh * a.W;
+        auto build = [&](int n, int s) {
+            uint8_t *img = sI + (size_t)s * img_bytes;
+            const uint8_t *src = in + (size_t)n * a.H0 * a.W0;
+            for (int i = tid; i < a.H0 * a.W0; i += EPI_THREADS)
+            {
+                const int h = i / a.W0, w = i - h * a.W0;
+                const uint8_t v = src[i];
+                img[(h + a.pad_t) * a.pitch + (w + a.pad_l)] = SIGNED_IN ? (uint8_t)(v ^ 0x80u) : v;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (q < a.HW)
+            {
+                const uint8_t *row = img + (oh * a.stride) * a.pitch + ow * a.stride;
+                uint8_t *arow = sA + (size_t)s * a_stage + (size_t)q * CB;
+                for (int j4 = 0; j4 * 4 < a.Fh; ++j4)
+                {
+                    unsigned wv[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                    for (int t = 0; t < 4; ++t)
+                    {
+                        const int kh = j4 * 4 + t;
+                        if (kh < a.Fh)
+                        {
+                            const uint8_t *pw = row + kh * a.pitch;
+                            const unsigned *al = reinterpret_cast<const unsigned *>(pw - ((size_t)pw & 3));
+                            wv[t] = __funnelshift_r(al[0], al[1], 8 * (unsigned)((size_t)pw & 3));
+                            if (a.Fw < 4)
+                                wv[t] &= (1u << (8 * a.Fw)) - 1u;
+                        }
+                    }
+                    *reinterpret_cast<uint4 *>(arow + (size_t)j4 * BM * CB) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                }
+            }
+            fence_proxy_async();
+            mbar_arrive(&a_full[s]);
+        };
+        if (STEM && count > 0)
+            build(first, 0);
+        for (int j = 0; j < count; ++j)
+        {
+            const int s = j & 1;
+            if (STEM)
+            {
+                // everyone is done with the padded copy of image j - 1 (and agrees on whether to go on)
+                if (!ok)
+                    *reinterpret_cast<volatile int *>(&failed1.v) = 1;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*reinterpret_cast<volatile int *>(&failed1.v))
+                    break;
+                if (j + 1 < count)
+                    build(first + (j + 1) * step, s ^ 1); // stage s^1 was read by the MMAs of image j - 1: waited for below, last turn
+            }
+            else if (!ok)
+                break;
+            ok = mbar_wait(&d1_full[s], (j >> 1) & 1, status, 36);
+            if (ok && j >= 2)
+                ok = mbar_wait(&p_free[s], ((j >> 1) - 1) & 1, status, 37);
+            if (!ok)
+                continue; // leaves at the top of the loop, together with the other warps
+            tc_fence_after_sync();
+            // this pixel in the copy for kw = 1 (entry q + W); the DW form keeps it between the other two
+            uint8_t *pc = sP + (size_t)s * p_stage + (POOL ? 0u : copy_bytes) + (size_t)(q + a.W) * CB;
+#pragma unroll 1
+            for (int h = 0; h < K / 32; ++h) // 32 channels per tensor-memory load
+            {
+                uint32_t r[32];
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(s * K + h * 32), r);
+                tmem_ld_wait();
+                uint4 o2[2];
+                requant32(r, corr1 + h * 32, seed1 + h * 32, a.q1, o2);
+#pragma unroll
+                for (int c2 = 0; c2 < 2; ++c2)
+                {
+                    uint4 o = o2[c2];
+                    o.x ^= sx; o.y ^= sx; o.z ^= sx; o.w ^= sx;
+                    if (q < a.HW)
+                    {
+                        uint8_t *p1 = pc + (size_t)(2 * h + c2) * a.E * CB;
+                        *reinterpret_cast<uint4 *>(p1) = o;
+                        if (!POOL)
+                        {
+                            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                            *reinterpret_cast<uint4 *>(p1 - copy_bytes + CB) = wraps_left ? z : o;   // copy kw = 0, entry q + W + 1
+                            *reinterpret_cast<uint4 *>(p1 + copy_bytes - CB) = wraps_right ? z : o;  // copy kw = 2, entry q + W - 1
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            fence_proxy_async();
+            mbar_arrive(&p_full[s]);
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(&d1_free[s]);
+        }
+    }
+    else
+    {
+        // ---------------- stage-2 epilogue ----------------
+        const int p = tid - EPI_THREADS, w4 = warp - 4;
+        bool ok = true;
+        if (!POOL)
+        {
+            for (int j = 0; j < count && ok; ++j)
+            {
+                const int t = j & 1;
+                ok = mbar_wait(&d2_full[t], (j >> 1) & 1, status, 38);
+                if (!ok)
+                    break;
+                tc_fence_after_sync();
+                uint8_t *o = out + ((size_t)(first + j * step) * KB * a.HW + p) * CB;
+#pragma unroll 1
+                for (int h = 0; h < K / 32; ++h)
+                {
+                    uint32_t r[32];
+                    tmem_ld32(tmem + ((uint32_t)(w4 * 32) << 16) + (uint32_t)(2 * K + t * K + h * 32), r);
+                    tmem_ld_wait();
+                    uint4 o2[2];
+                    requant32(r, corr2 + h * 32, seed2 + h * 32, a.q2, o2);
+                    if (p < a.HW)
+                    {
+                        *reinterpret_cast<uint4 *>(o + (size_t)(2 * h) * a.HW * CB) = o2[0];
+                        *reinterpret_cast<uint4 *>(o + (size_t)(2 * h + 1) * a.HW * CB) = o2[1];
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(&d2_free[t]);
+            }
+        }
+        else
+        {
+            for (int j = 0; j < count; ++j)
+            {
+                const int t = j & 1;
+                if (ok)
+                    ok = mbar_wait(&p_full[t], (j >> 1) & 1, status, 39);
+                if (ok)
+                {
+                    // channel sums of the intermediate: warp w4 takes channel blocks w4, w4 + 4, ...
+                    for (int cb = w4; cb < KB; cb += 4)
+                    {
+                        unsigned s16[16];
+#pragma unroll
+                        for (int e = 0; e < 16; ++e)
+                            s16[e] = 0u;
+                        const uint8_t *col = sP + (size_t)t * p_stage + ((size_t)cb * a.E + a.W) * CB;
+                        for (int px = lane; px < a.HW; px += 32)
+                        {
+                            const uint4 v = *reinterpret_cast<const uint4 *>(col + (size_t)px * CB);
+                            const unsigned wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                            for (int k4 = 0; k4 < 4; ++k4)
+                            {
+                                s16[4 * k4 + 0] = __dp4a(wv[k4], 0x00000001u, s16[4 * k4 + 0]);
+                                s16[4 * k4 + 1] = __dp4a(wv[k4], 0x00000100u, s16[4 * k4 + 1]);
+                                s16[4 * k4 + 2] = __dp4a(wv[k4], 0x00010000u, s16[4 * k4 + 2]);
+                                s16[4 * k4 + 3] = __dp4a(wv[k4], 0x01000000u, s16[4 * k4 + 3]);
+                            }
+                        }
+#pragma unroll
+                        for (int e = 0; e < 16; ++e)
+#pragma unroll
+                            for (int m = 16; m >= 1; m >>= 1)
+                                s16[e] += __shfl_xor_sync(0xffffffffu, s16[e], m);
+                        if (lane == 0)
+                        {
+                            int v[16];
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) // k_zero + sum over the window of (a + zero point)
+                                v[e] = a.q2.k_zero + (int)s16[e] + a.HW * a.zero_pool;
+                            *reinterpret_cast<uint4 *>(&pooled[t][cb * CB]) =
+                                requant_pack16(v, a.q2.lshift, a.q2.rshift, a.q2.mult);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&p_free[t]);
+                }
+                if (!ok)
+                    *reinterpret_cast<volatile int *>(&failed2.v) = 1;
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (*reinterpret_cast<volatile int *>(&failed2.v))
+                    break;
+                // dense layer on the pooled vector: filter [Kd/16][K/16][16 c][16 k]
+                if (p < a.Kd)
+                {
+                    int acc = a.qd.k_zero + (bias2 ? bias2[p] : 0);
+                    const uint8_t *wcol = filt2 + (size_t)(p / CB) * KB * CB * CB + (p % CB);
+                    for (int c = 0; c < K; ++c)
+                        acc += ((int)pooled[t][c] + a.zero_in_d) * ((int)__ldg(wcol + (size_t)c * CB) + a.zero_filt_d);
+                    out[(size_t)(first + j * step) * a.Kd + p] =
+                        (uint8_t)requant_dev(acc, a.qd.lshift, a.qd.rshift, a.qd.mult);
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 8)
+        tmem_dealloc(tmem, TMEM_COLS);
+}
+
+bool quant_ok(const small_b200_layer *L) { return L->lshift >= 0 && L->lshift < 32 && L->rshift >= 0 && L->rshift < 32; }
+
+// Fills the arguments of stage 1 and the geometry; false when the pair is not covered.
+bool plan_first(const small_b200_layer *c, BlockArgs &a, bool &stem)
+{
+    if (!c || c->N < 0 || c->K % 32 != 0 || c->K > 64 || c->zero_filt != -128 || !quant_ok(c) || c->accumulate)
+        return false;
+    a = BlockArgs{};
+    a.N = c->N; a.C = c->C;
+    a.H = out_dim(c->H, c->pad_t, c->pad_b, c->Fh, c->stride);
+    a.W = out_dim(c->W, c->pad_l, c->pad_r, c->Fw, c->stride);
+    a.HW = a.H * a.W;
+    if (a.HW <= 0 || a.HW > BM)
+        return false;
+    a.zero_in1 = c->zero_in;
+    a.q1 = Requant{c->lshift, c->rshift, c->multiplier, c->k_zero};
+    stem = c->C == 1;
+    if (stem)
+    {
+        if (c->Fw > 4 || c->Fh > 16 || (c->zero_in != 0 && c->zero_in != -128) || c->stride < 1)
+            return false;
+        a.H0 = c->H; a.W0 = c->W; a.Fh = c->Fh; a.Fw = c->Fw; a.stride = c->stride; a.pad_t = c->pad_t; a.pad_l = c->pad_l;
+        a.pitch = ((c->W + c->pad_l + c->pad_r + 12) + 3) & ~3; // room for the unaligned window read
+        a.prow = c->H + c->pad_t + c->pad_b + 1;
+    }
+    else
+    {
+        if (c->Fh != 1 || c->Fw != 1 || c->stride != 1 || c->pad_t || c->pad_b || c->pad_l || c->pad_r)
+            return false;
+        if (c->C % 32 != 0 || c->C > 128)
+            return false;
+    }
+    a.E = (BM + 2 * a.W + 7) & ~7;
+    return true;
+}
+
+size_t smem_need(const BlockArgs &a, int K, bool stem, bool pool)
+{
+    const size_t a_stage = stem ? (size_t)4 * BM * CB : (size_t)a.C * BM;
+    const size_t b1 = stem ? (size_t)4 * K * CB : (size_t)K * a.C;
+    const size_t b2 = pool ? 0 : (size_t)9 * (K / 32) * 1024;
+    const size_t p_stage = (size_t)(pool ? 1 : 3) * (K / CB) * a.E * CB;
+    const size_t img = stem ? (size_t)2 * a.prow * a.pitch : 0;
+    return 2 * a_stage + b1 + b2 + 2 * p_stage + ((img + 15) & ~(size_t)15) + 64;
+}
+
+template <int K, bool STEM, bool POOL, bool SIGNED_IN>
+int launch_block(const BlockArgs &a, size_t smem, const uint8_t *in, const uint8_t *f1, const int32_t *b1, const uint8_t *f2,
+                 const int32_t *b2, uint8_t *out, cudaStream_t st)
+{
+    auto kern = block_u8_tc_kernel<K, STEM, POOL, SIGNED_IN>;
+    static PerDeviceOnce configured;
+    int dev;
+    if (configured.needed(&dev))
+    {
+        SB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        configured.mark(dev);
+    }
+    int *status = device_status_ptr();
+    if (!status)
+        return fail(SMALL_B200_CUDA_ERROR, "device status word not available");
+    // CTAs per SM: tensor memory (4K or 2K of 512 columns) and shared memory
+    int per_sm = 512 / (POOL ? (2 * K < 32 ? 32 : 2 * K) : 4 * K);
+    const int by_smem = (int)((224 * 1024) / (smem + 4096));
+    if (per_sm > by_smem) per_sm = by_smem;
+    if (per_sm > 4) per_sm = 4;
+    if (per_sm < 1) per_sm = 1;
+    long long grid = (long long)num_sms() * per_sm;
+    if (grid > a.N) grid = a.N;
+    kern<<<(unsigned)grid, BLOCK_THREADS, smem, st>>>(a, in, f1, b1, f2, b2, out, status);
+    return launched("block_u8_tc_kernel");
+}
+
+template <bool POOL>
+int dispatch(const BlockArgs &a, int K, bool stem, size_t smem, const uint8_t *in, const uint8_t *f1, const int32_t *b1,
+             const uint8_t *f2, const int32_t *b2, uint8_t *out, cudaStream_t st)
+{
+    const bool sgn = a.zero_in1 != 0;
+#define SB_BLOCK_CASE(KK)                                                                                        \
+    if (K == KK)                                                                                                 \
+    {                                                                                                            \
+        if (!stem)                                                                                               \
+            return launch_block<KK, false, POOL, false>(a, smem, in, f1, b1, f2, b2, out, st);                   \
+        return sgn ? launch_block<KK, true, POOL, true>(a, smem, in, f1, b1, f2, b2, out, st)                    \
+                   : launch_block<KK, true, POOL, false>(a, smem, in, f1, b1, f2, b2, out, st);                  \
+    }
+    SB_BLOCK_CASE(32)
+    SB_BLOCK_CASE(64)
+#undef SB_BLOCK_CASE
+    return fail(SMALL_B200_INVALID_ARGUMENT, "fused uint8 block: channel count not covered");
+}
+
+bool plan_dw(const small_b200_layer *c, const small_b200_layer *d, BlockArgs &a, bool &stem)
+{
+    if (!plan_first(c, a, stem) || !d)
+        return false;
+    if (d->C != c->K || d->H != a.H || d->W != a.W || d->N != c->N || d->Fh != 3 || d->Fw != 3 || d->stride != 1 ||
+        d->pad_t != 1 || d->pad_b != 1 || d->pad_l != 1 || d->pad_r != 1 || d->accumulate || !quant_ok(d))
+        return false;
+    if (d->zero_filt != -128 || (d->zero_in != 0 && d->zero_in != -128))
+        return false;
+    a.mid_signed = d->zero_in != 0;
+    a.q2 = Requant{d->lshift, d->rshift, d->multiplier, d->k_zero};
+    return smem_need(a, c->K, stem, false) <= 200 * 1024;
+}
+
+bool plan_pool(const small_b200_layer *c, const small_b200_layer *pl, const small_b200_layer *dn, BlockArgs &a, bool &stem)
+{
+    if (!plan_first(c, a, stem) || !pl || !dn)
+        return false;
+    if (pl->C != c->K || pl->H != a.H || pl->W != a.W || pl->Fh != a.H || pl->Fw != a.W || pl->pad_t || pl->pad_b ||
+        pl->pad_l || pl->pad_r || pl->N != c->N || !quant_ok(pl))
+        return false;
+    if (dn->C != c->K || dn->H != 1 || dn->W != 1 || dn->Fh != 1 || dn->Fw != 1 || dn->stride != 1 || dn->pad_t ||
+        dn->pad_b || dn->pad_l || dn->pad_r || dn->K % CB != 0 || dn->K <= 0 || dn->K > 128 || dn->N != c->N ||
+        dn->accumulate || !quant_ok(dn))
+        return false;
+    a.mid_signed = 0;
+    a.zero_pool = pl->zero_in;
+    a.q2 = Requant{pl->lshift, pl->rshift, pl->multiplier, pl->k_zero};
+    a.Kd = dn->K; a.zero_in_d = dn->zero_in; a.zero_filt_d = dn->zero_filt;
+    a.qd = Requant{dn->lshift, dn->rshift, dn->multiplier, dn->k_zero};
+    return smem_need(a, c->K, stem, true) <= 200 * 1024;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+} // namespace
+
+extern "C"
+{
+int small_b200_conv2d_dwconv2d_u8_supported(const small_b200_layer *conv, const small_b200_layer *dw)
+{
+    BlockArgs a;
+    bool stem;
+    return plan_dw(conv, dw, a, stem) ? 1 : 0;
+}
+
+int small_b200_conv2d_dwconv2d_u8(const small_b200_layer *conv, const small_b200_layer *dw, const uint8_t *in,
+                                  const uint8_t *conv_filt, const int32_t *conv_bias, const uint8_t *dw_filt,
+                                  const int32_t *dw_bias, uint8_t *out, void *stream)
+{
+    BlockArgs a;
+    bool stem;
+    if (!plan_dw(conv, dw, a, stem))
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D_DepthwiseConv2D<quint8> ERROR: this pair of layers is not covered by the "
+                                                 "one-kernel form; call the two layers separately.");
+    if (a.N == 0)
+        return SMALL_B200_OK;
+    if (!aligned16(in) || !aligned16(out) || !aligned16(conv_filt))
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D_DepthwiseConv2D<quint8> ERROR: buffers must be 16-byte aligned.");
+    return dispatch<false>(a, conv->K, stem, smem_need(a, conv->K, stem, false), in, conv_filt, conv_bias, dw_filt, dw_bias, out,
+                           as_stream(stream));
+}
+
+int small_b200_conv2d_avgpool_dense_u8_supported(const small_b200_layer *conv, const small_b200_layer *pool,
+                                                 const small_b200_layer *dense)
+{
+    BlockArgs a;
+    bool stem;
+    return plan_pool(conv, pool, dense, a, stem) ? 1 : 0;
+}
+
+int small_b200_conv2d_avgpool_dense_u8(const small_b200_layer *conv, const small_b200_layer *pool,
+                                       const small_b200_layer *dense, const uint8_t *in, const uint8_t *conv_filt,
+                                       const int32_t *conv_bias, const uint8_t *dense_filt, const int32_t *dense_bias,
+                                       uint8_t *out, void *stream)
+{
+    BlockArgs a;
+    bool stem;
+    if (!plan_pool(conv, pool, dense, a, stem))
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D_AveragePool2D_Dense<quint8> ERROR: these layers are not covered by the "
+                                                 "one-kernel form; call them separately.");
+    if (a.N == 0)
+        return SMALL_B200_OK;
+    if (!aligned16(in) || !aligned16(conv_filt))
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D_AveragePool2D_Dense<quint8> ERROR: buffers must be 16-byte aligned.");
+    return dispatch<true>(a, conv->K, stem, smem_need(a, conv->K, stem, true), in, conv_filt, conv_bias, dense_filt, dense_bias, out,
+                          as_stream(stream));
+}
+} // extern "C"

@@ -447,3 +447,49 @@ def Conv2D_3xTF32(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pa
     check(lib().small_b200_conv2d_f32_tf32x3(C.byref(L), _ptr(input_buf),
                                              _ptr(prepared_filter_buf), _ptr(bias_buf),
                                              _ptr(output_buf), _stream(stream)))
+
+
+# --------------------------------------------------------------------------- fused uint8 blocks
+def _qlayer(batch, C_, K, H, W, Fh, Fw, stride, pads, inp_zero, filt_zero, out_q):
+    """A uint8 layer descriptor from explicit quantisation parameters: out_q = (lshift, rshift, multiplier)."""
+    L = Layer(batch, C_, K, H, W, Fh, Fw, stride, *pads, 0, ACT_NONE, 0.0, 0, 0, 0, 0, 0, 0)
+    L.zero_in, L.zero_filt = inp_zero, filt_zero
+    L.lshift, L.rshift, L.multiplier = out_q
+    return L
+
+
+def Conv2D_ReLU_DepthwiseConv2D_ReLU(conv_kernel_height, conv_kernel_width, conv_stride,
+                                     conv_t_pad, conv_b_pad, conv_l_pad, conv_r_pad,
+                                     dw_kernel_height, dw_kernel_width, dw_stride,
+                                     dw_t_pad, dw_b_pad, dw_l_pad, dw_r_pad,
+                                     output_channels, input_channels, input_height, input_width,
+                                     input_buf, filter_buf, inter_output_buf, dwise_filter_buf, output_buf, *,
+                                     conv_bias=None, dw_bias=None, batch=1, stream=None):
+    """small::Conv2D_ReLU_DepthwiseConv2D_ReLU (fused_interface_abstract.hpp:1840; the argument list is
+    the reference's) for QUInt8Buffer operands, where the clamp of each requantisation is the ReLU.
+    inter_output_buf carries the quantisation of the intermediate (its zero point and the
+    multiplier / shifts the convolution requantises with); no data is written to it when the pair
+    runs as one kernel.  Pairs the one-kernel form does not cover run as two calls through it."""
+    if not (_is_q(input_buf) and _is_q(output_buf) and _is_q(inter_output_buf)):
+        raise ValueError("Conv2D_ReLU_DepthwiseConv2D_ReLU: this form takes QUInt8Buffer operands")
+    Lc = _qlayer(batch, input_channels, output_channels, input_height, input_width, conv_kernel_height,
+                 conv_kernel_width, conv_stride, (conv_t_pad, conv_b_pad, conv_l_pad, conv_r_pad),
+                 input_buf.zero(), filter_buf.zero(),
+                 (inter_output_buf.lshift, inter_output_buf.rshift, inter_output_buf.multiplier))
+    ho, wo = Lc.out_hw()
+    Ld = _qlayer(batch, output_channels, output_channels, ho, wo, dw_kernel_height, dw_kernel_width, dw_stride,
+                 (dw_t_pad, dw_b_pad, dw_l_pad, dw_r_pad), inter_output_buf.zero(), dwise_filter_buf.zero(),
+                 (output_buf.lshift, output_buf.rshift, output_buf.multiplier))
+    po, pw = Ld.out_hw()
+    _need(output_buf, batch * output_channels * po * pw, "Conv2D_ReLU_DepthwiseConv2D_ReLU output")
+    if lib().small_b200_conv2d_dwconv2d_u8_supported(C.byref(Lc), C.byref(Ld)):
+        check(lib().small_b200_conv2d_dwconv2d_u8(C.byref(Lc), C.byref(Ld), _ptr(input_buf), _ptr(filter_buf),
+                                                  _ptr(conv_bias), _ptr(dwise_filter_buf), _ptr(dw_bias),
+                                                  _ptr(output_buf), _stream(stream)))
+        return True
+    _need(inter_output_buf, batch * output_channels * ho * wo, "Conv2D_ReLU_DepthwiseConv2D_ReLU intermediate")
+    check(lib().small_b200_conv2d_u8(C.byref(Lc), _ptr(input_buf), _ptr(filter_buf), _ptr(conv_bias),
+                                     _ptr(inter_output_buf), _stream(stream)))
+    check(lib().small_b200_dwconv2d_u8(C.byref(Ld), _ptr(inter_output_buf), _ptr(dwise_filter_buf), _ptr(dw_bias),
+                                       _ptr(output_buf), _stream(stream)))
+    return False

@@ -318,13 +318,17 @@ class Chain:
     into a CUDA graph; launch() replays it.  `x` (input) and `y` (output) are the device
     tensors at the two ends."""
 
-    def __init__(self, layers, batch, dtype="f32", device="cuda", tensor_core="auto", fuse_pool=True):
+    def __init__(self, layers, batch, dtype="f32", device="cuda", tensor_core="auto", fuse_pool=True,
+                 fuse_u8=True):
         """tensor_core: "auto" = fp32 convolutions run on the tensor cores where the library
         prefers them there (small_b200_conv2d_f32_tf32x3_preferred); True = every covered
         layer; False = CUDA cores only.  fuse_pool: a CUDA-core convolution followed by a 2x2
         stride-2 max pool runs as one kernel where the library covers the pair (the reference's
         Conv2D_Bias_ReLU_Maxpool2D path); the pool's entry in `fused_into` then names its
-        producer and enqueue_layer() does nothing for it."""
+        producer and enqueue_layer() does nothing for it.  fuse_u8: a uint8 convolution followed by a
+        3x3 depthwise convolution (the reference's Conv2D_ReLU_DepthwiseConv2D_ReLU pairing), or by the
+        global average pool and the dense layer that end the keyword-spotting network, runs as one kernel
+        where the library covers the shapes; the absorbed layers are entered in `fused_into` likewise."""
         self.layers, self.batch, self.dtype = layers, batch, dtype
         self.fuse_pool = fuse_pool
         self.tensor_core = tensor_core
@@ -385,10 +389,35 @@ class Chain:
                 dp = self._desc(Pn, padded(Pn["C"]))
                 if lib().small_b200_conv2d_maxpool_f32_supported(C.byref(dc), C.byref(dp)):
                     self.fused_into[i + 1] = i
+        if dtype == "u8" and fuse_u8:
+            i = 0
+            while i < len(layers) - 1:
+                L = layers[i]
+                if L["op"] == "conv" and "src" not in L:
+                    dc = self._desc(L, L["C"] if i == 0 else padded(L["C"]))
+                    nxt = layers[i + 1]
+                    if nxt["op"] == "dwconv" and lib().small_b200_conv2d_dwconv2d_u8_supported(
+                            C.byref(dc), C.byref(self._desc(nxt, padded(nxt["C"])))):
+                        self.fused_into[i + 1] = i
+                        i += 2
+                        continue
+                    if (nxt["op"] == "avgpool" and i + 2 < len(layers) and layers[i + 2]["op"] == "conv" and
+                            lib().small_b200_conv2d_avgpool_dense_u8_supported(
+                                C.byref(dc), C.byref(self._desc(nxt, padded(nxt["C"]))),
+                                C.byref(self._desc(layers[i + 2], padded(layers[i + 2]["C"]))))):
+                        self.fused_into[i + 1] = i
+                        self.fused_into[i + 2] = i
+                        i += 3
+                        continue
+                i += 1
         self.graph = None
         self.y = None
         self.kernels_per_step = 0
         self._descs = []
+
+    def absorbed(self, i):
+        """Indices of the layers that run inside layer i's kernel, in order."""
+        return sorted(k for k, v in self.fused_into.items() if v == i)
 
     def _desc(self, L, cin):
         t, b, l, r = L["pads"]
@@ -408,7 +437,17 @@ class Chain:
         p = lambda t: t.data_ptr() if t is not None else None
         if i in self.fused_into:
             return  # computed by its producer
-        if L["op"] == "conv" and (i + 1) in self.fused_into:
+        follow = self.absorbed(i)
+        if L["op"] == "conv" and follow and self.dtype == "u8":
+            ds = [self._desc(self.layers[k], padded(self.layers[k]["C"])) for k in follow]
+            w2, b2 = self.params[follow[-1]]
+            if len(follow) == 1:
+                check(l.small_b200_conv2d_dwconv2d_u8(C.byref(d), C.byref(ds[0]), p(src), p(wt), p(bs), p(w2), p(b2),
+                                                      p(dst), stream))
+            else:
+                check(l.small_b200_conv2d_avgpool_dense_u8(C.byref(d), C.byref(ds[0]), C.byref(ds[1]), p(src), p(wt),
+                                                           p(bs), p(w2), p(b2), p(dst), stream))
+        elif L["op"] == "conv" and follow:
             dp = self._desc(self.layers[i + 1], padded(self.layers[i + 1]["C"]))
             check(l.small_b200_conv2d_maxpool_f32(C.byref(d), C.byref(dp), p(src), p(wt), p(bs), p(dst), stream))
         elif L["op"] == "conv" and self.prepared[i] is not None:

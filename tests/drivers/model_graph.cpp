@@ -11,13 +11,18 @@
 //     can be used again afterwards.
 // Prints the time per inference of both forms.  Exit code 0 = all checks passed.
 //
-//   model_graph [image size = 416] [batch = 4] [timed runs = 20]
+// With a fourth argument (a directory) the filters, the single input image and the model's output
+// for it are written there as raw float32 files (f0.bin .. f8.bin, image.bin, out.bin), so that a
+// second party -- the test-suite's CPU restatement of the reference -- can recompute the output.
+//
+//   model_graph [image size = 416] [batch = 4] [timed runs = 20] [dump directory]
 #include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <random>
+#include <string>
 #include <vector>
 
 #include <small.h>
@@ -29,6 +34,19 @@ static double now_ms()
 {
     using namespace std::chrono;
     return duration<double, std::milli>(steady_clock::now().time_since_epoch()).count();
+}
+
+static void dump(const std::string &dir, const std::string &name, const float *p, size_t n)
+{
+    if (dir.empty())
+        return;
+    FILE *f = std::fopen((dir + "/" + name).c_str(), "wb");
+    if (!f || std::fwrite(p, sizeof(float), n, f) != n)
+    {
+        std::printf("FAIL: cannot write %s/%s\n", dir.c_str(), name.c_str());
+        std::exit(2);
+    }
+    std::fclose(f);
 }
 
 static void fill(BufferT &b, std::mt19937 &rng, float lo, float hi)
@@ -44,6 +62,7 @@ int main(int argc, char **argv)
     const uint32_t size = argc > 1 ? (uint32_t)std::atoi(argv[1]) : 416;
     const uint32_t batch = argc > 2 ? (uint32_t)std::atoi(argv[2]) : 4;
     const int runs = argc > 3 ? std::atoi(argv[3]) : 20;
+    const std::string dump_dir = argc > 4 ? argv[4] : "";
     int failures = 0;
     std::mt19937 rng(4);
 
@@ -57,6 +76,7 @@ int main(int argc, char **argv)
         const float bound = std::sqrt(6.0f / (float)(chans[l] * k * k)); // He-uniform keeps activations O(1)
         fill(*f, rng, -bound, bound);
         filters.push_back(f);
+        dump(dump_dir, "f" + std::to_string(l) + ".bin", f->data(), f->size());
     }
 
     // ---- one image: eager, then recorded and replayed
@@ -71,6 +91,8 @@ int main(int argc, char **argv)
         auto out = model.inference(&input);
         const size_t n = out[0]->size();
         single.assign(out[0]->buffer().data(), out[0]->buffer().data() + n);
+        dump(dump_dir, "image.bin", image.data(), image.size());
+        dump(dump_dir, "out.bin", single.data(), n);
 
         double t0 = now_ms();
         for (int r = 0; r < runs; ++r)

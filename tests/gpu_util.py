@@ -84,8 +84,8 @@ def oracle_chain(oracle, layers, x_packed, dtype="f32"):
 def run_layers_checked(oracle, chain, layers, images, dtype="f32", tol=1e-5):
     """Runs `chain` eagerly, one layer call at a time, and after each call compares the images
     in `images` with the oracle applied to THE SAME INPUT the device kernel read (so a layer's
-    error is its own, not the chain's).  A max pool that its producer absorbs is checked together
-    with that producer.  Returns per-layer (name, worst error) -- errors are max|x-ref|/max|ref| for
+    error is its own, not the chain's).  Layers that their producer absorbs (a max pool, a depthwise
+    convolution, the pool + dense tail) are checked together with that producer.  Returns per-layer (name, worst error) -- errors are max|x-ref|/max|ref| for
     fp32 and the count of differing bytes for uint8."""
     from smallframework_b200 import _lib
     from smallframework_b200.networks import _out_hw, padded
@@ -103,10 +103,8 @@ def run_layers_checked(oracle, chain, layers, images, dtype="f32", tol=1e-5):
         chain.stream.synchronize()
         cin = L["C"] if i == 0 else padded(L["C"])
         n_in = cin * L["H"] * L["W"]
-        last = L
-        fused_pool = (i + 1) in chain.fused_into
-        if fused_pool:
-            last = layers[i + 1]
+        follow = chain.absorbed(i)
+        last = layers[follow[-1]] if follow else L
         ho, wo = _out_hw(last)
         n_out = padded(last["K"]) * ho * wo
         xin = {n: src[n * n_in:(n + 1) * n_in].cpu().numpy() for n in images}
@@ -117,8 +115,8 @@ def run_layers_checked(oracle, chain, layers, images, dtype="f32", tol=1e-5):
         worst = 0.0
         for n in images:
             want = oracle_layer(oracle, L, i == 0, xin[n], dtype, before.get(n))
-            if fused_pool:
-                want = oracle_layer(oracle, layers[i + 1], False, want, dtype)
+            for k in follow:
+                want = oracle_layer(oracle, layers[k], False, want, dtype)
             got = dst[n * n_out:(n + 1) * n_out].cpu().numpy()
             if dtype == "f32":
                 err = rel_max_err(got, want)
@@ -127,5 +125,5 @@ def run_layers_checked(oracle, chain, layers, images, dtype="f32", tol=1e-5):
                 err = float(np.count_nonzero(got != want))
                 assert err == 0, (L["name"], n, err)
             worst = max(worst, err)
-        report.append((L["name"] + ("+pool" if fused_pool else ""), worst))
+        report.append(("+".join([L["name"]] + [layers[k]["name"] for k in follow]), worst))
     return report

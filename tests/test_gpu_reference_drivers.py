@@ -63,17 +63,46 @@ def test_reference_driver_on_cuda_cores_only(name):
     assert r.returncode == 0, f"{name} failed with SMALL_B200_TENSOR_CORE=0:\n{tail}"
 
 
+def _tiny_yolov2_model_on_the_oracle(oracle, size, filters, image):
+    """include/small/models/TinyYoloV2.hpp:161-240 layer by layer on the CPU restatement: six blocks of
+    Conv2D 3x3 'same' + ReLU and MaxPool2D 2x2 'same' (strides 2,2,2,2,2,1), two Conv2D 3x3 + ReLU to
+    1024 channels, one Conv2D 1x1 + ReLU to 16 channels.  Filters arrive packed."""
+    import numpy as np
+    from oracle.bindings import same_pads, shape
+    chans = [3, 16, 32, 64, 128, 256, 512, 1024, 1024, 16]
+    cur, h = image, size
+    for l in range(9):
+        k = 1 if l == 8 else 3
+        sh = shape(chans[l], chans[l + 1], h, h, k, k, 1, same_pads(h, h, k, k, 1), 16)
+        cur = oracle.conv2d_f32(sh, cur, filters[l], act=1)
+        if l < 6:
+            s = 2 if l < 5 else 1
+            shp = shape(chans[l + 1], chans[l + 1], h, h, 2, 2, s, same_pads(h, h, 2, 2, s), 16)
+            cur = oracle.pool2d_f32(shp, cur)
+            h = shp.out_hw()[0]
+    return cur
+
+
 @pytest.mark.parametrize("tensor_core", ["0", "1"])
-def test_model_classes_as_cuda_graph(tensor_core):
+def test_model_classes_as_cuda_graph(oracle, tensor_core, tmp_path):
     """tests/drivers/model_graph.cpp: the reference's TinyYoloV2 Model class run eagerly, recorded with
     small::b200::InferenceGraph and replayed (bit-identical), and batched with BatchScope (every image
-    equals its single-image result)."""
+    equals its single-image result).  The model's output for one 416x416 image is then recomputed from
+    the driver's own filters and image on the oracle (bit-identical to the reference's REF build)."""
+    import numpy as np
     exe = os.path.join(BUILD, "bin", "model_graph")
     if not os.path.exists(exe):
         pytest.skip(f"{exe} not built (run make -C tests/reference_drivers where the reference is mounted)")
     env = dict(os.environ, OMP_NUM_THREADS="4", SMALL_B200_TENSOR_CORE=tensor_core)
-    r = subprocess.run([exe, "416", "3", "10"], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
-                       text=True, timeout=900)
+    r = subprocess.run([exe, "416", "3", "10", str(tmp_path)], env=env, stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT, text=True, timeout=900)
     tail = "\n".join(l for l in r.stdout.splitlines() if not l.startswith("Model::dtor"))[-2000:]
     print(tail)
     assert r.returncode == 0, f"model_graph failed (SMALL_B200_TENSOR_CORE={tensor_core}):\n{tail}"
+    load = lambda name: np.fromfile(os.path.join(tmp_path, name), dtype=np.float32)
+    want = _tiny_yolov2_model_on_the_oracle(oracle, 416, [load(f"f{l}.bin") for l in range(9)], load("image.bin"))
+    got = load("out.bin")
+    assert got.shape == want.shape
+    err = float(np.abs(got.astype(np.float64) - want).max() / np.abs(want).max())
+    print(f"TinyYoloV2 Model class vs the oracle, SMALL_B200_TENSOR_CORE={tensor_core}: {err:.2e}")
+    assert err <= 1e-4
