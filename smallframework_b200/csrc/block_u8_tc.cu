@@ -26,9 +26,9 @@
 // requantisation is the ReLU; the reference keeps an intermediate buffer per output tile in
 // cache for the same purpose.
 //
-// Roles (320 threads): warps 0..3 stage-1 epilogue (thread = pixel = tensor-memory lane),
+// Roles (384 threads): warps 0..3 stage-1 epilogue (thread = pixel = tensor-memory lane),
 // warps 4..7 stage-2 epilogue, warp 8 bulk-copy producer (and owner of the tensor-memory
-// allocation), warp 9 MMA issuer.  A CTA walks over images n = blockIdx.x, + gridDim.x, ...;
+// allocation), warp 9 MMA issuer of stage 1, warps 10..11 MMA issuers of stage 2.  A CTA walks over images n = blockIdx.x, + gridDim.x, ...;
 // activations, the intermediate and both accumulators are double-buffered, so stage 1 of image
 // j + 1 overlaps the stage-1 epilogue of image j and stage 2 of image j - 1.
 // Requirements (else the layers run as separate kernels): H*W <= 128; filter zero points -128
@@ -40,7 +40,7 @@ namespace
 using namespace sb;
 
 constexpr int BM = 128;            // pixels per image tile = tensor-memory lanes
-constexpr int BLOCK_THREADS = 320;
+constexpr int BLOCK_THREADS = 384;   // 8 epilogue warps, producer, stage-1 issuer, up to two stage-2 issuers
 constexpr int EPI_THREADS = 128;
 
 struct Requant
@@ -71,17 +71,16 @@ struct RoleFlag
     int v;
 };
 
-// 32 accumulators of one pixel (32 consecutive channels) -> 32 output bytes.  The common quantiser
-// takes the seeded form (common.cuh); any other one adds the constants and goes the general way.
-__device__ __forceinline__ void requant32(const uint32_t *r, const int *corr, const long long *seed, const Requant &q,
-                                          uint4 *o2)
+// 16 accumulators of one pixel (one channel block) -> 16 output bytes.  The common quantiser takes
+// the seeded form (common.cuh); any other one adds the constants and goes the general way.
+__device__ __forceinline__ uint4 requant16(const uint32_t *r, const int *corr, const long long *seed, const Requant &q)
 {
     if (requant_is_fast(q.lshift, q.rshift, q.mult))
     {
         const int bit = 1 << (q.rshift - 2), sh1 = q.rshift - 1;
-        uint32_t w[8];
+        uint32_t w[4];
 #pragma unroll
-        for (int e4 = 0; e4 < 8; ++e4)
+        for (int e4 = 0; e4 < 4; ++e4)
         {
             int x[4];
 #pragma unroll
@@ -93,21 +92,13 @@ __device__ __forceinline__ void requant32(const uint32_t *r, const int *corr, co
             }
             w[e4] = pack4_sat(x[0], x[1], x[2], x[3]);
         }
-        o2[0] = make_uint4(w[0], w[1], w[2], w[3]);
-        o2[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        return make_uint4(w[0], w[1], w[2], w[3]);
     }
-    else
-    {
+    int v[16];
 #pragma unroll
-        for (int c2 = 0; c2 < 2; ++c2)
-        {
-            int v[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e)
-                v[e] = (int)r[16 * c2 + e] + corr[16 * c2 + e];
-            o2[c2] = requant_pack16(v, q.lshift, q.rshift, q.mult);
-        }
-    }
+    for (int e = 0; e < 16; ++e)
+        v[e] = (int)r[e] + corr[e];
+    return requant_pack16(v, q.lshift, q.rshift, q.mult);
 }
 
 template <int K, bool STEM, bool POOL, bool SIGNED_IN>
@@ -153,8 +144,8 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
             {
                 mbar_init(&a_full[i], STEM ? EPI_THREADS : 1);
                 mbar_init(&d1_full[i], 1); mbar_init(&d1_free[i], 4);
-                mbar_init(&p_full[i], EPI_THREADS); mbar_init(&p_free[i], POOL ? 4 : 1);
-                mbar_init(&d2_full[i], 1); mbar_init(&d2_free[i], 4);
+                mbar_init(&p_full[i], EPI_THREADS); mbar_init(&p_free[i], POOL ? 4 : K / 32);
+                mbar_init(&d2_full[i], K / 32); mbar_init(&d2_free[i], 4);
             }
             failed1.v = 0; failed2.v = 0;
             fence_barrier_init();
@@ -246,40 +237,28 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
     }
     else if (warp == 9)
     {
-        // ---------------- MMA issuer ----------------
+        // ---------------- MMA issuer, stage 1 ----------------
+        // Issuing one tcgen05.mma costs its thread about 150 cycles whatever the size of the MMA
+        // (measured here: 20 MMAs of an image took one thread 3000 cycles, with every descriptor
+        // precomputed), far longer than these small MMAs occupy the pipe.  So the MMAs of an image
+        // are spread over threads: this one issues stage 1, and each block of 32 depthwise channels
+        // (its own accumulator columns) has an issuing thread of its own in the warps that follow.
         if (lane == 0)
         {
             const uint32_t idesc1 = STEM ? make_idesc(2, SIGNED_IN ? 1u : 0u, 1, 0, 0, BM, K)
                                          : make_idesc(2, 0 /*u8*/, 1 /*s8*/, 0 /*A K-major*/, 1 /*B MN-major*/, BM, K);
-            const uint32_t idesc2 = make_idesc(2, a.mid_signed ? 1u : 0u, 1, 0, 0, BM, 32);
-            const uint32_t sb1 = smem_u32(sB1), sb2 = smem_u32(sB2);
+            const uint32_t a16 = a_stage >> 4;
+            const uint64_t da1_0 = STEM ? make_smem_desc(smem_u32(sA), BM * CB, 8 * CB, 0)
+                                        : make_smem_desc(smem_u32(sA), (uint32_t)(a.HW * CB), 8 * CB, 0);
+            const uint64_t db1_0 = STEM ? make_smem_desc(smem_u32(sB1), K * CB, 8 * CB, 0)
+                                        : make_smem_desc(smem_u32(sB1), 8 * CB, (uint32_t)(cbs * CB * CB), 0);
+            // 32 bytes of K per MMA = two 16-byte chunks of A (first-layer form: 128 rows each; 1x1 form:
+            // channel block cb of the image lies HW pixels after block cb - 1, the image being one
+            // contiguous run -- lanes >= HW read into the next block, their sums are never used)
+            const uint32_t a_step = STEM ? (uint32_t)(2 * BM) : (uint32_t)(2 * a.HW);
+            const uint32_t b_step = STEM ? (uint32_t)(2 * K) : (uint32_t)(2 * CB);
+            const int n1 = STEM ? KCH / 2 : cbs / 2;
             bool ok = true;
-            auto second = [&](int jj) {
-                const int t = jj & 1;
-                ok = mbar_wait(&p_full[t], (jj >> 1) & 1, status, 33);
-                if (ok && jj >= 2)
-                    ok = mbar_wait(&d2_free[t], ((jj >> 1) - 1) & 1, status, 34);
-                if (!ok)
-                    return;
-                tc_fence_after_sync();
-                const uint32_t pbase = smem_u32(sP + (size_t)t * p_stage);
-                for (int c32 = 0; c32 < K / 32; ++c32)
-                {
-                    const uint32_t d = tmem + (uint32_t)(2 * K + t * K + c32 * 32);
-#pragma unroll
-                    for (int tap = 0; tap < TAPS; ++tap)
-                    {
-                        const int kh = tap / 3, kw = tap - 3 * kh;
-                        const uint64_t da = make_smem_desc(pbase + (uint32_t)kw * copy_bytes + (uint32_t)(2 * c32 * a.E * CB) +
-                                                               (uint32_t)(kh * a.W * CB),
-                                                           (uint32_t)(a.E * CB), 8 * CB, 0);
-                        const uint64_t db = make_smem_desc(sb2 + (uint32_t)((tap * (K / 32) + c32) * 1024), 32 * CB, 8 * CB, 0);
-                        tc_mma_i8(d, da, db, idesc2, tap > 0 ? 1u : 0u);
-                    }
-                }
-                tc_commit(&d2_full[t]); // the sums are complete ...
-                tc_commit(&p_free[t]);  // ... and this copy of the intermediate may be overwritten
-            };
             for (int j = 0; j < count && ok; ++j)
             {
                 const int s = j & 1;
@@ -289,34 +268,51 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                 if (!ok)
                     break;
                 tc_fence_after_sync();
-                const uint32_t sa = smem_u32(sA + (size_t)s * a_stage);
                 const uint32_t d1 = tmem + (uint32_t)(s * K);
-                if (STEM)
-                {
-                    for (int i = 0; i < KCH / 2; ++i) // 32 bytes of K per MMA = two 16-byte chunks
-                    {
-                        const uint64_t da = make_smem_desc(sa + i * 2 * BM * CB, BM * CB, 8 * CB, 0);
-                        const uint64_t db = make_smem_desc(sb1 + i * 2 * K * CB, K * CB, 8 * CB, 0);
-                        tc_mma_i8(d1, da, db, idesc1, i > 0 ? 1u : 0u);
-                    }
-                }
-                else
-                {
-                    // channel block cb of the image lies HW pixels after block cb - 1 (the image is one
-                    // contiguous run); lanes >= HW read into the next block: their sums are never used
-                    for (int i = 0; i < cbs / 2; ++i)
-                    {
-                        const uint64_t da = make_smem_desc(sa + (uint32_t)(i * 2 * a.HW * CB), (uint32_t)(a.HW * CB), 8 * CB, 0);
-                        const uint64_t db = make_smem_desc(sb1 + i * 2 * CB * CB, 8 * CB, (uint32_t)(cbs * CB * CB), 0);
-                        tc_mma_i8(d1, da, db, idesc1, i > 0 ? 1u : 0u);
-                    }
-                }
+                const uint64_t da_s = da1_0 + (uint64_t)(s ? a16 : 0u);
+                for (int i = 0; i < n1; ++i)
+                    tc_mma_i8(d1, da_s + (uint64_t)(i * a_step), db1_0 + (uint64_t)(i * b_step), idesc1, i > 0 ? 1u : 0u);
                 tc_commit(&d1_full[s]);
-                if (!POOL && j >= 1)
-                    second(j - 1);
             }
-            if (!POOL && ok && count > 0)
-                second(count - 1);
+        }
+    }
+    else if (warp >= 10)
+    {
+        // ---------------- MMA issuers, stage 2: warp 10 + c32 owns channels 32*c32 .. 32*c32 + 31 ----------------
+        const int c32 = warp - 10;
+        if (!POOL && lane == 0 && c32 < K / 32)
+        {
+            const uint32_t idesc2 = make_idesc(2, a.mid_signed ? 1u : 0u, 1, 0, 0, BM, 32);
+            // all descriptor fields are fixed; an operand position is the base descriptor plus a
+            // precomputed count of 16-byte units
+            const uint64_t db2_0 = make_smem_desc(smem_u32(sB2), 32 * CB, 8 * CB, 0) + (uint64_t)(c32 * 64);
+            const uint64_t da2_0 = make_smem_desc(smem_u32(sP), (uint32_t)(a.E * CB), 8 * CB, 0) + (uint64_t)(c32 * 2 * a.E);
+            const uint32_t copy16 = copy_bytes >> 4, stage16 = p_stage >> 4;
+            uint32_t dA[3][3]; // [kh][kw]: entries of copy kw shifted by kh rows
+#pragma unroll
+            for (int kh = 0; kh < 3; ++kh)
+#pragma unroll
+                for (int kw = 0; kw < 3; ++kw)
+                    dA[kh][kw] = (uint32_t)kw * copy16 + (uint32_t)(kh * a.W);
+            bool ok = true;
+            for (int jj = 0; jj < count && ok; ++jj)
+            {
+                const int t = jj & 1;
+                ok = mbar_wait(&p_full[t], (jj >> 1) & 1, status, 33);
+                if (ok && jj >= 2)
+                    ok = mbar_wait(&d2_free[t], ((jj >> 1) - 1) & 1, status, 34);
+                if (!ok)
+                    break;
+                tc_fence_after_sync();
+                const uint64_t da_t = da2_0 + (uint64_t)(t ? stage16 : 0u);
+                const uint32_t d = tmem + (uint32_t)(2 * K + t * K + c32 * 32);
+#pragma unroll
+                for (int tap = 0; tap < TAPS; ++tap)
+                    tc_mma_i8(d, da_t + (uint64_t)dA[tap / 3][tap % 3], db2_0 + (uint64_t)(tap * (K / 32) * 64), idesc2,
+                              tap > 0 ? 1u : 0u);
+                tc_commit(&d2_full[t]); // this block's sums are complete ...
+                tc_commit(&p_free[t]);  // ... and its reads of the intermediate are done
+            }
         }
     }
     else if (warp < 4)
@@ -392,31 +388,32 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
             tc_fence_after_sync();
             // this pixel in the copy for kw = 1 (entry q + W); the DW form keeps it between the other two
             uint8_t *pc = sP + (size_t)s * p_stage + (POOL ? 0u : copy_bytes) + (size_t)(q + a.W) * CB;
-#pragma unroll 1
-            for (int h = 0; h < K / 32; ++h) // 32 channels per tensor-memory load
-            {
-                uint32_t r[32];
-                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(s * K + h * 32), r);
-                tmem_ld_wait();
-                uint4 o2[2];
-                requant32(r, corr1 + h * 32, seed1 + h * 32, a.q1, o2);
+            // the load of channel block cb + 1 is in flight while block cb is requantised
+            uint32_t ra[16], rb[16];
+            const uint32_t d1 = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(s * K);
+            tmem_ld16(d1, ra);
+            tmem_ld_wait();
 #pragma unroll
-                for (int c2 = 0; c2 < 2; ++c2)
+            for (int cb = 0; cb < KB; ++cb)
+            {
+                uint32_t *cur = (cb & 1) ? rb : ra, *nxt = (cb & 1) ? ra : rb;
+                if (cb + 1 < KB)
+                    tmem_ld16(d1 + (uint32_t)((cb + 1) * CB), nxt);
+                uint4 o = requant16(cur, corr1 + cb * CB, seed1 + cb * CB, a.q1);
+                o.x ^= sx; o.y ^= sx; o.z ^= sx; o.w ^= sx;
+                if (q < a.HW)
                 {
-                    uint4 o = o2[c2];
-                    o.x ^= sx; o.y ^= sx; o.z ^= sx; o.w ^= sx;
-                    if (q < a.HW)
+                    uint8_t *p1 = pc + (size_t)cb * a.E * CB;
+                    *reinterpret_cast<uint4 *>(p1) = o;
+                    if (!POOL)
                     {
-                        uint8_t *p1 = pc + (size_t)(2 * h + c2) * a.E * CB;
-                        *reinterpret_cast<uint4 *>(p1) = o;
-                        if (!POOL)
-                        {
-                            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-                            *reinterpret_cast<uint4 *>(p1 - copy_bytes + CB) = wraps_left ? z : o;   // copy kw = 0, entry q + W + 1
-                            *reinterpret_cast<uint4 *>(p1 + copy_bytes - CB) = wraps_right ? z : o;  // copy kw = 2, entry q + W - 1
-                        }
+                        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                        *reinterpret_cast<uint4 *>(p1 - copy_bytes + CB) = wraps_left ? z : o;   // copy kw = 0, entry q + W + 1
+                        *reinterpret_cast<uint4 *>(p1 + copy_bytes - CB) = wraps_right ? z : o;  // copy kw = 2, entry q + W - 1
                     }
                 }
+                if (cb + 1 < KB)
+                    tmem_ld_wait();
             }
             tc_fence_before_sync();
             fence_proxy_async();
@@ -441,19 +438,21 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                     break;
                 tc_fence_after_sync();
                 uint8_t *o = out + ((size_t)(first + j * step) * KB * a.HW + p) * CB;
-#pragma unroll 1
-                for (int h = 0; h < K / 32; ++h)
+                uint32_t ra[16], rb[16];
+                const uint32_t d2 = tmem + ((uint32_t)(w4 * 32) << 16) + (uint32_t)(2 * K + t * K);
+                tmem_ld16(d2, ra);
+                tmem_ld_wait();
+#pragma unroll
+                for (int cb = 0; cb < KB; ++cb)
                 {
-                    uint32_t r[32];
-                    tmem_ld32(tmem + ((uint32_t)(w4 * 32) << 16) + (uint32_t)(2 * K + t * K + h * 32), r);
-                    tmem_ld_wait();
-                    uint4 o2[2];
-                    requant32(r, corr2 + h * 32, seed2 + h * 32, a.q2, o2);
+                    uint32_t *cur = (cb & 1) ? rb : ra, *nxt = (cb & 1) ? ra : rb;
+                    if (cb + 1 < KB)
+                        tmem_ld16(d2 + (uint32_t)((cb + 1) * CB), nxt);
+                    const uint4 ov = requant16(cur, corr2 + cb * CB, seed2 + cb * CB, a.q2);
                     if (p < a.HW)
-                    {
-                        *reinterpret_cast<uint4 *>(o + (size_t)(2 * h) * a.HW * CB) = o2[0];
-                        *reinterpret_cast<uint4 *>(o + (size_t)(2 * h + 1) * a.HW * CB) = o2[1];
-                    }
+                        *reinterpret_cast<uint4 *>(o + (size_t)cb * a.HW * CB) = ov;
+                    if (cb + 1 < KB)
+                        tmem_ld_wait();
                 }
                 tc_fence_before_sync();
                 __syncwarp();
