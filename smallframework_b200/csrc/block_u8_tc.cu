@@ -26,9 +26,9 @@
 // requantisation is the ReLU; the reference keeps an intermediate buffer per output tile in
 // cache for the same purpose.
 //
-// Roles (384 threads): warps 0..3 stage-1 epilogue (thread = pixel = tensor-memory lane),
-// warps 4..7 stage-2 epilogue, warp 8 bulk-copy producer (and owner of the tensor-memory
-// allocation), warp 9 MMA issuer of stage 1, warps 10..11 MMA issuers of stage 2.  A CTA walks over images n = blockIdx.x, + gridDim.x, ...;
+// Roles: EW (8) warps stage-1 epilogue (thread = pixel = tensor-memory lane, the channel blocks split
+// between the two warps of a lane quarter), EW warps stage-2 epilogue, then the bulk-copy producer
+// (and owner of the tensor-memory allocation), the MMA issuer of stage 1 and the MMA issuers of stage 2.  A CTA walks over images n = blockIdx.x, + gridDim.x, ...;
 // activations, the intermediate and both accumulators are double-buffered, so stage 1 of image
 // j + 1 overlaps the stage-1 epilogue of image j and stage 2 of image j - 1.
 // Requirements (else the layers run as separate kernels): H*W <= 128; filter zero points -128
@@ -40,8 +40,8 @@ namespace
 using namespace sb;
 
 constexpr int BM = 128;            // pixels per image tile = tensor-memory lanes
-constexpr int BLOCK_THREADS = 384;   // 8 epilogue warps, producer, stage-1 issuer, up to two stage-2 issuers
-constexpr int EPI_THREADS = 128;
+// Warps: EW epilogue warps per stage, then the producer, the stage-1 issuer and up to two stage-2 issuers.
+__host__ __device__ constexpr int block_threads(int EW) { return (2 * EW + 4) * 32; }
 
 struct Requant
 {
@@ -101,8 +101,19 @@ __device__ __forceinline__ uint4 requant16(const uint32_t *r, const int *corr, c
     return requant_pack16(v, q.lshift, q.rshift, q.mult);
 }
 
-template <int K, bool STEM, bool POOL, bool SIGNED_IN>
-__global__ void __launch_bounds__(BLOCK_THREADS, 2)
+__device__ __forceinline__ int dp4a_u8_s8(unsigned a, unsigned b, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// EW: epilogue warps per stage, 4 or 8.  A warp covers the 32 pixels of tensor-memory lane quarter
+// (warp % 4); with 8 warps the channel blocks of an image are split between the two warps of a quarter.
+// The epilogues are long chains of dependent integer instructions: what keeps the SM's schedulers busy
+// is the number of such warps in flight, so the default is 8 per stage and two CTAs per SM.
+template <int K, bool STEM, bool POOL, bool SIGNED_IN, int EW>
+__global__ void __launch_bounds__(block_threads(EW), 2)
 block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint8_t *__restrict__ filt1,
                    const int32_t *__restrict__ bias1, const uint8_t *__restrict__ filt2,
                    const int32_t *__restrict__ bias2, uint8_t *__restrict__ out, int *status)
@@ -111,12 +122,22 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
     constexpr int KCH = 4;                           // first-layer form: 16-byte chunks of the im2col K = 64
     constexpr uint32_t TMEM_COLS = POOL ? (2 * K < 32 ? 32 : 2 * K) : 4 * K;
     constexpr int TAPS = 9;
+    constexpr int BLOCK_THREADS = block_threads(EW), EPI_THREADS = EW * 32;
+    constexpr int PARTS = EW / 4;                    // warps per lane quarter
+    constexpr int CBW = KB / PARTS;                  // channel blocks per epilogue warp
+    constexpr int W_PROD = 2 * EW, W_ISS1 = 2 * EW + 1, W_ISS2 = 2 * EW + 2;
+    constexpr int PPARTS = EW / KB;                  // POOL: warps that share the pixels of a channel block
+    constexpr int DPITCH = K + 4;                    // POOL: bytes per row of the dense filter in shared memory
+    static_assert(KB % PARTS == 0 && EW % KB == 0, "epilogue warps must divide the channel blocks");
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t a_full[2], d1_full[2], d1_free[2], p_full[2], p_free[2], d2_full[2], d2_free[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ __align__(16) int corr1[K], corr2[K];         // per-channel constants added to every accumulator
     __shared__ __align__(16) long long seed1[K], seed2[K];  // the same as seeds of the wide multiply (common.cuh)
     __shared__ __align__(16) uint8_t pooled[2][K];
+    __shared__ int pool_part[POOL ? PPARTS : 1][K];          // POOL: partial channel sums
+    __shared__ __align__(16) uint8_t dense_w[POOL ? 128 * DPITCH : 16]; // POOL: dense filter [k][c] as signed bytes
+    __shared__ int dense_c[POOL ? 128 : 1];                  // POOL: per-output constant of the dense layer
     __shared__ RoleFlag failed1, failed2;
 
     const int cbs = a.C / CB;
@@ -136,16 +157,16 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
     const int first = blockIdx.x, step = gridDim.x;
     const int count = first < a.N ? (a.N - first + step - 1) / step : 0;
 
-    if (warp == 8)
+    if (warp == W_PROD)
     {
         if (lane == 0)
         {
             for (int i = 0; i < 2; ++i)
             {
                 mbar_init(&a_full[i], STEM ? EPI_THREADS : 1);
-                mbar_init(&d1_full[i], 1); mbar_init(&d1_free[i], 4);
-                mbar_init(&p_full[i], EPI_THREADS); mbar_init(&p_free[i], POOL ? 4 : K / 32);
-                mbar_init(&d2_full[i], K / 32); mbar_init(&d2_free[i], 4);
+                mbar_init(&d1_full[i], 1); mbar_init(&d1_free[i], EW);
+                mbar_init(&p_full[i], EPI_THREADS); mbar_init(&p_free[i], POOL ? EW : K / 32);
+                mbar_init(&d2_full[i], K / 32); mbar_init(&d2_free[i], EW);
             }
             failed1.v = 0; failed2.v = 0;
             fence_barrier_init();
@@ -210,13 +231,31 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
         corr2[tid] = c2;
         seed2[tid] = requant_seed(c2, a.q2.mult);
     }
+    if (POOL)
+    {
+        // dense filter [Kd/16][K/16][16 c][16 k] -> rows [k][c] of signed bytes (w - 128), and per output
+        // k_zero + bias + zero_in * sum_c (w - 128)
+        for (int i = tid; i < a.Kd * K; i += BLOCK_THREADS)
+        {
+            const int c = i % K, k = i / K;
+            dense_w[k * DPITCH + c] = filt2[((size_t)(k / CB) * KB + c / CB) * CB * CB + (c % CB) * CB + (k % CB)] ^ 0x80u;
+        }
+        __syncthreads();
+        if (tid < a.Kd)
+        {
+            int wsum = 0;
+            for (int c = 0; c < K; ++c)
+                wsum += (int)(int8_t)dense_w[tid * DPITCH + c];
+            dense_c[tid] = a.qd.k_zero + (bias2 ? bias2[tid] : 0) + a.zero_in_d * wsum;
+        }
+    }
     fence_proxy_async();
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = tmem_base_s;
 
-    if (warp == 8)
+    if (warp == W_PROD)
     {
         // ---------------- producer (1x1 form): one bulk copy per image ----------------
         if (!STEM && lane == 0)
@@ -235,7 +274,7 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
             }
         }
     }
-    else if (warp == 9)
+    else if (warp == W_ISS1)
     {
         // ---------------- MMA issuer, stage 1 ----------------
         // Issuing one tcgen05.mma costs its thread about 150 cycles whatever the size of the MMA
@@ -276,10 +315,10 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
             }
         }
     }
-    else if (warp >= 10)
+    else if (warp >= W_ISS2)
     {
-        // ---------------- MMA issuers, stage 2: warp 10 + c32 owns channels 32*c32 .. 32*c32 + 31 ----------------
-        const int c32 = warp - 10;
+        // ---------------- MMA issuers, stage 2: each owns channels 32*c32 .. 32*c32 + 31 ----------------
+        const int c32 = warp - W_ISS2;
         if (!POOL && lane == 0 && c32 < K / 32)
         {
             const uint32_t idesc2 = make_idesc(2, a.mid_signed ? 1u : 0u, 1, 0, 0, BM, 32);
@@ -315,10 +354,12 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
             }
         }
     }
-    else if (warp < 4)
+    else if (warp < EW)
     {
         // ---------------- stage-1 epilogue: requantise into the shifted copies ----------------
-        const int q = tid;                         // this thread's pixel = tensor-memory lane
+        const int quarter = warp & 3, part = warp >> 2;
+        const int q = quarter * 32 + lane;         // this thread's pixel = tensor-memory lane
+        const int cb0 = part * CBW;                // its channel blocks: cb0 .. cb0 + CBW - 1
         const int cq = q % a.W;
         const bool wraps_left = cq == a.W - 1;     // copy kw = 0 must not show this pixel to the next row
         const bool wraps_right = cq == 0;          // copy kw = 2 must not show it to the previous row
@@ -335,12 +376,12 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                 const uint8_t v = src[i];
                 img[(h + a.pad_t) * a.pitch + (w + a.pad_l)] = SIGNED_IN ? (uint8_t)(v ^ 0x80u) : v;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
             if (q < a.HW)
             {
                 const uint8_t *row = img + (oh * a.stride) * a.pitch + ow * a.stride;
                 uint8_t *arow = sA + (size_t)s * a_stage + (size_t)q * CB;
-                for (int j4 = 0; j4 * 4 < a.Fh; ++j4)
+                for (int j4 = part; j4 * 4 < a.Fh; j4 += PARTS) // the warps of a quarter share the pixel's chunks
                 {
                     unsigned wv[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
@@ -372,7 +413,7 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                 // everyone is done with the padded copy of image j - 1 (and agrees on whether to go on)
                 if (!ok)
                     *reinterpret_cast<volatile int *>(&failed1.v) = 1;
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                 if (*reinterpret_cast<volatile int *>(&failed1.v))
                     break;
                 if (j + 1 < count)
@@ -390,15 +431,16 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
             uint8_t *pc = sP + (size_t)s * p_stage + (POOL ? 0u : copy_bytes) + (size_t)(q + a.W) * CB;
             // the load of channel block cb + 1 is in flight while block cb is requantised
             uint32_t ra[16], rb[16];
-            const uint32_t d1 = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(s * K);
+            const uint32_t d1 = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(s * K + cb0 * CB);
             tmem_ld16(d1, ra);
             tmem_ld_wait();
 #pragma unroll
-            for (int cb = 0; cb < KB; ++cb)
+            for (int i = 0; i < CBW; ++i)
             {
-                uint32_t *cur = (cb & 1) ? rb : ra, *nxt = (cb & 1) ? ra : rb;
-                if (cb + 1 < KB)
-                    tmem_ld16(d1 + (uint32_t)((cb + 1) * CB), nxt);
+                uint32_t *cur = (i & 1) ? rb : ra, *nxt = (i & 1) ? ra : rb;
+                const int cb = cb0 + i;
+                if (i + 1 < CBW)
+                    tmem_ld16(d1 + (uint32_t)((i + 1) * CB), nxt);
                 uint4 o = requant16(cur, corr1 + cb * CB, seed1 + cb * CB, a.q1);
                 o.x ^= sx; o.y ^= sx; o.z ^= sx; o.w ^= sx;
                 if (q < a.HW)
@@ -412,7 +454,7 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                         *reinterpret_cast<uint4 *>(p1 + copy_bytes - CB) = wraps_right ? z : o;  // copy kw = 2, entry q + W - 1
                     }
                 }
-                if (cb + 1 < KB)
+                if (i + 1 < CBW)
                     tmem_ld_wait();
             }
             tc_fence_before_sync();
@@ -426,7 +468,9 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
     else
     {
         // ---------------- stage-2 epilogue ----------------
-        const int p = tid - EPI_THREADS, w4 = warp - 4;
+        const int w2 = warp - EW, quarter = w2 & 3, part = w2 >> 2;
+        const int p = quarter * 32 + lane, cb0 = part * CBW;
+        const int rt = tid - EPI_THREADS; // thread index inside this role
         bool ok = true;
         if (!POOL)
         {
@@ -439,19 +483,20 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                 tc_fence_after_sync();
                 uint8_t *o = out + ((size_t)(first + j * step) * KB * a.HW + p) * CB;
                 uint32_t ra[16], rb[16];
-                const uint32_t d2 = tmem + ((uint32_t)(w4 * 32) << 16) + (uint32_t)(2 * K + t * K);
+                const uint32_t d2 = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(2 * K + t * K + cb0 * CB);
                 tmem_ld16(d2, ra);
                 tmem_ld_wait();
 #pragma unroll
-                for (int cb = 0; cb < KB; ++cb)
+                for (int i = 0; i < CBW; ++i)
                 {
-                    uint32_t *cur = (cb & 1) ? rb : ra, *nxt = (cb & 1) ? ra : rb;
-                    if (cb + 1 < KB)
-                        tmem_ld16(d2 + (uint32_t)((cb + 1) * CB), nxt);
+                    uint32_t *cur = (i & 1) ? rb : ra, *nxt = (i & 1) ? ra : rb;
+                    const int cb = cb0 + i;
+                    if (i + 1 < CBW)
+                        tmem_ld16(d2 + (uint32_t)((i + 1) * CB), nxt);
                     const uint4 ov = requant16(cur, corr2 + cb * CB, seed2 + cb * CB, a.q2);
                     if (p < a.HW)
                         *reinterpret_cast<uint4 *>(o + (size_t)cb * a.HW * CB) = ov;
-                    if (cb + 1 < KB)
+                    if (i + 1 < CBW)
                         tmem_ld_wait();
                 }
                 tc_fence_before_sync();
@@ -462,6 +507,11 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
         }
         else
         {
+            // Warp w2 sums channel block w2 % KB over every PPARTS-th group of 32 pixels.  A lane owns one
+            // 32-bit word (four channels) of eight-pixel-strided pixels, so a warp reads 128 contiguous
+            // bytes at a time; the eight lanes that share a word add up by three shuffles.
+            const int cbp = w2 % KB, ppart = w2 / KB;
+            const int quad = lane & 3, pg = lane >> 2;
             for (int j = 0; j < count; ++j)
             {
                 const int t = j & 1;
@@ -469,59 +519,52 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                     ok = mbar_wait(&p_full[t], (j >> 1) & 1, status, 39);
                 if (ok)
                 {
-                    // channel sums of the intermediate: warp w4 takes channel blocks w4, w4 + 4, ...
-                    for (int cb = w4; cb < KB; cb += 4)
+                    unsigned s4[4] = {0u, 0u, 0u, 0u};
+                    const uint8_t *col = sP + (size_t)t * p_stage + ((size_t)cbp * a.E + a.W) * CB + quad * 4;
+                    for (int px = ppart * 8 + pg; px < a.HW; px += PPARTS * 8)
                     {
-                        unsigned s16[16];
-#pragma unroll
-                        for (int e = 0; e < 16; ++e)
-                            s16[e] = 0u;
-                        const uint8_t *col = sP + (size_t)t * p_stage + ((size_t)cb * a.E + a.W) * CB;
-                        for (int px = lane; px < a.HW; px += 32)
-                        {
-                            const uint4 v = *reinterpret_cast<const uint4 *>(col + (size_t)px * CB);
-                            const unsigned wv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                            for (int k4 = 0; k4 < 4; ++k4)
-                            {
-                                s16[4 * k4 + 0] = __dp4a(wv[k4], 0x00000001u, s16[4 * k4 + 0]);
-                                s16[4 * k4 + 1] = __dp4a(wv[k4], 0x00000100u, s16[4 * k4 + 1]);
-                                s16[4 * k4 + 2] = __dp4a(wv[k4], 0x00010000u, s16[4 * k4 + 2]);
-                                s16[4 * k4 + 3] = __dp4a(wv[k4], 0x01000000u, s16[4 * k4 + 3]);
-                            }
-                        }
-#pragma unroll
-                        for (int e = 0; e < 16; ++e)
-#pragma unroll
-                            for (int m = 16; m >= 1; m >>= 1)
-                                s16[e] += __shfl_xor_sync(0xffffffffu, s16[e], m);
-                        if (lane == 0)
-                        {
-                            int v[16];
-#pragma unroll
-                            for (int e = 0; e < 16; ++e) // k_zero + sum over the window of (a + zero point)
-                                v[e] = a.q2.k_zero + (int)s16[e] + a.HW * a.zero_pool;
-                            *reinterpret_cast<uint4 *>(&pooled[t][cb * CB]) =
-                                requant_pack16(v, a.q2.lshift, a.q2.rshift, a.q2.mult);
-                        }
+                        const unsigned wv = *reinterpret_cast<const unsigned *>(col + (size_t)px * CB);
+                        s4[0] = __dp4a(wv, 0x00000001u, s4[0]);
+                        s4[1] = __dp4a(wv, 0x00000100u, s4[1]);
+                        s4[2] = __dp4a(wv, 0x00010000u, s4[2]);
+                        s4[3] = __dp4a(wv, 0x01000000u, s4[3]);
                     }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+#pragma unroll
+                        for (int m = 16; m >= 4; m >>= 1)
+                            s4[e] += __shfl_xor_sync(0xffffffffu, s4[e], m);
+                    if (lane < 4)
+                        *reinterpret_cast<int4 *>(&pool_part[ppart][cbp * CB + quad * 4]) =
+                            make_int4((int)s4[0], (int)s4[1], (int)s4[2], (int)s4[3]);
                     __syncwarp();
                     if (lane == 0)
-                        mbar_arrive(&p_free[t]);
+                        mbar_arrive(&p_free[t]); // this warp's reads of the intermediate are done
                 }
                 if (!ok)
                     *reinterpret_cast<volatile int *>(&failed2.v) = 1;
-                asm volatile("bar.sync 2, 128;" ::: "memory");
+                asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
                 if (*reinterpret_cast<volatile int *>(&failed2.v))
                     break;
-                // dense layer on the pooled vector: filter [Kd/16][K/16][16 c][16 k]
-                if (p < a.Kd)
+                if (rt < K)
                 {
-                    int acc = a.qd.k_zero + (bias2 ? bias2[p] : 0);
-                    const uint8_t *wcol = filt2 + (size_t)(p / CB) * KB * CB * CB + (p % CB);
-                    for (int c = 0; c < K; ++c)
-                        acc += ((int)pooled[t][c] + a.zero_in_d) * ((int)__ldg(wcol + (size_t)c * CB) + a.zero_filt_d);
-                    out[(size_t)(first + j * step) * a.Kd + p] =
+                    int v = a.q2.k_zero + a.HW * a.zero_pool; // k_zero + sum over the window of (a + zero point)
+#pragma unroll
+                    for (int pp = 0; pp < PPARTS; ++pp)
+                        v += pool_part[pp][rt];
+                    pooled[t][rt] = (uint8_t)requant_dev(v, a.q2.lshift, a.q2.rshift, a.q2.mult);
+                }
+                asm volatile("bar.sync 2, %0;" ::"n"(EPI_THREADS) : "memory");
+                // dense layer on the pooled vector: four channels per dp4a (unsigned activations, signed weights)
+                if (rt < a.Kd)
+                {
+                    int acc = dense_c[rt];
+                    const unsigned *wrow = reinterpret_cast<const unsigned *>(dense_w + rt * DPITCH);
+                    const unsigned *pv = reinterpret_cast<const unsigned *>(pooled[t]);
+#pragma unroll
+                    for (int c4 = 0; c4 < K / 4; ++c4)
+                        acc = dp4a_u8_s8(pv[c4], wrow[c4], acc);
+                    out[(size_t)(first + j * step) * a.Kd + rt] =
                         (uint8_t)requant_dev(acc, a.qd.lshift, a.qd.rshift, a.qd.mult);
                 }
             }
@@ -529,7 +572,7 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 8)
+    if (warp == W_PROD)
         tmem_dealloc(tmem, TMEM_COLS);
 }
 
@@ -579,11 +622,11 @@ size_t smem_need(const BlockArgs &a, int K, bool stem, bool pool)
     return 2 * a_stage + b1 + b2 + 2 * p_stage + ((img + 15) & ~(size_t)15) + 64;
 }
 
-template <int K, bool STEM, bool POOL, bool SIGNED_IN>
+template <int K, bool STEM, bool POOL, bool SIGNED_IN, int EW = 8>
 int launch_block(const BlockArgs &a, size_t smem, const uint8_t *in, const uint8_t *f1, const int32_t *b1, const uint8_t *f2,
                  const int32_t *b2, uint8_t *out, cudaStream_t st)
 {
-    auto kern = block_u8_tc_kernel<K, STEM, POOL, SIGNED_IN>;
+    auto kern = block_u8_tc_kernel<K, STEM, POOL, SIGNED_IN, EW>;
     static PerDeviceOnce configured;
     int dev;
     if (configured.needed(&dev))
@@ -598,11 +641,13 @@ int launch_block(const BlockArgs &a, size_t smem, const uint8_t *in, const uint8
     int per_sm = 512 / (POOL ? (2 * K < 32 ? 32 : 2 * K) : 4 * K);
     const int by_smem = (int)((224 * 1024) / (smem + 4096));
     if (per_sm > by_smem) per_sm = by_smem;
-    if (per_sm > 4) per_sm = 4;
+    const int by_threads = 2048 / block_threads(EW); // and the register file: 48 registers per thread at EW = 8
+    if (per_sm > by_threads) per_sm = by_threads;
+    if (per_sm > (EW == 8 ? 2 : 4)) per_sm = (EW == 8 ? 2 : 4);
     if (per_sm < 1) per_sm = 1;
     long long grid = (long long)num_sms() * per_sm;
     if (grid > a.N) grid = a.N;
-    kern<<<(unsigned)grid, BLOCK_THREADS, smem, st>>>(a, in, f1, b1, f2, b2, out, status);
+    kern<<<(unsigned)grid, block_threads(EW), smem, st>>>(a, in, f1, b1, f2, b2, out, status);
     return launched("block_u8_tc_kernel");
 }
 
@@ -648,7 +693,7 @@ bool plan_pool(const small_b200_layer *c, const small_b200_layer *pl, const smal
         return false;
     if (dn->C != c->K || dn->H != 1 || dn->W != 1 || dn->Fh != 1 || dn->Fw != 1 || dn->stride != 1 || dn->pad_t ||
         dn->pad_b || dn->pad_l || dn->pad_r || dn->K % CB != 0 || dn->K <= 0 || dn->K > 128 || dn->N != c->N ||
-        dn->accumulate || !quant_ok(dn))
+        dn->accumulate || !quant_ok(dn) || dn->zero_filt != -128)
         return false;
     a.mid_signed = 0;
     a.zero_pool = pl->zero_in;
