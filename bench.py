@@ -8,7 +8,12 @@ A step is one pass of the layer chain over one batch of seeded synthetic inputs
 (Tiny-YOLOv2 fp32: 64 images of 3x416x416 per GPU, i.e. the 512-image batch of the
 configuration sharded over 8 GPUs; DS-CNN uint8: 4096 images of 1x49x10 per GPU).  Images
 are independent, so ranks share nothing on the data path (weak scaling, no collective).
-Prints ONE JSON line on rank 0.
+Prints ONE JSON line on rank 0.  Without --workload the line is the Tiny-YOLOv2 measurement and
+carries the DS-CNN measurement (same fields) under "workloads".
+
+The K steps of --steps are timed as one round between two barriers; rounds are repeated until at
+least a second has been timed, and the median round is what the line reports (the fastest one is
+there too), with the SM clock sampled over the whole span.
 """
 from __future__ import annotations
 
@@ -40,6 +45,19 @@ WORKLOADS = {
                          desc="MobileNet-v1 x0.25 uint8 3x96x96, batch 2048 per GPU"),
 }
 METRIC = "inferences/s"
+
+
+def config_of(workload, batch, world):
+    """The `config` object of a JSON line: the same for the GPU arm and the reference arm."""
+    wl = WORKLOADS[workload]
+    small = wl["dtype"] == "u8"
+    return {"workload": wl["desc"], "per_gpu_batch": batch, "global_batch": batch * world,
+            "l2": ("the network input rotates over more batches than the 126 MB L2 holds; the activations "
+                   "between the layers of a step (32 MB per layer at batch 4096) are produced and consumed "
+                   "inside L2 by design, so per-layer figures of this workload are L2 figures"
+                   if small else
+                   "per-step input (133 MB) and every activation exceed the 126 MB L2; no flush needed"),
+            "graph": "whole network captured in one CUDA graph per GPU"}
 
 
 def load_peaks():
@@ -201,62 +219,94 @@ def time_reference(workload, layers, threads, budget_s=12.0, max_images=4096):
                        + ("" if dtype == "f32" else " (convolution layers only: stem + 4 x (dw, pw))"))
 
 
-def run_reference_arm(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    layers = make_layers(args.workload)
+def reference_line(args, workload):
+    """The reference's own CPU implementation of one workload on this host's cores, as a JSON line."""
+    layers = make_layers(workload)
     threads = os.cpu_count() or 1
     per = []
     for _ in range(max(args.warmup, 0) + max(args.steps, 1)):
-        per.append(time_reference(args.workload, layers, threads,
-                                  budget_s=max(2.0, 60.0 / (args.steps + args.warmup))))
+        per.append(time_reference(workload, layers, threads,
+                                  budget_s=max(2.0, 40.0 / (args.steps + args.warmup))))
     timed = per[max(args.warmup, 0):]
     v = float(np.mean([p["value"] for p in timed]))
-    wl = WORKLOADS[args.workload]
-    line = {
+    wl = WORKLOADS[workload]
+    return {
         "impl": "reference", "metric": METRIC, "value": v, "unit": METRIC, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / v if v else None,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"],
         "data": "synthetic (seeded), random-init weights",
-        "config": {"workload": wl["desc"], "per_gpu_batch": wl["per_gpu_batch"]},
+        "config": config_of(workload, args.batch or wl["per_gpu_batch"], max(args.gpus, 1)),
         "cpu_baseline": dict(timed[-1], value=v),
         "e2e": {"value": v, "unit": METRIC, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    line = reference_line(args, args.workload or "tinyyolov2")
+    if not args.workload:
+        line["workloads"] = {"dscnn": reference_line(args, "dscnn")}
     print(json.dumps(line), flush=True)
 
 
 # ------------------------------------------------------------------------- GPU arm
-def run_gpu_arm(args):
-    import torch
-    import torch.distributed as dist
+def measured_pipes(torch):
+    """tera-ops/s of the fp32 FMA pipe and of the tf32 / i8 tensor pipes of this GPU, from the
+    library's resident-operand probes (small_b200_peak_probe), next to what the nominal ratios to the
+    measured bf16 GEMM would give."""
+    from smallframework_b200 import _lib
+    peaks = load_peaks()
+    out = {}
+    for kind, name in ((0, "ffma"), (1, "tf32"), (2, "i8")):
+        v = C.c_double(0.0)
+        _lib.check(_lib.lib().small_b200_peak_probe(kind, C.byref(v)))
+        out[name] = v.value
+    torch.cuda.synchronize()
+    out["assumed"] = {"tf32": peaks["tensor_burst"] / 2.0, "i8": peaks["tensor_burst"] * 2.0}
+    out["how"] = "resident-operand issue loops: FFMA chains in registers; tcgen05.mma M128 N256 from shared memory, 2 issuing threads per SM"
+    return out
 
+
+def h2d_bandwidth(l, check, dst_ptr, host_ptr, nbytes, stream, torch):
+    """Upload alone: pinned host memory -> device, GB/s, per rank."""
+    reps = max(3, int(2e8 // max(nbytes, 1)))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    check(l.small_b200_memcpy_h2d(dst_ptr, host_ptr, nbytes, stream.cuda_stream))
+    e0.record(stream)
+    for _ in range(reps):
+        check(l.small_b200_memcpy_h2d(dst_ptr, host_ptr, nbytes, stream.cuda_stream))
+    e1.record(stream)
+    stream.synchronize()
+    return nbytes * reps / (e0.elapsed_time(e1) * 1e-3) / 1e9
+
+
+def measure_workload(args, workload, env, pipes):
+    """One workload on this rank's GPU: resident rounds, end-to-end rounds, per-layer report."""
+    torch, dist, world, rank, local = env
     from smallframework_b200 import _lib, networks, sharding
     from smallframework_b200._lib import check, lib
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    wl = WORKLOADS[args.workload]
+    wl = WORKLOADS[workload]
     batch = args.batch or wl["per_gpu_batch"]
-    layers = make_layers(args.workload)
+    layers = make_layers(workload)
     chain = networks.Chain(layers, batch, wl["dtype"])
     l = lib()
     st = chain.stream.cuda_stream
 
     # host side: pinned input / output staging through the C ABI
-    xp = make_input(args.workload, layers, batch, wl["seed"] + rank)
+    xp = make_input(workload, layers, batch, wl["seed"] + rank)
     in_bytes = xp.nbytes
     hin, hout = C.c_void_p(), C.c_void_p()
     check(l.small_b200_malloc_host(in_bytes, C.byref(hin)))
     C.memmove(hin, xp.ctypes.data, in_bytes)
     check(l.small_b200_memcpy_h2d(chain.x.data_ptr(), hin, in_bytes, st))
-    chain.capture()
+    chain.stream.synchronize()
+    # resident leg: the input rotates over copies of the batch that together exceed L2 (a network whose
+    # whole input is a few MB would otherwise be timed on an L2-resident input)
+    copies = 1 if in_bytes > 160e6 / 2 else int(min(96, -(-160e6 // in_bytes)))
+    inputs = [chain.x] + [chain.x.clone() for _ in range(copies - 1)]
+    chain.capture(inputs)
     out_bytes = chain.y.numel() * chain.y.element_size()
     check(l.small_b200_malloc_host(out_bytes, C.byref(hout)))
     chain.stream.synchronize()
@@ -267,7 +317,8 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed_round(fn, steps):
+        """exactly `steps` steps between two barriers; device time, max over ranks"""
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record(chain.stream)
@@ -278,8 +329,21 @@ def run_gpu_arm(args):
         barrier()
         return sharding.max_over_ranks(e0.elapsed_time(e1), device="cuda")
 
+    def timed(fn, steps, budget_s):
+        first = timed_round(fn, steps)
+        rounds = int(min(400, max(1, budget_s * 1e3 / max(first, 1e-3))))
+        if world > 1:  # every rank must run the same number of rounds
+            t = torch.tensor([rounds], device="cuda")
+            dist.broadcast(t, 0)
+            rounds = int(t.item())
+        ms = [first] + [timed_round(fn, steps) for _ in range(rounds - 1)]
+        return float(np.median(ms)), float(np.min(ms)), len(ms), float(np.sum(ms))
+
+    step_no = [0]
+
     def step_resident():
-        chain.launch()
+        chain.launch(step_no[0])
+        step_no[0] += 1
 
     # End to end: every step copies its batch from pinned host memory and reads its result
     # back.  The upload of step i+1 runs on a second stream while step i computes (two staging
@@ -300,52 +364,103 @@ def run_gpu_arm(args):
         chain.stream.wait_event(ev_up[i])
         check(l.small_b200_memcpy_d2d(chain.x.data_ptr(), staging[i].data_ptr(), in_bytes, st))
         ev_free[i].record(chain.stream)
-        chain.launch()
+        chain.launch(0)
         check(l.small_b200_memcpy_d2h(hout, chain.y.data_ptr(), out_bytes, st))
 
     for _ in range(max(args.warmup, 3)):
         step_resident()
-    n_before = _lib.launch_count()
+    budget = args.min_seconds
     with ClockSampler(local) as clk:
-        ms = timed(step_resident, args.steps)
+        ms, ms_min, rounds, span_ms = timed(step_resident, args.steps, budget)
         for _ in range(2):
             step_e2e()
-        ms_e2e = timed(step_e2e, args.steps)
-    total_images = batch * world * args.steps
-    value = total_images / (ms * 1e-3)
-    e2e_value = total_images / (ms_e2e * 1e-3)
-    clocks = clk.summary()
-
-    line = {
-        "metric": METRIC, "value": value, "unit": METRIC, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"],
-        "data": "synthetic (seeded), random-init weights",
-        "config": {"workload": wl["desc"], "per_gpu_batch": batch, "global_batch": batch * world,
-                   "l2": "per-step activations exceed the 126 MB L2 many times over; no flush needed",
-                   "graph": "whole network captured in one CUDA graph per GPU"},
-        "e2e": {"value": e2e_value, "unit": METRIC, "h2d_bytes_per_step": in_bytes,
-                "d2h_bytes_per_step": out_bytes, "ms_per_step": ms_e2e / args.steps,
-                "overlap": "upload of the next batch overlaps the current step (2 staging buffers)"},
-        "gpu_launches": chain.kernels_per_step * args.steps,
-        "clocks": clocks,
-    }
-
-    if rank == 0:
-        line.update(per_layer_report(chain, layers, batch, wl, clocks, torch))
+        ms_e2e, ms_e2e_min, rounds_e2e, span_e2e = timed(step_e2e, args.steps, budget)
+    h2d_gbs = h2d_bandwidth(l, check, staging[0].data_ptr(), hin, in_bytes, copy_stream, torch)
     if world > 1:
         dist.barrier()
-    if args.workload not in ("tinyyolov2", "dscnn"):
-        args.no_cpu_baseline = True  # the reference arm times the two headline chains only
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    images_per_round = batch * world * args.steps
+    clocks = clk.summary()
+    res = {
+        "metric": METRIC, "value": images_per_round / (ms * 1e-3), "unit": METRIC, "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+        "ms_per_step_min": ms_min / args.steps, "rounds": rounds, "timed_s": round((span_ms + span_e2e) * 1e-3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"],
+        "data": "synthetic (seeded), random-init weights",
+        "config": config_of(workload, batch, world),
+        "e2e": {"value": images_per_round / (ms_e2e * 1e-3), "unit": METRIC, "h2d_bytes_per_step": in_bytes,
+                "d2h_bytes_per_step": out_bytes, "ms_per_step": ms_e2e / args.steps,
+                "ms_per_step_min": ms_e2e_min / args.steps, "rounds": rounds_e2e, "h2d_gbs": round(h2d_gbs, 2),
+                "h2d_ms_alone": round(in_bytes / (h2d_gbs * 1e9) * 1e3, 4),
+                "overlap": "upload of the next batch overlaps the current step (2 staging buffers)"},
+        "gpu_launches": chain.kernels_per_step * args.steps * (rounds + rounds_e2e),
+        "kernels_per_step": chain.kernels_per_step,
+        "clocks": clocks,
+    }
+    if rank == 0:
+        res.update(per_layer_report(chain, layers, batch, wl, clocks, torch, pipes))
+    if world > 1:
+        dist.barrier()
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and workload in ("tinyyolov2", "dscnn"):
         try:
-            line["cpu_baseline"] = time_reference(args.workload, layers, os.cpu_count() or 1)
+            res["cpu_baseline"] = time_reference(workload, layers, os.cpu_count() or 1)
         except Exception as e:  # the checker library is absent: say so, do not hide it
-            line["cpu_baseline"] = {"value": None, "unit": METRIC, "cores": 0, "kind": "reference",
-                                    "sample": f"unavailable: {e}"}
+            res["cpu_baseline"] = {"value": None, "unit": METRIC, "cores": 0, "kind": "reference",
+                                   "sample": f"unavailable: {e}"}
+    check(l.small_b200_free_host(hin)); check(l.small_b200_free_host(hout))
+    del chain, staging, inputs
+    torch.cuda.empty_cache()
+    return res
+
+
+def cpp_boundary_leg():
+    """Throughput through the reference's own object API (small::TinyYoloV2<FloatBuffer> built from the
+    reference's headers against this platform, BatchScope(64) + InferenceGraph): the driver under
+    tests/reference_drivers/_build, when it has been built, with the tensor-core convolution on and
+    off.  inferences/s from its 'ms per image' line."""
+    exe = os.path.join(ROOT, "tests", "reference_drivers", "_build", "bin", "model_graph")
+    if not os.path.exists(exe):
+        return {"unavailable": "tests/reference_drivers/_build/bin/model_graph is not built"}
+    out = {"api": "small::TinyYoloV2<FloatBuffer>::inference under small::b200::BatchScope(64) + InferenceGraph",
+           "note": "the reference's model has no bias and ReLU; same convolution shapes as the benchmark network"}
+    for key, flag in (("tensor_cores", "1"), ("cuda_cores_only", "0")):
+        try:
+            r = subprocess.run([exe, "416", "64", "5"], env=dict(os.environ, SMALL_B200_TENSOR_CORE=flag),
+                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+            ms = [float(line.split("graph")[1].split("ms per image")[0]) for line in r.stdout.splitlines()
+                  if "images: graph" in line]
+            out[key] = {"inferences_per_s": 1e3 / ms[0], "ms_per_image": ms[0], "rc": r.returncode} if ms else \
+                {"unavailable": r.stdout[-200:]}
+        except Exception as e:
+            out[key] = {"unavailable": str(e)}
+    return out
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    env = (torch, dist, world, rank, local)
+    pipes = measured_pipes(torch)
+    primary = args.workload or "tinyyolov2"
+    line = measure_workload(args, primary, env, pipes)
+    if rank == 0:
+        line["pipes_measured"] = pipes
+    if not args.workload:
+        # the second half of the metric: DS-CNN uint8, same fields
+        other = measure_workload(args, "dscnn", env, pipes)
+        line["workloads"] = {"dscnn": other}
+        if rank == 0 and world == 1 and not args.no_cpp_boundary:
+            line["cpp_boundary"] = cpp_boundary_leg()
     if rank == 0:
         print(json.dumps(line), flush=True)
-    check(l.small_b200_free_host(hin)); check(l.small_b200_free_host(hout))
     if world > 1:
         dist.destroy_process_group()
 
@@ -356,6 +471,7 @@ def run_one_layer(args):
     import torch
 
     from smallframework_b200 import _lib, networks
+    args.workload = args.workload or "tinyyolov2"
     wl = WORKLOADS[args.workload]
     batch = args.batch or 8
     layers = make_layers(args.workload)
@@ -395,6 +511,7 @@ def run_layer_sweep(args):
     batch = args.batch or 256
     wl = dict(dtype="f32")
     rows, total_ms, total_flops = [], 0.0, 0.0
+    pipes = measured_pipes(torch)
     with ClockSampler(0) as clk:
         for layers in networks.yolov3_tiny_convs(seed=3):
             chain = networks.Chain(layers, batch, "f32")
@@ -403,7 +520,7 @@ def run_layer_sweep(args):
             chain.x.copy_(torch.rand(chain.x.numel(), device="cuda", generator=g) * 2 - 1)
             chain.enqueue()
             chain.stream.synchronize()
-            rep = per_layer_report(chain, layers, batch, wl, {"sm_mhz": 1965.0}, torch)  # alone: full clocks
+            rep = per_layer_report(chain, layers, batch, wl, {"sm_mhz": 1965.0}, torch, pipes)
             row = rep["layers"][0]
             L = layers[0]
             row["shape"] = f"{L['C']}->{L['K']} {L['Fh']}x{L['Fw']} @{L['H']}"
@@ -418,26 +535,30 @@ def run_layer_sweep(args):
         "data": "synthetic (seeded): inputs U[-1,1), weights N(0, 0.05)", "dtype": "f32",
         "sum_ms": round(total_ms, 4), "mean_tflops": round(total_flops / total_ms, 2) if total_ms else None,
         "peaks": {"hbm_gbs": peaks["hbm"], "bf16_tflops_burst": peaks["tensor_burst"], "source": peaks["source"]},
+        "pipes_measured": pipes,
         "clocks": clk.summary(), "layers": rows}), flush=True)
 
 
-# DRAM traffic of the dominant kernel's launch at the bench size, from a one-pass ncu capture
-# (dram__bytes_read.sum + dram__bytes_write.sum); the profile summary that holds it is named.
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of a layer's launch from a one-pass ncu
+# capture at the bench size: (layer, batch) -> (bytes, summary under profiles/, date of the capture).
+# A capture belongs to the kernel as it was that day; the line reports the provenance with the number.
 MEASURED_TRAFFIC = {
-    # profiles/conv_tf32x3_kernel_conv8_batch16.md (one-pass capture at batch 64)
-    ("conv8", 64): 582.4e6,
-    # profiles/dwconv3x3_u8_rows_kernel_dscnn_dw1_batch2048.md (one-pass capture at batch 4096)
-    ("dw1", 4096): 32.8e6, ("dw2", 4096): 32.8e6, ("dw3", 4096): 32.8e6, ("dw4", 4096): 32.8e6,
+    ("conv8", 64): (582.4e6, "conv_tf32x3_kernel_conv8_batch16.md", "2026-11-25"),
 }
 
 
 def kernel_class(chain, i, L, dtype):
-    """Which kernel runs layer i and what bounds it."""
+    """Which kernel runs layer i (with the layers it absorbs) and what bounds it."""
+    follow = chain.absorbed(i)
     if L["op"] == "conv":
         if dtype == "f32":
             if chain.prepared[i] is not None:
                 return "conv_tf32x3_kernel (tcgen05 kind::tf32, 3xTF32)", "tf32x3"
-            return ("conv2d_first_f32_kernel (FFMA)" if L["C"] < 16 else "conv2d_f32_kernel (FFMA)"), "ffma"
+            name = "conv2d_first_f32_kernel (FFMA)" if L["C"] < 16 else "conv2d_f32_kernel (FFMA)"
+            return name + (" + 2x2 max pool" if follow else ""), "ffma"
+        if follow:
+            tail = "depthwise 3x3 on tcgen05" if len(follow) == 1 else "global average pool + dense"
+            return f"block_u8_tc_kernel (tcgen05 kind::i8 {'im2col first layer' if L['C'] == 1 else '1x1'} -> {tail})", "i8"
         pw = (L["Fh"] == 1 and L["Fw"] == 1 and L["stride"] == 1 and L["C"] % 32 == 0 and L["C"] <= 256)
         if pw:
             return "pw_u8_tc_kernel (tcgen05 kind::i8)", "i8"
@@ -457,31 +578,32 @@ def networks_out_hw(L):
     return _out_hw(L)
 
 
-def per_layer_report(chain, layers, batch, wl, clocks, torch):
-    """Times every layer's launch alone with CUDA events on the launching stream (inputs of
-    each layer at this batch are far larger than L2) and charges it against its roofline:
-    t_roof = max(flops / pipe peak, bytes / HBM peak).  Pipe peaks: the fp32 FMA pipe at the
-    sampled clock for CUDA-core convolutions; for the 3xTF32 tensor-core convolution one sixth of
-    the measured bf16 rate (tf32 runs at half the bf16 rate and every product takes three
-    MMAs); for uint8 tensor-core layers twice the measured bf16 rate."""
+def per_layer_report(chain, layers, batch, wl, clocks, torch, pipes=None):
+    """Times every launch of the step alone with CUDA events on the launching stream and charges it
+    against its roofline: t_roof = max(flops / pipe peak, bytes / HBM peak).  Pipe peaks are MEASURED on
+    this GPU (small_b200_peak_probe): the fp32 FMA pipe for CUDA-core convolutions, one third of the tf32
+    tensor rate for the 3xTF32 convolution (three MMAs per product), the i8 tensor rate for uint8
+    tensor-core layers.  A launch that runs several layers (a producer and what it absorbs) is charged the
+    flops of all of them and the bytes it has to move: the first layer's input, the last one's output, all
+    the weights.  fp32 layers at their batch read inputs far larger than L2; the uint8 networks' layers are
+    L2-resident here as they are inside a step (see config.l2)."""
     from smallframework_b200 import networks
     peaks = load_peaks()
-    sm_mhz = clocks.get("sm_mhz") or 1700.0
-    sms = torch.cuda.get_device_properties(0).multi_processor_count
-    ffma_tflops = sms * 128 * 2 * sm_mhz * 1e6 / 1e12   # fp32 FMA pipe at the observed clock
-    # every layer is timed alone here, at full clocks: the burst figure of the bf16 GEMM applies
-    pipes = {"ffma": ffma_tflops, "tf32x3": peaks["tensor_burst"] / 6.0, "i8": peaks["tensor_burst"] * 2.0,
-             "cuda_u8": ffma_tflops, "stream": ffma_tflops}
+    if pipes is None:
+        pipes = measured_pipes(torch)
+    pipe_tops = {"ffma": pipes["ffma"], "tf32x3": pipes["tf32"] / 3.0, "i8": pipes["i8"],
+                 "cuda_u8": pipes["ffma"], "stream": pipes["ffma"]}
     elt = chain.elt
     st = chain.stream.cuda_stream
     reps = 5
     rows = []
     plan = chain.io_plan()
+    work = {}
     for i, L in enumerate(layers):
         if L["op"] == "alias":
             continue
         if plan[i] is None:
-            rows.append({"layer": L.get("name", L["op"]), "kernel": "fused into " + layers[chain.fused_into[i]]["name"],
+            rows.append({"layer": L.get("name", L["op"]), "kernel": "runs inside " + layers[chain.fused_into[i]]["name"],
                          "ms": 0.0, "tflops": 0.0, "gbs": 0.0, "bound": "fused", "roofline_frac": None})
             continue
         src, dst = plan[i]
@@ -494,44 +616,47 @@ def per_layer_report(chain, layers, batch, wl, clocks, torch):
         e1.record(chain.stream)
         chain.stream.synchronize()
         ms = e0.elapsed_time(e1) / reps
-        flops, abytes, wbytes = networks.algorithmic_work(L, elt)
-        if (i + 1) in chain.fused_into:
-            # the producer stores the pooled tensor only: its input + the pool's output
-            pf, pb, _ = networks.algorithmic_work(layers[i + 1], elt)
-            abytes = L["C"] * L["H"] * L["W"] * elt + (pb - layers[i + 1]["C"] * layers[i + 1]["H"] * layers[i + 1]["W"] * elt)
-            flops += pf
+        group = [i] + chain.absorbed(i)
+        flops = wbytes = 0
+        for k in group:
+            f, _, w = networks.algorithmic_work(layers[k], elt)
+            flops += f
+            wbytes += w
+        first, last = layers[group[0]], layers[group[-1]]
+        ho, wo = networks_out_hw(last)
+        abytes = (first["C"] * first["H"] * first["W"] + networks.padded(last["K"]) * ho * wo) * elt
         flops *= batch
         nbytes = abytes * batch + wbytes
+        work[len(rows)] = (flops, nbytes)
         kname, kcls = kernel_class(chain, i, L, wl["dtype"])
-        if (i + 1) in chain.fused_into:
-            kname += " + 2x2 max pool"
-        t_flop = flops / (pipes[kcls] * 1e12)
+        t_flop = flops / (pipe_tops[kcls] * 1e12)
         t_mem = nbytes / (peaks["hbm"] * 1e9)
-        rows.append({"layer": L.get("name", L["op"]), "kernel": kname, "ms": round(ms, 4),
-                     "tflops": round(flops / (ms * 1e-3) / 1e12, 3),
+        rows.append({"layer": "+".join(layers[k].get("name", layers[k]["op"]) for k in group), "kernel": kname,
+                     "ms": round(ms, 4), "tflops": round(flops / (ms * 1e-3) / 1e12, 3),
                      "gbs": round(nbytes / (ms * 1e-3) / 1e9, 1),
                      "bound": ("tensor" if kcls in ("tf32x3", "i8") else "fp32 pipe") if t_flop > t_mem else "hbm",
-                     "roofline_frac": round(max(t_flop, t_mem) / (ms * 1e-3), 4)})
+                     "pipe": kcls, "roofline_frac": round(max(t_flop, t_mem) / (ms * 1e-3), 4)})
     top = max(range(len(rows)), key=lambda i: rows[i]["ms"])
-    L = layers[top]
-    flops, abytes, wbytes = networks.algorithmic_work(L, elt)
-    kname, kcls = kernel_class(chain, top, L, wl["dtype"])
+    flops, nbytes = work[top]
+    kcls = rows[top]["pipe"]
     traffic = MEASURED_TRAFFIC.get((rows[top]["layer"], batch))
+    src = None if traffic is None else {"profile": "profiles/" + traffic[1], "captured": traffic[2]}
     if rows[top]["bound"] != "hbm":
-        achieved = flops * batch / (rows[top]["ms"] * 1e-3) / 1e12
+        achieved = flops / (rows[top]["ms"] * 1e-3) / 1e12
         roof = {"bound": "tensor", "achieved": achieved, "peak": peaks["tensor_burst"], "unit": "TFLOP/s",
-                "frac": achieved / peaks["tensor_burst"], "traffic": traffic,
-                "kernel": kname, "layer": rows[top]["layer"],
+                "frac": achieved / peaks["tensor_burst"], "traffic": None if traffic is None else traffic[0],
+                "traffic_source": src, "kernel": rows[top]["kernel"], "layer": rows[top]["layer"],
                 "peak_source": f"dense bf16 GEMM, burst (the kernel is timed alone), of {peaks['source']}",
-                "pipe": {"peak": pipes[kcls], "frac": achieved / pipes[kcls],
-                         "note": {"tf32x3": "fp32 result from three tf32 MMAs per product and tf32 at half the "
-                                            "bf16 rate: one sixth of the bf16 peak is what this kernel can reach",
-                                  "ffma": "SMs x 128 lanes x 2 x SM clock sampled under load",
-                                  "i8": "twice the bf16 rate"}.get(kcls, "")}}
+                "pipe": {"peak": pipe_tops[kcls], "frac": achieved / pipe_tops[kcls],
+                         "note": {"tf32x3": "fp32 result from three tf32 MMAs per product: one third of the tf32 "
+                                            "tensor rate measured on this GPU in this run",
+                                  "ffma": "fp32 FMA pipe measured on this GPU in this run",
+                                  "i8": "i8 tensor rate measured on this GPU in this run"}.get(kcls, "")}}
     else:
-        achieved = (abytes * batch + wbytes) / (rows[top]["ms"] * 1e-3) / 1e9
+        achieved = nbytes / (rows[top]["ms"] * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm"], "traffic": traffic, "kernel": kname,
+                "frac": achieved / peaks["hbm"], "traffic": None if traffic is None else traffic[0],
+                "traffic_source": src, "kernel": rows[top]["kernel"],
                 "layer": rows[top]["layer"], "peak_source": f"copy bandwidth, of {peaks['source']}"}
     return {"roofline": roof, "layers": rows}
 
@@ -542,7 +667,11 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="tinyyolov2", choices=sorted(WORKLOADS) + ["yolov3tiny_layers"])
+    ap.add_argument("--workload", default="", choices=[""] + sorted(WORKLOADS) + ["yolov3tiny_layers"],
+                    help="default: Tiny-YOLOv2 as the line, DS-CNN under 'workloads'")
+    ap.add_argument("--min-seconds", type=float, default=1.0,
+                    help="rounds of --steps steps are repeated until this much has been timed, per leg")
+    ap.add_argument("--no-cpp-boundary", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-layer", default="",

@@ -92,6 +92,12 @@ int small_b200_device_status(int *status);
  * memory and returns; the next small_b200_device_status() reports SMALL_B200_DEVICE_TIMEOUT
  * (code 99) and clears it.  No counterpart in the reference. */
 int small_b200_selftest_bounded_wait(uint32_t polls, void *stream);
+/* What a pipe of the current device delivers when only issue stands in the way (operands resident
+ * in registers / shared memory / tensor memory): kind 0 = fp32 FMA pipe, 1 = tcgen05 kind::tf32
+ * MMA, 2 = tcgen05 kind::i8 MMA.  Runs a short probe kernel on the default stream, synchronously,
+ * and returns tera-operations per second (2 per multiply-add) in *tera_ops.  These are the
+ * denominators of the benchmark's per-layer roofline figures.  No counterpart in the reference. */
+int small_b200_peak_probe(int kind, double *tera_ops);
 /* Number of kernels this library has launched in this process since it was loaded. */
 uint64_t small_b200_launch_count(void);
 

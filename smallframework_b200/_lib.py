@@ -44,6 +44,7 @@ SIGNATURES = {
     "small_b200_set_device": [C.c_int],
     "small_b200_device_status": [C.POINTER(C.c_int)],
     "small_b200_selftest_bounded_wait": [C.c_uint32, _VP],
+    "small_b200_peak_probe": [C.c_int, C.POINTER(C.c_double)],
     "small_b200_malloc": [_SZ, C.POINTER(_VP)],
     "small_b200_malloc_managed": [_SZ, C.POINTER(_VP)],
     "small_b200_malloc_host": [_SZ, C.POINTER(_VP)],

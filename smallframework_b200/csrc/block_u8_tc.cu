@@ -21,6 +21,15 @@
 //                   pooled vector (the tail of the keyword-spotting network), on the CUDA cores:
 //                   per image it is 64 sums and a 64 x 16 matrix-vector product.
 //
+// Per-channel constants (bias, k_zero, zero-point terms) also go through the tensor core: both stages
+// start their accumulation with one extra MMA whose A operand is a constant tile (31 bytes of 127 and one
+// byte of 1 in every row) and whose B operand holds, per output channel, 32 signed digits d_i with
+// 127 * (d_0 + ... + d_30) + d_31 = the constant.  The epilogues then need no per-channel value at all
+// (four register-only instructions per output); reading 8 bytes of constant per output from shared
+// memory instead cost as much shared-memory bandwidth as all the MMA operands together, and shared-memory
+// bandwidth is what bounds this kernel.  A constant beyond +-500000 (a bias of that size is possible, the
+// biases are data) switches that stage to the shared-memory form; the decision is made once per CTA.
+//
 // This is the reference's Conv2D_ReLU_DepthwiseConv2D_ReLU fusion
 // (include/small/fused_interface_abstract.hpp:1840) for quint8 buffers, where the clamp of the
 // requantisation is the ReLU; the reference keeps an intermediate buffer per output tile in
@@ -33,6 +42,8 @@
 // j + 1 overlaps the stage-1 epilogue of image j and stage 2 of image j - 1.
 // Requirements (else the layers run as separate kernels): H*W <= 128; filter zero points -128
 // (weights enter the tensor core as signed bytes); zero point of the intermediate 0 or -128.
+#include <cstdlib>
+
 #include "tc_common.cuh"
 
 namespace
@@ -71,14 +82,27 @@ struct RoleFlag
     int v;
 };
 
-// 16 accumulators of one pixel (one channel block) -> 16 output bytes.  The common quantiser takes
-// the seeded form (common.cuh); any other one adds the constants and goes the general way.
-__device__ __forceinline__ uint4 requant16(const uint32_t *r, const int *corr, const long long *seed, const Requant &q)
+// 16 accumulators of one pixel (one channel block) -> 16 output bytes.  in_acc: the per-channel
+// constants are already inside the accumulators (they came through the tensor core, see the kernel), so
+// the common quantiser is four register-only instructions per output; otherwise they are read from shared
+// memory, as seeds of the wide multiply (common.cuh) or, for any other quantiser, as plain addends.
+__device__ __forceinline__ uint4 requant16(const uint32_t *r, const int *corr, const long long *seed, const Requant &q,
+                                           bool in_acc)
 {
     if (requant_is_fast(q.lshift, q.rshift, q.mult))
     {
         const int bit = 1 << (q.rshift - 2), sh1 = q.rshift - 1;
         uint32_t w[4];
+        if (in_acc)
+        {
+#pragma unroll
+            for (int e4 = 0; e4 < 4; ++e4)
+                w[e4] = pack4_sat(requant_seeded_raw((int)r[4 * e4], q.mult, 1ll << 30, bit, sh1),
+                                  requant_seeded_raw((int)r[4 * e4 + 1], q.mult, 1ll << 30, bit, sh1),
+                                  requant_seeded_raw((int)r[4 * e4 + 2], q.mult, 1ll << 30, bit, sh1),
+                                  requant_seeded_raw((int)r[4 * e4 + 3], q.mult, 1ll << 30, bit, sh1));
+            return make_uint4(w[0], w[1], w[2], w[3]);
+        }
 #pragma unroll
         for (int e4 = 0; e4 < 4; ++e4)
         {
@@ -97,7 +121,7 @@ __device__ __forceinline__ uint4 requant16(const uint32_t *r, const int *corr, c
     int v[16];
 #pragma unroll
     for (int e = 0; e < 16; ++e)
-        v[e] = (int)r[e] + corr[e];
+        v[e] = (int)r[e] + (in_acc ? 0 : corr[e]);
     return requant_pack16(v, q.lshift, q.rshift, q.mult);
 }
 
@@ -139,6 +163,7 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
     __shared__ __align__(16) uint8_t dense_w[POOL ? 128 * DPITCH : 16]; // POOL: dense filter [k][c] as signed bytes
     __shared__ int dense_c[POOL ? 128 : 1];                  // POOL: per-output constant of the dense layer
     __shared__ RoleFlag failed1, failed2;
+    __shared__ int big1, big2; // a stage's constants do not fit the digit form: its epilogue adds them itself
 
     const int cbs = a.C / CB;
     const uint32_t a_stage = STEM ? (uint32_t)(KCH * BM * CB) : (uint32_t)(a.C * BM);
@@ -152,6 +177,9 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
     uint8_t *sP = sB2 + b2_bytes;                // [stage][copy kw][cb][entry][16 B]
     uint8_t *sI = sP + 2 * p_stage;              // first-layer form: [stage][prow][pitch] padded image
     const int img_bytes = STEM ? a.prow * a.pitch : 0;
+    uint8_t *sOnes = sI + ((2 * img_bytes + 15) & ~15); // [2 chunks][128 rows][16 B]: 127 ... 127 1
+    uint8_t *sC1 = sOnes + 2 * BM * CB;          // digits of the stage-1 constants, laid out like sB1 with 32 "input channels"
+    uint8_t *sC2 = sC1 + 32 * K;                 // digits of the stage-2 constants: [K/32][2 chunks][32 n][16 B]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int first = blockIdx.x, step = gridDim.x;
@@ -168,7 +196,7 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                 mbar_init(&p_full[i], EPI_THREADS); mbar_init(&p_free[i], POOL ? EW : K / 32);
                 mbar_init(&d2_full[i], K / 32); mbar_init(&d2_free[i], EW);
             }
-            failed1.v = 0; failed2.v = 0;
+            failed1.v = 0; failed2.v = 0; big1 = 0; big2 = 0;
             fence_barrier_init();
         }
         __syncwarp();
@@ -202,6 +230,10 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
     }
     for (int i = tid; i < (int)((b2_bytes + 2 * p_stage) / 16); i += BLOCK_THREADS) // sB2 and sP are adjacent
         reinterpret_cast<uint4 *>(sB2)[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = tid; i < 2 * BM; i += BLOCK_THREADS)
+        reinterpret_cast<uint4 *>(sOnes)[i] = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, i < BM ? 0x7f7f7f7fu : 0x017f7f7fu);
+    for (int i = tid; i < (32 * K + (POOL ? 0 : (K / 32) * 1024)) / 16; i += BLOCK_THREADS) // sC1 and sC2 are adjacent
+        reinterpret_cast<uint4 *>(sC1)[i] = make_uint4(0u, 0u, 0u, 0u);
     __syncthreads();
     if (!POOL)
     {
@@ -230,6 +262,39 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
         const int c2 = POOL ? 0 : a.q2.k_zero + (bias2 ? bias2[tid] : 0);
         corr2[tid] = c2;
         seed2[tid] = requant_seed(c2, a.q2.mult);
+        if (c / 127 > 31 * 127 || c / 127 < -31 * 127)
+            big1 = 1;
+        if (c2 / 127 > 31 * 127 || c2 / 127 < -31 * 127)
+            big2 = 1;
+    }
+    __syncthreads();
+    if (tid < 2 * K)
+    {
+        // digits of constant c: 31 digits worth 127 each, one worth 1 (the remainder of c / 127)
+        const int n = tid % K, stage2 = tid / K;
+        if (!(stage2 ? (POOL || big2) : big1))
+        {
+            const int c = stage2 ? corr2[n] : corr1[n];
+            int rest = c / 127;
+            const int last = c - 127 * rest;
+            for (int i = 0; i < 32; ++i)
+            {
+                int d = last;
+                if (i < 31)
+                {
+                    d = rest > 127 ? 127 : (rest < -127 ? -127 : rest);
+                    rest -= d;
+                }
+                uint8_t *dst;
+                if (stage2)
+                    dst = sC2 + (n >> 5) * 1024 + (i >> 4) * 512 + (n & 31) * CB + (i & 15);
+                else if (STEM) // K-major [chunk][n][16 B], like the first-layer filter
+                    dst = sC1 + (i >> 4) * K * CB + n * CB + (i & 15);
+                else           // MN-major slabs [n / 16][2][16 i][16 n], like the 1x1 filter
+                    dst = sC1 + (n >> 4) * 2 * CB * CB + (i >> 4) * CB * CB + (i & 15) * CB + (n & 15);
+                *dst = (uint8_t)(int8_t)d;
+            }
+        }
     }
     if (POOL)
     {
@@ -297,6 +362,11 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
             const uint32_t a_step = STEM ? (uint32_t)(2 * BM) : (uint32_t)(2 * a.HW);
             const uint32_t b_step = STEM ? (uint32_t)(2 * K) : (uint32_t)(2 * CB);
             const int n1 = STEM ? KCH / 2 : cbs / 2;
+            // the MMA that seeds the accumulators with the per-channel constants (all-zero digits when the
+            // stage adds them in its epilogue)
+            const uint64_t d_ones = make_smem_desc(smem_u32(sOnes), BM * CB, 8 * CB, 0);
+            const uint64_t d_c1 = STEM ? make_smem_desc(smem_u32(sC1), K * CB, 8 * CB, 0)
+                                       : make_smem_desc(smem_u32(sC1), 8 * CB, 2 * CB * CB, 0);
             bool ok = true;
             for (int j = 0; j < count && ok; ++j)
             {
@@ -309,8 +379,9 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                 tc_fence_after_sync();
                 const uint32_t d1 = tmem + (uint32_t)(s * K);
                 const uint64_t da_s = da1_0 + (uint64_t)(s ? a16 : 0u);
+                tc_mma_i8(d1, d_ones, d_c1, idesc1, 0u);
                 for (int i = 0; i < n1; ++i)
-                    tc_mma_i8(d1, da_s + (uint64_t)(i * a_step), db1_0 + (uint64_t)(i * b_step), idesc1, i > 0 ? 1u : 0u);
+                    tc_mma_i8(d1, da_s + (uint64_t)(i * a_step), db1_0 + (uint64_t)(i * b_step), idesc1, 1u);
                 tc_commit(&d1_full[s]);
             }
         }
@@ -333,6 +404,8 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
 #pragma unroll
                 for (int kw = 0; kw < 3; ++kw)
                     dA[kh][kw] = (uint32_t)kw * copy16 + (uint32_t)(kh * a.W);
+            const uint64_t d_ones = make_smem_desc(smem_u32(sOnes), BM * CB, 8 * CB, 0);
+            const uint64_t d_c2 = make_smem_desc(smem_u32(sC2) + (uint32_t)(c32 * 1024), 32 * CB, 8 * CB, 0);
             bool ok = true;
             for (int jj = 0; jj < count && ok; ++jj)
             {
@@ -345,10 +418,10 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                 tc_fence_after_sync();
                 const uint64_t da_t = da2_0 + (uint64_t)(t ? stage16 : 0u);
                 const uint32_t d = tmem + (uint32_t)(2 * K + t * K + c32 * 32);
+                tc_mma_i8(d, d_ones, d_c2, idesc2, 0u);
 #pragma unroll
                 for (int tap = 0; tap < TAPS; ++tap)
-                    tc_mma_i8(d, da_t + (uint64_t)dA[tap / 3][tap % 3], db2_0 + (uint64_t)(tap * (K / 32) * 64), idesc2,
-                              tap > 0 ? 1u : 0u);
+                    tc_mma_i8(d, da_t + (uint64_t)dA[tap / 3][tap % 3], db2_0 + (uint64_t)(tap * (K / 32) * 64), idesc2, 1u);
                 tc_commit(&d2_full[t]); // this block's sums are complete ...
                 tc_commit(&p_free[t]);  // ... and its reads of the intermediate are done
             }
@@ -364,6 +437,7 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
         const bool wraps_left = cq == a.W - 1;     // copy kw = 0 must not show this pixel to the next row
         const bool wraps_right = cq == 0;          // copy kw = 2 must not show it to the previous row
         const uint32_t sx = a.mid_signed ? 0x80808080u : 0u;
+        const bool in_acc = big1 == 0;
         bool ok = true;
         // first-layer form: the im2col tile of an image is built by these warps (see conv_u8_tc.cu)
         const int oh = q / a.W, ow = q - oh * a.W;
@@ -441,7 +515,7 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                 const int cb = cb0 + i;
                 if (i + 1 < CBW)
                     tmem_ld16(d1 + (uint32_t)((i + 1) * CB), nxt);
-                uint4 o = requant16(cur, corr1 + cb * CB, seed1 + cb * CB, a.q1);
+                uint4 o = requant16(cur, corr1 + cb * CB, seed1 + cb * CB, a.q1, in_acc);
                 o.x ^= sx; o.y ^= sx; o.z ^= sx; o.w ^= sx;
                 if (q < a.HW)
                 {
@@ -471,6 +545,7 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
         const int w2 = warp - EW, quarter = w2 & 3, part = w2 >> 2;
         const int p = quarter * 32 + lane, cb0 = part * CBW;
         const int rt = tid - EPI_THREADS; // thread index inside this role
+        const bool in_acc = big2 == 0;
         bool ok = true;
         if (!POOL)
         {
@@ -493,7 +568,7 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                     const int cb = cb0 + i;
                     if (i + 1 < CBW)
                         tmem_ld16(d2 + (uint32_t)((i + 1) * CB), nxt);
-                    const uint4 ov = requant16(cur, corr2 + cb * CB, seed2 + cb * CB, a.q2);
+                    const uint4 ov = requant16(cur, corr2 + cb * CB, seed2 + cb * CB, a.q2, in_acc);
                     if (p < a.HW)
                         *reinterpret_cast<uint4 *>(o + (size_t)cb * a.HW * CB) = ov;
                     if (i + 1 < CBW)
@@ -619,7 +694,8 @@ size_t smem_need(const BlockArgs &a, int K, bool stem, bool pool)
     const size_t b2 = pool ? 0 : (size_t)9 * (K / 32) * 1024;
     const size_t p_stage = (size_t)(pool ? 1 : 3) * (K / CB) * a.E * CB;
     const size_t img = stem ? (size_t)2 * a.prow * a.pitch : 0;
-    return 2 * a_stage + b1 + b2 + 2 * p_stage + ((img + 15) & ~(size_t)15) + 64;
+    const size_t consts = (size_t)2 * BM * CB + (size_t)32 * K + (pool ? 0 : (size_t)(K / 32) * 1024);
+    return 2 * a_stage + b1 + b2 + 2 * p_stage + ((img + 15) & ~(size_t)15) + consts + 64;
 }
 
 template <int K, bool STEM, bool POOL, bool SIGNED_IN, int EW = 8>
@@ -656,16 +732,19 @@ int dispatch(const BlockArgs &a, int K, bool stem, size_t smem, const uint8_t *i
              const uint8_t *f2, const int32_t *b2, uint8_t *out, cudaStream_t st)
 {
     const bool sgn = a.zero_in1 != 0;
-#define SB_BLOCK_CASE(KK)                                                                                        \
-    if (K == KK)                                                                                                 \
+    static const int ew = [] { const char *e = std::getenv("SMALL_B200_BLOCK_EW"); return (e && e[0] == '4') ? 4 : 8; }();
+#define SB_BLOCK_CASE(KK, EE)                                                                                    \
+    if (K == KK && ew == EE)                                                                                     \
     {                                                                                                            \
         if (!stem)                                                                                               \
-            return launch_block<KK, false, POOL, false>(a, smem, in, f1, b1, f2, b2, out, st);                   \
-        return sgn ? launch_block<KK, true, POOL, true>(a, smem, in, f1, b1, f2, b2, out, st)                    \
-                   : launch_block<KK, true, POOL, false>(a, smem, in, f1, b1, f2, b2, out, st);                  \
+            return launch_block<KK, false, POOL, false, EE>(a, smem, in, f1, b1, f2, b2, out, st);               \
+        return sgn ? launch_block<KK, true, POOL, true, EE>(a, smem, in, f1, b1, f2, b2, out, st)                \
+                   : launch_block<KK, true, POOL, false, EE>(a, smem, in, f1, b1, f2, b2, out, st);              \
     }
-    SB_BLOCK_CASE(32)
-    SB_BLOCK_CASE(64)
+    SB_BLOCK_CASE(32, 8)
+    SB_BLOCK_CASE(64, 8)
+    SB_BLOCK_CASE(32, 4)
+    SB_BLOCK_CASE(64, 4)
 #undef SB_BLOCK_CASE
     return fail(SMALL_B200_INVALID_ARGUMENT, "fused uint8 block: channel count not covered");
 }

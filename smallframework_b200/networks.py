@@ -411,6 +411,7 @@ class Chain:
                         continue
                 i += 1
         self.graph = None
+        self.graphs = []
         self.y = None
         self.kernels_per_step = 0
         self._descs = []
@@ -503,26 +504,36 @@ class Chain:
         self.y = src[: self.batch * padded(k) * ho * wo]
         return self.y
 
-    def capture(self):
+    def capture(self, inputs=None):
+        """Records the layer sequence into a CUDA graph.  `inputs`: a list of device tensors shaped
+        like `x`; one graph is recorded per tensor, reading its input from there (launch(k) replays
+        graph k), so that a benchmark can rotate over more input data than the L2 cache holds."""
         l = lib()
-        self.stream.synchronize()
-        gp = C.c_void_p()
-        check(l.small_b200_graph_begin(self.stream.cuda_stream))
-        try:
-            self.enqueue()
-        finally:
-            check(l.small_b200_graph_end(self.stream.cuda_stream, C.byref(gp)))
-        self.graph = gp
+        self.graphs = []
+        for xin in (inputs if inputs is not None else [self.x]):
+            saved, self.x = self.x, xin
+            self.named["in"] = xin
+            self.stream.synchronize()
+            gp = C.c_void_p()
+            check(l.small_b200_graph_begin(self.stream.cuda_stream))
+            try:
+                self.enqueue()
+            finally:
+                check(l.small_b200_graph_end(self.stream.cuda_stream, C.byref(gp)))
+                self.x = saved
+                self.named["in"] = saved
+            self.graphs.append(gp)
+        self.graph = self.graphs[0]
         return self
 
-    def launch(self):
+    def launch(self, k=0):
         if self.graph is None:
             self.capture()
-        check(lib().small_b200_graph_launch(self.graph, self.stream.cuda_stream))
+        check(lib().small_b200_graph_launch(self.graphs[k % len(self.graphs)], self.stream.cuda_stream))
 
     def __del__(self):
         try:
-            if self.graph is not None:
-                lib().small_b200_graph_destroy(self.graph)
+            for g in getattr(self, "graphs", []):
+                lib().small_b200_graph_destroy(g)
         except Exception:
             pass

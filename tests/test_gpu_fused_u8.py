@@ -45,6 +45,7 @@ PW_DW_CASES = [
     (32, 64, 1, 7, 4, 0, 0, False),        # one row
     (64, 64, 9, 1, 4, 0, 0, True),         # one column
     (32, 32, 1, 1, 3, 0, 0, True),         # one pixel
+    (128, 64, 10, 10, 3, -128, 0, "huge"),  # biases too large for the in-accumulator form of the constants
 ]
 
 
@@ -55,10 +56,11 @@ def test_pointwise_then_depthwise_one_kernel(oracle, case):
     x = rng.integers(0, 256, (N, Cn, H, W), dtype=np.uint8)
     w1 = rng.integers(0, 256, (K, Cn, 1, 1), dtype=np.uint8)
     w2 = rng.integers(0, 256, (K, 3, 3), dtype=np.uint8)
-    b1 = rng.integers(-1024, 1025, K).astype(np.int32) if with_bias else None
-    b2 = rng.integers(-1024, 1025, K).astype(np.int32) if with_bias else None
-    q1 = _quant_for(Cn * 128 * 100)
-    q2 = _quant_for(9 * 128 * 100)
+    top = 1025 if with_bias != "huge" else 3_000_000
+    b1 = rng.integers(-top + 1, top, K).astype(np.int32) if with_bias else None
+    b2 = rng.integers(-top + 1, top, K).astype(np.int32) if with_bias else None
+    q1 = _quant_for(Cn * 128 * 100 + (top if top > 2000 else 0))
+    q2 = _quant_for(9 * 128 * 100 + (top if top > 2000 else 0))
     xp, w1p, w2p = P.pack_activation(x), P.pack_conv_filter(w1), P.pack_dw_filter(w2)
     I, F1, F2 = _qbuf(xp, zi), _qbuf(w1p, -128), _qbuf(w2p, -128)
     mid = _qbuf(np.zeros(N * K * H * W, np.uint8), zm, q1)
