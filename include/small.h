@@ -13,6 +13,7 @@
 #define SMALL_SUB_VERSON 0
 #define SMALL_PLATFORM_B200 1
 
+#include <omp.h>   // the reference's <small.h> brings it in (abstract_layer.hpp:18); its demos rely on that
 #include <stdint.h>
 
 #include <params.h>      // include/small/platforms/b200

@@ -34,6 +34,7 @@ inline small_b200_layer describe(int C, int K, int H, int W, int Fh, int Fw, int
     L.C = C; L.K = K; L.H = H; L.W = W; L.Fh = Fh; L.Fw = Fw; L.stride = stride;
     L.pad_t = t; L.pad_b = b; L.pad_l = l; L.pad_r = r;
     L.accumulate = accumulate; L.act = act; L.slope = slope;
+    L.stride_h = row_stride();
     return L;
 }
 
@@ -282,10 +283,16 @@ void LeakyReLUActivation(int input_channels, int input_height, int input_width,
     b200::throw_on(small_b200_leaky_relu_f32(n, input_buf.device_ptr(), slope, output_buf.device_ptr(), b200::stream()));
 }
 
+// interface_abstract.hpp:1697 of the reference: output = input * filter_buf[0] (float only there too).
 template <class BufferT, bool = true>
-void Dropout(int, int, int, BufferT const &, BufferT const &, BufferT &)
+void Dropout(int input_channels, int input_height, int input_width,
+             BufferT const &input_buf, BufferT const &filter_buf, BufferT &output_buf)
 {
-    throw std::invalid_argument("Dropout ERROR: not provided on the B200 platform.");
+    static_assert(!b200::is_quint8<BufferT>, "Dropout: float only, as in the reference");
+    b200::require_block(input_channels, FLOAT_C_ib, "Dropout<float> ERROR: in_channels unsupported.");
+    const float rate = filter_buf.peek(0); // a parameter no kernel writes: no wait for the device
+    const int64_t n = (int64_t)b200::batch() * input_channels * input_height * input_width;
+    b200::throw_on(small_b200_scale_f32(n, input_buf.device_ptr(), rate, output_buf.device_ptr(), b200::stream()));
 }
 
 template <class BufferT, bool = true>

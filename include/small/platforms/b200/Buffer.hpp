@@ -46,6 +46,22 @@ struct BatchScope
     ~BatchScope() { batch() = saved; }
 };
 
+// Stride along the height for the layer calls of this thread when it differs from the stride argument
+// (0 = the same on both axes).  The 1-D family is the 2-D functions with a window height of 1 and a
+// row stride of 1: its wrappers open a RowStrideScope(1) around the 2-D call.
+inline int &row_stride()
+{
+    static thread_local int s = 0;
+    return s;
+}
+
+struct RowStrideScope
+{
+    int saved;
+    explicit RowStrideScope(int s) : saved(row_stride()) { row_stride() = s; }
+    ~RowStrideScope() { row_stride() = saved; }
+};
+
 // Stream the layer calls of this thread are enqueued on (nullptr = the default stream), and
 // whether that stream is being captured into a graph (see InferenceGraph below).
 inline void *&stream()

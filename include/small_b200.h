@@ -73,6 +73,13 @@ typedef struct small_b200_layer
     int32_t zero_in, zero_filt;
     int32_t lshift, rshift, multiplier;
     int32_t k_zero;
+    /* Stride along the height when it differs from `stride` (which then is the stride along the
+     * width only); 0 = the same stride on both axes.  The reference's 1-D family is its 2-D loop
+     * nest with the batch in place of the height (abstract_layer.hpp:1838-1846): a 1-D layer of
+     * stride s is a layer with Fh = 1, stride_h = 1, stride = s.  Honoured by the fp32 windowed
+     * layers (convolution on the CUDA cores, depthwise, grouped, pools); other entry points refuse
+     * a row stride that differs. */
+    int32_t stride_h;
 } small_b200_layer;
 
 /* ---- library / device ------------------------------------------------------------ */
@@ -194,6 +201,14 @@ int small_b200_dwconv2d_f32(const small_b200_layer *L, const float *in, const fl
  * checked against the reference built with a channel block of 1. */
 int small_b200_groupconv2d_f32(const small_b200_layer *L, int32_t groups, const float *in, const float *filt,
                                const float *bias, float *out, void *stream);
+/* The grouped convolution of the reference's FUSED interface (GroupConv2D_ReLU, Conv2D_GroupConv, ...,
+ * fused_interface_abstract.hpp:2507-3667), which is a different layer from small::GroupConv2D: there
+ * G = output_groups, K = C_ob, F_c = C_ib (:2740-2760), i.e. `groups` dense convolutions from 16 to 16
+ * channels, group g on channel block g:
+ *   in [N][G][H][W][16]   filt [G][Fh][Fw][16 c][16 k]   out [N][G][Ho][Wo][16]
+ * bias (may be NULL) [G][16]; L->C and L->K are ignored; stride in {1,2}; act / accumulate as usual. */
+int small_b200_blockconv2d_f32(const small_b200_layer *L, int32_t groups, const float *in, const float *filt,
+                               const float *bias, float *out, void *stream);
 /* small::MaxPool2D<FloatBuffer> (:778): border windows start from 0, interior from the
  * first tap. */
 int small_b200_maxpool2d_f32(const small_b200_layer *L, const float *in, float *out, void *stream);
@@ -203,11 +218,18 @@ int small_b200_avgpool2d_f32(const small_b200_layer *L, const float *in, float *
 int small_b200_relu_f32(int64_t n, const float *in, float *out, void *stream);
 int small_b200_leaky_relu_f32(int64_t n, const float *in, float slope, float *out, void *stream);
 int small_b200_accum_f32(int64_t n, const float *in, float *out, void *stream);
+/* small::Dropout (:1697): every element times the rate held in the filter buffer (OP_MUL,
+ * abstract_layer.hpp:82-86: the tile is loaded from the input and multiplied). */
+int small_b200_scale_f32(int64_t n, const float *in, float scale, float *out, void *stream);
 /* small::Bias / PartialBias (:1992, :2035): out[n][c][h][w] (+)= bias[c]. */
 int small_b200_bias_f32(int32_t N, int32_t C, int32_t H, int32_t W, const float *bias,
                         int32_t accumulate, float *out, void *stream);
 /* small::UpSample2D (:1845), scale 2: out[h][w] = in[h/2][w/2]. */
 int small_b200_upsample2d_f32(int32_t N, int32_t C, int32_t H, int32_t W, const float *in,
+                              float *out, void *stream);
+/* small::UpSample1D (interface_abstract_1D.hpp:1614), scale 2 along the width only:
+ * out[row][w] = in[row][w/2] over [C/16][rows][W][16] (rows = the 1-D family's batch). */
+int small_b200_upsample1d_f32(int32_t N, int32_t C, int32_t rows, int32_t W, const float *in,
                               float *out, void *stream);
 /* small::SoftMax (:1778): per image, exp / sum over all C*H*W elements, no max subtraction. */
 int small_b200_softmax_f32(int32_t N, int64_t elems_per_image, const float *in, float *out,

@@ -21,10 +21,10 @@ class Layer(C.Structure):
                   "pad_t", "pad_b", "pad_l", "pad_r", "accumulate", "act")]
                 + [("slope", C.c_float)]
                 + [(n, C.c_int32) for n in
-                   ("zero_in", "zero_filt", "lshift", "rshift", "multiplier", "k_zero")])
+                   ("zero_in", "zero_filt", "lshift", "rshift", "multiplier", "k_zero", "stride_h")])
 
     def out_hw(self):
-        ho = max((self.H + self.pad_t + self.pad_b - self.Fh) // self.stride + 1, 0)
+        ho = max((self.H + self.pad_t + self.pad_b - self.Fh) // (self.stride_h or self.stride) + 1, 0)
         wo = max((self.W + self.pad_l + self.pad_r - self.Fw) // self.stride + 1, 0)
         return ho, wo
 
@@ -72,13 +72,16 @@ SIGNATURES = {
     "small_b200_conv2d_f32_tf32x3_noalloc": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_dwconv2d_f32": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_groupconv2d_f32": [_LP, C.c_int32, _VP, _VP, _VP, _VP, _VP],
+    "small_b200_blockconv2d_f32": [_LP, C.c_int32, _VP, _VP, _VP, _VP, _VP],
     "small_b200_maxpool2d_f32": [_LP, _VP, _VP, _VP],
     "small_b200_avgpool2d_f32": [_LP, _VP, _VP, _VP],
     "small_b200_relu_f32": [_I64, _VP, _VP, _VP],
     "small_b200_leaky_relu_f32": [_I64, _VP, _F, _VP, _VP],
     "small_b200_accum_f32": [_I64, _VP, _VP, _VP],
+    "small_b200_scale_f32": [_I64, _VP, _F, _VP, _VP],
     "small_b200_bias_f32": [_I32, _I32, _I32, _I32, _VP, _I32, _VP, _VP],
     "small_b200_upsample2d_f32": [_I32, _I32, _I32, _I32, _VP, _VP, _VP],
+    "small_b200_upsample1d_f32": [_I32, _I32, _I32, _I32, _VP, _VP, _VP],
     "small_b200_softmax_f32": [_I32, _I64, _VP, _VP, _VP],
     "small_b200_concat": [_I32, _SZ, _VP, _SZ, _VP, _VP, _VP],
     "small_b200_conv2d_u8": [_LP, _VP, _VP, _VP, _VP, _VP],

@@ -191,9 +191,9 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
         {
             for (int i = 0; i < 2; ++i)
             {
-                mbar_init(&a_full[i], STEM ? EPI_THREADS : 1);
+                mbar_init(&a_full[i], STEM ? EW : 1);
                 mbar_init(&d1_full[i], 1); mbar_init(&d1_free[i], EW);
-                mbar_init(&p_full[i], EPI_THREADS); mbar_init(&p_free[i], POOL ? EW : K / 32);
+                mbar_init(&p_full[i], EW); mbar_init(&p_free[i], POOL ? EW : K / 32);
                 mbar_init(&d2_full[i], K / 32); mbar_init(&d2_free[i], EW);
             }
             failed1.v = 0; failed2.v = 0; big1 = 0; big2 = 0;
@@ -474,8 +474,12 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
                     *reinterpret_cast<uint4 *>(arow + (size_t)j4 * BM * CB) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
                 }
             }
+            // one arrival per warp: hundreds of arrivals on one barrier word are serialised by the hardware
+            // and were a sizeable part of an image's time
             fence_proxy_async();
-            mbar_arrive(&a_full[s]);
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(&a_full[s]);
         };
         if (STEM && count > 0)
             build(first, 0);
@@ -533,10 +537,12 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
             }
             tc_fence_before_sync();
             fence_proxy_async();
-            mbar_arrive(&p_full[s]);
             __syncwarp();
             if (lane == 0)
+            {
+                mbar_arrive(&p_full[s]);
                 mbar_arrive(&d1_free[s]);
+            }
         }
     }
     else
@@ -651,7 +657,10 @@ block_u8_tc_kernel(const BlockArgs a, const uint8_t *__restrict__ in, const uint
         tmem_dealloc(tmem, TMEM_COLS);
 }
 
-bool quant_ok(const small_b200_layer *L) { return L->lshift >= 0 && L->lshift < 32 && L->rshift >= 0 && L->rshift < 32; }
+bool quant_ok(const small_b200_layer *L)
+{
+    return L->lshift >= 0 && L->lshift < 32 && L->rshift >= 0 && L->rshift < 32 && row_stride(L) == L->stride;
+}
 
 // Fills the arguments of stage 1 and the geometry; false when the pair is not covered.
 bool plan_first(const small_b200_layer *c, BlockArgs &a, bool &stem)

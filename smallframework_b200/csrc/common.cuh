@@ -53,6 +53,9 @@ inline int out_dim(int in, int pf, int pb, int f, int s)
     return o > 0 ? o : 0;
 }
 
+// Stride along the height (the descriptor's stride_h, 0 = the same as along the width).
+inline int row_stride(const small_b200_layer *L) { return L->stride_h > 0 ? L->stride_h : L->stride; }
+
 // Channel block actually used for `channels` input channels (first-layer exception).
 inline int eff_block(int channels) { return (channels < CB) ? channels : CB; }
 

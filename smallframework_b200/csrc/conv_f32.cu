@@ -23,6 +23,7 @@ constexpr int PXT = 8;         // pixels per thread
 struct ConvArgs
 {
     int N, C, K, H, W, Ho, Wo, Fh, Fw, stride, pad_t, pad_l;
+    int sh;           // stride along the height (`stride` and the kernels' STRIDE are along the width)
     int cbs;          // input channel blocks
     int PH, PW;       // patch rows / cols
     int tiles_h, tiles_w, kblocks; // kblocks = K / BN
@@ -68,7 +69,7 @@ conv2d_f32_kernel(const ConvArgs a, const float *__restrict__ in, const float *_
     const int th = bid % a.tiles_h; bid /= a.tiles_h;
     const int n = bid;
     const int oh0 = th * TH, ow0 = tw * TW;
-    const int ih0 = oh0 * STRIDE - a.pad_t, iw0 = ow0 * STRIDE - a.pad_l;
+    const int ih0 = oh0 * a.sh - a.pad_t, iw0 = ow0 * STRIDE - a.pad_l;
 
     const int tid = threadIdx.x;
     const int cg = tid % CG;       // channel group (fast: lanes of a quarter warp share pixels)
@@ -164,7 +165,7 @@ conv2d_f32_kernel(const ConvArgs a, const float *__restrict__ in, const float *_
 
         const float *patch = smem + buf * stage_f;
         const float *wts = patch + patch_f;
-        const float *prow = patch + ((r * STRIDE) * a.PW + c0 * STRIDE) * CB;
+        const float *prow = patch + ((r * a.sh) * a.PW + c0 * STRIDE) * CB;
         for (int kh = 0; kh < a.Fh; ++kh)
         {
             for (int kw = 0; kw < a.Fw; ++kw)
@@ -294,7 +295,7 @@ conv2d_first_f32_kernel(const ConvArgs a, const float *__restrict__ in, const fl
     const float *img = in + (size_t)n * a.C * a.H * a.W;
     for (int kh = 0; kh < a.Fh; ++kh)
     {
-        const int ih = oh * a.stride - a.pad_t + kh;
+        const int ih = oh * a.sh - a.pad_t + kh;
         if (ih < 0 || ih >= a.H)
             continue;
         for (int kw = 0; kw < a.Fw; ++kw)
@@ -570,7 +571,10 @@ int conv2d_f32_impl(const small_b200_layer *L, int pool, const float *in, const 
     a.pool = pool;
     a.N = L->N; a.C = L->C; a.K = L->K; a.H = L->H; a.W = L->W;
     a.Fh = L->Fh; a.Fw = L->Fw; a.stride = L->stride; a.pad_t = L->pad_t; a.pad_l = L->pad_l;
-    a.Ho = out_dim(L->H, L->pad_t, L->pad_b, L->Fh, L->stride);
+    a.sh = row_stride(L);
+    if (pool && a.sh != L->stride)
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D+MaxPool2D<float> ERROR: shape not covered by the fused kernel.");
+    a.Ho = out_dim(L->H, L->pad_t, L->pad_b, L->Fh, a.sh);
     a.Wo = out_dim(L->W, L->pad_l, L->pad_r, L->Fw, L->stride);
     a.accumulate = L->accumulate; a.act = L->act; a.slope = L->slope;
     if (a.N == 0 || a.Ho == 0 || a.Wo == 0)
@@ -594,7 +598,7 @@ int conv2d_f32_impl(const small_b200_layer *L, int pool, const float *in, const 
             conv2d_first_pool_f32_kernel<<<grid, 128, smem, st>>>(a, in, filt, bias, out);
             return launched("conv2d_first_pool_f32_kernel");
         }
-        if (L->C == 3 && L->Fh == 3 && L->Fw == 3 && L->stride == 1 && !L->accumulate && a.Ho % 2 == 0 &&
+        if (L->C == 3 && L->Fh == 3 && L->Fw == 3 && L->stride == 1 && a.sh == 1 && !L->accumulate && a.Ho % 2 == 0 &&
             a.Wo % 2 == 0 && a.Ho > 0 && a.Wo > 0)
         {
             // 2x2 output blocks from a register patch, rows written through shared memory
@@ -608,7 +612,7 @@ int conv2d_f32_impl(const small_b200_layer *L, int pool, const float *in, const 
     }
 
     a.cbs = L->C / CB;
-    a.PH = (TH - 1) * L->stride + L->Fh;
+    a.PH = (TH - 1) * a.sh + L->Fh;
     a.PW = (TW - 1) * L->stride + L->Fw;
     a.tiles_h = (a.Ho + TH - 1) / TH;
     a.tiles_w = (a.Wo + TW - 1) / TW;
@@ -657,7 +661,7 @@ int small_b200_conv2d_f32(const small_b200_layer *L, const float *in, const floa
 
 int small_b200_conv2d_maxpool_f32_supported(const small_b200_layer *conv, const small_b200_layer *pool)
 {
-    if (!conv || !pool || conv->stride != 1 || conv->accumulate)
+    if (!conv || !pool || conv->stride != 1 || row_stride(conv) != 1 || row_stride(pool) != pool->stride || conv->accumulate)
         return 0;
     if (conv->K % (conv->C < CB ? 16 : 32) != 0) // the staged kernel pairs rows inside a warp: 32 or 64 channels per CTA
         return 0;

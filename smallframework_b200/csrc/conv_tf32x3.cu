@@ -891,7 +891,7 @@ bool plan_tiled(const small_b200_layer *L, TcArgs &a)
 // Tiling and shared-memory plan of one layer; false when the shape is not covered.
 bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm)
 {
-    if (!L || L->stride != 1 || L->C % CB != 0 || L->K % CB != 0 || L->C <= 0 || L->K <= 0)
+    if (!L || L->stride != 1 || row_stride(L) != 1 || L->C % CB != 0 || L->K % CB != 0 || L->C <= 0 || L->K <= 0)
         return false;
     if (L->H <= 0 || L->W <= 0 || L->Fh <= 0 || L->Fw <= 0 || L->Fw > 16 || L->Fh > 16)
         return false;

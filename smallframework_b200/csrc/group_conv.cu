@@ -23,7 +23,7 @@ using namespace sb;
 
 struct GArgs
 {
-    int N, G, C, K, H, W, Ho, Wo, Fh, Fw, stride, pad_t, pad_l;
+    int N, G, C, K, H, W, Ho, Wo, Fh, Fw, stride, sh, pad_t, pad_l; // sh: stride along the height
     int accumulate, act;
     float slope;
     int zero_in, zero_filt, lshift, rshift, mult, k_zero;
@@ -56,7 +56,7 @@ groupconv2d_f32_kernel(const GArgs a, const float *__restrict__ in, const float 
     const float *fk = filt + ((size_t)gb * a.K + k0) * fstride_k + q * 4;
     const size_t oplane = (size_t)a.Ho * a.Wo * CB;
     float *dst = out + (((size_t)n * (a.G / CB) + gb) * a.K + k0) * oplane + ((size_t)oh * a.Wo + ow) * CB + q * 4;
-    const int h0 = oh * a.stride - a.pad_t, w0 = ow * a.stride - a.pad_l;
+    const int h0 = oh * a.sh - a.pad_t, w0 = ow * a.stride - a.pad_l;
     float4 acc[KT];
 #pragma unroll
     for (int j = 0; j < KT; ++j)
@@ -129,7 +129,7 @@ groupconv2d_u8_kernel(const GArgs a, const uint8_t *__restrict__ in, const uint8
     const size_t plane = (size_t)a.H * a.W * CB;
     const uint8_t *src = in + (size_t)i * a.C * plane;
     const uint8_t *fk = filt + ((size_t)gb * a.K + k) * a.C * a.Fh * a.Fw * CB;
-    const int h0 = oh * a.stride - a.pad_t, w0 = ow * a.stride - a.pad_l;
+    const int h0 = oh * a.sh - a.pad_t, w0 = ow * a.stride - a.pad_l;
     int acc[CB];
 #pragma unroll
     for (int g = 0; g < CB; ++g)
@@ -159,11 +159,71 @@ groupconv2d_u8_kernel(const GArgs a, const uint8_t *__restrict__ in, const uint8
     *reinterpret_cast<uint4 *>(out + o * CB) = requant_pack16(acc, a.lshift, a.rshift, a.mult);
 }
 
+// Block-diagonal convolution: `groups` independent dense convolutions from 16 to 16 channels, group g
+// on channel block g -- the second stage of the reference's fused grouped forms
+// (fused_interface_abstract.hpp:2740-2760: G = output_groups, K = C_ob, F_c = C_ib):
+//     in [N][G][H][W][16 c]   filt [G][Fh][Fw][16 c][16 k]   out [N][G][Ho][Wo][16 k]
+// thread = four output channels of one output pixel of one group; flat index over [N][G][Ho][Wo][4].
+__global__ void __launch_bounds__(256)
+blockconv2d_f32_kernel(const GArgs a, const float *__restrict__ in, const float *__restrict__ filt,
+                       const float *__restrict__ bias, float *__restrict__ out)
+{
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = (long long)a.N * a.G * a.Ho * a.Wo * 4;
+    if (i >= total)
+        return;
+    const long long o = i;
+    const int q = (int)(i & 3); i >>= 2;
+    const int ow = (int)(i % a.Wo); i /= a.Wo;
+    const int oh = (int)(i % a.Ho); i /= a.Ho; // i = n * G + g
+    const int g = (int)(i % a.G);
+    const float *src = in + (size_t)i * a.H * a.W * CB;
+    const float *fg = filt + (size_t)g * a.Fh * a.Fw * CB * CB + q * 4;
+    float *dst = out + o * 4;
+    float4 acc = a.accumulate ? ld4(dst) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (bias)
+    {
+        const float4 b = ld4(bias + (size_t)g * CB + q * 4);
+        acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+    }
+    const int h0 = oh * a.sh - a.pad_t, w0 = ow * a.stride - a.pad_l;
+    for (int kh = 0; kh < a.Fh; ++kh)
+    {
+        const int ih = h0 + kh;
+        if (ih < 0 || ih >= a.H)
+            continue;
+        for (int kw = 0; kw < a.Fw; ++kw)
+        {
+            const int iw = w0 + kw;
+            if (iw < 0 || iw >= a.W)
+                continue;
+            const float *px = src + ((size_t)ih * a.W + iw) * CB;
+            const float *ft = fg + (size_t)(kh * a.Fw + kw) * CB * CB;
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4)
+            {
+                const float4 x = ld4(px + c4 * 4);
+                const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                {
+                    const float4 f = __ldg(reinterpret_cast<const float4 *>(ft + (c4 * 4 + j) * CB));
+                    acc.x = fmaf(xs[j], f.x, acc.x); acc.y = fmaf(xs[j], f.y, acc.y);
+                    acc.z = fmaf(xs[j], f.z, acc.z); acc.w = fmaf(xs[j], f.w, acc.w);
+                }
+            }
+        }
+    }
+    acc.x = apply_act(acc.x, a.act, a.slope); acc.y = apply_act(acc.y, a.act, a.slope);
+    acc.z = apply_act(acc.z, a.act, a.slope); acc.w = apply_act(acc.w, a.act, a.slope);
+    *reinterpret_cast<float4 *>(dst) = acc;
+}
+
 int check_group(const small_b200_layer *L, int groups, const char *name, GArgs &a)
 {
     if (!L)
         return fail(SMALL_B200_INVALID_ARGUMENT, std::string(name) + " ERROR: null layer.");
-    if (L->stride != 1 && L->stride != 2)
+    if ((L->stride != 1 && L->stride != 2) || L->stride_h < 0 || L->stride_h > 2)
         return fail(SMALL_B200_INVALID_ARGUMENT, std::string(name) + " ERROR: stride unsupported.");
     if (L->C <= 0 || L->K <= 0)
         return fail(SMALL_B200_INVALID_ARGUMENT, std::string(name) + " ERROR: in_channels unsupported.");
@@ -173,8 +233,8 @@ int check_group(const small_b200_layer *L, int groups, const char *name, GArgs &
         L->pad_b < 0 || L->pad_l < 0 || L->pad_r < 0)
         return fail(SMALL_B200_INVALID_ARGUMENT, std::string(name) + " ERROR: bad shape.");
     a.N = L->N; a.G = groups; a.C = L->C; a.K = L->K; a.H = L->H; a.W = L->W; a.Fh = L->Fh; a.Fw = L->Fw;
-    a.stride = L->stride; a.pad_t = L->pad_t; a.pad_l = L->pad_l;
-    a.Ho = out_dim(L->H, L->pad_t, L->pad_b, L->Fh, L->stride);
+    a.stride = L->stride; a.sh = row_stride(L); a.pad_t = L->pad_t; a.pad_l = L->pad_l;
+    a.Ho = out_dim(L->H, L->pad_t, L->pad_b, L->Fh, a.sh);
     a.Wo = out_dim(L->W, L->pad_l, L->pad_r, L->Fw, L->stride);
     a.accumulate = L->accumulate; a.act = L->act; a.slope = L->slope;
     a.zero_in = L->zero_in; a.zero_filt = L->zero_filt; a.lshift = L->lshift; a.rshift = L->rshift;
@@ -203,6 +263,26 @@ int small_b200_groupconv2d_f32(const small_b200_layer *L, int32_t groups, const 
     return launched("groupconv2d_f32_kernel");
 }
 
+int small_b200_blockconv2d_f32(const small_b200_layer *L, int32_t groups, const float *in, const float *filt,
+                               const float *bias, float *out, void *stream)
+{
+    if (!L)
+        return fail(SMALL_B200_INVALID_ARGUMENT, "GroupConv2D<float> (fused forms) ERROR: null layer.");
+    small_b200_layer B = *L;
+    B.C = B.K = CB;
+    GArgs a{};
+    if (groups <= 0)
+        return fail(SMALL_B200_INVALID_ARGUMENT, "GroupConv2D<float> (fused forms) ERROR: output_groups unsupported.");
+    if (int rc = check_group(&B, CB, "GroupConv2D<float> (fused forms)", a)) // the group count has no block here
+        return rc;
+    a.G = groups;
+    const long long items = (long long)a.N * a.G * a.Ho * a.Wo * 4;
+    if (items == 0)
+        return SMALL_B200_OK;
+    blockconv2d_f32_kernel<<<(unsigned)((items + 255) / 256), 256, 0, as_stream(stream)>>>(a, in, filt, bias, out);
+    return launched("blockconv2d_f32_kernel");
+}
+
 int small_b200_groupconv2d_u8(const small_b200_layer *L, int32_t groups, const uint8_t *in, const uint8_t *filt,
                               const int32_t *bias, uint8_t *out, void *stream)
 {
@@ -211,6 +291,8 @@ int small_b200_groupconv2d_u8(const small_b200_layer *L, int32_t groups, const u
         return rc;
     if (a.lshift < 0 || a.lshift > 31 || a.rshift < 0 || a.rshift > 31)
         return fail(SMALL_B200_INVALID_ARGUMENT, "GroupConv2D<quint8> ERROR: shift out of range.");
+    if (a.sh != a.stride)
+        return fail(SMALL_B200_INVALID_ARGUMENT, "GroupConv2D<quint8> ERROR: stride unsupported.");
     if (a.accumulate)
         return fail(SMALL_B200_INVALID_ARGUMENT,
                     "PartialGroupConv2D<quint8> ERROR: the int32 partial-sum form is not provided.");

@@ -570,6 +570,9 @@ int check_quant(const small_b200_layer *L, const char *name)
 {
     if (L->lshift < 0 || L->lshift > 31 || L->rshift < 0 || L->rshift > 31)
         return fail(SMALL_B200_INVALID_ARGUMENT, std::string(name) + " ERROR: shift out of range.");
+    if (row_stride(L) != L->stride)
+        return fail(SMALL_B200_INVALID_ARGUMENT, std::string(name) + " ERROR: stride unsupported (a row stride of its own "
+                                                                      "is provided for the fp32 layers only).");
     return SMALL_B200_OK;
 }
 

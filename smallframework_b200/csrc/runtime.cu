@@ -12,7 +12,7 @@ int check_window_layer(const small_b200_layer *L, const char *name, bool dense, 
 {
     if (!L)
         return fail(SMALL_B200_INVALID_ARGUMENT, std::string(name) + " ERROR: null layer.");
-    if (L->stride < 1 || L->stride > max_stride)
+    if (L->stride < 1 || L->stride > max_stride || L->stride_h < 0 || L->stride_h > max_stride)
         return fail(SMALL_B200_INVALID_ARGUMENT, std::string(name) + " ERROR: stride unsupported.");
     const bool first_layer = dense && (L->C == 1 || L->C == 2 || L->C == 3);
     if (L->C <= 0 || (L->C % CB != 0 && !first_layer))

@@ -16,6 +16,7 @@ using namespace sb;
 struct WinArgs
 {
     int N, C, H, W, Ho, Wo, Fh, Fw, stride, pad_t, pad_l;
+    int sh; // stride along the height (`stride` is along the width)
     int accumulate, act;
     float slope;
     float norm;
@@ -49,7 +50,7 @@ window_f32_kernel(const WinArgs a, const float *__restrict__ in, const float *__
         return;
     const float *src = in + (((size_t)n * (a.C / CB) + cb) * a.H * a.W) * CB + q * 4;
     float *dst = out + ((((size_t)n * (a.C / CB) + cb) * a.Ho + oh) * a.Wo + ow) * CB + q * 4;
-    const int h0 = oh * a.stride - a.pad_t, w0 = ow * a.stride - a.pad_l;
+    const int h0 = oh * a.sh - a.pad_t, w0 = ow * a.stride - a.pad_l;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (OP == 0)
     {
@@ -181,7 +182,7 @@ dwconv3x3_f32_strip_kernel(const WinArgs a, int strips, const float *__restrict_
         }
 }
 
-// OP: 0 ReLU, 1 LeakyReLU, 2 Accum (out += in).  n4 = number of float4.
+// OP: 0 ReLU, 1 LeakyReLU, 2 Accum (out += in), 3 scale (out = in * slope).  n4 = number of float4.
 template <int OP>
 __global__ void __launch_bounds__(256)
 eltwise_f32_kernel(long long n4, const float *in, float slope, float *out) // in may alias out
@@ -199,6 +200,10 @@ eltwise_f32_kernel(long long n4, const float *in, float slope, float *out) // in
         {
             x.x = x.x > 0.f ? x.x : x.x * slope; x.y = x.y > 0.f ? x.y : x.y * slope;
             x.z = x.z > 0.f ? x.z : x.z * slope; x.w = x.w > 0.f ? x.w : x.w * slope;
+        }
+        else if (OP == 3)
+        {
+            x.x *= slope; x.y *= slope; x.z *= slope; x.w *= slope;
         }
         else
         {
@@ -228,9 +233,9 @@ bias_f32_kernel(int N, int C, long long hw, const float *__restrict__ bias, int 
 }
 
 __global__ void __launch_bounds__(256)
-upsample2_f32_kernel(int N, int C, int H, int W, const float *__restrict__ in, float *__restrict__ out)
+upsample2_f32_kernel(int N, int C, int H, int W, int sh, const float *__restrict__ in, float *__restrict__ out)
 {
-    const int Ho = 2 * H, Wo = 2 * W;
+    const int Ho = sh * H, Wo = 2 * W; // sh = 1: the 1-D form, rows are batch entries
     const long long total = (long long)N * (C / CB) * Ho * Wo * 4;
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total)
@@ -239,7 +244,7 @@ upsample2_f32_kernel(int N, int C, int H, int W, const float *__restrict__ in, f
     const int q = (int)(i & 3); i >>= 2;
     const int ow = (int)(i % Wo); i /= Wo;
     const int oh = (int)(i % Ho); i /= Ho; // i = n*(C/16)+cb
-    st4(out + o * 4, ld4(in + ((i * H + oh / 2) * W + ow / 2) * CB + q * 4));
+    st4(out + o * 4, ld4(in + ((i * H + oh / sh) * W + ow / 2) * CB + q * 4));
 }
 
 // One CTA per image: exp pass with the sum kept in registers, block reduction with warp
@@ -297,7 +302,8 @@ int fill(const small_b200_layer *L, WinArgs &a)
 {
     a.N = L->N; a.C = L->C; a.H = L->H; a.W = L->W; a.Fh = L->Fh; a.Fw = L->Fw;
     a.stride = L->stride; a.pad_t = L->pad_t; a.pad_l = L->pad_l;
-    a.Ho = out_dim(L->H, L->pad_t, L->pad_b, L->Fh, L->stride);
+    a.sh = row_stride(L);
+    a.Ho = out_dim(L->H, L->pad_t, L->pad_b, L->Fh, a.sh);
     a.Wo = out_dim(L->W, L->pad_l, L->pad_r, L->Fw, L->stride);
     a.accumulate = L->accumulate; a.act = L->act; a.slope = L->slope;
     a.norm = (float)(1.0 / (1.0 * L->Fh * L->Fw)); // abstract_layer.hpp:565-569
@@ -328,7 +334,7 @@ int small_b200_dwconv2d_f32(const small_b200_layer *L, const float *in, const fl
     const long long items = (long long)a.N * (a.C / CB) * a.Ho * a.Wo * 4;
     if (items == 0)
         return SMALL_B200_OK;
-    if (a.Fh == 3 && a.Fw == 3 && a.Wo >= 4)
+    if (a.Fh == 3 && a.Fw == 3 && a.Wo >= 4 && a.sh == a.stride)
     {
         const int strips = (a.Wo + 3) / 4;
         const long long threads = (long long)a.N * (a.C / CB) * a.Ho * strips * 4;
@@ -393,6 +399,16 @@ int small_b200_leaky_relu_f32(int64_t n, const float *in, float slope, float *ou
     return launched("leaky_relu_f32");
 }
 
+int small_b200_scale_f32(int64_t n, const float *in, float scale, float *out, void *stream)
+{
+    if (int rc = check_n(n, "Dropout<float>"))
+        return rc;
+    if (n == 0)
+        return SMALL_B200_OK;
+    eltwise_f32_kernel<3><<<grid_stride_blocks(n / 4), 256, 0, as_stream(stream)>>>(n / 4, in, scale, out);
+    return launched("scale_f32");
+}
+
 int small_b200_accum_f32(int64_t n, const float *in, float *out, void *stream)
 {
     if (int rc = check_n(n, "Accum<float>"))
@@ -423,8 +439,19 @@ int small_b200_upsample2d_f32(int32_t N, int32_t C, int32_t H, int32_t W, const 
     const long long items = (long long)N * (C / CB) * H * W * 16;
     if (items <= 0)
         return SMALL_B200_OK;
-    upsample2_f32_kernel<<<blocks_for(items), 256, 0, as_stream(stream)>>>(N, C, H, W, in, out);
+    upsample2_f32_kernel<<<blocks_for(items), 256, 0, as_stream(stream)>>>(N, C, H, W, 2, in, out);
     return launched("upsample2d_f32");
+}
+
+int small_b200_upsample1d_f32(int32_t N, int32_t C, int32_t rows, int32_t W, const float *in, float *out, void *stream)
+{
+    if (C <= 0 || C % CB != 0)
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Upsample<float> ERROR: in_channels unsupported.");
+    const long long items = (long long)N * (C / CB) * rows * W * 8;
+    if (items <= 0)
+        return SMALL_B200_OK;
+    upsample2_f32_kernel<<<blocks_for(items), 256, 0, as_stream(stream)>>>(N, C, rows, W, 1, in, out);
+    return launched("upsample1d_f32");
 }
 
 int small_b200_softmax_f32(int32_t N, int64_t elems_per_image, const float *in, float *out, void *stream)

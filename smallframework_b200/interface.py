@@ -359,6 +359,14 @@ def LeakyReLUActivation(input_channels, input_height, input_width, input_buf, fi
     check(lib().small_b200_leaky_relu_f32(n, _ptr(input_buf), slope, _ptr(output_buf), _stream(stream)))
 
 
+def Dropout(input_channels, input_height, input_width, input_buf, filter_buf, output_buf, *, batch=1, stream=None):
+    """small::Dropout (:1697): output = input * rate, the rate arriving as a one-element buffer (or a float)."""
+    _chan_check("Dropout<float>", input_channels)
+    rate = float(filter_buf.t[0].item()) if isinstance(filter_buf, FloatBuffer) else float(filter_buf)
+    n = batch * input_channels * input_height * input_width
+    check(lib().small_b200_scale_f32(n, _ptr(input_buf), rate, _ptr(output_buf), _stream(stream)))
+
+
 def Accum(input_channels, input_height, input_width, input_buf, output_buf, *, batch=1, stream=None):
     """small::Accum (:1950): output += input."""
     _chan_check("Accum<float>", input_channels)

@@ -106,3 +106,60 @@ def test_model_classes_as_cuda_graph(oracle, tensor_core, tmp_path):
     err = float(np.abs(got.astype(np.float64) - want).max() / np.abs(want).max())
     print(f"TinyYoloV2 Model class vs the oracle, SMALL_B200_TENSOR_CORE={tensor_core}: {err:.2e}")
     assert err <= 1e-4
+
+
+# ---- the reference's demo programs (demo/CMakeLists.txt:26-78), built unchanged
+FUSED_DRIVERS = ["conv_fused_MAX_POOL", "conv_fused_MAX_POOL_n_bias", "conv_fused_MAX_POOL_n_bias_n_relu",
+                 "conv_fused_DW_CONV", "conv_fused_DW_CONV_n_bias", "conv_fused_DW_CONV_n_bias_n_relu"]
+# <C_i> <H> <W>  conv <k> <stride> <pad>  <C_o>  second layer <k> <stride> <pad> <C_o>
+FUSED_ARGS = {
+    "MAX_POOL": [["16", "32", "32", "3", "1", "f", "32", "2", "2", "v", "32"],      # one kernel (pool in registers)
+                 ["32", "13", "13", "3", "1", "f", "64", "3", "2", "v", "64"],      # 3x3 pool: two kernels
+                 ["3", "64", "64", "3", "1", "f", "16", "2", "2", "v", "16"]],      # first layer
+    "DW_CONV": [["16", "24", "24", "1", "1", "v", "32", "3", "1", "f", "32"],
+                ["32", "12", "12", "3", "1", "f", "64", "3", "2", "f", "64"]],
+}
+
+
+@pytest.mark.parametrize("name", FUSED_DRIVERS)
+def test_reference_fused_block_driver(name):
+    """demo/fused_block_driver.cpp (conv_fused_*.exe of the reference's build): a fused call
+    (Conv2D[_Bias][_ReLU]_Maxpool2D / ..._DepthwiseConv2D...) against the unfused pair of calls, with the
+    driver's own element-wise check (it asserts)."""
+    exe = os.path.join(BUILD, "bin", name)
+    if not os.path.exists(exe):
+        pytest.skip(f"{exe} not built (run make -C tests/reference_drivers where the reference is mounted)")
+    for argv in FUSED_ARGS["MAX_POOL" if "MAX_POOL" in name else "DW_CONV"]:
+        r = subprocess.run([exe] + argv, cwd=os.path.join(BUILD, "run"), env=dict(os.environ, OMP_NUM_THREADS="4"),
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900)
+        tail = "\n".join(r.stdout.splitlines()[-15:])
+        assert r.returncode == 0, f"{name} {' '.join(argv)} failed (rc {r.returncode}):\n{tail}"
+
+
+MODEL_DEMOS = ["model_mobilenet", "model_mobilenet_reshuffled", "model_resnet", "model_resnet_1D", "model_dscnn",
+               "model_dscnn_square", "model_autoencoder", "model_tinyyolov2"]
+
+
+@pytest.mark.parametrize("name", MODEL_DEMOS)
+def test_reference_model_demo(name):
+    """The reference's model demos (model_*.exe): each builds its network from the functional interface
+    and from the Layer classes, compares the two and times them."""
+    exe = os.path.join(BUILD, "bin", name)
+    if not os.path.exists(exe):
+        pytest.skip(f"{exe} not built (run make -C tests/reference_drivers where the reference is mounted)")
+    r = subprocess.run([exe], cwd=os.path.join(BUILD, "run"), env=dict(os.environ, OMP_NUM_THREADS="4"),
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=1800)
+    tail = "\n".join(r.stdout.splitlines()[-15:])
+    assert r.returncode == 0, f"{name} failed (rc {r.returncode}):\n{tail}"
+
+
+def test_every_fused_form_through_the_small_boundary():
+    """tests/drivers/fused_forms.cpp: the 15 fused 2-D functions, the 1-D family with stride 2, UpSample1D
+    and Dropout through the small:: headers, each against the unfused composition or a direct loop."""
+    exe = os.path.join(BUILD, "bin", "fused_forms")
+    if not os.path.exists(exe):
+        pytest.skip(f"{exe} not built (run make -C tests/reference_drivers where the reference is mounted)")
+    r = subprocess.run([exe], env=dict(os.environ, OMP_NUM_THREADS="4"), stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT, text=True, timeout=900)
+    print(r.stdout[-3000:])
+    assert r.returncode == 0, r.stdout[-3000:]
