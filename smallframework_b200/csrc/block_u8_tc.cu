@@ -42,8 +42,6 @@
 // j + 1 overlaps the stage-1 epilogue of image j and stage 2 of image j - 1.
 // Requirements (else the layers run as separate kernels): H*W <= 128; filter zero points -128
 // (weights enter the tensor core as signed bytes); zero point of the intermediate 0 or -128.
-#include <cstdlib>
-
 #include "tc_common.cuh"
 
 namespace
@@ -741,19 +739,16 @@ int dispatch(const BlockArgs &a, int K, bool stem, size_t smem, const uint8_t *i
              const uint8_t *f2, const int32_t *b2, uint8_t *out, cudaStream_t st)
 {
     const bool sgn = a.zero_in1 != 0;
-    static const int ew = [] { const char *e = std::getenv("SMALL_B200_BLOCK_EW"); return (e && e[0] == '4') ? 4 : 8; }();
-#define SB_BLOCK_CASE(KK, EE)                                                                                    \
-    if (K == KK && ew == EE)                                                                                     \
+#define SB_BLOCK_CASE(KK)                                                                                        \
+    if (K == KK)                                                                                                 \
     {                                                                                                            \
         if (!stem)                                                                                               \
-            return launch_block<KK, false, POOL, false, EE>(a, smem, in, f1, b1, f2, b2, out, st);               \
-        return sgn ? launch_block<KK, true, POOL, true, EE>(a, smem, in, f1, b1, f2, b2, out, st)                \
-                   : launch_block<KK, true, POOL, false, EE>(a, smem, in, f1, b1, f2, b2, out, st);              \
+            return launch_block<KK, false, POOL, false>(a, smem, in, f1, b1, f2, b2, out, st);                   \
+        return sgn ? launch_block<KK, true, POOL, true>(a, smem, in, f1, b1, f2, b2, out, st)                    \
+                   : launch_block<KK, true, POOL, false>(a, smem, in, f1, b1, f2, b2, out, st);                  \
     }
-    SB_BLOCK_CASE(32, 8)
-    SB_BLOCK_CASE(64, 8)
-    SB_BLOCK_CASE(32, 4)
-    SB_BLOCK_CASE(64, 4)
+    SB_BLOCK_CASE(32)
+    SB_BLOCK_CASE(64)
 #undef SB_BLOCK_CASE
     return fail(SMALL_B200_INVALID_ARGUMENT, "fused uint8 block: channel count not covered");
 }
