@@ -239,6 +239,48 @@ int small_b200_softmax_f32(int32_t N, int64_t elems_per_image, const float *in, 
 int small_b200_concat(int32_t N, size_t bytes0, const void *in0, size_t bytes1, const void *in1,
                       void *out, void *stream);
 
+/* ---- weights ----------------------------------------------------------------------- */
+/* detail::initialize_conv2d_buffers (include/small/Conv2DLayer.hpp:135-341) on the device: the
+ * unpacked filter [K_effective][C][Fh][Fw] is packed to [K_padded/16][C/cib][Fh][Fw][cib][16] with
+ * zero filters for the padded output channels (:393-404), the bias (may be NULL) is padded with
+ * zeros, and batch-normalisation parameters (all four or none) are folded into both:
+ * scale = gamma / sqrt(var + eps), filters *= scale, bias = beta - mean * scale (no bias) or
+ * beta + scale * (bias - mean).  packed_bias (K_padded floats) may be NULL when there is neither a
+ * bias nor batch normalisation.  All pointers are device pointers.  Bit-identical to the host code. */
+int small_b200_conv_weights_prepare_f32(int32_t K_padded, int32_t K_effective, int32_t C, int32_t Fh, int32_t Fw,
+                                        const float *filters, const float *bias, const float *bn_weight,
+                                        const float *bn_bias, const float *bn_running_mean,
+                                        const float *bn_running_var, float bn_eps, float *packed_filters,
+                                        float *packed_bias, void *stream);
+
+/* ---- detection head ---------------------------------------------------------------- */
+/* small::YOLOLayer::compute_output (include/small/YOLOLayer.hpp:96-222): the packed activation
+ * [N][C_padded/16][H][W][16], read as [anchor][5 + classes][H][W], becomes one record
+ * [x, y, w, h, objectness, class scores...] per anchor and pixel:
+ *   x = stride * (sigmoid(v) + column), y = stride * (sigmoid(v) + row), w = exp(v) * anchor_w,
+ *   h = exp(v) * anchor_h, everything else sigmoid(v).
+ * out: [N][num_anchors * H * W][5 + num_classes], prediction index (anchor * H + row) * W + column.
+ * anchor_wh is a HOST array of num_anchors (width, height) pairs (at most 16).  Channels beyond
+ * num_anchors * (5 + num_classes) are the padding of the layer before and are ignored. */
+int small_b200_yolo_decode_f32(int32_t N, int32_t C_padded, int32_t H, int32_t W, int32_t num_anchors,
+                               int32_t num_classes, float stride, const float *anchor_wh, const float *in,
+                               float *out, void *stream);
+/* Darknet::process_outputs + small::basic_nms (include/small/models/Darknet.hpp:78-122,
+ * include/small/non_max_suppression.hpp:98-155) for num_pred records of 5 + num_classes floats (the
+ * outputs of one or several decode calls, back to back): every (record, class) pair whose objectness
+ * AND class score exceed confidence_threshold is a detection; detections are ordered by objectness,
+ * descending (ties: the order the host loop meets them in), and a kept detection removes every later
+ * one of its class whose IoU with it is not below iou_threshold.
+ *   detections  [max_detections][7] = x, y, w, h, objectness, class score, class id; in keep order
+ *   counts      [2] (device) = detections that survive (may exceed max_detections: only that many
+ *               are written), pairs above the confidence threshold (if it exceeds max_candidates,
+ *               the surplus was dropped and the result is incomplete)
+ *   scratch     small_b200_nms_scratch_bytes(max_candidates) bytes of device memory */
+size_t small_b200_nms_scratch_bytes(int32_t max_candidates);
+int small_b200_nms_f32(const float *pred, int32_t num_pred, int32_t num_classes, float confidence_threshold,
+                       float iou_threshold, int32_t max_candidates, void *scratch, int32_t max_detections,
+                       float *detections, int32_t *counts, void *stream);
+
 /* ---- uint8 layers ------------------------------------------------------------------ */
 /* small::Conv2D<QUInt8Buffer> (:229-404) with an optional per-channel int32 bias added to
  * the accumulator seed.  The int32 partial sums never leave the chip, so the output buffer

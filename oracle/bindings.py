@@ -178,6 +178,37 @@ class Oracle:
         x = _u8(x); o = np.empty_like(x)
         self.lib.so_relu_u8(C.c_int64(x.size), C.byref(q), _p(x), _p(o)); return o
 
+    def conv_weights_prepare_f32(self, K, w, bias=None, bn=None, eps=1e-5, cb=16):
+        """w: [Keff, C, Fh, Fw]; bn: (gamma, beta, mean, var) or None.  Returns (packed filters, packed bias or None)."""
+        Keff, Cn, Fh, Fw = w.shape
+        w = _f32(w)
+        packed = np.zeros(K * Cn * Fh * Fw, np.float32)
+        pb = np.zeros(K, np.float32) if (bias is not None or bn is not None) else None
+        b = _f32(bias) if bias is not None else None
+        g = [_f32(v) for v in bn] if bn is not None else [None] * 4
+        self.lib.so_conv_weights_prepare_f32(K, Keff, Cn, Fh, Fw, cb, _p(w), _p(b), _p(g[0]), _p(g[1]), _p(g[2]), _p(g[3]),
+                                             C.c_float(eps), _p(packed), _p(pb))
+        return packed, pb
+
+    # -- detection head
+    def yolo_decode_f32(self, Cp, H, W, cb, anchors, num_classes, stride, x):
+        """anchors: list of (w, h); returns [len(anchors)*H*W, 5 + num_classes]."""
+        x = _f32(x)
+        a = _f32(np.asarray(anchors, np.float32).ravel())
+        o = np.zeros((len(anchors) * H * W, num_classes + 5), np.float32)
+        self.lib.so_yolo_decode_f32(Cp, H, W, cb, len(anchors), num_classes, C.c_float(stride), _p(a), _p(x), _p(o))
+        return o
+
+    def nms_f32(self, pred, num_classes, conf_thr, iou_thr, max_det=4096):
+        """pred: [P, 5 + num_classes]; returns (kept rows [n, 7], candidates above the threshold)."""
+        pred = _f32(pred)
+        o = np.zeros((max_det, 7), np.float32)
+        cand = C.c_int32(0)
+        self.lib.so_nms_f32.restype = C.c_int32
+        n = self.lib.so_nms_f32(_p(pred), pred.shape[0], num_classes, C.c_float(conf_thr), C.c_float(iou_thr),
+                                max_det, _p(o), C.byref(cand))
+        return o[:min(n, max_det)], cand.value
+
 
 class Ref:
     """The unmodified reference behind ref_shim.cpp.  platform: 'ref' or 'zen2'."""

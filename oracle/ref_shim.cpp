@@ -9,6 +9,7 @@
 // It serves as the second opinion for oracle/small_oracle.c and as the timed CPU
 // baseline.  The shipped CUDA library never loads it.
 #include <small.h>
+#include <small/Conv2DLayer.hpp>
 
 #include <cstdint>
 #include <cstdlib>
@@ -85,6 +86,27 @@ int ref_quint8_cb() { return 0; }
 void ref_set_threads(int n)
 {
     setenv("OMP_NUM_THREADS", std::to_string(n).c_str(), 1);
+}
+
+// detail::initialize_conv2d_buffers (include/small/Conv2DLayer.hpp:135): what a Conv2DLayer does to its
+// weights when it is built.  n_bias / n_bn = 0 mean "no bias" / "no batch normalisation".
+int ref_init_conv2d_buffers(int K, int Keff, int C, int Fh, int Fw, const float *filt, const float *bias, int n_bias,
+                            const float *gamma, const float *beta, const float *mean, const float *var, int n_bn,
+                            float eps, float *packed, float *packed_bias)
+{
+    GUARD({
+        auto F = make<small::FloatBuffer>(filt, (size_t)Keff * C * Fh * Fw);
+        auto B = make<small::FloatBuffer>(bias, (size_t)n_bias);
+        auto G = make<small::FloatBuffer>(gamma, (size_t)n_bn);
+        auto Be = make<small::FloatBuffer>(beta, (size_t)n_bn);
+        auto M = make<small::FloatBuffer>(mean, (size_t)n_bn);
+        auto V = make<small::FloatBuffer>(var, (size_t)n_bn);
+        small::FloatBuffer PF, PB;
+        small::detail::initialize_conv2d_buffers(K, Keff, C, Fh, Fw, F, B, G, Be, M, V, eps, false, PF, PB);
+        std::memcpy(packed, PF.data(), PF.size() * sizeof(float));
+        if (PB.size())
+            std::memcpy(packed_bias, PB.data(), PB.size() * sizeof(float));
+    })
 }
 
 // ------------------------------------------------------------------ float ops

@@ -513,3 +513,161 @@ void so_avgpool2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in, ui
                     (uint8_t)so_requant(acc, q->lshift, q->rshift, q->multiplier);
             }
 }
+
+/* ---------------------------------------------------------------- detection head */
+static float so_sigmoid(float v)
+{
+    /* include/small/YOLOLayer.hpp:22-24: 1.0 / (1.0 + std::exp(-v)) in double, result back to float */
+    return (float)(1.0 / (1.0 + (double)expf(-v)));
+}
+
+void so_yolo_decode_f32(int32_t Cp, int32_t H, int32_t W, int32_t cb, int32_t num_anchors, int32_t num_classes,
+                        float stride, const float *anchor_wh, const float *in, float *out)
+{
+    /* include/small/YOLOLayer.hpp:168-222 on the packed input (the reference unpacks first) */
+    const int32_t rec = num_classes + 5;
+    size_t pred = 0;
+    for (int32_t a = 0; a < num_anchors; ++a)
+        for (int32_t h = 0; h < H; ++h)
+            for (int32_t w = 0; w < W; ++w, ++pred)
+                for (int32_t j = 0; j < rec; ++j)
+                {
+                    const float v = in[act_idx(H, W, cb, a * rec + j, h, w)];
+                    float r;
+                    if (j == 0)
+                        r = stride * (so_sigmoid(v) + (float)w);
+                    else if (j == 1)
+                        r = stride * (so_sigmoid(v) + (float)h);
+                    else if (j == 2)
+                        r = expf(v) * anchor_wh[2 * a];
+                    else if (j == 3)
+                        r = expf(v) * anchor_wh[2 * a + 1];
+                    else
+                        r = so_sigmoid(v);
+                    out[pred * rec + j] = r;
+                }
+    (void)Cp;
+}
+
+typedef struct
+{
+    float x, y, w, h, obj, score;
+    int32_t cls;
+} so_det;
+
+static float so_overlap(float x1, float w1, float x2, float w2)
+{
+    /* include/small/non_max_suppression.hpp:33-42 */
+    const float l1 = x1 - w1 / 2, l2 = x2 - w2 / 2;
+    const float left = l1 > l2 ? l1 : l2;
+    const float r1 = x1 + w1 / 2, r2 = x2 + w2 / 2;
+    const float right = r1 < r2 ? r1 : r2;
+    return right - left;
+}
+
+static float so_iou(const so_det *a, const so_det *b)
+{
+    /* include/small/non_max_suppression.hpp:45-59 */
+    const float area_a = a->w * a->h, area_b = b->w * b->h;
+    const float wo = so_overlap(a->x, a->w, b->x, b->w), ho = so_overlap(a->y, a->h, b->y, b->h);
+    const float inter = (wo < 0.f || ho < 0.f) ? 0.f : wo * ho;
+    const float uni = area_a + area_b - inter;
+    return inter / uni;
+}
+
+int32_t so_nms_f32(const float *pred, int32_t num_pred, int32_t num_classes, float conf_thr, float iou_thr,
+                   int32_t max_det, float *out, int32_t *candidates)
+{
+    /* Darknet.hpp:85-122 (collection, in prediction-then-class order) and non_max_suppression.hpp:98-155.
+     * std::sort leaves the order of equal objectness values open; here ties keep the collection order
+     * (an insertion sort is stable). */
+    const int32_t rec = num_classes + 5;
+    int32_t n = 0, cap = 1024;
+    so_det *d = (so_det *)malloc((size_t)cap * sizeof(so_det));
+    for (int32_t p = 0; p < num_pred; ++p)
+    {
+        const float *r = pred + (size_t)p * rec;
+        if (!(r[4] > conf_thr))
+            continue;
+        for (int32_t c = 0; c < num_classes; ++c)
+            if (r[5 + c] > conf_thr)
+            {
+                if (n == cap)
+                    d = (so_det *)realloc(d, (size_t)(cap *= 2) * sizeof(so_det));
+                const so_det v = {r[0], r[1], r[2], r[3], r[4], r[5 + c], c};
+                d[n++] = v;
+            }
+    }
+    *candidates = n;
+    for (int32_t i = 1; i < n; ++i)
+    {
+        const so_det v = d[i];
+        int32_t j = i - 1;
+        while (j >= 0 && d[j].obj < v.obj)
+        {
+            d[j + 1] = d[j];
+            --j;
+        }
+        d[j + 1] = v;
+    }
+    char *alive = (char *)malloc((size_t)(n > 0 ? n : 1));
+    for (int32_t i = 0; i < n; ++i)
+        alive[i] = 1;
+    int32_t kept = 0;
+    for (int32_t i = 0; i < n; ++i)
+    {
+        if (!alive[i])
+            continue;
+        if (kept < max_det)
+        {
+            float *o = out + (size_t)kept * 7;
+            o[0] = d[i].x; o[1] = d[i].y; o[2] = d[i].w; o[3] = d[i].h; o[4] = d[i].obj; o[5] = d[i].score;
+            o[6] = (float)d[i].cls;
+        }
+        ++kept;
+        for (int32_t j = i + 1; j < n; ++j)
+            if (alive[j] && d[j].cls == d[i].cls && !(so_iou(&d[i], &d[j]) < iou_thr))
+                alive[j] = 0;
+    }
+    free(alive);
+    free(d);
+    return kept;
+}
+
+/* ---------------------------------------------------------------- weight preparation */
+void so_conv_weights_prepare_f32(int32_t K, int32_t Keff, int32_t C, int32_t Fh, int32_t Fw, int32_t cb,
+                                 const float *filt, const float *bias, const float *gamma, const float *beta,
+                                 const float *mean, const float *var, float eps, float *packed, float *packed_bias)
+{
+    /* detail::initialize_conv2d_buffers, include/small/Conv2DLayer.hpp:135-341: zero-padded packing
+     * (:179-209, packed_weight_index buffers.hpp:33-79), padded bias (:225-240), BN folding (:284-331) */
+    const int32_t cib = eff_cib(C, cb);
+    const size_t total = (size_t)K * C * Fh * Fw;
+    for (size_t i = 0; i < total; ++i)
+        packed[i] = 0.f;
+    for (int32_t k = 0; k < Keff; ++k)
+        for (int32_t c = 0; c < C; ++c)
+            for (int32_t h = 0; h < Fh; ++h)
+                for (int32_t w = 0; w < Fw; ++w)
+                    packed[((((size_t)(k / cb) * (C / cib) + c / cib) * Fh + h) * Fw + w) * cib * cb +
+                           (size_t)(c % cib) * cb + (k % cb)] = filt[(((size_t)k * C + c) * Fh + h) * Fw + w];
+    if (packed_bias)
+        for (int32_t k = 0; k < K; ++k)
+            packed_bias[k] = (bias && k < Keff) ? bias[k] : 0.f;
+    if (!gamma)
+        return;
+    for (int32_t k = 0; k < Keff; ++k)
+    {
+        const float rsq = 1.0f / sqrtf(var[k] + eps);
+        const float scale = gamma[k] * rsq;
+        if (!bias)
+            packed_bias[k] = beta[k] - mean[k] * scale;
+        else
+            packed_bias[k] = beta[k] + scale * (packed_bias[k] - mean[k]);
+        for (int32_t c = 0; c < C; ++c)
+            for (int32_t h = 0; h < Fh; ++h)
+                for (int32_t w = 0; w < Fw; ++w)
+                    packed[((((size_t)(k / cb) * (C / cib) + c / cib) * Fh + h) * Fw + w) * cib * cb +
+                           (size_t)(c % cib) * cb + (k % cb)] *= scale;
+    }
+}

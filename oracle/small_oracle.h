@@ -96,6 +96,24 @@ void so_relu_u8(int64_t n, const so_quant *q, const uint8_t *in, uint8_t *out);
  * over valid taps, requantised with the output's parameters. Parity unpinned. */
 void so_avgpool2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in, uint8_t *out);
 
+/* Weight preparation of a convolution layer (include/small/Conv2DLayer.hpp:135-341): zero-padded
+ * packing of [Keff][C][Fh][Fw] into K output channels, padded bias, batch-normalisation folding
+ * (gamma/beta/mean/var all given or all NULL).  packed_bias may be NULL without bias and BN. */
+void so_conv_weights_prepare_f32(int32_t K, int32_t Keff, int32_t C, int32_t Fh, int32_t Fw, int32_t cb,
+                                 const float *filt, const float *bias, const float *gamma, const float *beta,
+                                 const float *mean, const float *var, float eps, float *packed, float *packed_bias);
+
+/* Detection head.  Box decoding of one packed activation [Cp/cb][H][W][cb] into
+ * [num_anchors*H*W][5 + num_classes] records (include/small/YOLOLayer.hpp:96-222); collection of the
+ * (record, class) pairs above a confidence threshold and non-maximum suppression
+ * (include/small/models/Darknet.hpp:78-122, include/small/non_max_suppression.hpp:98-155): writes up
+ * to max_det rows [x, y, w, h, objectness, class score, class id] in keep order, returns how many
+ * detections survive, *candidates = pairs above the threshold. */
+void so_yolo_decode_f32(int32_t Cp, int32_t H, int32_t W, int32_t cb, int32_t num_anchors, int32_t num_classes,
+                        float stride, const float *anchor_wh, const float *in, float *out);
+int32_t so_nms_f32(const float *pred, int32_t num_pred, int32_t num_classes, float conf_thr, float iou_thr,
+                   int32_t max_det, float *out, int32_t *candidates);
+
 #ifdef __cplusplus
 }
 #endif

@@ -84,6 +84,9 @@ SIGNATURES = {
     "small_b200_upsample1d_f32": [_I32, _I32, _I32, _I32, _VP, _VP, _VP],
     "small_b200_softmax_f32": [_I32, _I64, _VP, _VP, _VP],
     "small_b200_concat": [_I32, _SZ, _VP, _SZ, _VP, _VP, _VP],
+    "small_b200_conv_weights_prepare_f32": [_I32, _I32, _I32, _I32, _I32, _VP, _VP, _VP, _VP, _VP, _VP, _F, _VP, _VP, _VP],
+    "small_b200_yolo_decode_f32": [_I32, _I32, _I32, _I32, _I32, _I32, _F, _VP, _VP, _VP, _VP],
+    "small_b200_nms_f32": [_VP, _I32, _I32, _F, _F, _I32, _VP, _I32, _VP, _VP, _VP],
     "small_b200_conv2d_u8": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_dwconv2d_u8": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_conv2d_dwconv2d_u8_supported": [_LP, _LP],
@@ -95,7 +98,8 @@ SIGNATURES = {
     "small_b200_avgpool2d_u8": [_LP, _VP, _VP, _VP],
     "small_b200_relu_u8": [_I64, _LP, _VP, _VP, _VP],
 }
-OTHER = {"small_b200_last_error": ([], C.c_char_p), "small_b200_launch_count": ([], C.c_uint64)}
+OTHER = {"small_b200_last_error": ([], C.c_char_p), "small_b200_launch_count": ([], C.c_uint64),
+         "small_b200_nms_scratch_bytes": ([C.c_int32], C.c_size_t)}
 
 
 def exported_names():

@@ -501,3 +501,35 @@ def Conv2D_ReLU_DepthwiseConv2D_ReLU(conv_kernel_height, conv_kernel_width, conv
     check(lib().small_b200_dwconv2d_u8(C.byref(Ld), _ptr(inter_output_buf), _ptr(dwise_filter_buf), _ptr(dw_bias),
                                        _ptr(output_buf), _stream(stream)))
     return False
+
+
+# --------------------------------------------------------------------------- detection head
+def YOLODecode(anchors, num_classes, input_img_size, padded_channels, input_height, input_width, input_buf,
+               output_buf, *, batch=1, stream=None):
+    """small::YOLOLayer::compute_output (include/small/YOLOLayer.hpp:96-222) on the device: the packed
+    activation becomes [batch][len(anchors) * H * W][5 + num_classes] records.  anchors: (w, h) pairs of
+    this layer's mask; the stride is input_img_size / input_height as in the layer's constructor."""
+    a = np.ascontiguousarray(np.asarray(anchors, np.float32).ravel())
+    _need(input_buf, batch * padded_channels * input_height * input_width, "YOLOLayer input")
+    _need(output_buf, batch * len(anchors) * input_height * input_width * (num_classes + 5), "YOLOLayer output")
+    check(lib().small_b200_yolo_decode_f32(batch, padded_channels, input_height, input_width, len(anchors),
+                                           num_classes, float(input_img_size // input_height),
+                                           a.ctypes.data, _ptr(input_buf), _ptr(output_buf), _stream(stream)))
+
+
+def NonMaxSuppression(pred_buf, num_pred, num_classes, confidence_threshold=0.25, iou_threshold=0.45, *,
+                      max_candidates=16384, max_detections=1024, stream=None):
+    """Darknet::process_outputs + small::basic_nms (include/small/models/Darknet.hpp:78-122,
+    include/small/non_max_suppression.hpp:98-155) on the device.  Returns a numpy array [n, 7] of
+    x, y, w, h, objectness, class score, class id in keep order (this call waits for the device)."""
+    l = lib()
+    scratch = torch.empty(l.small_b200_nms_scratch_bytes(max_candidates), dtype=torch.uint8, device=pred_buf.t.device)
+    dets = torch.zeros(max_detections * 7, dtype=torch.float32, device=pred_buf.t.device)
+    counts = torch.zeros(2, dtype=torch.int32, device=pred_buf.t.device)
+    check(l.small_b200_nms_f32(_ptr(pred_buf), num_pred, num_classes, confidence_threshold, iou_threshold,
+                               max_candidates, scratch.data_ptr(), max_detections, dets.data_ptr(),
+                               counts.data_ptr(), _stream(stream)))
+    kept, cand = (int(v) for v in counts.cpu())
+    if cand > max_candidates:
+        raise _lib.SmallB200Error(f"NMS: {cand} candidates above the confidence threshold, room for {max_candidates}")
+    return dets.cpu().numpy().reshape(max_detections, 7)[:min(kept, max_detections)]

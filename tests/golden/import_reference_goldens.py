@@ -4,7 +4,7 @@ The files are the PyTorch-generated regression data the reference's layer tests 
 (test/regression_data, written by test/gen_reg_data.py with torch.manual_seed(0); format:
 big-endian uint32 element count, then raw little-endian float32, test/test_utils.hpp
 :187-215).  Everything up to 150 KB is taken, plus a few 96-channel 30x30 cases that give
-the convolution kernels a non-trivial size.  Run once where the reference tree is mounted:
+the convolution kernels a non-trivial size and the 19x19 box-decoding case.  Run once where the reference tree is mounted:
 
     python tests/golden/import_reference_goldens.py /path/to/reference
 """
@@ -17,6 +17,7 @@ EXTRA = [
     "{}__conv2d_Ci96_H30_W30_k3_s2_f_Co96_{}.bin",
     "{}__dw_conv_Ci96_H30_W30_k3_s2_f_{}.bin",
     "{}__pool_Ci96_H30_W30_k3_s2_f_{}.bin",
+    "{}__yolo_Ci255_H19_W19_k0_s0_f_{}.bin",   # box decoding (YOLOLayer), the smallest of the three cases
 ]
 
 
@@ -31,8 +32,8 @@ def main():
     extra_keys = [e.split("{}")[1] for e in EXTRA]
     n = 0
     for name in names:
-        if "yolo" in name or not name.endswith(".bin"):
-            continue  # box decoding is outside the layer path
+        if "yolov3tiny" in name or not name.endswith(".bin"):
+            continue  # whole-network vectors need the Darknet weights, which the checkout lacks
         path = os.path.join(src, name)
         small = os.path.getsize(path) <= 150 * 1024
         extra = any(k in name for k in extra_keys)
