@@ -102,7 +102,7 @@ def test_gpu_nms_keeps_exactly_what_the_oracle_keeps(oracle, case):
     P_, classes, clusters, seed = case
     pred = synthetic_predictions(np.random.default_rng(seed), P_, classes, clusters)
     want, cand = oracle.nms_f32(pred, classes, 0.25, 0.45)
-    got = S.NonMaxSuppression(S.FloatBuffer(data=pred), P_, classes, 0.25, 0.45)
+    got = S.NonMaxSuppression(S.FloatBuffer(data=pred), P_, classes, 0.25, 0.45, max_detections=4096)
     assert cand > len(want) > 0
     assert got.shape == want.shape and np.array_equal(got, want)
 
