@@ -304,7 +304,7 @@ def measure_workload(args, workload, env, pipes):
     chain.stream.synchronize()
     # resident leg: the input rotates over copies of the batch that together exceed L2 (a network whose
     # whole input is a few MB would otherwise be timed on an L2-resident input)
-    copies = 1 if in_bytes > 160e6 / 2 else int(min(96, -(-160e6 // in_bytes)))
+    copies = 2 if in_bytes > 160e6 / 2 else int(min(96, -(-160e6 // in_bytes)))
     inputs = [chain.x] + [chain.x.clone() for _ in range(copies - 1)]
     chain.capture(inputs)
     out_bytes = chain.y.numel() * chain.y.element_size()
@@ -317,26 +317,28 @@ def measure_workload(args, workload, env, pipes):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed_round(fn, steps):
+    def timed_round(fn, steps, finish=None):
         """exactly `steps` steps between two barriers; device time, max over ranks"""
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record(chain.stream)
         for _ in range(steps):
             fn()
+        if finish:
+            finish()  # work of these steps on other streams is inside the timed span
         e1.record(chain.stream)
         chain.stream.synchronize()
         barrier()
         return sharding.max_over_ranks(e0.elapsed_time(e1), device="cuda")
 
-    def timed(fn, steps, budget_s):
-        first = timed_round(fn, steps)
+    def timed(fn, steps, budget_s, finish=None):
+        first = timed_round(fn, steps, finish)
         rounds = int(min(400, max(1, budget_s * 1e3 / max(first, 1e-3))))
         if world > 1:  # every rank must run the same number of rounds
             t = torch.tensor([rounds], device="cuda")
             dist.broadcast(t, 0)
             rounds = int(t.item())
-        ms = [first] + [timed_round(fn, steps) for _ in range(rounds - 1)]
+        ms = [first] + [timed_round(fn, steps, finish) for _ in range(rounds - 1)]
         return float(np.median(ms)), float(np.min(ms)), len(ms), float(np.sum(ms))
 
     step_no = [0]
@@ -345,27 +347,40 @@ def measure_workload(args, workload, env, pipes):
         chain.launch(step_no[0])
         step_no[0] += 1
 
-    # End to end: every step copies its batch from pinned host memory and reads its result
-    # back.  The upload of step i+1 runs on a second stream while step i computes (two staging
-    # buffers); the compute stream copies the staged batch into the chain's input, replays the
-    # graph and downloads the result.
-    copy_stream = torch.cuda.Stream()
-    staging = [torch.empty_like(chain.x) for _ in range(2)]
+    # End to end: every step copies its batch from pinned host memory and reads its result back.
+    # Three streams: the upload of step i+1 (into the other of two input buffers, which the recorded
+    # graphs read directly) and the download of step i-1's result (from a small device copy of it)
+    # both overlap the graph of step i.
+    copy_stream, down_stream = torch.cuda.Stream(), torch.cuda.Stream()
+    y_stage = [torch.empty_like(chain.y) for _ in range(2)]
+    hout2 = C.c_void_p()
+    check(l.small_b200_malloc_host(out_bytes, C.byref(hout2)))
+    houts = [hout, hout2]
     ev_up = [torch.cuda.Event() for _ in range(2)]
     ev_free = [torch.cuda.Event() for _ in range(2)]
+    ev_y = [torch.cuda.Event() for _ in range(2)]
+    ev_down = [torch.cuda.Event() for _ in range(2)]
     e2e_count = [0]
 
     def step_e2e():
         i = e2e_count[0] & 1
         e2e_count[0] += 1
-        copy_stream.wait_event(ev_free[i])          # staging[i] was consumed two steps ago
-        check(l.small_b200_memcpy_h2d(staging[i].data_ptr(), hin, in_bytes, copy_stream.cuda_stream))
+        copy_stream.wait_event(ev_free[i])          # input buffer i was consumed two steps ago
+        check(l.small_b200_memcpy_h2d(inputs[i].data_ptr(), hin, in_bytes, copy_stream.cuda_stream))
         ev_up[i].record(copy_stream)
         chain.stream.wait_event(ev_up[i])
-        check(l.small_b200_memcpy_d2d(chain.x.data_ptr(), staging[i].data_ptr(), in_bytes, st))
+        chain.launch(i)                             # graph i reads input buffer i
         ev_free[i].record(chain.stream)
-        chain.launch(0)
-        check(l.small_b200_memcpy_d2h(hout, chain.y.data_ptr(), out_bytes, st))
+        chain.stream.wait_event(ev_down[i])         # result copy i went to the host two steps ago
+        check(l.small_b200_memcpy_d2d(y_stage[i].data_ptr(), chain.y.data_ptr(), out_bytes, st))
+        ev_y[i].record(chain.stream)
+        down_stream.wait_event(ev_y[i])
+        check(l.small_b200_memcpy_d2h(houts[i], y_stage[i].data_ptr(), out_bytes, down_stream.cuda_stream))
+        ev_down[i].record(down_stream)
+
+    def finish_e2e():
+        for ev in ev_down:
+            chain.stream.wait_event(ev)
 
     for _ in range(max(args.warmup, 3)):
         step_resident()
@@ -374,8 +389,27 @@ def measure_workload(args, workload, env, pipes):
         ms, ms_min, rounds, span_ms = timed(step_resident, args.steps, budget)
         for _ in range(2):
             step_e2e()
-        ms_e2e, ms_e2e_min, rounds_e2e, span_e2e = timed(step_e2e, args.steps, budget)
-    h2d_gbs = h2d_bandwidth(l, check, staging[0].data_ptr(), hin, in_bytes, copy_stream, torch)
+        ms_e2e, ms_e2e_min, rounds_e2e, span_e2e = timed(step_e2e, args.steps, budget, finish_e2e)
+    h2d_gbs = h2d_bandwidth(l, check, inputs[1].data_ptr(), hin, in_bytes, copy_stream, torch)
+    # The final host gather (outside the timed spans): every rank's result for its own batch goes to
+    # rank 0, which recomputes each shard from that rank's seed on its own GPU and compares the bytes.
+    shards_verified = None
+    if world > 1:
+        check(l.small_b200_memcpy_h2d(chain.x.data_ptr(), hin, in_bytes, st))
+        chain.launch(0)
+        chain.stream.synchronize()
+        feats = chain.y.numel() // batch
+        gathered = sharding.gather_to_host(chain.y.reshape(batch, feats), batch * world, 0)
+        if rank == 0:
+            shards_verified = 0
+            for r in range(world):
+                xr = make_input(workload, layers, batch, wl["seed"] + r)
+                chain.x.copy_(torch.from_numpy(xr).reshape(-1))
+                torch.cuda.synchronize()
+                chain.launch(0)
+                chain.stream.synchronize()
+                mine = chain.y.reshape(batch, feats).cpu()
+                shards_verified += int(torch.equal(mine, gathered[r * batch:(r + 1) * batch]))
     if world > 1:
         dist.barrier()
     images_per_round = batch * world * args.steps
@@ -391,11 +425,14 @@ def measure_workload(args, workload, env, pipes):
                 "d2h_bytes_per_step": out_bytes, "ms_per_step": ms_e2e / args.steps,
                 "ms_per_step_min": ms_e2e_min / args.steps, "rounds": rounds_e2e, "h2d_gbs": round(h2d_gbs, 2),
                 "h2d_ms_alone": round(in_bytes / (h2d_gbs * 1e9) * 1e3, 4),
-                "overlap": "upload of the next batch overlaps the current step (2 staging buffers)"},
+                "overlap": "upload of the next batch and download of the previous result overlap the current step "
+                           "(three streams, two input buffers read directly by the recorded graphs)"},
         "gpu_launches": chain.kernels_per_step * args.steps * (rounds + rounds_e2e),
         "kernels_per_step": chain.kernels_per_step,
         "clocks": clocks,
     }
+    if shards_verified is not None:
+        res["host_gather"] = {"shards": world, "shards_bit_identical_to_rank0_recomputation": shards_verified}
     if rank == 0:
         res.update(per_layer_report(chain, layers, batch, wl, clocks, torch, pipes))
     if world > 1:
@@ -406,8 +443,9 @@ def measure_workload(args, workload, env, pipes):
         except Exception as e:  # the checker library is absent: say so, do not hide it
             res["cpu_baseline"] = {"value": None, "unit": METRIC, "cores": 0, "kind": "reference",
                                    "sample": f"unavailable: {e}"}
-    check(l.small_b200_free_host(hin)); check(l.small_b200_free_host(hout))
-    del chain, staging, inputs
+    torch.cuda.synchronize()
+    check(l.small_b200_free_host(hin)); check(l.small_b200_free_host(hout)); check(l.small_b200_free_host(hout2))
+    del chain, y_stage, inputs
     torch.cuda.empty_cache()
     return res
 

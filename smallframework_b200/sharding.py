@@ -32,18 +32,20 @@ def max_over_ranks(value: float, device="cpu") -> float:
 
 
 def gather_to_host(local: torch.Tensor, total_images: int, dst: int = 0):
-    """Final host gather: every rank sends its [images, features] CPU tensor to `dst`, which
-    returns them stacked in image order (others return None)."""
+    """Final host gather: every rank sends its [images, features] tensor to `dst`, which returns
+    them stacked in image order on the host (others return None).  The tensors travel as they are:
+    device tensors over NCCL, host tensors over gloo."""
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
-        return local
+        return local.cpu()
     world, rank = dist.get_world_size(), dist.get_rank()
     sizes = [shard_range(total_images, world, r) for r in range(world)]
     if rank == dst:
-        parts = [torch.empty((e - b,) + tuple(local.shape[1:]), dtype=local.dtype) for b, e in sizes]
+        parts = [torch.empty((e - b,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+                 for b, e in sizes]
         parts[dst] = local
         reqs = [dist.irecv(parts[r], src=r) for r in range(world) if r != dst]
         for q in reqs:
             q.wait()
-        return torch.cat(parts, dim=0)
+        return torch.cat([p.cpu() for p in parts], dim=0)
     dist.send(local.contiguous(), dst=dst)
     return None
