@@ -287,6 +287,12 @@ int small_b200_nms_f32(const float *pred, int32_t num_pred, int32_t num_classes,
  * needs no 4x over-allocation (the reference's does, q_abstract_layer.hpp:1144). */
 int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
                          const int32_t *bias, uint8_t *out, void *stream);
+/* The same layer kept on the CUDA cores (dp4a / direct kernels).  small_b200_conv2d_u8 puts every
+ * shape on tcgen05 kind::i8 that its kernels cover -- all windows, strides, paddings, channel counts
+ * and zero points; this entry point is the other implementation of the same arithmetic, kept callable
+ * so that the two can be compared bit for bit.  No reference counterpart. */
+int small_b200_conv2d_u8_cuda_cores(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
+                                    const int32_t *bias, uint8_t *out, void *stream);
 /* Two uint8 layers as ONE kernel, the intermediate activation kept in shared memory: the
  * reference's Conv2D_ReLU_DepthwiseConv2D_ReLU fusion (fused_interface_abstract.hpp:1840, float
  * there) for quint8 buffers, where the clamp of the requantisation is the ReLU.  `conv` is a 1x1

@@ -648,12 +648,16 @@ int conv2d_u8_tensor_core(const small_b200_layer *L, const uint8_t *in, const ui
                           const int32_t *bias, uint8_t *out, cudaStream_t st);
 int conv2d_u8_one_channel_tc(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
                              const int32_t *bias, uint8_t *out, cudaStream_t st);
+// Defined in conv_u8_ring.cu: every other window / stride / channel count as an implicit GEMM on the
+// tensor core, for the zero points it covers; -1 otherwise.
+int conv2d_u8_ring(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt, const int32_t *bias,
+                   uint8_t *out, cudaStream_t st);
 }
 
-extern "C"
+namespace
 {
-int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
-                         const int32_t *bias, uint8_t *out, void *stream)
+int conv2d_u8_dispatch(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt, const int32_t *bias,
+                       uint8_t *out, void *stream, bool tensor_core)
 {
     if (int rc = check_window_layer(L, "Conv2D<quint8>", true, 2))
         return rc;
@@ -662,16 +666,23 @@ int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uin
     if (L->accumulate)
         return fail(SMALL_B200_INVALID_ARGUMENT,
                     "PartialConv2D<quint8> ERROR: the int32 partial-sum form is not provided.");
-    const int tc = conv2d_u8_tensor_core(L, in, filt, bias, out, as_stream(stream));
+    const int tc = tensor_core ? conv2d_u8_tensor_core(L, in, filt, bias, out, as_stream(stream)) : -1;
     if (tc >= 0)
         return tc;
     QArgs a; fill(L, a, true);
     if (a.N == 0 || a.Ho == 0 || a.Wo == 0)
         return SMALL_B200_OK;
+    if (tensor_core)
     {
         const int tc1 = conv2d_u8_one_channel_tc(L, in, filt, bias, out, as_stream(stream));
         if (tc1 >= 0)
             return tc1;
+    }
+    if (tensor_core)
+    {
+        const int tc2 = conv2d_u8_ring(L, in, filt, bias, out, as_stream(stream));
+        if (tc2 >= 0)
+            return tc2;
     }
     if (a.C == 1 && a.zero_filt == -128 && (a.zero_in == 0 || a.zero_in == -128))
     {
@@ -701,6 +712,21 @@ int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uin
     dim3 grid((a.Ho * a.Wo + 127) / 128, a.K / CB, a.N);
     conv2d_u8_direct_kernel<<<grid, 128, 0, as_stream(stream)>>>(a, in, filt, bias, out);
     return launched("conv2d_u8_direct_kernel");
+}
+} // namespace
+
+extern "C"
+{
+int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
+                         const int32_t *bias, uint8_t *out, void *stream)
+{
+    return conv2d_u8_dispatch(L, in, filt, bias, out, stream, true);
+}
+
+int small_b200_conv2d_u8_cuda_cores(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
+                                    const int32_t *bias, uint8_t *out, void *stream)
+{
+    return conv2d_u8_dispatch(L, in, filt, bias, out, stream, false);
 }
 
 int small_b200_dwconv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,

@@ -133,7 +133,7 @@ def _need(buf, elems, what):
 
 # --------------------------------------------------------------------------- dense conv
 def _conv(name, partial, kh, kw, stride, t, b, l, r, K, C_, H, W, inp, filt, out, bias, act,
-          slope, batch, stream):
+          slope, batch, stream, cuda_cores=False):
     L = _layer(batch, C_, K, H, W, kh, kw, stride, t, b, l, r, int(partial), act, slope, inp, filt, out)
     ho, wo = L.out_hw()
     if C_ % CB == 0 or C_ in (1, 2, 3):
@@ -141,17 +141,21 @@ def _conv(name, partial, kh, kw, stride, t, b, l, r, K, C_, H, W, inp, filt, out
         _need(filt, K * C_ * kh * kw, name + " filter")
     if K % CB == 0:
         _need(out, batch * K * ho * wo, name + " output")
-    fn = lib().small_b200_conv2d_u8 if _is_q(out) else lib().small_b200_conv2d_f32
+    if _is_q(out):
+        fn = lib().small_b200_conv2d_u8_cuda_cores if cuda_cores else lib().small_b200_conv2d_u8
+    else:
+        fn = lib().small_b200_conv2d_f32
     check(fn(C.byref(L), _ptr(inp), _ptr(filt), _ptr(bias), _ptr(out), _stream(stream)))
 
 
 def Conv2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
            output_channels, input_channels, input_height, input_width,
-           input_buf, filter_buf, output_buf, *, batch=1, stream=None):
-    """small::Conv2D (interface_abstract.hpp:46-221 float, :229-404 quint8)."""
+           input_buf, filter_buf, output_buf, *, batch=1, stream=None, cuda_cores=False):
+    """small::Conv2D (interface_abstract.hpp:46-221 float, :229-404 quint8).  cuda_cores=True keeps a
+    quint8 layer off the tensor cores (the other implementation of the same arithmetic)."""
     _conv("Conv2D", False, kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
           output_channels, input_channels, input_height, input_width, input_buf, filter_buf,
-          output_buf, None, ACT_NONE, 0.0, batch, stream)
+          output_buf, None, ACT_NONE, 0.0, batch, stream, cuda_cores)
 
 
 def PartialConv2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
@@ -184,14 +188,14 @@ def Conv2D_Bias_ReLU(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r
 def Conv2D_Bias_Activation(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
                            output_channels, input_channels, input_height, input_width,
                            input_buf, filter_buf, bias_buf, output_buf, *, activation=ACT_NONE,
-                           negative_slope=0.0, batch=1, stream=None):
+                           negative_slope=0.0, batch=1, stream=None, cuda_cores=False):
     """The single-element-before / -after slots of the reference's fused loop nest
     (abstract_layer.hpp:131-177) with bias before and none / ReLU / LeakyReLU after; equals
     the unfused chain Bias -> PartialConv2D -> activation of Conv2DLayer.hpp:827-878.
     For quint8 buffers bias_buf is an int32 torch tensor added to the accumulator seed."""
     _conv("Conv2D_Bias_Activation", False, kernel_height, kernel_width, stride, t_pad, b_pad,
           l_pad, r_pad, output_channels, input_channels, input_height, input_width, input_buf,
-          filter_buf, output_buf, bias_buf, activation, negative_slope, batch, stream)
+          filter_buf, output_buf, bias_buf, activation, negative_slope, batch, stream, cuda_cores)
 
 
 def conv2d_maxpool_supported(conv_kernel_height, conv_kernel_width, conv_stride, conv_pads,

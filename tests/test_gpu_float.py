@@ -99,6 +99,45 @@ def test_fused_equals_unfused_chain(oracle):
     assert np.array_equal(O1.numpy(), O2.numpy())
 
 
+@pytest.mark.parametrize("tensor_core", [False, True])
+@pytest.mark.parametrize("act,slope", [(0, 0.0), (1, 0.0), (2, 0.1)])
+def test_activation_of_special_values(oracle, tensor_core, act, slope):
+    """Accumulators that are -inf, +inf or NaN go through the fused activation as through the
+    reference's separate one: ReLU gives 0 for -inf and NaN (x > 0 ? x : 0), LeakyReLU scales them."""
+    rng = np.random.default_rng(5)
+    C, K, H, W, N = 32, 32, 12, 12, 1
+    x = rng.uniform(0.1, 1, (N, C, H, W)).astype(np.float32)
+    if not tensor_core:
+        # the 3xTF32 split of an infinity is (inf, inf - inf = NaN): on the tensor-core path an infinite
+        # input gives NaN where the reference gives an infinity; NaN inputs behave alike on both
+        x[0, 3, 2, 2] = -np.inf
+        x[0, 5, 9, 3] = np.inf
+    x[0, 7, 6, 8] = np.nan
+    w = np.abs(rng.normal(0, 0.1, (K, C, 1, 1))).astype(np.float32) + 0.01
+    bias = rng.uniform(-0.5, 0.5, K).astype(np.float32)
+    sh = shape(C, K, H, W, 1, 1, 1, (0, 0, 0, 0), CB)
+    xp, wp = P.pack_activation(x), P.pack_conv_filter(w)
+    O = S.FloatBuffer(N * K * H * W)
+    if tensor_core:
+        FP = S.FloatBuffer(2 * wp.size)
+        S.prepare_filter_3xTF32(1, 1, K, C, fbuf(wp), FP)
+        S.Conv2D_3xTF32(1, 1, 1, 0, 0, 0, 0, K, C, H, W, fbuf(xp), FP, fbuf(bias), O, activation=act,
+                        negative_slope=slope, batch=N)
+    else:
+        S.Conv2D_Bias_Activation(1, 1, 1, 0, 0, 0, 0, K, C, H, W, fbuf(xp), fbuf(wp), fbuf(bias), O,
+                                 activation=act, negative_slope=slope, batch=N)
+    want = oracle_conv_batch(oracle, sh, xp, wp, bias=bias, act=act, slope=slope)
+    got = O.numpy().reshape(N, -1)
+    special = ~np.isfinite(want)
+    assert special.sum() >= (0 if act == 1 and tensor_core else K)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    assert np.array_equal(got[special & ~np.isnan(want)], want[special & ~np.isnan(want)])
+    zeros = (want == 0)
+    assert np.array_equal(got[zeros], want[zeros])
+    fin = np.isfinite(want)
+    assert rel_max_err(got[fin], want[fin]) <= TOL
+
+
 def test_conv2d_is_deterministic():
     rng = np.random.default_rng(2)
     C, K, H, W, N = 64, 64, 26, 26, 4

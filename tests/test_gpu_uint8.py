@@ -23,10 +23,12 @@ def _out(n, q):
     return O
 
 
-def _quant(rng, taps_c):
+def _quant(rng, taps_c, zero_points=None):
     """Zero points plus a multiplier / shift that spread the accumulator over 0..255 for a
     reduction of `taps_c` terms of uniform bytes."""
     zi = int(rng.choice([0, -128, 128, 5])); zf = int(rng.choice([-128, 0, 128, -7]))
+    if zero_points is not None:
+        zi, zf = zero_points
     ma, mw = 127.5 + zi, 127.5 + zf
     var = (74.0 ** 2 + ma ** 2) * (74.0 ** 2 + mw ** 2) - (ma * mw) ** 2
     top = abs(taps_c * ma * mw) + 2.0 * np.sqrt(taps_c * var)
@@ -50,14 +52,57 @@ CONV_CASES = [
 ]
 
 
-@pytest.mark.parametrize("case", CONV_CASES, ids=lambda c: "C{}_K{}_{}x{}_k{}x{}_s{}_{}_n{}".format(*[
-    "".join(map(str, v)) if isinstance(v, tuple) else v for v in c]))
+_case_id = lambda c: "C{}_K{}_{}x{}_k{}x{}_s{}_{}_n{}".format(*[
+    "".join(map(str, v)) if isinstance(v, tuple) else v for v in c])
+
+
+@pytest.mark.parametrize("case", CONV_CASES, ids=_case_id)
 @pytest.mark.parametrize("with_bias", [False, True])
-def test_conv2d_u8(oracle, case, with_bias):
+@pytest.mark.parametrize("cuda_cores", [False, True], ids=["tensor_core", "cuda_cores"])
+def test_conv2d_u8(oracle, case, with_bias, cuda_cores):
     C, K, H, W, Fh, Fw, s, pm, N = case
     pads = same_pads(H, W, Fh, Fw, s) if pm == "same" else (0, 0, 0, 0) if pm == "valid" else pm
     rng = np.random.default_rng(abs(hash((case, with_bias))) % (1 << 31))
     q = _quant(rng, C * Fh * Fw)
+    _check_conv(oracle, case, pads, q, rng, with_bias, cuda_cores)
+
+
+# Shapes for the implicit-GEMM kernel (every window / stride / padding / channel count on tcgen05
+# kind::i8): odd numbers of channel blocks, more than 256 channels, first layers with 1..3 channels,
+# windows larger than the image border, stride 2, several pixel tiles, several channel groups.
+RING_CASES = [
+    (16, 16, 24, 24, 1, 1, 1, "valid", 3),     # one channel block: half of every reduction step is zero
+    (48, 32, 10, 7, 1, 1, 1, "valid", 2),      # odd number of blocks
+    (512, 64, 5, 5, 1, 1, 1, "valid", 2),      # more channels than the pointwise kernel holds
+    (16, 32, 48, 48, 3, 3, 2, "same", 2),      # MobileNet-like stride-2 layer
+    (64, 128, 13, 13, 3, 3, 1, "same", 3),
+    (32, 48, 9, 14, 5, 5, 1, "same", 2),       # K = 48: tiles of 16 channels
+    (32, 192, 6, 6, 3, 3, 1, "same", 2),       # three channel groups of 64
+    (3, 16, 96, 96, 3, 3, 2, "same", 2),       # MobileNet stem
+    (3, 32, 20, 31, 5, 5, 1, "same", 1),       # first layer, more than two reduction steps
+    (2, 16, 11, 9, 3, 3, 1, "valid", 2),
+    (1, 16, 30, 30, 7, 7, 2, "same", 2),
+    (16, 16, 3, 3, 7, 7, 1, (3, 3, 3, 3), 4),  # every pixel is a border pixel
+    (80, 16, 17, 5, 2, 4, 2, "valid", 3),
+]
+ZERO_POINTS = [(0, -128), (-128, -128), (128, 128), (5, -7), (0, 0), (-128, 0), (3, -128)]
+
+
+@pytest.mark.parametrize("case", RING_CASES, ids=_case_id)
+@pytest.mark.parametrize("zp", ZERO_POINTS, ids=lambda z: "zi{}_zf{}".format(*z))
+def test_conv2d_u8_implicit_gemm(oracle, case, zp):
+    """Every zero-point class of the tensor-core kernel: shifted operands without correction
+    (filter -128, activation 0 / -128), row sums through the extra accumulator columns (filter zero
+    point not -128), per-tap channel sums at the border (activation zero point not 0)."""
+    C, K, H, W, Fh, Fw, s, pm, N = case
+    pads = same_pads(H, W, Fh, Fw, s) if pm == "same" else (0, 0, 0, 0) if pm == "valid" else pm
+    rng = np.random.default_rng(abs(hash((case, zp))) % (1 << 31))
+    q = _quant(rng, C * Fh * Fw, zp)
+    _check_conv(oracle, case, pads, q, rng, True, False)
+
+
+def _check_conv(oracle, case, pads, q, rng, with_bias, cuda_cores):
+    C, K, H, W, Fh, Fw, s, pm, N = case
     x = P.pack_activation(rng.integers(0, 256, (N, C, H, W)).astype(np.uint8))
     w = P.pack_conv_filter(rng.integers(0, 256, (K, C, Fh, Fw)).astype(np.uint8))
     bias = rng.integers(-1024, 1025, K).astype(np.int32) if with_bias else None
@@ -67,9 +112,9 @@ def test_conv2d_u8(oracle, case, with_bias):
     if with_bias:
         import torch
         S.Conv2D_Bias_Activation(Fh, Fw, s, *pads, K, C, H, W, I, F,
-                                 torch.from_numpy(bias).cuda(), O, batch=N)
+                                 torch.from_numpy(bias).cuda(), O, batch=N, cuda_cores=cuda_cores)
     else:
-        S.Conv2D(Fh, Fw, s, *pads, K, C, H, W, I, F, O, batch=N)
+        S.Conv2D(Fh, Fw, s, *pads, K, C, H, W, I, F, O, batch=N, cuda_cores=cuda_cores)
     want = np.stack([oracle.conv2d_u8(sh, q, x[n], w, bias=bias) for n in range(N)])
     got = O.numpy().reshape(N, -1)
     assert _lib.device_status() == 0  # no tensor-core kernel gave up on a bounded wait
