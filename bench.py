@@ -603,6 +603,8 @@ def kernel_class(chain, i, L, dtype):
         ho, wo = networks_out_hw(L)
         if L["C"] == 1 and L["Fw"] <= 4 and L["Fh"] <= 16 and ho * wo <= 128 and L["K"] <= 128:
             return "stem_u8_tc_kernel (im2col in shared memory + tcgen05 kind::i8)", "i8"
+        if L["C"] * L["Fh"] * L["Fw"] > 32 or (L["C"] >= 16 and L["K"] >= 32):
+            return "conv_u8_ring_kernel (implicit GEMM, tcgen05 kind::i8)", "i8"
         return "conv2d_u8_direct_kernel", "cuda_u8"
     if L["op"] == "dwconv" and dtype == "u8":
         rows = L["Fh"] == 3 and L["Fw"] == 3 and L["stride"] == 1

@@ -114,8 +114,9 @@ inline void dwconv(bool partial, int act, int kh, int kw, int stride, int t, int
     quantise(L, in, &filt, out);
     if constexpr (is_quint8<BufferT>)
     {
-        if (partial || bias)
-            throw std::invalid_argument("DepthwiseConv2D<quint8> ERROR: partial / bias form not provided.");
+        if (bias)
+            throw std::invalid_argument("DepthwiseConv2D<quint8> ERROR: a uint8 bias buffer is not meaningful; "
+                                        "pass an int32 bias through the C ABI.");
         throw_on(small_b200_dwconv2d_u8(&L, in.device_ptr(), filt.device_ptr(), nullptr, out.device_ptr(), b200::stream()));
     }
     else

@@ -284,15 +284,27 @@ int small_b200_nms_f32(const float *pred, int32_t num_pred, int32_t num_classes,
 /* ---- uint8 layers ------------------------------------------------------------------ */
 /* small::Conv2D<QUInt8Buffer> (:229-404) with an optional per-channel int32 bias added to
  * the accumulator seed.  The int32 partial sums never leave the chip, so the output buffer
- * needs no 4x over-allocation (the reference's does, q_abstract_layer.hpp:1144). */
+ * needs no 4x over-allocation (the reference's does, q_abstract_layer.hpp:1144).
+ * L->accumulate = 1 is small::PartialConv2D<QUInt8Buffer> (:595-767): `out` holds int32 partial sums
+ * [Ho*Wo][16] on entry (4 * 16 * Ho*Wo bytes) and the bytes [Ho*Wo][16] of requantise(entry +
+ * convolution) at its start on return.  The reference keeps the int32 sums of output channel block k
+ * at BYTE k * Ho*Wo*block of the uint8 buffer, four times the block's length, so the sums of one block
+ * lie over the next three: the form has a defined result for one block only, and this entry point
+ * takes K = 16, N = 1, bias = NULL and refuses the rest (SMALL_B200_INVALID_ARGUMENT). */
 int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
                          const int32_t *bias, uint8_t *out, void *stream);
-/* The same layer kept on the CUDA cores (dp4a / direct kernels).  small_b200_conv2d_u8 puts every
- * shape on tcgen05 kind::i8 that its kernels cover -- all windows, strides, paddings, channel counts
- * and zero points; this entry point is the other implementation of the same arithmetic, kept callable
- * so that the two can be compared bit for bit.  No reference counterpart. */
+/* The same layer on a path of the caller's choosing.  small_b200_conv2d_u8 picks, per shape, the faster
+ * of two implementations of the same arithmetic: tcgen05 kind::i8 kernels (1x1 layers from shared-memory
+ * resident filters, the one-channel first layer as an im2col GEMM, and an implicit GEMM over a ring of
+ * im2col stages that covers every window, stride, padding, channel count and zero point) and CUDA-core
+ * kernels (dp4a / direct), which keep the layers whose reduction is a single 32-byte step.
+ * ..._cuda_cores never uses the tensor cores; ..._tensor_core always does and fails with
+ * SMALL_B200_INVALID_ARGUMENT for what they do not cover (the int32 partial-sum form, unaligned
+ * buffers).  All three give identical bits.  No reference counterpart. */
 int small_b200_conv2d_u8_cuda_cores(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
                                     const int32_t *bias, uint8_t *out, void *stream);
+int small_b200_conv2d_u8_tensor_core(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
+                                     const int32_t *bias, uint8_t *out, void *stream);
 /* Two uint8 layers as ONE kernel, the intermediate activation kept in shared memory: the
  * reference's Conv2D_ReLU_DepthwiseConv2D_ReLU fusion (fused_interface_abstract.hpp:1840, float
  * there) for quint8 buffers, where the clamp of the requantisation is the ReLU.  `conv` is a 1x1
@@ -318,12 +330,15 @@ int small_b200_conv2d_avgpool_dense_u8(const small_b200_layer *conv, const small
                                        const small_b200_layer *dense, const uint8_t *in, const uint8_t *conv_filt,
                                        const int32_t *conv_bias, const uint8_t *dense_filt, const int32_t *dense_bias,
                                        uint8_t *out, void *stream);
-/* small::DepthwiseConv2D<QUInt8Buffer> (:1059). */
+/* small::DepthwiseConv2D<QUInt8Buffer> (:1059); with L->accumulate = 1 PartialDepthwiseConv2D (:1194)
+ * under the conditions of the partial convolution above (C = 16, N = 1, bias = NULL). */
 int small_b200_dwconv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
                            const int32_t *bias, uint8_t *out, void *stream);
 /* small::GroupConv2D<QUInt8Buffer> (:1332; lane-wise op_class 1 at :1358), layouts as in the
- * float form, arithmetic as in small_b200_conv2d_u8.  The Partial form (:1470) would reload
- * int32 partial sums from the uint8 output and is refused like PartialConv2D<quint8>. */
+ * float form, arithmetic as in small_b200_conv2d_u8.  The Partial form (:1470) keeps the int32
+ * sums of output channel k of the groups at byte k * Ho*Wo*16, four times the channel's length: for
+ * the multiples of 16 channels per group the interface accepts they always overlap, so no shape has
+ * a defined result and L->accumulate = 1 is refused. */
 int small_b200_groupconv2d_u8(const small_b200_layer *L, int32_t groups, const uint8_t *in, const uint8_t *filt,
                               const int32_t *bias, uint8_t *out, void *stream);
 /* small::MaxPool2D<QUInt8Buffer> (:843): interior windows start from the raw first tap,

@@ -158,6 +158,19 @@ class Oracle:
         fn(C.byref(s), C.byref(q), _p(x), _p(f), _p(b), _p(o))
         return o
 
+    def partial_conv2d_u8(self, s, q, x, f, partial, depthwise=False):
+        """One block of output channels; `partial` = int32 [Ho*Wo*block] (see small_oracle.h)."""
+        ho, wo = s.out_hw()
+        k = s.C if depthwise else s.K
+        assert k == s.cob
+        o = np.zeros(k * ho * wo, np.uint8)
+        x, f = _u8(x), _u8(f)
+        part = np.ascontiguousarray(partial, dtype=np.int32)
+        assert part.size == o.size
+        fn = self.lib.so_partial_dwconv2d_u8 if depthwise else self.lib.so_partial_conv2d_u8
+        fn(C.byref(s), C.byref(q), _p(x), _p(f), _p(part), _p(o))
+        return o
+
     def groupconv2d_u8(self, s, q, groups, x, f, bias=None):
         ho, wo = s.out_hw()
         o = np.zeros(groups * s.K * ho * wo, np.uint8)
@@ -271,6 +284,20 @@ class Ref:
         x, f = _u8(x), _u8(f)
         self._check(self.lib.ref_conv2d_u8(C.byref(s), C.byref(q), C.c_int(int(depthwise)),
                                            _p(x), _p(f), _p(o)))
+        return o
+
+    def partial_conv2d_u8(self, s, q, x, f, partial, depthwise=False):
+        """small::PartialConv2D / PartialDepthwiseConv2D<QUInt8Buffer> on one block of output channels
+        (this build's block is 1 channel): the int32 partial sums are placed at the start of the
+        four-times over-allocated output buffer, as the loop nest expects them."""
+        ho, wo = s.out_hw()
+        k = s.C if depthwise else s.K
+        o = np.zeros(k * ho * wo, np.uint8)
+        x, f = _u8(x), _u8(f)
+        part = np.ascontiguousarray(partial, dtype=np.int32)
+        assert part.size == o.size
+        self._check(self.lib.ref_partial_conv2d_u8(C.byref(s), C.byref(q), C.c_int(int(depthwise)),
+                                                   _p(x), _p(f), _p(part), _p(o)))
         return o
 
     def groupconv2d_f32(self, s, groups, x, f, out=None):

@@ -274,6 +274,35 @@ int ref_conv2d_u8(const so_shape *s, const so_quant *q, int depthwise, const uin
     })
 }
 
+// small::PartialConv2D / PartialDepthwiseConv2D<QUInt8Buffer> (interface_abstract.hpp:595, :1194): the
+// loop nest reads its starting accumulators as int32 from the output buffer (block k at BYTE offset
+// k * Ho*Wo*block, q_abstract_layer.hpp:1135-1144) and leaves the bytes at the start.  Meaningful for
+// one block of output channels; the caller passes such a shape.
+int ref_partial_conv2d_u8(const so_shape *s, const so_quant *q, int depthwise, const uint8_t *in,
+                          const uint8_t *filt, const int32_t *partial, uint8_t *out)
+{
+    const int K = depthwise ? s->C : s->K;
+    const size_t ni = (size_t)s->C * s->H * s->W;
+    const size_t nf = depthwise ? (size_t)s->C * s->Fh * s->Fw : (size_t)s->K * s->C * s->Fh * s->Fw;
+    const size_t no = (size_t)K * out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride) *
+                      out_dim(s->W, s->pad_l, s->pad_r, s->Fw, s->stride);
+    GUARD({
+        ref_set_threads(1);
+        auto I = make<small::QUInt8Buffer>(in, ni);
+        auto F = make<small::QUInt8Buffer>(filt, nf);
+        auto O = make<small::QUInt8Buffer>(nullptr, no, 4 * no + 64);
+        set_q(I, &F, O, q);
+        std::memcpy(O.data(), partial, no * sizeof(int32_t));
+        if (depthwise)
+            small::PartialDepthwiseConv2D(s->Fh, s->Fw, s->stride, s->pad_t, s->pad_b, s->pad_l, s->pad_r,
+                                          s->C, s->H, s->W, I, F, O);
+        else
+            small::PartialConv2D(s->Fh, s->Fw, s->stride, s->pad_t, s->pad_b, s->pad_l, s->pad_r, s->K,
+                                 s->C, s->H, s->W, I, F, O);
+        std::memcpy(out, O.data(), no);
+    })
+}
+
 // small::GroupConv2D<QUInt8Buffer> (interface_abstract.hpp:1332)
 int ref_groupconv2d_u8(const so_shape *s, const so_quant *q, int groups, const uint8_t *in,
                        const uint8_t *filt, uint8_t *out)

@@ -346,8 +346,8 @@ int32_t so_requant(int32_t acc, int32_t lshift, int32_t rshift, int32_t multipli
     return v > 0 ? (v < 255 ? v : 255) : 0;
 }
 
-void so_conv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
-                  const uint8_t *filt, const int32_t *bias, uint8_t *out)
+static void conv2d_u8_impl(const so_shape *s, const so_quant *q, const uint8_t *in,
+                           const uint8_t *filt, const int32_t *bias, const int32_t *partial, uint8_t *out)
 {
     const int32_t cib = eff_cib(s->C, s->cib), cob = s->cob;
     const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
@@ -357,7 +357,9 @@ void so_conv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
         for (int32_t oh = 0; oh < Ho; ++oh)
             for (int32_t ow = 0; ow < Wo; ++ow)
             {
-                int32_t acc = q->k_zero + (bias ? bias[k] : 0);
+                /* Partial form: the tile is loaded from the int32 values kept in the output buffer
+                 * instead of being set to k_zero (q_abstract_layer.hpp:1151, first = false) */
+                int32_t acc = partial ? partial[act_idx(Ho, Wo, cob, k, oh, ow)] : q->k_zero + (bias ? bias[k] : 0);
                 for (int32_t b = 0; b < ncb; ++b)
                     for (int32_t kh = 0; kh < s->Fh; ++kh)
                     {
@@ -380,8 +382,20 @@ void so_conv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
             }
 }
 
-void so_dwconv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
-                    const uint8_t *filt, const int32_t *bias, uint8_t *out)
+void so_conv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
+                  const uint8_t *filt, const int32_t *bias, uint8_t *out)
+{
+    conv2d_u8_impl(s, q, in, filt, bias, NULL, out);
+}
+
+void so_partial_conv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
+                          const uint8_t *filt, const int32_t *partial, uint8_t *out)
+{
+    conv2d_u8_impl(s, q, in, filt, NULL, partial, out);
+}
+
+static void dwconv2d_u8_impl(const so_shape *s, const so_quant *q, const uint8_t *in,
+                             const uint8_t *filt, const int32_t *bias, const int32_t *partial, uint8_t *out)
 {
     const int32_t cb = s->cob;
     const int32_t Ho = so_out_dim(s->H, s->pad_t, s->pad_b, s->Fh, s->stride);
@@ -390,7 +404,7 @@ void so_dwconv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
         for (int32_t oh = 0; oh < Ho; ++oh)
             for (int32_t ow = 0; ow < Wo; ++ow)
             {
-                int32_t acc = q->k_zero + (bias ? bias[c] : 0);
+                int32_t acc = partial ? partial[act_idx(Ho, Wo, cb, c, oh, ow)] : q->k_zero + (bias ? bias[c] : 0);
                 for (int32_t kh = 0; kh < s->Fh; ++kh)
                 {
                     const int32_t ih = oh * s->stride - s->pad_t + kh;
@@ -409,6 +423,18 @@ void so_dwconv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
                 out[act_idx(Ho, Wo, cb, c, oh, ow)] =
                     (uint8_t)so_requant(acc, q->lshift, q->rshift, q->multiplier);
             }
+}
+
+void so_dwconv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
+                    const uint8_t *filt, const int32_t *bias, uint8_t *out)
+{
+    dwconv2d_u8_impl(s, q, in, filt, bias, NULL, out);
+}
+
+void so_partial_dwconv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
+                            const uint8_t *filt, const int32_t *partial, uint8_t *out)
+{
+    dwconv2d_u8_impl(s, q, in, filt, NULL, partial, out);
 }
 
 void so_groupconv2d_u8(const so_shape *s, const so_quant *q, int32_t groups, const uint8_t *in,

@@ -90,6 +90,14 @@ void so_dwconv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
                     const uint8_t *filt, const int32_t *bias, uint8_t *out);
 void so_groupconv2d_u8(const so_shape *s, const so_quant *q, int32_t groups, const uint8_t *in,
                        const uint8_t *filt, const int32_t *bias, uint8_t *out);
+/* PartialConv2D / PartialDepthwiseConv2D<QUInt8Buffer> (interface_abstract.hpp:595-767, :1194): the
+ * accumulators start from the int32 values `partial`, laid out like the output ([Ho][Wo][cob] for the one
+ * block of cob output channels for which the reference's in-buffer int32 storage does not overlap
+ * itself: s->K == s->cob, resp. s->C == s->cob), and the requantised bytes go to `out`. */
+void so_partial_conv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
+                          const uint8_t *filt, const int32_t *partial, uint8_t *out);
+void so_partial_dwconv2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in,
+                            const uint8_t *filt, const int32_t *partial, uint8_t *out);
 void so_maxpool2d_u8(const so_shape *s, const so_quant *q, const uint8_t *in, uint8_t *out);
 void so_relu_u8(int64_t n, const so_quant *q, const uint8_t *in, uint8_t *out);
 /* NOT in the reference (no quint8 AveragePool2D exists there): sum of (a+zero_in)

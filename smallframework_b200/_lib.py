@@ -89,6 +89,7 @@ SIGNATURES = {
     "small_b200_nms_f32": [_VP, _I32, _I32, _F, _F, _I32, _VP, _I32, _VP, _VP, _VP],
     "small_b200_conv2d_u8": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_conv2d_u8_cuda_cores": [_LP, _VP, _VP, _VP, _VP, _VP],
+    "small_b200_conv2d_u8_tensor_core": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_dwconv2d_u8": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_conv2d_dwconv2d_u8_supported": [_LP, _LP],
     "small_b200_conv2d_dwconv2d_u8": [_LP, _LP, _VP, _VP, _VP, _VP, _VP, _VP, _VP],

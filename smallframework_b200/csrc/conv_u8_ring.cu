@@ -215,105 +215,116 @@ conv_u8_ring_kernel(const RingArgs a, const uint8_t *__restrict__ in, const uint
         const bool has_b = pt < NT * 2;
         const int bgrp = pt >> 5, bhalf = (pt >> 4) & 1, brow = pt & 15;
         bool ok = true;
-        unsigned produced = 0; // reduction steps this CTA has produced so far
-        for (int tile = blockIdx.x; tile < a.tiles && ok; tile += gridDim.x)
+        // The (tile, reduction step) pairs of this CTA form one sequence; a thread keeps the loads of
+        // IN_FLIGHT consecutive pairs outstanding, across tile boundaries, before it stores any of them.
+        const unsigned my_tiles = ((unsigned)a.tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+        const unsigned units = my_tiles * (unsigned)a.steps;
+        const unsigned hw_out = (unsigned)(a.Ho * a.Wo);
+        const int fwc = a.Fw * a.C;
+        for (unsigned w0 = 0; w0 < units && ok; w0 += IN_FLIGHT)
         {
-            const long long g = (long long)tile * TILE_M + row;
-            const bool live = g < total_px;
-            const int n = live ? (int)(g / ((long long)a.Ho * a.Wo)) : 0;
-            const int px = live ? (int)(g - (long long)n * a.Ho * a.Wo) : 0;
-            const int oh = px / a.Wo, ow = px - oh * a.Wo;
-            const int ih0 = oh * a.row_stride - a.pad_t, iw0 = ow * a.stride - a.pad_l;
-            const uint8_t *img = in + (size_t)n * a.C * a.H * a.W;
-            for (int q0 = 0; q0 < a.steps && ok; q0 += IN_FLIGHT)
+            uint4 va[IN_FLIGHT], vb[IN_FLIGHT];
+#pragma unroll
+            for (int u = 0; u < IN_FLIGHT; ++u)
             {
-                uint4 va[IN_FLIGHT], vb[IN_FLIGHT];
-#pragma unroll
-                for (int u = 0; u < IN_FLIGHT; ++u)
+                va[u] = make_uint4(0u, 0u, 0u, 0u);
+                vb[u] = make_uint4(0u, 0u, 0u, 0u);
+                const unsigned w = w0 + u;
+                if (w >= units)
+                    continue;
+                const unsigned ti = w / (unsigned)a.steps;
+                const int q = (int)(w - ti * (unsigned)a.steps);
+                const unsigned g = (blockIdx.x + ti * gridDim.x) * TILE_M + row;
+                const bool live = g < total_px;
+                const unsigned n = live ? g / hw_out : 0u;
+                const unsigned px = live ? g - n * hw_out : 0u;
+                const int oh = (int)(px / (unsigned)a.Wo), ow = (int)px - oh * a.Wo;
+                const int ih0 = oh * a.row_stride - a.pad_t, iw0 = ow * a.stride - a.pad_l;
+                const uint8_t *img = in + (size_t)n * a.C * a.H * a.W;
+                if (FIRST)
                 {
-                    const int q = q0 + u;
-                    va[u] = make_uint4(0u, 0u, 0u, 0u);
-                    vb[u] = make_uint4(0u, 0u, 0u, 0u);
-                    if (q >= a.steps)
-                        continue;
-                    if (FIRST)
+                    // reduction index k = (kh * Fw + kw) * C + c, 16 of them per chunk; the three
+                    // counters advance byte by byte
+                    const int k0 = q * 32 + half * 16;
+                    unsigned wv[4] = {0u, 0u, 0u, 0u};
+                    if (live && k0 < kmax)
                     {
-                        // reduction index k = (kh * Fw + kw) * C + c, 16 of them per chunk
-                        const int k0 = q * 32 + half * 16;
-                        unsigned w[4] = {0u, 0u, 0u, 0u};
-                        if (live)
-                        {
+                        int kh = k0 / fwc;
+                        const int r = k0 - kh * fwc;
+                        int kw = r / a.C, c = r - kw * a.C;
 #pragma unroll
-                            for (int b = 0; b < 16; ++b)
+                        for (int b = 0; b < 16; ++b)
+                        {
+                            const int ih = ih0 + kh, iw = iw0 + kw;
+                            if (kh < a.Fh && ih >= 0 && ih < a.H && iw >= 0 && iw < a.W)
                             {
-                                const int k = k0 + b;
-                                if (k < kmax)
+                                const unsigned v = (unsigned)img[((size_t)ih * a.W + iw) * a.C + c] ^ (flip_a & 0xffu);
+                                wv[b >> 2] |= v << (8 * (b & 3));
+                            }
+                            if (++c == a.C)
+                            {
+                                c = 0;
+                                if (++kw == a.Fw)
                                 {
-                                    const int tap = k / a.C, c = k - tap * a.C;
-                                    const int kh = tap / a.Fw, kw = tap - kh * a.Fw;
-                                    const int ih = ih0 + kh, iw = iw0 + kw;
-                                    if (ih >= 0 && ih < a.H && iw >= 0 && iw < a.W)
-                                    {
-                                        const unsigned v = (unsigned)img[((size_t)ih * a.W + iw) * a.C + c] ^ (flip_a & 0xffu);
-                                        w[b >> 2] |= v << (8 * (b & 3));
-                                    }
+                                    kw = 0;
+                                    ++kh;
                                 }
                             }
                         }
-                        va[u] = make_uint4(w[0], w[1], w[2], w[3]);
-                        if (has_b)
-                        {
-                            const int k = q * 32 + bhalf * 16 + brow;
-                            if (k < kmax) // filter [K/16][Fh*Fw*C rows][16]
-                            {
-                                const uint4 v = *reinterpret_cast<const uint4 *>(
-                                    filt + (((size_t)(nb * (NT / CB) + bgrp)) * kmax + k) * CB);
-                                vb[u] = make_uint4(v.x ^ flip_b, v.y ^ flip_b, v.z ^ flip_b, v.w ^ flip_b);
-                            }
-                        }
                     }
-                    else
+                    va[u] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                    if (has_b)
                     {
-                        const int tap = q / jpairs, j = q - tap * jpairs;
-                        const int kh = tap / a.Fw, kw = tap - kh * a.Fw;
-                        const int cb = 2 * j + half;
-                        const int ih = ih0 + kh, iw = iw0 + kw;
-                        if (live && cb < a.cbs && ih >= 0 && ih < a.H && iw >= 0 && iw < a.W)
-                        {
-                            const uint4 v = *reinterpret_cast<const uint4 *>(img + (((size_t)cb * a.H + ih) * a.W + iw) * CB);
-                            va[u] = make_uint4(v.x ^ flip_a, v.y ^ flip_a, v.z ^ flip_a, v.w ^ flip_a);
-                        }
-                        const int cbb = 2 * j + bhalf;
-                        if (has_b && cbb < a.cbs) // filter [K/16][C/16][Fh][Fw][16 c][16 k]
+                        const int k = q * 32 + bhalf * 16 + brow;
+                        if (k < kmax) // filter [K/16][Fh*Fw*C rows][16]
                         {
                             const uint4 v = *reinterpret_cast<const uint4 *>(
-                                filt + ((((size_t)(nb * (NT / CB) + bgrp)) * a.cbs + cbb) * taps + tap) * (CB * CB) +
-                                (size_t)brow * CB);
+                                filt + (((size_t)(nb * (NT / CB) + bgrp)) * kmax + k) * CB);
                             vb[u] = make_uint4(v.x ^ flip_b, v.y ^ flip_b, v.z ^ flip_b, v.w ^ flip_b);
                         }
                     }
                 }
-#pragma unroll
-                for (int u = 0; u < IN_FLIGHT; ++u)
+                else
                 {
-                    if (q0 + u >= a.steps || !ok)
-                        continue;
-                    const unsigned s = produced % STAGES, use = produced / STAGES;
-                    if (use > 0) // every lane waits; the verdict is made the same for the whole warp
-                        ok = __all_sync(0xffffffffu, mbar_wait(&empty_bar[s], (use - 1) & 1u, status, 32));
-                    if (ok)
+                    const int tap = q / jpairs, j = q - tap * jpairs;
+                    const int kh = tap / a.Fw, kw = tap - kh * a.Fw;
+                    const int cb = 2 * j + half;
+                    const int ih = ih0 + kh, iw = iw0 + kw;
+                    if (live && cb < a.cbs && ih >= 0 && ih < a.H && iw >= 0 && iw < a.W)
                     {
-                        uint8_t *st = smem + (size_t)s * G::STAGE;
-                        *reinterpret_cast<uint4 *>(st + (size_t)half * TILE_M * CB + (size_t)row * CB) = va[u];
-                        if (has_b)
-                            *reinterpret_cast<uint4 *>(st + G::A_BYTES + (size_t)bgrp * 2 * CB * CB + (size_t)bhalf * CB * CB +
-                                                       (size_t)brow * CB) = vb[u];
-                        fence_proxy_async();
-                        __syncwarp();
-                        if (lane == 0)
-                            mbar_arrive(&full_bar[s]);
+                        const uint4 v = *reinterpret_cast<const uint4 *>(img + (((size_t)cb * a.H + ih) * a.W + iw) * CB);
+                        va[u] = make_uint4(v.x ^ flip_a, v.y ^ flip_a, v.z ^ flip_a, v.w ^ flip_a);
                     }
-                    ++produced;
+                    const int cbb = 2 * j + bhalf;
+                    if (has_b && cbb < a.cbs) // filter [K/16][C/16][Fh][Fw][16 c][16 k]
+                    {
+                        const uint4 v = *reinterpret_cast<const uint4 *>(
+                            filt + ((((size_t)(nb * (NT / CB) + bgrp)) * a.cbs + cbb) * taps + tap) * (CB * CB) +
+                            (size_t)brow * CB);
+                        vb[u] = make_uint4(v.x ^ flip_b, v.y ^ flip_b, v.z ^ flip_b, v.w ^ flip_b);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < IN_FLIGHT; ++u)
+            {
+                const unsigned w = w0 + u;
+                if (w >= units || !ok)
+                    continue;
+                const unsigned s = w % STAGES, use = w / STAGES;
+                if (use > 0) // every lane waits; the verdict is made the same for the whole warp
+                    ok = __all_sync(0xffffffffu, mbar_wait(&empty_bar[s], (use - 1) & 1u, status, 32));
+                if (ok)
+                {
+                    uint8_t *st = smem + (size_t)s * G::STAGE;
+                    *reinterpret_cast<uint4 *>(st + (size_t)half * TILE_M * CB + (size_t)row * CB) = va[u];
+                    if (has_b)
+                        *reinterpret_cast<uint4 *>(st + G::A_BYTES + (size_t)bgrp * 2 * CB * CB + (size_t)bhalf * CB * CB +
+                                                   (size_t)brow * CB) = vb[u];
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(&full_bar[s]);
                 }
             }
         }
@@ -421,8 +432,8 @@ int conv2d_u8_ring(const small_b200_layer *L, const uint8_t *in, const uint8_t *
     a.cbs = first ? 1 : L->C / CB;
     a.steps = first ? (a.Fh * a.Fw * a.C + 31) / 32 : a.Fh * a.Fw * ((a.cbs + 1) / 2);
     const long long px = (long long)a.N * a.Ho * a.Wo;
-    if ((px + TILE_M - 1) / TILE_M > 0x3fffffffLL / (L->K / CB))
-        return -1;
+    if (px + TILE_M >= 0x7fffffffLL || ((px + TILE_M - 1) / TILE_M) * a.steps >= 0x7fffffffLL)
+        return -1; // 32-bit pixel and step counters in the kernel
     a.tiles = (int)((px + TILE_M - 1) / TILE_M);
     a.zero_in = L->zero_in; a.zero_filt = L->zero_filt;
     a.lshift = L->lshift; a.rshift = L->rshift; a.mult = L->multiplier; a.k_zero = L->k_zero;

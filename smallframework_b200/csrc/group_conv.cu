@@ -294,8 +294,13 @@ int small_b200_groupconv2d_u8(const small_b200_layer *L, int32_t groups, const u
     if (a.sh != a.stride)
         return fail(SMALL_B200_INVALID_ARGUMENT, "GroupConv2D<quint8> ERROR: stride unsupported.");
     if (a.accumulate)
+        // The int32 partial sums of output channel k of the groups start at byte k * Ho*Wo*16 of the
+        // output buffer and are four times as long as the channel's bytes (interface_abstract.hpp:1470,
+        // q_abstract_layer.hpp:1135-1144), so they overlap unless a group has ONE output channel -- and
+        // the interface accepts multiples of 16 channels per group only.  No shape has a defined result.
         return fail(SMALL_B200_INVALID_ARGUMENT,
-                    "PartialGroupConv2D<quint8> ERROR: the int32 partial-sum form is not provided.");
+                    "PartialGroupConv2D<quint8> ERROR: the int32 partial sums of different output channels overlap "
+                    "inside the output buffer for every shape the interface accepts.");
     const long long items = (long long)a.N * (a.G / CB) * a.K * a.Ho * a.Wo;
     if (items == 0)
         return SMALL_B200_OK;

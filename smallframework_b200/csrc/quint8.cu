@@ -42,9 +42,13 @@ __device__ __forceinline__ uint4 pack16(const int *v)
 // Dense convolution, one thread per output pixel and block of 16 output channels.
 // All threads of a CTA share the output-channel block, so filter reads are warp-uniform
 // 16-byte loads served by L1.
+// PARTIAL (the reference's int32 partial-sum form, one image and one block of output channels): the
+// accumulators start from the int32 values the output buffer holds, [pixel][16], and go back there as
+// int32; requant_in_place_kernel turns them into bytes afterwards.
+template <bool PARTIAL>
 __global__ void __launch_bounds__(128)
 conv2d_u8_direct_kernel(const QArgs a, const uint8_t *__restrict__ in, const uint8_t *__restrict__ filt,
-                        const int32_t *__restrict__ bias, uint8_t *__restrict__ out)
+                        const int32_t *__restrict__ bias, uint8_t *out)
 {
     const int p = blockIdx.x * blockDim.x + threadIdx.x;
     const int kb = blockIdx.y, n = blockIdx.z;
@@ -52,9 +56,22 @@ conv2d_u8_direct_kernel(const QArgs a, const uint8_t *__restrict__ in, const uin
         return;
     const int oh = p / a.Wo, ow = p - oh * a.Wo;
     int acc[CB];
+    if (PARTIAL)
+    {
+        const int4 *seed = reinterpret_cast<const int4 *>(out) + (size_t)p * 4;
 #pragma unroll
-    for (int k = 0; k < CB; ++k)
-        acc[k] = a.k_zero + (bias ? bias[kb * CB + k] : 0);
+        for (int k4 = 0; k4 < 4; ++k4)
+        {
+            const int4 v = seed[k4];
+            acc[4 * k4] = v.x; acc[4 * k4 + 1] = v.y; acc[4 * k4 + 2] = v.z; acc[4 * k4 + 3] = v.w;
+        }
+    }
+    else
+    {
+#pragma unroll
+        for (int k = 0; k < CB; ++k)
+            acc[k] = a.k_zero + (bias ? bias[kb * CB + k] : 0);
+    }
     const int taps = a.Fh * a.Fw;
     const uint8_t *img = in + (size_t)n * a.C * a.H * a.W;
     const uint8_t *fk = filt + (size_t)kb * a.cbs * taps * a.cib * CB;
@@ -101,16 +118,51 @@ conv2d_u8_direct_kernel(const QArgs a, const uint8_t *__restrict__ in, const uin
             }
         }
     }
+    if (PARTIAL)
+    {
+        int4 *dst = reinterpret_cast<int4 *>(out) + (size_t)p * 4;
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)
+            dst[k4] = make_int4(acc[4 * k4], acc[4 * k4 + 1], acc[4 * k4 + 2], acc[4 * k4 + 3]);
+        return;
+    }
     *reinterpret_cast<uint4 *>(out + (((size_t)n * (a.K / CB) + kb) * a.Ho * a.Wo + p) * CB) =
         requant_pack16(acc, a.lshift, a.rshift, a.mult);
 }
 
+// The int32 accumulators [pixels][16] at the start of a buffer become the bytes [pixels][16] at the start
+// of the same buffer.  Pixel p's bytes land on the accumulators of pixel p / 4, so the pass runs as ONE
+// CTA that walks the pixels in order, a block of 1024 at a time: read, barrier, write, barrier -- every
+// accumulator is read before anything is written over it, as in the reference's sequential loop nest.
+__global__ void __launch_bounds__(1024) requant_in_place_kernel(int pixels, const QArgs a, uint8_t *buf)
+{
+    for (int base = 0; base < pixels; base += 1024)
+    {
+        const int p = base + (int)threadIdx.x;
+        int acc[CB];
+        if (p < pixels)
+        {
+            const int4 *src = reinterpret_cast<const int4 *>(buf) + (size_t)p * 4;
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4)
+            {
+                const int4 v = src[k4];
+                acc[4 * k4] = v.x; acc[4 * k4 + 1] = v.y; acc[4 * k4 + 2] = v.z; acc[4 * k4 + 3] = v.w;
+            }
+        }
+        __syncthreads();
+        if (p < pixels)
+            *reinterpret_cast<uint4 *>(buf + (size_t)p * CB) = requant_pack16(acc, a.lshift, a.rshift, a.mult);
+        __syncthreads();
+    }
+}
+
 // OP: 0 depthwise conv, 1 max pool, 2 average pool; one thread per output pixel and block
 // of 16 channels (one 128-bit load per tap, one 128-bit store).
-template <int OP>
+template <int OP, bool PARTIAL = false>
 __global__ void __launch_bounds__(256)
 window_u8_kernel(const QArgs a, const uint8_t *__restrict__ in, const uint8_t *__restrict__ filt,
-                 const int32_t *__restrict__ bias, uint8_t *__restrict__ out)
+                 const int32_t *__restrict__ bias, uint8_t *out)
 {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long total = (long long)a.N * (a.C / CB) * a.Ho * a.Wo;
@@ -126,6 +178,16 @@ window_u8_kernel(const QArgs a, const uint8_t *__restrict__ in, const uint8_t *_
 #pragma unroll
     for (int k = 0; k < CB; ++k)
         acc[k] = a.k_zero + ((OP == 0 && bias) ? bias[cb * CB + k] : 0);
+    if (PARTIAL) // one image, one channel block: o is the pixel
+    {
+        const int4 *seed = reinterpret_cast<const int4 *>(out) + (size_t)o * 4;
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)
+        {
+            const int4 v = seed[k4];
+            acc[4 * k4] = v.x; acc[4 * k4 + 1] = v.y; acc[4 * k4 + 2] = v.z; acc[4 * k4 + 3] = v.w;
+        }
+    }
     if (OP == 1)
     {
         // q_abstract_layer.hpp:277-288: interior tiles are seeded with the RAW first tap
@@ -173,6 +235,14 @@ window_u8_kernel(const QArgs a, const uint8_t *__restrict__ in, const uint8_t *_
                     acc[k] += byte_of(v, k) + a.zero_in;
             }
         }
+    }
+    if (PARTIAL)
+    {
+        int4 *dst = reinterpret_cast<int4 *>(out) + (size_t)o * 4;
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)
+            dst[k4] = make_int4(acc[4 * k4], acc[4 * k4 + 1], acc[4 * k4 + 2], acc[4 * k4 + 3]);
+        return;
     }
     *reinterpret_cast<uint4 *>(out + o * CB) = requant_pack16(acc, a.lshift, a.rshift, a.mult);
 }
@@ -576,6 +646,25 @@ int check_quant(const small_b200_layer *L, const char *name)
     return SMALL_B200_OK;
 }
 
+// The reference's quint8 Partial forms (interface_abstract.hpp:595-767 PartialConv2D, :1194
+// PartialDepthwiseConv2D) reuse the uint8 output buffer as int32 storage: the accumulators of output
+// channel block k start at BYTE k * Ho*Wo*block and are four times as long as the block's bytes
+// (q_abstract_layer.hpp:1135-1144), so the accumulators of one block lie over those of the next three and
+// the form has a defined meaning for ONE block of output channels only -- 16 channels on this platform --
+// and one image.  There: out holds int32 [Ho*Wo][16] on entry and the bytes [Ho*Wo][16] of
+// requantise(entry + convolution) at its start on return.  Anything else is refused.
+int check_partial_u8(const small_b200_layer *L, const char *name, int channels, const int32_t *bias)
+{
+    if (channels != CB || L->N != 1)
+        return fail(SMALL_B200_INVALID_ARGUMENT,
+                    std::string(name) + " ERROR: the int32 partial sums of different blocks of output channels (and of "
+                                        "different images) overlap inside the output buffer; only 16 output channels "
+                                        "and one image have a defined result.");
+    if (bias)
+        return fail(SMALL_B200_INVALID_ARGUMENT, std::string(name) + " ERROR: the partial-sum form takes no bias.");
+    return SMALL_B200_OK;
+}
+
 template <int OP>
 int launch_window(const small_b200_layer *L, const char *name, int max_stride, const uint8_t *in,
                   const uint8_t *filt, const int32_t *bias, uint8_t *out, void *stream)
@@ -586,6 +675,20 @@ int launch_window(const small_b200_layer *L, const char *name, int max_stride, c
         return rc;
     QArgs a; fill(L, a, false);
     const long long items = (long long)a.N * (a.C / CB) * a.Ho * a.Wo;
+    if (L->accumulate)
+    {
+        if (OP != 0)
+            return fail(SMALL_B200_INVALID_ARGUMENT, std::string(name) + " ERROR: no partial form.");
+        if (int rc = check_partial_u8(L, "PartialDepthwiseConv2D<quint8>", L->C, bias))
+            return rc;
+        if (items == 0)
+            return SMALL_B200_OK;
+        window_u8_kernel<OP, true><<<(unsigned)((items + 255) / 256), 256, 0, as_stream(stream)>>>(a, in, filt, nullptr, out);
+        if (int rc = launched(name))
+            return rc;
+        requant_in_place_kernel<<<1, 1024, 0, as_stream(stream)>>>(a.Ho * a.Wo, a, out);
+        return launched("requant_in_place_kernel");
+    }
     if (items == 0)
         return SMALL_B200_OK;
     if (OP == 0 && a.zero_filt == -128 && (a.zero_in == 0 || a.zero_in == -128) && a.Fh == 3 && a.Fw == 3 &&
@@ -656,16 +759,31 @@ int conv2d_u8_ring(const small_b200_layer *L, const uint8_t *in, const uint8_t *
 
 namespace
 {
+// path: 0 = the faster kernel for the shape, 1 = CUDA cores only, 2 = tensor cores or an error
 int conv2d_u8_dispatch(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt, const int32_t *bias,
-                       uint8_t *out, void *stream, bool tensor_core)
+                       uint8_t *out, void *stream, int path)
 {
+    const bool tensor_core = path != 1;
     if (int rc = check_window_layer(L, "Conv2D<quint8>", true, 2))
         return rc;
     if (int rc = check_quant(L, "Conv2D<quint8>"))
         return rc;
     if (L->accumulate)
-        return fail(SMALL_B200_INVALID_ARGUMENT,
-                    "PartialConv2D<quint8> ERROR: the int32 partial-sum form is not provided.");
+    {
+        if (int rc = check_partial_u8(L, "PartialConv2D<quint8>", L->K, bias))
+            return rc;
+        if (path == 2)
+            return fail(SMALL_B200_INVALID_ARGUMENT, "PartialConv2D<quint8> ERROR: runs on the CUDA cores only.");
+        QArgs a; fill(L, a, true);
+        if (a.Ho <= 0 || a.Wo <= 0)
+            return SMALL_B200_OK;
+        dim3 grid((a.Ho * a.Wo + 127) / 128, 1, 1);
+        conv2d_u8_direct_kernel<true><<<grid, 128, 0, as_stream(stream)>>>(a, in, filt, nullptr, out);
+        if (int rc = launched("conv2d_u8_direct_kernel"))
+            return rc;
+        requant_in_place_kernel<<<1, 1024, 0, as_stream(stream)>>>(a.Ho * a.Wo, a, out);
+        return launched("requant_in_place_kernel");
+    }
     const int tc = tensor_core ? conv2d_u8_tensor_core(L, in, filt, bias, out, as_stream(stream)) : -1;
     if (tc >= 0)
         return tc;
@@ -678,12 +796,19 @@ int conv2d_u8_dispatch(const small_b200_layer *L, const uint8_t *in, const uint8
         if (tc1 >= 0)
             return tc1;
     }
-    if (tensor_core)
+    // A reduction of one 32-byte step into 16 channels (a 1x1 layer on 16 channels, a 3x3 first layer on
+    // 3) is a streaming layer with nothing for the tensor core to do: measured on MobileNet-v1 0.25 uint8
+    // at batch 2048, the implicit GEMM takes 0.43 ms against 0.35 ms for the 3x3x3 first layer and 0.188
+    // against 0.185 ms for 16 -> 16 channels, and wins from 16 -> 32 channels on (0.052 against 0.097 ms).
+    const long long red = (long long)L->C * L->Fh * L->Fw;
+    if (path == 2 || (tensor_core && (red > 32 || (L->C >= CB && L->K >= 32))))
     {
         const int tc2 = conv2d_u8_ring(L, in, filt, bias, out, as_stream(stream));
         if (tc2 >= 0)
             return tc2;
     }
+    if (path == 2)
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<quint8> ERROR: layer not covered by the tensor-core kernels.");
     if (a.C == 1 && a.zero_filt == -128 && (a.zero_in == 0 || a.zero_in == -128))
     {
         // one-channel image: rows of the window are words of the (zero-padded) image
@@ -710,7 +835,7 @@ int conv2d_u8_dispatch(const small_b200_layer *L, const uint8_t *in, const uint8
         }
     }
     dim3 grid((a.Ho * a.Wo + 127) / 128, a.K / CB, a.N);
-    conv2d_u8_direct_kernel<<<grid, 128, 0, as_stream(stream)>>>(a, in, filt, bias, out);
+    conv2d_u8_direct_kernel<false><<<grid, 128, 0, as_stream(stream)>>>(a, in, filt, bias, out);
     return launched("conv2d_u8_direct_kernel");
 }
 } // namespace
@@ -720,13 +845,19 @@ extern "C"
 int small_b200_conv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
                          const int32_t *bias, uint8_t *out, void *stream)
 {
-    return conv2d_u8_dispatch(L, in, filt, bias, out, stream, true);
+    return conv2d_u8_dispatch(L, in, filt, bias, out, stream, 0);
 }
 
 int small_b200_conv2d_u8_cuda_cores(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
                                     const int32_t *bias, uint8_t *out, void *stream)
 {
-    return conv2d_u8_dispatch(L, in, filt, bias, out, stream, false);
+    return conv2d_u8_dispatch(L, in, filt, bias, out, stream, 1);
+}
+
+int small_b200_conv2d_u8_tensor_core(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,
+                                     const int32_t *bias, uint8_t *out, void *stream)
+{
+    return conv2d_u8_dispatch(L, in, filt, bias, out, stream, 2);
 }
 
 int small_b200_dwconv2d_u8(const small_b200_layer *L, const uint8_t *in, const uint8_t *filt,

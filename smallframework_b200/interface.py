@@ -133,16 +133,18 @@ def _need(buf, elems, what):
 
 # --------------------------------------------------------------------------- dense conv
 def _conv(name, partial, kh, kw, stride, t, b, l, r, K, C_, H, W, inp, filt, out, bias, act,
-          slope, batch, stream, cuda_cores=False):
+          slope, batch, stream, path=None):
     L = _layer(batch, C_, K, H, W, kh, kw, stride, t, b, l, r, int(partial), act, slope, inp, filt, out)
     ho, wo = L.out_hw()
     if C_ % CB == 0 or C_ in (1, 2, 3):
         _need(inp, batch * C_ * H * W, name + " input")
         _need(filt, K * C_ * kh * kw, name + " filter")
     if K % CB == 0:
-        _need(out, batch * K * ho * wo, name + " output")
+        # the quint8 partial form finds its int32 partial sums in the output buffer
+        _need(out, (4 if partial and _is_q(out) else 1) * batch * K * ho * wo, name + " output")
     if _is_q(out):
-        fn = lib().small_b200_conv2d_u8_cuda_cores if cuda_cores else lib().small_b200_conv2d_u8
+        fn = {None: lib().small_b200_conv2d_u8, "cuda_cores": lib().small_b200_conv2d_u8_cuda_cores,
+              "tensor_core": lib().small_b200_conv2d_u8_tensor_core}[path]
     else:
         fn = lib().small_b200_conv2d_f32
     check(fn(C.byref(L), _ptr(inp), _ptr(filt), _ptr(bias), _ptr(out), _stream(stream)))
@@ -150,18 +152,20 @@ def _conv(name, partial, kh, kw, stride, t, b, l, r, K, C_, H, W, inp, filt, out
 
 def Conv2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
            output_channels, input_channels, input_height, input_width,
-           input_buf, filter_buf, output_buf, *, batch=1, stream=None, cuda_cores=False):
-    """small::Conv2D (interface_abstract.hpp:46-221 float, :229-404 quint8).  cuda_cores=True keeps a
-    quint8 layer off the tensor cores (the other implementation of the same arithmetic)."""
+           input_buf, filter_buf, output_buf, *, batch=1, stream=None, path=None):
+    """small::Conv2D (interface_abstract.hpp:46-221 float, :229-404 quint8).  For quint8 buffers path =
+    "cuda_cores" / "tensor_core" forces one of the two implementations of the same arithmetic."""
     _conv("Conv2D", False, kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
           output_channels, input_channels, input_height, input_width, input_buf, filter_buf,
-          output_buf, None, ACT_NONE, 0.0, batch, stream, cuda_cores)
+          output_buf, None, ACT_NONE, 0.0, batch, stream, path)
 
 
 def PartialConv2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
                   output_channels, input_channels, input_height, input_width,
                   input_buf, filter_buf, output_buf, *, batch=1, stream=None):
-    """small::PartialConv2D (:416-587): accumulates onto the existing output."""
+    """small::PartialConv2D (:416-587 float, :595-767 quint8): accumulates onto the existing output.  The
+    quint8 form finds int32 partial sums [Ho*Wo][16] at the start of output_buf (four bytes per element)
+    and is defined for 16 output channels and one image only (further blocks' sums would overlap)."""
     _conv("PartialConv2D", True, kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
           output_channels, input_channels, input_height, input_width, input_buf, filter_buf,
           output_buf, None, ACT_NONE, 0.0, batch, stream)
@@ -188,14 +192,14 @@ def Conv2D_Bias_ReLU(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r
 def Conv2D_Bias_Activation(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
                            output_channels, input_channels, input_height, input_width,
                            input_buf, filter_buf, bias_buf, output_buf, *, activation=ACT_NONE,
-                           negative_slope=0.0, batch=1, stream=None, cuda_cores=False):
+                           negative_slope=0.0, batch=1, stream=None, path=None):
     """The single-element-before / -after slots of the reference's fused loop nest
     (abstract_layer.hpp:131-177) with bias before and none / ReLU / LeakyReLU after; equals
     the unfused chain Bias -> PartialConv2D -> activation of Conv2DLayer.hpp:827-878.
     For quint8 buffers bias_buf is an int32 torch tensor added to the accumulator seed."""
     _conv("Conv2D_Bias_Activation", False, kernel_height, kernel_width, stride, t_pad, b_pad,
           l_pad, r_pad, output_channels, input_channels, input_height, input_width, input_buf,
-          filter_buf, output_buf, bias_buf, activation, negative_slope, batch, stream, cuda_cores)
+          filter_buf, output_buf, bias_buf, activation, negative_slope, batch, stream, path)
 
 
 def conv2d_maxpool_supported(conv_kernel_height, conv_kernel_width, conv_stride, conv_pads,
@@ -236,7 +240,7 @@ def _window(fn_f32, fn_u8, name, has_filter, kh, kw, stride, t, b, l, r, C_, H, 
     ho, wo = L.out_hw()
     if C_ % CB == 0:
         _need(inp, batch * C_ * H * W, name + " input")
-        _need(out, batch * C_ * ho * wo, name + " output")
+        _need(out, (4 if partial and _is_q(out) else 1) * batch * C_ * ho * wo, name + " output")
     fn = getattr(lib(), fn_u8 if _is_q(out) else fn_f32)
     if has_filter:
         check(fn(C.byref(L), _ptr(inp), _ptr(filt), _ptr(bias), _ptr(out), _stream(stream)))
@@ -257,9 +261,9 @@ def DepthwiseConv2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_
 def PartialDepthwiseConv2D(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad,
                            input_channels, input_height, input_width,
                            input_buf, filter_buf, output_buf, *, batch=1, stream=None):
-    """small::PartialDepthwiseConv2D (:1127), float only."""
-    if _is_q(output_buf):
-        raise ValueError("PartialDepthwiseConv2D<quint8> ERROR: not provided.")
+    """small::PartialDepthwiseConv2D (:1127 float, :1194 quint8).  The quint8 form finds int32 partial
+    sums [Ho*Wo][16] at the start of output_buf (four bytes per element) and is defined for 16 channels and
+    one image only: the partial sums of further channel blocks would overlap there."""
     _window("small_b200_dwconv2d_f32", "small_b200_dwconv2d_u8", "PartialDepthwiseConv2D", True,
             kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pad, input_channels,
             input_height, input_width, input_buf, filter_buf, output_buf, None, True, ACT_NONE,
@@ -305,10 +309,9 @@ def GroupConv2D(kernel_height, kernel_width, stride, output_groups, t_pad, b_pad
 def PartialGroupConv2D(kernel_height, kernel_width, stride, output_groups, t_pad, b_pad, l_pad, r_pad,
                        input_channels, input_height, input_width, input_buf, filter_buf, output_buf,
                        *, batch=1, stream=None):
-    """small::PartialGroupConv2D (:1402), float only (the quint8 form, :1470, would reload int32
-    partial sums from the uint8 output)."""
-    if _is_q(output_buf):
-        raise ValueError("PartialGroupConv2D<quint8> ERROR: not provided.")
+    """small::PartialGroupConv2D (:1402 float).  The quint8 form (:1470) keeps the int32 partial sums of
+    output channel k at byte k * Ho*Wo*16 of the uint8 output, four times the channel's length: for the
+    16-or-more channels per group the interface accepts they always overlap, so the library refuses it."""
     _group("PartialGroupConv2D", True, kernel_height, kernel_width, stride, output_groups, t_pad,
            b_pad, l_pad, r_pad, input_channels, input_height, input_width, input_buf, filter_buf,
            output_buf, None, ACT_NONE, 0.0, batch, stream)

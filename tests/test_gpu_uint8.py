@@ -58,13 +58,13 @@ _case_id = lambda c: "C{}_K{}_{}x{}_k{}x{}_s{}_{}_n{}".format(*[
 
 @pytest.mark.parametrize("case", CONV_CASES, ids=_case_id)
 @pytest.mark.parametrize("with_bias", [False, True])
-@pytest.mark.parametrize("cuda_cores", [False, True], ids=["tensor_core", "cuda_cores"])
-def test_conv2d_u8(oracle, case, with_bias, cuda_cores):
+@pytest.mark.parametrize("path", [None, "cuda_cores", "tensor_core"], ids=["auto", "cuda_cores", "tensor_core"])
+def test_conv2d_u8(oracle, case, with_bias, path):
     C, K, H, W, Fh, Fw, s, pm, N = case
     pads = same_pads(H, W, Fh, Fw, s) if pm == "same" else (0, 0, 0, 0) if pm == "valid" else pm
     rng = np.random.default_rng(abs(hash((case, with_bias))) % (1 << 31))
     q = _quant(rng, C * Fh * Fw)
-    _check_conv(oracle, case, pads, q, rng, with_bias, cuda_cores)
+    _check_conv(oracle, case, pads, q, rng, with_bias, path)
 
 
 # Shapes for the implicit-GEMM kernel (every window / stride / padding / channel count on tcgen05
@@ -98,10 +98,10 @@ def test_conv2d_u8_implicit_gemm(oracle, case, zp):
     pads = same_pads(H, W, Fh, Fw, s) if pm == "same" else (0, 0, 0, 0) if pm == "valid" else pm
     rng = np.random.default_rng(abs(hash((case, zp))) % (1 << 31))
     q = _quant(rng, C * Fh * Fw, zp)
-    _check_conv(oracle, case, pads, q, rng, True, False)
+    _check_conv(oracle, case, pads, q, rng, True, "tensor_core")
 
 
-def _check_conv(oracle, case, pads, q, rng, with_bias, cuda_cores):
+def _check_conv(oracle, case, pads, q, rng, with_bias, path):
     C, K, H, W, Fh, Fw, s, pm, N = case
     x = P.pack_activation(rng.integers(0, 256, (N, C, H, W)).astype(np.uint8))
     w = P.pack_conv_filter(rng.integers(0, 256, (K, C, Fh, Fw)).astype(np.uint8))
@@ -112,9 +112,9 @@ def _check_conv(oracle, case, pads, q, rng, with_bias, cuda_cores):
     if with_bias:
         import torch
         S.Conv2D_Bias_Activation(Fh, Fw, s, *pads, K, C, H, W, I, F,
-                                 torch.from_numpy(bias).cuda(), O, batch=N, cuda_cores=cuda_cores)
+                                 torch.from_numpy(bias).cuda(), O, batch=N, path=path)
     else:
-        S.Conv2D(Fh, Fw, s, *pads, K, C, H, W, I, F, O, batch=N, cuda_cores=cuda_cores)
+        S.Conv2D(Fh, Fw, s, *pads, K, C, H, W, I, F, O, batch=N, path=path)
     want = np.stack([oracle.conv2d_u8(sh, q, x[n], w, bias=bias) for n in range(N)])
     got = O.numpy().reshape(N, -1)
     assert _lib.device_status() == 0  # no tensor-core kernel gave up on a bounded wait
@@ -276,3 +276,64 @@ def test_global_average_pool_u8(oracle, shape_, zero_in):
     want = np.stack([oracle.pool2d_u8(sh, q, x[n], average=True) for n in range(N)])
     assert np.array_equal(O.numpy().reshape(N, -1), want)
     assert want.min() < want.max()
+
+
+PARTIAL_CASES = [
+    # C, H, W, Fh, Fw, stride, pads
+    (16, 9, 11, 3, 3, 1, "same"),
+    (64, 40, 37, 1, 1, 1, "valid"),     # more than one block of 1024 pixels in the in-place pass
+    (48, 12, 12, 3, 3, 2, "same"),
+    (3, 16, 16, 3, 3, 2, "same"),       # first layer
+    (32, 7, 5, 5, 3, 1, (2, 2, 1, 1)),
+]
+
+
+@pytest.mark.parametrize("case", PARTIAL_CASES, ids=lambda c: "C{}_{}x{}_k{}x{}_s{}_{}".format(*[
+    "".join(map(str, v)) if isinstance(v, tuple) else v for v in c]))
+def test_partial_forms_u8(oracle, case):
+    """PartialConv2D / PartialDepthwiseConv2D<quint8>: int32 partial sums waiting at
+    the start of the output buffer, 16 output channels, one image -- where the reference's in-buffer
+    int32 storage does not overlap itself.  The oracle's form is pinned to the compiled reference in
+    tests/test_oracle_reference.py."""
+    import torch
+    C, H, W, Fh, Fw, s, pm = case
+    K = 16
+    pads = same_pads(H, W, Fh, Fw, s) if pm == "same" else (0, 0, 0, 0) if pm == "valid" else pm
+    rng = np.random.default_rng(abs(hash(case)) % (1 << 31))
+    q = _quant(rng, C * Fh * Fw)
+    x = P.pack_activation(rng.integers(0, 256, (1, C, H, W)).astype(np.uint8))
+    w = P.pack_conv_filter(rng.integers(0, 256, (K, C, Fh, Fw)).astype(np.uint8))
+    sh = shape(C, K, H, W, Fh, Fw, s, pads, CB)
+    ho, wo = sh.out_hw()
+    part = rng.integers(-30000, 30000, ho * wo * K).astype(np.int32)
+    O = _out(4 * K * ho * wo, q)
+    O.data()[:] = torch.from_numpy(part.view(np.uint8)).cuda()
+    S.PartialConv2D(Fh, Fw, s, *pads, K, C, H, W, qbuf(x, q.zero_in), qbuf(w, q.zero_filt), O)
+    want = oracle.partial_conv2d_u8(sh, q, x[0], w, part)
+    assert np.array_equal(O.numpy()[:K * ho * wo], want)
+    assert want.min() < want.max()
+    if C != 16:
+        return
+    # depthwise on the same 16 channels
+    qd = _quant(rng, Fh * Fw)
+    wd = P.pack_dw_filter(rng.integers(0, 256, (C, Fh, Fw)).astype(np.uint8))
+    sd = shape(C, C, H, W, Fh, Fw, s, pads, CB)
+    partd = rng.integers(-3000, 3000, ho * wo * C).astype(np.int32)
+    want = oracle.partial_conv2d_u8(sd, qd, x[0], wd, partd, depthwise=True)
+    O = _out(4 * C * ho * wo, qd)
+    O.data()[:] = torch.from_numpy(partd.view(np.uint8)).cuda()
+    S.PartialDepthwiseConv2D(Fh, Fw, s, *pads, C, H, W, qbuf(x, qd.zero_in), qbuf(wd, qd.zero_filt), O)
+    assert np.array_equal(O.numpy()[:C * ho * wo], want)
+
+
+def test_partial_forms_u8_refuse_overlapping_blocks():
+    rng = np.random.default_rng(4)
+    x = qbuf(P.pack_activation(rng.integers(0, 256, (1, 16, 6, 6)).astype(np.uint8)), 0)
+    w = qbuf(P.pack_conv_filter(rng.integers(0, 256, (32, 16, 1, 1)).astype(np.uint8)), -128)
+    O = S.QUInt8Buffer(4 * 32 * 36)
+    with pytest.raises(Exception, match="overlap"):
+        S.PartialConv2D(1, 1, 1, 0, 0, 0, 0, 32, 16, 6, 6, x, w, O)
+    g = qbuf(rng.integers(0, 256, 16 * 16 * 36).astype(np.uint8), 0)
+    wg = qbuf(rng.integers(0, 256, 16 * 16 * 16).astype(np.uint8), -128)
+    with pytest.raises(Exception, match="overlap"):
+        S.PartialGroupConv2D(1, 1, 1, 16, 0, 0, 0, 0, 16, 6, 6, g, wg, S.QUInt8Buffer(4 * 16 * 16 * 36))

@@ -103,6 +103,29 @@ def test_uint8_bit_exact(oracle, ref, c):
     assert np.array_equal(oracle.relu_u8(q, x), ref.relu_u8(C, H, W, q, x))
 
 
+@pytest.mark.parametrize("c", RNG_CASES[:24], ids=_id)
+def test_uint8_partial_forms_bit_exact(oracle, ref, c):
+    """PartialConv2D / PartialDepthwiseConv2D<QUInt8Buffer>: int32 partial sums waiting in the output
+    buffer, one block of output channels (the reference build's block is one channel, so K = 1 and a
+    one-channel depthwise layer)."""
+    _, H, W, Fh, Fw, s, pads = c
+    rng = np.random.default_rng(hash(c) & 0xFFFF)
+    C = int(rng.choice([1, 3, 4, 8]))
+    q = _quants(rng, 1)[0]
+    x = P.pack_activation(rng.integers(0, 256, (C, H, W)).astype(np.uint8), 1)
+    w = P.pack_conv_filter(rng.integers(0, 256, (1, C, Fh, Fw)).astype(np.uint8), 1, 1)
+    sh = shape(C, 1, H, W, Fh, Fw, s, pads, 1)
+    ho, wo = sh.out_hw()
+    part = rng.integers(-40000, 40000, ho * wo).astype(np.int32)
+    got, want = oracle.partial_conv2d_u8(sh, q, x, w, part), ref.partial_conv2d_u8(sh, q, x, w, part)
+    assert np.array_equal(got, want)
+    x1 = x[:H * W]
+    wd = P.pack_dw_filter(rng.integers(0, 256, (1, Fh, Fw)).astype(np.uint8), 1)
+    sd = shape(1, 1, H, W, Fh, Fw, s, pads, 1)
+    assert np.array_equal(oracle.partial_conv2d_u8(sd, q, x1, wd, part, depthwise=True),
+                          ref.partial_conv2d_u8(sd, q, x1, wd, part, depthwise=True))
+
+
 def test_uint8_default_quantisation(oracle, ref):
     """Buffers as the reference constructs them: zero 128, multiplier 1077952576,
     rshift 6 (QUInt8Buffer.hpp:234-272)."""
