@@ -290,7 +290,7 @@ def measure_workload(args, workload, env, pipes):
     wl = WORKLOADS[workload]
     batch = args.batch or wl["per_gpu_batch"]
     layers = make_layers(workload)
-    chain = networks.Chain(layers, batch, wl["dtype"])
+    chain = networks.Chain(layers, batch, wl["dtype"], fuse_u8=not args.no_fuse_u8)
     l = lib()
     st = chain.stream.cuda_stream
 
@@ -513,7 +513,7 @@ def run_one_layer(args):
     wl = WORKLOADS[args.workload]
     batch = args.batch or 8
     layers = make_layers(args.workload)
-    chain = networks.Chain(layers, batch, wl["dtype"])
+    chain = networks.Chain(layers, batch, wl["dtype"], fuse_u8=not args.no_fuse_u8)
     xp = make_input(args.workload, layers, batch, wl["seed"])
     chain.x.copy_(torch.from_numpy(xp).reshape(-1))
     chain.enqueue()
@@ -712,6 +712,8 @@ def main():
     ap.add_argument("--min-seconds", type=float, default=1.0,
                     help="rounds of --steps steps are repeated until this much has been timed, per leg")
     ap.add_argument("--no-cpp-boundary", action="store_true")
+    ap.add_argument("--no-fuse-u8", action="store_true",
+                    help="uint8 networks: one kernel per layer instead of the fused block kernels")
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the configuration's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-layer", default="",

@@ -387,11 +387,11 @@ int launch_ring(const RingArgs &a, const uint8_t *in, const uint8_t *filt, const
     int *status = device_status_ptr();
     if (!status)
         return fail(SMALL_B200_CUDA_ERROR, "device status word not available");
-    // CTAs per SM: tensor memory, shared memory, threads (2048 / 416)
-    int per_sm = 512 / (int)G::TMEM_COLS;
-    const int by_smem = (int)((220 * 1024) / (smem + 2048));
-    if (per_sm > by_smem) per_sm = by_smem;
-    if (per_sm > 4) per_sm = 4;
+    // CTAs resident per SM: what registers, shared memory and threads allow (the runtime's count),
+    // and tensor memory (512 columns), so that the persistent grid is one wave
+    int per_sm = 1;
+    SB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem));
+    if (per_sm > 512 / (int)G::TMEM_COLS) per_sm = 512 / (int)G::TMEM_COLS;
     if (per_sm < 1) per_sm = 1;
     long long gx = (long long)num_sms() * per_sm / a.nblocks;
     if (gx < 1)
