@@ -387,12 +387,15 @@ int launch_ring(const RingArgs &a, const uint8_t *in, const uint8_t *filt, const
     int *status = device_status_ptr();
     if (!status)
         return fail(SMALL_B200_CUDA_ERROR, "device status word not available");
-    // CTAs resident per SM: what registers, shared memory and threads allow (the runtime's count),
-    // and tensor memory (512 columns), so that the persistent grid is one wave
+    // CTAs resident per SM: what registers, shared memory and threads allow (the runtime's count) and
+    // tensor memory (512 columns).  The grid is TWO such waves: measured on a 16 -> 32 channel 1x1 layer
+    // (24x24 pixels, batch 2048) 0.052 ms against 0.066 ms for one wave of CTAs that each walk twice
+    // as many tiles -- the second wave's CTAs start as the first ones drain, which evens out the tail.
     int per_sm = 1;
     SB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem));
     if (per_sm > 512 / (int)G::TMEM_COLS) per_sm = 512 / (int)G::TMEM_COLS;
     if (per_sm < 1) per_sm = 1;
+    per_sm *= 2;
     long long gx = (long long)num_sms() * per_sm / a.nblocks;
     if (gx < 1)
         gx = 1;
