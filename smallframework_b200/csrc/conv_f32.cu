@@ -11,6 +11,8 @@
 //          image) and that block's filter slice are staged in shared memory with
 //          cp.async, double buffered
 //   thread: 8 consecutive pixels of one tile row x CH output channels in registers
+#include <mutex>
+
 #include "common.cuh"
 
 namespace
@@ -419,19 +421,32 @@ conv2d_first_pool_f32_kernel(const ConvArgs a, const float *__restrict__ in, con
 // bytes and a warp's are 4 KB, but written straight from the registers every store instruction
 // would touch 32 separate 16-byte pieces; the warp passes each row through its own 4.5 KB of shared
 // memory (144-byte pitch: conflict-free both ways) and writes 512 contiguous bytes per instruction.
-template <int C, int FH, int FW, bool POOL = true>
+// SLOT >= 0: the filter of the layer's ONE block of 16 output channels sits in constant memory
+// (c_first_w[SLOT], copied there by the launch on the same stream), and every multiply-add takes its
+// weight straight from the constant bank.  With the filter in shared memory each 128-bit weight
+// fetch feeds only 16 multiply-adds, and those broadcast fetches, not the FMA pipe, set the pace
+// (the kernel ran at half the pipe's rate whatever its occupancy).
+constexpr int FIRST_W_SLOTS = 4;
+constexpr int FIRST_W_FLOATS = 3 * 3 * 3 * CB;
+__constant__ float c_first_w[FIRST_W_SLOTS][FIRST_W_FLOATS];
+
+template <int C, int FH, int FW, bool POOL = true, int SLOT = -1>
 __global__ void __launch_bounds__(128)
 conv2d_first_pool_fixed_f32_kernel(const ConvArgs a, const float *__restrict__ in, const float *__restrict__ filt,
                                    const float *__restrict__ bias, float *__restrict__ out)
 {
-    __shared__ __align__(16) float w[FH * FW * C * CB]; // [taps][C][16]
+    constexpr int wn = FH * FW * C * CB;
+    __shared__ __align__(16) float w_s[SLOT < 0 ? wn : 4]; // [taps][C][16]
     const int kb = blockIdx.y;
     const int n = blockIdx.z;
-    constexpr int wn = FH * FW * C * CB;
-    const float *fsrc = filt + (size_t)kb * wn;
-    for (int i = threadIdx.x; i < wn; i += blockDim.x)
-        w[i] = fsrc[i];
-    __syncthreads();
+    if (SLOT < 0)
+    {
+        const float *fsrc = filt + (size_t)kb * wn;
+        for (int i = threadIdx.x; i < wn; i += blockDim.x)
+            w_s[i] = fsrc[i];
+        __syncthreads();
+    }
+    const float *w = SLOT < 0 ? w_s : c_first_w[SLOT < 0 ? 0 : SLOT];
     const int Hp = a.Ho / 2, Wp = a.Wo / 2;
     int p = blockIdx.x * blockDim.x + threadIdx.x;
     const bool live = p < Hp * Wp;
@@ -475,11 +490,12 @@ conv2d_first_pool_fixed_f32_kernel(const ConvArgs a, const float *__restrict__ i
 #pragma unroll
             for (int c = 0; c < C; ++c)
             {
-                const float4 *wt = reinterpret_cast<const float4 *>(w + ((kh * FW + kw) * C + c) * CB);
+                const float *wt = w + ((kh * FW + kw) * C + c) * CB;
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4)
                 {
-                    const float4 wv = wt[k4];
+                    const float4 wv = SLOT < 0 ? reinterpret_cast<const float4 *>(wt)[k4]
+                                               : make_float4(wt[4 * k4], wt[4 * k4 + 1], wt[4 * k4 + 2], wt[4 * k4 + 3]);
 #pragma unroll
                     for (int o = 0; o < 4; ++o)
                     {
@@ -562,6 +578,50 @@ int launch_conv(const ConvArgs &a, size_t smem_bytes, const float *in, const flo
 namespace
 {
 // pool: 0 = plain convolution; 1 = fused 2x2 stride-2 max pool (the caller has checked the shape)
+// Constant-memory slot of a first-layer filter: a filter pointer keeps the slot it got, for the life of
+// the process, and the filter's bytes are copied into it again on every call, on the call's stream.
+// Slots are never taken away, so a kernel in flight on another stream can only meet a copy of the
+// same filter; the fifth distinct filter of a device (and every later one) gets -1 and runs the
+// shared-memory form.
+int first_layer_slot(const float *filt)
+{
+    static std::mutex mu;
+    static const float *owner[16][FIRST_W_SLOTS] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16)
+        return -1;
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < FIRST_W_SLOTS; ++i)
+        if (owner[dev][i] == filt)
+            return i;
+    for (int i = 0; i < FIRST_W_SLOTS; ++i)
+        if (!owner[dev][i])
+        {
+            owner[dev][i] = filt;
+            return i;
+        }
+    return -1;
+}
+
+template <bool POOL>
+int launch_first_fixed(const ConvArgs &a, dim3 grid, const float *in, const float *filt, const float *bias, float *out,
+                       cudaStream_t st)
+{
+    const int slot = a.K == CB ? first_layer_slot(filt) : -1;
+    if (slot >= 0)
+        SB_CUDA(cudaMemcpyToSymbolAsync(c_first_w, filt, FIRST_W_FLOATS * sizeof(float),
+                                        (size_t)slot * FIRST_W_FLOATS * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    switch (slot)
+    {
+    case 0: conv2d_first_pool_fixed_f32_kernel<3, 3, 3, POOL, 0><<<grid, 128, 0, st>>>(a, in, filt, bias, out); break;
+    case 1: conv2d_first_pool_fixed_f32_kernel<3, 3, 3, POOL, 1><<<grid, 128, 0, st>>>(a, in, filt, bias, out); break;
+    case 2: conv2d_first_pool_fixed_f32_kernel<3, 3, 3, POOL, 2><<<grid, 128, 0, st>>>(a, in, filt, bias, out); break;
+    case 3: conv2d_first_pool_fixed_f32_kernel<3, 3, 3, POOL, 3><<<grid, 128, 0, st>>>(a, in, filt, bias, out); break;
+    default: conv2d_first_pool_fixed_f32_kernel<3, 3, 3, POOL><<<grid, 128, 0, st>>>(a, in, filt, bias, out); break;
+    }
+    return launched(POOL ? "conv2d_first_pool_fixed_f32_kernel" : "conv2d_first_fixed_f32_kernel");
+}
+
 int conv2d_f32_impl(const small_b200_layer *L, int pool, const float *in, const float *filt,
                     const float *bias, float *out, void *stream)
 {
@@ -592,8 +652,7 @@ int conv2d_f32_impl(const small_b200_layer *L, int pool, const float *in, const 
             dim3 grid(((a.Ho / 2) * (a.Wo / 2) + 127) / 128, a.K / CB, a.N);
             if (L->C == 3 && L->Fh == 3 && L->Fw == 3)
             {
-                conv2d_first_pool_fixed_f32_kernel<3, 3, 3><<<grid, 128, 0, st>>>(a, in, filt, bias, out);
-                return launched("conv2d_first_pool_fixed_f32_kernel");
+                return launch_first_fixed<true>(a, grid, in, filt, bias, out, st);
             }
             conv2d_first_pool_f32_kernel<<<grid, 128, smem, st>>>(a, in, filt, bias, out);
             return launched("conv2d_first_pool_f32_kernel");
@@ -603,8 +662,7 @@ int conv2d_f32_impl(const small_b200_layer *L, int pool, const float *in, const 
         {
             // 2x2 output blocks from a register patch, rows written through shared memory
             dim3 grid(((a.Ho / 2) * (a.Wo / 2) + 127) / 128, a.K / CB, a.N);
-            conv2d_first_pool_fixed_f32_kernel<3, 3, 3, false><<<grid, 128, 0, st>>>(a, in, filt, bias, out);
-            return launched("conv2d_first_fixed_f32_kernel");
+            return launch_first_fixed<false>(a, grid, in, filt, bias, out, st);
         }
         dim3 grid((a.Ho * a.Wo + 255) / 256, a.K / CB, a.N);
         conv2d_first_f32_kernel<<<grid, 256, smem, st>>>(a, in, filt, bias, out);

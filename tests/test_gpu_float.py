@@ -386,3 +386,30 @@ def test_conv2d_maxpool_fused_refuses_other_pools():
     assert not S.conv2d_maxpool_supported(3, 3, 1, (1, 1, 1, 1), 2, 2, 2, (0, 0, 0, 0), 32, 16, 13, 13)  # odd output
     assert not S.conv2d_maxpool_supported(3, 3, 2, (0, 1, 0, 1), 2, 2, 2, (0, 0, 0, 0), 32, 16, 16, 16)  # stride-2 conv
     assert not S.conv2d_maxpool_supported(3, 3, 1, (1, 1, 1, 1), 2, 2, 2, (0, 0, 0, 0), 16, 16, 16, 16)  # 16 channels
+
+
+def test_first_layer_filters_in_constant_memory_slots(oracle):
+    """The 3-channel 3x3 first layer with 16 output channels keeps its filter in one of four
+    constant-memory slots (one per filter buffer, refreshed on every call); further filter buffers run
+    the shared-memory form.  Six filter buffers, each used twice in alternation, all against the oracle."""
+    rng = np.random.default_rng(12)
+    C, K, H, W, N = 3, 16, 32, 40, 2
+    pads = same_pads(H, W, 3, 3, 1)
+    sh = shape(C, K, H, W, 3, 3, 1, pads, CB)
+    x = rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    xp = P.pack_activation(x)
+    I = fbuf(xp)
+    filters = [P.pack_conv_filter(rng.normal(0, 0.2, (K, C, 3, 3)).astype(np.float32)) for _ in range(6)]
+    bufs = [fbuf(w) for w in filters]
+    want = [oracle_conv_batch(oracle, sh, xp, w, act=1) for w in filters]
+    for rep in range(2):
+        for w, F, ref in zip(filters, bufs, want):
+            O = S.FloatBuffer(N * K * H * W)
+            S.Conv2D_ReLU(3, 3, 1, *pads, K, C, H, W, I, F, O, batch=N)
+            assert rel_max_err(O.numpy().reshape(N, -1), ref) <= TOL
+    # a filter buffer whose contents change between calls: the slot is refreshed every time
+    F = bufs[0]
+    F.data().copy_(bufs[5].data())
+    O = S.FloatBuffer(N * K * H * W)
+    S.Conv2D_ReLU(3, 3, 1, *pads, K, C, H, W, I, F, O, batch=N)
+    assert rel_max_err(O.numpy().reshape(N, -1), want[5]) <= TOL
