@@ -413,3 +413,42 @@ def test_first_layer_filters_in_constant_memory_slots(oracle):
     O = S.FloatBuffer(N * K * H * W)
     S.Conv2D_ReLU(3, 3, 1, *pads, K, C, H, W, I, F, O, batch=N)
     assert rel_max_err(O.numpy().reshape(N, -1), want[5]) <= TOL
+
+
+@pytest.mark.parametrize("c", [(16, 9, 11, 3, 3, 1, "same"), (64, 12, 12, 3, 3, 2, "same"),
+                               (32, 7, 5, 5, 3, 1, (2, 2, 1, 1)), (128, 6, 6, 1, 1, 1, "valid")],
+                         ids=lambda c: "C{}_{}x{}_k{}x{}_s{}_{}".format(*[
+                             "".join(map(str, v)) if isinstance(v, tuple) else v for v in c]))
+def test_partial_depthwise_conv2d_f32(oracle, c):
+    """small::PartialDepthwiseConv2D<FloatBuffer> (interface_abstract.hpp:1127): the depthwise
+    convolution accumulated onto the existing output."""
+    C, H, W, Fh, Fw, s, pm = c
+    N = 2
+    pads = _pads(H, W, Fh, Fw, s, pm)
+    rng = np.random.default_rng(abs(hash(c)) % (1 << 31))
+    x = P.pack_activation(rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32))
+    w = P.pack_dw_filter(rng.normal(0, 0.3, (C, Fh, Fw)).astype(np.float32))
+    sh = shape(C, C, H, W, Fh, Fw, s, pads, CB)
+    ho, wo = sh.out_hw()
+    seed = rng.uniform(-1, 1, (N, C * ho * wo)).astype(np.float32)
+    O = fbuf(seed)
+    S.PartialDepthwiseConv2D(Fh, Fw, s, *pads, C, H, W, fbuf(x), fbuf(w), O, batch=N)
+    want = oracle_conv_batch(oracle, sh, x, w, seed=seed, depthwise=True)
+    assert rel_max_err(O.numpy().reshape(N, -1), want) <= TOL
+
+
+@pytest.mark.parametrize("io", [(64, 16, 5), (256, 16, 300), (1024, 32, 7), (3, 16, 4)],
+                         ids=lambda v: "in{}_out{}_n{}".format(*v))
+def test_dense_wrapper(oracle, io):
+    """Dense() = Conv2D 1x1 on a 1x1 image (the way the reference's models build their heads,
+    include/small/models/DSCNNTiny.hpp:255-263), at batches that take the CUDA-core kernel and the
+    tensor-core kernel with the batch as the pixel axis."""
+    cin, cout, N = io
+    rng = np.random.default_rng(cin * 7 + cout)
+    x = P.pack_activation(rng.uniform(-1, 1, (N, cin, 1, 1)).astype(np.float32))
+    w = P.pack_conv_filter(rng.normal(0, 0.1, (cout, cin, 1, 1)).astype(np.float32))
+    O = S.FloatBuffer(N * cout)
+    S.Dense(cout, cin, fbuf(x), fbuf(w), O, batch=N)
+    sh = shape(cin, cout, 1, 1, 1, 1, 1, (0, 0, 0, 0), CB)
+    want = oracle_conv_batch(oracle, sh, x, w)
+    assert rel_max_err(O.numpy().reshape(N, -1), want) <= TOL
