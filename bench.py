@@ -605,7 +605,7 @@ def kernel_class(chain, i, L, dtype):
             return "stem_u8_tc_kernel (im2col in shared memory + tcgen05 kind::i8)", "i8"
         if L["C"] * L["Fh"] * L["Fw"] > 32 or (L["C"] >= 16 and L["K"] >= 32):
             return "conv_u8_ring_kernel (implicit GEMM, tcgen05 kind::i8)", "i8"
-        return "conv2d_u8_direct_kernel", "cuda_u8"
+        return "conv2d_u8_onestep_kernel (dp4a, streaming)", "stream"
     if L["op"] == "dwconv" and dtype == "u8":
         rows = L["Fh"] == 3 and L["Fw"] == 3 and L["stride"] == 1
         return ("dwconv3x3_u8_rows_kernel (dp4a)" if rows else "dwconv_u8_dp4a_kernel"), "stream"

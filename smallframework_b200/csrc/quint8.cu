@@ -494,6 +494,143 @@ dwconv3x3_u8_rows_kernel(const QArgs a, const uint8_t *__restrict__ in, const ui
     }
 }
 
+// Dense convolution whose whole reduction is at most 32 bytes: a 1x1 layer on 16 channels, or a first
+// layer (1..3 channels, [H][W][C] image) whose window holds at most 32 values, e.g. 3x3 on 3 channels.
+// These are streaming layers -- one 16-byte load (or a few byte loads) and one 16-byte store per pixel
+// and block of output channels -- with too little arithmetic for the tensor core to matter.  A thread
+// makes one output pixel: its reduction row sits in up to eight registers of four bytes, the filter in
+// shared memory as words of four reduction bytes, [word][output channel], so one 128-bit broadcast
+// fetch feeds four dp4a.  Filter zero point -128, input zero point 0 or -128 (operands enter shifted);
+// taps outside the image are zero bytes, i.e. skipped, as in the reference.
+// FIX333: the 3x3 window on 3 channels.  A kernel row of the window is 9 contiguous bytes of the
+// [H][W][3] image: three aligned 32-bit loads and two funnel shifts instead of nine byte loads; rows at
+// the left border, or whose aligned reads would pass the end of the buffer, take the byte path.
+template <bool SIGNED_IN, bool FIRST, bool FIX333 = false>
+__global__ void __launch_bounds__(256)
+conv2d_u8_onestep_kernel(const QArgs a, int words, const uint8_t *__restrict__ in, const uint8_t *__restrict__ filt,
+                         const int32_t *__restrict__ bias, uint8_t *__restrict__ out)
+{
+    extern __shared__ __align__(16) unsigned smem_u[]; // [K/16][words][16 k]
+    const int R = a.Fh * a.Fw * a.C; // reduction length in bytes (<= 32)
+    const int kbs = a.K / CB;
+    for (int i = threadIdx.x; i < kbs * words * CB; i += blockDim.x)
+    {
+        const int k = i % CB, j = (i / CB) % words, kb = i / (CB * words);
+        unsigned wv = 0;
+        for (int t = 0; t < 4; ++t)
+        {
+            const int r = 4 * j + t;
+            if (r < R) // filter [K/16][R rows][16 k] for both layouts
+                wv |= (unsigned)(filt[((size_t)kb * R + r) * CB + k] ^ 0x80u) << (8 * t);
+        }
+        smem_u[i] = wv;
+    }
+    __syncthreads();
+    const long long total = (long long)a.N * a.Ho * a.Wo;
+    const int hw = a.Ho * a.Wo;
+    // a CTA keeps its copy of the filter for many pixels
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (long long)gridDim.x * blockDim.x)
+    {
+    const int n = (int)(g / hw), p = (int)(g - (long long)n * hw);
+    const int oh = p / a.Wo, ow = p - oh * a.Wo;
+    const int ih0 = oh * a.stride - a.pad_t, iw0 = ow * a.stride - a.pad_l;
+    unsigned x[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    bool gathered = false;
+    if (FIRST && FIX333)
+    {
+        const uint8_t *img = in + (size_t)n * 3 * a.H * a.W;
+        const uint8_t *in_end = in + (size_t)a.N * 3 * a.H * a.W;
+        const uint8_t *last = img + ((size_t)(ih0 + 2 < a.H ? ih0 + 2 : a.H - 1) * a.W + iw0) * 3;
+        if (iw0 >= 0 && ih0 + 2 >= 0 && (reinterpret_cast<uintptr_t>(last) & ~(uintptr_t)3) + 12 <= reinterpret_cast<uintptr_t>(in_end))
+        {
+            const int vb = (a.W - iw0) >= 3 ? 9 : (a.W - iw0) * 3; // bytes of a row's run inside the image
+            const unsigned f = SIGNED_IN ? 0x80808080u : 0u;
+            unsigned r0[3], r1[3], r2[3];
+#pragma unroll
+            for (int kh = 0; kh < 3; ++kh)
+            {
+                const int ih = ih0 + kh;
+                r0[kh] = r1[kh] = r2[kh] = 0u;
+                if (ih >= 0 && ih < a.H)
+                {
+                    const uintptr_t addr = reinterpret_cast<uintptr_t>(img + ((size_t)ih * a.W + iw0) * 3);
+                    const unsigned *wp = reinterpret_cast<const unsigned *>(addr & ~(uintptr_t)3);
+                    const unsigned sh = (unsigned)(addr & 3) * 8;
+                    const unsigned w0 = wp[0], w1 = wp[1], w2 = wp[2];
+                    r0[kh] = __funnelshift_r(w0, w1, sh) ^ f;
+                    r1[kh] = __funnelshift_r(w1, w2, sh) ^ f;
+                    r2[kh] = ((w2 >> sh) ^ f) & 0xffu;
+                    if (vb <= 6) { r2[kh] = 0u; r1[kh] &= 0x0000ffffu; }
+                    if (vb <= 3) { r1[kh] = 0u; r0[kh] &= 0x00ffffffu; }
+                }
+            }
+            x[0] = r0[0]; x[1] = r1[0];
+            x[2] = r2[0] | (r0[1] << 8);
+            x[3] = (r0[1] >> 24) | (r1[1] << 8);
+            x[4] = (r1[1] >> 24) | (r2[1] << 8) | (r0[2] << 16);
+            x[5] = (r0[2] >> 16) | (r1[2] << 16);
+            x[6] = (r1[2] >> 16) | (r2[2] << 16);
+            gathered = true;
+        }
+    }
+    if (FIRST && !gathered)
+    {
+        const uint8_t *img = in + (size_t)n * a.C * a.H * a.W;
+        int kh = 0, kw = 0, c = 0;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) // unrolled: x[] stays in registers
+        {
+            const int ih = ih0 + kh, iw = iw0 + kw;
+            if (r < R && ih >= 0 && ih < a.H && iw >= 0 && iw < a.W)
+            {
+                const unsigned v = (unsigned)img[((size_t)ih * a.W + iw) * a.C + c] ^ (SIGNED_IN ? 0x80u : 0u);
+                x[r >> 2] |= v << (8 * (r & 3));
+            }
+            if (++c == a.C)
+            {
+                c = 0;
+                if (++kw == a.Fw)
+                {
+                    kw = 0;
+                    ++kh;
+                }
+            }
+        }
+    }
+    if (!FIRST && ih0 >= 0 && ih0 < a.H && iw0 >= 0 && iw0 < a.W) // 1x1 window on one block of 16 channels
+    {
+        const uint4 v = *reinterpret_cast<const uint4 *>(in + (((size_t)n * a.H + ih0) * a.W + iw0) * CB);
+        const unsigned f = SIGNED_IN ? 0x80808080u : 0u;
+        x[0] = v.x ^ f; x[1] = v.y ^ f; x[2] = v.z ^ f; x[3] = v.w ^ f;
+    }
+    uint8_t *o = out + ((size_t)n * kbs * hw + p) * CB;
+    for (int kb = 0; kb < kbs; ++kb)
+    {
+        int acc[CB];
+#pragma unroll
+        for (int k = 0; k < CB; ++k)
+            acc[k] = a.k_zero + (bias ? bias[kb * CB + k] : 0);
+        const uint4 *w4 = reinterpret_cast<const uint4 *>(smem_u + (size_t)kb * words * CB);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+        {
+            if (j >= words)
+                break;
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4)
+            {
+                const uint4 wv = w4[j * 4 + k4];
+                acc[4 * k4 + 0] = dp4a_in<SIGNED_IN>(x[j], wv.x, acc[4 * k4 + 0]);
+                acc[4 * k4 + 1] = dp4a_in<SIGNED_IN>(x[j], wv.y, acc[4 * k4 + 1]);
+                acc[4 * k4 + 2] = dp4a_in<SIGNED_IN>(x[j], wv.z, acc[4 * k4 + 2]);
+                acc[4 * k4 + 3] = dp4a_in<SIGNED_IN>(x[j], wv.w, acc[4 * k4 + 3]);
+            }
+        }
+        *reinterpret_cast<uint4 *>(o + (size_t)kb * hw * CB) = requant_pack16(acc, a.lshift, a.rshift, a.mult);
+    }
+    }
+}
+
 // Dense convolution of a ONE-channel image (the first layer of the keyword-spotting network):
 // the Fw taps of a kernel row are consecutive bytes of the image, so a row of the window is one
 // (unaligned) 32-bit word per 4 taps and feeds dp4a directly.  A CTA takes IMGS images: it
@@ -796,12 +933,38 @@ int conv2d_u8_dispatch(const small_b200_layer *L, const uint8_t *in, const uint8
         if (tc1 >= 0)
             return tc1;
     }
-    // A reduction of one 32-byte step into 16 channels (a 1x1 layer on 16 channels, a 3x3 first layer on
-    // 3) is a streaming layer with nothing for the tensor core to do: measured on MobileNet-v1 0.25 uint8
-    // at batch 2048, the implicit GEMM takes 0.43 ms against 0.35 ms for the 3x3x3 first layer and 0.188
-    // against 0.185 ms for 16 -> 16 channels, and wins from 16 -> 32 channels on (0.052 against 0.097 ms).
+    // A reduction of one 32-byte step (a 1x1 layer on 16 channels, a 3x3 first layer on 3) is a streaming
+    // layer with nothing for the tensor core to do: measured on MobileNet-v1 0.25 uint8 at batch 2048, the
+    // implicit GEMM takes 0.43 ms for the 3x3x3 first layer and 0.188 ms for 16 -> 16 channels (the direct
+    // kernel 0.35 and 0.185), and wins from 16 -> 32 channels on (0.052 against 0.097 ms).  Those layers
+    // run the one-step dp4a kernel when the zero points let the operands enter shifted.
     const long long red = (long long)L->C * L->Fh * L->Fw;
-    if (path == 2 || (tensor_core && (red > 32 || (L->C >= CB && L->K >= 32))))
+    const bool ring_first = red > 32 || (L->C >= CB && L->K >= 32);
+    if (path != 2 && !(tensor_core && ring_first) && red <= 32 && (L->C < CB || (L->Fh == 1 && L->Fw == 1)) &&
+        a.zero_filt == -128 && (a.zero_in == 0 || a.zero_in == -128) && a.K <= 1024 &&
+        reinterpret_cast<uintptr_t>(in) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0)
+    {
+        const int words = (int)((red + 3) / 4);
+        const size_t smem = (size_t)(a.K / CB) * words * CB * sizeof(unsigned);
+        const long long total = (long long)a.N * a.Ho * a.Wo;
+        long long nb = (total + 255) / 256;
+        if (nb > (long long)num_sms() * 16)
+            nb = (long long)num_sms() * 16;
+        const unsigned blocks = (unsigned)nb;
+        const bool sgn = a.zero_in != 0, first = L->C < CB;
+        cudaStream_t st = as_stream(stream);
+        if (first && a.C == 3 && a.Fh == 3 && a.Fw == 3)
+            sgn ? conv2d_u8_onestep_kernel<true, true, true><<<blocks, 256, smem, st>>>(a, words, in, filt, bias, out)
+                : conv2d_u8_onestep_kernel<false, true, true><<<blocks, 256, smem, st>>>(a, words, in, filt, bias, out);
+        else if (first)
+            sgn ? conv2d_u8_onestep_kernel<true, true><<<blocks, 256, smem, st>>>(a, words, in, filt, bias, out)
+                : conv2d_u8_onestep_kernel<false, true><<<blocks, 256, smem, st>>>(a, words, in, filt, bias, out);
+        else
+            sgn ? conv2d_u8_onestep_kernel<true, false><<<blocks, 256, smem, st>>>(a, words, in, filt, bias, out)
+                : conv2d_u8_onestep_kernel<false, false><<<blocks, 256, smem, st>>>(a, words, in, filt, bias, out);
+        return launched("conv2d_u8_onestep_kernel");
+    }
+    if (path == 2 || (tensor_core && ring_first))
     {
         const int tc2 = conv2d_u8_ring(L, in, filt, bias, out, as_stream(stream));
         if (tc2 >= 0)

@@ -101,6 +101,34 @@ def test_conv2d_u8_implicit_gemm(oracle, case, zp):
     _check_conv(oracle, case, pads, q, rng, True, "tensor_core")
 
 
+# Reductions of at most 32 bytes (a 1x1 layer on 16 channels, small windows on 1..3 channels) with the
+# zero points of the quantised networks run the one-step dp4a kernel; the 3x3x3 window has a path of its
+# own (aligned word loads), with the byte path at the left border and at the end of the buffer.
+ONESTEP_CASES = [
+    (3, 16, 15, 17, 3, 3, 1, "same", 3),
+    (3, 16, 96, 96, 3, 3, 2, "same", 2),
+    (3, 32, 9, 5, 3, 3, 2, "valid", 2),
+    (3, 16, 7, 7, 3, 3, 1, (0, 1, 0, 1), 1),
+    (3, 16, 5, 4, 3, 3, 1, "same", 4),
+    (3, 16, 3, 3, 3, 3, 1, "valid", 5),      # one output pixel per image: the run ends at the buffer's end
+    (16, 16, 24, 24, 1, 1, 1, "valid", 3),
+    (16, 16, 9, 9, 1, 1, 2, "valid", 2),
+    (2, 16, 11, 9, 3, 3, 1, "valid", 2),
+    (1, 16, 8, 8, 5, 5, 1, "same", 2),
+    (3, 48, 10, 10, 2, 2, 2, "valid", 2),
+]
+
+
+@pytest.mark.parametrize("case", ONESTEP_CASES, ids=_case_id)
+@pytest.mark.parametrize("zp", [(0, -128), (-128, -128)], ids=lambda z: "zi{}_zf{}".format(*z))
+def test_conv2d_u8_single_step_reductions(oracle, case, zp):
+    C, K, H, W, Fh, Fw, s, pm, N = case
+    pads = same_pads(H, W, Fh, Fw, s) if pm == "same" else (0, 0, 0, 0) if pm == "valid" else pm
+    rng = np.random.default_rng(abs(hash((case, zp))) % (1 << 31))
+    q = _quant(rng, C * Fh * Fw, zp)
+    _check_conv(oracle, case, pads, q, rng, True, "cuda_cores")
+
+
 def _check_conv(oracle, case, pads, q, rng, with_bias, path):
     C, K, H, W, Fh, Fw, s, pm, N = case
     x = P.pack_activation(rng.integers(0, 256, (N, C, H, W)).astype(np.uint8))
