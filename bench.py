@@ -269,9 +269,9 @@ def measured_pipes(torch):
     return out
 
 
-def h2d_bandwidth(l, check, dst_ptr, host_ptr, nbytes, stream, torch):
+def h2d_bandwidth(l, check, dst_ptr, host_ptr, nbytes, stream, torch, min_bytes=2e8):
     """Upload alone: pinned host memory -> device, GB/s, per rank."""
-    reps = max(3, int(2e8 // max(nbytes, 1)))
+    reps = max(3, int(min_bytes // max(nbytes, 1)))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     check(l.small_b200_memcpy_h2d(dst_ptr, host_ptr, nbytes, stream.cuda_stream))
     e0.record(stream)
@@ -391,6 +391,19 @@ def measure_workload(args, workload, env, pipes):
             step_e2e()
         ms_e2e, ms_e2e_min, rounds_e2e, span_e2e = timed(step_e2e, args.steps, budget, finish_e2e)
     h2d_gbs = h2d_bandwidth(l, check, inputs[1].data_ptr(), hin, in_bytes, copy_stream, torch)
+    # the same upload with every rank of the box uploading at once: what the host side (memory, root
+    # complexes) gives one GPU when all of them pull, i.e. the ceiling of the end-to-end leg at this N
+    h2d_all = None
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        mine = h2d_bandwidth(l, check, inputs[1].data_ptr(), hin, in_bytes, copy_stream, torch, min_bytes=1.5e9)
+        t = torch.tensor([mine, -mine, mine], dtype=torch.float64, device="cuda")
+        parts = [t.clone() for _ in range(world)]
+        dist.all_gather(parts, t)
+        vals = [float(p[0]) for p in parts]
+        h2d_all = {"per_rank_min_gbs": round(min(vals), 2), "per_rank_max_gbs": round(max(vals), 2),
+                   "aggregate_gbs": round(sum(vals), 1)}
     # The final host gather (outside the timed spans): every rank's result for its own batch goes to
     # rank 0, which recomputes each shard from that rank's seed on its own GPU and compares the bytes.
     shards_verified = None
@@ -431,6 +444,13 @@ def measure_workload(args, workload, env, pipes):
         "kernels_per_step": chain.kernels_per_step,
         "clocks": clocks,
     }
+    if h2d_all is not None:
+        # a step cannot be shorter than its upload at the bandwidth a rank gets when all ranks upload
+        bound_ms = in_bytes / (h2d_all["per_rank_min_gbs"] * 1e9) * 1e3
+        h2d_all["upload_bound_ms_per_step"] = round(bound_ms, 4)
+        h2d_all["upload_bound_value"] = round(batch * world / (max(bound_ms, ms / args.steps) * 1e-3), 1)
+        h2d_all["e2e_of_upload_bound"] = round(res["e2e"]["value"] / h2d_all["upload_bound_value"], 3)
+        res["e2e"]["all_ranks_uploading"] = h2d_all
     if shards_verified is not None:
         res["host_gather"] = {"shards": world, "shards_bit_identical_to_rank0_recomputation": shards_verified}
     if rank == 0:

@@ -2,12 +2,13 @@
 // fused_interface_abstract.hpp:55-3667 and the 1-D file beside it) through the small:: boundary of
 // the B200 platform, each against the composition of the unfused small:: functions that defines it
 // (the way the reference's demo/fused_block_driver.cpp checks its two variants), plus the 1-D family
-// with stride 2 against a direct loop, and Dropout.  The unfused functions themselves are what the
+// with stride 2 against a direct loop, Dropout, and the quint8 Partial forms.  The unfused functions themselves are what the
 // reference's own test drivers and the oracle tests pin.  Exit code 0 = all checks passed.
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <random>
+#include <stdexcept>
 #include <vector>
 
 #include <small.h>
@@ -228,6 +229,42 @@ int main()
             same = same && o.data()[i] == x.data()[i] * 0.75f;
         std::printf("%-46s %s\n", "Dropout", same ? "ok" : "FAIL");
         failures += !same;
+    }
+    // ---- quint8 Partial forms: with zero partial sums waiting in the output buffer they equal the plain
+    // forms (one block of 16 output channels, where the reference's in-buffer int32 storage is defined);
+    // more than one block is refused with std::invalid_argument
+    {
+        const int C1 = 32, H = 9, W = 7, K1 = 16;
+        small::QUInt8Buffer x((size_t)C1 * H * W), w((size_t)K1 * C1 * 9), wd((size_t)K1 * 9);
+        std::uniform_int_distribution<int> d(0, 255);
+        for (size_t i = 0; i < x.size(); ++i) x.data()[i] = (uint8_t)d(rng);
+        for (size_t i = 0; i < w.size(); ++i) w.data()[i] = (uint8_t)d(rng);
+        for (size_t i = 0; i < wd.size(); ++i) wd.data()[i] = (uint8_t)d(rng);
+        const size_t n = (size_t)K1 * H * W;
+        small::QUInt8Buffer plain(n), part(4 * n), x16(n), dplain(n), dpart(4 * n);
+        plain.multiplier = part.multiplier = 1 << 30; plain.rshift = part.rshift = 14; plain.lshift = part.lshift = 0;
+        dplain.multiplier = dpart.multiplier = 1 << 30; dplain.rshift = dpart.rshift = 9; dplain.lshift = dpart.lshift = 0;
+        small::Conv2D(3, 3, 1, 1, 1, 1, 1, K1, C1, H, W, x, w, plain);
+        for (size_t i = 0; i < 4 * n; ++i) part.data()[i] = 0;
+        small::PartialConv2D(3, 3, 1, 1, 1, 1, 1, K1, C1, H, W, x, w, part);
+        bool same = true;
+        for (size_t i = 0; i < n; ++i) same = same && plain.data()[i] == part.data()[i];
+        std::printf("%-46s %s\n", "PartialConv2D<quint8> from zero partial sums", same ? "ok" : "FAIL");
+        failures += !same;
+        for (size_t i = 0; i < n; ++i) x16.data()[i] = x.data()[i];
+        small::DepthwiseConv2D(3, 3, 1, 1, 1, 1, 1, K1, H, W, x16, wd, dplain);
+        for (size_t i = 0; i < 4 * n; ++i) dpart.data()[i] = 0;
+        small::PartialDepthwiseConv2D(3, 3, 1, 1, 1, 1, 1, K1, H, W, x16, wd, dpart);
+        same = true;
+        for (size_t i = 0; i < n; ++i) same = same && dplain.data()[i] == dpart.data()[i];
+        std::printf("%-46s %s\n", "PartialDepthwiseConv2D<quint8>", same ? "ok" : "FAIL");
+        failures += !same;
+        bool refused = false;
+        small::QUInt8Buffer w32((size_t)32 * C1 * 9), o32((size_t)4 * 32 * H * W);
+        try { small::PartialConv2D(3, 3, 1, 1, 1, 1, 1, 32, C1, H, W, x, w32, o32); }
+        catch (std::invalid_argument const &) { refused = true; }
+        std::printf("%-46s %s\n", "PartialConv2D<quint8>, two blocks: refused", refused ? "ok" : "FAIL");
+        failures += !refused;
     }
     std::printf(failures ? "FAILED (%d)\n" : "OK\n", failures);
     return failures ? 1 : 0;
