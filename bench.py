@@ -298,7 +298,8 @@ def measure_workload(args, workload, env, pipes):
     xp = make_input(workload, layers, batch, wl["seed"] + rank)
     in_bytes = xp.nbytes
     hin, hout = C.c_void_p(), C.c_void_p()
-    check(l.small_b200_malloc_host(in_bytes, C.byref(hin)))
+    alloc_in = l.small_b200_malloc_host_upload if args.upload_memory == "wc" else l.small_b200_malloc_host
+    check(alloc_in(in_bytes, C.byref(hin)))
     C.memmove(hin, xp.ctypes.data, in_bytes)
     check(l.small_b200_memcpy_h2d(chain.x.data_ptr(), hin, in_bytes, st))
     chain.stream.synchronize()
@@ -732,6 +733,8 @@ def main():
     ap.add_argument("--min-seconds", type=float, default=1.0,
                     help="rounds of --steps steps are repeated until this much has been timed, per leg")
     ap.add_argument("--no-cpp-boundary", action="store_true")
+    ap.add_argument("--upload-memory", default="pinned", choices=["pinned", "wc"],
+                    help="host staging memory of the end-to-end leg's input: pinned, or pinned write-combined")
     ap.add_argument("--no-fuse-u8", action="store_true",
                     help="uint8 networks: one kernel per layer instead of the fused block kernels")
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the configuration's)")

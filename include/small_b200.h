@@ -113,6 +113,10 @@ uint64_t small_b200_launch_count(void);
 int small_b200_malloc(size_t bytes, void **ptr);         /* device memory                  */
 int small_b200_malloc_managed(size_t bytes, void **ptr); /* host-visible (Buffer::data()) */
 int small_b200_malloc_host(size_t bytes, void **ptr);    /* pinned host staging            */
+/* Pinned, write-combined host memory for staging buffers the host only WRITES (sequentially) and the
+ * device reads: the device's reads do not snoop the CPU caches.  Host reads from it are very slow.
+ * Freed with small_b200_free_host. */
+int small_b200_malloc_host_upload(size_t bytes, void **ptr);
 int small_b200_free(void *ptr);
 int small_b200_free_host(void *ptr);
 int small_b200_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream);

@@ -48,6 +48,7 @@ SIGNATURES = {
     "small_b200_malloc": [_SZ, C.POINTER(_VP)],
     "small_b200_malloc_managed": [_SZ, C.POINTER(_VP)],
     "small_b200_malloc_host": [_SZ, C.POINTER(_VP)],
+    "small_b200_malloc_host_upload": [_SZ, C.POINTER(_VP)],
     "small_b200_free": [_VP],
     "small_b200_free_host": [_VP],
     "small_b200_memcpy_h2d": [_VP, _VP, _SZ, _VP],

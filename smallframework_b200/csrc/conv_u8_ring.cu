@@ -312,7 +312,7 @@ conv_u8_ring_kernel(const RingArgs a, const uint8_t *__restrict__ in, const uint
                 if (w >= units || !ok)
                     continue;
                 const unsigned s = w % STAGES, use = w / STAGES;
-                if (use > 0) // every lane waits; the verdict is made the same for the whole warp
+                if (use > 0) // every lane waits; the outcome is made the same for the whole warp
                     ok = __all_sync(0xffffffffu, mbar_wait(&empty_bar[s], (use - 1) & 1u, status, 32));
                 if (ok)
                 {

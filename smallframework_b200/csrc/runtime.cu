@@ -64,6 +64,12 @@ int small_b200_malloc_host(size_t bytes, void **ptr)
     return SMALL_B200_OK;
 }
 
+int small_b200_malloc_host_upload(size_t bytes, void **ptr)
+{
+    SB_CUDA(cudaHostAlloc(ptr, bytes ? bytes : 1, cudaHostAllocWriteCombined));
+    return SMALL_B200_OK;
+}
+
 int small_b200_free(void *ptr)
 {
     SB_CUDA(cudaFree(ptr));
