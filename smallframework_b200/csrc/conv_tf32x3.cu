@@ -88,6 +88,7 @@ struct TcArgs
     int total_tiles;     // N * px_tiles * k_tiles
     int persistent;      // 1: one CTA per SM walks over the tiles; 0: one tile per CTA
     int ksplit;          // 2: a cluster of two CTAs shares a tile, each reduces half of the channel blocks
+    int tile_base;       // first tile of this launch (a layer may run as two launches, see the launch code)
 };
 
 // Output channels per CTA, a function of K alone so that filter preparation and the
@@ -234,7 +235,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
     const int cb_begin = (int)crank * cbs_l;
     const int steps = a.cbs * a.taps;
     const int groups_per_cb = a.taps / a.group, groups = cbs_l * groups_per_cb;
-    const int first_tile = split ? blockIdx.x / 2 : blockIdx.x, tile_step = gridDim.x;
+    const int first_tile = a.tile_base + (split ? blockIdx.x / 2 : blockIdx.x), tile_step = gridDim.x;
 
     // patch number pc / group number gc count over every tile of this CTA
     auto issue_patch = [&](const Tile &T, int cb, int pc) {
@@ -1075,6 +1076,42 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
             blocks = 2 * tiles;
         }
     }
+    const float *flo_ = filt_prepared + (size_t)a.K * a.C * a.Fh * a.Fw;
+    auto launch_split = [&](const TcArgs &ta, long long nblocks) -> int {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)nblocks); cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = ta.smem_bytes; cfg.stream = as_stream(stream);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        SB_CUDA(cudaLaunchKernelEx(&cfg, conv_tf32x3_kernel<false, true>, mx, filt_prepared, flo_, ta, bias, out, status));
+        return SMALL_B200_OK;
+    };
+    // One tile per CTA and a last wave that fills less than half of the SMs (512 tiles on 148 SMs: three
+    // full waves and 68 tiles): that wave runs as clusters of two CTAs that split the reduction, in a
+    // launch of its own behind the full waves, and takes a little over half a round instead of a whole
+    // one.  (Splitting EVERY tile of such a layer was measured slower: 512 -> 1024 channels at 13x13
+    // 0.415 -> 0.425 ms; the exchange between the two CTAs costs about a sixth of a half tile.)
+    if (!a.pixm && !a.persistent && a.ksplit == 1 && a.cbs % 2 == 0 && a.cbs >= 8 && a.cg == 1)
+    {
+        const long long sms = num_sms();
+        const long long full = tiles / sms * sms, rem = tiles - full;
+        if (full > 0 && rem > 0 && 2 * rem <= sms)
+        {
+            TcArgs a1 = a;
+            a1.tile_base = 0;
+            conv_tf32x3_kernel<false, false><<<(unsigned)full, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
+                mx, filt_prepared, flo_, a1, bias, out, status);
+            if (int rc = launched("conv_tf32x3_kernel"))
+                return rc;
+            TcArgs a2 = a;
+            a2.tile_base = (int)full; a2.ksplit = 2;
+            if (int rc = launch_split(a2, 2 * rem))
+                return rc;
+            return launched("conv_tf32x3_kernel");
+        }
+    }
     if (a.pixm)
         conv_tf32x3_kernel<true, false, true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
             mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.Fh * a.Fw, a, bias, out, status);
@@ -1083,15 +1120,8 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
             mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.Fh * a.Fw, a, bias, out, status);
     else if (a.ksplit == 2)
     {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)blocks); cfg.blockDim = dim3(NUM_THREADS);
-        cfg.dynamicSmemBytes = a.smem_bytes; cfg.stream = as_stream(stream);
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr; cfg.numAttrs = 1;
-        const float *flo = filt_prepared + (size_t)a.K * a.C * a.Fh * a.Fw;
-        SB_CUDA(cudaLaunchKernelEx(&cfg, conv_tf32x3_kernel<false, true>, mx, filt_prepared, flo, a, bias, out, status));
+        if (int rc = launch_split(a, blocks))
+            return rc;
     }
     else
         conv_tf32x3_kernel<false, false><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
