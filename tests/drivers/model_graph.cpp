@@ -6,7 +6,8 @@
 // small::b200::InferenceGraph and replays it.  Checks:
 //   - the replayed graph leaves bit-identical results to the eager run, on repeated replays too;
 //   - with small::b200::BatchScope(B) and an input shape whose batch entry is B, every image of
-//     the batch equals the single-image result of that image;
+//     the batch equals the single-image result of that image (bit for bit where both launches split
+//     the reductions alike, within fp32 rounding otherwise);
 //   - host access to a buffer inside a capture is refused with an exception, and the graph object
 //     can be used again afterwards.
 // Prints the time per inference of both forms.  Exit code 0 = all checks passed.
@@ -173,19 +174,43 @@ int main(int argc, char **argv)
         small::b200::BatchScope one(1);
         small::shape_type shape1({1UL, 3UL, size, size});
         small::TinyYoloV2<BufferT> model1(shape1, filters, true);
+        uint32_t inexact = 0;
         for (uint32_t b = 0; b < batch; ++b)
         {
             BufferT image(per_image);
             std::memcpy(image.data(), images.data() + b * per_image, per_image * sizeof(float));
             small::Tensor<BufferT> input1(shape1, image);
             auto out = model1.inference(&input1);
-            if (out[0]->size() != n ||
-                std::memcmp(out[0]->buffer().data(), batched.data() + b * n, n * sizeof(float)) != 0)
+            // Bit-identical wherever the library splits the reductions of an image's tiles the same way
+            // in both launches.  It decides per launch, from the number of tiles, whether the two CTAs of
+            // a cluster share a tile's reduction (the last, partial wave of a large batch does), so the
+            // sums of some images may be associated differently than in their single-image run: a
+            // difference of fp32 rounding, held here to 2e-6 of the output range.
+            bool same = out[0]->size() == n;
+            double worst = 0, top = 0;
+            if (same)
             {
-                std::printf("FAIL: image %u of the batch differs from its single-image result\n", b);
+                const float *s1 = out[0]->buffer().data(), *sb = batched.data() + b * n;
+                if (std::memcmp(s1, sb, n * sizeof(float)) != 0)
+                {
+                    ++inexact;
+                    for (size_t i = 0; i < n; ++i)
+                    {
+                        worst = std::fmax(worst, std::fabs((double)s1[i] - sb[i]));
+                        top = std::fmax(top, std::fabs((double)s1[i]));
+                    }
+                    same = worst <= 2e-6 * (top > 0 ? top : 1);
+                }
+            }
+            if (!same)
+            {
+                std::printf("FAIL: image %u of the batch differs from its single-image result (%.3g of %.3g)\n", b,
+                            worst, top);
                 ++failures;
             }
         }
+        std::printf("batch: %u of %u images bit-identical to their single-image result, the others within 2e-6\n",
+                    batch - inexact, batch);
     }
 
     for (auto f : filters)
