@@ -163,16 +163,17 @@ struct Tile
 
 __device__ __forceinline__ Tile decode_tile(const TcArgs &a, int t)
 {
-    // Image fastest, channel tile slowest: the CTAs that run at the same time then share one or two
-    // filter slices (a slice of a 1024 -> 1024 3x3 layer is 9.4 MB with its lo copy), which stay in L2
-    // while every image's tile passes over them, and the activations of the whole batch (44 MB there)
-    // stay in L2 from one slice to the next.  With the channel tile fastest, every 9 images streamed
+    // Pixel tile fastest, then the image, channel tile slowest.  The CTAs that run at the same time then
+    // share one or two filter slices (a slice of a 1024 -> 1024 3x3 layer is 9.4 MB with its lo copy),
+    // which stay in L2 while every image's tiles pass over them, and the activations of the whole batch
+    // (44 MB there) stay in L2 from one slice to the next; neighbouring tiles of an image, whose patches
+    // share their halo rows, still run side by side.  With the channel tile fastest, every 9 images streamed
     // all 75 MB of filter again: 541 MB of DRAM reads per launch for 126 MB of algorithmic bytes (176 MB
     // now, and the layer 3 % faster).
     Tile T;
-    T.n = t % a.N; t /= a.N;
-    const int pt = t % a.px_tiles;
-    T.kt = t / a.px_tiles;
+    const int pt = t % a.px_tiles; t /= a.px_tiles;
+    T.n = t % a.N;
+    T.kt = t / a.N;
     if (!a.tiled)
     {
         const int m0 = pt * a.NPX;
