@@ -150,10 +150,29 @@ inline void conv_then_dw(int act, BufferT const *bias, BufferT const *dw_bias, S
                          SMALL_B200_POOL_ARGS, int K, int C, int H, int W, BufferT const &in,
                          BufferT const &filt, BufferT const &dw_filt, BufferT &inter, BufferT &out)
 {
-    BufferT &mid = fused_mid(inter, conv_out_elems(K, H, W, SMALL_B200_CONV_PASS));
-    conv(false, act, SMALL_B200_CONV_PASS, K, C, H, W, in, filt, bias, mid);
     const int Hm = out_h(H, conv_t_pad, conv_b_pad, conv_stride, conv_kernel_height);
     const int Wm = out_w(W, conv_l_pad, conv_r_pad, conv_stride, conv_kernel_width);
+    if constexpr (is_quint8<BufferT>)
+    {
+        // One kernel where the library covers the pair (a 1x1 or one-channel first convolution, a 3x3
+        // 'same' depthwise convolution, images of at most 128 pixels): the intermediate stays in shared
+        // memory and inter only lends its quantisation fields.  The clamp of the requantisation is the
+        // ReLU of the quint8 forms.
+        small_b200_layer Lc = describe(C, K, H, W, conv_kernel_height, conv_kernel_width, conv_stride,
+                                       conv_t_pad, conv_b_pad, conv_l_pad, conv_r_pad);
+        quantise(Lc, in, &filt, inter);
+        small_b200_layer Ld = describe(K, K, Hm, Wm, pool_kernel_height, pool_kernel_width, pool_stride,
+                                       pool_t_pad, pool_b_pad, pool_l_pad, pool_r_pad);
+        quantise(Ld, inter, &dw_filt, out);
+        if (!bias && !dw_bias && small_b200_conv2d_dwconv2d_u8_supported(&Lc, &Ld))
+        {
+            throw_on(small_b200_conv2d_dwconv2d_u8(&Lc, &Ld, in.device_ptr(), filt.device_ptr(), nullptr,
+                                                   dw_filt.device_ptr(), nullptr, out.device_ptr(), b200::stream()));
+            return;
+        }
+    }
+    BufferT &mid = fused_mid(inter, conv_out_elems(K, H, W, SMALL_B200_CONV_PASS));
+    conv(false, act, SMALL_B200_CONV_PASS, K, C, H, W, in, filt, bias, mid);
     dwconv(false, act, SMALL_B200_POOL_PASS, K, Hm, Wm, mid, dw_filt, dw_bias, out);
 }
 

@@ -4,6 +4,7 @@
 // (the way the reference's demo/fused_block_driver.cpp checks its two variants), plus the 1-D family
 // with stride 2 against a direct loop, Dropout, and the quint8 Partial forms.  The unfused functions themselves are what the
 // reference's own test drivers and the oracle tests pin.  Exit code 0 = all checks passed.
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -265,6 +266,34 @@ int main()
         catch (std::invalid_argument const &) { refused = true; }
         std::printf("%-46s %s\n", "PartialConv2D<quint8>, two blocks: refused", refused ? "ok" : "FAIL");
         failures += !refused;
+    }
+    // ---- quint8 Conv2D_ReLU_DepthwiseConv2D_ReLU: one kernel (1x1 64 -> 64 on a 25x5 image, depthwise 3x3)
+    // against the two calls, bit for bit
+    {
+        const int C1 = 64, K1 = 64, H = 25, W = 5;
+        small::QUInt8Buffer x((size_t)C1 * H * W), w((size_t)K1 * C1), wd((size_t)K1 * 9);
+        std::uniform_int_distribution<int> d(0, 255);
+        for (size_t i = 0; i < x.size(); ++i) x.data()[i] = (uint8_t)d(rng);
+        for (size_t i = 0; i < w.size(); ++i) w.data()[i] = (uint8_t)d(rng);
+        for (size_t i = 0; i < wd.size(); ++i) wd.data()[i] = (uint8_t)d(rng);
+        x.m_zero = 0; w.m_zero = -128; wd.m_zero = -128;
+        const size_t n = (size_t)K1 * H * W;
+        small::QUInt8Buffer mid(n), fused(n), mid2(n), two(n);
+        for (auto *b : {&mid, &mid2}) { b->m_zero = 0; b->multiplier = 1 << 30; b->rshift = 13; b->lshift = 0; }
+        for (auto *b : {&fused, &two}) { b->multiplier = 1 << 30; b->rshift = 9; b->lshift = 0; }
+        small::Conv2D_ReLU_DepthwiseConv2D_ReLU(1, 1, 1, 0, 0, 0, 0, 3, 3, 1, 1, 1, 1, 1, K1, C1, H, W, x, w, mid, wd, fused);
+        small::Conv2D(1, 1, 1, 0, 0, 0, 0, K1, C1, H, W, x, w, mid2);
+        small::DepthwiseConv2D(3, 3, 1, 1, 1, 1, 1, K1, H, W, mid2, wd, two);
+        bool same = true;
+        int lo = 255, hi = 0;
+        for (size_t i = 0; i < n; ++i)
+        {
+            same = same && fused.data()[i] == two.data()[i];
+            lo = std::min<int>(lo, two.data()[i]); hi = std::max<int>(hi, two.data()[i]);
+        }
+        same = same && lo < hi;
+        std::printf("%-46s %s (values %d..%d)\n", "Conv2D_ReLU_DepthwiseConv2D_ReLU<quint8>", same ? "ok" : "FAIL", lo, hi);
+        failures += !same;
     }
     std::printf(failures ? "FAILED (%d)\n" : "OK\n", failures);
     return failures ? 1 : 0;
