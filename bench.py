@@ -725,7 +725,7 @@ def per_layer_report(chain, layers, batch, wl, clocks, torch, pipes=None):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="", choices=[""] + sorted(WORKLOADS) + ["yolov3tiny_layers"],
