@@ -263,6 +263,12 @@ def measured_pipes(torch):
         v = C.c_double(0.0)
         _lib.check(_lib.lib().small_b200_peak_probe(kind, C.byref(v)))
         out[name] = v.value
+    floor = {}
+    for kind, name in ((3, "tf32_m128_n32"), (4, "i8_m128_n32")):
+        v = C.c_double(0.0)
+        _lib.check(_lib.lib().small_b200_peak_probe(kind, C.byref(v)))
+        floor[name] = round(v.value, 1)
+    out["mma_floor_cycles_per_instruction"] = floor
     torch.cuda.synchronize()
     out["assumed"] = {"tf32": peaks["tensor_burst"] / 2.0, "i8": peaks["tensor_burst"] * 2.0}
     out["how"] = "resident-operand issue loops: FFMA chains in registers; tcgen05.mma M128 N256 from shared memory, 2 issuing threads per SM"

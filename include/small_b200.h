@@ -103,7 +103,10 @@ int small_b200_selftest_bounded_wait(uint32_t polls, void *stream);
  * in registers / shared memory / tensor memory): kind 0 = fp32 FMA pipe, 1 = tcgen05 kind::tf32
  * MMA, 2 = tcgen05 kind::i8 MMA.  Runs a short probe kernel on the default stream, synchronously,
  * and returns tera-operations per second (2 per multiply-add) in *tera_ops.  These are the
- * denominators of the benchmark's per-layer roofline figures.  No counterpart in the reference. */
+ * denominators of the benchmark's per-layer roofline figures.  kind 3 / 4: the same probe with
+ * M = 128, N = 32 instructions of kind::tf32 / kind::i8; the result is then the pipe's CYCLES PER
+ * INSTRUCTION at the device's maximum clock -- the floor a narrow MMA costs, which bounds layers
+ * that need many small instructions.  No counterpart in the reference. */
 int small_b200_peak_probe(int kind, double *tera_ops);
 /* Number of kernels this library has launched in this process since it was loaded. */
 uint64_t small_b200_launch_count(void);

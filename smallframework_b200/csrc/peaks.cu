@@ -4,6 +4,8 @@
 //   kind 0  fp32 FMA pipe            independent FFMA chains in registers
 //   kind 1  tcgen05 kind::tf32       M = 128, N = 256, K = 8 MMAs on shared-memory operands
 //   kind 2  tcgen05 kind::i8         M = 128, N = 256, K = 32
+//   kind 3  tcgen05 kind::tf32       M = 128, N = 32: the result is CYCLES PER INSTRUCTION at this GPU's
+//   kind 4  tcgen05 kind::i8         M = 128, N = 32  clock, the floor a narrow MMA costs the pipe
 // The tensor probes use two issuing threads per CTA, each with its own accumulator in tensor memory
 // (one thread alone cannot keep the pipe busy), one CTA per SM.  The reference has no counterpart.
 #include "tc_common.cuh"
@@ -34,9 +36,7 @@ __global__ void __launch_bounds__(256) ffma_probe_kernel(int iters, float a, flo
         sink[0] = s;
 }
 
-constexpr int PROBE_N = 256;
-
-template <bool I8>
+template <bool I8, int PROBE_N = 256>
 __global__ void __launch_bounds__(128) mma_probe_kernel(int iters, int *status)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -90,8 +90,9 @@ __global__ void __launch_bounds__(128) mma_probe_kernel(int iters, int *status)
 
 extern "C" int small_b200_peak_probe(int kind, double *tera_ops)
 {
-    if (!tera_ops || kind < 0 || kind > 2)
-        return fail(SMALL_B200_INVALID_ARGUMENT, "peak_probe: kind must be 0 (fp32 FMA), 1 (tf32 MMA) or 2 (i8 MMA)");
+    if (!tera_ops || kind < 0 || kind > 4)
+        return fail(SMALL_B200_INVALID_ARGUMENT,
+                    "peak_probe: kind must be 0 (fp32 FMA), 1 (tf32 MMA), 2 (i8 MMA), 3 or 4 (cycles per narrow tf32 / i8 MMA)");
     int *status = device_status_ptr();
     if (!status)
         return fail(SMALL_B200_CUDA_ERROR, "device status word not available");
@@ -113,12 +114,17 @@ extern "C" int small_b200_peak_probe(int kind, double *tera_ops)
         else
         {
             const int iters = 1 << 14;
-            const size_t smem = 128 * 32 + PROBE_N * 32;
+            const int n = kind >= 3 ? 32 : 256;
+            const size_t smem = 128 * 32 + (size_t)n * 32;
             if (kind == 1)
                 mma_probe_kernel<false><<<sms, 128, smem>>>(iters, status);
-            else
+            else if (kind == 2)
                 mma_probe_kernel<true><<<sms, 128, smem>>>(iters, status);
-            ops = 2.0 * 128.0 * PROBE_N * (kind == 1 ? 8.0 : 32.0) * (double)iters * 2.0 * sms;
+            else if (kind == 3)
+                mma_probe_kernel<false, 32><<<sms, 128, smem>>>(iters, status);
+            else
+                mma_probe_kernel<true, 32><<<sms, 128, smem>>>(iters, status);
+            ops = 2.0 * 128.0 * n * ((kind == 1 || kind == 3) ? 8.0 : 32.0) * (double)iters * 2.0 * sms;
         }
         if (int rc = launched("peak_probe_kernel"))
             return rc;
@@ -132,5 +138,13 @@ extern "C" int small_b200_peak_probe(int kind, double *tera_ops)
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     *tera_ops = ops / (best * 1e-3) / 1e12;
+    if (kind >= 3)
+    {
+        // two issuing threads per SM, `iters` instructions each: pipe cycles per instruction
+        int khz = 0, dev = 0;
+        SB_CUDA(cudaGetDevice(&dev));
+        SB_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
+        *tera_ops = (best * 1e-3) * (khz * 1e3) / (2.0 * (1 << 14));
+    }
     return SMALL_B200_OK;
 }
