@@ -407,8 +407,11 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     {
                         if (turn == me)
                         {
-                            if (!(a.w_resident && g >= a.w_stages)) // resident stages were waited for on the first tile
-                                ok = mbar_wait(&w_full[st], wphase, status, 14);
+                            // resident stages complete phase 0 once and stay there; every issuer still has
+                            // to observe that itself the first time it uses a stage (with 1, 2, 4 or 5
+                            // stages a stage is not always the same thread's), and a completed phase
+                            // answers at once
+                            ok = mbar_wait(&w_full[st], a.w_resident ? 0u : (uint32_t)wphase, status, 14);
                             if (ok && g > tb_mask)
                                 ok = mbar_wait(&t_empty[g & tb_mask], ((g >> tb_shift) - 1) & 1, status, 16);
                             if (!ok)
