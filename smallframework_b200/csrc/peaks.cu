@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(128) mma_probe_kernel(int iters, int *status)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // operands: A 128 rows x 32 bytes, B 256 rows x 32 bytes, K-major without swizzle; zeros are as
     // good as any data for the pipe's timing
-    for (int i = tid; i < (128 * 32 + PROBE_N * 32) / 16; i += 128)
+    for (int i = tid; i < (128 * 32 + PROBE_N * 32 + (PROBE_N < 256 ? 16 * 512 : 0)) / 16; i += 128)
         reinterpret_cast<uint4 *>(smem)[i] = make_uint4(0u, 0u, 0u, 0u);
     if (warp == 0)
     {
@@ -68,15 +68,19 @@ __global__ void __launch_bounds__(128) mma_probe_kernel(int iters, int *status)
         const int me = warp - 1;
         const uint32_t idesc = I8 ? make_idesc(2, 0, 0, 0, 0, 128, PROBE_N) : make_idesc(1, 2, 2, 0, 0, 128, PROBE_N);
         // two 16-byte K chunks per operand row: rows 16 bytes apart inside a chunk
-        const uint64_t da = make_smem_desc(smem_u32(smem), 128 * 16, 128, 0);
-        const uint64_t db = make_smem_desc(smem_u32(smem + 128 * 32), PROBE_N * 16, 128, 0);
+        // B first, then the A tile and (narrow probes) the room its 16 positions need
+        const uint64_t db = make_smem_desc(smem_u32(smem), PROBE_N * 16, 128, 0);
+        const uint64_t da = make_smem_desc(smem_u32(smem + PROBE_N * 32), 128 * 16, 128, 0);
         const uint32_t d = tmem + (uint32_t)(me * PROBE_N);
         for (int it = 0; it < iters; ++it)
         {
+            // narrow instructions: a different A tile every time (16 positions 512 bytes apart), as in a
+            // kernel that walks over its operands; the wide probes keep one position
+            const uint64_t step = PROBE_N < 256 ? (uint64_t)((it & 15) * 32) : 0;
             if (I8)
-                tc_mma_i8(d, da, db, idesc, it > 0 ? 1u : 0u);
+                tc_mma_i8(d, da + step, db, idesc, it > 0 ? 1u : 0u);
             else
-                tc_mma_tf32(d, da, db, idesc, it > 0 ? 1u : 0u);
+                tc_mma_tf32(d, da + step, db, idesc, it > 0 ? 1u : 0u);
         }
         tc_commit(&done[me]);
         mbar_wait(&done[me], 0, status, 90, 1u << 22);
@@ -115,7 +119,7 @@ extern "C" int small_b200_peak_probe(int kind, double *tera_ops)
         {
             const int iters = 1 << 14;
             const int n = kind >= 3 ? 32 : 256;
-            const size_t smem = 128 * 32 + (size_t)n * 32;
+            const size_t smem = 128 * 32 + (size_t)n * 32 + (n < 256 ? 16 * 512 : 0);
             if (kind == 1)
                 mma_probe_kernel<false><<<sms, 128, smem>>>(iters, status);
             else if (kind == 2)
