@@ -58,6 +58,14 @@ CASES = [
     (32, 16, 13, 13, 3, 3, "same", 3),
     (64, 16, 8, 8, 1, 1, "valid", 9),
     (256, 16, 1, 1, 1, 1, "valid", 500),
+    # pixel-major persistent tiles whose whole filter stays in shared memory (one stage per group of a
+    # tile: 1, 3, 5 and 6 stages), with more tiles than CTAs, so that every issuing thread meets stages
+    # another thread used first
+    (16, 16, 26, 26, 1, 1, "valid", 96),
+    (48, 32, 26, 26, 1, 1, "valid", 64),
+    (80, 64, 20, 20, 1, 1, "valid", 64),
+    (16, 32, 32, 32, 3, 3, "same", 48),
+    (32, 64, 26, 26, 3, 3, "same", 48),
 ]
 
 
