@@ -17,6 +17,7 @@
 #include <type_traits>
 
 #include <small/op_type.hpp>
+#include <small/utils.hpp>
 
 namespace small
 {
@@ -73,6 +74,7 @@ inline void conv(bool partial, int act, int kh, int kw, int stride, int t, int b
                  int K, int C, int H, int W, BufferT const &in, BufferT const &filt,
                  BufferT const *bias, BufferT &out)
 {
+    flush_deferred();
     small_b200_layer L = describe(C, K, H, W, kh, kw, stride, t, b, l, r, partial, act);
     quantise(L, in, &filt, out);
     if constexpr (is_quint8<BufferT>)
@@ -84,6 +86,14 @@ inline void conv(bool partial, int act, int kh, int kw, int stride, int t, int b
     }
     else
     {
+        // A call without an activation whose arguments the library accepts waits for the next call:
+        // an in-place ReLU / LeakyReLU of its output becomes its epilogue (DeferredConv, Buffer.hpp).
+        const bool acceptable = (stride == 1 || stride == 2) && (C % SMALL_B200_CB == 0 || C == 1 || C == 2 || C == 3) &&
+                                K > 0 && K % SMALL_B200_CB == 0 && H > 0 && W > 0 && kh > 0 && kw > 0;
+        const bool defer = act == SMALL_B200_ACT_NONE && acceptable;
+        const long long out_elems = (long long)L.N * K *
+                                    (long long)small::output_dim(H + t + b, row_stride() > 0 ? row_stride() : stride, kh) *
+                                    (long long)small::output_dim(W + l + r, stride, kw);
         // Wide stride-1 layers run on the tensor cores (tcgen05 kind::tf32, 3xTF32 split).  The
         // kernel wants the filter re-laid; that copy is made once and kept with the filter buffer
         // until the host touches the buffer again.
@@ -96,12 +106,48 @@ inline void conv(bool partial, int act, int kh, int kw, int stride, int t, int b
                 prepared = filt.make_companion(key, 2 * (size_t)K * C * kh * kw);
                 throw_on(small_b200_filter_prepare_tf32x3(&L, filt.device_ptr(), prepared, b200::stream()));
             }
-            throw_on(small_b200_conv2d_f32_tf32x3(&L, in.device_ptr(), prepared, bias ? bias->device_ptr() : nullptr,
-                                                  out.device_ptr(), b200::stream()));
+            const float *ip = in.device_ptr(), *bp = bias ? bias->device_ptr() : nullptr;
+            float *op = out.device_ptr();
+            if (defer)
+            {
+                DeferredConv &d = deferred();
+                d.L = L; d.in = ip; d.filt = prepared; d.bias = bp; d.out = op; d.on_stream = b200::stream();
+                d.tensor_core = true; d.out_elems = out_elems; d.valid = true;
+            }
+            else
+                throw_on(small_b200_conv2d_f32_tf32x3(&L, ip, prepared, bp, op, b200::stream()));
         }
         else
-            throw_on(small_b200_conv2d_f32(&L, in.device_ptr(), filt.device_ptr(),
-                                           bias ? bias->device_ptr() : nullptr, out.device_ptr(), b200::stream()));
+        {
+            const float *ip = in.device_ptr(), *fp = filt.device_ptr(), *bp = bias ? bias->device_ptr() : nullptr;
+            float *op = out.device_ptr();
+            if (defer)
+            {
+                DeferredConv &d = deferred();
+                d.L = L; d.in = ip; d.filt = fp; d.bias = bp; d.out = op; d.on_stream = b200::stream();
+                d.tensor_core = false; d.out_elems = out_elems; d.valid = true;
+            }
+            else
+                throw_on(small_b200_conv2d_f32(&L, ip, fp, bp, op, b200::stream()));
+        }
+    }
+}
+
+// An in-place activation of the output of the convolution that is waiting: taken into its epilogue.
+template <class BufferT>
+inline bool fuse_activation(BufferT const &in, BufferT &out, int64_t n, int act, float slope)
+{
+    if constexpr (is_quint8<BufferT>)
+        return false;
+    else
+    {
+        DeferredConv &d = deferred();
+        if (!d.valid || d.L.act != SMALL_B200_ACT_NONE || in.raw_ptr() != out.raw_ptr() || out.raw_ptr() != d.out ||
+            n != d.out_elems || d.on_stream != b200::stream())
+            return false;
+        d.L.act = act;
+        d.L.slope = slope;
+        return true;
     }
 }
 
@@ -268,6 +314,8 @@ void ReLUActivation(int input_channels, int input_height, int input_width,
     else
     {
         b200::require_block(input_channels, FLOAT_C_ib, "ReLUActivation<float> ERROR: in_channels unsupported.");
+        if (b200::fuse_activation(input_buf, output_buf, n, SMALL_B200_ACT_RELU, 0.f))
+            return;
         b200::throw_on(small_b200_relu_f32(n, input_buf.device_ptr(), output_buf.device_ptr(), b200::stream()));
     }
 }
@@ -281,6 +329,8 @@ void LeakyReLUActivation(int input_channels, int input_height, int input_width,
     b200::require_block(input_channels, FLOAT_C_ib, "LeakyReLUActivation<float> ERROR: in_channels unsupported.");
     const float slope = filter_buf.peek(0); // a parameter no kernel writes: no wait for the device
     const int64_t n = (int64_t)b200::batch() * input_channels * input_height * input_width;
+    if (b200::fuse_activation(input_buf, output_buf, n, SMALL_B200_ACT_LEAKY, slope))
+        return;
     b200::throw_on(small_b200_leaky_relu_f32(n, input_buf.device_ptr(), slope, output_buf.device_ptr(), b200::stream()));
 }
 

@@ -78,8 +78,8 @@ inline bool &capturing()
 struct StreamScope
 {
     void *saved;
-    explicit StreamScope(void *s) : saved(stream()) { stream() = s; }
-    ~StreamScope() { stream() = saved; }
+    explicit StreamScope(void *s); // flushes a deferred convolution first: it belongs to the old stream
+    ~StreamScope();
 };
 
 inline void throw_on(int rc)
@@ -94,8 +94,56 @@ inline void throw_on(int rc)
     throw std::runtime_error(msg);
 }
 
+// A float convolution that has been described but not launched yet.  The reference's layer classes
+// run a convolution and its activation as two calls (Conv2DLayer.hpp:827-878: Bias, PartialConv2D,
+// then ReLUActivation / LeakyReLUActivation in place); on a GPU the second call is a whole extra
+// pass over the activation.  So a convolution call only records itself here, and
+//   * an in-place activation of exactly its output, as the next call, becomes the convolution's own
+//     epilogue (the bytes in the buffer afterwards are the same: the fused epilogue computes the
+//     same function of the same sums);
+//   * anything else -- another layer call (every call fetches its buffers with device_ptr()), host
+//     access to any buffer, the end of a graph capture, a change of stream, the destruction of a
+//     buffer -- launches it first.
+// Only calls whose arguments the library accepts are deferred, so argument errors still surface at
+// the call that made them.
+struct DeferredConv
+{
+    bool valid = false;
+    bool tensor_core = false;
+    small_b200_layer L{};
+    const float *in = nullptr, *filt = nullptr, *bias = nullptr;
+    float *out = nullptr;
+    void *on_stream = nullptr;
+    long long out_elems = 0;
+};
+inline DeferredConv &deferred()
+{
+    static thread_local DeferredConv d;
+    return d;
+}
+inline void flush_deferred()
+{
+    DeferredConv &d = deferred();
+    if (!d.valid)
+        return;
+    d.valid = false;
+    throw_on(d.tensor_core ? small_b200_conv2d_f32_tf32x3(&d.L, d.in, d.filt, d.bias, d.out, d.on_stream)
+                           : small_b200_conv2d_f32(&d.L, d.in, d.filt, d.bias, d.out, d.on_stream));
+}
+inline void flush_deferred_quietly() noexcept
+{
+    try
+    {
+        flush_deferred();
+    }
+    catch (...)
+    {
+    }
+}
+
 inline void sync_for_host()
 {
+    flush_deferred();
     if (capturing())
         throw std::runtime_error("small::b200: host access to a buffer (data(), operator[], copy) while a graph "
                                  "is being captured; a captured inference must only enqueue layer calls");
@@ -207,9 +255,14 @@ public:
         return m_companion;
     }
 
-    // Device view for a layer call: no wait; brings host-touched pages back first.
+    // The address without any side effect (to recognise a buffer, never to hand to a kernel).
+    T *raw_ptr() const { return m_buffer; }
+
+    // Device view for a layer call: no wait; brings host-touched pages back first.  A convolution that
+    // is still waiting for its activation goes first: this call is not that activation.
     T *device_ptr() const
     {
+        flush_deferred();
         if (m_host_touched && m_buffer && !capturing()) // a capture only records kernels; pages move on demand
         {
             small_b200_prefetch(m_buffer, m_num_elts * sizeof(T), stream());
@@ -248,6 +301,7 @@ private:
     {
         if (m_buffer)
         {
+            flush_deferred_quietly(); // it may read or write this buffer
             if (pending())
             {
                 small_b200_device_sync();
@@ -266,6 +320,17 @@ private:
     mutable T *m_companion;
     mutable uint64_t m_companion_key;
 };
+inline StreamScope::StreamScope(void *s) : saved(stream())
+{
+    flush_deferred();
+    stream() = s;
+}
+inline StreamScope::~StreamScope()
+{
+    flush_deferred_quietly();
+    stream() = saved;
+}
+
 // A whole inference as one CUDA graph.  The reference's Model classes (Model.hpp:74,
 // models/TinyYoloV2.hpp:93, DSCNNTiny.hpp, Resnet8Tiny.hpp, MobileNetTiny.hpp) run a network as a
 // sequence of Layer::compute_output() calls, each of which ends in the layer functions of this
@@ -304,6 +369,7 @@ public:
             m_exec = nullptr;
         }
         run();
+        flush_deferred();
         throw_on(small_b200_device_sync());
         pending() = false;
         StreamScope on(m_stream);
@@ -312,9 +378,11 @@ public:
         try
         {
             run();
+            flush_deferred();
         }
         catch (...)
         {
+            deferred().valid = false;
             capturing() = false;
             void *dead = nullptr;
             small_b200_graph_end(m_stream, &dead); // ends the capture; its graph is discarded
@@ -333,6 +401,7 @@ public:
     {
         if (!m_exec)
             throw std::logic_error("small::b200::InferenceGraph::launch before capture");
+        flush_deferred();
         throw_on(small_b200_graph_launch(m_exec, m_stream));
         pending() = true;
     }
