@@ -267,6 +267,49 @@ int main()
         std::printf("%-46s %s\n", "PartialConv2D<quint8>, two blocks: refused", refused ? "ok" : "FAIL");
         failures += !refused;
     }
+    // ---- a convolution call waits for the next call (an in-place activation joins it): what the buffers
+    // hold must not depend on that
+    {
+        const int C1 = 32, K1 = 64, H = 13, W = 13;
+        Buf x((size_t)C1 * H * W), w((size_t)K1 * C1 * 9), bias(K1), slope(1);
+        fill(x, -1, 1); fill(w, -0.1f, 0.1f); fill(bias, -0.5f, 0.5f);
+        slope.data()[0] = 0.1f;
+        const size_t n = (size_t)K1 * H * W;
+        Buf fused(n), a(n), b(n), c(n);
+        small::Conv2D_ReLU(3, 3, 1, 1, 1, 1, 1, K1, C1, H, W, x, w, fused);
+        small::Conv2D(3, 3, 1, 1, 1, 1, 1, K1, C1, H, W, x, w, a);
+        small::ReLUActivation(K1, H, W, a, a);                       // joins the convolution
+        expect_close("Conv2D, then ReLU in place", a, fused, n);
+        small::Conv2D(3, 3, 1, 1, 1, 1, 1, K1, C1, H, W, x, w, b);
+        bool neg = false;
+        for (size_t i = 0; i < n; ++i) neg = neg || b.data()[i] < 0;  // host access launches it as it is
+        small::ReLUActivation(K1, H, W, b, c);                        // not in place: a kernel of its own
+        expect_close("Conv2D, host access, then ReLU out of place", c, fused, n);
+        std::printf("%-46s %s\n", "  the plain result keeps its negative values", neg ? "ok" : "FAIL");
+        failures += !neg;
+        {
+            Buf *tmp = new Buf(x.size());
+            for (size_t i = 0; i < x.size(); ++i) tmp->data()[i] = x.data()[i];
+            small::Conv2D(3, 3, 1, 1, 1, 1, 1, K1, C1, H, W, *tmp, w, c);
+            delete tmp;                                               // the input goes away before anything else is called
+            small::ReLUActivation(K1, H, W, c, c);
+            expect_close("Conv2D, input destroyed, then ReLU", c, fused, n);
+        }
+        Buf lf(n), lu(n);
+        small::Bias(K1, H, W, bias, lu);
+        small::PartialConv2D(3, 3, 1, 1, 1, 1, 1, K1, C1, H, W, x, w, lu);
+        small::LeakyReLUActivation(K1, H, W, lu, slope, lu);          // joins the partial convolution
+        small::Bias(K1, H, W, bias, lf);
+        small::PartialConv2D(3, 3, 1, 1, 1, 1, 1, K1, C1, H, W, x, w, lf);
+        (void)lf.data();                                              // launched without the activation
+        small::LeakyReLUActivation(K1, H, W, lf, slope, lf);
+        expect_close("Bias, PartialConv2D, LeakyReLU in place", lu, lf, n);
+        bool thrown = false;
+        try { small::Conv2D(3, 3, 3, 0, 0, 0, 0, K1, C1, H, W, x, w, a); }
+        catch (std::invalid_argument const &) { thrown = true; }
+        std::printf("%-46s %s\n", "Conv2D with stride 3 throws at the call", thrown ? "ok" : "FAIL");
+        failures += !thrown;
+    }
     // ---- quint8 Conv2D_ReLU_DepthwiseConv2D_ReLU: one kernel (1x1 64 -> 64 on a 25x5 image, depthwise 3x3)
     // against the two calls, bit for bit
     {
