@@ -112,7 +112,7 @@ inline void conv(bool partial, int act, int kh, int kw, int stride, int t, int b
             {
                 DeferredConv &d = deferred();
                 d.L = L; d.in = ip; d.filt = prepared; d.bias = bp; d.out = op; d.on_stream = b200::stream();
-                d.tensor_core = true; d.out_elems = out_elems; d.valid = true;
+                d.tensor_core = true; d.depthwise = false; d.out_elems = out_elems; d.valid = true;
             }
             else
                 throw_on(small_b200_conv2d_f32_tf32x3(&L, ip, prepared, bp, op, b200::stream()));
@@ -125,7 +125,7 @@ inline void conv(bool partial, int act, int kh, int kw, int stride, int t, int b
             {
                 DeferredConv &d = deferred();
                 d.L = L; d.in = ip; d.filt = fp; d.bias = bp; d.out = op; d.on_stream = b200::stream();
-                d.tensor_core = false; d.out_elems = out_elems; d.valid = true;
+                d.tensor_core = false; d.depthwise = false; d.out_elems = out_elems; d.valid = true;
             }
             else
                 throw_on(small_b200_conv2d_f32(&L, ip, fp, bp, op, b200::stream()));
@@ -166,8 +166,23 @@ inline void dwconv(bool partial, int act, int kh, int kw, int stride, int t, int
         throw_on(small_b200_dwconv2d_u8(&L, in.device_ptr(), filt.device_ptr(), nullptr, out.device_ptr(), b200::stream()));
     }
     else
-        throw_on(small_b200_dwconv2d_f32(&L, in.device_ptr(), filt.device_ptr(),
-                                         bias ? bias->device_ptr() : nullptr, out.device_ptr(), b200::stream()));
+    {
+        // deferred like the dense convolution (DeferredConv, Buffer.hpp): an in-place activation joins it
+        const float *ip = in.device_ptr(), *fp = filt.device_ptr(), *bp = bias ? bias->device_ptr() : nullptr;
+        float *op = out.device_ptr();
+        if (act == SMALL_B200_ACT_NONE && (stride == 1 || stride == 2) && C > 0 && C % SMALL_B200_CB == 0 && H > 0 &&
+            W > 0 && kh > 0 && kw > 0)
+        {
+            DeferredConv &d = deferred();
+            d.L = L; d.in = ip; d.filt = fp; d.bias = bp; d.out = op; d.on_stream = b200::stream();
+            d.tensor_core = false; d.depthwise = true; d.valid = true;
+            d.out_elems = (long long)L.N * C *
+                          (long long)small::output_dim(H + t + b, row_stride() > 0 ? row_stride() : stride, kh) *
+                          (long long)small::output_dim(W + l + r, stride, kw);
+        }
+        else
+            throw_on(small_b200_dwconv2d_f32(&L, ip, fp, bp, op, b200::stream()));
+    }
 }
 
 template <class BufferT>

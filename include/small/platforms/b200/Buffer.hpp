@@ -109,7 +109,8 @@ inline void throw_on(int rc)
 struct DeferredConv
 {
     bool valid = false;
-    bool tensor_core = false;
+    bool tensor_core = false; // small_b200_conv2d_f32_tf32x3 (filt = the re-laid filter)
+    bool depthwise = false;   // small_b200_dwconv2d_f32
     small_b200_layer L{};
     const float *in = nullptr, *filt = nullptr, *bias = nullptr;
     float *out = nullptr;
@@ -127,8 +128,9 @@ inline void flush_deferred()
     if (!d.valid)
         return;
     d.valid = false;
-    throw_on(d.tensor_core ? small_b200_conv2d_f32_tf32x3(&d.L, d.in, d.filt, d.bias, d.out, d.on_stream)
-                           : small_b200_conv2d_f32(&d.L, d.in, d.filt, d.bias, d.out, d.on_stream));
+    throw_on(d.depthwise     ? small_b200_dwconv2d_f32(&d.L, d.in, d.filt, d.bias, d.out, d.on_stream)
+             : d.tensor_core ? small_b200_conv2d_f32_tf32x3(&d.L, d.in, d.filt, d.bias, d.out, d.on_stream)
+                             : small_b200_conv2d_f32(&d.L, d.in, d.filt, d.bias, d.out, d.on_stream));
 }
 inline void flush_deferred_quietly() noexcept
 {

@@ -304,6 +304,14 @@ int main()
         (void)lf.data();                                              // launched without the activation
         small::LeakyReLUActivation(K1, H, W, lf, slope, lf);
         expect_close("Bias, PartialConv2D, LeakyReLU in place", lu, lf, n);
+        {
+            Buf wd((size_t)C1 * 9), xd((size_t)C1 * H * W), d1((size_t)C1 * H * W), d2((size_t)C1 * H * W);
+            fill(wd, -0.3f, 0.3f); fill(xd, -1, 1);
+            small::DepthwiseConv2D_ReLU(3, 3, 1, 1, 1, 1, 1, C1, H, W, xd, wd, d1);
+            small::DepthwiseConv2D(3, 3, 1, 1, 1, 1, 1, C1, H, W, xd, wd, d2);
+            small::ReLUActivation(C1, H, W, d2, d2);                  // joins the depthwise convolution
+            expect_close("DepthwiseConv2D, then ReLU in place", d2, d1, d1.size());
+        }
         bool thrown = false;
         try { small::Conv2D(3, 3, 3, 0, 0, 0, 0, K1, C1, H, W, x, w, a); }
         catch (std::invalid_argument const &) { thrown = true; }
