@@ -489,7 +489,7 @@ def cpp_boundary_leg():
            "note": "the reference's model has no bias and ReLU; same convolution shapes as the benchmark network"}
     for key, flag in (("tensor_cores", "1"), ("cuda_cores_only", "0")):
         try:
-            r = subprocess.run([exe, "416", "64", "5"], env=dict(os.environ, SMALL_B200_TENSOR_CORE=flag),
+            r = subprocess.run([exe, "416", "64", "20"], env=dict(os.environ, SMALL_B200_TENSOR_CORE=flag),
                                stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
             ms = [float(line.split("graph")[1].split("ms per image")[0]) for line in r.stdout.splitlines()
                   if "images: graph" in line]

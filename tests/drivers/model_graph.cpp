@@ -168,7 +168,7 @@ int main(int argc, char **argv)
         for (int r = 0; r < runs; ++r)
             graph.launch();
         graph.sync();
-        std::printf("TinyYoloV2 %ux%u, %u images: graph %.3f ms per image\n", size, size, batch,
+        std::printf("TinyYoloV2 %ux%u, %u images: graph %.4f ms per image\n", size, size, batch,
                     (now_ms() - t0) / runs / batch);
 
         small::b200::BatchScope one(1);
