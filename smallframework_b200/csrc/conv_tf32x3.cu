@@ -90,17 +90,23 @@ struct TcArgs
     int ksplit;          // 2: a cluster of two CTAs shares a tile, each reduces half of the channel blocks
     int tile_base;       // first tile of this launch (a layer may run as two launches, see the launch code)
     int w_resident;      // 1: every group of a tile has a filter stage of its own, loaded once per CTA (see fit_rings)
+    // Filters with 16 or 32 output channels are prepared with the lo rows of every 4-channel chunk right
+    // behind its hi rows ([slab][c/4][hi k | lo k][4 c], interleaved_filter()): a pixel-major MMA then
+    // takes [W_hi | W_lo] as ONE operand of 2K columns (the MERGED kernel, see its issuer).
+    int merged;
 };
 
 // Output channels per CTA, a function of K alone so that filter preparation and the
 // convolution agree.
 __host__ __device__ inline int pick_mt(int K) { return K >= 128 ? 128 : 64; }
+// Layout of the prepared filter, a function of K alone for the same reason.
+__host__ __device__ inline bool interleaved_filter(int K) { return K == 16 || K == 32; }
 
 // packed filter [K/16][slab][16 c][16 k] -> hi and lo copies in [K/MT][slab][c/4][kv k][4 c];
-// kv = MT except in a last, partial tile (K % MT channels).
+// kv = MT except in a last, partial tile (K % MT channels).  inter: one array [slab][c/4][hi K | lo K][4 c].
 __global__ void __launch_bounds__(256)
-prepare_filter_kernel(long long n, int slabs, int MT, int K, const float *__restrict__ w, float *__restrict__ hi,
-                      float *__restrict__ lo)
+prepare_filter_kernel(long long n, int slabs, int MT, int K, int inter, const float *__restrict__ w,
+                      float *__restrict__ hi, float *__restrict__ lo)
 {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n)
@@ -114,8 +120,16 @@ prepare_filter_kernel(long long n, int slabs, int MT, int K, const float *__rest
     const long long o = (long long)tile * MT * slabs * 16 + ((long long)slab * 4 + (c >> 2)) * kv * 4 +
                         (long long)(k - tile * MT) * 4 + (c & 3);
     const float v = w[i];
+    const float vl = v - __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+    if (inter)
+    {
+        const long long oi = (((long long)slab * 4 + (c >> 2)) * 2 * K + k) * 4 + (c & 3);
+        hi[oi] = v;
+        hi[oi + (long long)K * 4] = vl;
+        return;
+    }
     hi[o] = v;
-    lo[o] = v - __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+    lo[o] = vl;
 }
 
 // Tensor-core accumulation truncates: every MMA adds into the fp32 accumulator with
@@ -202,7 +216,7 @@ __device__ __forceinline__ Tile decode_tile(const TcArgs &a, int t)
 #define SB_TILE_LOOP(cond_extra) \
     for (int t = first_tile, once_ = 0; (PERSIST ? (t < a.total_tiles) : (once_ == 0)) && (cond_extra); t += tile_step, ++once_)
 
-template <bool PERSIST, bool SPLIT, bool PIXM = false>
+template <bool PERSIST, bool SPLIT, bool PIXM = false, bool MERGED = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__restrict__ filt,
                    const float *__restrict__ filt_lo, const TcArgs a, const float *__restrict__ bias, float *__restrict__ out, int *status)
@@ -225,7 +239,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint32_t tmem_cols = 32;
-    while ((int)tmem_cols < (PIXM ? a.tbufs * (a.NPX >> 7) * a.K : a.tbufs * a.NPX))
+    while ((int)tmem_cols < (PIXM ? a.tbufs * (a.NPX >> 7) * a.K * (MERGED ? 2 : 1) : a.tbufs * a.NPX))
         tmem_cols <<= 1;
 
     // Split reduction (one tile per CTA only): the two CTAs of a cluster take one half of the channel
@@ -251,6 +265,12 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
         uint8_t *wd = sW + (size_t)st * 2 * w_half_stage;
         const size_t off = (size_t)T.kt * a.MT * steps * 16 + (size_t)(g + cb_begin * groups_per_cb) * a.group * T.kv * 16;
         mbar_expect_tx(&w_full[st], 2u * a.group * T.kv * 64);
+        if (MERGED)
+        {
+            // hi and lo rows of a chunk lie side by side in one array: one run of twice the length
+            tma_load_1d(wd, filt + 2 * off, 2u * a.group * T.kv * 64, &w_full[st]);
+            return;
+        }
         // the group's taps are contiguous, [tap][c/4][kv k][4 c]: a partial last tile (kv < MT) simply
         // is a shorter run, and the MMA descriptors take kv * 16 bytes as the chunk stride
         tma_load_1d(wd, filt + off, (uint32_t)a.group * T.kv * 64, &w_full[st]);
@@ -383,7 +403,9 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             const uint64_t x_desc_base = make_smem_desc(smem_u32(sX), 16, 512, 4);
             const uint32_t idesc = make_idesc(1 /*f32*/, 2 /*tf32*/, 2 /*tf32*/, 0 /*A K-major*/, 0 /*B K-major*/,
                                               PIXM ? 128u : (uint32_t)a.MT, PIXM ? (uint32_t)a.K : (uint32_t)a.NPX);
+            const uint32_t idesc_wide = make_idesc(1, 2, 2, 0, 0, 128u, 2u * (uint32_t)a.K); // MERGED: N = [hi | lo]
             const uint64_t x_lo_off = x_part >> 4, w_lo_off = w_half_stage >> 4;
+            constexpr uint32_t w_rows = MERGED ? 2u : 1u; // rows of a 4-channel chunk: kv, or kv hi + kv lo
             const uint64_t x_half = 2; // channels 8..15 of the block
             const uint64_t tap_step = (uint64_t)a.tap_step;
             const uint64_t w_stage_step = (uint64_t)2 * w_half_stage >> 4;
@@ -395,8 +417,8 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                 const Tile T = decode_tile(a, t);
                 const uint64_t x_desc0 = x_desc_base + (uint64_t)T.m_local0 * 4;
                 // filter stage: [tap][c/4][kv rows][16 B], kv = channels of this tile
-                const uint64_t w_desc0 = make_smem_desc(smem_u32(sW), (uint32_t)T.kv * 16, 128, 0);
-                const uint64_t w_tap = (uint64_t)T.kv * 4, w_half = (uint64_t)T.kv * 2;
+                const uint64_t w_desc0 = make_smem_desc(smem_u32(sW), (uint32_t)T.kv * 16 * w_rows, 128, 0);
+                const uint64_t w_tap = (uint64_t)T.kv * 4 * w_rows, w_half = (uint64_t)T.kv * 2 * w_rows;
                 for (int cb = 0; cb < cbs_l && ok; ++cb)
                 {
                     ok = mbar_wait(&x_ready[slot], xphase, status, 13);
@@ -418,7 +440,26 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                 break;
                             tc_fence_after_sync();
                             uint64_t wh = w_desc0 + w_stage_off, xh = x_row;
-                            if (PIXM)
+                            if (PIXM && MERGED)
+                            {
+                                // [W_hi | W_lo] is one operand of 2K columns: x_hi times it gives the hi*hi sums in
+                                // columns [0, K) and one cross term in [K, 2K), x_lo * W_hi adds the other cross
+                                // term there.  Four instructions per tap and 128 pixels instead of six, the 128-pixel
+                                // operand read from shared memory four times instead of six, and the small terms
+                                // never meet a full-size accumulator; the accumulation warps add the two halves.
+                                const uint32_t d0 = tmem + (uint32_t)((g & tb_mask) * mtiles * 2 * a.K);
+                                for (int tp = 0; tp < a.group; ++tp, wh += w_tap, xh += tap_step)
+                                    for (int mt = 0; mt < mtiles; ++mt)
+                                    {
+                                        const uint64_t xa = xh + (uint64_t)mt * 512, xl = xa + x_lo_off;
+                                        const uint32_t d = d0 + (uint32_t)(mt * 2 * a.K);
+                                        tc_mma_tf32(d, xa, wh, idesc_wide, tp == 0 ? 0u : 1u);
+                                        tc_mma_tf32(d + (uint32_t)a.K, xl, wh, idesc, 1u);
+                                        tc_mma_tf32(d, xa + x_half, wh + w_half, idesc_wide, 1u);
+                                        tc_mma_tf32(d + (uint32_t)a.K, xl + x_half, wh + w_half, idesc, 1u);
+                                    }
+                            }
+                            else if (PIXM)
                             {
                                 const uint32_t d0 = tmem + (uint32_t)((g & tb_mask) * mtiles * a.K);
                                 // The small cross terms of the whole group first, the hi*hi terms last: the
@@ -532,9 +573,10 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             {
                 const Tile T = decode_tile(a, t);
                 // the bias seeds the sums (these loads overlap the wait for the first group)
-                float acc[64];
+                constexpr int ACC = MERGED ? 32 : 64; // output channels a thread can hold
+                float acc[ACC];
 #pragma unroll
-                for (int c4 = 0; c4 < 16; ++c4)
+                for (int c4 = 0; c4 < ACC / 4; ++c4)
                 {
                     const float4 b = (bias && c4 * 4 < a.K) ? __ldg(reinterpret_cast<const float4 *>(bias) + c4)
                                                             : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -549,17 +591,33 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     tc_fence_after_sync();
                     if (active)
                     {
-                        const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((tb * mtiles + mt) * a.K);
-                        if (a.K == 16) // a buffer is 16 columns wide: the 32-column load would reach past it
+                        const uint32_t tbase = tmem + ((uint32_t)(quarter * 32) << 16) +
+                                               (uint32_t)((tb * mtiles + mt) * a.K * (MERGED ? 2 : 1));
+                        if (MERGED)
                         {
-                            uint32_t v[16];
-                            tmem_ld16(tbase, v);
+                            // columns [0, K): the hi*hi sums, [K, 2K): the cross terms of the same channels
+                            uint32_t v[32];
+                            tmem_ld32(tbase, v);
                             tmem_ld_wait();
+                            if (a.K == 16)
+                            {
 #pragma unroll
-                            for (int e = 0; e < 16; ++e)
-                                acc[e] += __uint_as_float(v[e]);
+                                for (int e = 0; e < 16; ++e)
+                                    acc[e] += __uint_as_float(v[e]) + __uint_as_float(v[16 + e]);
+                            }
+                            else
+                            {
+#pragma unroll
+                                for (int e = 0; e < 32; ++e)
+                                    acc[e] += __uint_as_float(v[e]);
+                                tmem_ld32(tbase + 32u, v);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int e = 0; e < 32; ++e)
+                                    acc[e] += __uint_as_float(v[e]);
+                            }
                         }
-                        else
+                        else // K = 64
                         {
 #pragma unroll
                         for (int piece = 0; piece < 2; ++piece)
@@ -588,7 +646,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     {
                         float *o = out + (size_t)T.n * (a.K / CB) * plane + (size_t)r * a.o_row_stride + (size_t)c * CB;
 #pragma unroll
-                        for (int kb = 0; kb < 4; ++kb)
+                        for (int kb = 0; kb < ACC / 16; ++kb)
                             if (kb * CB < a.K)
                             {
 #pragma unroll
@@ -945,6 +1003,7 @@ bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm)
     a.cg = 1; a.tap_step = 4;
     // few output channels: pixels on the tensor core's M (see the kernel's PIXM paths)
     a.pixm = pixm ? 1 : 0;
+    a.merged = (pixm && interleaved_filter(a.K)) ? 1 : 0;
     if (a.Ho == 0 || a.Wo == 0)
         return true;
     if (L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r) > 64)
@@ -989,6 +1048,9 @@ bool plan_shape(const small_b200_layer *L, TcArgs &a)
     const bool want_pixm = L && (L->K == 16 || L->K == 32 || L->K == 64);
     if (want_pixm && plan_as(L, a, true))
         return true;
+    // the interleaved filter layout is only read by the pixel-major kernel
+    if (L && interleaved_filter(L->K))
+        return false;
     return plan_as(L, a, false);
 }
 bool plan(const small_b200_layer *L, TcArgs &a)
@@ -1040,7 +1102,7 @@ int small_b200_filter_prepare_tf32x3(const small_b200_layer *L, const float *fil
         return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: shape not covered by the tensor-core path.");
     const long long n = (long long)L->K * L->C * L->Fh * L->Fw;
     prepare_filter_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(
-        n, (L->C / CB) * L->Fh * L->Fw, pick_mt(L->K), L->K, filt, prepared, prepared + n);
+        n, (L->C / CB) * L->Fh * L->Fw, pick_mt(L->K), L->K, interleaved_filter(L->K) ? 1 : 0, filt, prepared, prepared + n);
     return launched("prepare_filter_kernel");
 }
 
@@ -1075,6 +1137,7 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
     {
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         configured.mark(dev);
@@ -1141,7 +1204,10 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
             return launched("conv_tf32x3_kernel");
         }
     }
-    if (a.pixm)
+    if (a.merged)
+        conv_tf32x3_kernel<true, false, true, true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
+            mx, filt_prepared, flo_, a, bias, out, status);
+    else if (a.pixm)
         conv_tf32x3_kernel<true, false, true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
             mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.Fh * a.Fw, a, bias, out, status);
     else if (a.persistent)
