@@ -618,7 +618,7 @@ def kernel_class(chain, i, L, dtype):
     if L["op"] == "conv":
         if dtype == "f32":
             if chain.prepared[i] is not None:
-                return "conv_tf32x3_kernel (tcgen05 kind::tf32, 3xTF32)", "tf32x3"
+                return "conv_tf32x3_kernel (tcgen05 kind::tf32, 3xTF32)" + (" + 2x2 max pool" if follow else ""), "tf32x3"
             name = "conv2d_first_f32_kernel (FFMA)" if L["C"] < 16 else "conv2d_f32_kernel (FFMA)"
             return name + (" + 2x2 max pool" if follow else ""), "ffma"
         if follow:

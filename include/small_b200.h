@@ -174,6 +174,15 @@ int small_b200_conv2d_f32_tf32x3_preferred(const small_b200_layer *L);
 int small_b200_filter_prepare_tf32x3(const small_b200_layer *L, const float *filt, float *prepared, void *stream);
 int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, const float *filt_prepared,
                                  const float *bias, float *out, void *stream);
+/* small::Conv2D_Maxpool2D / Conv2D_ReLU_Maxpool2D / Conv2D_Bias_ReLU_Maxpool2D<FloatBuffer>
+ * (fused_interface_abstract.hpp:463-1418) on the tensor cores: the convolution above with the 2x2
+ * stride-2 unpadded max pool `pool` in its epilogue; `out` holds the pooled tensor
+ * [N][K/16][Ho/2][Wo/2][16].  Covered: 32 or 64 output channels on images wider than 64 pixels
+ * (with padding), odd filter width, even Ho and Wo, no accumulation, an activation that does not
+ * decrease (it is applied after the maximum); ..._supported() says so, other pairs run as two calls. */
+int small_b200_conv2d_maxpool_f32_tf32x3_supported(const small_b200_layer *conv, const small_b200_layer *pool);
+int small_b200_conv2d_maxpool_f32_tf32x3(const small_b200_layer *conv, const small_b200_layer *pool, const float *in,
+                                         const float *filt_prepared, const float *bias, float *out, void *stream);
 /* The tensor-core convolution above for callers that cannot allocate device memory (code
  * running where cudaMalloc is forbidden or would stall the device, plug-ins that are handed
  * nothing but their input and output pointers).  It takes the PACKED filter as the reference

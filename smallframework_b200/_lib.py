@@ -66,6 +66,8 @@ SIGNATURES = {
     "small_b200_conv2d_f32": [_LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_conv2d_maxpool_f32_supported": [_LP, _LP],
     "small_b200_conv2d_maxpool_f32": [_LP, _LP, _VP, _VP, _VP, _VP, _VP],
+    "small_b200_conv2d_maxpool_f32_tf32x3_supported": [_LP, _LP],
+    "small_b200_conv2d_maxpool_f32_tf32x3": [_LP, _LP, _VP, _VP, _VP, _VP, _VP],
     "small_b200_conv2d_f32_tf32x3_supported": [_LP],
     "small_b200_conv2d_f32_tf32x3_preferred": [_LP],
     "small_b200_filter_prepare_tf32x3": [_LP, _VP, _VP, _VP],

@@ -94,6 +94,9 @@ struct TcArgs
     // behind its hi rows ([slab][c/4][hi k | lo k][4 c], interleaved_filter()): a pixel-major MMA then
     // takes [W_hi | W_lo] as ONE operand of 2K columns (the MERGED kernel, see its issuer).
     int merged;
+    // 1: a 2x2 stride-2 max pool follows in the epilogue (pixel-major tiled plans only); the output strides
+    // then describe the pooled tensor and `stage_off` locates the exchange rows of the pooling step
+    int pool;
 };
 
 // Output channels per CTA, a function of K alone so that filter preparation and the
@@ -216,7 +219,7 @@ __device__ __forceinline__ Tile decode_tile(const TcArgs &a, int t)
 #define SB_TILE_LOOP(cond_extra) \
     for (int t = first_tile, once_ = 0; (PERSIST ? (t < a.total_tiles) : (once_ == 0)) && (cond_extra); t += tile_step, ++once_)
 
-template <bool PERSIST, bool SPLIT, bool PIXM = false, bool MERGED = false>
+template <bool PERSIST, bool SPLIT, bool PIXM = false, bool MERGED = false, bool POOL = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__restrict__ filt,
                    const float *__restrict__ filt_lo, const TcArgs a, const float *__restrict__ bias, float *__restrict__ out, int *status)
@@ -637,7 +640,70 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     if (lane == 0)
                         mbar_arrive(&t_empty[tb]);
                 }
-                if (ok && active)
+                if (POOL)
+                {
+                    // 2x2 max pool, stride 2, on the sums in registers (K = 32 or 64: a thread holds ACC = K
+                    // sums).  Tiles have even heights and widths and an even patch width, so the horizontal
+                    // neighbour of pixel (rl, cl) is the next lane of the same warp: the even lane of a pair keeps
+                    // the lower half of the channels of BOTH pixels' maximum, the odd lane the upper half (one
+                    // shuffle per kept channel).  The vertical neighbour is PW lanes further on, in another warp:
+                    // odd rows leave their halves in shared memory, even rows pick them up behind a barrier of the
+                    // eight accumulation warps, apply the activation (monotonic, so it commutes with the maximum;
+                    // the launch code checks that) and store their half of the pooled pixel.  A first barrier
+                    // keeps a warp from writing into the exchange rows while a slower one still reads the previous
+                    // tile's.  Every instruction here competes with the MMA-issuing threads for the issue slots of
+                    // the four schedulers, which is why the work is split between the lanes of a pair.
+                    // Every warp comes to the first barrier at every tile; a warp whose wait ran out says so
+                    // before it and all leave together (see the channel-major epilogue).
+                    constexpr int HALF = ACC / 2;
+                    const int ml = mt * 128 + quarter * 32 + lane; // tiled plans: m_local0 = 0
+                    const int rl = ml / a.PW, cl = ml - rl * a.PW;
+                    const int upper = lane & 1;
+                    float *xrow = reinterpret_cast<float *>(smem + a.stage_off) +
+                                  ((size_t)(rl >> 1) * (a.PW >> 1) + (cl >> 1)) * (ACC + 4) + upper * HALF;
+                    if (!ok)
+                        *reinterpret_cast<volatile int *>(&acc_failed) = 1;
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    if (*reinterpret_cast<volatile int *>(&acc_failed))
+                        ok = false;
+                    if (ok)
+                    {
+                        float keep[HALF];
+                        if (active)
+                        {
+#pragma unroll
+                            for (int e = 0; e < HALF; ++e)
+                            {
+                                const float mine = upper ? acc[HALF + e] : acc[e], theirs = upper ? acc[e] : acc[HALF + e];
+                                keep[e] = fmaxf(mine, __shfl_xor_sync(0xffffffffu, theirs, 1));
+                            }
+                            if ((rl & 1) && rl < a.TH)
+                            {
+#pragma unroll
+                                for (int j = 0; j < HALF / 4; ++j)
+                                    reinterpret_cast<float4 *>(xrow)[j] = make_float4(keep[4 * j], keep[4 * j + 1], keep[4 * j + 2], keep[4 * j + 3]);
+                            }
+                        }
+                        asm volatile("bar.sync 1, 256;" ::: "memory");
+                        const int r = T.row_base + rl, c = T.col_base + (cl & ~1);
+                        if (active && !(rl & 1) && (cl & ~1) < T.tw_valid && rl < a.TH && r < a.Ho)
+                        {
+                            float *o = out + ((size_t)T.n * (a.K / CB) + (size_t)upper * (HALF / CB)) * plane +
+                                       (size_t)(r >> 1) * a.o_row_stride + (size_t)(c >> 1) * CB;
+#pragma unroll
+                            for (int j = 0; j < HALF / 4; ++j)
+                            {
+                                const float4 y = reinterpret_cast<const float4 *>(xrow)[j]; // row rl + 1 shares the slot
+                                float4 x = make_float4(fmaxf(keep[4 * j], y.x), fmaxf(keep[4 * j + 1], y.y),
+                                                       fmaxf(keep[4 * j + 2], y.z), fmaxf(keep[4 * j + 3], y.w));
+                                x.x = apply_act_ns(x.x, act_ns); x.y = apply_act_ns(x.y, act_ns);
+                                x.z = apply_act_ns(x.z, act_ns); x.w = apply_act_ns(x.w, act_ns);
+                                *(reinterpret_cast<float4 *>(o + (size_t)(j >> 2) * plane) + (j & 3)) = x;
+                            }
+                        }
+                    }
+                }
+                else if (ok && active)
                 {
                     const int ml = T.m_local0 + mt * 128 + quarter * 32 + lane;
                     const int rl = ml / a.PW, cl = ml - rl * a.PW;
@@ -908,17 +974,20 @@ bool fit_rings(TcArgs &a, bool need_two)
     // these layers that chain, not the MMAs, sets the pace (16 -> 32 channels at 208x208: 0.22 ms
     // with no MMA issued at all, 0.30 ms with them).
     a.w_resident = 0;
+    // pooled epilogue: exchange rows, one slot of K + 4 floats per pair of columns of every odd row
+    const size_t pool_rows = a.pool ? (size_t)(a.TH / 2) * (a.PW / 2) * (a.K + 4) * 4 : 0;
     if (a.pixm && a.k_tiles == 1 && a.cg == 1)
     {
         const int stages = a.cbs * (a.taps / a.group);
         if (stages <= W_STAGES_MAX)
             for (int xs = 3; xs >= 2; --xs)
             {
-                const size_t smem = (size_t)xs * 2 * x_part + (size_t)stages * 2 * w_part;
+                const size_t ops = (size_t)xs * 2 * x_part + (size_t)stages * 2 * w_part;
+                const size_t smem = ops + pool_rows;
                 if (smem <= limit)
                 {
                     a.x_slots = xs; a.w_stages = stages; a.smem_bytes = (unsigned)smem; a.tbufs = 4;
-                    a.persistent = 1; a.stage_off = (unsigned)smem; a.w_resident = 1;
+                    a.persistent = 1; a.stage_off = (unsigned)ops; a.w_resident = 1;
                     return true;
                 }
             }
@@ -931,7 +1000,7 @@ bool fit_rings(TcArgs &a, bool need_two)
                 continue;
             const size_t ops = (size_t)xs * 2 * x_part + (size_t)p[1] * 2 * w_part;
             const size_t full = (size_t)a.NPX * (a.MT + 16) * 4; // one tile per CTA stages the whole tile
-            const size_t smem = persistent ? ops + (a.pixm ? 0 : staging) : (ops > full ? ops : full);
+            const size_t smem = persistent ? ops + (a.pixm ? pool_rows : staging) : (ops > full ? ops : full);
             if (smem <= limit)
             {
                 a.x_slots = xs; a.w_stages = p[1]; a.smem_bytes = (unsigned)smem;
@@ -952,12 +1021,14 @@ bool plan_tiled(const small_b200_layer *L, TcArgs &a)
     double best = 0.0;
     int best_tw = 0, best_th = 0;
     const int cap = 256, gran = a.pixm ? 128 : 64;
-    for (int tw = 8; tw <= a.Wo && tw + a.Fw - 1 <= cap; ++tw)
+    for (int tw = 8; tw <= a.Wo && tw + a.Fw - 1 <= cap; tw += (a.pool ? 2 : 1))
     {
         const int pw = tw + a.Fw - 1;
         int th = (cap - tw) / pw + 1;
         if (th > a.Ho)
             th = a.Ho;
+        if (a.pool && (th &= ~1) == 0) // pooled epilogue: pairs of rows and of columns stay inside a tile
+            continue;
         const int npx = ((th - 1) * pw + tw + gran - 1) / gran * gran;
         const long long tiles = (long long)((a.Wo + tw - 1) / tw) * ((a.Ho + th - 1) / th);
         const double eff = (double)a.Wo * a.Ho / ((double)tiles * npx);
@@ -983,7 +1054,7 @@ bool plan_tiled(const small_b200_layer *L, TcArgs &a)
 }
 
 // Tiling and shared-memory plan of one layer; false when the shape is not covered.
-bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm)
+bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm, bool pool = false)
 {
     if (!L || L->stride != 1 || row_stride(L) != 1 || L->C % CB != 0 || L->K % CB != 0 || L->C <= 0 || L->K <= 0)
         return false;
@@ -1004,6 +1075,15 @@ bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm)
     // few output channels: pixels on the tensor core's M (see the kernel's PIXM paths)
     a.pixm = pixm ? 1 : 0;
     a.merged = (pixm && interleaved_filter(a.K)) ? 1 : 0;
+    a.pool = pool ? 1 : 0;
+    if (pool)
+    {
+        // only the pixel-major tiled plan has the pooled epilogue; even sizes and an even patch width
+        if (!pixm || a.accumulate || a.Ho % 2 || a.Wo % 2 || a.Fw % 2 == 0 || a.Ho == 0 || a.Wo == 0 ||
+            L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r) <= 64)
+            return false;
+        return plan_tiled(L, a);
+    }
     if (a.Ho == 0 || a.Wo == 0)
         return true;
     if (L->W + (L->pad_l > L->pad_r ? L->pad_l : L->pad_r) > 64)
@@ -1074,6 +1154,28 @@ bool plan(const small_b200_layer *L, TcArgs &a)
     a.o_row_stride = (long long)a.Wo * CB;
     return true;
 }
+// The convolution with the 2x2 stride-2 max pool `pool` in its epilogue; the strides describe the pooled tensor.
+bool plan_pooled(const small_b200_layer *L, const small_b200_layer *pool, TcArgs &a)
+{
+    if (!L || !pool || !(L->K == 32 || L->K == 64) || L->accumulate)
+        return false;
+    // the activation is applied after the maximum: it must not decrease (ReLU, or LeakyReLU with a slope >= 0)
+    if (L->act == SMALL_B200_ACT_LEAKY && !(L->slope >= 0.f))
+        return false;
+    if (pool->Fh != 2 || pool->Fw != 2 || pool->stride != 2 || row_stride(pool) != 2 || pool->pad_t || pool->pad_b ||
+        pool->pad_l || pool->pad_r)
+        return false;
+    if (!plan_as(L, a, true, true))
+        return false;
+    if (pool->H != a.Ho || pool->W != a.Wo || pool->C != L->K || pool->N != L->N)
+        return false;
+    a.o_kb_stride = (long long)(a.Ho / 2) * (a.Wo / 2) * CB;
+    a.o_row_stride = (long long)(a.Wo / 2) * CB;
+    return true;
+}
+
+int run_tc(const small_b200_layer *L, const small_b200_layer *pool, const float *in, const float *filt_prepared,
+           const float *bias, float *out, void *stream);
 } // namespace
 
 extern "C"
@@ -1109,11 +1211,35 @@ int small_b200_filter_prepare_tf32x3(const small_b200_layer *L, const float *fil
 int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, const float *filt_prepared,
                                  const float *bias, float *out, void *stream)
 {
+    return run_tc(L, nullptr, in, filt_prepared, bias, out, stream);
+}
+
+int small_b200_conv2d_maxpool_f32_tf32x3_supported(const small_b200_layer *conv, const small_b200_layer *pool)
+{
+    TcArgs a;
+    return plan_pooled(conv, pool, a) ? 1 : 0;
+}
+
+int small_b200_conv2d_maxpool_f32_tf32x3(const small_b200_layer *conv, const small_b200_layer *pool, const float *in,
+                                         const float *filt_prepared, const float *bias, float *out, void *stream)
+{
+    if (!conv || !pool)
+        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D+MaxPool2D<float> (3xTF32) ERROR: null layer.");
+    return run_tc(conv, pool, in, filt_prepared, bias, out, stream);
+}
+} // extern "C"
+
+namespace
+{
+int run_tc(const small_b200_layer *L, const small_b200_layer *pool, const float *in, const float *filt_prepared,
+           const float *bias, float *out, void *stream)
+{
     if (int rc = check_window_layer(L, "Conv2D<float>", true, 2))
         return rc;
     TcArgs a;
-    if (!plan(L, a))
-        return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: shape not covered by the tensor-core path.");
+    if (pool ? !plan_pooled(L, pool, a) : !plan(L, a))
+        return fail(SMALL_B200_INVALID_ARGUMENT, pool ? "Conv2D+MaxPool2D<float> (3xTF32) ERROR: shape not covered by the fused tensor-core path."
+                                                      : "Conv2D<float> (3xTF32) ERROR: shape not covered by the tensor-core path.");
     if (a.N == 0 || a.Ho == 0 || a.Wo == 0)
         return SMALL_B200_OK;
 
@@ -1138,6 +1264,8 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         configured.mark(dev);
@@ -1204,7 +1332,13 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
             return launched("conv_tf32x3_kernel");
         }
     }
-    if (a.merged)
+    if (a.pool && a.merged)
+        conv_tf32x3_kernel<true, false, true, true, true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
+            mx, filt_prepared, flo_, a, bias, out, status);
+    else if (a.pool)
+        conv_tf32x3_kernel<true, false, true, false, true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
+            mx, filt_prepared, flo_, a, bias, out, status);
+    else if (a.merged)
         conv_tf32x3_kernel<true, false, true, true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
             mx, filt_prepared, flo_, a, bias, out, status);
     else if (a.pixm)
@@ -1223,7 +1357,7 @@ int small_b200_conv2d_f32_tf32x3(const small_b200_layer *L, const float *in, con
             mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.Fh * a.Fw, a, bias, out, status);
     return launched("conv_tf32x3_kernel");
 }
-} // extern "C"
+} // namespace
 
 // ---------------------------------------------------------------------------------------------
 // The same tensor-core convolution for callers that must not allocate device memory.

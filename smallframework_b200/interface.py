@@ -464,6 +464,33 @@ def Conv2D_3xTF32(kernel_height, kernel_width, stride, t_pad, b_pad, l_pad, r_pa
                                              _ptr(output_buf), _stream(stream)))
 
 
+def conv2d_maxpool_3xTF32_supported(conv_kernel_height, conv_kernel_width, conv_pads, output_channels,
+                                    input_channels, input_height, input_width):
+    """Whether Conv2D_Maxpool2D_3xTF32 covers this convolution followed by a 2x2 stride-2 max pool."""
+    Lc = _layer(1, input_channels, output_channels, input_height, input_width, conv_kernel_height,
+                conv_kernel_width, 1, *conv_pads)
+    ho, wo = Lc.out_hw()
+    Lp = _layer(1, output_channels, output_channels, ho, wo, 2, 2, 2, 0, 0, 0, 0)
+    return bool(lib().small_b200_conv2d_maxpool_f32_tf32x3_supported(C.byref(Lc), C.byref(Lp)))
+
+
+def Conv2D_Maxpool2D_3xTF32(conv_kernel_height, conv_kernel_width, conv_pads, output_channels, input_channels,
+                            input_height, input_width, input_buf, prepared_filter_buf, bias_buf, output_buf, *,
+                            activation=ACT_NONE, negative_slope=0.0, batch=1, stream=None):
+    """small::Conv2D_Maxpool2D / Conv2D_ReLU_Maxpool2D / Conv2D_Bias_ReLU_Maxpool2D<FloatBuffer>
+    (fused_interface_abstract.hpp:463-1418 of the reference) on the tensor cores: stride-1 convolution
+    (+ bias, + activation) with the 2x2 stride-2 max pool in its epilogue;
+    prepared_filter_buf = prepare_filter_3xTF32(filter)."""
+    Lc = _layer(batch, input_channels, output_channels, input_height, input_width, conv_kernel_height,
+                conv_kernel_width, 1, *conv_pads, 0, activation, negative_slope)
+    ho, wo = Lc.out_hw()
+    Lp = _layer(batch, output_channels, output_channels, ho, wo, 2, 2, 2, 0, 0, 0, 0)
+    _need(output_buf, batch * output_channels * (ho // 2) * (wo // 2), "Conv2D_Maxpool2D output")
+    check(lib().small_b200_conv2d_maxpool_f32_tf32x3(C.byref(Lc), C.byref(Lp), _ptr(input_buf),
+                                                     _ptr(prepared_filter_buf), _ptr(bias_buf),
+                                                     _ptr(output_buf), _stream(stream)))
+
+
 # --------------------------------------------------------------------------- fused uint8 blocks
 def _qlayer(batch, C_, K, H, W, Fh, Fw, stride, pads, inp_zero, filt_zero, out_q):
     """A uint8 layer descriptor from explicit quantisation parameters: out_q = (lshift, rshift, multiplier)."""

@@ -383,10 +383,15 @@ class Chain:
         if dtype == "f32" and fuse_pool:
             for i in range(len(layers) - 1):
                 L, Pn = layers[i], layers[i + 1]
-                if L["op"] != "conv" or Pn["op"] != "maxpool" or self.prepared[i] is not None or "src" in L:
+                if L["op"] != "conv" or Pn["op"] != "maxpool" or "src" in L:
                     continue
                 dc = self._desc(L, L["C"] if i == 0 else padded(L["C"]))
                 dp = self._desc(Pn, padded(Pn["C"]))
+                if self.prepared[i] is not None:
+                    # tensor-core convolution: the pool runs in its epilogue where the library covers the pair
+                    if lib().small_b200_conv2d_maxpool_f32_tf32x3_supported(C.byref(dc), C.byref(dp)):
+                        self.fused_into[i + 1] = i
+                    continue
                 if lib().small_b200_conv2d_maxpool_f32_supported(C.byref(dc), C.byref(dp)):
                     self.fused_into[i + 1] = i
         if dtype == "u8" and fuse_u8:
@@ -448,6 +453,10 @@ class Chain:
             else:
                 check(l.small_b200_conv2d_avgpool_dense_u8(C.byref(d), C.byref(ds[0]), C.byref(ds[1]), p(src), p(wt),
                                                            p(bs), p(w2), p(b2), p(dst), stream))
+        elif L["op"] == "conv" and follow and self.prepared[i] is not None:
+            dp = self._desc(self.layers[i + 1], padded(self.layers[i + 1]["C"]))
+            check(l.small_b200_conv2d_maxpool_f32_tf32x3(C.byref(d), C.byref(dp), p(src), p(self.prepared[i]), p(bs),
+                                                         p(dst), stream))
         elif L["op"] == "conv" and follow:
             dp = self._desc(self.layers[i + 1], padded(self.layers[i + 1]["C"]))
             check(l.small_b200_conv2d_maxpool_f32(C.byref(d), C.byref(dp), p(src), p(wt), p(bs), p(dst), stream))

@@ -66,6 +66,10 @@ CASES = [
     (80, 64, 20, 20, 1, 1, "valid", 64),
     (16, 32, 32, 32, 3, 3, "same", 48),
     (32, 64, 26, 26, 3, 3, "same", 48),
+    # 64 output channels, two blocks of 128 pixels per tile: two accumulator buffers of 256 columns and two
+    # issuing threads, more tiles than CTAs (buffer phases run on over many groups)
+    (32, 64, 104, 104, 3, 3, "same", 4),
+    (64, 64, 20, 20, 3, 3, "same", 80),
 ]
 
 
@@ -98,6 +102,61 @@ def test_conv2d_3xtf32(oracle, case, mode):
     got = O.numpy().reshape(N, -1)
     assert _lib.device_status() == 0
     assert rel_max_err(got, want) <= TOL
+
+
+POOLED_CASES = [
+    # C, K, H, W, Fh, Fw, pads, batch: images wider than 64 pixels, even output sizes
+    (16, 32, 40, 130, 3, 3, "same", 2),    # merged-operand kernel, partial tiles at the right edge
+    (32, 64, 70, 90, 3, 3, "same", 2),     # 64 output channels
+    (16, 32, 208, 208, 3, 3, "same", 1),   # Tiny-YOLOv2 conv2 + maxpool2: more tiles than CTAs
+    (32, 64, 104, 104, 3, 3, "same", 3),   # conv3 + maxpool3
+    (16, 32, 12, 100, 1, 1, "valid", 2),
+    (32, 32, 52, 68, 5, 3, (2, 2, 1, 1), 1),
+]
+
+
+@pytest.mark.parametrize("case", POOLED_CASES, ids=lambda c: "C{}_K{}_{}x{}_k{}x{}_{}_n{}".format(*[
+    "".join(map(str, v)) if isinstance(v, tuple) else v for v in c]))
+@pytest.mark.parametrize("mode", ["plain", "bias_leaky"])
+def test_conv2d_maxpool_3xtf32(oracle, case, mode):
+    """Conv2D(+bias)(+activation) -> MaxPool2D 2x2 / 2 in the epilogue of the tensor-core kernel (the
+    reference's Conv2D_Bias_ReLU_Maxpool2D family, fused_interface_abstract.hpp:463-1418) against the
+    oracle's convolution followed by its max pool, and bit-identical to the two-call path."""
+    C, K, H, W, Fh, Fw, pm, N = case
+    pads = same_pads(H, W, Fh, Fw, 1) if pm == "same" else (0, 0, 0, 0) if pm == "valid" else pm
+    assert S.conv2d_maxpool_3xTF32_supported(Fh, Fw, pads, K, C, H, W)
+    rng = np.random.default_rng(abs(hash((case, mode, "pool"))) % (1 << 31))
+    x = P.pack_activation(rng.uniform(-1, 1, (N, C, H, W)).astype(np.float32))
+    w = P.pack_conv_filter(rng.normal(0, np.sqrt(2.0 / (C * Fh * Fw)), (K, C, Fh, Fw)).astype(np.float32))
+    bias = None if mode == "plain" else rng.uniform(-0.5, 0.5, K).astype(np.float32)
+    act, slope = (0, 0.0) if mode == "plain" else (S.ACT_LEAKY, 0.1)
+    sh = shape(C, K, H, W, Fh, Fw, 1, pads, CB)
+    ho, wo = sh.out_hw()
+    shp = shape(K, K, ho, wo, 2, 2, 2, (0, 0, 0, 0), CB)
+    I, F = fbuf(x), fbuf(w)
+    B = None if bias is None else fbuf(bias)
+    Fp = S.FloatBuffer(2 * F.size())
+    S.prepare_filter_3xTF32(Fh, Fw, K, C, F, Fp)
+    O = S.FloatBuffer(N * K * (ho // 2) * (wo // 2))
+    S.Conv2D_Maxpool2D_3xTF32(Fh, Fw, pads, K, C, H, W, I, Fp, B, O, activation=act, negative_slope=slope, batch=N)
+    got = O.numpy().reshape(N, -1)
+    assert _lib.device_status() == 0
+    conv = oracle_conv_batch(oracle, sh, x, w, bias=bias, act=act, slope=slope)
+    want = np.stack([oracle.pool2d_f32(shp, conv[n]) for n in range(N)])
+    assert rel_max_err(got, want) <= TOL
+    # same sums in the same order with or without the pool
+    mid, two = S.FloatBuffer(N * K * ho * wo), S.FloatBuffer(N * K * (ho // 2) * (wo // 2))
+    S.Conv2D_3xTF32(Fh, Fw, 1, *pads, K, C, H, W, I, Fp, B, mid, activation=act, negative_slope=slope, batch=N)
+    S.MaxPool2D(2, 2, 2, 0, 0, 0, 0, K, ho, wo, mid, two, batch=N)
+    assert np.array_equal(got, two.numpy().reshape(N, -1))
+
+
+def test_pooled_epilogue_refuses_other_shapes():
+    assert not S.conv2d_maxpool_3xTF32_supported(3, 3, (1, 1, 1, 1), 32, 16, 52, 52)     # narrow image: row-range tiles
+    assert not S.conv2d_maxpool_3xTF32_supported(3, 3, (1, 1, 1, 1), 128, 64, 104, 104)  # channel-major kernel
+    assert not S.conv2d_maxpool_3xTF32_supported(3, 3, (1, 1, 1, 1), 32, 16, 101, 101)   # odd output
+    assert not S.conv2d_maxpool_3xTF32_supported(2, 2, (0, 0, 0, 0), 32, 16, 101, 101)   # even filter width
+    assert not S.conv2d_maxpool_3xTF32_supported(3, 3, (1, 1, 1, 1), 16, 16, 104, 104)   # 16 output channels
 
 
 def test_unsupported_shapes_are_refused():
