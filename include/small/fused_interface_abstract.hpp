@@ -133,6 +133,23 @@ inline void conv_then_pool(int act, BufferT const *bias, SMALL_B200_CONV_ARGS, S
                                        conv_t_pad, conv_b_pad, conv_l_pad, conv_r_pad, 0, act);
         small_b200_layer Lp = describe(K, K, Hm, Wm, pool_kernel_height, pool_kernel_width, pool_stride,
                                        pool_t_pad, pool_b_pad, pool_l_pad, pool_r_pad);
+        // on the tensor cores where the library prefers them for the convolution and its kernel has the
+        // pooled epilogue for the pair (the re-laid filter is kept with the filter buffer, as in conv())
+        if (tensor_core_enabled() && small_b200_conv2d_f32_tf32x3_preferred(&Lc) &&
+            small_b200_conv2d_maxpool_f32_tf32x3_supported(&Lc, &Lp))
+        {
+            const uint64_t key = ((uint64_t)K << 40) ^ ((uint64_t)C << 20) ^ ((uint64_t)conv_kernel_height << 8) ^
+                                 (uint64_t)conv_kernel_width;
+            float *prepared = filt.companion(key);
+            if (!prepared)
+            {
+                prepared = filt.make_companion(key, 2 * (size_t)K * C * conv_kernel_height * conv_kernel_width);
+                throw_on(small_b200_filter_prepare_tf32x3(&Lc, filt.device_ptr(), prepared, b200::stream()));
+            }
+            throw_on(small_b200_conv2d_maxpool_f32_tf32x3(&Lc, &Lp, in.device_ptr(), prepared,
+                                                          bias ? bias->device_ptr() : nullptr, out.device_ptr(), b200::stream()));
+            return;
+        }
         if (small_b200_conv2d_maxpool_f32_supported(&Lc, &Lp))
         {
             throw_on(small_b200_conv2d_maxpool_f32(&Lc, &Lp, in.device_ptr(), filt.device_ptr(),

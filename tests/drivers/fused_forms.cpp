@@ -105,6 +105,24 @@ int main()
         unfused(true, true);
         expect_close(pk == 2 ? "Conv2D_Bias_ReLU_Maxpool2D 2x2" : "Conv2D_Bias_ReLU_Maxpool2D 3x3", a, b, a.size());
     }
+    // ---- conv -> max pool on an image wider than 64 pixels with 32 output channels: the tensor-core
+    //      kernel takes the pool in its epilogue
+    {
+        const int C2 = 16, K2 = 32, H2 = 20, W2 = 100;
+        Buf in2((size_t)C2 * H2 * W2), f2((size_t)K2 * C2 * 9), bias2(K2);
+        Buf a((size_t)K2 * (H2 / 2) * (W2 / 2)), b((size_t)K2 * (H2 / 2) * (W2 / 2)), c((size_t)K2 * H2 * W2);
+        fill(in2, -1, 1); fill(f2, -0.1f, 0.1f); fill(bias2, -0.5f, 0.5f);
+        small::Conv2D_Bias_ReLU_Maxpool2D(3, 3, 1, p, p, p, p, 2, 2, 2, 0, 0, 0, 0, K2, C2, H2, W2, in2, f2, bias2, tile, a);
+        small::Bias(K2, H2, W2, bias2, c);
+        small::PartialConv2D(3, 3, 1, p, p, p, p, K2, C2, H2, W2, in2, f2, c);
+        small::ReLUActivation(K2, H2, W2, c, c);
+        small::MaxPool2D(2, 2, 2, 0, 0, 0, 0, K2, H2, W2, c, b);
+        expect_close("Conv2D_Bias_ReLU_Maxpool2D wide image", a, b, a.size());
+        small::Conv2D_Maxpool2D(3, 3, 1, p, p, p, p, 2, 2, 2, 0, 0, 0, 0, K2, C2, H2, W2, in2, f2, tile, a);
+        small::Conv2D(3, 3, 1, p, p, p, p, K2, C2, H2, W2, in2, f2, c);
+        small::MaxPool2D(2, 2, 2, 0, 0, 0, 0, K2, H2, W2, c, b);
+        expect_close("Conv2D_Maxpool2D wide image", a, b, a.size());
+    }
     // ---- conv -> depthwise conv
     {
         Buf a((size_t)K * Hc * Wc), b((size_t)K * Hc * Wc), c((size_t)K * Hc * Wc);
