@@ -94,6 +94,11 @@ struct TcArgs
     // behind its hi rows ([slab][c/4][hi k | lo k][4 c], interleaved_filter()): a pixel-major MMA then
     // takes [W_hi | W_lo] as ONE operand of 2K columns (the MERGED kernel, see its issuer).
     int merged;
+    // Layers of one 16-channel block with the merged operand sum a WHOLE window in tensor memory (group = taps,
+    // at most 18 full-size accumulations): one flush and one round of hand-overs per tile instead of one per
+    // kernel row, and the issuing threads take whole tiles in turn.  row_skip: descriptor units from the last
+    // tap of a kernel row to the first tap of the next one, beyond the one-pixel step.
+    int row_skip;
     // 1: a 2x2 stride-2 max pool follows in the epilogue (pixel-major tiled plans only); the output strides
     // then describe the pooled tensor and `stage_off` locates the exchange rows of the pooling step
     int pool;
@@ -219,7 +224,7 @@ __device__ __forceinline__ Tile decode_tile(const TcArgs &a, int t)
 #define SB_TILE_LOOP(cond_extra) \
     for (int t = first_tile, once_ = 0; (PERSIST ? (t < a.total_tiles) : (once_ == 0)) && (cond_extra); t += tile_step, ++once_)
 
-template <bool PERSIST, bool SPLIT, bool PIXM = false, bool MERGED = false, bool POOL = false>
+template <bool PERSIST, bool SPLIT, bool PIXM = false, int MERGED = 0, bool POOL = false> // MERGED: 1 merged operand, 2 with whole-window groups
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__restrict__ filt,
                    const float *__restrict__ filt_lo, const TcArgs a, const float *__restrict__ bias, float *__restrict__ out, int *status)
@@ -451,7 +456,9 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                 // operand read from shared memory four times instead of six, and the small terms
                                 // never meet a full-size accumulator; the accumulation warps add the two halves.
                                 const uint32_t d0 = tmem + (uint32_t)((g & tb_mask) * mtiles * 2 * a.K);
+                                int kw = 0;
                                 for (int tp = 0; tp < a.group; ++tp, wh += w_tap, xh += tap_step)
+                                {
                                     for (int mt = 0; mt < mtiles; ++mt)
                                     {
                                         const uint64_t xa = xh + (uint64_t)mt * 512, xl = xa + x_lo_off;
@@ -461,6 +468,12 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                                         tc_mma_tf32(d, xa + x_half, wh + w_half, idesc_wide, 1u);
                                         tc_mma_tf32(d + (uint32_t)a.K, xl + x_half, wh + w_half, idesc, 1u);
                                     }
+                                    if (MERGED == 2 && ++kw == a.Fw) // the group spans kernel rows: on to the next patch row
+                                    {
+                                        kw = 0;
+                                        xh += (uint64_t)a.row_skip;
+                                    }
+                                }
                             }
                             else if (PIXM)
                             {
@@ -959,6 +972,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
 // next to the operand buffers; the others keep the deepest rings and let the staging alias them.  need_two: only accept plans with two patches in flight.
 bool fit_rings(TcArgs &a, bool need_two)
 {
+    a.row_skip = (a.cg == 1 && a.group != a.Fw) ? (a.PW - a.Fw) * 4 : 0;
     const size_t limit = 226 * 1024;
     const int entries = a.PR * a.PW;
     const size_t x_part = ((size_t)entries * 64 * a.cg + 1023) & ~(size_t)1023;
@@ -1054,7 +1068,7 @@ bool plan_tiled(const small_b200_layer *L, TcArgs &a)
 }
 
 // Tiling and shared-memory plan of one layer; false when the shape is not covered.
-bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm, bool pool = false)
+bool plan_as_g(const small_b200_layer *L, TcArgs &a, bool pixm, bool pool, bool whole)
 {
     if (!L || L->stride != 1 || row_stride(L) != 1 || L->C % CB != 0 || L->K % CB != 0 || L->C <= 0 || L->K <= 0)
         return false;
@@ -1075,6 +1089,14 @@ bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm, bool pool = false)
     // few output channels: pixels on the tensor core's M (see the kernel's PIXM paths)
     a.pixm = pixm ? 1 : 0;
     a.merged = (pixm && interleaved_filter(a.K)) ? 1 : 0;
+    a.row_skip = 0;
+    if (whole)
+    {
+        // the whole window in one group (TcArgs::row_skip): one channel block, at most 3x3
+        if (!a.merged || a.cbs != 1 || a.Fh < 2 || a.taps > 9)
+            return false;
+        a.group = a.taps;
+    }
     a.pool = pool ? 1 : 0;
     if (pool)
     {
@@ -1122,6 +1144,13 @@ bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm, bool pool = false)
                 return true;
         }
     return false;
+}
+bool plan_as(const small_b200_layer *L, TcArgs &a, bool pixm, bool pool = false)
+{
+    // whole-window groups only where the filter stays resident in shared memory
+    if (pixm && plan_as_g(L, a, pixm, pool, true) && (a.w_resident || a.Ho == 0 || a.Wo == 0))
+        return true;
+    return plan_as_g(L, a, pixm, pool, false);
 }
 bool plan_shape(const small_b200_layer *L, TcArgs &a)
 {
@@ -1263,9 +1292,11 @@ int run_tc(const small_b200_layer *L, const small_b200_layer *pool, const float 
     {
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true, 0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<true, false, true, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         SB_CUDA(cudaFuncSetAttribute(conv_tf32x3_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         configured.mark(dev);
@@ -1332,15 +1363,21 @@ int run_tc(const small_b200_layer *L, const small_b200_layer *pool, const float 
             return launched("conv_tf32x3_kernel");
         }
     }
-    if (a.pool && a.merged)
-        conv_tf32x3_kernel<true, false, true, true, true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
-            mx, filt_prepared, flo_, a, bias, out, status);
+    const bool whole = a.merged && a.cg == 1 && a.group != a.Fw; // whole-window groups (TcArgs::row_skip)
+#define SB_LAUNCH_PIXM(M, P) \
+    conv_tf32x3_kernel<true, false, true, M, P><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>( \
+        mx, filt_prepared, flo_, a, bias, out, status)
+    if (a.pool && whole)
+        SB_LAUNCH_PIXM(2, true);
+    else if (a.pool && a.merged)
+        SB_LAUNCH_PIXM(1, true);
     else if (a.pool)
-        conv_tf32x3_kernel<true, false, true, false, true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
-            mx, filt_prepared, flo_, a, bias, out, status);
+        SB_LAUNCH_PIXM(0, true);
+    else if (whole)
+        SB_LAUNCH_PIXM(2, false);
     else if (a.merged)
-        conv_tf32x3_kernel<true, false, true, true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
-            mx, filt_prepared, flo_, a, bias, out, status);
+        SB_LAUNCH_PIXM(1, false);
+#undef SB_LAUNCH_PIXM
     else if (a.pixm)
         conv_tf32x3_kernel<true, false, true><<<(unsigned)blocks, NUM_THREADS, a.smem_bytes, as_stream(stream)>>>(
             mx, filt_prepared, filt_prepared + (size_t)a.K * a.C * a.Fh * a.Fw, a, bias, out, status);

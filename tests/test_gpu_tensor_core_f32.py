@@ -70,6 +70,10 @@ CASES = [
     # issuing threads, more tiles than CTAs (buffer phases run on over many groups)
     (32, 64, 104, 104, 3, 3, "same", 4),
     (64, 64, 20, 20, 3, 3, "same", 80),
+    # one 16-channel block, 16 / 32 output channels: the whole window is one group (2x3, 3x1 and 1x3 windows too)
+    (16, 32, 20, 24, 2, 3, "valid", 3),
+    (16, 16, 30, 18, 3, 1, (1, 1, 0, 0), 40),
+    (16, 32, 18, 90, 1, 3, (0, 0, 1, 1), 2),
 ]
 
 
