@@ -161,7 +161,9 @@ int small_b200_conv2d_maxpool_f32(const small_b200_layer *conv, const small_b200
  * tensor core:
  *   filt_prepared  small_b200_filter_prepare_tf32x3(filt), once per set of weights,
  *                  2 * K*C*Fh*Fw floats: per CTA tile and tap the filter as [c/4][k][4 c]
- *                  (what the tensor core reads directly) followed by its lo copy.
+ *                  (what the tensor core reads directly) followed by its lo copy; for K = 16 or 32
+ *                  the lo rows of every 4-channel chunk follow its hi rows directly
+ *                  ([c/4][hi k | lo k][4 c]).  The layout depends on K alone; treat it as opaque.
  * ..._supported() says whether a shape is covered (1) or not (0).  The reference has no
  * counterpart of the preparation call (its filters are used as packed). */
 int small_b200_conv2d_f32_tf32x3_supported(const small_b200_layer *L);
