@@ -19,6 +19,10 @@
 // full (a 64-row M costs the same pipe time as 128 rows), an MMA takes N/2 = 16 or 32 cycles, and a
 // thread of the accumulation warps owns one pixel with all its channels: its sums go to the packed
 // output as 64-byte runs without any transposition.  Three threads issue the MMAs there.
+// Variants of the pixel-major kernel (template arguments MERGED, POOL): for 16 / 32 output channels
+// [W_hi | W_lo] is one operand of 2K columns (four MMAs per tap instead of six, TcArgs::merged); layers of
+// one 16-channel block then sum the whole window in tensor memory (TcArgs::row_skip); for 32 / 64 output
+// channels on wide images a following 2x2 stride-2 max pool can run in the epilogue (TcArgs::pool).
 //
 // Implicit GEMM without im2col ("linear shift"):
 //   For one image and one block of 16 input channels, TMA copies a patch of the packed
