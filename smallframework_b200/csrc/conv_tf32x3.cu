@@ -426,7 +426,17 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             uint64_t x_slot_off = 0, w_stage_off = 0;
             SB_TILE_LOOP(ok)
             {
-                const Tile T = decode_tile(a, t);
+                // Of a tile the issuing threads need only its first GEMM column inside the patch and the channels
+                // of its channel tile; 2-D pixel tiles of a layer with one channel tile always start at column 0
+                // with all K channels, and the decode (three integer divisions per tile, for every issuing
+                // thread and every tile, its own or not) is issue time taken from the MMAs.
+                Tile T;
+                if (a.tiled && a.k_tiles == 1)
+                {
+                    T.m_local0 = 0; T.kv = a.K;
+                }
+                else
+                    T = decode_tile(a, t);
                 const uint64_t x_desc0 = x_desc_base + (uint64_t)T.m_local0 * 4;
                 // filter stage: [tap][c/4][kv rows][16 B], kv = channels of this tile
                 const uint64_t w_desc0 = make_smem_desc(smem_u32(sW), (uint32_t)T.kv * 16 * w_rows, 128, 0);
