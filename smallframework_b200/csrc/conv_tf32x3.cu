@@ -56,6 +56,24 @@ using namespace sb;
 constexpr int W_STAGES_MAX = 6; // filter stages, each one group of taps (a kernel row)
 constexpr int X_SLOTS_MAX = 3;
 
+// Division of a non-negative int below 2^31 by a divisor fixed per launch: one multiply-high, an add and a
+// shift instead of the two dozen instructions of a 32-bit division.  Every role decodes a tile per tile and
+// the accumulation warps turn a GEMM column into a pixel with a division by the patch width; these run on the
+// schedulers the MMA-issuing threads need.
+struct FastDiv
+{
+    uint32_t mul, shift;
+    __host__ void set(int d)
+    {
+        uint32_t s = 0;
+        while ((1ull << s) < (unsigned long long)d)
+            ++s;
+        shift = s;
+        mul = (uint32_t)((((1ull << 32) * ((1ull << s) - (unsigned long long)d)) / (unsigned long long)d) + 1);
+    }
+    __device__ __forceinline__ int div(int x) const { return (int)((__umulhi((uint32_t)x, mul) + (uint32_t)x) >> shift); }
+};
+
 struct TcArgs
 {
     int N, C, K, H, W, Ho, Wo, Fh, Fw, pad_t, pad_l;
@@ -106,6 +124,7 @@ struct TcArgs
     // 1: a 2x2 stride-2 max pool follows in the epilogue (pixel-major tiled plans only); the output strides
     // then describe the pooled tensor and `stage_off` locates the exchange rows of the pooling step
     int pool;
+    FastDiv by_px_tiles, by_N, by_tiles_x, by_PW;
 };
 
 // Output channels per CTA, a function of K alone so that filter preparation and the
@@ -198,18 +217,18 @@ __device__ __forceinline__ Tile decode_tile(const TcArgs &a, int t)
     // all 75 MB of filter again: 541 MB of DRAM reads per launch for 126 MB of algorithmic bytes (176 MB
     // now, and the layer 3 % faster).
     Tile T;
-    const int pt = t % a.px_tiles; t /= a.px_tiles;
-    T.n = t % a.N;
-    T.kt = t / a.N;
+    const int t1 = a.by_px_tiles.div(t), pt = t - t1 * a.px_tiles;
+    T.kt = a.by_N.div(t1);
+    T.n = t1 - T.kt * a.N;
     if (!a.tiled)
     {
         const int m0 = pt * a.NPX;
-        T.row_base = m0 / a.PW; T.col_base = 0; T.m_local0 = m0 - T.row_base * a.PW;
+        T.row_base = a.by_PW.div(m0); T.col_base = 0; T.m_local0 = m0 - T.row_base * a.PW;
         T.tw_valid = a.Wo; T.th_valid = a.Ho;
     }
     else
     {
-        const int ty = pt / a.tiles_x, tx = pt - ty * a.tiles_x;
+        const int ty = a.by_tiles_x.div(pt), tx = pt - ty * a.tiles_x;
         T.row_base = ty * a.TH; T.col_base = tx * a.TW; T.m_local0 = 0;
         T.tw_valid = (a.Wo - T.col_base) < a.TW ? (a.Wo - T.col_base) : a.TW; T.th_valid = a.TH;
     }
@@ -684,7 +703,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     // before it and all leave together (see the channel-major epilogue).
                     constexpr int HALF = ACC / 2;
                     const int ml = mt * 128 + quarter * 32 + lane; // tiled plans: m_local0 = 0
-                    const int rl = ml / a.PW, cl = ml - rl * a.PW;
+                    const int rl = a.by_PW.div(ml), cl = ml - rl * a.PW;
                     const int upper = lane & 1;
                     float *xrow = reinterpret_cast<float *>(smem + a.stage_off) +
                                   ((size_t)(rl >> 1) * (a.PW >> 1) + (cl >> 1)) * (ACC + 4) + upper * HALF;
@@ -733,7 +752,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                 else if (ok && active)
                 {
                     const int ml = T.m_local0 + mt * 128 + quarter * 32 + lane;
-                    const int rl = ml / a.PW, cl = ml - rl * a.PW;
+                    const int rl = a.by_PW.div(ml), cl = ml - rl * a.PW;
                     const int r = T.row_base + rl, c = T.col_base + cl;
                     if (cl < T.tw_valid && rl < T.th_valid && r < a.Ho)
                     {
@@ -870,7 +889,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     {
                         const int px = pg * 8 + psub;
                         const int ml = T.m_local0 + px;
-                        const int rl = ml / a.PW, cl = ml - rl * a.PW;
+                        const int rl = a.by_PW.div(ml), cl = ml - rl * a.PW;
                         const int r = T.row_base + rl, c = T.col_base + cl;
                         if (cl < T.tw_valid && rl < T.th_valid && r < a.Ho)
                         {
@@ -945,7 +964,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                         const int s_row = (warp - FIRST_ACC_WARP) * 8 + psub;
                         const int px = (s_row >> 5) * my_cols + piece * 32 + (s_row & 31);
                         const int ml = T.m_local0 + px;
-                        const int rl = ml / a.PW, cl = ml - rl * a.PW;
+                        const int rl = a.by_PW.div(ml), cl = ml - rl * a.PW;
                         const int r = T.row_base + rl, c = T.col_base + cl;
                         if (cl < T.tw_valid && rl < T.th_valid && r < a.Ho)
                         {
@@ -1322,6 +1341,7 @@ int run_tc(const small_b200_layer *L, const small_b200_layer *pool, const float 
     if (tiles > 0x7fffffffLL)
         return fail(SMALL_B200_INVALID_ARGUMENT, "Conv2D<float> (3xTF32) ERROR: too many tiles.");
     a.total_tiles = (int)tiles;
+    a.by_px_tiles.set(a.px_tiles); a.by_N.set(a.N); a.by_tiles_x.set(a.tiled ? a.tiles_x : 1); a.by_PW.set(a.PW);
     long long blocks = tiles;
     if (a.persistent && blocks > num_sms())
         blocks = num_sms();
