@@ -207,6 +207,10 @@ struct Tile
     int tw_valid, th_valid;    // real outputs per patch row / patch rows that hold outputs
 };
 
+// FAST = false keeps the plain divisions: the whole-window instantiations (MERGED == 2) are at the edge of their
+// register budget, and with the multiply-high form the compiler's spill landed in their MMA issue loop
+// (16 -> 32 channels at 208x208: 0.203 -> 0.225 ms), so they divide the slow way.
+template <bool FAST = true>
 __device__ __forceinline__ Tile decode_tile(const TcArgs &a, int t)
 {
     // Pixel tile fastest, then the image, channel tile slowest.  The CTAs that run at the same time then
@@ -217,18 +221,18 @@ __device__ __forceinline__ Tile decode_tile(const TcArgs &a, int t)
     // all 75 MB of filter again: 541 MB of DRAM reads per launch for 126 MB of algorithmic bytes (176 MB
     // now, and the layer 3 % faster).
     Tile T;
-    const int t1 = a.by_px_tiles.div(t), pt = t - t1 * a.px_tiles;
-    T.kt = a.by_N.div(t1);
+    const int t1 = FAST ? a.by_px_tiles.div(t) : t / a.px_tiles, pt = t - t1 * a.px_tiles;
+    T.kt = FAST ? a.by_N.div(t1) : t1 / a.N;
     T.n = t1 - T.kt * a.N;
     if (!a.tiled)
     {
         const int m0 = pt * a.NPX;
-        T.row_base = a.by_PW.div(m0); T.col_base = 0; T.m_local0 = m0 - T.row_base * a.PW;
+        T.row_base = FAST ? a.by_PW.div(m0) : m0 / a.PW; T.col_base = 0; T.m_local0 = m0 - T.row_base * a.PW;
         T.tw_valid = a.Wo; T.th_valid = a.Ho;
     }
     else
     {
-        const int ty = a.by_tiles_x.div(pt), tx = pt - ty * a.tiles_x;
+        const int ty = FAST ? a.by_tiles_x.div(pt) : pt / a.tiles_x, tx = pt - ty * a.tiles_x;
         T.row_base = ty * a.TH; T.col_base = tx * a.TW; T.m_local0 = 0;
         T.tw_valid = (a.Wo - T.col_base) < a.TW ? (a.Wo - T.col_base) : a.TW; T.th_valid = a.TH;
     }
@@ -326,7 +330,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             fence_barrier_init();
             // The first patch and the first filter stage only need their barriers: their round
             // trip to memory overlaps the tensor-memory allocation and the CTA-wide barrier.
-            const Tile T = decode_tile(a, first_tile);
+            const Tile T = decode_tile<MERGED != 2>(a, first_tile);
             issue_patch(T, 0, 0);
             issue_filter(T, 0, 0);
         }
@@ -356,14 +360,14 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             // The patch cursor (p_t, p_cb) walks the same (tile, channel block) sequence as everybody else.
             int pc = 1, gc = 0, q = 0; // pc: patches issued (patch 0 already is), q: patches the groups have entered
             int p_t = first_tile, p_cb = 1;
-            Tile PT = decode_tile(a, p_t); // decoded once per tile (the decode divides)
+            Tile PT = decode_tile<MERGED != 2>(a, p_t); // decoded once per tile (the decode divides)
             auto step_cursor = [&]() {
                 if (p_cb == cbs_l)
                 {
                     p_cb = 0;
                     p_t += tile_step;
                     if (PERSIST && p_t < a.total_tiles)
-                        PT = decode_tile(a, p_t);
+                        PT = decode_tile<MERGED != 2>(a, p_t);
                 }
             };
             step_cursor();
@@ -375,7 +379,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             };
             SB_TILE_LOOP(ok)
             {
-                const Tile T = decode_tile(a, t);
+                const Tile T = decode_tile<MERGED != 2>(a, t);
                 for (int g = 0; g < groups && ok; ++g, ++gc)
                 {
                     if (g % groups_per_cb == 0)
@@ -455,7 +459,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     T.m_local0 = 0; T.kv = a.K;
                 }
                 else
-                    T = decode_tile(a, t);
+                    T = decode_tile<MERGED != 2>(a, t);
                 const uint64_t x_desc0 = x_desc_base + (uint64_t)T.m_local0 * 4;
                 // filter stage: [tap][c/4][kv rows][16 B], kv = channels of this tile
                 const uint64_t w_desc0 = make_smem_desc(smem_u32(sW), (uint32_t)T.kv * 16 * w_rows, 128, 0);
@@ -620,7 +624,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
             int gc = 0;
             SB_TILE_LOOP(ok)
             {
-                const Tile T = decode_tile(a, t);
+                const Tile T = decode_tile<MERGED != 2>(a, t);
                 // the bias seeds the sums (these loads overlap the wait for the first group)
                 constexpr int ACC = MERGED ? 32 : 64; // output channels a thread can hold
                 float acc[ACC];
@@ -703,7 +707,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                     // before it and all leave together (see the channel-major epilogue).
                     constexpr int HALF = ACC / 2;
                     const int ml = mt * 128 + quarter * 32 + lane; // tiled plans: m_local0 = 0
-                    const int rl = a.by_PW.div(ml), cl = ml - rl * a.PW;
+                    const int rl = (MERGED == 2 ? ml / a.PW : a.by_PW.div(ml)), cl = ml - rl * a.PW;
                     const int upper = lane & 1;
                     float *xrow = reinterpret_cast<float *>(smem + a.stage_off) +
                                   ((size_t)(rl >> 1) * (a.PW >> 1) + (cl >> 1)) * (ACC + 4) + upper * HALF;
@@ -752,7 +756,7 @@ conv_tf32x3_kernel(const __grid_constant__ CUtensorMap map_x, const float *__res
                 else if (ok && active)
                 {
                     const int ml = T.m_local0 + mt * 128 + quarter * 32 + lane;
-                    const int rl = a.by_PW.div(ml), cl = ml - rl * a.PW;
+                    const int rl = (MERGED == 2 ? ml / a.PW : a.by_PW.div(ml)), cl = ml - rl * a.PW;
                     const int r = T.row_base + rl, c = T.col_base + cl;
                     if (cl < T.tw_valid && rl < T.th_valid && r < a.Ho)
                     {
